@@ -1,0 +1,16 @@
+"""B200-native EXL3 quantized-linear kernels behind Ampstein's operator boundary.
+
+The package is a thin host layer over libampstein_b200.so (hand-written sm_100a CUDA behind a
+C ABI, see include/ampstein_b200.h). There is no CPU or library fallback: every operator
+raises if the shared library is missing or the tensors are not on a CUDA device.
+"""
+from . import _lib  # noqa: F401
+from .exl3 import (  # noqa: F401
+    exl3_gemm,
+    exl3_gemm_recon,
+    exl3_reconstruct,
+    exl3_reconstruct_had,
+    had_r_128,
+)
+
+__all__ = ["exl3_gemm", "exl3_gemm_recon", "exl3_reconstruct", "exl3_reconstruct_had", "had_r_128"]

@@ -1,0 +1,64 @@
+"""ctypes binding of libampstein_b200.so. Loading is lazy but loud: a missing or stale library
+raises, nothing falls back to another implementation."""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libampstein_b200.so")
+
+_lib = None
+
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+_l = ctypes.c_long
+_f = ctypes.c_float
+
+# name -> argtypes; every entry returns int except where noted. Mirrors include/ampstein_b200.h.
+SIGNATURES = {
+    "amp_b200_version": [],
+    "amp_exl3_reconstruct": [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "amp_exl3_reconstruct_had": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "amp_had_r_128": [_vp, _vp, _vp, _vp, _l, _i, _i, _f, _vp],
+    "amp_exl3_gemv": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "amp_exl3_gemv_cfg": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "amp_exl3_gemv_status": [ctypes.POINTER(ctypes.c_int)],
+    "amp_exl3_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+}
+
+
+class AmpError(RuntimeError):
+    """Raised for every non-zero return code of the C ABI."""
+
+    def __init__(self, fn, rc, msg):
+        super().__init__("%s failed (rc=%d): %s" % (fn, rc, msg))
+        self.rc = rc
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                "ampstein_b200: %s is missing; build it with `python -m ampstein_b200.build` "
+                "(there is no fallback path)" % LIB_PATH)
+        L = ctypes.CDLL(LIB_PATH)
+        for name, args in SIGNATURES.items():
+            fn = getattr(L, name)          # AttributeError here = stale library
+            fn.argtypes = args
+            fn.restype = ctypes.c_int
+        L.amp_b200_last_error.restype = ctypes.c_char_p
+        L.amp_b200_last_error.argtypes = []
+        _lib = L
+    return _lib
+
+
+def last_error():
+    return lib().amp_b200_last_error().decode("utf-8", "replace")
+
+
+def call(name, *args):
+    """Call a C-ABI entry point; raise AmpError on a non-zero return code."""
+    rc = getattr(lib(), name)(*args)
+    if rc != 0:
+        raise AmpError(name, rc, last_error())
+    return rc

@@ -1,0 +1,26 @@
+// Kernel instances of the trellis-decode GEMV for one bitrate; compiled once per K with
+// -DAMP_GEMV_K=<1..8> so the eight translation units build in parallel.
+#include "exl3_gemv_kernel.cuh"
+
+#ifndef AMP_GEMV_K
+#error "compile with -DAMP_GEMV_K=<bits>"
+#endif
+
+#define AMP_CAT_(a, b) a##b
+#define AMP_CAT(a, b) AMP_CAT_(a, b)
+
+namespace amp {
+
+gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB)
+{
+    static const gemv_fn fn[3][2] =
+    {
+        { exl3_gemv_kernel<AMP_GEMV_K, 0, 1>, exl3_gemv_kernel<AMP_GEMV_K, 0, 2> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 1, 1>, exl3_gemv_kernel<AMP_GEMV_K, 1, 2> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 2, 1>, exl3_gemv_kernel<AMP_GEMV_K, 2, 2> },
+    };
+    if (cb < 0 || cb > 2 || MB < 1 || MB > 2) return nullptr;
+    return fn[cb][MB - 1];
+}
+
+}  // namespace amp

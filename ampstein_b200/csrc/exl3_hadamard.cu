@@ -1,0 +1,99 @@
+// Blockwise 128-point Hadamard with optional pre / post scale vectors, as its own launch.
+// Replaces the reference's had_r_128 (vendor/exl3/exllamav3_ext/quant/hadamard.cu:125-207;
+// arithmetic of hadamard_inner.cuh:93-279): fp16 data is scaled in fp16 before the transform,
+// transformed in fp32, multiplied by scale/sqrt(128), rounded once, post-scaled in fp16; fp32
+// data stays fp32 throughout. Works in place.
+#include "exl3_common.cuh"
+#include "host_common.h"
+
+namespace amp {
+
+template <bool F32>
+__global__ __launch_bounds__(256)
+void had_r_128_kernel(const void* __restrict__ in, void* __restrict__ out,
+                      const __half* __restrict__ pre, const __half* __restrict__ post,
+                      long chunks, int chunks_per_row, float r_scale)
+{
+    const int lane = threadIdx.x & 31;
+    const long chunk = (long) blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (chunk >= chunks) return;
+    const int cb = (int) (chunk % chunks_per_row);       // which 128-block of the row
+
+    float h0, h1, h2, h3;
+    if constexpr (F32)
+    {
+        float4 v = reinterpret_cast<const float4*>(in)[chunk * 32 + lane];
+        h0 = v.x; h1 = v.y; h2 = v.z; h3 = v.w;
+        if (pre)
+        {
+            half4 s = reinterpret_cast<const half4*>(pre)[cb * 32 + lane];
+            h0 *= __low2float(s.x); h1 *= __high2float(s.x);
+            h2 *= __low2float(s.y); h3 *= __high2float(s.y);
+        }
+    }
+    else
+    {
+        half4 v = reinterpret_cast<const half4*>(in)[chunk * 32 + lane];
+        if (pre)
+        {
+            half4 s = reinterpret_cast<const half4*>(pre)[cb * 32 + lane];
+            v.x = __hmul2(v.x, s.x);
+            v.y = __hmul2(v.y, s.y);
+        }
+        h0 = __low2float(v.x); h1 = __high2float(v.x);
+        h2 = __low2float(v.y); h3 = __high2float(v.y);
+    }
+
+    warp_had128(h0, h1, h2, h3, lane);
+    h0 *= r_scale; h1 *= r_scale; h2 *= r_scale; h3 *= r_scale;
+
+    if constexpr (F32)
+    {
+        if (post)
+        {
+            half4 s = reinterpret_cast<const half4*>(post)[cb * 32 + lane];
+            h0 *= __low2float(s.x); h1 *= __high2float(s.x);
+            h2 *= __low2float(s.y); h3 *= __high2float(s.y);
+        }
+        reinterpret_cast<float4*>(out)[chunk * 32 + lane] = make_float4(h0, h1, h2, h3);
+    }
+    else
+    {
+        half4 o;
+        o.x = __floats2half2_rn(h0, h1);
+        o.y = __floats2half2_rn(h2, h3);
+        if (post)
+        {
+            half4 s = reinterpret_cast<const half4*>(post)[cb * 32 + lane];
+            o.x = __hmul2(o.x, s.x);
+            o.y = __hmul2(o.y, s.y);
+        }
+        reinterpret_cast<half4*>(out)[chunk * 32 + lane] = o;
+    }
+}
+
+}  // namespace amp
+
+using namespace amp;
+
+// dtype: 0 = fp16 in/out, 1 = fp32 in/out. pre / post: fp16 vectors of `cols` values or null.
+AMP_API int amp_had_r_128(const void* in, void* out, const void* pre, const void* post,
+                             long rows, int cols, int dtype, float scale, cudaStream_t stream)
+{
+    AMP_REQUIRE(dtype == 0 || dtype == 1, "had_r_128: unsupported datatype");
+    AMP_REQUIRE(rows >= 0 && cols >= 0 && cols % 128 == 0, "had_r_128: columns must be divisible by 128");
+    if (rows == 0 || cols == 0) return 0;
+    AMP_REQUIRE(in && out, "had_r_128: null pointer");
+    const uintptr_t amask = dtype ? 15 : 7;
+    AMP_REQUIRE(((uintptr_t) in & amask) == 0 && ((uintptr_t) out & amask) == 0, "had_r_128: misaligned pointer");
+    AMP_REQUIRE(((uintptr_t) pre & 7) == 0 && ((uintptr_t) post & 7) == 0, "had_r_128: misaligned scale vector");
+    const long chunks = rows * (cols / 128);
+    const long blocks = (chunks + 7) / 8;
+    AMP_REQUIRE(blocks <= 0x7fffffffL, "had_r_128: too many rows");
+    const float rs = scale * kRScale;
+    if (dtype)
+        had_r_128_kernel<true><<<(unsigned) blocks, 256, 0, stream>>>(in, out, (const __half*) pre, (const __half*) post, chunks, cols / 128, rs);
+    else
+        had_r_128_kernel<false><<<(unsigned) blocks, 256, 0, stream>>>(in, out, (const __half*) pre, (const __half*) post, chunks, cols / 128, rs);
+    return cuda_rc(cudaGetLastError(), "amp_had_r_128");
+}

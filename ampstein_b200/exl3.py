@@ -1,0 +1,143 @@
+"""Host-side mirror of the operators Ampstein's native module exposes for the EXL3 path
+(reference: src/torch/amp_torch.cpp, handlers torch_exl3_reconstruct :11015-11060,
+torch_exl3_gemm :11250-11293, torch_exl3_gemm_recon :11148-11230). Same argument order, same
+meaning, same error behaviour (bad arguments raise; nothing returns None). Tensors are torch
+CUDA tensors; torch only supplies device memory and the current stream, the work is done by
+libampstein_b200.so.
+"""
+import torch
+
+from . import _lib
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _check_cuda(name, *ts):
+    for t in ts:
+        if not isinstance(t, torch.Tensor):
+            raise TypeError("%s: expected torch tensors" % name)
+        if not t.is_cuda:
+            raise RuntimeError("%s: tensors must live on a CUDA device (no CPU path exists)" % name)
+        if not t.is_contiguous():
+            raise ValueError("%s: tensors must be contiguous" % name)
+
+
+def _cb(mul1, mcg):
+    if mul1 and mcg:
+        raise ValueError("Specified both mcg and mul1")
+    return 2 if mul1 else (1 if mcg else 0)
+
+
+def _trellis_dims(name, trellis):
+    if trellis.dim() != 3:
+        raise ValueError("%s: trellis must be 3-D" % name)
+    if trellis.dtype not in (torch.int16, torch.uint16):
+        raise TypeError("%s: trellis must be int16" % name)
+    w = trellis.shape[2]
+    if w % 16 != 0 or not (1 <= w // 16 <= 8):
+        raise ValueError("%s: unsupported EXL3 bitrate %s (integer 1..8)" % (name, w / 16))
+    return trellis.shape[0] * 16, trellis.shape[1] * 16, w // 16
+
+
+def exl3_reconstruct(unpacked, packed, K, mul1=False, mcg=False):
+    """Dequantize an EXL3 trellis tensor into `unpacked` (fp16 (k, n), in place); returns it.
+    K is the bitrate (packed.shape[-1] / 16)."""
+    _check_cuda("exl3_reconstruct", unpacked, packed)
+    k, n, Kt = _trellis_dims("exl3_reconstruct", packed)
+    if float(K) != float(Kt):
+        raise ValueError("exl3_reconstruct: K=%s does not match the trellis (%d)" % (K, Kt))
+    if unpacked.dtype != torch.float16 or unpacked.dim() != 2:
+        raise TypeError("exl3_reconstruct: unpacked must be 2-D float16")
+    if unpacked.shape[0] != k or unpacked.shape[1] != n:
+        raise ValueError("exl3_reconstruct: unpacked must be (%d, %d)" % (k, n))
+    with torch.cuda.device(packed.device):
+        _lib.call("amp_exl3_reconstruct", unpacked.data_ptr(), packed.data_ptr(), k, n, Kt,
+                  _cb(mul1, mcg), 0, n, _stream(packed))
+    return unpacked
+
+
+def exl3_reconstruct_had(unpacked, packed, suh, svh, K, mul1=False, mcg=False, n_offset=0):
+    """Original-basis weight diag(suh) H W_hat H diag(svh) / 128 for columns
+    [n_offset, n_offset + unpacked.shape[1]); svh is the slice's own vector (reference:
+    reconstruct_had_slice, vendor/exl3/exllamav3_ext/quant/reconstruct.cu:431-503)."""
+    _check_cuda("exl3_reconstruct_had", unpacked, packed, suh, svh)
+    k, n, Kt = _trellis_dims("exl3_reconstruct_had", packed)
+    if float(K) != float(Kt):
+        raise ValueError("exl3_reconstruct_had: K does not match the trellis")
+    if unpacked.dtype != torch.float16 or suh.dtype != torch.float16 or svh.dtype != torch.float16:
+        raise TypeError("exl3_reconstruct_had: unpacked, suh, svh must be float16")
+    if unpacked.dim() != 2 or unpacked.shape[0] != k:
+        raise ValueError("exl3_reconstruct_had: unpacked must have %d rows" % k)
+    if suh.numel() < k or svh.numel() < unpacked.shape[1]:
+        raise ValueError("reconstruct_had: suh / svh size")
+    with torch.cuda.device(packed.device):
+        _lib.call("amp_exl3_reconstruct_had", unpacked.data_ptr(), packed.data_ptr(), suh.data_ptr(),
+                  svh.data_ptr(), k, n, Kt, _cb(mul1, mcg), int(n_offset), unpacked.shape[1],
+                  _stream(packed))
+    return unpacked
+
+
+def had_r_128(input, output, pre_scale=None, post_scale=None, scale=1.0):
+    """output = blockwise H128(input [* pre_scale]) * scale / sqrt(128) [* post_scale]; fp16 or
+    fp32, may run in place (reference: had_r_128, .../quant/hadamard.cu:125-207)."""
+    ts = [input, output] + [t for t in (pre_scale, post_scale) if t is not None]
+    _check_cuda("had_r_128", *ts)
+    if input.shape != output.shape or input.dim() != 2:
+        raise ValueError("had_r_128: input and output must be 2-D and of one shape")
+    if input.dtype != output.dtype or input.dtype not in (torch.float16, torch.float32):
+        raise TypeError("had_r_128: unsupported datatype")
+    rows, cols = input.shape
+    if cols % 128:
+        raise ValueError("had_r_128: columns must be divisible by 128")
+    for s in (pre_scale, post_scale):
+        if s is not None and (s.dtype != torch.float16 or s.numel() < cols):
+            raise ValueError("had_r_128: scale vectors must be float16 with one value per column")
+    with torch.cuda.device(input.device):
+        _lib.call("amp_had_r_128", input.data_ptr(), output.data_ptr(),
+                  pre_scale.data_ptr() if pre_scale is not None else None,
+                  post_scale.data_ptr() if post_scale is not None else None,
+                  rows, cols, 1 if input.dtype == torch.float32 else 0, float(scale), _stream(input))
+    return output
+
+
+def exl3_gemm(A, B, C, suh, svh, mul1=False, mcg=False):
+    """C = had(A * suh) @ dequant(B) -> had(.) * svh, written in place; returns C.
+    A (m, k) fp16, B trellis (k/16, n/16, 16K) int16, C (m, n) fp16 or fp32, suh (k), svh (n).
+    Both scale vectors are required (reference: torch_exl3_gemm)."""
+    if suh is None or svh is None:
+        raise TypeError("expected (A, B, C, suh, svh, mul1?, mcg?)")
+    _check_cuda("exl3_gemm", A, B, C, suh, svh)
+    k, n, K = _trellis_dims("exl3_gemm", B)
+    if A.dtype != torch.float16 or suh.dtype != torch.float16 or svh.dtype != torch.float16:
+        raise TypeError("exl3_gemm: A, suh, svh must be float16")
+    if C.dtype not in (torch.float16, torch.float32):
+        raise TypeError("exl3_gemm: C must be float16 or float32")
+    if A.shape[-1] != k or C.shape[-1] != n:
+        raise ValueError("exl3_gemm: incompatible shapes (A %s, weight %d x %d, C %s)"
+                         % (tuple(A.shape), k, n, tuple(C.shape)))
+    m = A.numel() // k
+    if C.numel() != m * n or suh.numel() != k or svh.numel() != n:
+        raise ValueError("exl3_gemm: incompatible shapes")
+    if m == 0:
+        return C
+    with torch.cuda.device(A.device):
+        _lib.call("amp_exl3_gemm", A.data_ptr(), B.data_ptr(), C.data_ptr(), suh.data_ptr(), None,
+                  svh.data_ptr(), m, k, n, K, _cb(mul1, mcg), 1 if C.dtype == torch.float32 else 0,
+                  _stream(A))
+    return C
+
+
+def exl3_gemm_recon(x, trellis, suh, svh, K, mul1=False, mcg=False):
+    """EXL3 matmul for many rows (prefill); returns a new (rows, n) fp16 tensor
+    (reference: torch_exl3_gemm_recon)."""
+    _check_cuda("exl3_gemm_recon", x, trellis, suh, svh)
+    k, n, Kt = _trellis_dims("exl3_gemm_recon", trellis)
+    if x.dim() != 2 or x.shape[1] != k or suh.numel() != k or svh.numel() != n or n > 32768:
+        raise ValueError("exl3_gemm_recon: incompatible shapes (x %s, weight %d x %d)"
+                         % (tuple(x.shape), k, n))
+    if float(K) != float(Kt):
+        raise ValueError("exl3_gemm_recon: K does not match the trellis")
+    y = torch.empty((x.shape[0], n), dtype=torch.float16, device=x.device)
+    return exl3_gemm(x, trellis, y, suh, svh, mul1, mcg)

@@ -1,0 +1,106 @@
+/*
+ * ampstein_b200 -- C ABI of the B200-native EXL3 quantized-linear path.
+ *
+ * This is the drop-in boundary: plain pointers and sizes, no C++ or torch types. Every entry
+ * point launches on the given stream of the CURRENT device and returns immediately; none
+ * synchronises, allocates or frees device memory unless its comment says so, which keeps
+ * them capturable in CUDA graphs once warmed up.
+ *
+ * Return codes (the convention of the reference's own launchers,
+ * src/torch/amp_torch.cpp:238-256): 0 = launched; negative = bad argument / unsupported
+ * configuration (text in amp_b200_last_error()); positive = a cudaError_t.
+ *
+ * "Reference" citations below are paths inside the jow-/ampstein tree; Q/ abbreviates
+ * vendor/exl3/exllamav3_ext/quant/.
+ *
+ * Data layout shared by all entry points:
+ *   trellis  int16/uint16 (k/16, n/16, 16*K): one 16x16 tile = 256*K bits, K = 1..8
+ *   suh      fp16 (k) input sign/scale vector,  svh  fp16 (n) output sign/scale vector
+ *   cb       codebook: 0 = default ("3INST"), 1 = mcg, 2 = mul1
+ *   the linear is  C = had128(A * suh) @ W_hat  ->  had128(.) * svh,   W_hat = decoded tiles (k, n)
+ */
+#ifndef AMPSTEIN_B200_H
+#define AMPSTEIN_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef __CUDA_RUNTIME_API_H__
+typedef struct CUstream_st* cudaStream_t;
+#endif
+
+/* Library version (bumped on ABI changes). */
+int amp_b200_version(void);
+
+/* Text of the last error reported on the calling thread ("" when none). */
+const char* amp_b200_last_error(void);
+
+/*
+ * Dequantize a trellis into fp16 W_hat (rotated basis). Bit-exact with the reference.
+ * Replaces: reconstruct / reconstruct_slice, Q/reconstruct.cu:141-197, 512-523
+ *           (binding torch.exl3_reconstruct, src/torch/amp_torch.cpp:11015-11060).
+ * unpacked: fp16 (k, n_out) receiving columns [n_offset, n_offset + n_out) of the (k, n) weight.
+ * n_out and n_offset multiples of 128, k a multiple of 16. Empty tensors are a no-op.
+ */
+int amp_exl3_reconstruct(void* unpacked, const void* trellis, int k, int n, int K, int cb,
+                         int n_offset, int n_out, cudaStream_t stream);
+
+/*
+ * Dequantize into the ORIGINAL basis: diag(suh) . H128 . W_hat . H128 . diag(svh) / 128, with
+ * the reference's per-element operation order (bit-exact with it).
+ * Replaces: reconstruct_had_slice, Q/reconstruct.cu:431-503.
+ * k, n_out, n_offset multiples of 128; svh points at the slice's first column.
+ */
+int amp_exl3_reconstruct_had(void* unpacked, const void* trellis, const void* suh, const void* svh,
+                             int k, int n, int K, int cb, int n_offset, int n_out,
+                             cudaStream_t stream);
+
+/*
+ * Blockwise 128-point Hadamard of a (rows, cols) matrix, out = H(in [* pre]) * scale/sqrt(128)
+ * [* post]; in place allowed. dtype 0 = fp16, 1 = fp32. pre / post: fp16 (cols) or NULL.
+ * Replaces: had_r_128, Q/hadamard.cu:125-207.
+ */
+int amp_had_r_128(const void* in, void* out, const void* pre, const void* post,
+                  long rows, int cols, int dtype, float scale, cudaStream_t stream);
+
+/*
+ * EXL3 linear, any m: C (m, n) fp16 (c_fp32 = 0) or fp32 (c_fp32 = 1) = A (m, k) fp16 through
+ * the quantized weight. suh and svh are required. A_had is the reference's scratch argument
+ * (same size as A); it is accepted and not used. k and n multiples of 128.
+ * Replaces: exl3_gemm, Q/exl3_gemm.cu:114-349 (binding torch.exl3_gemm,
+ * src/torch/amp_torch.cpp:11250-11293), including its GEMV dispatch Q/exl3_gemv.cu:92-184.
+ */
+int amp_exl3_gemm(const void* A, const void* trellis, void* C, const void* suh, void* A_had,
+                  const void* svh, int m, int k, int n, int K, int cb, int c_fp32,
+                  cudaStream_t stream);
+
+/*
+ * The decode-batch kernel on its own, m = 1..16.
+ * Replaces: exl3_gemv_kernel / exl3_gemv_try_launch, Q/exl3_gemv_kernel.cuh:186-482,
+ * Q/exl3_gemv.cu:92-184.
+ */
+int amp_exl3_gemv(const void* x, const void* trellis, void* c, const void* suh, const void* svh,
+                  int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream);
+
+/*
+ * Same with a fixed k-split (cluster size, 1..8) and ring depth (1..4); 0 = choose. The
+ * counterpart of the reference's force_shape_idx / force_num_sms arguments
+ * (Q/exl3_gemm.cu:114-127), used by tuning and tests.
+ */
+int amp_exl3_gemv_cfg(const void* x, const void* trellis, void* c, const void* suh, const void* svh,
+                      int m, int k, int n, int K, int cb, int c_fp32, int split, int stages,
+                      cudaStream_t stream);
+
+/*
+ * Reads and clears the current device's GEMV status word: non-zero after a bounded wait inside
+ * a kernel ran out (the kernel then returns without finishing its tile instead of spinning;
+ * the reference traps). Synchronises; for tests and diagnostics, not for the hot path.
+ */
+int amp_exl3_gemv_status(int* out);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* AMPSTEIN_B200_H */

@@ -1,0 +1,186 @@
+"""ctypes/numpy front end of oracle/libexl3_oracle.so (the CPU restatement of the reference's
+EXL3 arithmetic). TEST INFRASTRUCTURE ONLY: used by tests/, __graft_entry__.smoke() and the
+CPU-baseline legs of bench.py as the checker; the package never imports it.
+
+fp16 data is exchanged as numpy float16 arrays; trellis tensors as uint16 (or int16) arrays of
+shape (k/16, n/16, 16*K), exactly the on-disk layout the reference loads
+(src/ucode/ampstein/models.uc:9-15).
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+_u16p = ctypes.POINTER(ctypes.c_uint16)
+_f32p = ctypes.POINTER(ctypes.c_float)
+
+
+def build(force=False):
+    """Compile the C restatement with the Makefile beside it."""
+    so = os.path.join(_HERE, "libexl3_oracle.so")
+    src = os.path.join(_HERE, "exl3_oracle.c")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "-B", "libexl3_oracle.so"])
+    return so
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        _LIB = ctypes.CDLL(build())
+        _LIB.exl3o_h2f.restype = ctypes.c_float
+        _LIB.exl3o_h2f.argtypes = [ctypes.c_uint16]
+        _LIB.exl3o_f2h.restype = ctypes.c_uint16
+        _LIB.exl3o_f2h.argtypes = [ctypes.c_float]
+        _LIB.exl3o_d2h.restype = ctypes.c_uint16
+        _LIB.exl3o_d2h.argtypes = [ctypes.c_double]
+        _LIB.exl3o_decode_state.restype = ctypes.c_uint16
+        _LIB.exl3o_decode_state.argtypes = [ctypes.c_uint32, ctypes.c_int]
+    return _LIB
+
+
+def _p16(a):
+    return a.ctypes.data_as(_u16p)
+
+
+def _p32(a):
+    return a.ctypes.data_as(_f32p)
+
+
+def _h(a):
+    """contiguous uint16 view of an fp16 / uint16 / int16 array"""
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.float16 or a.dtype == np.int16:
+        return a.view(np.uint16)
+    assert a.dtype == np.uint16, a.dtype
+    return a
+
+
+def trellis_dims(trellis):
+    tk, tn, w = trellis.shape
+    assert w % 16 == 0
+    return tk * 16, tn * 16, w // 16
+
+
+def decode_table(cb):
+    """fp16 value of every 16-bit state (65536 entries)."""
+    L = lib()
+    out = np.empty(65536, np.uint16)
+    for s in range(65536):
+        out[s] = L.exl3o_decode_state(s, cb)
+    return out.view(np.float16)
+
+
+def tile_states(tile, K):
+    t = _h(tile).reshape(-1)
+    assert t.size == 16 * K
+    out = np.empty(256, np.uint16)
+    lib().exl3o_tile_states(_p16(t), K, _p16(out))
+    return out
+
+
+def pack_tile(codes, K):
+    c = np.ascontiguousarray(codes, dtype=np.uint16)
+    out = np.zeros(16 * K, np.uint16)
+    lib().exl3o_pack_tile(_p16(c), K, _p16(out))
+    return out
+
+
+def tile_pos(t):
+    r, c = ctypes.c_int(), ctypes.c_int()
+    lib().exl3o_tile_pos(t, ctypes.byref(r), ctypes.byref(c))
+    return r.value, c.value
+
+
+def reconstruct(trellis, cb=0):
+    t = _h(trellis)
+    k, n, K = trellis_dims(t)
+    out = np.empty((k, n), np.uint16)
+    rc = lib().exl3o_reconstruct(_p16(t), k, n, K, cb, _p16(out))
+    assert rc == 0, rc
+    return out.view(np.float16)
+
+
+def reconstruct_had(trellis, suh, svh, cb=0):
+    t = _h(trellis)
+    k, n, K = trellis_dims(t)
+    out = np.empty((k, n), np.uint16)
+    rc = lib().exl3o_reconstruct_had(_p16(t), _p16(_h(suh)), _p16(_h(svh)), k, n, K, cb, _p16(out))
+    assert rc == 0, rc
+    return out.view(np.float16)
+
+
+def had_hf(x, pre=None, post=None, scale=1.0):
+    xx = _h(x)
+    rows, cols = xx.shape
+    out = np.empty_like(xx)
+    lib().exl3o_had_hf(_p16(xx), _p16(out), rows, cols,
+                       _p16(_h(pre)) if pre is not None else None,
+                       _p16(_h(post)) if post is not None else None, ctypes.c_float(scale))
+    return out.view(np.float16)
+
+
+def had_fh(x, post=None, scale=1.0):
+    xx = np.ascontiguousarray(x, dtype=np.float32)
+    rows, cols = xx.shape
+    out = np.empty((rows, cols), np.uint16)
+    lib().exl3o_had_fh(_p32(xx), _p16(out), rows, cols,
+                       _p16(_h(post)) if post is not None else None, ctypes.c_float(scale))
+    return out.view(np.float16)
+
+
+def had_ff(x, post=None, scale=1.0):
+    xx = np.ascontiguousarray(x, dtype=np.float32)
+    rows, cols = xx.shape
+    out = np.empty((rows, cols), np.float32)
+    lib().exl3o_had_ff(_p32(xx), _p32(out), rows, cols,
+                       _p16(_h(post)) if post is not None else None, ctypes.c_float(scale))
+    return out
+
+
+def linear(x, trellis, suh, svh, cb=0, fp32_out=False, what=None):
+    """y = had(x*suh) @ W_hat -> had(.)*svh with fp32 accumulation (the reference's
+    reconstruct-then-matmul semantics). Returns fp16 (m,n), or fp32 when fp32_out."""
+    xx = _h(x)
+    m, k = xx.shape
+    t = _h(trellis)
+    kk, n, K = trellis_dims(t)
+    assert kk == k
+    o16 = np.empty((m, n), np.uint16)
+    o32 = np.empty((m, n), np.float32)
+    if what is None:
+        rc = lib().exl3o_linear(_p16(xx), _p16(t), _p16(_h(suh)), _p16(_h(svh)), m, k, n, K, cb,
+                                _p16(o16), _p32(o32))
+    else:
+        rc = lib().exl3o_linear_w(_p16(xx), _p16(_h(what)), _p16(_h(suh)), _p16(_h(svh)), m, k, n,
+                                  _p16(o16), _p32(o32))
+    assert rc == 0, rc
+    return o32 if fp32_out else o16.view(np.float16)
+
+
+def matmul_f32(a, w):
+    aa, ww = _h(a), _h(w)
+    m, k = aa.shape
+    k2, n = ww.shape
+    assert k == k2
+    y = np.empty((m, n), np.float32)
+    rc = lib().exl3o_matmul_f32(_p16(aa), _p16(ww), m, k, n, _p32(y))
+    assert rc == 0, rc
+    return y
+
+
+def allreduce_fp16(parts):
+    ps = [_h(p).reshape(-1) for p in parts]
+    n = ps[0].size
+    arr = (_u16p * len(ps))(*[_p16(p) for p in ps])
+    out = np.empty(n, np.uint16)
+    lib().exl3o_allreduce_fp16(arr, len(ps), ctypes.c_long(n), _p16(out))
+    return out.view(np.float16)
+
+
+def num_threads():
+    return lib().exl3o_num_threads()

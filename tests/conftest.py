@@ -1,0 +1,31 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+def make_linear(k, n, K, seed, m=1):
+    """Seeded synthetic EXL3 linear: uniform random trellis words (every bit pattern is a valid
+    stream), +-1 sign vectors, N(0,1) activations."""
+    rng = np.random.default_rng(seed)
+    trellis = rng.integers(0, 65536, size=(k // 16, n // 16, 16 * K), dtype=np.uint16)
+    suh = rng.choice(np.array([-1.0, 1.0], np.float16), size=k)
+    svh = rng.choice(np.array([-1.0, 1.0], np.float16), size=n)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    return trellis, suh, svh, x
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    from oracle import exl3_oracle
+    exl3_oracle.lib()
+    return exl3_oracle

@@ -1,0 +1,214 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle on identical
+seeded inputs. Decoded weights and Hadamard outputs must be bit-exact; linear outputs within
+max relative error 1e-2 of the fp32-accumulated reference (the tolerance of the specification;
+measured errors are ~5e-4, fp16 output rounding)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from conftest import make_linear
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+MAX_REL = 1e-2       # max |y - ref| / max |ref|
+REL_RMS = 2e-3
+
+
+def dev(a):
+    if a.dtype == np.uint16:
+        a = a.view(np.int16)
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host16(t):
+    return t.cpu().numpy().view(np.uint16)
+
+
+def check_close(got, ref):
+    got, ref = got.astype(np.float64), ref.astype(np.float64)
+    assert np.all(np.isfinite(got))
+    max_rel = np.max(np.abs(got - ref)) / np.max(np.abs(ref))
+    rms = np.sqrt(np.mean((got - ref) ** 2) / np.mean(ref ** 2))
+    assert max_rel < MAX_REL and rms < REL_RMS, (max_rel, rms)
+    return max_rel, rms
+
+
+@pytest.fixture(scope="module")
+def amp():
+    import ampstein_b200
+    from ampstein_b200 import _lib
+    _lib.lib()
+    return ampstein_b200
+
+
+@pytest.mark.parametrize("cb", [0, 1, 2])
+@pytest.mark.parametrize("K", range(1, 9))
+def test_reconstruct_bit_exact(amp, oracle, K, cb):
+    trellis, _, _, _ = make_linear(64, 256, K, seed=1000 + 10 * K + cb)
+    out = torch.empty((64, 256), dtype=torch.float16, device="cuda")
+    amp.exl3_reconstruct(out, dev(trellis), K, mul1=(cb == 2), mcg=(cb == 1))
+    assert np.array_equal(host16(out), oracle.reconstruct(trellis, cb).view(np.uint16))
+
+
+def test_reconstruct_4096_bit_exact_and_slices(amp, oracle):
+    trellis, _, _, _ = make_linear(4096, 4096, 4, seed=0)
+    t = dev(trellis)
+    out = torch.empty((4096, 4096), dtype=torch.float16, device="cuda")
+    amp.exl3_reconstruct(out, t, 4)
+    ref = oracle.reconstruct(trellis, 0).view(np.uint16)
+    assert np.array_equal(host16(out), ref)
+    # column slice through the C ABI (reconstruct_slice semantics)
+    from ampstein_b200 import _lib
+    sl = torch.empty((4096, 256), dtype=torch.float16, device="cuda")
+    _lib.call("amp_exl3_reconstruct", sl.data_ptr(), t.data_ptr(), 4096, 4096, 4, 0, 1024, 256,
+              torch.cuda.current_stream().cuda_stream)
+    assert np.array_equal(host16(sl), ref[:, 1024:1280])
+
+
+@pytest.mark.parametrize("K,cb", [(1, 0), (3, 2), (4, 0), (5, 1), (6, 0), (8, 2)])
+def test_reconstruct_had_bit_exact(amp, oracle, K, cb):
+    trellis, suh, svh, _ = make_linear(256, 384, K, seed=2000 + K)
+    rng = np.random.default_rng(K)
+    suh = (suh.astype(np.float32) * rng.uniform(0.5, 2.0, suh.shape)).astype(np.float16)
+    out = torch.empty((256, 384), dtype=torch.float16, device="cuda")
+    amp.exl3_reconstruct_had(out, dev(trellis), dev(suh), dev(svh), K, mul1=(cb == 2), mcg=(cb == 1))
+    ref = oracle.reconstruct_had(trellis, suh, svh, cb).view(np.uint16)
+    assert np.array_equal(host16(out), ref)
+    # slice: columns 128..383 with the slice's own svh
+    sl = torch.empty((256, 256), dtype=torch.float16, device="cuda")
+    amp.exl3_reconstruct_had(sl, dev(trellis), dev(suh), dev(svh[128:]), K, mul1=(cb == 2), mcg=(cb == 1), n_offset=128)
+    assert np.array_equal(host16(sl), ref[:, 128:])
+
+
+def test_had_r_128_bit_exact(amp, oracle):
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((37, 512)).astype(np.float16)
+    pre = rng.choice(np.array([-1.0, 1.0], np.float16), 512)
+    post = (rng.uniform(0.5, 2, 512)).astype(np.float16)
+    for kw in ({"pre": pre}, {"post": post}, {}, {"pre": pre, "post": post}):
+        out = torch.empty((37, 512), dtype=torch.float16, device="cuda")
+        amp.had_r_128(dev(x), out, dev(kw["pre"]) if "pre" in kw else None,
+                      dev(kw["post"]) if "post" in kw else None)
+        assert np.array_equal(host16(out), oracle.had_hf(x, **kw).view(np.uint16)), kw
+    xf = rng.standard_normal((5, 256)).astype(np.float32)
+    outf = torch.empty((5, 256), dtype=torch.float32, device="cuda")
+    amp.had_r_128(dev(xf), outf, None, dev(post[:256]))
+    assert np.array_equal(outf.cpu().numpy(), oracle.had_ff(xf, post=post[:256]))
+    # in place
+    t = dev(x)
+    amp.had_r_128(t, t, dev(pre), None)
+    assert np.array_equal(host16(t), oracle.had_hf(x, pre=pre).view(np.uint16))
+
+
+def run_gemm(amp, trellis, suh, svh, x, cb, fp32=False, split=0, stages=0):
+    from ampstein_b200 import _lib
+    m, k = x.shape
+    n = trellis.shape[1] * 16
+    K = trellis.shape[2] // 16
+    out = torch.full((m, n), float("nan"), dtype=torch.float32 if fp32 else torch.float16, device="cuda")
+    t, s, v, xx = dev(trellis), dev(suh), dev(svh), dev(x)
+    if split or stages:
+        _lib.call("amp_exl3_gemv_cfg", xx.data_ptr(), t.data_ptr(), out.data_ptr(), s.data_ptr(), v.data_ptr(),
+                  m, k, n, K, cb, int(fp32), split, stages, torch.cuda.current_stream().cuda_stream)
+    else:
+        amp.exl3_gemm(xx, t, out, s, v, mul1=(cb == 2), mcg=(cb == 1))
+    torch.cuda.synchronize()
+    st = ctypes.c_int(-1)
+    _lib.call("amp_exl3_gemv_status", ctypes.byref(st))
+    assert st.value == 0, "a bounded wait ran out inside the kernel"
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("cb", [0, 1, 2])
+@pytest.mark.parametrize("K", range(1, 9))
+def test_gemv_all_bitrates(amp, oracle, K, cb):
+    trellis, suh, svh, x = make_linear(512, 256, K, seed=3000 + 10 * K + cb, m=3)
+    got = run_gemm(amp, trellis, suh, svh, x, cb)
+    check_close(got, oracle.linear(x, trellis, suh, svh, cb, fp32_out=True))
+
+
+@pytest.mark.parametrize("m", [1, 2, 7, 8, 9, 16])
+def test_gemv_batch_sizes(amp, oracle, m):
+    trellis, suh, svh, x = make_linear(1024, 384, 4, seed=4000 + m, m=m)
+    ref = oracle.linear(x, trellis, suh, svh, 0, fp32_out=True)
+    check_close(run_gemm(amp, trellis, suh, svh, x, 0), ref)
+    check_close(run_gemm(amp, trellis, suh, svh, x, 0, fp32=True), ref)
+
+
+@pytest.mark.parametrize("split,stages", [(1, 1), (1, 3), (2, 2), (3, 2), (5, 1), (8, 2), (8, 4)])
+def test_gemv_splits_and_ring_depths(amp, oracle, split, stages):
+    # k = 2304 = 18 blocks of 128: ragged over 5 and 8 splits, more than one 1024-row chunk
+    trellis, suh, svh, x = make_linear(2304, 256, 4, seed=5000, m=2)
+    ref = oracle.linear(x, trellis, suh, svh, 0, fp32_out=True)
+    check_close(run_gemm(amp, trellis, suh, svh, x, 0, split=split, stages=stages), ref)
+
+
+def test_gemv_split_larger_than_blocks(amp, oracle):
+    trellis, suh, svh, x = make_linear(256, 128, 5, seed=5100, m=1)
+    ref = oracle.linear(x, trellis, suh, svh, 0, fp32_out=True)
+    check_close(run_gemm(amp, trellis, suh, svh, x, 0, split=8, stages=2), ref)
+
+
+def test_config1_single_layer_4096(amp, oracle):
+    """in = out = 4096, K = 4, batch 1, +-1 sign vectors (the reference's CPU-runnable case)."""
+    trellis, suh, svh, x = make_linear(4096, 4096, 4, seed=0, m=1)
+    ref = oracle.linear(x, trellis, suh, svh, 0, fp32_out=True)
+    check_close(run_gemm(amp, trellis, suh, svh, x, 0), ref)
+
+
+@pytest.mark.parametrize("k,n,K", [(4096, 1024, 4), (4096, 14336, 4), (14336, 4096, 4), (4096, 2048, 6), (5120, 6144, 5)])
+def test_llama_shapes(amp, oracle, k, n, K):
+    trellis, suh, svh, x = make_linear(k, n, K, seed=k + n + K, m=1)
+    ref = oracle.linear(x, trellis, suh, svh, 0, fp32_out=True)
+    check_close(run_gemm(amp, trellis, suh, svh, x, 0), ref)
+
+
+def test_gemm_more_than_16_rows(amp, oracle):
+    trellis, suh, svh, x = make_linear(256, 256, 3, seed=6000, m=37)
+    ref = oracle.linear(x, trellis, suh, svh, 1, fp32_out=True)
+    check_close(run_gemm(amp, trellis, suh, svh, x, 1), ref)
+    # the many-rows operator of the reference (exl3_gemm_recon) returns a new tensor
+    y = amp.exl3_gemm_recon(dev(x), dev(trellis), dev(suh), dev(svh), 3, mcg=True)
+    check_close(y.cpu().numpy(), ref)
+
+
+def test_linearity_and_determinism_at_full_size(amp):
+    """Size-independent properties at the benchmark's shapes: exact scaling by two, bitwise
+    reproducibility across launches."""
+    trellis, suh, svh, x = make_linear(4096, 14336, 4, seed=77, m=4)
+    a = run_gemm(amp, trellis, suh, svh, x, 0, fp32=True)
+    b = run_gemm(amp, trellis, suh, svh, x, 0, fp32=True)
+    assert np.array_equal(a, b)
+    c = run_gemm(amp, trellis, suh, svh, (x * np.float16(2)), 0, fp32=True)
+    assert np.array_equal(c, 2.0 * a)
+
+
+def test_reference_kernels_agree_when_built(amp, oracle):
+    """When the reference's own reconstruct / Hadamard kernels were compiled (oracle/_ref), run
+    them on the same inputs: bit-exact three ways (reference, oracle, this library)."""
+    import os
+    from conftest import ROOT
+    so = os.path.join(ROOT, "oracle", "_ref", "libexl3_ref.so")
+    if not os.path.exists(so):
+        pytest.skip("reference kernels not built")
+    R = ctypes.CDLL(so)
+    for K, cb in [(2, 1), (4, 0), (6, 2)]:
+        trellis, suh, svh, x = make_linear(256, 256, K, seed=8000 + K, m=4)
+        t = dev(trellis)
+        ref = torch.empty((256, 256), dtype=torch.float16, device="cuda")
+        assert R.ref_reconstruct(ctypes.c_void_p(ref.data_ptr()), ctypes.c_void_p(t.data_ptr()), 256, 256, K, cb, 0) == 0
+        mine = torch.empty_like(ref)
+        amp.exl3_reconstruct(mine, t, K, mul1=(cb == 2), mcg=(cb == 1))
+        torch.cuda.synchronize()
+        assert np.array_equal(host16(ref), host16(mine))
+        assert np.array_equal(host16(ref), oracle.reconstruct(trellis, cb).view(np.uint16))
+        refh = torch.empty_like(ref)
+        assert R.ref_reconstruct_had(ctypes.c_void_p(refh.data_ptr()), ctypes.c_void_p(t.data_ptr()),
+                                     ctypes.c_void_p(dev(suh).data_ptr()), ctypes.c_void_p(dev(svh).data_ptr()),
+                                     256, 256, K, cb, 0) == 0
+        mineh = torch.empty_like(ref)
+        amp.exl3_reconstruct_had(mineh, t, dev(suh), dev(svh), K, mul1=(cb == 2), mcg=(cb == 1))
+        torch.cuda.synchronize()
+        assert np.array_equal(host16(refh), host16(mineh))
