@@ -28,8 +28,12 @@ def main(out_dir):
     os.makedirs(out_dir, exist_ok=True)
     rng = np.random.default_rng(20240)
 
+    keep = []      # device tensors stay referenced until their kernels have run
+
     def cuda(a):
-        return torch.from_numpy(np.ascontiguousarray(a.view(np.int16) if a.dtype == np.uint16 else a)).cuda()
+        t = torch.from_numpy(np.ascontiguousarray(a.view(np.int16) if a.dtype == np.uint16 else a)).cuda()
+        keep.append(t)
+        return t
 
     # reconstruct: every bitrate and codebook, one 32 x 128 slab each (4 KB of fp16 per case)
     for cb in range(3):
