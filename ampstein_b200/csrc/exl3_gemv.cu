@@ -42,9 +42,10 @@ static gemv_fn gemv_kernel_for(int K, int cb, int MB)
     return nullptr;
 }
 
-// k-split (= cluster size along y): fewest "waves x per-CTA work", where a wave is what the
-// device holds at once and per-CTA work is its rows plus a fixed prologue/epilogue cost
-static int choose_split(int k, int n, int slots)
+// k-split (= cluster size along y). CTAs spread round-robin over the SMs; an SM's time is the
+// rows it decodes divided by its issue efficiency, which is poor with a single resident CTA
+// (8 warps). Pick the split whose busiest SM finishes first.
+static int choose_split(int k, int n, int sms, int ctas_per_sm)
 {
     const int nb = n / 128, B2 = k / 128;
     int best = 1;
@@ -53,9 +54,10 @@ static int choose_split(int k, int n, int slots)
     {
         if (S > B2) break;
         const long ctas = (long) nb * S;
-        const long waves = (ctas + slots - 1) / slots;
+        const long per_sm = (ctas + sms - 1) / sms;                   // CTAs on the busiest SM
         const int rows = ((B2 + S - 1) / S) * 128;
-        const double cost = (double) waves * (rows + 384.0);
+        const double eff = (per_sm >= 2 && ctas_per_sm >= 2) ? 1.0 : 0.7;
+        const double cost = (double) per_sm * (rows + 256.0) / eff;
         if (cost < best_cost - 1e-9) { best_cost = cost; best = S; }
     }
     return best;
@@ -84,21 +86,19 @@ int launch_gemv(const void* x, const void* trellis, void* c, const void* suh, co
     gemv_fn fn = gemv_kernel_for(K, cb, MB);
     if (!fn) return fail(AMP_E_UNSUPPORTED, "exl3_gemv: no kernel for K=%d cb=%d", K, cb);
 
-    // ring depth: deepest that still lets two CTAs share an SM (MB == 1), else what fits
-    int stages = force_stages > 0 ? force_stages : 0;
-    if (!stages)
-    {
-        const int budget = (MB == 1) ? (D.smem_optin > 0 ? (D.smem_optin + 1024) / 2 - 1024 : 100 * 1024) : D.smem_optin;
-        stages = GEMV_MAX_STAGES;
-        while (stages > 1 && gemv_smem_layout(K, MB, stages).total > budget) --stages;
-        if (stages > 3) stages = 3;
-    }
+    // ring depth: two stages per warp cover the refill latency; fall back to one if that is all
+    // that fits. CTAs per SM follow from shared memory (registers allow two for m <= 8).
+    int stages = force_stages > 0 ? force_stages : 2;
+    while (stages > 1 && gemv_smem_layout(K, m, stages).total > D.smem_optin) --stages;
     AMP_REQUIRE(stages >= 1 && stages <= GEMV_MAX_STAGES, "exl3_gemv: stages out of range");
-    const GemvSmem L = gemv_smem_layout(K, MB, stages);
+    const GemvSmem L = gemv_smem_layout(K, m, stages);
     AMP_REQUIRE(L.total <= D.smem_optin, "exl3_gemv: shared memory layout does not fit (%d bytes)", L.total);
-    const int ctas_per_sm = (MB == 1 && 2 * (L.total + 1024) <= D.smem_optin + 2048) ? 2 : 1;
+    const int smem_per_sm = D.smem_optin + 1024;                       // opt-in limit excludes 1 KB per CTA
+    int ctas_per_sm = smem_per_sm / (L.total + 1024);
+    if (ctas_per_sm > (MB == 1 ? 2 : 1)) ctas_per_sm = (MB == 1 ? 2 : 1);
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
 
-    int S = force_split > 0 ? force_split : choose_split(k, n, D.sms * ctas_per_sm);
+    int S = force_split > 0 ? force_split : choose_split(k, n, D.sms, ctas_per_sm);
     AMP_REQUIRE(S >= 1 && S <= 8, "exl3_gemv: split out of range");
 
     if (cudaError_t e = ensure_smem(fn, L.total, dev)) return cuda_rc(e, "exl3_gemv smem attribute");

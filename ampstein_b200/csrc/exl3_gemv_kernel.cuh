@@ -60,18 +60,18 @@ struct GemvSmem
     int bars, part, ytot, xh, ring, total;
 };
 
-__host__ __device__ inline GemvSmem gemv_smem_layout(int K, int MB, int stages)
+// xrows: rows of x~ / partial sums kept (the batch size m, at most 8*MB)
+__host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int stages)
 {
     GemvSmem L;
-    const int mrows = 8 * MB;
     L.bars = 0;                                             // 8 warps x 4 stages x 8 bytes
-    L.part = 512;                                           // [mrows][128] fp32, read by the cluster leader
-    L.ytot = L.part + mrows * 128 * 4;                      // [mrows][128] fp32
-    L.xh = L.ytot + mrows * 128 * 4;                        // [mrows][XPITCH] fp16
-    L.ring = L.xh + mrows * GEMV_XPITCH * 2;
+    L.part = 512;                                           // [xrows][128] fp32, read by the cluster leader
+    L.ytot = L.part + xrows * 128 * 4;                      // [xrows][128] fp32
+    L.xh = L.ytot + xrows * 128 * 4;                        // [xrows][XPITCH] fp16
+    L.ring = L.xh + xrows * GEMV_XPITCH * 2;
     L.ring = (L.ring + 127) & ~127;
     int ring_bytes = GEMV_WARPS * stages * gemv_stage_bytes(K);
-    int red_bytes = GEMV_WARPS * mrows * GEMV_RPITCH * 4;   // overlays the ring after the main loop
+    int red_bytes = GEMV_WARPS * xrows * GEMV_RPITCH * 4;   // overlays the ring after the main loop
     L.total = L.ring + (ring_bytes > red_bytes ? ring_bytes : red_bytes);
     return L;
 }
@@ -114,22 +114,50 @@ __device__ __forceinline__ uint32_t a_word(uint32_t s)
     else return cb_halves<CB>(s);
 }
 
-// Decode the lane's 32 weights of one tile (four "virtual lanes" of 8 positions) and issue the
-// eight MMAs. w/prev: the lane's K words and the word before them. xb: duplicated activations
-// of the tile's 16 rows for this lane's batch row(s).
+// The eight 16-bit states of virtual lane R (positions 8R..8R+7 of the lane's chunk).
+// When K divides 16, windows 16/K positions apart are exactly 16 bits apart, so one 32-bit
+// word cut from the stream holds two states (high and low half): one funnel shift serves two
+// weights. Other bitrates cut each window on its own.
+template <int K, int R>
+__device__ __forceinline__ void states8(const uint32_t (&w)[K], uint32_t prev, uint32_t (&s)[8])
+{
+    if constexpr (K == 4 || K == 8)
+    {
+        constexpr int D = 16 / K;                       // pair distance in positions
+        #pragma unroll
+        for (int j = 0; j < 8; ++j)
+        {
+            if ((j / D) % 2 != 0) continue;             // j is the earlier (high-half) member of its pair
+            const int i_lo = R * 8 + j + D;             // later member: its window ends the 32-bit word
+            const int last = (i_lo + 1) * K - 1;
+            const int j1 = last / 32, sh = 31 - (last % 32);
+            uint32_t r;
+            if (sh == 0) r = w[j1];
+            else r = __funnelshift_r(w[j1], j1 == 0 ? prev : w[j1 > 0 ? j1 - 1 : 0], sh);
+            s[j] = r >> 16;
+            s[j + D] = r & 0xffffu;
+        }
+    }
+    else
+    {
+        s[0] = window_ct<K, R * 8 + 0, K>(w, prev); s[1] = window_ct<K, R * 8 + 1, K>(w, prev);
+        s[2] = window_ct<K, R * 8 + 2, K>(w, prev); s[3] = window_ct<K, R * 8 + 3, K>(w, prev);
+        s[4] = window_ct<K, R * 8 + 4, K>(w, prev); s[5] = window_ct<K, R * 8 + 5, K>(w, prev);
+        s[6] = window_ct<K, R * 8 + 6, K>(w, prev); s[7] = window_ct<K, R * 8 + 7, K>(w, prev);
+    }
+}
+
+// Decode the lane's 8 weights of virtual lane R of one tile and issue the two MMAs. w/prev: the
+// lane's K words and the word before them. xb: duplicated activations of the tile's 16 rows for
+// this lane's batch row(s).
 template <int K, int CB, int MB, int R>
 __device__ __forceinline__ void decode_mma_r(const uint32_t (&w)[K], uint32_t prev,
                                              const uint32_t (&xb)[MB][16], float (&acc)[MB][4])
 {
-    uint32_t a[8];
-    a[0] = a_word<CB>(window_ct<K, R * 8 + 0, K>(w, prev));
-    a[1] = a_word<CB>(window_ct<K, R * 8 + 1, K>(w, prev));
-    a[2] = a_word<CB>(window_ct<K, R * 8 + 2, K>(w, prev));
-    a[3] = a_word<CB>(window_ct<K, R * 8 + 3, K>(w, prev));
-    a[4] = a_word<CB>(window_ct<K, R * 8 + 4, K>(w, prev));
-    a[5] = a_word<CB>(window_ct<K, R * 8 + 5, K>(w, prev));
-    a[6] = a_word<CB>(window_ct<K, R * 8 + 6, K>(w, prev));
-    a[7] = a_word<CB>(window_ct<K, R * 8 + 7, K>(w, prev));
+    uint32_t s[8], a[8];
+    states8<K, R>(w, prev, s);
+    #pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = a_word<CB>(s[j]);
     #pragma unroll
     for (int mb = 0; mb < MB; ++mb)
     {
@@ -145,14 +173,13 @@ __global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? 2 : 1))
 void exl3_gemv_kernel(const GemvParams P)
 {
     extern __shared__ __align__(128) unsigned char smem[];
-    const GemvSmem L = gemv_smem_layout(K, MB, P.stages);
+    const GemvSmem L = gemv_smem_layout(K, P.m, P.stages);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars);
     float* part = reinterpret_cast<float*>(smem + L.part);
     float* ytot = reinterpret_cast<float*>(smem + L.ytot);
     __half* xh = reinterpret_cast<__half*>(smem + L.xh);
     unsigned char* ring = smem + L.ring;
 
-    constexpr int MROWS = 8 * MB;
     constexpr int ROWB = 256 * K;                      // bytes of one tile row of this column block
     constexpr int PITCH = gemv_row_pitch(K);
     constexpr int STAGE = gemv_stage_bytes(K);
@@ -195,10 +222,6 @@ void exl3_gemv_kernel(const GemvParams P)
         // the weight stream does not depend on the previous kernel: start it before anything else
         for (int q = 0; q < stages && q < my_groups; ++q) issue(q);
     }
-
-    // zero x~ (rows >= m stay zero and keep unused MMA columns finite)
-    for (int i = t; i < MROWS * GEMV_XPITCH / 2; i += GEMV_THREADS)
-        reinterpret_cast<uint32_t*>(xh)[i] = 0u;
 
     float acc[MB][8][4];
     #pragma unroll
@@ -257,8 +280,9 @@ void exl3_gemv_kernel(const GemvParams P)
             #pragma unroll
             for (int mb = 0; mb < MB; ++mb)
             {
+                // batch rows >= m do not exist: read row m-1 instead (their MMA columns are never stored)
                 const uint4* xp = reinterpret_cast<const uint4*>(
-                    xh + (mb * 8 + gq) * GEMV_XPITCH + (g - cg0) * 64 + 16 * pq);
+                    xh + min(mb * 8 + gq, m - 1) * GEMV_XPITCH + (g - cg0) * 64 + 16 * pq);
                 uint4 v0 = xp[0], v1 = xp[1];
                 const uint32_t r[8] = { v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w };
                 #pragma unroll
@@ -317,7 +341,7 @@ void exl3_gemv_kernel(const GemvParams P)
 
     __syncthreads();                                    // ring is free: reuse it for the cross-warp reduction
 
-    float* red = reinterpret_cast<float*>(ring);        // [warp][MROWS][RPITCH]
+    float* red = reinterpret_cast<float*>(ring);        // [warp][m][RPITCH]
     #pragma unroll
     for (int mb = 0; mb < MB; ++mb)
     {
@@ -334,7 +358,7 @@ void exl3_gemv_kernel(const GemvParams P)
                 d0 = d0 * kinv + acc1[mb][0] * kbias; d1 = d1 * kinv + acc1[mb][1] * kbias;
                 d2 = d2 * kinv + acc1[mb][2] * kbias; d3 = d3 * kinv + acc1[mb][3] * kbias;
             }
-            float* r0 = red + ((size_t) warp * MROWS + b0) * GEMV_RPITCH + nt * 16 + gq;
+            float* r0 = red + ((size_t) warp * m + b0) * GEMV_RPITCH + nt * 16 + gq;
             if (b0 < m) { r0[0] = d0; r0[8] = d2; }
             if (b0 + 1 < m) { r0[GEMV_RPITCH] = d1; r0[GEMV_RPITCH + 8] = d3; }
         }
@@ -347,7 +371,7 @@ void exl3_gemv_kernel(const GemvParams P)
         float sum = 0.f;
         #pragma unroll
         for (int w8 = 0; w8 < GEMV_WARPS; ++w8)
-            sum += red[((size_t) w8 * MROWS + b) * GEMV_RPITCH + col];
+            sum += red[((size_t) w8 * m + b) * GEMV_RPITCH + col];
         part[b * 128 + col] = sum;
     }
 
