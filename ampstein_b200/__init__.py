@@ -11,6 +11,8 @@ from .exl3 import (  # noqa: F401
     exl3_reconstruct,
     exl3_reconstruct_had,
     had_r_128,
+    mgemm,
+    ptr_array,
 )
 
-__all__ = ["exl3_gemm", "exl3_gemm_recon", "exl3_reconstruct", "exl3_reconstruct_had", "had_r_128"]
+__all__ = ["exl3_gemm", "exl3_gemm_recon", "exl3_reconstruct", "exl3_reconstruct_had", "had_r_128", "mgemm", "ptr_array"]

@@ -22,6 +22,8 @@ SIGNATURES = {
     "amp_exl3_gemv": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "amp_exl3_gemv_cfg": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "amp_exl3_gemv_status": [ctypes.POINTER(ctypes.c_int)],
+    "amp_exl3_mgemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
+    "amp_exl3_set_pdl": [_i],
     "amp_exl3_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
 }
 

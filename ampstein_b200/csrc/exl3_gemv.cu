@@ -42,71 +42,123 @@ static gemv_fn gemv_kernel_for(int K, int cb, int MB)
     return nullptr;
 }
 
-// k-split (= cluster size along y). CTAs spread round-robin over the SMs; an SM's time is the
-// rows it decodes divided by its issue efficiency, which is poor with a single resident CTA
-// (8 warps). Pick the split whose busiest SM finishes first.
-static int choose_split(int k, int n, int sms, int ctas_per_sm)
+// Per-device workspace of the decode kernels: arrival counters and partial-sum slots for column
+// blocks whose rows are shared between CTAs. Allocated on the first launch on a device (like
+// the reference's DevCtx lock buffer, vendor/exl3/exllamav3_ext/quant/exl3_devctx.cu:81-94), so
+// the first call on a device must come before stream capture. Launches rotate through
+// GEMV_REGIONS independent regions, so kernels that overlap on the GPU (other streams, graph
+// branches) do not share counters as long as fewer than GEMV_REGIONS are in flight.
+constexpr int GEMV_REGIONS = 4;
+constexpr int GEMV_MAX_BLOCKS = 16384;                       // column blocks per launch
+constexpr int GEMV_MAX_CTAS = 1024;
+constexpr size_t GEMV_COUNTER_BYTES = GEMV_MAX_BLOCKS * sizeof(int);
+constexpr size_t GEMV_SCRATCH_BYTES = (size_t) GEMV_MAX_CTAS * 2 * 16 * 128 * sizeof(float);
+constexpr size_t GEMV_REGION_BYTES = GEMV_COUNTER_BYTES + GEMV_SCRATCH_BYTES;
+
+struct Workspace { unsigned char* base = nullptr; unsigned seq = 0; };
+
+static int workspace_region(int dev, int** counters, float** scratch)
 {
-    const int nb = n / 128, B2 = k / 128;
-    int best = 1;
-    double best_cost = 1e30;
-    for (int S = 1; S <= 8; ++S)
+    static Workspace ws[64];
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    Workspace& W = ws[dev & 63];
+    if (!W.base)
     {
-        if (S > B2) break;
-        const long ctas = (long) nb * S;
-        const long per_sm = (ctas + sms - 1) / sms;                   // CTAs on the busiest SM
-        const int rows = ((B2 + S - 1) / S) * 128;
-        const double eff = (per_sm >= 2 && ctas_per_sm >= 2) ? 1.0 : 0.7;
-        const double cost = (double) per_sm * (rows + 256.0) / eff;
-        if (cost < best_cost - 1e-9) { best_cost = cost; best = S; }
+        void* p = nullptr;
+        if (cudaError_t e = cudaMalloc(&p, GEMV_REGION_BYTES * GEMV_REGIONS)) return cuda_rc(e, "exl3_gemv workspace");
+        if (cudaError_t e = cudaMemset(p, 0, GEMV_REGION_BYTES * GEMV_REGIONS)) return cuda_rc(e, "exl3_gemv workspace clear");
+        if (cudaError_t e = cudaDeviceSynchronize()) return cuda_rc(e, "exl3_gemv workspace sync");
+        W.base = (unsigned char*) p;
     }
-    return best;
+    unsigned char* r = W.base + (size_t) (W.seq++ % GEMV_REGIONS) * GEMV_REGION_BYTES;
+    *counters = (int*) r;
+    *scratch = (float*) (r + GEMV_COUNTER_BYTES);
+    return 0;
 }
 
-int launch_gemv(const void* x, const void* trellis, void* c, const void* suh, const void* svh,
-                int m, int k, int n, int K, int cb, int c_fp32, int force_split, int force_stages,
-                cudaStream_t stream)
+struct GemvLaunch
 {
-    AMP_REQUIRE(x && trellis && c && suh && svh, "exl3_gemv: null pointer (suh and svh are required)");
+    const void* x; const void* trellis; const void* suh; const void* svh; void* c;
+    const long long* t_trellis; const long long* t_suh; const long long* t_svh; const long long* t_c;
+    const int* t_stride; const int* t_src;
+    int tables, slices, width, stride, m, k, K, cb, c_fp32;
+    int force_split, force_stages;
+};
+
+static int g_pdl = 1;     // programmatic dependent launch on by default
+
+int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
+{
+    const int m = A.m, k = A.k, K = A.K;
     AMP_REQUIRE(K >= 1 && K <= 8, "exl3_gemv: unsupported EXL3 bitrate %d (integer 1..8)", K);
-    AMP_REQUIRE(cb >= 0 && cb <= 2, "exl3_gemv: codebook index %d out of range", cb);
+    AMP_REQUIRE(A.cb >= 0 && A.cb <= 2, "exl3_gemv: codebook index %d out of range", A.cb);
     AMP_REQUIRE(m >= 1 && m <= 16, "exl3_gemv: m must be 1..16 (got %d)", m);
-    AMP_REQUIRE(k > 0 && n > 0 && k % 128 == 0 && n % 128 == 0, "exl3_gemv: k and n must be multiples of 128");
-    AMP_REQUIRE(((uintptr_t) trellis & 15) == 0, "exl3_gemv: trellis must be 16-byte aligned");
-    AMP_REQUIRE(((uintptr_t) x & 7) == 0 && ((uintptr_t) suh & 7) == 0 && ((uintptr_t) svh & 7) == 0,
-                "exl3_gemv: x, suh, svh must be 8-byte aligned");
-    AMP_REQUIRE(((uintptr_t) c & (c_fp32 ? 15 : 7)) == 0, "exl3_gemv: output misaligned");
-    AMP_REQUIRE(n / 128 <= 0x7fffffff, "exl3_gemv: n too large");
+    AMP_REQUIRE(k > 0 && A.width > 0 && k % 128 == 0 && A.width % 128 == 0 && A.stride % 128 == 0,
+                "exl3_gemv: k and n must be multiples of 128");
+    AMP_REQUIRE(A.slices >= 1 && (long) A.slices * (A.width / 128) <= 0x7fffffffL, "exl3_gemv: bad slice count");
+    AMP_REQUIRE(A.x && ((uintptr_t) A.x & 7) == 0, "exl3_gemv: x must be a non-null 8-byte aligned pointer");
+    if (A.tables)
+    {
+        AMP_REQUIRE(A.t_trellis && A.t_suh && A.t_svh, "exl3_mgemm: pointer tables are required");
+        AMP_REQUIRE(A.t_c || A.c, "exl3_mgemm: no output");
+    }
+    else
+    {
+        AMP_REQUIRE(A.trellis && A.c && A.suh && A.svh, "exl3_gemv: null pointer (suh and svh are required)");
+        AMP_REQUIRE(((uintptr_t) A.trellis & 15) == 0, "exl3_gemv: trellis must be 16-byte aligned");
+        AMP_REQUIRE(((uintptr_t) A.suh & 7) == 0 && ((uintptr_t) A.svh & 7) == 0, "exl3_gemv: suh, svh must be 8-byte aligned");
+        AMP_REQUIRE(((uintptr_t) A.c & (A.c_fp32 ? 15 : 7)) == 0, "exl3_gemv: output misaligned");
+    }
 
     int dev = 0;
     if (cudaError_t e = cudaGetDevice(&dev)) return cuda_rc(e, "cudaGetDevice");
     const DevInfo& D = dev_info(dev);
 
     const int MB = m <= 8 ? 1 : 2;
-    gemv_fn fn = gemv_kernel_for(K, cb, MB);
-    if (!fn) return fail(AMP_E_UNSUPPORTED, "exl3_gemv: no kernel for K=%d cb=%d", K, cb);
+    gemv_fn fn = gemv_kernel_for(K, A.cb, MB);
+    if (!fn) return fail(AMP_E_UNSUPPORTED, "exl3_gemv: no kernel for K=%d cb=%d", K, A.cb);
 
-    // ring depth: two stages per warp cover the refill latency; fall back to one if that is all
-    // that fits. CTAs per SM follow from shared memory (registers allow two for m <= 8).
-    int stages = force_stages > 0 ? force_stages : 2;
-    while (stages > 1 && gemv_smem_layout(K, m, stages).total > D.smem_optin) --stages;
+    // x~ rows resident at a time: up to 16 KB per batch row (whole segments for small batches, so
+    // the main loop runs without block-wide barriers), 32 KB in total
+    int xgroups = (32 * 1024 / (m * 4)) / 64;
+    xgroups &= ~3;
+    if (xgroups > GEMV_XCHUNK_MAX / 64) xgroups = GEMV_XCHUNK_MAX / 64;
+    if (xgroups > (k / 64 + 3) / 4 * 4) xgroups = (k / 64 + 3) / 4 * 4;
+    if (xgroups < 4) xgroups = 4;
+    int stages = A.force_stages > 0 ? A.force_stages : 3;
     AMP_REQUIRE(stages >= 1 && stages <= GEMV_MAX_STAGES, "exl3_gemv: stages out of range");
-    const GemvSmem L = gemv_smem_layout(K, m, stages);
+    const GemvSmem L = gemv_smem_layout(K, m, stages, xgroups);
     AMP_REQUIRE(L.total <= D.smem_optin, "exl3_gemv: shared memory layout does not fit (%d bytes)", L.total);
     const int smem_per_sm = D.smem_optin + 1024;                       // opt-in limit excludes 1 KB per CTA
+    const int reg_ctas = (MB == 1 ? 3 : 2);
     int ctas_per_sm = smem_per_sm / (L.total + 1024);
-    if (ctas_per_sm > (MB == 1 ? 2 : 1)) ctas_per_sm = (MB == 1 ? 2 : 1);
+    if (ctas_per_sm > reg_ctas) ctas_per_sm = reg_ctas;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
 
-    int S = force_split > 0 ? force_split : choose_split(k, n, D.sms, ctas_per_sm);
-    AMP_REQUIRE(S >= 1 && S <= 8, "exl3_gemv: split out of range");
+    // one contiguous range of (column block, 64-row group) units per CTA; as many CTAs as the
+    // device holds at once, fewer when that would leave a CTA with less than four units
+    const long col_blocks = (long) A.slices * (A.width / 128);
+    AMP_REQUIRE(col_blocks <= GEMV_MAX_BLOCKS, "exl3_gemv: too many column blocks (%ld)", col_blocks);
+    const long units = col_blocks * (k / 64);
+    long ncta = (long) D.sms * ctas_per_sm;
+    while (ncta > D.sms && units / ncta < 4) ncta -= D.sms;
+    if (A.force_split > 0) ncta = A.force_split;
+    if (ncta > units) ncta = units;
+    if (ncta > GEMV_MAX_CTAS) ncta = GEMV_MAX_CTAS;
+    AMP_REQUIRE(ncta >= 1, "exl3_gemv: empty problem");
 
     if (cudaError_t e = ensure_smem(fn, L.total, dev)) return cuda_rc(e, "exl3_gemv smem attribute");
 
     GemvParams P;
-    P.x = (const __half*) x; P.trellis = (const uint16_t*) trellis;
-    P.suh = (const __half*) suh; P.svh = (const __half*) svh; P.c = c;
-    P.m = m; P.k = k; P.n = n; P.c_fp32 = c_fp32; P.stages = stages;
+    P.x = (const __half*) A.x; P.trellis = (const uint16_t*) A.trellis;
+    P.suh = (const __half*) A.suh; P.svh = (const __half*) A.svh; P.c = A.c;
+    P.t_trellis = A.t_trellis; P.t_suh = A.t_suh; P.t_svh = A.t_svh; P.t_c = A.t_c;
+    P.t_stride = A.t_stride; P.t_src = A.t_src;
+    P.tables = A.tables; P.width = A.width; P.stride = A.stride;
+    P.m = m; P.k = k; P.c_fp32 = A.c_fp32; P.stages = stages; P.xgroups = xgroups; P.pdl = g_pdl;
+    P.blocks = (int) col_blocks;
+    if (int rc = workspace_region(dev, &P.counters, &P.scratch)) return rc;
     {
         // address of the status word, looked up once per device
         static int* status_ptr[64] = {};
@@ -117,18 +169,27 @@ int launch_gemv(const void* x, const void* trellis, void* c, const void* suh, co
     }
 
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(n / 128, S, 1);
+    cfg.gridDim = dim3((unsigned) ncta, 1, 1);
     cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
     cfg.dynamicSmemBytes = L.total;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = S;
-    attr[0].val.clusterDim.z = 1;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_pdl ? 1 : 0;
     return cuda_rc(cudaLaunchKernelEx(&cfg, fn, P), "exl3_gemv launch");
+}
+
+static GemvLaunch direct(const void* x, const void* trellis, void* c, const void* suh, const void* svh,
+                         int m, int k, int n, int K, int cb, int c_fp32, int split, int stages)
+{
+    GemvLaunch A = {};
+    A.x = x; A.trellis = trellis; A.suh = suh; A.svh = svh; A.c = c;
+    A.tables = 0; A.slices = 1; A.width = n; A.stride = n;
+    A.m = m; A.k = k; A.K = K; A.cb = cb; A.c_fp32 = c_fp32;
+    A.force_split = split; A.force_stages = stages;
+    return A;
 }
 
 }  // namespace amp
@@ -136,17 +197,17 @@ int launch_gemv(const void* x, const void* trellis, void* c, const void* suh, co
 using namespace amp;
 
 AMP_API int amp_exl3_gemv(const void* x, const void* trellis, void* c, const void* suh, const void* svh,
-                             int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream)
+                          int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream)
 {
-    return launch_gemv(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, 0, 0, stream);
+    return launch_gemv(direct(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, 0, 0), stream);
 }
 
-// tuning / test hook: fixed k-split and ring depth
+// tuning / test hook: fixed CTA count (split) and ring depth (stages); 0 = choose
 AMP_API int amp_exl3_gemv_cfg(const void* x, const void* trellis, void* c, const void* suh, const void* svh,
-                                 int m, int k, int n, int K, int cb, int c_fp32, int split, int stages,
-                                 cudaStream_t stream)
+                              int m, int k, int n, int K, int cb, int c_fp32, int split, int stages,
+                              cudaStream_t stream)
 {
-    return launch_gemv(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, split, stages, stream);
+    return launch_gemv(direct(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, split, stages), stream);
 }
 
 // Reads and clears the GEMV status word of the current device (synchronises the device).
@@ -157,6 +218,14 @@ AMP_API int amp_exl3_gemv_status(int* out)
     if (cudaError_t e = cudaMemcpyToSymbol(g_gemv_status, &zero, sizeof(int))) return cuda_rc(e, "status clear");
     if (out) *out = v;
     return 0;
+}
+
+// Programmatic dependent launch of the decode kernels (on by default): returns the old setting.
+AMP_API int amp_exl3_set_pdl(int enable)
+{
+    const int old = g_pdl;
+    g_pdl = enable ? 1 : 0;
+    return old;
 }
 
 // C = had(A*suh) @ W_hat -> had(.)*svh for any m. A_had (scratch of A's size in the reference's
@@ -173,7 +242,31 @@ AMP_API int amp_exl3_gemm(const void* A, const void* trellis, void* C, const voi
         const int rows = m - r < 16 ? m - r : 16;
         const char* a = (const char*) A + (size_t) r * k * 2;
         char* c = (char*) C + (size_t) r * n * (c_fp32 ? 4 : 2);
-        if (int rc = launch_gemv(a, trellis, c, suh, svh, rows, k, n, K, cb, c_fp32, 0, 0, stream)) return rc;
+        if (int rc = launch_gemv(direct(a, trellis, c, suh, svh, rows, k, n, K, cb, c_fp32, 0, 0), stream)) return rc;
     }
     return 0;
+}
+
+// Several EXL3 matrices (or equal-width column slices of matrices) against ONE shared input in a
+// single launch, identified by DEVICE pointer tables exactly as the reference's exl3_mgemm takes
+// them (int64 device arrays). num entries in trellis_ptrs / svh_ptrs (and c_ptrs, n_stride_list,
+// had_src_list when given); suh_ptrs has one entry per source (num_had_src, or num when
+// had_src_list is null). Outputs go to c_ptrs[i] with row width n_stride_list[i], or stacked
+// into C as (num, m, width) when c_ptrs is null. m <= 16.
+AMP_API int amp_exl3_mgemm(const void* x, const void* trellis_ptrs, void* C, const void* suh_ptrs,
+                           void* A_had, const void* svh_ptrs, int num, int m, int k, int width,
+                           int K, int cb, int c_fp32, const void* c_ptrs, const void* n_stride_list,
+                           const void* had_src_list, int num_had_src, cudaStream_t stream)
+{
+    (void) A_had; (void) num_had_src;
+    if (num == 0 || m == 0) return 0;
+    AMP_REQUIRE(num > 0, "exl3_mgemm: negative matrix count");
+    GemvLaunch A = {};
+    A.x = x; A.c = C;
+    A.t_trellis = (const long long*) trellis_ptrs; A.t_suh = (const long long*) suh_ptrs;
+    A.t_svh = (const long long*) svh_ptrs; A.t_c = (const long long*) c_ptrs;
+    A.t_stride = (const int*) n_stride_list; A.t_src = (const int*) had_src_list;
+    A.tables = 1; A.slices = num; A.width = width; A.stride = width;
+    A.m = m; A.k = k; A.K = K; A.cb = cb; A.c_fp32 = c_fp32;
+    return launch_gemv(A, stream);
 }

@@ -1,16 +1,30 @@
-// Trellis-decode GEMV for decode batches (m <= 16): C = had(A*suh) @ W_hat -> had(.)*svh.
+// Trellis-decode GEMV for decode batches (m <= 16): C = had(A*suh) @ W_hat -> had(.)*svh, for
+// one matrix or a bundle of matrices / column slices that share one input.
 //
-// Replaces the reference's exl3_gemv_kernel / exl3_gemm_kernel at small m
-// (vendor/exl3/exllamav3_ext/quant/exl3_gemv_kernel.cuh:186-482, exl3_gemm_kernel.cuh:8-80) with
-// a different organisation for B200:
+// Replaces the reference's exl3_gemv_kernel, exl3_gemm_kernel at small m and exl3_mgemm_kernel
+// (vendor/exl3/exllamav3_ext/quant/exl3_gemv_kernel.cuh:186-482, exl3_gemm_kernel.cuh:8-343)
+// with a different organisation for B200:
 //
-//  * One CTA owns a 128-column block of the output and a contiguous range of 128-row blocks of
-//    k. The k-splits of one column block form a thread-block cluster; partial sums are
-//    reduced through distributed shared memory, so the kernel needs no global scratch, no
-//    locks and no grid-wide barrier (the reference needs two grid.sync()s and a lock buffer).
-//  * Packed trellis words are streamed global -> shared by bulk async copies (TMA, untiled
-//    form) into per-warp multi-stage rings, each copy a contiguous 256*K-byte run of one tile
-//    row. A stage is four tile rows (64 rows of k) by 128 columns.
+//  * The work -- (128-column block, 64-row group) units in block-major order -- is cut into as
+//    many equal contiguous ranges as the device holds CTAs at once, so every SM decodes the
+//    same number of weights whatever the shape (no wave quantisation, no tail). A range
+//    touches one to three column blocks; a block whose rows are shared between CTAs is
+//    finished by whichever contributor arrives last (per-block arrival counter, partial sums
+//    in a small global scratch area, summed in ascending-k order so results are bitwise
+//    reproducible). Nobody waits: there is no spin, no lock and no grid-wide barrier (the
+//    reference needs two grid.sync()s, an A_had scratch tensor and a lock buffer).
+//  * Inside the CTA a warp owns 64 of the 128 columns and every fourth unit of the range:
+//    16 fp32 accumulators per thread, which keeps the register count low enough for three
+//    CTAs (24 warps) per SM -- the decode is bound by instruction issue, so warps in flight
+//    are what hides its latencies.
+//  * Packed trellis words are streamed global -> shared with 16-byte cp.async copies into
+//    per-warp rings (a stage = four tile rows x four tiles = 512*K bytes, every copy
+//    instruction of a warp covers whole 128-byte lines). Bulk (TMA) copies were measured and
+//    rejected for this access pattern: one warp sustains only about one bulk copy per 1000
+//    cycles whatever the ring depth, so the 0.5-1 KB row pieces of a column block cap the
+//    kernel near 1.4 TB/s, while cp.async streams at the full HBM rate. The copies are
+//    issued before the kernel waits for its predecessor (programmatic dependent launch), so
+//    a layer's weight stream starts under the previous layer's tail.
 //  * Decode stays in registers. The decoded weights are the A operand of mma.sync.m16n8k16
 //    (16 output columns x 16 k-slots) and the activations the B operand (k-slots x 8 batch
 //    rows), so a batch of up to 8 costs one MMA per 128 weights. For codebooks 0/1 the final
@@ -18,61 +32,76 @@
 //    product sit in adjacent k-slots against a duplicated activation, which removes the
 //    byte-permute and half-add per weight from the instruction stream (fp32 accumulation of
 //    x*lo + x*hi is at least as accurate as x*fp16(lo+hi)).
-//  * The input Hadamard runs in each CTA's prologue per 1024-row chunk (x is tiny and L2
-//    resident); the output Hadamard, svh scale and store run in the cluster leader.
+//  * The input Hadamard runs in each CTA per column-block segment (x is tiny and L2 resident)
+//    and leaves x~ in shared memory already duplicated and in fragment order; the output
+//    Hadamard, svh scale and store run in the CTA that finishes the block.
 //
-// HBM-bound by design (K/8 bytes per weight, read once); in practice limited by integer
-// issue rate: about three integer instructions per weight (window, multiply-add, lop3).
+// HBM-bound by design (K/8 bytes per weight, read once); in practice limited by instruction
+// issue: window cut, multiply-add, lop3 per weight plus a quarter MMA (about four issue slots
+// per weight, i.e. ~30 weights per clock per SM).
 #pragma once
 #include "exl3_common.cuh"
-#include <cooperative_groups.h>
 
 namespace amp {
 
-namespace cg = cooperative_groups;
-
 constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_WARPS = 8;
-constexpr int GEMV_XCHUNK = 1024;              // rows of x~ held in shared memory at a time
-constexpr int GEMV_XPITCH = GEMV_XCHUNK + 8;   // halves; +16 bytes keeps B-fragment loads conflict-free
-constexpr int GEMV_RPITCH = 132;               // floats; cross-warp reduction rows
+constexpr int GEMV_KSLOTS = 4;                 // warps along k (times 2 column halves = 8 warps)
+constexpr int GEMV_XCHUNK_MAX = 8192;          // most rows of x~ held in shared memory at a time
+constexpr int GEMV_RPITCH = 68;                // floats per row of a warp's 64-column partial
 constexpr int GEMV_MAX_STAGES = 4;
 
 struct GemvParams
 {
-    const __half* x;            // (m, k)
-    const uint16_t* trellis;    // (k/16, n/16, 16K)
+    // direct mode (tables == 0): one matrix
+    const __half* x;            // (m, k), shared by every slice
+    const uint16_t* trellis;    // (k/16, stride/16, 16K)
     const __half* suh;          // (k)
-    const __half* svh;          // (n)
-    void* c;                    // (m, n) fp16 or fp32
-    int m, k, n;
+    const __half* svh;          // (width)
+    void* c;                    // (m, stride) fp16 or fp32; stacked (num, m, width) in table mode without t_c
+    // table mode (tables == 1): device pointer tables, one entry per slice (suh: per source)
+    const long long* t_trellis;
+    const long long* t_suh;
+    const long long* t_svh;
+    const long long* t_c;       // may be null: outputs stacked in c
+    const int* t_stride;        // may be null: stride = width
+    const int* t_src;           // may be null: source = slice
+    int tables;
+    int width;                  // columns per slice (multiple of 128)
+    int stride;                 // row width of trellis / output in direct mode
+    int m, k;
     int c_fp32;
     int stages;                 // ring depth per warp, 1..GEMV_MAX_STAGES
-    int* status;                // device word, set non-zero when a bounded wait ran out
+    int xgroups;                // 64-row groups of x~ held in shared memory at a time (multiple of 4)
+    int pdl;                    // launched with programmatic stream serialization
+    int blocks;                 // column blocks in total (slices * width / 128)
+    float* scratch;             // [gridDim.x][2][m][128] partial sums of blocks shared between CTAs
+    int* counters;              // [blocks] arrival counters, zero between launches
+    int* status;                // device status word (the kernel has no waits that can run out; kept for the ABI)
 };
 
-__host__ __device__ constexpr int gemv_row_pitch(int K) { return 256 * K + 32; }     // bytes per tile row in a stage
+__host__ __device__ constexpr int gemv_row_pitch(int K) { return 128 * K + 32; }     // bytes per tile row (4 tiles) in a stage
 __host__ __device__ constexpr int gemv_stage_bytes(int K) { return 4 * gemv_row_pitch(K); }
 
 // byte offsets inside dynamic shared memory
 struct GemvSmem
 {
-    int bars, part, ytot, xh, ring, total;
+    int part, xd, red, ring, total;
 };
 
-// xrows: rows of x~ / partial sums kept (the batch size m, at most 8*MB)
-__host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int stages)
+// 32-bit words per batch row of the duplicated x~ (+16 keeps fragment loads conflict-free)
+__host__ __device__ constexpr int gemv_xpitch(int xgroups) { return xgroups * 64 + 16; }
+
+// xrows: rows of x~ / partial sums kept (the batch size m)
+__host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int stages, int xgroups)
 {
     GemvSmem L;
-    L.bars = 0;                                             // 8 warps x 4 stages x 8 bytes
-    L.part = 512;                                           // [xrows][128] fp32, read by the cluster leader
-    L.ytot = L.part + xrows * 128 * 4;                      // [xrows][128] fp32
-    L.xh = L.ytot + xrows * 128 * 4;                        // [xrows][XPITCH] fp16
-    L.ring = L.xh + xrows * GEMV_XPITCH * 2;
+    L.part = 0;                                             // [xrows][128] fp32: the finished block
+    L.xd = L.part + xrows * 128 * 4;                        // [xrows][XPITCH] duplicated fp16 pairs
+    L.red = L.xd + xrows * gemv_xpitch(xgroups) * 4;        // [8 warps][xrows][RPITCH] fp32
+    L.ring = L.red + GEMV_WARPS * xrows * GEMV_RPITCH * 4;
     L.ring = (L.ring + 127) & ~127;
-    int ring_bytes = GEMV_WARPS * stages * gemv_stage_bytes(K);
-    int red_bytes = GEMV_WARPS * xrows * GEMV_RPITCH * 4;   // overlays the ring after the main loop
-    L.total = L.ring + (ring_bytes > red_bytes ? ring_bytes : red_bytes);
+    L.total = L.ring + GEMV_WARPS * stages * gemv_stage_bytes(K);
     return L;
 }
 
@@ -149,15 +178,28 @@ __device__ __forceinline__ void states8(const uint32_t (&w)[K], uint32_t prev, u
 
 // Decode the lane's 8 weights of virtual lane R of one tile and issue the two MMAs. w/prev: the
 // lane's K words and the word before them. xb: duplicated activations of the tile's 16 rows for
-// this lane's batch row(s).
+// this lane's batch row(s), xb[r] = row r.
 template <int K, int CB, int MB, int R>
 __device__ __forceinline__ void decode_mma_r(const uint32_t (&w)[K], uint32_t prev,
                                              const uint32_t (&xb)[MB][16], float (&acc)[MB][4])
 {
     uint32_t s[8], a[8];
+#ifdef AMP_LAB_NODECODE
+    #pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = w[R % K] + j + prev;
+#else
     states8<K, R>(w, prev, s);
     #pragma unroll
     for (int j = 0; j < 8; ++j) a[j] = a_word<CB>(s[j]);
+#endif
+#ifdef AMP_LAB_NOMMA
+    #pragma unroll
+    for (int mb = 0; mb < MB; ++mb)
+    {
+        uint32_t u = a[0] ^ a[1] ^ a[2] ^ a[3] ^ a[4] ^ a[5] ^ a[6] ^ a[7] ^ xb[mb][2 * R];
+        acc[mb][0] += __uint_as_float(u);
+    }
+#else
     #pragma unroll
     for (int mb = 0; mb < MB; ++mb)
     {
@@ -166,252 +208,361 @@ __device__ __forceinline__ void decode_mma_r(const uint32_t (&w)[K], uint32_t pr
         mma_16816(acc[mb], a[0], a[4], a[1], a[5], xb[mb][2 * R], xb[mb][2 * R + 1]);
         mma_16816(acc[mb], a[2], a[6], a[3], a[7], xb[mb][2 * R + 8], xb[mb][2 * R + 9]);
     }
+#endif
+}
+
+__device__ __forceinline__ void pdl_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void pdl_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(dst)), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit()
+{
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// wait until at most `pending` of this thread's committed groups are still in flight
+__device__ __forceinline__ void cp_async_wait(int pending)
+{
+    switch (pending)
+    {
+        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    }
 }
 
 template <int K, int CB, int MB>
-__global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? 2 : 1))
+__global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? 3 : 2))
 void exl3_gemv_kernel(const GemvParams P)
 {
     extern __shared__ __align__(128) unsigned char smem[];
-    const GemvSmem L = gemv_smem_layout(K, P.m, P.stages);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars);
+    const GemvSmem L = gemv_smem_layout(K, P.m, P.stages, P.xgroups);
+    const int GEMV_XPITCH = gemv_xpitch(P.xgroups);
+    const int XG = P.xgroups;
     float* part = reinterpret_cast<float*>(smem + L.part);
-    float* ytot = reinterpret_cast<float*>(smem + L.ytot);
-    __half* xh = reinterpret_cast<__half*>(smem + L.xh);
+    uint32_t* xd = reinterpret_cast<uint32_t*>(smem + L.xd);
+    float* red = reinterpret_cast<float*>(smem + L.red);
     unsigned char* ring = smem + L.ring;
+    __shared__ int s_last;
 
-    constexpr int ROWB = 256 * K;                      // bytes of one tile row of this column block
     constexpr int PITCH = gemv_row_pitch(K);
     constexpr int STAGE = gemv_stage_bytes(K);
 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int gq = lane >> 2, pq = lane & 3;
-    const int nb = blockIdx.x;
-    const int S = gridDim.y, split = blockIdx.y;
+    const int half = warp & 1, ks = warp >> 1;         // column half, k slot
     const int stages = P.stages;
-    const int m = P.m, k = P.k, n = P.n;
+    const int m = P.m, k = P.k;
+    const int G = k >> 6;                              // 64-row groups per column block
+    const int nbw = P.width >> 7;                      // column blocks per slice
 
-    // this CTA's k range in 64-row groups (128-row aligned so Hadamard blocks stay whole)
-    const int B2 = k >> 7;
-    const int g_begin = 2 * (int) ((long) B2 * split / S);
-    const int g_end = 2 * (int) ((long) B2 * (split + 1) / S);
-    const int my_groups = (g_end - g_begin - warp + GEMV_WARPS - 1) / GEMV_WARPS;   // groups of this warp (may be <= 0)
+    // Work = (column block, group) units in block-major order, cut into gridDim.x equal contiguous
+    // ranges: every CTA decodes the same number of weights (+-1 group) whatever the shape.
+    const long U = (long) P.blocks * G;
+    const int cta = blockIdx.x, ncta = gridDim.x;
+    const long u0 = U * cta / ncta, u1 = U * (cta + 1) / ncta;
+    const int len = (int) (u1 - u0);
+    const int my_items = (len - ks + GEMV_KSLOTS - 1) / GEMV_KSLOTS;      // this warp's units: u0 + ks + 4j
 
-    uint64_t* my_bars = bars + warp * GEMV_MAX_STAGES;
     unsigned char* my_ring = ring + (size_t) warp * stages * STAGE;
-    const size_t tiles_n = (size_t) n >> 4;
 
-    auto issue = [&](int q)                            // lane 0 only
+    // per-slice addressing (device tables in bundle mode)
+    auto slice_of = [&](int blk, const uint16_t*& trellis, int& stride, int& nb)
     {
-        const int g = g_begin + warp + GEMV_WARPS * q;
-        const int s = q % stages;
-        uint64_t* bar = my_bars + s;
-        mbar_expect_tx(bar, 4 * ROWB);
-        const unsigned char* src = reinterpret_cast<const unsigned char*>(P.trellis)
-                                 + ((size_t) (4 * g) * tiles_n + (size_t) nb * 8) * (32 * K);
-        unsigned char* dst = my_ring + (size_t) s * STAGE;
-        #pragma unroll
-        for (int p = 0; p < 4; ++p)
-            bulk_g2s(dst + p * PITCH, src + (size_t) p * tiles_n * (32 * K), ROWB, bar);
+        const int slice = blk / nbw;
+        nb = blk - slice * nbw;
+        if (P.tables)
+        {
+            trellis = reinterpret_cast<const uint16_t*>(P.t_trellis[slice]);
+            stride = P.t_stride ? P.t_stride[slice] : P.width;
+        }
+        else { trellis = P.trellis; stride = P.stride; }
     };
 
-    if (lane == 0)
+    // One stage = four tile rows x four tiles of one unit; the warp copies it as 16-byte pieces
+    // (K per lane). A group is committed even when nothing is left to copy so that the group
+    // count stays in step with the item index.
+    auto issue = [&](int j)
     {
-        for (int s = 0; s < stages; ++s) mbar_init(my_bars + s, 1);
-        fence_mbar_init();
-        // the weight stream does not depend on the previous kernel: start it before anything else
-        for (int q = 0; q < stages && q < my_groups; ++q) issue(q);
+#ifndef AMP_LAB_NOLOAD
+        if (j < my_items)
+#else
+        if (j < 0)
+#endif
+        {
+            const long u = u0 + ks + GEMV_KSLOTS * j;
+            const int blk = (int) (u / G), g = (int) (u - (long) blk * G);
+            const uint16_t* trellis; int stride, nb;
+            slice_of(blk, trellis, stride, nb);
+            const size_t tiles_n = (size_t) stride >> 4;
+            const unsigned char* src = reinterpret_cast<const unsigned char*>(trellis)
+                                     + ((size_t) (4 * g) * tiles_n + (size_t) nb * 8 + half * 4) * (32 * K);
+            unsigned char* dst = my_ring + (size_t) (j % stages) * STAGE;
+            #pragma unroll
+            for (int i8 = 0; i8 < K; ++i8)
+            {
+                const int i = lane + 32 * i8;           // piece index: 8K pieces per tile row
+                const int row = i / (8 * K), off = (i - row * 8 * K) * 16;
+                cp_async16(dst + row * PITCH + off, src + (size_t) row * tiles_n * (32 * K) + off);
+            }
+        }
+        cp_async_commit();
+    };
+
+    // the weight stream does not depend on the previous kernel: start it before anything else
+    for (int j = 0; j < stages; ++j) issue(j);
+    if (P.pdl)
+    {
+        pdl_launch_dependents();                       // the next kernel may start its own weight stream
+        pdl_wait();                                    // x is the previous kernel's output
     }
 
-    float acc[MB][8][4];
-    #pragma unroll
-    for (int mb = 0; mb < MB; ++mb)
-        #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
-            acc[mb][nt][0] = acc[mb][nt][1] = acc[mb][nt][2] = acc[mb][nt][3] = 0.f;
-    float acc1[MB][4];                                 // cb 2 only: sum of activations (all-ones weights)
-    #pragma unroll
-    for (int mb = 0; mb < MB; ++mb) acc1[mb][0] = acc1[mb][1] = acc1[mb][2] = acc1[mb][3] = 0.f;
-
-    bool ok = true;
-    int q = 0;                                          // index of this warp's next group
-    int q_fail = 0;                                     // first group whose data never arrived
-    const int n_chunks = (g_end - g_begin + 15) >> 4;
-
-    for (int c = 0; c < n_chunks; ++c)
+    int j = 0;                                         // this warp's next item
+    long useg = u0;
+    while (useg < u1)
     {
-        const int cg0 = g_begin + 16 * c;
-        const int cg1 = min(cg0 + 16, g_end);
-        const int nblk = (cg1 - cg0) >> 1;              // 128-row blocks in this chunk
-        __syncthreads();                                // previous chunk's x~ fully consumed (and zero fill done)
-
-        for (int idx = warp; idx < m * nblk; idx += GEMV_WARPS)
+        // ---- one segment: the part of this CTA's range that lies in one column block ----
+        const int blk = (int) (useg / G);
+        const int g0 = (int) (useg - (long) blk * G);
+        const int g1 = (int) min((long) G, (long) g0 + (u1 - useg));
+        const int slice = blk / nbw, nb = blk - slice * nbw;
+        const __half* suh = P.suh;
+        const __half* svh = P.svh;
+        unsigned char* cbase = reinterpret_cast<unsigned char*>(P.c);
+        int stride = P.stride;
+        if (P.tables)
         {
-            const int b = idx / nblk, j = idx - b * nblk;
-            const size_t col = (size_t) cg0 * 64 + (size_t) j * 128 + lane * 4;
-            half4 v = *reinterpret_cast<const half4*>(P.x + (size_t) b * k + col);
-            half4 sc = *reinterpret_cast<const half4*>(P.suh + col);
-            v.x = __hmul2(v.x, sc.x);
-            v.y = __hmul2(v.y, sc.y);
-            float h0 = __low2float(v.x), h1 = __high2float(v.x), h2 = __low2float(v.y), h3 = __high2float(v.y);
-            warp_had128(h0, h1, h2, h3, lane);
-            half4 o;
-            o.x = __floats2half2_rn(h0 * kRScale, h1 * kRScale);
-            o.y = __floats2half2_rn(h2 * kRScale, h3 * kRScale);
-            *reinterpret_cast<half4*>(xh + b * GEMV_XPITCH + j * 128 + lane * 4) = o;
+            const int src = P.t_src ? P.t_src[slice] : slice;
+            suh = reinterpret_cast<const __half*>(P.t_suh[src]);
+            svh = reinterpret_cast<const __half*>(P.t_svh[slice]);
+            stride = P.t_stride ? P.t_stride[slice] : P.width;
+            if (P.t_c) cbase = reinterpret_cast<unsigned char*>(P.t_c[slice]);
+            else cbase += (size_t) slice * m * P.width * (P.c_fp32 ? 4 : 2);
+        }
+
+        float acc[MB][4][4];
+        #pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+            #pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+                acc[mb][nt][0] = acc[mb][nt][1] = acc[mb][nt][2] = acc[mb][nt][3] = 0.f;
+        float acc1[MB][4];                             // cb 2 only: sum of activations (all-ones weights)
+        #pragma unroll
+        for (int mb = 0; mb < MB; ++mb) acc1[mb][0] = acc1[mb][1] = acc1[mb][2] = acc1[mb][3] = 0.f;
+
+        // x~ is needed in whole 128-row blocks: chunks start at an even group
+        const int ga = g0 & ~1;
+        for (int cg0 = ga; cg0 < g1; cg0 += XG)
+        {
+            const int cg1 = min(cg0 + XG, g1);
+            const int nblk = (cg1 - cg0 + 1) >> 1;      // 128-row blocks in this chunk
+            __syncthreads();                            // previous x~ (and reduction buffers) fully consumed
+
+            // x~ = fp16(H(x * suh) / sqrt(128)), stored duplicated ((v, v) per word) and in the
+            // order the B fragments are read: word = group*64 + (row%16 / 4)*16 + (row%64 / 16)*4 + row%4
+            for (int idx = warp; idx < m * nblk; idx += GEMV_WARPS)
+            {
+                const int b = idx / nblk, jb = idx - b * nblk;
+                const size_t col = (size_t) cg0 * 64 + (size_t) jb * 128 + lane * 4;
+                half4 v = *reinterpret_cast<const half4*>(P.x + (size_t) b * k + col);
+                half4 sc = *reinterpret_cast<const half4*>(suh + col);
+                v.x = __hmul2(v.x, sc.x);
+                v.y = __hmul2(v.y, sc.y);
+                float h0 = __low2float(v.x), h1 = __high2float(v.x), h2 = __low2float(v.y), h3 = __high2float(v.y);
+                warp_had128(h0, h1, h2, h3, lane);
+                const __half2 o01 = __floats2half2_rn(h0 * kRScale, h1 * kRScale);
+                const __half2 o23 = __floats2half2_rn(h2 * kRScale, h3 * kRScale);
+                const uint32_t u01 = *reinterpret_cast<const uint32_t*>(&o01);
+                const uint32_t u23 = *reinterpret_cast<const uint32_t*>(&o23);
+                uint4 d;
+                d.x = __byte_perm(u01, u01, 0x1010); d.y = __byte_perm(u01, u01, 0x3232);
+                d.z = __byte_perm(u23, u23, 0x1010); d.w = __byte_perm(u23, u23, 0x3232);
+                const int r = jb * 128 + lane * 4;      // row inside the chunk
+                const int word = (r >> 6) * 64 + ((r & 15) >> 2) * 16 + ((r & 63) >> 4) * 4;
+                *reinterpret_cast<uint4*>(xd + b * GEMV_XPITCH + word) = d;
+            }
+            __syncthreads();
+
+            // this warp's units of the chunk: u = u0 + ks + 4j inside [blk*G + max(cg0,g0), blk*G + cg1)
+            const long cu1 = (long) blk * G + cg1;
+            for (; u0 + ks + (long) GEMV_KSLOTS * j < cu1; ++j)
+            {
+                const int g = (int) (u0 + ks + (long) GEMV_KSLOTS * j - (long) blk * G);
+                const int s = j % stages;
+                cp_async_wait(stages - 1);              // item j has landed (this lane's pieces)
+                __syncwarp();                           // ... and every other lane's
+
+                // duplicated activations of this lane's tile (rows 16*pq .. +15 of the group): four
+                // 16-byte loads. Batch rows >= m do not exist: read row m-1 (their MMA columns are
+                // never stored).
+                uint32_t xb[MB][16];
+                #pragma unroll
+                for (int mb = 0; mb < MB; ++mb)
+                {
+                    const uint32_t* xp = xd + min(mb * 8 + gq, m - 1) * GEMV_XPITCH + (g - cg0) * 64 + pq * 4;
+                    #pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                    {
+                        uint4 v = *reinterpret_cast<const uint4*>(xp + i * 16);
+                        xb[mb][4 * i] = v.x; xb[mb][4 * i + 1] = v.y; xb[mb][4 * i + 2] = v.z; xb[mb][4 * i + 3] = v.w;
+                    }
+                }
+
+                const unsigned char* st = my_ring + (size_t) s * STAGE + pq * PITCH;
+                #pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+                {
+                    const uint32_t* tile = reinterpret_cast<const uint32_t*>(st + nt * (32 * K));
+                    uint32_t w[K];
+                    load_chunk<K>(tile + gq * K, w);
+                    const uint32_t prev = tile[(gq * K + 8 * K - 1) % (8 * K)];
+                    float a4[MB][4];
+                    #pragma unroll
+                    for (int mb = 0; mb < MB; ++mb)
+                    {
+                        a4[mb][0] = acc[mb][nt][0]; a4[mb][1] = acc[mb][nt][1];
+                        a4[mb][2] = acc[mb][nt][2]; a4[mb][3] = acc[mb][nt][3];
+                    }
+                    decode_mma_r<K, CB, MB, 0>(w, prev, xb, a4);
+                    decode_mma_r<K, CB, MB, 1>(w, prev, xb, a4);
+                    decode_mma_r<K, CB, MB, 2>(w, prev, xb, a4);
+                    decode_mma_r<K, CB, MB, 3>(w, prev, xb, a4);
+                    #pragma unroll
+                    for (int mb = 0; mb < MB; ++mb)
+                    {
+                        acc[mb][nt][0] = a4[mb][0]; acc[mb][nt][1] = a4[mb][1];
+                        acc[mb][nt][2] = a4[mb][2]; acc[mb][nt][3] = a4[mb][3];
+                    }
+                }
+                if constexpr (CB == 2)
+                {
+                    // sum of x~ over the 64 rows of this group: weights of 1.0 in the low half
+                    #pragma unroll
+                    for (int mb = 0; mb < MB; ++mb)
+                        #pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            mma_16816(acc1[mb], 0x3c00u, 0x3c00u, 0x3c00u, 0x3c00u, xb[mb][2 * i], xb[mb][2 * i + 1]);
+                }
+
+                __syncwarp();                           // every lane has its words in registers
+                issue(j + stages);
+            }
+        }
+
+        // ---- segment done: reduce the eight warps' partial sums ----
+        #pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+        {
+            const int b0 = mb * 8 + 2 * pq;
+            #pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+            {
+                float d0 = acc[mb][nt][0], d1 = acc[mb][nt][1], d2 = acc[mb][nt][2], d3 = acc[mb][nt][3];
+                if constexpr (CB == 2)
+                {
+                    // w = raw * k_inv + k_bias  ->  sum x*w = k_inv * sum x*raw + k_bias * sum x
+                    const float kinv = __half2float(__ushort_as_half((unsigned short) 0x1eee));
+                    const float kbias = __half2float(__ushort_as_half((unsigned short) 0xc931));
+                    d0 = d0 * kinv + acc1[mb][0] * kbias; d1 = d1 * kinv + acc1[mb][1] * kbias;
+                    d2 = d2 * kinv + acc1[mb][2] * kbias; d3 = d3 * kinv + acc1[mb][3] * kbias;
+                }
+                float* r0 = red + ((size_t) warp * m + b0) * GEMV_RPITCH + nt * 16 + gq;
+                if (b0 < m) { r0[0] = d0; r0[8] = d2; }
+                if (b0 + 1 < m) { r0[GEMV_RPITCH] = d1; r0[GEMV_RPITCH + 8] = d3; }
+            }
         }
         __syncthreads();
 
-        for (int g = cg0 + warp; g < cg1; g += GEMV_WARPS, ++q)
-        {
-            const int s = q % stages;
-            const uint32_t parity = (uint32_t) (q / stages) & 1u;
-            if (!ok) continue;
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(my_bars + s, parity)))
-            {
-                ok = false;
-                q_fail = q;
-                if (lane == 0) atomicExch(P.status, 1);
-                continue;
-            }
+        const bool whole = (g0 == 0 && g1 == G);       // this CTA owns every row of the block
+        // contributors of this block: the CTAs whose ranges meet [blk*G, (blk+1)*G)
+        const int i_first = (int) ((((long) blk * G + 1) * ncta + U - 1) / U) - 1;
+        const int i_last = (int) ((((long) (blk + 1) * G) * ncta + U - 1) / U) - 1;
+        float* slots = P.scratch;                      // [cta][2][m][128]
+        const int my_slot = 2 * cta + ((long) blk * G > u0 ? 1 : 0);
 
-            // activations of this lane's tile row block: rows (g - cg0)*64 + 16*pq .. +15
-            uint32_t xb[MB][16];
-            #pragma unroll
-            for (int mb = 0; mb < MB; ++mb)
-            {
-                // batch rows >= m do not exist: read row m-1 instead (their MMA columns are never stored)
-                const uint4* xp = reinterpret_cast<const uint4*>(
-                    xh + min(mb * 8 + gq, m - 1) * GEMV_XPITCH + (g - cg0) * 64 + 16 * pq);
-                uint4 v0 = xp[0], v1 = xp[1];
-                const uint32_t r[8] = { v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w };
-                #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                {
-                    xb[mb][2 * i] = __byte_perm(r[i], r[i], 0x1010);
-                    xb[mb][2 * i + 1] = __byte_perm(r[i], r[i], 0x3232);
-                }
-            }
-
-            const unsigned char* st = my_ring + (size_t) s * STAGE + pq * PITCH;
-            #pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
-            {
-                const uint32_t* tile = reinterpret_cast<const uint32_t*>(st + nt * (32 * K));
-                uint32_t w[K];
-                load_chunk<K>(tile + gq * K, w);
-                const uint32_t prev = tile[(gq * K + 8 * K - 1) % (8 * K)];
-                float a4[MB][4];
-                #pragma unroll
-                for (int mb = 0; mb < MB; ++mb)
-                {
-                    a4[mb][0] = acc[mb][nt][0]; a4[mb][1] = acc[mb][nt][1];
-                    a4[mb][2] = acc[mb][nt][2]; a4[mb][3] = acc[mb][nt][3];
-                }
-                decode_mma_r<K, CB, MB, 0>(w, prev, xb, a4);
-                decode_mma_r<K, CB, MB, 1>(w, prev, xb, a4);
-                decode_mma_r<K, CB, MB, 2>(w, prev, xb, a4);
-                decode_mma_r<K, CB, MB, 3>(w, prev, xb, a4);
-                #pragma unroll
-                for (int mb = 0; mb < MB; ++mb)
-                {
-                    acc[mb][nt][0] = a4[mb][0]; acc[mb][nt][1] = a4[mb][1];
-                    acc[mb][nt][2] = a4[mb][2]; acc[mb][nt][3] = a4[mb][3];
-                }
-            }
-            if constexpr (CB == 2)
-            {
-                // sum of x~ over the 64 rows of this group: weights of 1.0 in the low half
-                #pragma unroll
-                for (int mb = 0; mb < MB; ++mb)
-                    #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        mma_16816(acc1[mb], 0x3c00u, 0x3c00u, 0x3c00u, 0x3c00u, xb[mb][2 * i], xb[mb][2 * i + 1]);
-            }
-
-            __syncwarp();                               // every lane has its words in registers
-            if (lane == 0 && q + stages < my_groups) issue(q + stages);
-        }
-    }
-
-    // drain copies that were issued but never consumed (only possible after a failed wait)
-    if (!ok)
-        for (int qq = q_fail; qq < q_fail + stages && qq < my_groups; ++qq)
-            mbar_wait_bounded(my_bars + (qq % stages), (uint32_t) (qq / stages) & 1u);
-
-    __syncthreads();                                    // ring is free: reuse it for the cross-warp reduction
-
-    float* red = reinterpret_cast<float*>(ring);        // [warp][m][RPITCH]
-    #pragma unroll
-    for (int mb = 0; mb < MB; ++mb)
-    {
-        const int b0 = mb * 8 + 2 * pq;
-        #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
-        {
-            float d0 = acc[mb][nt][0], d1 = acc[mb][nt][1], d2 = acc[mb][nt][2], d3 = acc[mb][nt][3];
-            if constexpr (CB == 2)
-            {
-                // w = raw * k_inv + k_bias  ->  sum x*w = k_inv * sum x*raw + k_bias * sum x
-                const float kinv = __half2float(__ushort_as_half((unsigned short) 0x1eee));
-                const float kbias = __half2float(__ushort_as_half((unsigned short) 0xc931));
-                d0 = d0 * kinv + acc1[mb][0] * kbias; d1 = d1 * kinv + acc1[mb][1] * kbias;
-                d2 = d2 * kinv + acc1[mb][2] * kbias; d3 = d3 * kinv + acc1[mb][3] * kbias;
-            }
-            float* r0 = red + ((size_t) warp * m + b0) * GEMV_RPITCH + nt * 16 + gq;
-            if (b0 < m) { r0[0] = d0; r0[8] = d2; }
-            if (b0 + 1 < m) { r0[GEMV_RPITCH] = d1; r0[GEMV_RPITCH + 8] = d3; }
-        }
-    }
-    __syncthreads();
-
-    for (int idx = t; idx < m * 128; idx += GEMV_THREADS)
-    {
-        const int b = idx >> 7, col = idx & 127;
-        float sum = 0.f;
-        #pragma unroll
-        for (int w8 = 0; w8 < GEMV_WARPS; ++w8)
-            sum += red[((size_t) w8 * m + b) * GEMV_RPITCH + col];
-        part[b * 128 + col] = sum;
-    }
-
-    cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();                                     // partial sums of every split are in place
-
-    if (split == 0)
-    {
         for (int idx = t; idx < m * 128; idx += GEMV_THREADS)
         {
+            const int b = idx >> 7, col = idx & 127;
+            const int hf = col >> 6, cl = col & 63;
             float sum = 0.f;
-            for (int r = 0; r < S; ++r)                 // rank order: deterministic
-                sum += cluster.map_shared_rank(part, r)[idx];
-            ytot[idx] = sum;
+            #pragma unroll
+            for (int s4 = 0; s4 < GEMV_KSLOTS; ++s4)    // k-slot order: deterministic
+                sum += red[((size_t) (s4 * 2 + hf) * m + b) * GEMV_RPITCH + cl];
+            if (whole) part[idx] = sum;
+            else slots[(size_t) my_slot * m * 128 + idx] = sum;
         }
-    }
-    cluster.sync();                                     // peers may exit; ytot visible to the leader's warps
-    if (split != 0) return;
 
-    for (int b = warp; b < m; b += GEMV_WARPS)
-    {
-        float4 v = reinterpret_cast<const float4*>(ytot + b * 128)[lane];
-        float h0 = v.x, h1 = v.y, h2 = v.z, h3 = v.w;
-        warp_had128(h0, h1, h2, h3, lane);
-        h0 *= kRScale; h1 *= kRScale; h2 *= kRScale; h3 *= kRScale;
-        const half4 sv = reinterpret_cast<const half4*>(P.svh + (size_t) nb * 128)[lane];
-        if (P.c_fp32)
+        bool finish = whole;
+        if (!whole)
         {
-            float4 o = make_float4(h0 * __low2float(sv.x), h1 * __high2float(sv.x),
-                                   h2 * __low2float(sv.y), h3 * __high2float(sv.y));
-            reinterpret_cast<float4*>(reinterpret_cast<float*>(P.c) + (size_t) b * n + (size_t) nb * 128)[lane] = o;
+            // publish the partial, then count arrivals: the last contributor finishes the block
+            __threadfence();
+            __syncthreads();
+            if (t == 0)
+            {
+                const int prev = atomicAdd(P.counters + blk, 1);
+                s_last = (prev == i_last - i_first);
+                if (s_last) P.counters[blk] = 0;        // self-reset for the next launch
+            }
+            __syncthreads();
+            finish = s_last != 0;
+            if (finish)
+            {
+                __threadfence();
+                for (int idx = t; idx < m * 128; idx += GEMV_THREADS)
+                {
+                    float sum = 0.f;
+                    for (int i = i_first; i <= i_last; ++i)       // ascending k: deterministic
+                    {
+                        const long iu0 = U * i / ncta;
+                        const int slot = 2 * i + ((long) blk * G > iu0 ? 1 : 0);
+                        sum += __ldcg(slots + (size_t) slot * m * 128 + idx);
+                    }
+                    part[idx] = sum;
+                }
+            }
         }
-        else
+        __syncthreads();
+
+        if (finish)
         {
-            half4 o;
-            o.x = __hmul2(__floats2half2_rn(h0, h1), sv.x);
-            o.y = __hmul2(__floats2half2_rn(h2, h3), sv.y);
-            reinterpret_cast<half4*>(reinterpret_cast<__half*>(P.c) + (size_t) b * n + (size_t) nb * 128)[lane] = o;
+            for (int b = warp; b < m; b += GEMV_WARPS)
+            {
+                float4 v = reinterpret_cast<const float4*>(part + b * 128)[lane];
+                float h0 = v.x, h1 = v.y, h2 = v.z, h3 = v.w;
+                warp_had128(h0, h1, h2, h3, lane);
+                h0 *= kRScale; h1 *= kRScale; h2 *= kRScale; h3 *= kRScale;
+                const half4 sv = reinterpret_cast<const half4*>(svh + (size_t) nb * 128)[lane];
+                if (P.c_fp32)
+                {
+                    float4 o = make_float4(h0 * __low2float(sv.x), h1 * __high2float(sv.x),
+                                           h2 * __low2float(sv.y), h3 * __high2float(sv.y));
+                    reinterpret_cast<float4*>(reinterpret_cast<float*>(cbase) + (size_t) b * stride + (size_t) nb * 128)[lane] = o;
+                }
+                else
+                {
+                    half4 o;
+                    o.x = __hmul2(__floats2half2_rn(h0, h1), sv.x);
+                    o.y = __hmul2(__floats2half2_rn(h2, h3), sv.y);
+                    reinterpret_cast<half4*>(reinterpret_cast<__half*>(cbase) + (size_t) b * stride + (size_t) nb * 128)[lane] = o;
+                }
+            }
         }
+        useg += g1 - g0;
     }
+    cp_async_wait(0);
 }
 
 typedef void (*gemv_fn)(const GemvParams);

@@ -141,3 +141,60 @@ def exl3_gemm_recon(x, trellis, suh, svh, K, mul1=False, mcg=False):
         raise ValueError("exl3_gemm_recon: K does not match the trellis")
     y = torch.empty((x.shape[0], n), dtype=torch.float16, device=x.device)
     return exl3_gemm(x, trellis, y, suh, svh, mul1, mcg)
+
+
+def ptr_array(values, device=None):
+    """1-D int64 CUDA tensor of raw device addresses: the pointer tables mgemm consumes
+    (reference: torch.ptr_array, src/torch/amp_torch.cpp:10332-...)."""
+    if not all(isinstance(v, int) for v in values):
+        raise TypeError("ptr_array: values must be integers")
+    return torch.tensor(list(values), dtype=torch.int64, device=device if device is not None else "cuda")
+
+
+def mgemm(x, B_ptrs, C, suh_ptrs, A_had, svh_ptrs, K, mcg, mul1, opts=None):
+    """Several EXL3 weights against one shared input in ONE launch (reference: torch.mgemm,
+    src/torch/amp_torch.cpp:10193-10322). x (1, m, k) fp16; B_ptrs / suh_ptrs / svh_ptrs int64
+    CUDA pointer tables; C (num, m, n) stacked output. opts selects sliced mode:
+    {size_n_list, c_ptrs, n_stride_list, had_src_list, num_had_src}; C is then only a
+    (num_slices, m, width) descriptor. A_had is accepted and unused. Returns C."""
+    for name, t in (("B_ptrs", B_ptrs), ("suh_ptrs", suh_ptrs), ("svh_ptrs", svh_ptrs)):
+        if not isinstance(t, torch.Tensor) or t.dtype != torch.int64 or not t.is_cuda:
+            raise TypeError("mgemm: %s must be an int64 CUDA tensor" % name)
+    _check_cuda("mgemm", x, C)
+    if x.dtype != torch.float16 or C.dtype not in (torch.float16, torch.float32):
+        raise TypeError("mgemm: x must be float16, C float16 or float32")
+    if x.dim() != 3 or x.shape[0] != 1 or C.dim() != 3:
+        raise ValueError("mgemm: x must be (1, m, k) and C (num, m, n)")
+    if float(K) != int(K) or not (1 <= int(K) <= 8):
+        raise ValueError("mgemm: unsupported EXL3 bitrate %s" % K)
+    num, m, width = C.shape
+    k = x.shape[2]
+    if x.shape[1] != m:
+        raise ValueError("mgemm: row count of x and C differ")
+    c_ptrs = n_stride = had_src = None
+    num_had_src = 0
+    if opts is not None:
+        if not isinstance(opts, dict):
+            raise TypeError("mgemm: opts must be an object")
+        want = {"size_n_list": torch.int32, "c_ptrs": torch.int64, "n_stride_list": torch.int32,
+                "had_src_list": torch.int32}
+        for key, dt in want.items():
+            t = opts.get(key)
+            if not isinstance(t, torch.Tensor) or t.dtype != dt or not t.is_cuda or not t.is_contiguous():
+                raise TypeError("mgemm: opts.%s must be a contiguous %s CUDA tensor" % (key, dt))
+        if not isinstance(opts.get("num_had_src"), int):
+            raise TypeError("mgemm: num_had_src missing")
+        c_ptrs, n_stride, had_src = opts["c_ptrs"], opts["n_stride_list"], opts["had_src_list"]
+        num_had_src = opts["num_had_src"]
+        if opts["size_n_list"].numel() != num or c_ptrs.numel() != num:
+            raise ValueError("mgemm: slice tables do not match C")
+    if B_ptrs.numel() < num or svh_ptrs.numel() < num:
+        raise ValueError("mgemm: pointer tables shorter than the matrix count")
+    with torch.cuda.device(x.device):
+        _lib.call("amp_exl3_mgemm", x.data_ptr(), B_ptrs.data_ptr(), C.data_ptr(), suh_ptrs.data_ptr(),
+                  A_had.data_ptr() if A_had is not None else None, svh_ptrs.data_ptr(), num, m, k, width,
+                  int(K), _cb(mul1, mcg), 1 if C.dtype == torch.float32 else 0,
+                  c_ptrs.data_ptr() if c_ptrs is not None else None,
+                  n_stride.data_ptr() if n_stride is not None else None,
+                  had_src.data_ptr() if had_src is not None else None, num_had_src, _stream(x))
+    return C

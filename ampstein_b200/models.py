@@ -44,6 +44,76 @@ class LinearEXL3:
         return self.trellis.numel() * 2
 
 
+def _bundle_check(linears):
+    a = linears[0]
+    for i, w in enumerate(linears[1:], 1):
+        if (w.K, w.mul1, w.mcg, w.in_features) != (a.K, a.mul1, a.mcg, a.in_features):
+            raise ValueError("models.bundle: fused linears must share K, in_features and codebook "
+                             "(matrix %d differs)" % i)
+
+
+class Multi:
+    """Equal-shape bundle (reference: models.uc multi(), :338-361): run(x) writes all outputs
+    stacked into `out` (num, m, n) with ONE launch. x is (1, m, k)."""
+
+    def __init__(self, linears, out):
+        _bundle_check(linears)
+        dev = out.device
+        self.linears, self.out = linears, out
+        self.B = exl3.ptr_array([w.trellis.data_ptr() for w in linears], dev)
+        self.suh = exl3.ptr_array([w.suh.data_ptr() for w in linears], dev)
+        self.svh = exl3.ptr_array([w.svh.data_ptr() for w in linears], dev)
+
+    def run(self, x):
+        a = self.linears[0]
+        return exl3.mgemm(x, self.B, self.out, self.suh, None, self.svh, a.K, a.mcg, a.mul1)
+
+
+class Sliced:
+    """Bundle for unequal widths such as Q/K/V (reference: models.uc sliced(), :367-432): every
+    matrix is cut into column slices of the widths' gcd (a multiple of 128); outputs are written
+    in place into `outs`, one (1, m, out_features) buffer per linear."""
+
+    def __init__(self, linears, outs):
+        import math
+        _bundle_check(linears)
+        dev = outs[0].device
+        width = 0
+        for w in linears:
+            width = math.gcd(width, w.out_features)
+        if width % 128 or width < 128:
+            raise ValueError("models.sliced: unsuitable slice width %d" % width)
+        t, svh, cp, stride, src = [], [], [], [], []
+        for i, w in enumerate(linears):
+            tw = w.trellis.shape[2]
+            for n0 in range(0, w.out_features, width):
+                t.append(w.trellis.data_ptr() + (n0 // 16) * tw * 2)
+                svh.append(w.svh.data_ptr() + n0 * 2)
+                cp.append(outs[i].data_ptr() + n0 * 2)
+                stride.append(w.out_features)
+                src.append(i)
+        self.linears, self.outs, self.width, self.slices = linears, outs, width, len(t)
+        m = outs[0].shape[1]
+        self.B = exl3.ptr_array(t, dev)
+        self.svh = exl3.ptr_array(svh, dev)
+        self.suh = exl3.ptr_array([w.suh.data_ptr() for w in linears], dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.opts = {
+            "size_n_list": torch.tensor([width] * len(t), **i32),
+            "c_ptrs": exl3.ptr_array(cp, dev),
+            "n_stride_list": torch.tensor(stride, **i32),
+            "had_src_list": torch.tensor(src, **i32),
+            "num_had_src": len(linears),
+        }
+        # descriptor only: (num_slices, m, width); the data goes through c_ptrs
+        self.carrier = torch.empty((len(t), m, width), dtype=torch.float16, device=dev)
+
+    def run(self, x):
+        a = self.linears[0]
+        exl3.mgemm(x, self.B, self.carrier, self.suh, None, self.svh, a.K, a.mcg, a.mul1, self.opts)
+        return self.outs
+
+
 class DecodeGraph:
     """Captures `step_fn()` (a sequence of operator calls on fixed buffers) in one CUDA graph
     after warm-up runs, then replays it: one host->device crossing per step, as the reference's

@@ -76,7 +76,9 @@ int amp_exl3_gemm(const void* A, const void* trellis, void* C, const void* suh, 
                   cudaStream_t stream);
 
 /*
- * The decode-batch kernel on its own, m = 1..16.
+ * The decode-batch kernel on its own, m = 1..16. The first call on a device allocates a
+ * per-device workspace (about 70 MB: arrival counters and partial-sum slots) and must
+ * therefore come before any stream capture; later calls allocate nothing.
  * Replaces: exl3_gemv_kernel / exl3_gemv_try_launch, Q/exl3_gemv_kernel.cuh:186-482,
  * Q/exl3_gemv.cu:92-184.
  */
@@ -84,18 +86,45 @@ int amp_exl3_gemv(const void* x, const void* trellis, void* c, const void* suh, 
                   int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream);
 
 /*
- * Same with a fixed k-split (cluster size, 1..8) and ring depth (1..4); 0 = choose. The
- * counterpart of the reference's force_shape_idx / force_num_sms arguments
- * (Q/exl3_gemm.cu:114-127), used by tuning and tests.
+ * Same with a fixed number of CTAs (split, 1..1024: the work is cut into that many equal
+ * ranges) and cp.async ring depth per warp (stages, 1..4); 0 = choose. The counterpart of the
+ * reference's force_shape_idx / force_num_sms arguments (Q/exl3_gemm.cu:114-127), used by
+ * tuning and tests.
  */
 int amp_exl3_gemv_cfg(const void* x, const void* trellis, void* c, const void* suh, const void* svh,
                       int m, int k, int n, int K, int cb, int c_fp32, int split, int stages,
                       cudaStream_t stream);
 
 /*
- * Reads and clears the current device's GEMV status word: non-zero after a bounded wait inside
- * a kernel ran out (the kernel then returns without finishing its tile instead of spinning;
- * the reference traps). Synchronises; for tests and diagnostics, not for the hot path.
+ * Several EXL3 matrices -- or equal-width column slices of matrices -- against ONE shared input
+ * x (m, k) in a single launch, m <= 16. Matrices are named by DEVICE pointer tables (int64
+ * device arrays), exactly as the reference takes them, so no host synchronisation is needed:
+ *   trellis_ptrs[num], svh_ptrs[num]  per slice (already offset to the slice's first column)
+ *   suh_ptrs[num_had_src]             per source matrix; had_src_list[num] (int32) maps a slice
+ *                                     to its source, NULL = identity
+ *   c_ptrs[num] + n_stride_list[num]  per-slice output pointer and row width of the matrix it
+ *                                     belongs to; both NULL = outputs stacked in C (num, m, width)
+ * All slices share k, K, the codebook and the width (a multiple of 128). A_had is accepted
+ * and not used.
+ * Replaces: exl3_mgemm, Q/exl3_gemm.cu:351-735 (binding torch.mgemm,
+ * src/torch/amp_torch.cpp:10193-10322; bundle builders src/ucode/ampstein/models.uc:338-432).
+ */
+int amp_exl3_mgemm(const void* x, const void* trellis_ptrs, void* C, const void* suh_ptrs,
+                   void* A_had, const void* svh_ptrs, int num, int m, int k, int width,
+                   int K, int cb, int c_fp32, const void* c_ptrs, const void* n_stride_list,
+                   const void* had_src_list, int num_had_src, cudaStream_t stream);
+
+/*
+ * Programmatic dependent launch of the decode kernels (default on): each kernel starts its
+ * weight stream before waiting for the kernel in front of it. Returns the previous setting.
+ * The reference has no counterpart (it launches cooperative kernels back to back).
+ */
+int amp_exl3_set_pdl(int enable);
+
+/*
+ * Reads and clears the current device's GEMV status word (non-zero = a kernel reported an
+ * internal error). The decode kernels contain no spin-waits, so it stays zero; it is kept so
+ * that tests can assert it. Synchronises; not for the hot path.
  */
 int amp_exl3_gemv_status(int* out);
 

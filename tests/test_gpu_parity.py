@@ -137,9 +137,10 @@ def test_gemv_batch_sizes(amp, oracle, m):
     check_close(run_gemm(amp, trellis, suh, svh, x, 0, fp32=True), ref)
 
 
-@pytest.mark.parametrize("split,stages", [(1, 1), (1, 3), (2, 2), (3, 2), (5, 1), (8, 2), (8, 4)])
+@pytest.mark.parametrize("split,stages", [(1, 1), (1, 3), (2, 2), (3, 2), (5, 1), (8, 2), (8, 4), (37, 3), (72, 2), (148, 3)])
 def test_gemv_splits_and_ring_depths(amp, oracle, split, stages):
-    # k = 2304 = 18 blocks of 128: ragged over 5 and 8 splits, more than one 1024-row chunk
+    # k = 2304 = 36 groups x 2 column blocks = 72 units: one CTA walking both blocks, ragged
+    # ranges that start and end inside a block, one unit per CTA, more CTAs than units
     trellis, suh, svh, x = make_linear(2304, 256, 4, seed=5000, m=2)
     ref = oracle.linear(x, trellis, suh, svh, 0, fp32_out=True)
     check_close(run_gemm(amp, trellis, suh, svh, x, 0, split=split, stages=stages), ref)
@@ -163,6 +164,46 @@ def test_llama_shapes(amp, oracle, k, n, K):
     trellis, suh, svh, x = make_linear(k, n, K, seed=k + n + K, m=1)
     ref = oracle.linear(x, trellis, suh, svh, 0, fp32_out=True)
     check_close(run_gemm(amp, trellis, suh, svh, x, 0), ref)
+
+
+@pytest.mark.parametrize("m", [1, 4, 12])
+def test_shared_blocks_large_batch_chunks(amp, oracle, m):
+    """k large enough that x~ does not fit in one chunk at m = 12 and every block is shared by
+    several CTAs."""
+    trellis, suh, svh, x = make_linear(6144, 384, 4, seed=5200 + m, m=m)
+    ref = oracle.linear(x, trellis, suh, svh, 0, fp32_out=True)
+    check_close(run_gemm(amp, trellis, suh, svh, x, 0), ref)
+    check_close(run_gemm(amp, trellis, suh, svh, x, 0, split=11, stages=2), ref)
+
+
+def test_mgemm_multi_and_sliced(amp, oracle):
+    """Bundles (models.uc multi / sliced): gate|up stacked, q|k|v sliced by the gcd of the widths,
+    each slice with its own suh source; results equal the separate linears'."""
+    from ampstein_b200.models import LinearEXL3, Multi, Sliced
+    k, m = 1024, 3
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    xd = dev(x).reshape(1, m, k)
+
+    def lin(n, seed):
+        trellis, suh, svh, _ = make_linear(k, n, 4, seed=seed)
+        return (trellis, suh, svh), LinearEXL3(dev(trellis), dev(suh), dev(svh))
+
+    (g_np, g), (u_np, u) = lin(768, 1), lin(768, 2)
+    out = torch.full((2, m, 768), float("nan"), dtype=torch.float16, device="cuda")
+    Multi([g, u], out).run(xd)
+    torch.cuda.synchronize()
+    for i, (t, su, sv) in enumerate((g_np, u_np)):
+        check_close(out[i].cpu().numpy(), oracle.linear(x, t, su, sv, 0, fp32_out=True))
+
+    (q_np, q), (k_np, kk), (v_np, v) = lin(1024, 3), lin(256, 4), lin(256, 5)
+    outs = [torch.full((1, m, n), float("nan"), dtype=torch.float16, device="cuda") for n in (1024, 256, 256)]
+    sl = Sliced([q, kk, v], outs)
+    assert sl.width == 256 and sl.slices == 6
+    sl.run(xd)
+    torch.cuda.synchronize()
+    for o, (t, su, sv) in zip(outs, (q_np, k_np, v_np)):
+        check_close(o[0].cpu().numpy(), oracle.linear(x, t, su, sv, 0, fp32_out=True))
 
 
 def test_gemm_more_than_16_rows(amp, oracle):
