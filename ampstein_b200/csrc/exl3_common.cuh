@@ -74,9 +74,19 @@ __device__ __forceinline__ uint32_t window_rt(const uint32_t* ring, int t)
     return __funnelshift_r(ring[j1], ring[j0], sh) & 0xffffu;
 }
 
+// (x & 0xffff) on the FMA-heavy pipe (dp2a with a one-hot byte vector), leaving the integer ALU
+// to the shifts
+__device__ __forceinline__ uint32_t mask16_fma(uint32_t x)
+{
+    uint32_t d;
+    asm("dp2a.lo.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(0x00000001u), "r"(0u));
+    return d;
+}
+
 // compile-time position inside a register chunk w[0..NW) preceded by `prev`; bit 0 of the chunk
-// is the MSB of w[0]. I = index of the weight inside the chunk.
-template <int K, int I, int NW>
+// is the MSB of w[0]. I = index of the weight inside the chunk. FMA: do the 16-bit mask on the
+// FMA-heavy pipe instead of the ALU.
+template <int K, int I, int NW, bool FMA = true>
 __device__ __forceinline__ uint32_t window_ct(const uint32_t (&w)[NW], uint32_t prev)
 {
     constexpr int last = (I + 1) * K - 1;
@@ -86,13 +96,14 @@ __device__ __forceinline__ uint32_t window_ct(const uint32_t (&w)[NW], uint32_t 
     if constexpr (sh + 16 <= 32)
     {
         if constexpr (sh == 16) return w[j1] >> 16;
-        else if constexpr (sh == 0) return w[j1] & 0xffffu;
-        else return (w[j1] >> sh) & 0xffffu;
+        else if constexpr (sh == 0) return FMA ? mask16_fma(w[j1]) : (w[j1] & 0xffffu);
+        else return FMA ? mask16_fma(w[j1] >> sh) : ((w[j1] >> sh) & 0xffffu);
     }
     else
     {
         const uint32_t hi = (j1 == 0) ? prev : w[j1 > 0 ? j1 - 1 : 0];
-        return __funnelshift_r(w[j1], hi, sh) & 0xffffu;
+        const uint32_t v = __funnelshift_r(w[j1], hi, sh);
+        return FMA ? mask16_fma(v) : (v & 0xffffu);
     }
 }
 
@@ -184,7 +195,11 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1)
 {
+#ifdef AMP_MMA_VOLATILE
     asm volatile(
+#else
+    asm(
+#endif
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));

@@ -141,8 +141,18 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     const long col_blocks = (long) A.slices * (A.width / 128);
     AMP_REQUIRE(col_blocks <= GEMV_MAX_BLOCKS, "exl3_gemv: too many column blocks (%ld)", col_blocks);
     const long units = col_blocks * (k / 64);
+    AMP_REQUIRE(units < (1L << 30), "exl3_gemv: problem too large (%ld work units)", units);
+    const int G = k / 64;
     long ncta = (long) D.sms * ctas_per_sm;
-    while (ncta > D.sms && units / ncta < 4) ncta -= D.sms;
+    if (units / ncta < 16)
+    {
+        // small problem: give every column block the same whole number of CTAs, so that a CTA
+        // works on one block only (one partial-sum exchange per CTA instead of two or three)
+        long S = ncta / col_blocks;
+        while (S > 1 && G / S < 4) --S;
+        if (S >= 1) ncta = col_blocks * S;
+        else { ncta = (long) D.sms * ctas_per_sm; while (ncta > D.sms && units / ncta < 4) ncta -= D.sms; }
+    }
     if (A.force_split > 0) ncta = A.force_split;
     if (ncta > units) ncta = units;
     if (ncta > GEMV_MAX_CTAS) ncta = GEMV_MAX_CTAS;

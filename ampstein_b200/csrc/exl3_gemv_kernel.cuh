@@ -143,16 +143,43 @@ __device__ __forceinline__ uint32_t a_word(uint32_t s)
     else return cb_halves<CB>(s);
 }
 
+// 16-bit field extraction on the FMA-heavy pipe: dp2a with a one-hot byte vector is
+// (x & 0xffff) + 0 or (x >> 16) + 0. The integer ALU and the FMA-heavy pipe each accept one warp
+// instruction every two cycles on sm_100, and everything else in the decode except the
+// multiply-add is ALU work (funnel shifts, lop3), so splitting the field extraction between the
+// two pipes is what keeps either from becoming the only bottleneck.
+__device__ __forceinline__ uint32_t lo16_fma(uint32_t r)
+{
+    uint32_t d;
+    asm("dp2a.lo.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(r), "r"(0x00000001u), "r"(0u));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t hi16_fma(uint32_t r)
+{
+    uint32_t d;
+    asm("dp2a.lo.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(r), "r"(0x00000100u), "r"(0u));
+    return d;
+}
+
+#ifndef AMP_GEMV_HI_FMA_MASK
+#define AMP_GEMV_HI_FMA_MASK 0x6      // which of a word's (up to four) pairs take their high state on the FMA pipe
+#endif
+#ifndef AMP_GEMV_LO_FMA_MASK
+#define AMP_GEMV_LO_FMA_MASK 0xf      // ... and their low state
+#endif
+
 // The eight 16-bit states of virtual lane R (positions 8R..8R+7 of the lane's chunk).
 // When K divides 16, windows 16/K positions apart are exactly 16 bits apart, so one 32-bit
 // word cut from the stream holds two states (high and low half): one funnel shift serves two
-// weights. Other bitrates cut each window on its own.
+// weights. Other bitrates cut each window on its own (shift on the ALU, mask on the FMA pipe).
 template <int K, int R>
 __device__ __forceinline__ void states8(const uint32_t (&w)[K], uint32_t prev, uint32_t (&s)[8])
 {
     if constexpr (K == 4 || K == 8)
     {
         constexpr int D = 16 / K;                       // pair distance in positions
+        int pair = 0;
         #pragma unroll
         for (int j = 0; j < 8; ++j)
         {
@@ -163,8 +190,9 @@ __device__ __forceinline__ void states8(const uint32_t (&w)[K], uint32_t prev, u
             uint32_t r;
             if (sh == 0) r = w[j1];
             else r = __funnelshift_r(w[j1], j1 == 0 ? prev : w[j1 > 0 ? j1 - 1 : 0], sh);
-            s[j] = r >> 16;
-            s[j + D] = r & 0xffffu;
+            s[j] = ((AMP_GEMV_HI_FMA_MASK >> pair) & 1) ? hi16_fma(r) : (r >> 16);
+            s[j + D] = ((AMP_GEMV_LO_FMA_MASK >> pair) & 1) ? lo16_fma(r) : (r & 0xffffu);
+            ++pair;
         }
     }
     else
@@ -243,13 +271,17 @@ __device__ __forceinline__ void cp_async_wait(int pending)
     }
 }
 
+#ifndef AMP_GEMV_MINBLOCKS
+#define AMP_GEMV_MINBLOCKS 3
+#endif
+
 template <int K, int CB, int MB>
-__global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? 3 : 2))
+__global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 2))
 void exl3_gemv_kernel(const GemvParams P)
 {
     extern __shared__ __align__(128) unsigned char smem[];
     const GemvSmem L = gemv_smem_layout(K, P.m, P.stages, P.xgroups);
-    const int GEMV_XPITCH = gemv_xpitch(P.xgroups);
+    const int XPITCH = gemv_xpitch(P.xgroups);
     const int XG = P.xgroups;
     float* part = reinterpret_cast<float*>(smem + L.part);
     uint32_t* xd = reinterpret_cast<uint32_t*>(smem + L.xd);
@@ -259,6 +291,7 @@ void exl3_gemv_kernel(const GemvParams P)
 
     constexpr int PITCH = gemv_row_pitch(K);
     constexpr int STAGE = gemv_stage_bytes(K);
+    constexpr int TILE_BYTES = 32 * K;
 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int gq = lane >> 2, pq = lane & 3;
@@ -270,73 +303,100 @@ void exl3_gemv_kernel(const GemvParams P)
 
     // Work = (column block, group) units in block-major order, cut into gridDim.x equal contiguous
     // ranges: every CTA decodes the same number of weights (+-1 group) whatever the shape.
-    const long U = (long) P.blocks * G;
+    const int U = P.blocks * G;
     const int cta = blockIdx.x, ncta = gridDim.x;
-    const long u0 = U * cta / ncta, u1 = U * (cta + 1) / ncta;
-    const int len = (int) (u1 - u0);
-    const int my_items = (len - ks + GEMV_KSLOTS - 1) / GEMV_KSLOTS;      // this warp's units: u0 + ks + 4j
+    const int u0 = (int) ((long) U * cta / ncta), u1 = (int) ((long) U * (cta + 1) / ncta);
 
     unsigned char* my_ring = ring + (size_t) warp * stages * STAGE;
 
-    // per-slice addressing (device tables in bundle mode)
-    auto slice_of = [&](int blk, const uint16_t*& trellis, int& stride, int& nb)
+    // ---- weight stream: this warp's units are u0 + ks + 4j; a cursor walks them without divisions ----
+    int iu = u0 + ks;                                  // next unit to fetch
+    int iblk = iu / G, ig = iu - iblk * G;
+    int istage = 0;
+    const unsigned char* ibase = nullptr;              // first tile row of the cursor's block, this warp's four tiles
+    size_t irow = 0;                                   // bytes between tile rows there
+
+    auto set_block = [&](int blk)
     {
-        const int slice = blk / nbw;
-        nb = blk - slice * nbw;
+        const int slice = blk / nbw, nb = blk - slice * nbw;
+        const unsigned char* tr = reinterpret_cast<const unsigned char*>(P.trellis);
+        int stride = P.stride;
         if (P.tables)
         {
-            trellis = reinterpret_cast<const uint16_t*>(P.t_trellis[slice]);
+            tr = reinterpret_cast<const unsigned char*>(P.t_trellis[slice]);
             stride = P.t_stride ? P.t_stride[slice] : P.width;
         }
-        else { trellis = P.trellis; stride = P.stride; }
+        irow = (size_t) (stride >> 4) * TILE_BYTES;
+        ibase = tr + (size_t) (nb * 8 + half * 4) * TILE_BYTES;
     };
 
     // One stage = four tile rows x four tiles of one unit; the warp copies it as 16-byte pieces
     // (K per lane). A group is committed even when nothing is left to copy so that the group
     // count stays in step with the item index.
-    auto issue = [&](int j)
+    auto issue = [&]()
     {
 #ifndef AMP_LAB_NOLOAD
-        if (j < my_items)
+        if (iu < u1)
 #else
-        if (j < 0)
+        if (iu < 0)
 #endif
         {
-            const long u = u0 + ks + GEMV_KSLOTS * j;
-            const int blk = (int) (u / G), g = (int) (u - (long) blk * G);
-            const uint16_t* trellis; int stride, nb;
-            slice_of(blk, trellis, stride, nb);
-            const size_t tiles_n = (size_t) stride >> 4;
-            const unsigned char* src = reinterpret_cast<const unsigned char*>(trellis)
-                                     + ((size_t) (4 * g) * tiles_n + (size_t) nb * 8 + half * 4) * (32 * K);
-            unsigned char* dst = my_ring + (size_t) (j % stages) * STAGE;
+            const unsigned char* src = ibase + (size_t) (4 * ig) * irow;
+            unsigned char* dst = my_ring + istage * STAGE;
             #pragma unroll
             for (int i8 = 0; i8 < K; ++i8)
             {
-                const int i = lane + 32 * i8;           // piece index: 8K pieces per tile row
-                const int row = i / (8 * K), off = (i - row * 8 * K) * 16;
-                cp_async16(dst + row * PITCH + off, src + (size_t) row * tiles_n * (32 * K) + off);
+                int row, off;                           // piece lane + 32*i8 of 8K pieces per tile row
+                if constexpr ((8 * K) % 32 == 0)
+                {
+                    row = (32 * i8) / (8 * K);
+                    off = (lane + 32 * i8 - row * 8 * K) * 16;
+                }
+                else
+                {
+                    const int i = lane + 32 * i8;
+                    row = (i >= 8 * K) + (i >= 16 * K) + (i >= 24 * K);
+                    off = (i - row * 8 * K) * 16;
+                }
+                cp_async16(dst + row * PITCH + off, src + row * irow + off);
+            }
+            iu += GEMV_KSLOTS;
+            ig += GEMV_KSLOTS;
+            if (ig >= G)
+            {
+                do { ig -= G; ++iblk; } while (ig >= G);
+                if (iu < u1) set_block(iblk);
             }
         }
         cp_async_commit();
+        if (++istage == stages) istage = 0;
     };
 
     // the weight stream does not depend on the previous kernel: start it before anything else
-    for (int j = 0; j < stages; ++j) issue(j);
+    if (iu < u1) set_block(iblk);
+    for (int j = 0; j < stages; ++j) issue();
     if (P.pdl)
     {
         pdl_launch_dependents();                       // the next kernel may start its own weight stream
         pdl_wait();                                    // x is the previous kernel's output
     }
 
-    int j = 0;                                         // this warp's next item
-    long useg = u0;
+    // per-lane constants of the consume side
+    int xrow[MB];                                      // word offset of this lane's batch row in xd
+    #pragma unroll
+    for (int mb = 0; mb < MB; ++mb) xrow[mb] = min(mb * 8 + gq, m - 1) * XPITCH + pq * 4;
+    const int w_off = pq * PITCH + gq * K * 4;                                // this lane's K words of a tile
+    const int p_off = pq * PITCH + ((gq * K + 8 * K - 1) % (8 * K)) * 4;      // the word before them (ring)
+
+    int cu = u0 + ks;                                  // this warp's next unit to consume
+    int cstage = 0;
+    int useg = u0;
     while (useg < u1)
     {
         // ---- one segment: the part of this CTA's range that lies in one column block ----
-        const int blk = (int) (useg / G);
-        const int g0 = (int) (useg - (long) blk * G);
-        const int g1 = (int) min((long) G, (long) g0 + (u1 - useg));
+        const int blk = useg / G;
+        const int g0 = useg - blk * G;
+        const int g1 = min(G, g0 + (u1 - useg));
         const int slice = blk / nbw, nb = blk - slice * nbw;
         const __half* suh = P.suh;
         const __half* svh = P.svh;
@@ -352,19 +412,18 @@ void exl3_gemv_kernel(const GemvParams P)
             else cbase += (size_t) slice * m * P.width * (P.c_fp32 ? 4 : 2);
         }
 
-        float acc[MB][4][4];
+        float acc[4][MB][4];                           // [tile of this warp's four][batch block][fragment]
         #pragma unroll
-        for (int mb = 0; mb < MB; ++mb)
+        for (int nt = 0; nt < 4; ++nt)
             #pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
-                acc[mb][nt][0] = acc[mb][nt][1] = acc[mb][nt][2] = acc[mb][nt][3] = 0.f;
+            for (int mb = 0; mb < MB; ++mb)
+                acc[nt][mb][0] = acc[nt][mb][1] = acc[nt][mb][2] = acc[nt][mb][3] = 0.f;
         float acc1[MB][4];                             // cb 2 only: sum of activations (all-ones weights)
         #pragma unroll
         for (int mb = 0; mb < MB; ++mb) acc1[mb][0] = acc1[mb][1] = acc1[mb][2] = acc1[mb][3] = 0.f;
 
         // x~ is needed in whole 128-row blocks: chunks start at an even group
-        const int ga = g0 & ~1;
-        for (int cg0 = ga; cg0 < g1; cg0 += XG)
+        for (int cg0 = g0 & ~1; cg0 < g1; cg0 += XG)
         {
             const int cg1 = min(cg0 + XG, g1);
             const int nblk = (cg1 - cg0 + 1) >> 1;      // 128-row blocks in this chunk
@@ -391,27 +450,26 @@ void exl3_gemv_kernel(const GemvParams P)
                 d.z = __byte_perm(u23, u23, 0x1010); d.w = __byte_perm(u23, u23, 0x3232);
                 const int r = jb * 128 + lane * 4;      // row inside the chunk
                 const int word = (r >> 6) * 64 + ((r & 15) >> 2) * 16 + ((r & 63) >> 4) * 4;
-                *reinterpret_cast<uint4*>(xd + b * GEMV_XPITCH + word) = d;
+                *reinterpret_cast<uint4*>(xd + b * XPITCH + word) = d;
             }
             __syncthreads();
 
-            // this warp's units of the chunk: u = u0 + ks + 4j inside [blk*G + max(cg0,g0), blk*G + cg1)
-            const long cu1 = (long) blk * G + cg1;
-            for (; u0 + ks + (long) GEMV_KSLOTS * j < cu1; ++j)
+            // this warp's units of the chunk
+            const int cu1 = blk * G + cg1;
+            const int xbase = (blk * G + cg0) * 64;     // xd word offset of unit u is u*64 - xbase
+            for (; cu < cu1; cu += GEMV_KSLOTS)
             {
-                const int g = (int) (u0 + ks + (long) GEMV_KSLOTS * j - (long) blk * G);
-                const int s = j % stages;
-                cp_async_wait(stages - 1);              // item j has landed (this lane's pieces)
+                cp_async_wait(stages - 1);              // the unit has landed (this lane's pieces)
                 __syncwarp();                           // ... and every other lane's
 
                 // duplicated activations of this lane's tile (rows 16*pq .. +15 of the group): four
-                // 16-byte loads. Batch rows >= m do not exist: read row m-1 (their MMA columns are
-                // never stored).
+                // 16-byte loads. Batch rows >= m do not exist: row m-1 is read instead (their MMA
+                // columns are never stored).
                 uint32_t xb[MB][16];
                 #pragma unroll
                 for (int mb = 0; mb < MB; ++mb)
                 {
-                    const uint32_t* xp = xd + min(mb * 8 + gq, m - 1) * GEMV_XPITCH + (g - cg0) * 64 + pq * 4;
+                    const uint32_t* xp = xd + (cu * 64 - xbase) + xrow[mb];
                     #pragma unroll
                     for (int i = 0; i < 4; ++i)
                     {
@@ -420,31 +478,17 @@ void exl3_gemv_kernel(const GemvParams P)
                     }
                 }
 
-                const unsigned char* st = my_ring + (size_t) s * STAGE + pq * PITCH;
+                const unsigned char* st = my_ring + cstage * STAGE;
                 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt)
                 {
-                    const uint32_t* tile = reinterpret_cast<const uint32_t*>(st + nt * (32 * K));
                     uint32_t w[K];
-                    load_chunk<K>(tile + gq * K, w);
-                    const uint32_t prev = tile[(gq * K + 8 * K - 1) % (8 * K)];
-                    float a4[MB][4];
-                    #pragma unroll
-                    for (int mb = 0; mb < MB; ++mb)
-                    {
-                        a4[mb][0] = acc[mb][nt][0]; a4[mb][1] = acc[mb][nt][1];
-                        a4[mb][2] = acc[mb][nt][2]; a4[mb][3] = acc[mb][nt][3];
-                    }
-                    decode_mma_r<K, CB, MB, 0>(w, prev, xb, a4);
-                    decode_mma_r<K, CB, MB, 1>(w, prev, xb, a4);
-                    decode_mma_r<K, CB, MB, 2>(w, prev, xb, a4);
-                    decode_mma_r<K, CB, MB, 3>(w, prev, xb, a4);
-                    #pragma unroll
-                    for (int mb = 0; mb < MB; ++mb)
-                    {
-                        acc[mb][nt][0] = a4[mb][0]; acc[mb][nt][1] = a4[mb][1];
-                        acc[mb][nt][2] = a4[mb][2]; acc[mb][nt][3] = a4[mb][3];
-                    }
+                    load_chunk<K>(reinterpret_cast<const uint32_t*>(st + nt * TILE_BYTES + w_off), w);
+                    const uint32_t prev = *reinterpret_cast<const uint32_t*>(st + nt * TILE_BYTES + p_off);
+                    decode_mma_r<K, CB, MB, 0>(w, prev, xb, acc[nt]);
+                    decode_mma_r<K, CB, MB, 1>(w, prev, xb, acc[nt]);
+                    decode_mma_r<K, CB, MB, 2>(w, prev, xb, acc[nt]);
+                    decode_mma_r<K, CB, MB, 3>(w, prev, xb, acc[nt]);
                 }
                 if constexpr (CB == 2)
                 {
@@ -457,7 +501,8 @@ void exl3_gemv_kernel(const GemvParams P)
                 }
 
                 __syncwarp();                           // every lane has its words in registers
-                issue(j + stages);
+                issue();
+                if (++cstage == stages) cstage = 0;
             }
         }
 
@@ -469,7 +514,7 @@ void exl3_gemv_kernel(const GemvParams P)
             #pragma unroll
             for (int nt = 0; nt < 4; ++nt)
             {
-                float d0 = acc[mb][nt][0], d1 = acc[mb][nt][1], d2 = acc[mb][nt][2], d3 = acc[mb][nt][3];
+                float d0 = acc[nt][mb][0], d1 = acc[nt][mb][1], d2 = acc[nt][mb][2], d3 = acc[nt][mb][3];
                 if constexpr (CB == 2)
                 {
                     // w = raw * k_inv + k_bias  ->  sum x*w = k_inv * sum x*raw + k_bias * sum x
@@ -490,7 +535,7 @@ void exl3_gemv_kernel(const GemvParams P)
         const int i_first = (int) ((((long) blk * G + 1) * ncta + U - 1) / U) - 1;
         const int i_last = (int) ((((long) (blk + 1) * G) * ncta + U - 1) / U) - 1;
         float* slots = P.scratch;                      // [cta][2][m][128]
-        const int my_slot = 2 * cta + ((long) blk * G > u0 ? 1 : 0);
+        const int my_slot = 2 * cta + (blk * G > u0 ? 1 : 0);
 
         for (int idx = t; idx < m * 128; idx += GEMV_THREADS)
         {
@@ -507,27 +552,32 @@ void exl3_gemv_kernel(const GemvParams P)
         bool finish = whole;
         if (!whole)
         {
-            // publish the partial, then count arrivals: the last contributor finishes the block
-            __threadfence();
+            // publish the partial, then count arrivals: the last contributor finishes the block.
+            // One thread fences after the block-wide barrier (the fence is cumulative over the
+            // stores the barrier ordered before it).
             __syncthreads();
             if (t == 0)
             {
+                __threadfence();
                 const int prev = atomicAdd(P.counters + blk, 1);
                 s_last = (prev == i_last - i_first);
-                if (s_last) P.counters[blk] = 0;        // self-reset for the next launch
+                if (s_last)
+                {
+                    P.counters[blk] = 0;                // self-reset for the next launch
+                    __threadfence();                    // acquire side: the other partials are visible
+                }
             }
             __syncthreads();
             finish = s_last != 0;
             if (finish)
             {
-                __threadfence();
                 for (int idx = t; idx < m * 128; idx += GEMV_THREADS)
                 {
                     float sum = 0.f;
                     for (int i = i_first; i <= i_last; ++i)       // ascending k: deterministic
                     {
-                        const long iu0 = U * i / ncta;
-                        const int slot = 2 * i + ((long) blk * G > iu0 ? 1 : 0);
+                        const int iu0 = (int) ((long) U * i / ncta);
+                        const int slot = 2 * i + (blk * G > iu0 ? 1 : 0);
                         sum += __ldcg(slots + (size_t) slot * m * 128 + idx);
                     }
                     part[idx] = sum;

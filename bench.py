@@ -119,7 +119,7 @@ def build_stack(torch, device, seed):
 def run_gpu(args):
     import torch
     import ampstein_b200  # noqa: F401  (raises if the CUDA library is missing)
-    from ampstein_b200.models import DecodeGraph
+    from ampstein_b200.models import DecodeGraph, Multi, Sliced
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -136,29 +136,33 @@ def run_gpu(args):
     m = 1
     layers, head = build_stack(torch, device, seed=1234 + rank)
     f16 = dict(dtype=torch.float16, device=device)
-    h_in = torch.empty((m, HIDDEN), **f16)
-    bufs = {"q": torch.empty((m, HIDDEN), **f16), "k": torch.empty((m, KV), **f16),
-            "v": torch.empty((m, KV), **f16), "a": torch.empty((m, HIDDEN), **f16),
-            "g": torch.empty((m, FFN), **f16), "u": torch.empty((m, FFN), **f16),
-            "h": torch.empty((m, HIDDEN), **f16), "logits": torch.empty((m, VOCAB), **f16)}
+    h_in = torch.empty((1, m, HIDDEN), **f16)
+    bufs = {"q": torch.empty((1, m, HIDDEN), **f16), "k": torch.empty((1, m, KV), **f16),
+            "v": torch.empty((1, m, KV), **f16), "a": torch.empty((1, m, HIDDEN), **f16),
+            "gu": torch.empty((2, m, FFN), **f16), "h": torch.empty((1, m, HIDDEN), **f16),
+            "logits": torch.empty((m, VOCAB), **f16)}
+    # the reference's decode step runs q|k|v as one sliced bundle and gate|up as one stacked bundle
+    # (src/ucode/ampstein/graphdec.uc:163-210): four launches per layer
+    qkv = [Sliced([L["q"], L["k"], L["v"]], [bufs["q"], bufs["k"], bufs["v"]]) for L in layers]
+    gu = [Multi([L["gate"], L["up"]], bufs["gu"]) for L in layers]
     launches = [0]
 
     def step():
         x = h_in
         n = 0
-        for L in layers:
-            L["q"].forward(x, bufs["q"]); L["k"].forward(x, bufs["k"]); L["v"].forward(x, bufs["v"])
-            L["o"].forward(bufs["q"], bufs["a"])          # attention itself is outside the path
-            L["gate"].forward(bufs["a"], bufs["g"]); L["up"].forward(bufs["a"], bufs["u"])
-            L["down"].forward(bufs["g"], bufs["h"])
+        for i, L in enumerate(layers):
+            qkv[i].run(x)
+            L["o"].forward(bufs["q"][0], bufs["a"][0])    # attention itself is outside the path
+            gu[i].run(bufs["a"])
+            L["down"].forward(bufs["gu"][0], bufs["h"][0])
             x = bufs["h"]
-            n += 7
-        head.forward(x, bufs["logits"])
+            n += 4
+        head.forward(x[0], bufs["logits"])
         launches[0] = n + 1
 
     host_x = torch.randn((m, HIDDEN), dtype=torch.float16).pin_memory()
     host_logits = torch.empty((m, VOCAB), dtype=torch.float16).pin_memory()
-    h_in.copy_(host_x)
+    h_in.copy_(host_x.view(1, m, HIDDEN))
     graph = DecodeGraph(step, warmup=2)
     stream = graph.stream
 
@@ -187,7 +191,7 @@ def run_gpu(args):
         graph.replay()
 
     def e2e_step():
-        h_in.copy_(host_x, non_blocking=True)
+        h_in.copy_(host_x.view(1, m, HIDDEN), non_blocking=True)
         graph.replay()
         host_logits.copy_(bufs["logits"], non_blocking=True)
 
