@@ -12,7 +12,9 @@ from .exl3 import (  # noqa: F401
     exl3_reconstruct_had,
     had_r_128,
     mgemm,
+    moe_coop,
+    moe_coop_ctr_len,
     ptr_array,
 )
 
-__all__ = ["exl3_gemm", "exl3_gemm_recon", "exl3_reconstruct", "exl3_reconstruct_had", "had_r_128", "mgemm", "ptr_array"]
+__all__ = ["exl3_gemm", "exl3_gemm_recon", "exl3_reconstruct", "exl3_reconstruct_had", "had_r_128", "mgemm", "moe_coop", "moe_coop_ctr_len", "ptr_array"]

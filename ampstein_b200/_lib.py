@@ -24,6 +24,8 @@ SIGNATURES = {
     "amp_exl3_gemv_status": [ctypes.POINTER(ctypes.c_int)],
     "amp_exl3_mgemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
     "amp_exl3_set_pdl": [_i],
+    "amp_exl3_moe_coop": [_vp, _vp],
+    "amp_exl3_moe_coop_ctr_len": [_l],
     "amp_exl3_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
 }
 
@@ -48,6 +50,7 @@ def lib():
             fn = getattr(L, name)          # AttributeError here = stale library
             fn.argtypes = args
             fn.restype = ctypes.c_int
+        L.amp_exl3_moe_coop_ctr_len.restype = ctypes.c_long
         L.amp_b200_last_error.restype = ctypes.c_char_p
         L.amp_b200_last_error.argtypes = []
         _lib = L

@@ -3,6 +3,7 @@
 // vendor/exl3/exllamav3_ext/quant/exl3_gemm.cu:114-349, maps onto).
 #include "exl3_gemv_kernel.cuh"
 #include "host_common.h"
+#include "exl3_gemv_host.h"
 #include <mutex>
 
 namespace amp {
@@ -26,18 +27,18 @@ static DevInfo& dev_info(int dev)
     return d;
 }
 
-static gemv_fn gemv_kernel_for(int K, int cb, int MB)
+static gemv_fn gemv_kernel_for(int K, int cb, int MB, int mode)
 {
     switch (K)
     {
-        case 1: return gemv_kernel_k1(cb, MB);
-        case 2: return gemv_kernel_k2(cb, MB);
-        case 3: return gemv_kernel_k3(cb, MB);
-        case 4: return gemv_kernel_k4(cb, MB);
-        case 5: return gemv_kernel_k5(cb, MB);
-        case 6: return gemv_kernel_k6(cb, MB);
-        case 7: return gemv_kernel_k7(cb, MB);
-        case 8: return gemv_kernel_k8(cb, MB);
+        case 1: return gemv_kernel_k1(cb, MB, mode);
+        case 2: return gemv_kernel_k2(cb, MB, mode);
+        case 3: return gemv_kernel_k3(cb, MB, mode);
+        case 4: return gemv_kernel_k4(cb, MB, mode);
+        case 5: return gemv_kernel_k5(cb, MB, mode);
+        case 6: return gemv_kernel_k6(cb, MB, mode);
+        case 7: return gemv_kernel_k7(cb, MB, mode);
+        case 8: return gemv_kernel_k8(cb, MB, mode);
     }
     return nullptr;
 }
@@ -77,16 +78,7 @@ static int workspace_region(int dev, int** counters, float** scratch)
     return 0;
 }
 
-struct GemvLaunch
-{
-    const void* x; const void* trellis; const void* suh; const void* svh; void* c;
-    const long long* t_trellis; const long long* t_suh; const long long* t_svh; const long long* t_c;
-    const int* t_stride; const int* t_src;
-    int tables, slices, width, stride, m, k, K, cb, c_fp32;
-    int force_split, force_stages;
-};
-
-static int g_pdl = 1;     // programmatic dependent launch on by default
+int g_pdl = 1;            // programmatic dependent launch on by default
 
 int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
 {
@@ -97,8 +89,12 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     AMP_REQUIRE(k > 0 && A.width > 0 && k % 128 == 0 && A.width % 128 == 0 && A.stride % 128 == 0,
                 "exl3_gemv: k and n must be multiples of 128");
     AMP_REQUIRE(A.slices >= 1 && (long) A.slices * (A.width / 128) <= 0x7fffffffL, "exl3_gemv: bad slice count");
-    AMP_REQUIRE(A.x && ((uintptr_t) A.x & 7) == 0, "exl3_gemv: x must be a non-null 8-byte aligned pointer");
-    if (A.tables)
+    AMP_REQUIRE(A.mode || (A.x && ((uintptr_t) A.x & 7) == 0), "exl3_gemv: x must be a non-null 8-byte aligned pointer");
+    if (A.mode)
+    {
+        AMP_REQUIRE(A.moe.runs && A.max_slices >= 1, "exl3_moe: run table missing");
+    }
+    else if (A.tables)
     {
         AMP_REQUIRE(A.t_trellis && A.t_suh && A.t_svh, "exl3_mgemm: pointer tables are required");
         AMP_REQUIRE(A.t_c || A.c, "exl3_mgemm: no output");
@@ -116,7 +112,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     const DevInfo& D = dev_info(dev);
 
     const int MB = m <= 8 ? 1 : 2;
-    gemv_fn fn = gemv_kernel_for(K, A.cb, MB);
+    gemv_fn fn = gemv_kernel_for(K, A.cb, MB, A.mode);
     if (!fn) return fail(AMP_E_UNSUPPORTED, "exl3_gemv: no kernel for K=%d cb=%d", K, A.cb);
 
     // x~ rows resident at a time: up to 16 KB per batch row (whole segments for small batches, so
@@ -138,13 +134,19 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
 
     // one contiguous range of (column block, 64-row group) units per CTA; as many CTAs as the
     // device holds at once, fewer when that would leave a CTA with less than four units
-    const long col_blocks = (long) A.slices * (A.width / 128);
+    const long col_blocks = (long) (A.mode ? A.max_slices : A.slices) * (A.width / 128);
     AMP_REQUIRE(col_blocks <= GEMV_MAX_BLOCKS, "exl3_gemv: too many column blocks (%ld)", col_blocks);
     const long units = col_blocks * (k / 64);
     AMP_REQUIRE(units < (1L << 30), "exl3_gemv: problem too large (%ld work units)", units);
     const int G = k / 64;
     long ncta = (long) D.sms * ctas_per_sm;
-    if (units / ncta < 16)
+    if (A.mode)
+    {
+        // the run count is only known on the device: size the grid for the expected load
+        const long expect = (long) A.slices * (A.width / 128) * G;
+        while (ncta > D.sms && expect / ncta < 8) ncta -= D.sms;
+    }
+    else if (units / ncta < 16)
     {
         // small problem: give every column block the same whole number of CTAs, so that a CTA
         // works on one block only (one partial-sum exchange per CTA instead of two or three)
@@ -168,6 +170,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     P.tables = A.tables; P.width = A.width; P.stride = A.stride;
     P.m = m; P.k = k; P.c_fp32 = A.c_fp32; P.stages = stages; P.xgroups = xgroups; P.pdl = g_pdl;
     P.blocks = (int) col_blocks;
+    P.moe = A.moe;
     if (int rc = workspace_region(dev, &P.counters, &P.scratch)) return rc;
     {
         // address of the status word, looked up once per device

@@ -1,0 +1,24 @@
+// Host-side launch descriptor of the decode GEMV kernel, shared by the dense / bundle entry points
+// (exl3_gemv.cu) and the grouped-expert entry point (exl3_moe.cu).
+#pragma once
+#include "exl3_gemv_kernel.cuh"
+
+namespace amp {
+
+struct GemvLaunch
+{
+    const void* x; const void* trellis; const void* suh; const void* svh; void* c;
+    const long long* t_trellis; const long long* t_suh; const long long* t_svh; const long long* t_c;
+    const int* t_stride; const int* t_src;
+    int tables, slices, width, stride, m, k, K, cb, c_fp32;
+    int force_split, force_stages;
+    int mode;            // 0 dense / bundle, 1 grouped gate+up, 2 grouped down
+    int max_slices;      // grouped modes: most slices the run table can describe (slices = the expected count)
+    GemvMoe moe;
+};
+
+int launch_gemv(const GemvLaunch& A, cudaStream_t stream);
+
+extern int g_pdl;
+
+}  // namespace amp

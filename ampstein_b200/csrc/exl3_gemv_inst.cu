@@ -11,7 +11,7 @@
 
 namespace amp {
 
-gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB)
+gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB, int mode)
 {
     static const gemv_fn fn[3][2] =
     {
@@ -19,7 +19,14 @@ gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB)
         { exl3_gemv_kernel<AMP_GEMV_K, 1, 1>, exl3_gemv_kernel<AMP_GEMV_K, 1, 2> },
         { exl3_gemv_kernel<AMP_GEMV_K, 2, 1>, exl3_gemv_kernel<AMP_GEMV_K, 2, 2> },
     };
-    if (cb < 0 || cb > 2 || MB < 1 || MB > 2) return nullptr;
+    static const gemv_fn moe[3][2] =
+    {
+        { exl3_gemv_kernel<AMP_GEMV_K, 0, 1, 1>, exl3_gemv_kernel<AMP_GEMV_K, 0, 1, 2> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 1, 1, 1>, exl3_gemv_kernel<AMP_GEMV_K, 1, 1, 2> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 1>, exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 2> },
+    };
+    if (cb < 0 || cb > 2 || MB < 1 || MB > 2 || mode < 0 || mode > 2) return nullptr;
+    if (mode) return MB == 1 ? moe[cb][mode - 1] : nullptr;
     return fn[cb][MB - 1];
 }
 

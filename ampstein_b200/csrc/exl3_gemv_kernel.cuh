@@ -51,6 +51,27 @@ constexpr int GEMV_XCHUNK_MAX = 8192;          // most rows of x~ held in shared
 constexpr int GEMV_RPITCH = 68;                // floats per row of a warp's 64-column partial
 constexpr int GEMV_MAX_STAGES = 4;
 
+// Grouped expert GEMV (fused decode MoE): the kernel's slices are expert runs described by a
+// device-side run table, the input rows are gathered per run, outputs scatter to slot rows.
+constexpr int MOE_RUN_INTS = 4;                 // per run: local expert, row count, eight slot indices as bytes
+constexpr int MOE_ACT_SILU = 0, MOE_ACT_GELU = 1, MOE_ACT_RELU2 = 2, MOE_ACT_SILU_OAI = 3;
+
+struct GemvMoe
+{
+    const int* runs;            // [0] run count, [1] active slots, then MOE_RUN_INTS per run
+    const __half* x;            // (tokens, H) input rows, row stride x_stride (gate/up stage)
+    int x_stride, H, topk;
+    const long long* trellis[3];   // per-expert pointer tables: gate, up, down
+    const long long* suh[3];
+    const long long* svh[3];
+    const long long* bias[3];      // nullable
+    void* gu[2];                // (slots, I) gate / up outputs (un-activated, after svh and bias), fp32 or fp16
+    int gu_f32;
+    float* d_out;               // (slots, Ho) fp32 down outputs (after svh and bias)
+    int Hi, I, Ho;
+    int act; float act_limit; int gated;
+};
+
 struct GemvParams
 {
     // direct mode (tables == 0): one matrix
@@ -78,6 +99,7 @@ struct GemvParams
     float* scratch;             // [gridDim.x][2][m][128] partial sums of blocks shared between CTAs
     int* counters;              // [blocks] arrival counters, zero between launches
     int* status;                // device status word (the kernel has no waits that can run out; kept for the ABI)
+    GemvMoe moe;                // grouped-expert modes only
 };
 
 __host__ __device__ constexpr int gemv_row_pitch(int K) { return 128 * K + 32; }     // bytes per tile row (4 tiles) in a stage
@@ -271,11 +293,36 @@ __device__ __forceinline__ void cp_async_wait(int pending)
     }
 }
 
+// Gated activations of the fused MoE (reference: exl3_moe_coop_kernel.cuh:79-132)
+__device__ __forceinline__ float moe_act_gate(int act, bool gated, float g, float u, float limit)
+{
+    if (act == MOE_ACT_SILU_OAI)
+    {
+        if (limit != 0.0f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+        const float glu = g * (1.0f / (1.0f + __expf(-1.702f * g)));
+        return (u + 1.0f) * glu;
+    }
+    float x;
+    if (!gated) x = fmaxf(0.0f, u);
+    else if (act == MOE_ACT_SILU) x = g * __fdividef(1.0f, 1.0f + __expf(-g));
+    else if (act == MOE_ACT_GELU)
+    {
+        const float t = 0.797884560803f * (g + 0.044715f * g * g * g);
+        x = 0.5f * g * (1.0f + tanhf(t));
+    }
+    else { x = fmaxf(0.0f, g); x = x * x; }
+    if (limit != 0.0f) { u = fminf(fmaxf(u, -limit), limit); x = fminf(x, limit); }
+    return x * u;
+}
+
 #ifndef AMP_GEMV_MINBLOCKS
 #define AMP_GEMV_MINBLOCKS 3
 #endif
 
-template <int K, int CB, int MB>
+// MODE 0: one matrix or a bundle sharing one input.  MODE 1: grouped expert gate/up (slice = expert
+// run x projection, input rows gathered by token).  MODE 2: grouped expert down (input = the
+// activation of the run's gate/up rows, computed on the fly).
+template <int K, int CB, int MB, int MODE = 0>
 __global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 2))
 void exl3_gemv_kernel(const GemvParams P)
 {
@@ -303,8 +350,19 @@ void exl3_gemv_kernel(const GemvParams P)
 
     // Work = (column block, group) units in block-major order, cut into gridDim.x equal contiguous
     // ranges: every CTA decodes the same number of weights (+-1 group) whatever the shape.
-    const int U = P.blocks * G;
-    const int cta = blockIdx.x, ncta = gridDim.x;
+    const int nproj = (MODE == 1 && P.moe.gated) ? 2 : 1;
+    if constexpr (MODE != 0)
+    {
+        // the run table is the previous kernel's output: nothing can be fetched before it exists
+        if (P.pdl) { pdl_launch_dependents(); pdl_wait(); }
+    }
+    const int U = (MODE == 0 ? P.blocks : P.moe.runs[0] * nproj * nbw) * G;
+    const int cta = blockIdx.x, ncta = min((int) gridDim.x, U);    // never more ranges than units
+    if (cta >= ncta)
+    {
+        if (MODE == 0 && P.pdl) { pdl_launch_dependents(); pdl_wait(); }
+        return;
+    }
     const int u0 = (int) ((long) U * cta / ncta), u1 = (int) ((long) U * (cta + 1) / ncta);
 
     unsigned char* my_ring = ring + (size_t) warp * stages * STAGE;
@@ -321,7 +379,14 @@ void exl3_gemv_kernel(const GemvParams P)
         const int slice = blk / nbw, nb = blk - slice * nbw;
         const unsigned char* tr = reinterpret_cast<const unsigned char*>(P.trellis);
         int stride = P.stride;
-        if (P.tables)
+        if constexpr (MODE != 0)
+        {
+            const int run = slice / nproj, proj = (MODE == 2) ? 2 : (P.moe.gated ? slice - run * nproj : 1);
+            const int expert = P.moe.runs[2 + run * MOE_RUN_INTS];
+            tr = reinterpret_cast<const unsigned char*>(P.moe.trellis[proj][expert]);
+            stride = P.width;
+        }
+        else if (P.tables)
         {
             tr = reinterpret_cast<const unsigned char*>(P.t_trellis[slice]);
             stride = P.t_stride ? P.t_stride[slice] : P.width;
@@ -375,10 +440,13 @@ void exl3_gemv_kernel(const GemvParams P)
     // the weight stream does not depend on the previous kernel: start it before anything else
     if (iu < u1) set_block(iblk);
     for (int j = 0; j < stages; ++j) issue();
-    if (P.pdl)
+    if constexpr (MODE == 0)
     {
-        pdl_launch_dependents();                       // the next kernel may start its own weight stream
-        pdl_wait();                                    // x is the previous kernel's output
+        if (P.pdl)
+        {
+            pdl_launch_dependents();                   // the next kernel may start its own weight stream
+            pdl_wait();                                // x is the previous kernel's output
+        }
     }
 
     // per-lane constants of the consume side
@@ -400,9 +468,27 @@ void exl3_gemv_kernel(const GemvParams P)
         const int slice = blk / nbw, nb = blk - slice * nbw;
         const __half* suh = P.suh;
         const __half* svh = P.svh;
+        const __half* bias = nullptr;
         unsigned char* cbase = reinterpret_cast<unsigned char*>(P.c);
         int stride = P.stride;
-        if (P.tables)
+        int nrows = m;                                 // batch rows of this segment
+        const unsigned char* run_slots = nullptr;      // grouped modes: the run's slot indices
+        if constexpr (MODE != 0)
+        {
+            const int run = slice / nproj, proj = (MODE == 2) ? 2 : (P.moe.gated ? slice - run * nproj : 1);
+            const int* rec = P.moe.runs + 2 + run * MOE_RUN_INTS;
+            const int expert = rec[0];
+            nrows = rec[1];
+            run_slots = reinterpret_cast<const unsigned char*>(rec + 2);
+            suh = reinterpret_cast<const __half*>(P.moe.suh[proj][expert]);
+            svh = reinterpret_cast<const __half*>(P.moe.svh[proj][expert]);
+            if (P.moe.bias[proj]) bias = reinterpret_cast<const __half*>(P.moe.bias[proj][expert]);
+            cbase = reinterpret_cast<unsigned char*>(MODE == 2 ? P.moe.d_out : P.moe.gu[proj]);
+            stride = P.width;
+            #pragma unroll
+            for (int mb = 0; mb < MB; ++mb) xrow[mb] = min(mb * 8 + gq, nrows - 1) * XPITCH + pq * 4;
+        }
+        else if (P.tables)
         {
             const int src = P.t_src ? P.t_src[slice] : slice;
             suh = reinterpret_cast<const __half*>(P.t_suh[src]);
@@ -431,15 +517,66 @@ void exl3_gemv_kernel(const GemvParams P)
 
             // x~ = fp16(H(x * suh) / sqrt(128)), stored duplicated ((v, v) per word) and in the
             // order the B fragments are read: word = group*64 + (row%16 / 4)*16 + (row%64 / 16)*4 + row%4
-            for (int idx = warp; idx < m * nblk; idx += GEMV_WARPS)
+            for (int idx = warp; idx < nrows * nblk; idx += GEMV_WARPS)
             {
                 const int b = idx / nblk, jb = idx - b * nblk;
                 const size_t col = (size_t) cg0 * 64 + (size_t) jb * 128 + lane * 4;
-                half4 v = *reinterpret_cast<const half4*>(P.x + (size_t) b * k + col);
-                half4 sc = *reinterpret_cast<const half4*>(suh + col);
-                v.x = __hmul2(v.x, sc.x);
-                v.y = __hmul2(v.y, sc.y);
-                float h0 = __low2float(v.x), h1 = __high2float(v.x), h2 = __low2float(v.y), h3 = __high2float(v.y);
+                float h0, h1, h2, h3;
+                if constexpr (MODE == 0)
+                {
+                    half4 v = *reinterpret_cast<const half4*>(P.x + (size_t) b * k + col);
+                    half4 sc = *reinterpret_cast<const half4*>(suh + col);
+                    v.x = __hmul2(v.x, sc.x);
+                    v.y = __hmul2(v.y, sc.y);
+                    h0 = __low2float(v.x); h1 = __high2float(v.x); h2 = __low2float(v.y); h3 = __high2float(v.y);
+                }
+                else
+                {
+                    // grouped modes scale in fp32 (reference: exl3_moe_coop_kernel.cuh:643-660, 826-838)
+                    const int slot = run_slots[b];
+                    if constexpr (MODE == 1)
+                    {
+                        const __half* xr = P.moe.x + (size_t) (slot / P.moe.topk) * P.moe.x_stride;
+                        h0 = h1 = h2 = h3 = 0.f;                  // zero padding from H to Hi
+                        if ((int) col + 3 < P.moe.H)
+                        {
+                            half4 v = *reinterpret_cast<const half4*>(xr + col);
+                            h0 = __low2float(v.x); h1 = __high2float(v.x); h2 = __low2float(v.y); h3 = __high2float(v.y);
+                        }
+                        else
+                        {
+                            if ((int) col + 0 < P.moe.H) h0 = __half2float(xr[col + 0]);
+                            if ((int) col + 1 < P.moe.H) h1 = __half2float(xr[col + 1]);
+                            if ((int) col + 2 < P.moe.H) h2 = __half2float(xr[col + 2]);
+                        }
+                    }
+                    else
+                    {
+                        float4 u4, g4;
+                        if (P.moe.gu_f32)
+                        {
+                            u4 = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.moe.gu[1]) + (size_t) slot * P.moe.I + col));
+                            g4 = u4;
+                            if (P.moe.gated) g4 = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.moe.gu[0]) + (size_t) slot * P.moe.I + col));
+                        }
+                        else
+                        {
+                            auto ld = [&](const void* base) {
+                                const uint2 r = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(base) + (size_t) slot * P.moe.I + col));
+                                const __half2 a = *reinterpret_cast<const __half2*>(&r.x), b2 = *reinterpret_cast<const __half2*>(&r.y);
+                                return make_float4(__low2float(a), __high2float(a), __low2float(b2), __high2float(b2));
+                            };
+                            u4 = ld(P.moe.gu[1]);
+                            g4 = P.moe.gated ? ld(P.moe.gu[0]) : u4;
+                        }
+                        h0 = moe_act_gate(P.moe.act, P.moe.gated, g4.x, u4.x, P.moe.act_limit);
+                        h1 = moe_act_gate(P.moe.act, P.moe.gated, g4.y, u4.y, P.moe.act_limit);
+                        h2 = moe_act_gate(P.moe.act, P.moe.gated, g4.z, u4.z, P.moe.act_limit);
+                        h3 = moe_act_gate(P.moe.act, P.moe.gated, g4.w, u4.w, P.moe.act_limit);
+                    }
+                    half4 sc = *reinterpret_cast<const half4*>(suh + col);
+                    h0 *= __low2float(sc.x); h1 *= __high2float(sc.x); h2 *= __low2float(sc.y); h3 *= __high2float(sc.y);
+                }
                 warp_had128(h0, h1, h2, h3, lane);
                 const __half2 o01 = __floats2half2_rn(h0 * kRScale, h1 * kRScale);
                 const __half2 o23 = __floats2half2_rn(h2 * kRScale, h3 * kRScale);
@@ -524,8 +661,8 @@ void exl3_gemv_kernel(const GemvParams P)
                     d2 = d2 * kinv + acc1[mb][2] * kbias; d3 = d3 * kinv + acc1[mb][3] * kbias;
                 }
                 float* r0 = red + ((size_t) warp * m + b0) * GEMV_RPITCH + nt * 16 + gq;
-                if (b0 < m) { r0[0] = d0; r0[8] = d2; }
-                if (b0 + 1 < m) { r0[GEMV_RPITCH] = d1; r0[GEMV_RPITCH + 8] = d3; }
+                if (b0 < nrows) { r0[0] = d0; r0[8] = d2; }
+                if (b0 + 1 < nrows) { r0[GEMV_RPITCH] = d1; r0[GEMV_RPITCH + 8] = d3; }
             }
         }
         __syncthreads();
@@ -537,7 +674,7 @@ void exl3_gemv_kernel(const GemvParams P)
         float* slots = P.scratch;                      // [cta][2][m][128]
         const int my_slot = 2 * cta + (blk * G > u0 ? 1 : 0);
 
-        for (int idx = t; idx < m * 128; idx += GEMV_THREADS)
+        for (int idx = t; idx < nrows * 128; idx += GEMV_THREADS)
         {
             const int b = idx >> 7, col = idx & 127;
             const int hf = col >> 6, cl = col & 63;
@@ -571,7 +708,7 @@ void exl3_gemv_kernel(const GemvParams P)
             finish = s_last != 0;
             if (finish)
             {
-                for (int idx = t; idx < m * 128; idx += GEMV_THREADS)
+                for (int idx = t; idx < nrows * 128; idx += GEMV_THREADS)
                 {
                     float sum = 0.f;
                     for (int i = i_first; i <= i_last; ++i)       // ascending k: deterministic
@@ -588,14 +725,34 @@ void exl3_gemv_kernel(const GemvParams P)
 
         if (finish)
         {
-            for (int b = warp; b < m; b += GEMV_WARPS)
+            for (int b = warp; b < nrows; b += GEMV_WARPS)
             {
                 float4 v = reinterpret_cast<const float4*>(part + b * 128)[lane];
                 float h0 = v.x, h1 = v.y, h2 = v.z, h3 = v.w;
                 warp_had128(h0, h1, h2, h3, lane);
                 h0 *= kRScale; h1 *= kRScale; h2 *= kRScale; h3 *= kRScale;
                 const half4 sv = reinterpret_cast<const half4*>(svh + (size_t) nb * 128)[lane];
-                if (P.c_fp32)
+                if constexpr (MODE != 0)
+                {
+                    // fp32 scale, optional bias, scattered to the slot's row
+                    float4 o = make_float4(h0 * __low2float(sv.x), h1 * __high2float(sv.x),
+                                           h2 * __low2float(sv.y), h3 * __high2float(sv.y));
+                    if (bias)
+                    {
+                        const half4 bv = reinterpret_cast<const half4*>(bias + (size_t) nb * 128)[lane];
+                        o.x += __low2float(bv.x); o.y += __high2float(bv.x); o.z += __low2float(bv.y); o.w += __high2float(bv.y);
+                    }
+                    if (MODE == 2 || P.moe.gu_f32)
+                        reinterpret_cast<float4*>(reinterpret_cast<float*>(cbase) + (size_t) run_slots[b] * stride + (size_t) nb * 128)[lane] = o;
+                    else
+                    {
+                        half4 oh;
+                        oh.x = __floats2half2_rn(o.x, o.y);
+                        oh.y = __floats2half2_rn(o.z, o.w);
+                        reinterpret_cast<half4*>(reinterpret_cast<__half*>(cbase) + (size_t) run_slots[b] * stride + (size_t) nb * 128)[lane] = oh;
+                    }
+                }
+                else if (P.c_fp32)
                 {
                     float4 o = make_float4(h0 * __low2float(sv.x), h1 * __high2float(sv.x),
                                            h2 * __low2float(sv.y), h3 * __high2float(sv.y));
@@ -617,8 +774,9 @@ void exl3_gemv_kernel(const GemvParams P)
 
 typedef void (*gemv_fn)(const GemvParams);
 
-// one lookup function per K, defined by the per-K translation units: (cb, MB) -> kernel
-#define AMP_GEMV_LOOKUP_DECL(K) gemv_fn gemv_kernel_k##K(int cb, int MB);
+// one lookup function per K, defined by the per-K translation units: (cb, MB, mode) -> kernel
+// (grouped-expert modes exist for MB == 1 only: a run holds at most eight rows)
+#define AMP_GEMV_LOOKUP_DECL(K) gemv_fn gemv_kernel_k##K(int cb, int MB, int mode);
 AMP_GEMV_LOOKUP_DECL(1) AMP_GEMV_LOOKUP_DECL(2) AMP_GEMV_LOOKUP_DECL(3) AMP_GEMV_LOOKUP_DECL(4)
 AMP_GEMV_LOOKUP_DECL(5) AMP_GEMV_LOOKUP_DECL(6) AMP_GEMV_LOOKUP_DECL(7) AMP_GEMV_LOOKUP_DECL(8)
 #undef AMP_GEMV_LOOKUP_DECL

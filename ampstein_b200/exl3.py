@@ -198,3 +198,99 @@ def mgemm(x, B_ptrs, C, suh_ptrs, A_had, svh_ptrs, K, mcg, mul1, opts=None):
                   n_stride.data_ptr() if n_stride is not None else None,
                   had_src.data_ptr() if had_src is not None else None, num_had_src, _stream(x))
     return C
+
+
+class _MoeArgs(__import__("ctypes").Structure):
+    """ctypes image of amp_moe_coop_args (include/ampstein_b200.h)."""
+    import ctypes as _c
+    _fields_ = [
+        ("x", _c.c_void_p), ("x_stride", _c.c_int), ("sel", _c.c_void_p), ("rw", _c.c_void_p),
+        ("bsz", _c.c_int), ("topk", _c.c_int), ("H", _c.c_int), ("Hi", _c.c_int), ("I", _c.c_int),
+        ("Ho", _c.c_int), ("H_out", _c.c_int), ("min_expert", _c.c_int), ("max_expert", _c.c_int),
+        ("n_local", _c.c_int),
+        ("g_trellis", _c.c_void_p), ("g_suh", _c.c_void_p), ("g_svh", _c.c_void_p),
+        ("u_trellis", _c.c_void_p), ("u_suh", _c.c_void_p), ("u_svh", _c.c_void_p),
+        ("d_trellis", _c.c_void_p), ("d_suh", _c.c_void_p), ("d_svh", _c.c_void_p),
+        ("g_bias", _c.c_void_p), ("u_bias", _c.c_void_p), ("d_bias", _c.c_void_p),
+        ("Kgu", _c.c_int), ("Kd", _c.c_int), ("cb", _c.c_int), ("act", _c.c_int),
+        ("act_limit", _c.c_float), ("gated", _c.c_int),
+        ("gu_g", _c.c_void_p), ("gu_u", _c.c_void_p), ("gu_f32", _c.c_int), ("d_out", _c.c_void_p),
+        ("ctr", _c.c_void_p), ("slots_max", _c.c_int),
+        ("out", _c.c_void_p), ("out_stride", _c.c_int),
+        ("sh_out", _c.c_void_p), ("sh_gate_w", _c.c_void_p),
+    ]
+
+
+def moe_coop_ctr_len(slots_max):
+    return int(_lib.lib().amp_exl3_moe_coop_ctr_len(int(slots_max)))
+
+
+def moe_coop(x, sel, rw, cfg, sh_out=None):
+    """Fused decode-shaped MoE (reference: torch.moe_coop, src/torch/amp_torch.cpp:7852-7934):
+    every (token, expert) slot of x through gate/up, the activation and down, weighted by rw and
+    summed per token into cfg["out"] (fp32). Routing stays on the device. cfg holds the static
+    parts under the reference's keys: int64 pointer tables g_trellis g_suh g_svh u_* d_*, scratch
+    gu_g gu_u d_out ctr out, numbers Hi Kg Ku Kd act act_limit min_expert max_expert, booleans
+    mcg mul1 (had_g, had_u, act_out are accepted and unused; optional g_bias u_bias d_bias tables,
+    sh_gate_w, gated)."""
+    import ctypes
+    if not isinstance(cfg, dict):
+        raise TypeError("moe_coop: cfg must be an object")
+    need = ["g_trellis", "g_suh", "g_svh", "u_trellis", "u_suh", "u_svh", "d_trellis", "d_suh", "d_svh",
+            "gu_g", "gu_u", "d_out", "ctr", "out"]
+    for n in need:
+        if not isinstance(cfg.get(n), torch.Tensor):
+            raise TypeError("moe_coop: cfg.%s must be a tensor" % n)
+    _check_cuda("moe_coop", x, sel, rw)
+    if x.dtype != torch.float16 or sel.dtype != torch.int64 or rw.dtype != torch.float16:
+        raise TypeError("moe_coop: x fp16, sel int64, rw fp16 expected")
+    if sel.shape != rw.shape or sel.dim() != 2 or sel.shape[0] != x.shape[0] or x.dim() != 2:
+        raise ValueError("exl3_moe_coop: sel/rw must be (bsz, topk)")
+    for n in ("g_trellis", "g_suh", "g_svh", "u_trellis", "u_suh", "u_svh", "d_trellis", "d_suh", "d_svh"):
+        if cfg[n].dtype != torch.int64 or not cfg[n].is_contiguous():
+            raise TypeError("exl3_moe_coop: pointer tables must be contiguous int64")
+    if cfg["ctr"].dtype != torch.int32:
+        raise TypeError("exl3_moe_coop: ctr must be int32")
+    if cfg["d_out"].dtype != torch.float32 or cfg["out"].dtype != torch.float32:
+        raise TypeError("exl3_moe_coop: d_out and out must be float32")
+    gu_dt = cfg["gu_u"].dtype
+    if gu_dt not in (torch.float16, torch.float32) or cfg["gu_g"].dtype != gu_dt:
+        raise TypeError("exl3_moe_coop: gate/up scratch dtype mismatch")
+    mcg, mul1 = bool(cfg.get("mcg", False)), bool(cfg.get("mul1", False))
+    Kg, Ku, Kd = cfg.get("Kg", 0), cfg.get("Ku", 0), cfg.get("Kd", 0)
+    gated = bool(cfg.get("gated", True))
+    if gated and Kg != Ku:
+        raise ValueError("exl3_moe_coop: gate and up must share a bit width")
+    I, Ho = cfg["gu_u"].shape[-1], cfg["d_out"].shape[-1]
+    out = cfg["out"]
+    slots_max = min(cfg["gu_g"].numel() // I, cfg["gu_u"].numel() // I, cfg["d_out"].numel() // Ho)
+    bsz, topk = sel.shape
+    if bsz > out.shape[-2]:
+        raise ValueError("exl3_moe_coop: batch exceeds the scratch")
+    if cfg["ctr"].numel() < moe_coop_ctr_len(slots_max):
+        raise ValueError("exl3_moe_coop: counter scratch too small")
+    if sh_out is not None:
+        _check_cuda("moe_coop", sh_out)
+        if sh_out.dtype != torch.float32 or sh_out.shape[-1] != x.shape[1] or sh_out.numel() < x.numel():
+            raise ValueError("exl3_moe_coop: shared expert output shape")
+    a = _MoeArgs()
+    p = lambda t: t.data_ptr() if t is not None else None
+    a.x, a.x_stride, a.sel, a.rw = p(x), x.stride(0), p(sel), p(rw)
+    a.bsz, a.topk, a.H = bsz, topk, x.shape[1]
+    a.Hi, a.I, a.Ho, a.H_out = int(cfg.get("Hi", 0)), I, Ho, out.shape[-1]
+    a.min_expert, a.max_expert = int(cfg.get("min_expert", -1)), int(cfg.get("max_expert", -1))
+    a.n_local = cfg["u_trellis"].shape[0]
+    for n in ("g_trellis", "g_suh", "g_svh", "u_trellis", "u_suh", "u_svh", "d_trellis", "d_suh", "d_svh"):
+        setattr(a, n, p(cfg[n]))
+    for n in ("g_bias", "u_bias", "d_bias"):
+        setattr(a, n, p(cfg.get(n)))
+    a.Kgu, a.Kd, a.cb = int(Ku), int(Kd), _cb(mul1, mcg)
+    a.act, a.act_limit, a.gated = int(cfg.get("act", 0)), float(cfg.get("act_limit", 0.0)), int(gated)
+    a.gu_g, a.gu_u, a.gu_f32, a.d_out = p(cfg["gu_g"]), p(cfg["gu_u"]), int(gu_dt == torch.float32), p(cfg["d_out"])
+    a.ctr, a.slots_max = p(cfg["ctr"]), slots_max
+    a.out, a.out_stride = p(out), out.stride(-2)
+    a.sh_out = p(sh_out)
+    a.sh_gate_w = p(cfg.get("sh_gate_w"))
+    with torch.cuda.device(x.device):
+        _lib.call("amp_exl3_moe_coop", ctypes.byref(a), _stream(x))
+    return None

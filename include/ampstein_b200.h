@@ -115,6 +115,55 @@ int amp_exl3_mgemm(const void* x, const void* trellis_ptrs, void* C, const void*
                    const void* had_src_list, int num_had_src, cudaStream_t stream);
 
 /*
+ * Fused decode-shaped MoE: out[row] = sum over the row's active picks of rw * expert(x[row]),
+ * expert = down(act(gate(x), up(x))), plus an optional shared-expert term. Up to 256
+ * (token, pick) slots per call. Routing (sel, rw) is read on the device; nothing synchronises.
+ * Replaces: exl3_moe_coop, Q/exl3_moe_coop.cu:309-371 and its parameter block MoeCoopParams,
+ * Q/exl3_moe_coop.cuh:21-83 (binding torch.moe_coop, src/torch/amp_torch.cpp:7852-7934). Fields
+ * keep the reference's names and meaning; scratch the new kernels do not need (had_g, had_u,
+ * act_out) has no field.
+ */
+typedef struct amp_moe_coop_args
+{
+    const void* x;              /* (bsz, H) fp16, row stride x_stride */
+    int x_stride;
+    const void* sel;            /* (bsz, topk) int64 global expert indices */
+    const void* rw;             /* (bsz, topk) fp16 routing weights (0 = inactive pick) */
+    int bsz, topk;
+    int H;                      /* x width (<= Hi, multiple of 4) */
+    int Hi, I, Ho;              /* padded gate/up input, intermediate, down output widths (x128) */
+    int H_out;                  /* output width (<= Ho) */
+    int min_expert, max_expert; /* min_expert < 0: no range filter; else sel in [min, max) is local */
+    int n_local;                /* entries in the pointer tables */
+    /* per-expert int64 device pointer tables, indexed by local expert */
+    const void* g_trellis; const void* g_suh; const void* g_svh;
+    const void* u_trellis; const void* u_suh; const void* u_svh;
+    const void* d_trellis; const void* d_suh; const void* d_svh;
+    const void* g_bias; const void* u_bias; const void* d_bias;   /* nullable */
+    int Kgu, Kd;                /* bit widths of gate/up and down */
+    int cb;                     /* codebook, uniform across the three projections */
+    int act;                    /* 0 silu, 1 gelu, 2 relu2, 3 gpt-oss clamped swiglu */
+    float act_limit;
+    int gated;                  /* 0: no gate projection, activation is relu(u) * u */
+    /* scratch, leading dimension >= slots_max */
+    void* gu_g; void* gu_u;     /* (slots_max, I) fp32 (gu_f32 = 1) or fp16 (gu_f32 = 0) */
+    int gu_f32;
+    void* d_out;                /* (slots_max, Ho) fp32 */
+    int* ctr;                   /* int32, amp_exl3_moe_coop_ctr_len(slots_max) entries: the run table */
+    int slots_max;
+    void* out;                  /* (bsz, H_out) fp32, row stride out_stride */
+    int out_stride;
+    const void* sh_out;         /* nullable: (bsz, H) fp32 shared-expert output */
+    const void* sh_gate_w;      /* nullable: (H) fp16, gate = sigmoid(x . w) */
+} amp_moe_coop_args;
+
+int amp_exl3_moe_coop(const amp_moe_coop_args* args, cudaStream_t stream);
+
+/* Length (int32 entries) of the ctr scratch for slots_max slots. Replaces
+ * exl3_moe_coop_ctr_len, Q/exl3_moe_coop.cuh:164-167. */
+long amp_exl3_moe_coop_ctr_len(long slots_max);
+
+/*
  * Programmatic dependent launch of the decode kernels (default on): each kernel starts its
  * weight stream before waiting for the kernel in front of it. Returns the previous setting.
  * The reference has no counterpart (it launches cooperative kernels back to back).

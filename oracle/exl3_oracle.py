@@ -184,3 +184,61 @@ def allreduce_fp16(parts):
 
 def num_threads():
     return lib().exl3o_num_threads()
+
+
+def moe_coop(x, sel, rw, experts, act=0, act_limit=0.0, gated=True, min_expert=-1, max_expert=-1,
+             cb=0, H_out=None, sh_out=None, sh_gate_w=None, gu_f16=False, biases=None):
+    """Fused decode MoE on the CPU. experts: list of dicts with keys gate/up/down, each a
+    (trellis, suh, svh) triple (gate may be None when not gated). Returns fp32 (bsz, H_out)."""
+    xx = _h(x)
+    bsz, H = xx.shape
+    topk = sel.shape[1]
+    up0, dn0 = experts[0]["up"], experts[0]["down"]
+    Hi, I, _ = trellis_dims(_h(up0[0]))
+    _, Ho, _ = trellis_dims(_h(dn0[0]))
+    H_out = H if H_out is None else H_out
+    keep, tabs = [], {}
+    PP = ctypes.POINTER(ctypes.c_uint16)
+
+    def table(fn):
+        arr = (PP * len(experts))()
+        for i, e in enumerate(experts):
+            a = fn(e)
+            if a is None:
+                arr[i] = None
+            else:
+                a = np.ascontiguousarray(_h(a))
+                keep.append(a)
+                arr[i] = _p16(a)
+        return arr
+
+    whats = {}
+    for name in ("gate", "up", "down"):
+        whats[name] = table(lambda e, n=name: reconstruct(e[n][0], cb) if e.get(n) is not None else None)
+        tabs[name + "_suh"] = table(lambda e, n=name: e[n][1] if e.get(n) is not None else None)
+        tabs[name + "_svh"] = table(lambda e, n=name: e[n][2] if e.get(n) is not None else None)
+    bias_t = []
+    for name in ("gate", "up", "down"):
+        if biases is not None and biases.get(name) is not None:
+            bias_t.append(table(lambda e, n=name, bb=biases: bb[n][experts.index(e)]))
+        else:
+            bias_t.append(None)
+    selc = np.ascontiguousarray(sel, dtype=np.int64)
+    rwc = np.ascontiguousarray(_h(rw))
+    out = np.zeros((bsz, H_out), np.float32)
+    sh = np.ascontiguousarray(sh_out, dtype=np.float32) if sh_out is not None else None
+    shg = np.ascontiguousarray(_h(sh_gate_w)) if sh_gate_w is not None else None
+    L = lib()
+    L.exl3o_moe_coop.restype = ctypes.c_int
+    rc = L.exl3o_moe_coop(
+        _p16(xx), ctypes.c_int(xx.strides[0] // 2), selc.ctypes.data_as(ctypes.POINTER(ctypes.c_int64)), _p16(rwc),
+        bsz, topk, H, Hi, I, Ho, H_out, min_expert, max_expert, len(experts),
+        whats["gate"], whats["up"], whats["down"],
+        tabs["gate_suh"], tabs["up_suh"], tabs["down_suh"],
+        tabs["gate_svh"], tabs["up_svh"], tabs["down_svh"],
+        bias_t[0], bias_t[1], bias_t[2],
+        act, ctypes.c_float(act_limit), int(gated), int(gu_f16),
+        _p32(sh) if sh is not None else None, _p16(shg) if shg is not None else None,
+        _p32(out), ctypes.c_int(out.strides[0] // 4))
+    assert rc == 0, rc
+    return out

@@ -197,6 +197,39 @@ def test_allreduce_rank_order_sum(oracle):
     assert np.array_equal(got.view(np.uint16), acc.astype(np.float16).view(np.uint16))
 
 
+def test_moe_oracle_equals_composition_of_linears(oracle):
+    """The MoE oracle against float64 algebra in the original basis: every expert is
+    down(silu(gate x) * up x) with dense original-basis weights."""
+    rng = np.random.default_rng(12)
+    Hi, I, Ho, K = 128, 128, 128, 4
+    H = sylvester(128)
+
+    def dense(trellis, suh, svh):
+        what = oracle.reconstruct(trellis, 0).astype(np.float64)
+        return suh.astype(np.float64)[:, None] * (H @ what @ H / 128.0) * svh.astype(np.float64)[None, :]
+
+    ex, Ws = [], []
+    for e in range(3):
+        trip = []
+        for s, (k, n) in enumerate(((Hi, I), (Hi, I), (I, Ho))):
+            t, su, sv, _ = make_linear(k, n, K, seed=40 + 3 * e + s)
+            sv = (sv.astype(np.float32) / (1.2437 * np.sqrt(k))).astype(np.float16)
+            trip.append((t, su, sv))
+        ex.append({"gate": trip[0], "up": trip[1], "down": trip[2]})
+        Ws.append([dense(*t) for t in trip])
+    x = rng.standard_normal((2, Hi)).astype(np.float16)
+    sel = np.array([[0, 2], [1, 0]], np.int64)
+    rw = np.array([[0.7, 0.3], [0.4, 0.6]], np.float16)
+    got = oracle.moe_coop(x, sel, rw, ex)
+    want = np.zeros((2, Ho))
+    for r in range(2):
+        for k in range(2):
+            Wg, Wu, Wd = Ws[sel[r, k]]
+            g, u = x[r].astype(np.float64) @ Wg, x[r].astype(np.float64) @ Wu
+            want[r] += float(rw[r, k]) * ((g / (1 + np.exp(-g)) * u) @ Wd)
+    assert rel_rms(got, want) < 5e-3
+
+
 def test_empty_shapes(oracle):
     assert oracle.reconstruct(np.zeros((0, 8, 64), np.uint16), 0).shape == (0, 128)
 
