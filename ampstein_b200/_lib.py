@@ -24,6 +24,16 @@ SIGNATURES = {
     "amp_exl3_gemv_status": [ctypes.POINTER(ctypes.c_int)],
     "amp_exl3_mgemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
     "amp_exl3_set_pdl": [_i],
+    "amp_comm_allreduce_fp16": [_vp, _vp, _vp, _vp, _i, _i, _l, _l, _i, _i, _vp],
+    "amp_comm_buffer_bytes": [_i, _l],
+    "amp_comm_ctl_bytes": [],
+    "amp_comm_blocks": [_i, _l],
+    "amp_comm_status": [_vp, ctypes.POINTER(ctypes.c_int)],
+    "amp_comm_enable_peer": [_i],
+    "amp_comm_ipc_alloc": [_l, ctypes.POINTER(ctypes.c_void_p), _vp],
+    "amp_comm_ipc_open": [_vp, ctypes.POINTER(ctypes.c_void_p)],
+    "amp_comm_ipc_close": [_vp],
+    "amp_comm_free": [_vp],
     "amp_exl3_moe_coop": [_vp, _vp],
     "amp_exl3_moe_coop_ctr_len": [_l],
     "amp_exl3_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
@@ -51,6 +61,8 @@ def lib():
             fn.argtypes = args
             fn.restype = ctypes.c_int
         L.amp_exl3_moe_coop_ctr_len.restype = ctypes.c_long
+        L.amp_comm_buffer_bytes.restype = ctypes.c_long
+        L.amp_comm_ctl_bytes.restype = ctypes.c_long
         L.amp_b200_last_error.restype = ctypes.c_char_p
         L.amp_b200_last_error.argtypes = []
         _lib = L

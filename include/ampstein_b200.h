@@ -177,6 +177,46 @@ int amp_exl3_set_pdl(int enable);
  */
 int amp_exl3_gemv_status(int* out);
 
+/*
+ * ---- tensor-parallel decode: fp16 all-reduce over peer-mapped memory (NVLink) ----
+ *
+ * rank's part of an N-way (2..8) all-reduce of the ranks' contiguous fp16 partials: x and out are
+ * n halves on this rank's device (n % 8 == 0, n <= cap); bufs[p] / ctls[p] are every rank's buffer
+ * and control block as THIS process addresses them (peer access or IPC mappings), each
+ * zero-filled once before the first call and sized by amp_comm_buffer_bytes / amp_comm_ctl_bytes.
+ * All ranks must issue the same sequence of calls with the same n, mode and blocks. mode 0 =
+ * one-shot, 1 = two-phase (reduce-scatter + all-gather); blocks 1..16 (amp_comm_blocks gives the
+ * value every rank should use). The sum accumulates in fp32 in rank order and rounds once:
+ * bit-identical on every rank. Graph-capturable; waits on peers are bounded (a rank that never
+ * arrives makes the call return with the status word set, it does not trap).
+ * Same signature and return convention (a cudaError_t) as the reference:
+ * amp_comm_allreduce_fp16, src/torch/amp_kernels.cu:2966-2986 (binding comm.allreduce,
+ * src/torch/amp_torch.cpp:7710-7759). The buffer layout differs from the reference's (the flags
+ * travel inside the data), hence the sizing functions below; the reference sizes its buffers
+ * in torch_p2p_comm, src/torch/amp_torch.cpp:7682-7689.
+ */
+int amp_comm_allreduce_fp16(const void* x, void* out, void* const* bufs, int* const* ctls,
+                            int rank, int N, long n, long cap, int mode, int blocks,
+                            cudaStream_t stream);
+long amp_comm_buffer_bytes(int N, long cap);
+long amp_comm_ctl_bytes(void);
+int amp_comm_blocks(int N, long n);
+
+/* Reads and clears the status word of a LOCAL control block (non-zero: a wait for a peer ran
+ * out). Synchronises; diagnostics only. The reference has no counterpart (its kernel traps,
+ * src/torch/amp_kernels.cu:2835-2839). */
+int amp_comm_status(int* ctl, int* out);
+
+/* Set-up helpers for communicator construction (allocate; never on the hot path). The
+ * reference builds its communicator inside one process (torch_p2p_comm,
+ * src/torch/amp_torch.cpp:7606-7708); these cover both that case (enable_peer) and one process
+ * per GPU (CUDA IPC: alloc exports a 64-byte handle, open maps a peer's). */
+int amp_comm_enable_peer(int peer);
+int amp_comm_ipc_alloc(long bytes, void** ptr, void* handle64);
+int amp_comm_ipc_open(const void* handle64, void** ptr);
+int amp_comm_ipc_close(void* ptr);
+int amp_comm_free(void* ptr);
+
 #ifdef __cplusplus
 }
 #endif

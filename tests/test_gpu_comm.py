@@ -1,0 +1,115 @@
+"""GPU tests of the NVLink all-reduce. Ranks run on DIFFERENT GPUs (kernels that wait on one
+another are never co-scheduled on one device); with fewer GPUs than ranks the tests skip. The
+bounded-wait test uses one kernel on one GPU whose peer never arrives."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from conftest import ROOT
+
+
+def ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def partial(rank, n, call):
+    i = np.arange(n, dtype=np.float64)
+    return (np.sin(0.37 * i + 1.7 * rank + 0.11 * call) * (1.0 + 0.25 * rank)).astype(np.float16)
+
+
+@pytest.mark.parametrize("mode", ["oneshot", "twophase"])
+def test_allreduce_exact_single_process(oracle, mode):
+    """Every N = 2..min(GPUs, 8): result == fp32 rank-order sum rounded once (exact), identical on
+    all ranks, 21 back-to-back calls over 7 sizes including ones no rank count divides."""
+    if ngpu() < 2:
+        pytest.skip("needs at least two GPUs")
+    from ampstein_b200.comm import p2p_comm
+    sizes = [8, 5120, 40, 40960, 1000 * 8, 8 * 1237, 65536]
+    for N in range(2, min(ngpu(), 8) + 1):
+        comm = p2p_comm(list(range(N)), 65536, mode)
+        for call in range(21):
+            n = sizes[call % len(sizes)]
+            parts = [partial(r, n, call) for r in range(N)]
+            outs = []
+            for r in range(N):
+                x = torch.from_numpy(parts[r]).to("cuda:%d" % r)
+                outs.append(comm.allreduce(x, r))
+            want = oracle.allreduce_fp16(parts).view(np.uint16)
+            for r in range(N):
+                got = outs[r].cpu().numpy().view(np.uint16)
+                assert np.array_equal(got, want), (N, call, n, r)
+        for r in range(N):
+            assert comm.status(r) == 0
+        comm.close()
+
+
+def test_allreduce_inside_cuda_graphs(oracle):
+    """64 all-reduces captured in one CUDA graph per rank and replayed: the call sequence number
+    lives on the device."""
+    if ngpu() < 2:
+        pytest.skip("needs at least two GPUs")
+    from ampstein_b200.comm import p2p_comm
+    N, n = 2, 5120
+    comm = p2p_comm([0, 1], 5120)
+    xs = [torch.from_numpy(partial(r, n, 0)).to("cuda:%d" % r) for r in range(N)]
+    for r in range(N):                         # warm-up outside capture
+        comm.allreduce(xs[r], r)
+    for r in range(N):
+        torch.cuda.synchronize(r)
+    graphs, outs = [], []
+    for r in range(N):
+        with torch.cuda.device(r):
+            g = torch.cuda.CUDAGraph()
+            s = torch.cuda.Stream()
+            with torch.cuda.stream(s), torch.cuda.graph(g, stream=s):
+                y = xs[r]
+                for _ in range(64):
+                    y = comm.allreduce(xs[r], r)
+            graphs.append(g)
+            outs.append(y)
+    for rep in range(3):
+        for r in range(N):
+            with torch.cuda.device(r):
+                graphs[r].replay()
+        for r in range(N):
+            torch.cuda.synchronize(r)
+    want = oracle.allreduce_fp16([partial(r, n, 0) for r in range(N)]).view(np.uint16)
+    for r in range(N):
+        assert np.array_equal(outs[r].cpu().numpy().view(np.uint16), want)
+        assert comm.status(r) == 0
+    comm.close()
+
+
+def test_one_process_per_gpu_over_torch_distributed(oracle):
+    """torchrun-style: two processes, one GPU each, buffers exchanged as CUDA IPC handles."""
+    if ngpu() < 2:
+        pytest.skip("needs at least two GPUs")
+    script = os.path.join(ROOT, "tests", "comm_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29731", script],
+                       capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "comm_worker ok rank 0" in r.stdout and "comm_worker ok rank 1" in r.stdout
+
+
+def test_wait_for_a_missing_peer_runs_out_and_reports():
+    """A rank whose peer never launches: the kernel's bounded wait expires (about a second), the
+    call returns, the status word says so and the context stays usable. One kernel, one GPU,
+    nothing it waits for ever runs."""
+    from ampstein_b200.comm import P2PComm
+    comm = P2PComm.single_process([0, 0], 1024)          # both ranks' buffers on device 0
+    x = torch.ones(1024, dtype=torch.float16, device="cuda:0")
+    out = comm.allreduce(x, 0)                           # rank 1 never calls
+    torch.cuda.synchronize()
+    assert comm.status(0) == 1
+    assert comm.status(0) == 0                           # reading clears it
+    y = (out.float() + 1).sum().item()                   # the context still works
+    assert np.isfinite(y)
+    comm.close()
