@@ -188,6 +188,32 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 }
 
 // ------------------------------------------------------------------------------------------
+// cp.async (16-byte global -> shared copies, per-thread commit groups)
+// ------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(dst)), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit()
+{
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// wait until at most `pending` of this thread's committed groups are still in flight
+__device__ __forceinline__ void cp_async_wait(int pending)
+{
+    switch (pending)
+    {
+        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // mma.sync m16n8k16, fp16 operands, fp32 accumulate (register operands: the decoded weights
 // never touch shared memory)
 // ------------------------------------------------------------------------------------------

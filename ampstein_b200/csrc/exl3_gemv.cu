@@ -241,23 +241,45 @@ AMP_API int amp_exl3_set_pdl(int enable)
     return old;
 }
 
-// C = had(A*suh) @ W_hat -> had(.)*svh for any m. A_had (scratch of A's size in the reference's
-// signature) is accepted for drop-in compatibility and not used: the input transform lives in
-// each CTA's prologue. Rows are processed in slabs of 16 by the GEMV kernel.
+namespace amp {
+int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh, int M, int k, int n,
+                   int K, int cb, int c_fp32, cudaStream_t stream);
+}
+extern "C" int amp_had_r_128(const void* in, void* out, const void* pre, const void* post,
+                             long rows, int cols, int dtype, float scale, cudaStream_t stream);
+
+// C = had(A*suh) @ W_hat -> had(.)*svh for any m. Up to 16 rows run on the decode kernel (A_had is
+// then unused: the input transform lives in the kernel's prologue); more rows take the
+// tensor-core path: x~ is written into A_had (same shape as A, fp16: required) by the Hadamard
+// kernel and the tcgen05 GEMM consumes it. a_bf16: A holds bf16 instead of fp16 (m > 16 only).
+static int gemm_any(const void* A, int a_bf16, const void* trellis, void* C, const void* suh, void* A_had,
+                    const void* svh, int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream)
+{
+    AMP_REQUIRE(m >= 0, "exl3_gemm: negative m");
+    if (m == 0) return 0;
+    if (m <= 16 && !a_bf16)
+        return launch_gemv(direct(A, trellis, C, suh, svh, m, k, n, K, cb, c_fp32, 0, 0), stream);
+    AMP_REQUIRE(A_had, "exl3_gemm: A_had scratch (same shape as A, fp16) is required above 16 rows");
+    AMP_REQUIRE(A && suh && k > 0 && k % 128 == 0, "exl3_gemm: bad input");
+    if (int rc = amp_had_r_128(A, A_had, suh, nullptr, m, k, a_bf16 ? 2 : 0, 1.0f, stream)) return rc;
+    return launch_gemm_tc(A_had, trellis, C, svh, m, k, n, K, cb, c_fp32, stream);
+}
+
 AMP_API int amp_exl3_gemm(const void* A, const void* trellis, void* C, const void* suh, void* A_had,
                           const void* svh, int m, int k, int n, int K, int cb, int c_fp32,
                           cudaStream_t stream)
 {
-    (void) A_had;
-    AMP_REQUIRE(m >= 0, "exl3_gemm: negative m");
-    for (int r = 0; r < m; r += 16)
-    {
-        const int rows = m - r < 16 ? m - r : 16;
-        const char* a = (const char*) A + (size_t) r * k * 2;
-        char* c = (char*) C + (size_t) r * n * (c_fp32 ? 4 : 2);
-        if (int rc = launch_gemv(direct(a, trellis, c, suh, svh, rows, k, n, K, cb, c_fp32, 0, 0), stream)) return rc;
-    }
-    return 0;
+    return gemm_any(A, 0, trellis, C, suh, A_had, svh, m, k, n, K, cb, c_fp32, stream);
+}
+
+// Same with bf16 activations (prefill). The reference has no bf16 form (exl3_gemm checks for
+// fp16, vendor/exl3/exllamav3_ext/quant/exl3_gemm.cu:136); the conversion is folded into the
+// input rotation: fp32 scale, fp32 Hadamard, one rounding to fp16.
+AMP_API int amp_exl3_gemm_bf16(const void* A, const void* trellis, void* C, const void* suh, void* A_had,
+                               const void* svh, int m, int k, int n, int K, int cb, int c_fp32,
+                               cudaStream_t stream)
+{
+    return gemm_any(A, 1, trellis, C, suh, A_had, svh, m, k, n, K, cb, c_fp32, stream);
 }
 
 // Several EXL3 matrices (or equal-width column slices of matrices) against ONE shared input in a

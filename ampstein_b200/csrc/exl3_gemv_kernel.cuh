@@ -271,28 +271,6 @@ __device__ __forceinline__ void pdl_wait()
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
-__device__ __forceinline__ void cp_async16(void* dst, const void* src)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(dst)), "l"(src) : "memory");
-}
-
-__device__ __forceinline__ void cp_async_commit()
-{
-    asm volatile("cp.async.commit_group;" ::: "memory");
-}
-
-// wait until at most `pending` of this thread's committed groups are still in flight
-__device__ __forceinline__ void cp_async_wait(int pending)
-{
-    switch (pending)
-    {
-        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-        default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-    }
-}
-
 // Gated activations of the fused MoE (reference: exl3_moe_coop_kernel.cuh:79-132)
 __device__ __forceinline__ float moe_act_gate(int act, bool gated, float g, float u, float limit)
 {

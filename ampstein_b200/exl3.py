@@ -110,8 +110,8 @@ def exl3_gemm(A, B, C, suh, svh, mul1=False, mcg=False):
         raise TypeError("expected (A, B, C, suh, svh, mul1?, mcg?)")
     _check_cuda("exl3_gemm", A, B, C, suh, svh)
     k, n, K = _trellis_dims("exl3_gemm", B)
-    if A.dtype != torch.float16 or suh.dtype != torch.float16 or svh.dtype != torch.float16:
-        raise TypeError("exl3_gemm: A, suh, svh must be float16")
+    if A.dtype not in (torch.float16, torch.bfloat16) or suh.dtype != torch.float16 or svh.dtype != torch.float16:
+        raise TypeError("exl3_gemm: A must be float16 (or bfloat16), suh and svh float16")
     if C.dtype not in (torch.float16, torch.float32):
         raise TypeError("exl3_gemm: C must be float16 or float32")
     if A.shape[-1] != k or C.shape[-1] != n:
@@ -122,10 +122,14 @@ def exl3_gemm(A, B, C, suh, svh, mul1=False, mcg=False):
         raise ValueError("exl3_gemm: incompatible shapes")
     if m == 0:
         return C
+    bf16 = A.dtype == torch.bfloat16
+    # the binding allocates the input-rotation scratch per call, as the reference's does
+    # (src/torch/amp_torch.cpp:11282); the decode kernel (<= 16 rows) does not need it
+    A_had = torch.empty(A.shape, dtype=torch.float16, device=A.device) if (m > 16 or bf16) else None
     with torch.cuda.device(A.device):
-        _lib.call("amp_exl3_gemm", A.data_ptr(), B.data_ptr(), C.data_ptr(), suh.data_ptr(), None,
-                  svh.data_ptr(), m, k, n, K, _cb(mul1, mcg), 1 if C.dtype == torch.float32 else 0,
-                  _stream(A))
+        _lib.call("amp_exl3_gemm_bf16" if bf16 else "amp_exl3_gemm", A.data_ptr(), B.data_ptr(), C.data_ptr(),
+                  suh.data_ptr(), A_had.data_ptr() if A_had is not None else None, svh.data_ptr(), m, k, n, K,
+                  _cb(mul1, mcg), 1 if C.dtype == torch.float32 else 0, _stream(A))
     return C
 
 

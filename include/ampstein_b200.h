@@ -58,7 +58,8 @@ int amp_exl3_reconstruct_had(void* unpacked, const void* trellis, const void* su
 
 /*
  * Blockwise 128-point Hadamard of a (rows, cols) matrix, out = H(in [* pre]) * scale/sqrt(128)
- * [* post]; in place allowed. dtype 0 = fp16, 1 = fp32. pre / post: fp16 (cols) or NULL.
+ * [* post]; in place allowed. dtype 0 = fp16, 1 = fp32, 2 = bf16 in / fp16 out (not in place).
+ * pre / post: fp16 (cols) or NULL.
  * Replaces: had_r_128, Q/hadamard.cu:125-207.
  */
 int amp_had_r_128(const void* in, void* out, const void* pre, const void* post,
@@ -66,14 +67,29 @@ int amp_had_r_128(const void* in, void* out, const void* pre, const void* post,
 
 /*
  * EXL3 linear, any m: C (m, n) fp16 (c_fp32 = 0) or fp32 (c_fp32 = 1) = A (m, k) fp16 through
- * the quantized weight. suh and svh are required. A_had is the reference's scratch argument
- * (same size as A); it is accepted and not used. k and n multiples of 128.
+ * the quantized weight. suh and svh are required. k and n multiples of 128. Up to 16 rows run on
+ * the decode kernel; more rows on the tensor-core (tcgen05) prefill kernel, which needs A_had:
+ * the reference's scratch argument, fp16, same shape as A (it receives the rotated input).
  * Replaces: exl3_gemm, Q/exl3_gemm.cu:114-349 (binding torch.exl3_gemm,
- * src/torch/amp_torch.cpp:11250-11293), including its GEMV dispatch Q/exl3_gemv.cu:92-184.
+ * src/torch/amp_torch.cpp:11250-11293), including its GEMV dispatch Q/exl3_gemv.cu:92-184, and,
+ * above 144 rows, the reconstruct + cuBLAS path of torch.exl3_gemm_recon
+ * (src/torch/amp_torch.cpp:11148-11230).
  */
 int amp_exl3_gemm(const void* A, const void* trellis, void* C, const void* suh, void* A_had,
                   const void* svh, int m, int k, int n, int K, int cb, int c_fp32,
                   cudaStream_t stream);
+
+/*
+ * Same with bf16 activations (A is (m, k) bf16; A_had (m, k) fp16 is required at every m). The
+ * reference has no counterpart: its exl3_gemm accepts fp16 only (Q/exl3_gemm.cu:136).
+ */
+int amp_exl3_gemm_bf16(const void* A, const void* trellis, void* C, const void* suh, void* A_had,
+                       const void* svh, int m, int k, int n, int K, int cb, int c_fp32,
+                       cudaStream_t stream);
+
+/* Reads and clears the prefill GEMM's status word (non-zero: a bounded wait on a tensor-core
+ * completion barrier ran out). Synchronises; diagnostics only. */
+int amp_exl3_gemm_status(int* out);
 
 /*
  * The decode-batch kernel on its own, m = 1..16. The first call on a device allocates a

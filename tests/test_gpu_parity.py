@@ -215,6 +215,50 @@ def test_gemm_more_than_16_rows(amp, oracle):
     check_close(y.cpu().numpy(), ref)
 
 
+def gemm_status():
+    from ampstein_b200 import _lib
+    st = ctypes.c_int(-1)
+    _lib.call("amp_exl3_gemm_status", ctypes.byref(st))
+    return st.value
+
+
+@pytest.mark.parametrize("m,k,n,K,cb", [(17, 128, 128, 4, 0), (200, 256, 256, 4, 0), (512, 512, 384, 3, 0),
+                                        (1100, 1024, 256, 5, 0), (130, 256, 128, 2, 1), (96, 384, 256, 6, 2),
+                                        (640, 256, 256, 8, 0), (300, 128, 256, 1, 0)])
+def test_prefill_gemm_tensor_core(amp, oracle, m, k, n, K, cb):
+    """More than 16 rows: x~ by the Hadamard kernel, weights decoded into shared memory, tcgen05
+    MMA with fp32 accumulators in tensor memory; ragged row counts included."""
+    trellis, suh, svh, x = make_linear(k, n, K, seed=7000 + m + K, m=m)
+    svh = (svh.astype(np.float32) / (1.2437 * np.sqrt(k))).astype(np.float16)
+    ref = oracle.linear(x, trellis, suh, svh, cb, fp32_out=True)
+    got = run_gemm(amp, trellis, suh, svh, x, cb)
+    assert gemm_status() == 0
+    check_close(got, ref)
+    got32 = run_gemm(amp, trellis, suh, svh, x, cb, fp32=True)
+    assert gemm_status() == 0
+    check_close(got32, ref)
+
+
+def test_prefill_gemm_bf16_activations(amp, oracle):
+    """bf16 activations (the prefill configuration): the oracle consumes the bf16 values exactly,
+    with the fp32 input scale the bf16 form uses."""
+    k, n, K, m = 512, 256, 4, 257
+    trellis, suh, svh, _ = make_linear(k, n, K, seed=7100)
+    svh = (svh.astype(np.float32) / (1.2437 * np.sqrt(k))).astype(np.float16)
+    xb = torch.randn((m, k), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    x32 = xb.float().numpy()
+    # oracle: rotate in fp32 (bf16 is a subset of fp32), then the usual chain on the rotated input
+    xt = oracle.had_ff(x32 * suh.astype(np.float32)[None, :]).astype(np.float16)
+    what = oracle.reconstruct(trellis, 0)
+    acc = oracle.matmul_f32(xt, what)
+    ref = oracle.had_ff(acc, post=svh)
+    out = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+    amp.exl3_gemm(xb.cuda(), dev(trellis), out, dev(suh), dev(svh))
+    torch.cuda.synchronize()
+    assert gemm_status() == 0
+    check_close(out.cpu().numpy(), ref)
+
+
 def test_linearity_and_determinism_at_full_size(amp):
     """Size-independent properties at the benchmark's shapes: exact scaling by two, bitwise
     reproducibility across launches."""
