@@ -61,18 +61,50 @@ __device__ __forceinline__ void st_ll2(uint2* dst, uint32_t d0, uint32_t d1, uin
                  :: "l"(dst), "r"(d0), "r"(seq), "r"(d1), "r"(seq) : "memory");
 }
 
+__device__ __forceinline__ void ld_ll2_once(const uint2* src, uint32_t (&v)[4])
+{
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "l"(src) : "memory");
+}
+
 // Poll two LL words until both carry `seq`; false when the budget ran out. `budget` is the
 // thread's remaining polls for the whole call, so a dead peer costs one limit, not one per word.
 __device__ __forceinline__ bool ld_ll2(const uint2* src, uint32_t seq, uint32_t* d0, uint32_t* d1, unsigned& budget)
 {
     for (; budget > 0; --budget)
     {
-        uint32_t a, fa, b, fb;
-        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(a), "=r"(fa), "=r"(b), "=r"(fb) : "l"(src) : "memory");
-        if (fa == seq && fb == seq) { *d0 = a; *d1 = b; return true; }
+        uint32_t v[4];
+        ld_ll2_once(src, v);
+        if (v[1] == seq && v[3] == seq) { *d0 = v[0]; *d1 = v[2]; return true; }
     }
     return false;
+}
+
+// One unit from every sender: all loads are issued before any flag is looked at, so a unit costs
+// one memory round trip when the data is already there (polling sender after sender would cost
+// one per sender); only the senders still missing are polled again.
+__device__ __forceinline__ bool gather_unit(uint2* const* srcs, const uint2* xv_unit, int rank, int N, uint32_t seq,
+                                            uint32_t (&d)[COMM_MAXN][2], unsigned& budget)
+{
+    uint32_t v[COMM_MAXN][4];
+    unsigned missing = 0;
+    #pragma unroll
+    for (int p = 0; p < COMM_MAXN; ++p)
+        if (p < N && p != rank) ld_ll2_once(srcs[p], v[p]);
+    #pragma unroll
+    for (int p = 0; p < COMM_MAXN; ++p)
+    {
+        if (p >= N) continue;
+        if (p == rank) { const uint2 x = *xv_unit; d[p][0] = x.x; d[p][1] = x.y; continue; }
+        if (v[p][1] == seq && v[p][3] == seq) { d[p][0] = v[p][0]; d[p][1] = v[p][2]; }
+        else missing |= 1u << p;
+    }
+    bool ok = true;
+    #pragma unroll
+    for (int p = 0; p < COMM_MAXN; ++p)
+        if (missing & (1u << p))
+            if (!ld_ll2(srcs[p], seq, &d[p][0], &d[p][1], budget)) { ok = false; d[p][0] = d[p][1] = 0; }
+    return ok;
 }
 
 __device__ __forceinline__ void acc4(float (&acc)[4], uint32_t d0, uint32_t d1)
@@ -129,14 +161,15 @@ void comm_allreduce_kernel(const __half* __restrict__ x, __half* __restrict__ ou
         }
         for (long i = u0 + threadIdx.x; i < u1; i += blockDim.x)
         {
+            uint2* srcs[COMM_MAXN];
+            #pragma unroll
+            for (int p = 0; p < COMM_MAXN; ++p) srcs[p] = (p < N) ? A_of(rank, p) + 2 * i : nullptr;
+            uint32_t d[COMM_MAXN][2];
+            if (!gather_unit(srcs, xv + i, rank, N, seq, d, budget)) bad = true;
             float acc[4] = { 0.f, 0.f, 0.f, 0.f };
-            for (int p = 0; p < N; ++p)                 // rank order, fp32
-            {
-                uint32_t d0, d1;
-                if (p == rank) { const uint2 v = xv[i]; d0 = v.x; d1 = v.y; }
-                else if (!ld_ll2(A_of(rank, p) + 2 * i, seq, &d0, &d1, budget)) { bad = true; d0 = d1 = 0; }
-                acc4(acc, d0, d1);
-            }
+            #pragma unroll
+            for (int p = 0; p < COMM_MAXN; ++p)         // rank order, fp32
+                if (p < N) acc4(acc, d[p][0], d[p][1]);
             const __half2 h0 = __floats2half2_rn(acc[0], acc[1]), h1 = __floats2half2_rn(acc[2], acc[3]);
             uint2 o;
             o.x = *reinterpret_cast<const uint32_t*>(&h0);
@@ -166,14 +199,15 @@ void comm_allreduce_kernel(const __half* __restrict__ x, __half* __restrict__ ou
         comm_part(c1 - c0, nb, b, &u0, &u1);
         for (long i = c0 + u0 + threadIdx.x; i < c0 + u1; i += blockDim.x)
         {
+            uint2* srcs[COMM_MAXN];
+            #pragma unroll
+            for (int p = 0; p < COMM_MAXN; ++p) srcs[p] = (p < N) ? A_of(rank, p) + 2 * i : nullptr;
+            uint32_t d[COMM_MAXN][2];
+            if (!gather_unit(srcs, xv + i, rank, N, seq, d, budget)) bad = true;
             float acc[4] = { 0.f, 0.f, 0.f, 0.f };
-            for (int p = 0; p < N; ++p)
-            {
-                uint32_t d0, d1;
-                if (p == rank) { const uint2 v = xv[i]; d0 = v.x; d1 = v.y; }
-                else if (!ld_ll2(A_of(rank, p) + 2 * i, seq, &d0, &d1, budget)) { bad = true; d0 = d1 = 0; }
-                acc4(acc, d0, d1);
-            }
+            #pragma unroll
+            for (int p = 0; p < COMM_MAXN; ++p)         // rank order, fp32
+                if (p < N) acc4(acc, d[p][0], d[p][1]);
             const __half2 h0 = __floats2half2_rn(acc[0], acc[1]), h1 = __floats2half2_rn(acc[2], acc[3]);
             uint2 o;
             o.x = *reinterpret_cast<const uint32_t*>(&h0);
@@ -232,7 +266,7 @@ AMP_API long amp_comm_ctl_bytes(void)
 // Blocks the launch should use for n halves among N ranks (the same value on every rank).
 AMP_API int amp_comm_blocks(int N, long n)
 {
-    long b = n / 4 / 2048;                              // about four units per thread
+    long b = (n / 4 + COMM_THREADS - 1) / COMM_THREADS;  // one 4-half unit per thread where possible
     (void) N;
     return (int) (b < 1 ? 1 : (b > COMM_MAXB ? COMM_MAXB : b));
 }

@@ -124,7 +124,7 @@ def test_c_abi_rejects_bad_arguments_without_a_gpu():
     assert L.amp_comm_buffer_bytes(1, 1024) == -1 and L.amp_comm_buffer_bytes(9, 1024) == -1
     assert L.amp_comm_buffer_bytes(2, 1001) == -1
     assert L.amp_comm_buffer_bytes(8, 40960) == 18 * 20480 * 8
-    assert L.amp_comm_blocks(8, 5120) == 1 and L.amp_comm_blocks(8, 40960) == 5
+    assert L.amp_comm_blocks(8, 5120) == 3 and L.amp_comm_blocks(8, 40960) == 16 and L.amp_comm_blocks(2, 8) == 1
     arr = (ctypes.c_void_p * 2)(1, 2)
     bad = [dict(N=1), dict(n=12), dict(n=2048, cap=1024), dict(blocks=17), dict(rank=2), dict(mode=2)]
     for kw in bad:
