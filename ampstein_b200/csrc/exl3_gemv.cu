@@ -115,19 +115,25 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     gemv_fn fn = gemv_kernel_for(K, A.cb, MB, A.mode);
     if (!fn) return fail(AMP_E_UNSUPPORTED, "exl3_gemv: no kernel for K=%d cb=%d", K, A.cb);
 
-    // x~ rows resident at a time: up to 16 KB per batch row (whole segments for small batches, so
-    // the main loop runs without block-wide barriers), 32 KB in total
-    int xgroups = (32 * 1024 / (m * 4)) / 64;
-    xgroups &= ~3;
-    if (xgroups > GEMV_XCHUNK_MAX / 64) xgroups = GEMV_XCHUNK_MAX / 64;
-    if (xgroups > (k / 64 + 3) / 4 * 4) xgroups = (k / 64 + 3) / 4 * 4;
-    if (xgroups < 4) xgroups = 4;
-    int stages = A.force_stages > 0 ? A.force_stages : 3;
-    AMP_REQUIRE(stages >= 1 && stages <= GEMV_MAX_STAGES, "exl3_gemv: stages out of range");
-    const GemvSmem L = gemv_smem_layout(K, m, stages, xgroups);
+    // x~ rows resident at a time: at most 16 KB of shared memory (whole segments for small
+    // batches, so the main loop rarely meets a block-wide barrier); shrunk below to what a
+    // CTA's range needs
+    const int G = k / 64;
+    int xcap = (16 * 1024 / (m * 4)) / 64;
+    xcap &= ~3;
+    if (xcap > GEMV_XCHUNK_MAX / 64) xcap = GEMV_XCHUNK_MAX / 64;
+    if (xcap > (G + 3) / 4 * 4) xcap = (G + 3) / 4 * 4;
+    if (xcap < 4) xcap = 4;
+    if (A.force_xgroups > 0)
+    {
+        AMP_REQUIRE(A.force_xgroups % 4 == 0 && A.force_xgroups <= GEMV_XCHUNK_MAX / 64,
+                    "exl3_gemv: xgroups must be a multiple of 4, at most %d", GEMV_XCHUNK_MAX / 64);
+        xcap = A.force_xgroups;
+    }
+    GemvSmem L = gemv_smem_layout(K, m, xcap);
     AMP_REQUIRE(L.total <= D.smem_optin, "exl3_gemv: shared memory layout does not fit (%d bytes)", L.total);
     const int smem_per_sm = D.smem_optin + 1024;                       // opt-in limit excludes 1 KB per CTA
-    const int reg_ctas = (MB == 1 ? 3 : 2);
+    const int reg_ctas = (MB == 1 ? 4 : 2);
     int ctas_per_sm = smem_per_sm / (L.total + 1024);
     if (ctas_per_sm > reg_ctas) ctas_per_sm = reg_ctas;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
@@ -138,7 +144,6 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     AMP_REQUIRE(col_blocks <= GEMV_MAX_BLOCKS, "exl3_gemv: too many column blocks (%ld)", col_blocks);
     const long units = col_blocks * (k / 64);
     AMP_REQUIRE(units < (1L << 30), "exl3_gemv: problem too large (%ld work units)", units);
-    const int G = k / 64;
     long ncta = (long) D.sms * ctas_per_sm;
     if (A.mode)
     {
@@ -160,6 +165,16 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     if (ncta > GEMV_MAX_CTAS) ncta = GEMV_MAX_CTAS;
     AMP_REQUIRE(ncta >= 1, "exl3_gemv: empty problem");
 
+    // a range of `per` units starting anywhere needs per + 1 groups of x~ (chunks start at an
+    // even group); the grouped modes learn their unit count on the device and keep the cap
+    int xgroups = xcap;
+    if (!A.mode && A.force_xgroups <= 0)
+    {
+        const long per = (units + ncta - 1) / ncta;
+        const long need = (per + 1 + 3) / 4 * 4;
+        if (need < xgroups) xgroups = (int) need;
+    }
+    L = gemv_smem_layout(K, m, xgroups);
     if (cudaError_t e = ensure_smem(fn, L.total, dev)) return cuda_rc(e, "exl3_gemv smem attribute");
 
     GemvParams P;
@@ -168,7 +183,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     P.t_trellis = A.t_trellis; P.t_suh = A.t_suh; P.t_svh = A.t_svh; P.t_c = A.t_c;
     P.t_stride = A.t_stride; P.t_src = A.t_src;
     P.tables = A.tables; P.width = A.width; P.stride = A.stride;
-    P.m = m; P.k = k; P.c_fp32 = A.c_fp32; P.stages = stages; P.xgroups = xgroups; P.pdl = g_pdl;
+    P.m = m; P.k = k; P.c_fp32 = A.c_fp32; P.xgroups = xgroups; P.pdl = g_pdl;
     P.blocks = (int) col_blocks;
     P.moe = A.moe;
     if (int rc = workspace_region(dev, &P.counters, &P.scratch)) return rc;
@@ -195,13 +210,13 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
 }
 
 static GemvLaunch direct(const void* x, const void* trellis, void* c, const void* suh, const void* svh,
-                         int m, int k, int n, int K, int cb, int c_fp32, int split, int stages)
+                         int m, int k, int n, int K, int cb, int c_fp32, int split, int xgroups)
 {
     GemvLaunch A = {};
     A.x = x; A.trellis = trellis; A.suh = suh; A.svh = svh; A.c = c;
     A.tables = 0; A.slices = 1; A.width = n; A.stride = n;
     A.m = m; A.k = k; A.K = K; A.cb = cb; A.c_fp32 = c_fp32;
-    A.force_split = split; A.force_stages = stages;
+    A.force_split = split; A.force_xgroups = xgroups;
     return A;
 }
 
@@ -215,12 +230,12 @@ AMP_API int amp_exl3_gemv(const void* x, const void* trellis, void* c, const voi
     return launch_gemv(direct(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, 0, 0), stream);
 }
 
-// tuning / test hook: fixed CTA count (split) and ring depth (stages); 0 = choose
+// tuning / test hook: fixed CTA count (split) and x~ chunk size (xgroups); 0 = choose
 AMP_API int amp_exl3_gemv_cfg(const void* x, const void* trellis, void* c, const void* suh, const void* svh,
-                              int m, int k, int n, int K, int cb, int c_fp32, int split, int stages,
+                              int m, int k, int n, int K, int cb, int c_fp32, int split, int xgroups,
                               cudaStream_t stream)
 {
-    return launch_gemv(direct(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, split, stages), stream);
+    return launch_gemv(direct(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, split, xgroups), stream);
 }
 
 // Reads and clears the GEMV status word of the current device (synchronises the device).

@@ -11,7 +11,7 @@ struct GemvLaunch
     const long long* t_trellis; const long long* t_suh; const long long* t_svh; const long long* t_c;
     const int* t_stride; const int* t_src;
     int tables, slices, width, stride, m, k, K, cb, c_fp32;
-    int force_split, force_stages;
+    int force_split, force_xgroups;
     int mode;            // 0 dense / bundle, 1 grouped gate+up, 2 grouped down
     int max_slices;      // grouped modes: most slices the run table can describe (slices = the expected count)
     GemvMoe moe;

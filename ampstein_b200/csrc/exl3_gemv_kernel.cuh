@@ -13,18 +13,19 @@
 //    in a small global scratch area, summed in ascending-k order so results are bitwise
 //    reproducible). Nobody waits: there is no spin, no lock and no grid-wide barrier (the
 //    reference needs two grid.sync()s, an A_had scratch tensor and a lock buffer).
-//  * Inside the CTA a warp owns 64 of the 128 columns and every fourth unit of the range:
-//    16 fp32 accumulators per thread, which keeps the register count low enough for three
-//    CTAs (24 warps) per SM -- the decode is bound by instruction issue, so warps in flight
+//  * Inside the CTA each of the eight warps owns one 16-column tile column of the block and
+//    walks every unit of the range: the warps stay in step (no imbalance inside a CTA, nothing
+//    to reduce between warps), a warp's unit is only 1024 weights, so small matrices still
+//    spread evenly, and a thread needs eight fp32 accumulators, which leaves room for four
+//    CTAs (32 warps) per SM -- the decode is bound by instruction issue, so warps in flight
 //    are what hides its latencies.
 //  * Packed trellis words are streamed global -> shared with 16-byte cp.async copies into
-//    per-warp rings (a stage = four tile rows x four tiles = 512*K bytes, every copy
-//    instruction of a warp covers whole 128-byte lines). Bulk (TMA) copies were measured and
-//    rejected for this access pattern: one warp sustains only about one bulk copy per 1000
-//    cycles whatever the ring depth, so the 0.5-1 KB row pieces of a column block cap the
-//    kernel near 1.4 TB/s, while cp.async streams at the full HBM rate. The copies are
-//    issued before the kernel waits for its predecessor (programmatic dependent launch), so
-//    a layer's weight stream starts under the previous layer's tail.
+//    per-warp rings (a slot = one unit = four tiles of one tile column, 128*K bytes). Bulk
+//    (TMA) copies were measured and rejected for this access pattern: one warp sustains only
+//    about one bulk copy per 1000 cycles whatever the ring depth, so the small row pieces of
+//    a column block cap the kernel near 1.4 TB/s, while cp.async streams at the full HBM
+//    rate. The copies are issued before the kernel waits for its predecessor (programmatic
+//    dependent launch), so a layer's weight stream starts under the previous layer's tail.
 //  * Decode stays in registers. The decoded weights are the A operand of mma.sync.m16n8k16
 //    (16 output columns x 16 k-slots) and the activations the B operand (k-slots x 8 batch
 //    rows), so a batch of up to 8 costs one MMA per 128 weights. For codebooks 0/1 the final
@@ -45,11 +46,8 @@
 namespace amp {
 
 constexpr int GEMV_THREADS = 256;
-constexpr int GEMV_WARPS = 8;
-constexpr int GEMV_KSLOTS = 4;                 // warps along k (times 2 column halves = 8 warps)
+constexpr int GEMV_WARPS = 8;                  // one per 16-column tile column of a 128-column block
 constexpr int GEMV_XCHUNK_MAX = 8192;          // most rows of x~ held in shared memory at a time
-constexpr int GEMV_RPITCH = 68;                // floats per row of a warp's 64-column partial
-constexpr int GEMV_MAX_STAGES = 4;
 
 // Grouped expert GEMV (fused decode MoE): the kernel's slices are expert runs described by a
 // device-side run table, the input rows are gathered per run, outputs scatter to slot rows.
@@ -92,7 +90,6 @@ struct GemvParams
     int stride;                 // row width of trellis / output in direct mode
     int m, k;
     int c_fp32;
-    int stages;                 // ring depth per warp, 1..GEMV_MAX_STAGES
     int xgroups;                // 64-row groups of x~ held in shared memory at a time (multiple of 4)
     int pdl;                    // launched with programmatic stream serialization
     int blocks;                 // column blocks in total (slices * width / 128)
@@ -102,57 +99,63 @@ struct GemvParams
     GemvMoe moe;                // grouped-expert modes only
 };
 
-__host__ __device__ constexpr int gemv_row_pitch(int K) { return 128 * K + 32; }     // bytes per tile row (4 tiles) in a stage
-__host__ __device__ constexpr int gemv_stage_bytes(int K) { return 4 * gemv_row_pitch(K); }
+// A ring slot holds one unit of one warp: four tiles (one per tile row of the 64-row group),
+// each padded by 32 bytes so that the four tile rows start in different banks.
+__host__ __device__ constexpr int gemv_row_pitch(int K) { return 32 * K + 32; }      // bytes per tile inside a slot
+__host__ __device__ constexpr int gemv_slot_bytes(int K) { return 4 * gemv_row_pitch(K); }
+// ring depth per warp: enough bytes in flight per SM (depth-1 slots x 32 warps) to cover the HBM latency
+__host__ __device__ constexpr int gemv_stages(int K) { return K <= 2 ? 8 : (K <= 4 ? 6 : 4); }
 
 // byte offsets inside dynamic shared memory
 struct GemvSmem
 {
-    int part, xd, red, ring, total;
+    int part, xd, gsum, ring, total;
 };
 
 // 32-bit words per batch row of the duplicated x~ (+16 keeps fragment loads conflict-free)
 __host__ __device__ constexpr int gemv_xpitch(int xgroups) { return xgroups * 64 + 16; }
 
 // xrows: rows of x~ / partial sums kept (the batch size m)
-__host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int stages, int xgroups)
+__host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int xgroups)
 {
     GemvSmem L;
     L.part = 0;                                             // [xrows][128] fp32: the finished block
     L.xd = L.part + xrows * 128 * 4;                        // [xrows][XPITCH] duplicated fp16 pairs
-    L.red = L.xd + xrows * gemv_xpitch(xgroups) * 4;        // [8 warps][xrows][RPITCH] fp32
-    L.ring = L.red + GEMV_WARPS * xrows * GEMV_RPITCH * 4;
+    L.gsum = L.xd + xrows * gemv_xpitch(xgroups) * 4;       // [xrows][xgroups] fp32 (codebook 2: sum of x~ per group)
+    L.ring = L.gsum + xrows * xgroups * 4;
     L.ring = (L.ring + 127) & ~127;
-    L.total = L.ring + GEMV_WARPS * stages * gemv_stage_bytes(K);
+    L.total = L.ring + GEMV_WARPS * gemv_stages(K) * gemv_slot_bytes(K);
     return L;
 }
 
-// K words of one lane's chunk, widest loads the alignment allows
+__device__ __forceinline__ uint32_t lds32(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// K words of one lane's chunk from shared memory, widest loads the alignment allows
 template <int K>
-__device__ __forceinline__ void load_chunk(const uint32_t* p, uint32_t (&w)[K])
+__device__ __forceinline__ void load_chunk_s(uint32_t addr, uint32_t (&w)[K])
 {
     if constexpr (K % 4 == 0)
     {
         #pragma unroll
         for (int i = 0; i < K / 4; ++i)
-        {
-            uint4 v = reinterpret_cast<const uint4*>(p)[i];
-            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-        }
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3]) : "r"(addr + 16 * i));
     }
     else if constexpr (K % 2 == 0)
     {
         #pragma unroll
         for (int i = 0; i < K / 2; ++i)
-        {
-            uint2 v = reinterpret_cast<const uint2*>(p)[i];
-            w[2 * i] = v.x; w[2 * i + 1] = v.y;
-        }
+            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w[2 * i]), "=r"(w[2 * i + 1]) : "r"(addr + 8 * i));
     }
     else
     {
         #pragma unroll
-        for (int i = 0; i < K; ++i) w[i] = p[i];
+        for (int i = 0; i < K; ++i) w[i] = lds32(addr + 4 * i);
     }
 }
 
@@ -226,12 +229,13 @@ __device__ __forceinline__ void states8(const uint32_t (&w)[K], uint32_t prev, u
     }
 }
 
-// Decode the lane's 8 weights of virtual lane R of one tile and issue the two MMAs. w/prev: the
-// lane's K words and the word before them. xb: duplicated activations of the tile's 16 rows for
-// this lane's batch row(s), xb[r] = row r.
+// Decode the lane's 8 weights of virtual lane R of one tile and issue the two MMAs (into two
+// accumulators, so that they do not wait for each other). w/prev: the lane's K words and the
+// word before them. xb: duplicated activations of the tile's 16 rows for this lane's batch
+// row(s), xb[r] = row r.
 template <int K, int CB, int MB, int R>
-__device__ __forceinline__ void decode_mma_r(const uint32_t (&w)[K], uint32_t prev,
-                                             const uint32_t (&xb)[MB][16], float (&acc)[MB][4])
+__device__ __forceinline__ void decode_mma_r(const uint32_t (&w)[K], uint32_t prev, const uint32_t (&xb)[MB][16],
+                                             float (&acc0)[MB][4], float (&acc1)[MB][4])
 {
     uint32_t s[8], a[8];
 #ifdef AMP_LAB_NODECODE
@@ -247,7 +251,7 @@ __device__ __forceinline__ void decode_mma_r(const uint32_t (&w)[K], uint32_t pr
     for (int mb = 0; mb < MB; ++mb)
     {
         uint32_t u = a[0] ^ a[1] ^ a[2] ^ a[3] ^ a[4] ^ a[5] ^ a[6] ^ a[7] ^ xb[mb][2 * R];
-        acc[mb][0] += __uint_as_float(u);
+        acc0[mb][0] += __uint_as_float(u);
     }
 #else
     #pragma unroll
@@ -255,8 +259,8 @@ __device__ __forceinline__ void decode_mma_r(const uint32_t (&w)[K], uint32_t pr
     {
         // positions j and j+4 are the same row in columns c and c+8 -> MMA rows g and g+8;
         // positions (0,1) are tile rows (2R, 2R+1), positions (2,3) rows (2R+8, 2R+9)
-        mma_16816(acc[mb], a[0], a[4], a[1], a[5], xb[mb][2 * R], xb[mb][2 * R + 1]);
-        mma_16816(acc[mb], a[2], a[6], a[3], a[7], xb[mb][2 * R + 8], xb[mb][2 * R + 9]);
+        mma_16816(acc0[mb], a[0], a[4], a[1], a[5], xb[mb][2 * R], xb[mb][2 * R + 1]);
+        mma_16816(acc1[mb], a[2], a[6], a[3], a[7], xb[mb][2 * R + 8], xb[mb][2 * R + 9]);
     }
 #endif
 }
@@ -294,8 +298,32 @@ __device__ __forceinline__ float moe_act_gate(int act, bool gated, float g, floa
 }
 
 #ifndef AMP_GEMV_MINBLOCKS
-#define AMP_GEMV_MINBLOCKS 3
+#define AMP_GEMV_MINBLOCKS 4
 #endif
+
+__device__ __forceinline__ void cp_async16_s(uint32_t dst, const void* src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(src) : "memory");
+}
+
+template <int N>
+__device__ __forceinline__ void cp_async_wait_n()
+{
+    asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory");
+}
+
+// The CTAs' ranges: U units over ncta CTAs, the first r ranges one unit longer (q = U / ncta,
+// r = U % ncta). All 32-bit, no division on the way from a CTA to its range.
+struct GemvSplit
+{
+    int q, r;
+    __device__ __forceinline__ int begin(int i) const { return i * q + min(i, r); }
+    __device__ __forceinline__ int owner(int u) const
+    {
+        const int edge = r * (q + 1);
+        return u < edge ? u / (q + 1) : r + (u - edge) / q;
+    }
+};
 
 // MODE 0: one matrix or a bundle sharing one input.  MODE 1: grouped expert gate/up (slice = expert
 // run x projection, input rows gathered by token).  MODE 2: grouped expert down (input = the
@@ -305,29 +333,29 @@ __global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 2))
 void exl3_gemv_kernel(const GemvParams P)
 {
     extern __shared__ __align__(128) unsigned char smem[];
-    const GemvSmem L = gemv_smem_layout(K, P.m, P.stages, P.xgroups);
+    const GemvSmem L = gemv_smem_layout(K, P.m, P.xgroups);
     const int XPITCH = gemv_xpitch(P.xgroups);
     const int XG = P.xgroups;
     float* part = reinterpret_cast<float*>(smem + L.part);
     uint32_t* xd = reinterpret_cast<uint32_t*>(smem + L.xd);
-    float* red = reinterpret_cast<float*>(smem + L.red);
-    unsigned char* ring = smem + L.ring;
+    float* gsum = reinterpret_cast<float*>(smem + L.gsum);
     __shared__ int s_last;
 
-    constexpr int PITCH = gemv_row_pitch(K);
-    constexpr int STAGE = gemv_stage_bytes(K);
+    constexpr int S = gemv_stages(K);
+    constexpr int RP = gemv_row_pitch(K);
+    constexpr int SLOT = gemv_slot_bytes(K);
     constexpr int TILE_BYTES = 32 * K;
+    constexpr int PIECES = 8 * K;                      // 16-byte pieces of a unit (four tiles of 2K pieces)
+    constexpr int NP = (PIECES + 31) / 32;             // copy instructions per unit and lane
 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int gq = lane >> 2, pq = lane & 3;
-    const int half = warp & 1, ks = warp >> 1;         // column half, k slot
-    const int stages = P.stages;
     const int m = P.m, k = P.k;
     const int G = k >> 6;                              // 64-row groups per column block
     const int nbw = P.width >> 7;                      // column blocks per slice
 
-    // Work = (column block, group) units in block-major order, cut into gridDim.x equal contiguous
-    // ranges: every CTA decodes the same number of weights (+-1 group) whatever the shape.
+    // Work = (column block, group) units in block-major order, cut into equal contiguous ranges:
+    // every CTA decodes the same number of weights (+-1 group) whatever the shape.
     const int nproj = (MODE == 1 && P.moe.gated) ? 2 : 1;
     if constexpr (MODE != 0)
     {
@@ -341,18 +369,30 @@ void exl3_gemv_kernel(const GemvParams P)
         if (MODE == 0 && P.pdl) { pdl_launch_dependents(); pdl_wait(); }
         return;
     }
-    const int u0 = (int) ((long) U * cta / ncta), u1 = (int) ((long) U * (cta + 1) / ncta);
+    GemvSplit split;
+    split.q = U / ncta;
+    split.r = U - split.q * ncta;
+    const int u0 = split.begin(cta), u1 = split.begin(cta + 1);
 
-    unsigned char* my_ring = ring + (size_t) warp * stages * STAGE;
+    const uint32_t ring_s = smem_u32(smem + L.ring) + warp * (S * SLOT);      // this warp's ring
 
-    // ---- weight stream: this warp's units are u0 + ks + 4j; a cursor walks them without divisions ----
-    int iu = u0 + ks;                                  // next unit to fetch
+    // ---- weight stream: a cursor walks the range's units; piece p = lane + 32 j of a unit is
+    // 16 bytes of tile row p / 2K ----
+    int iu = u0;                                       // next unit to fetch
     int iblk = iu / G, ig = iu - iblk * G;
-    int istage = 0;
-    const unsigned char* ibase = nullptr;              // first tile row of the cursor's block, this warp's four tiles
-    size_t irow = 0;                                   // bytes between tile rows there
+    uint32_t islot = 0;                                // byte offset of the next slot to fill
+    const unsigned char* isrc[NP];                     // this lane's pieces of the cursor's unit
+    size_t istep = 0;                                  // bytes from one unit to the next (four tile rows)
+    uint32_t idst[NP];
+    #pragma unroll
+    for (int j = 0; j < NP; ++j)
+    {
+        const int p = lane + 32 * j, row = p / (2 * K);
+        idst[j] = ring_s + row * RP + (p - row * 2 * K) * 16;
+        isrc[j] = nullptr;
+    }
 
-    auto set_block = [&](int blk)
+    auto set_block = [&](int blk, int g)
     {
         const int slice = blk / nbw, nb = blk - slice * nbw;
         const unsigned char* tr = reinterpret_cast<const unsigned char*>(P.trellis);
@@ -369,13 +409,19 @@ void exl3_gemv_kernel(const GemvParams P)
             tr = reinterpret_cast<const unsigned char*>(P.t_trellis[slice]);
             stride = P.t_stride ? P.t_stride[slice] : P.width;
         }
-        irow = (size_t) (stride >> 4) * TILE_BYTES;
-        ibase = tr + (size_t) (nb * 8 + half * 4) * TILE_BYTES;
+        const size_t irow = (size_t) (stride >> 4) * TILE_BYTES;          // bytes between tile rows
+        const unsigned char* base = tr + (size_t) (nb * 8 + warp) * TILE_BYTES + (size_t) (4 * g) * irow;
+        istep = 4 * irow;
+        #pragma unroll
+        for (int j = 0; j < NP; ++j)
+        {
+            const int p = lane + 32 * j, row = p / (2 * K);
+            isrc[j] = base + (size_t) row * irow + (p - row * 2 * K) * 16;
+        }
     };
 
-    // One stage = four tile rows x four tiles of one unit; the warp copies it as 16-byte pieces
-    // (K per lane). A group is committed even when nothing is left to copy so that the group
-    // count stays in step with the item index.
+    // A group is committed even when nothing is left to copy so that the group count stays in
+    // step with the unit index.
     auto issue = [&]()
     {
 #ifndef AMP_LAB_NOLOAD
@@ -384,40 +430,29 @@ void exl3_gemv_kernel(const GemvParams P)
         if (iu < 0)
 #endif
         {
-            const unsigned char* src = ibase + (size_t) (4 * ig) * irow;
-            unsigned char* dst = my_ring + istage * STAGE;
             #pragma unroll
-            for (int i8 = 0; i8 < K; ++i8)
+            for (int j = 0; j < NP; ++j)
             {
-                int row, off;                           // piece lane + 32*i8 of 8K pieces per tile row
-                if constexpr ((8 * K) % 32 == 0)
-                {
-                    row = (32 * i8) / (8 * K);
-                    off = (lane + 32 * i8 - row * 8 * K) * 16;
-                }
-                else
-                {
-                    const int i = lane + 32 * i8;
-                    row = (i >= 8 * K) + (i >= 16 * K) + (i >= 24 * K);
-                    off = (i - row * 8 * K) * 16;
-                }
-                cp_async16(dst + row * PITCH + off, src + row * irow + off);
+                if (NP * 32 == PIECES || lane + 32 * j < PIECES) cp_async16_s(idst[j] + islot, isrc[j]);
+                isrc[j] += istep;
             }
-            iu += GEMV_KSLOTS;
-            ig += GEMV_KSLOTS;
-            if (ig >= G)
+            ++iu;
+            if (++ig == G)
             {
-                do { ig -= G; ++iblk; } while (ig >= G);
-                if (iu < u1) set_block(iblk);
+                ig = 0;
+                ++iblk;
+                if (iu < u1) set_block(iblk, 0);
             }
         }
         cp_async_commit();
-        if (++istage == stages) istage = 0;
+        islot += SLOT;
+        if (islot == S * SLOT) islot = 0;
     };
 
     // the weight stream does not depend on the previous kernel: start it before anything else
-    if (iu < u1) set_block(iblk);
-    for (int j = 0; j < stages; ++j) issue();
+    if (iu < u1) set_block(iblk, ig);
+    #pragma unroll
+    for (int j = 0; j < S - 1; ++j) issue();
     if constexpr (MODE == 0)
     {
         if (P.pdl)
@@ -431,11 +466,10 @@ void exl3_gemv_kernel(const GemvParams P)
     int xrow[MB];                                      // word offset of this lane's batch row in xd
     #pragma unroll
     for (int mb = 0; mb < MB; ++mb) xrow[mb] = min(mb * 8 + gq, m - 1) * XPITCH + pq * 4;
-    const int w_off = pq * PITCH + gq * K * 4;                                // this lane's K words of a tile
-    const int p_off = pq * PITCH + ((gq * K + 8 * K - 1) % (8 * K)) * 4;      // the word before them (ring)
+    const uint32_t w_off = ring_s + pq * RP + gq * K * 4;                             // this lane's K words of a tile
+    const uint32_t p_off = ring_s + pq * RP + ((gq * K + 8 * K - 1) % (8 * K)) * 4;   // the word before them (ring)
 
-    int cu = u0 + ks;                                  // this warp's next unit to consume
-    int cstage = 0;
+    uint32_t cslot = 0;                                // byte offset of the next slot to consume
     int useg = u0;
     while (useg < u1)
     {
@@ -476,106 +510,136 @@ void exl3_gemv_kernel(const GemvParams P)
             else cbase += (size_t) slice * m * P.width * (P.c_fp32 ? 4 : 2);
         }
 
-        float acc[4][MB][4];                           // [tile of this warp's four][batch block][fragment]
+        float acc0[MB][4], acc1[MB][4];                // this warp's 16 columns x this lane's batch rows
         #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
-            #pragma unroll
-            for (int mb = 0; mb < MB; ++mb)
-                acc[nt][mb][0] = acc[nt][mb][1] = acc[nt][mb][2] = acc[nt][mb][3] = 0.f;
-        float acc1[MB][4];                             // cb 2 only: sum of activations (all-ones weights)
+        for (int mb = 0; mb < MB; ++mb)
+        {
+            acc0[mb][0] = acc0[mb][1] = acc0[mb][2] = acc0[mb][3] = 0.f;
+            acc1[mb][0] = acc1[mb][1] = acc1[mb][2] = acc1[mb][3] = 0.f;
+        }
+        float xsum[MB][2];                             // cb 2 only: sum of x~ over the segment's rows, batch rows 2pq, 2pq+1
         #pragma unroll
-        for (int mb = 0; mb < MB; ++mb) acc1[mb][0] = acc1[mb][1] = acc1[mb][2] = acc1[mb][3] = 0.f;
+        for (int mb = 0; mb < MB; ++mb) xsum[mb][0] = xsum[mb][1] = 0.f;
 
         // x~ is needed in whole 128-row blocks: chunks start at an even group
         for (int cg0 = g0 & ~1; cg0 < g1; cg0 += XG)
         {
             const int cg1 = min(cg0 + XG, g1);
             const int nblk = (cg1 - cg0 + 1) >> 1;      // 128-row blocks in this chunk
-            __syncthreads();                            // previous x~ (and reduction buffers) fully consumed
+            __syncthreads();                            // previous x~ fully consumed
 
             // x~ = fp16(H(x * suh) / sqrt(128)), stored duplicated ((v, v) per word) and in the
-            // order the B fragments are read: word = group*64 + (row%16 / 4)*16 + (row%64 / 16)*4 + row%4
-            for (int idx = warp; idx < nrows * nblk; idx += GEMV_WARPS)
+            // order the B fragments are read: word = group*64 + (row%16 / 4)*16 + (row%64 / 16)*4 + row%4.
+            // Tasks (batch row b, 128-row block jb) go round the warps.
             {
-                const int b = idx / nblk, jb = idx - b * nblk;
-                const size_t col = (size_t) cg0 * 64 + (size_t) jb * 128 + lane * 4;
-                float h0, h1, h2, h3;
-                if constexpr (MODE == 0)
+                int b = 0, jb = warp;
+                while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
+                while (b < nrows)
                 {
-                    half4 v = *reinterpret_cast<const half4*>(P.x + (size_t) b * k + col);
-                    half4 sc = *reinterpret_cast<const half4*>(suh + col);
-                    v.x = __hmul2(v.x, sc.x);
-                    v.y = __hmul2(v.y, sc.y);
-                    h0 = __low2float(v.x); h1 = __high2float(v.x); h2 = __low2float(v.y); h3 = __high2float(v.y);
-                }
-                else
-                {
-                    // grouped modes scale in fp32 (reference: exl3_moe_coop_kernel.cuh:643-660, 826-838)
-                    const int slot = run_slots[b];
-                    if constexpr (MODE == 1)
+                    const size_t col = (size_t) cg0 * 64 + (size_t) jb * 128 + lane * 4;
+                    float h0, h1, h2, h3;
+                    if constexpr (MODE == 0)
                     {
-                        const __half* xr = P.moe.x + (size_t) (slot / P.moe.topk) * P.moe.x_stride;
-                        h0 = h1 = h2 = h3 = 0.f;                  // zero padding from H to Hi
-                        if ((int) col + 3 < P.moe.H)
-                        {
-                            half4 v = *reinterpret_cast<const half4*>(xr + col);
-                            h0 = __low2float(v.x); h1 = __high2float(v.x); h2 = __low2float(v.y); h3 = __high2float(v.y);
-                        }
-                        else
-                        {
-                            if ((int) col + 0 < P.moe.H) h0 = __half2float(xr[col + 0]);
-                            if ((int) col + 1 < P.moe.H) h1 = __half2float(xr[col + 1]);
-                            if ((int) col + 2 < P.moe.H) h2 = __half2float(xr[col + 2]);
-                        }
+                        half4 v = *reinterpret_cast<const half4*>(P.x + (size_t) b * k + col);
+                        half4 sc = *reinterpret_cast<const half4*>(suh + col);
+                        v.x = __hmul2(v.x, sc.x);
+                        v.y = __hmul2(v.y, sc.y);
+                        h0 = __low2float(v.x); h1 = __high2float(v.x); h2 = __low2float(v.y); h3 = __high2float(v.y);
                     }
                     else
                     {
-                        float4 u4, g4;
-                        if (P.moe.gu_f32)
+                        // grouped modes scale in fp32 (reference: exl3_moe_coop_kernel.cuh:643-660, 826-838)
+                        const int slot = run_slots[b];
+                        if constexpr (MODE == 1)
                         {
-                            u4 = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.moe.gu[1]) + (size_t) slot * P.moe.I + col));
-                            g4 = u4;
-                            if (P.moe.gated) g4 = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.moe.gu[0]) + (size_t) slot * P.moe.I + col));
+                            const __half* xr = P.moe.x + (size_t) (slot / P.moe.topk) * P.moe.x_stride;
+                            h0 = h1 = h2 = h3 = 0.f;                  // zero padding from H to Hi
+                            if ((int) col + 3 < P.moe.H)
+                            {
+                                half4 v = *reinterpret_cast<const half4*>(xr + col);
+                                h0 = __low2float(v.x); h1 = __high2float(v.x); h2 = __low2float(v.y); h3 = __high2float(v.y);
+                            }
+                            else
+                            {
+                                if ((int) col + 0 < P.moe.H) h0 = __half2float(xr[col + 0]);
+                                if ((int) col + 1 < P.moe.H) h1 = __half2float(xr[col + 1]);
+                                if ((int) col + 2 < P.moe.H) h2 = __half2float(xr[col + 2]);
+                            }
                         }
                         else
                         {
-                            auto ld = [&](const void* base) {
-                                const uint2 r = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(base) + (size_t) slot * P.moe.I + col));
-                                const __half2 a = *reinterpret_cast<const __half2*>(&r.x), b2 = *reinterpret_cast<const __half2*>(&r.y);
-                                return make_float4(__low2float(a), __high2float(a), __low2float(b2), __high2float(b2));
-                            };
-                            u4 = ld(P.moe.gu[1]);
-                            g4 = P.moe.gated ? ld(P.moe.gu[0]) : u4;
+                            float4 u4, g4;
+                            if (P.moe.gu_f32)
+                            {
+                                u4 = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.moe.gu[1]) + (size_t) slot * P.moe.I + col));
+                                g4 = u4;
+                                if (P.moe.gated) g4 = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.moe.gu[0]) + (size_t) slot * P.moe.I + col));
+                            }
+                            else
+                            {
+                                auto ld = [&](const void* base) {
+                                    const uint2 r = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(base) + (size_t) slot * P.moe.I + col));
+                                    const __half2 a = *reinterpret_cast<const __half2*>(&r.x), b2 = *reinterpret_cast<const __half2*>(&r.y);
+                                    return make_float4(__low2float(a), __high2float(a), __low2float(b2), __high2float(b2));
+                                };
+                                u4 = ld(P.moe.gu[1]);
+                                g4 = P.moe.gated ? ld(P.moe.gu[0]) : u4;
+                            }
+                            h0 = moe_act_gate(P.moe.act, P.moe.gated, g4.x, u4.x, P.moe.act_limit);
+                            h1 = moe_act_gate(P.moe.act, P.moe.gated, g4.y, u4.y, P.moe.act_limit);
+                            h2 = moe_act_gate(P.moe.act, P.moe.gated, g4.z, u4.z, P.moe.act_limit);
+                            h3 = moe_act_gate(P.moe.act, P.moe.gated, g4.w, u4.w, P.moe.act_limit);
                         }
-                        h0 = moe_act_gate(P.moe.act, P.moe.gated, g4.x, u4.x, P.moe.act_limit);
-                        h1 = moe_act_gate(P.moe.act, P.moe.gated, g4.y, u4.y, P.moe.act_limit);
-                        h2 = moe_act_gate(P.moe.act, P.moe.gated, g4.z, u4.z, P.moe.act_limit);
-                        h3 = moe_act_gate(P.moe.act, P.moe.gated, g4.w, u4.w, P.moe.act_limit);
+                        half4 sc = *reinterpret_cast<const half4*>(suh + col);
+                        h0 *= __low2float(sc.x); h1 *= __high2float(sc.x); h2 *= __low2float(sc.y); h3 *= __high2float(sc.y);
                     }
-                    half4 sc = *reinterpret_cast<const half4*>(suh + col);
-                    h0 *= __low2float(sc.x); h1 *= __high2float(sc.x); h2 *= __low2float(sc.y); h3 *= __high2float(sc.y);
+                    warp_had128(h0, h1, h2, h3, lane);
+                    const __half2 o01 = __floats2half2_rn(h0 * kRScale, h1 * kRScale);
+                    const __half2 o23 = __floats2half2_rn(h2 * kRScale, h3 * kRScale);
+                    const uint32_t u01 = *reinterpret_cast<const uint32_t*>(&o01);
+                    const uint32_t u23 = *reinterpret_cast<const uint32_t*>(&o23);
+                    uint4 d;
+                    d.x = __byte_perm(u01, u01, 0x1010); d.y = __byte_perm(u01, u01, 0x3232);
+                    d.z = __byte_perm(u23, u23, 0x1010); d.w = __byte_perm(u23, u23, 0x3232);
+                    const int r = jb * 128 + lane * 4;      // row inside the chunk
+                    const int word = (r >> 6) * 64 + ((r & 15) >> 2) * 16 + ((r & 63) >> 4) * 4;
+                    *reinterpret_cast<uint4*>(xd + b * XPITCH + word) = d;
+                    if constexpr (CB == 2)
+                    {
+                        // sum of the rounded x~ over each 64-row group (lanes 0-15 / 16-31), fixed order
+                        float sg = (__low2float(o01) + __high2float(o01)) + (__low2float(o23) + __high2float(o23));
+                        #pragma unroll
+                        for (int i = 1; i < 16; i <<= 1) sg += __shfl_xor_sync(0xffffffffu, sg, i);
+                        if ((lane & 15) == 0) gsum[b * XG + 2 * jb + (lane >> 4)] = sg;
+                    }
+                    jb += GEMV_WARPS;
+                    while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
                 }
-                warp_had128(h0, h1, h2, h3, lane);
-                const __half2 o01 = __floats2half2_rn(h0 * kRScale, h1 * kRScale);
-                const __half2 o23 = __floats2half2_rn(h2 * kRScale, h3 * kRScale);
-                const uint32_t u01 = *reinterpret_cast<const uint32_t*>(&o01);
-                const uint32_t u23 = *reinterpret_cast<const uint32_t*>(&o23);
-                uint4 d;
-                d.x = __byte_perm(u01, u01, 0x1010); d.y = __byte_perm(u01, u01, 0x3232);
-                d.z = __byte_perm(u23, u23, 0x1010); d.w = __byte_perm(u23, u23, 0x3232);
-                const int r = jb * 128 + lane * 4;      // row inside the chunk
-                const int word = (r >> 6) * 64 + ((r & 15) >> 2) * 16 + ((r & 63) >> 4) * 4;
-                *reinterpret_cast<uint4*>(xd + b * XPITCH + word) = d;
             }
             __syncthreads();
 
-            // this warp's units of the chunk
-            const int cu1 = blk * G + cg1;
-            const int xbase = (blk * G + cg0) * 64;     // xd word offset of unit u is u*64 - xbase
-            for (; cu < cu1; cu += GEMV_KSLOTS)
+            const int c0 = max(cg0, g0);                // first group of the chunk that belongs to the range
+            if constexpr (CB == 2)
             {
-                cp_async_wait(stages - 1);              // the unit has landed (this lane's pieces)
-                __syncwarp();                           // ... and every other lane's
+                #pragma unroll
+                for (int mb = 0; mb < MB; ++mb)
+                    #pragma unroll
+                    for (int e = 0; e < 2; ++e)
+                    {
+                        const int b = min(mb * 8 + 2 * pq + e, nrows - 1);
+                        float sacc = xsum[mb][e];
+                        for (int g = c0; g < cg1; ++g) sacc += gsum[b * XG + (g - cg0)];
+                        xsum[mb][e] = sacc;
+                    }
+            }
+
+            // every warp walks the chunk's units c0 .. cg1-1
+            const uint32_t* xq = xd + (c0 - cg0) * 64;
+            for (int g = c0; g < cg1; ++g, xq += 64)
+            {
+                cp_async_wait_n<S - 2>();               // the unit has landed (this lane's pieces)
+                __syncwarp();                           // ... and every other lane's; the slot consumed last is free
+                issue();
 
                 // duplicated activations of this lane's tile (rows 16*pq .. +15 of the group): four
                 // 16-byte loads. Batch rows >= m do not exist: row m-1 is read instead (their MMA
@@ -584,7 +648,7 @@ void exl3_gemv_kernel(const GemvParams P)
                 #pragma unroll
                 for (int mb = 0; mb < MB; ++mb)
                 {
-                    const uint32_t* xp = xd + (cu * 64 - xbase) + xrow[mb];
+                    const uint32_t* xp = xq + xrow[mb];
                     #pragma unroll
                     for (int i = 0; i < 4; ++i)
                     {
@@ -593,75 +657,44 @@ void exl3_gemv_kernel(const GemvParams P)
                     }
                 }
 
-                const unsigned char* st = my_ring + cstage * STAGE;
-                #pragma unroll
-                for (int nt = 0; nt < 4; ++nt)
-                {
-                    uint32_t w[K];
-                    load_chunk<K>(reinterpret_cast<const uint32_t*>(st + nt * TILE_BYTES + w_off), w);
-                    const uint32_t prev = *reinterpret_cast<const uint32_t*>(st + nt * TILE_BYTES + p_off);
-                    decode_mma_r<K, CB, MB, 0>(w, prev, xb, acc[nt]);
-                    decode_mma_r<K, CB, MB, 1>(w, prev, xb, acc[nt]);
-                    decode_mma_r<K, CB, MB, 2>(w, prev, xb, acc[nt]);
-                    decode_mma_r<K, CB, MB, 3>(w, prev, xb, acc[nt]);
-                }
-                if constexpr (CB == 2)
-                {
-                    // sum of x~ over the 64 rows of this group: weights of 1.0 in the low half
-                    #pragma unroll
-                    for (int mb = 0; mb < MB; ++mb)
-                        #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            mma_16816(acc1[mb], 0x3c00u, 0x3c00u, 0x3c00u, 0x3c00u, xb[mb][2 * i], xb[mb][2 * i + 1]);
-                }
+                uint32_t w[K];
+                load_chunk_s<K>(w_off + cslot, w);
+                const uint32_t prev = lds32(p_off + cslot);
+                decode_mma_r<K, CB, MB, 0>(w, prev, xb, acc0, acc1);
+                decode_mma_r<K, CB, MB, 1>(w, prev, xb, acc0, acc1);
+                decode_mma_r<K, CB, MB, 2>(w, prev, xb, acc0, acc1);
+                decode_mma_r<K, CB, MB, 3>(w, prev, xb, acc0, acc1);
 
-                __syncwarp();                           // every lane has its words in registers
-                issue();
-                if (++cstage == stages) cstage = 0;
+                cslot += SLOT;
+                if (cslot == S * SLOT) cslot = 0;
             }
         }
 
-        // ---- segment done: reduce the eight warps' partial sums ----
+        // ---- segment done: every lane holds final sums of this CTA's rows for its columns ----
+        const bool whole = (g0 == 0 && g1 == G);       // this CTA owns every row of the block
+        // contributors of this block: the CTAs whose ranges meet [blk*G, (blk+1)*G)
+        const int i_first = split.owner(blk * G);
+        const int i_last = split.owner((blk + 1) * G - 1);
+        float* slots = P.scratch;                      // [cta][2][m][128]
+        const int my_slot = 2 * cta + (blk * G > u0 ? 1 : 0);
+        float* dst = whole ? part : slots + (size_t) my_slot * m * 128;
         #pragma unroll
         for (int mb = 0; mb < MB; ++mb)
         {
-            const int b0 = mb * 8 + 2 * pq;
-            #pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
+            float d0 = acc0[mb][0] + acc1[mb][0], d1 = acc0[mb][1] + acc1[mb][1];
+            float d2 = acc0[mb][2] + acc1[mb][2], d3 = acc0[mb][3] + acc1[mb][3];
+            if constexpr (CB == 2)
             {
-                float d0 = acc[nt][mb][0], d1 = acc[nt][mb][1], d2 = acc[nt][mb][2], d3 = acc[nt][mb][3];
-                if constexpr (CB == 2)
-                {
-                    // w = raw * k_inv + k_bias  ->  sum x*w = k_inv * sum x*raw + k_bias * sum x
-                    const float kinv = __half2float(__ushort_as_half((unsigned short) 0x1eee));
-                    const float kbias = __half2float(__ushort_as_half((unsigned short) 0xc931));
-                    d0 = d0 * kinv + acc1[mb][0] * kbias; d1 = d1 * kinv + acc1[mb][1] * kbias;
-                    d2 = d2 * kinv + acc1[mb][2] * kbias; d3 = d3 * kinv + acc1[mb][3] * kbias;
-                }
-                float* r0 = red + ((size_t) warp * m + b0) * GEMV_RPITCH + nt * 16 + gq;
-                if (b0 < nrows) { r0[0] = d0; r0[8] = d2; }
-                if (b0 + 1 < nrows) { r0[GEMV_RPITCH] = d1; r0[GEMV_RPITCH + 8] = d3; }
+                // w = raw * k_inv + k_bias  ->  sum x*w = k_inv * sum x*raw + k_bias * sum x
+                const float kinv = __half2float(__ushort_as_half((unsigned short) 0x1eee));
+                const float kbias = __half2float(__ushort_as_half((unsigned short) 0xc931));
+                d0 = d0 * kinv + xsum[mb][0] * kbias; d1 = d1 * kinv + xsum[mb][1] * kbias;
+                d2 = d2 * kinv + xsum[mb][0] * kbias; d3 = d3 * kinv + xsum[mb][1] * kbias;
             }
-        }
-        __syncthreads();
-
-        const bool whole = (g0 == 0 && g1 == G);       // this CTA owns every row of the block
-        // contributors of this block: the CTAs whose ranges meet [blk*G, (blk+1)*G)
-        const int i_first = (int) ((((long) blk * G + 1) * ncta + U - 1) / U) - 1;
-        const int i_last = (int) ((((long) (blk + 1) * G) * ncta + U - 1) / U) - 1;
-        float* slots = P.scratch;                      // [cta][2][m][128]
-        const int my_slot = 2 * cta + (blk * G > u0 ? 1 : 0);
-
-        for (int idx = t; idx < nrows * 128; idx += GEMV_THREADS)
-        {
-            const int b = idx >> 7, col = idx & 127;
-            const int hf = col >> 6, cl = col & 63;
-            float sum = 0.f;
-            #pragma unroll
-            for (int s4 = 0; s4 < GEMV_KSLOTS; ++s4)    // k-slot order: deterministic
-                sum += red[((size_t) (s4 * 2 + hf) * m + b) * GEMV_RPITCH + cl];
-            if (whole) part[idx] = sum;
-            else slots[(size_t) my_slot * m * 128 + idx] = sum;
+            const int b0 = mb * 8 + 2 * pq;
+            float* r0 = dst + b0 * 128 + warp * 16 + gq;
+            if (b0 < nrows) { r0[0] = d0; r0[8] = d2; }
+            if (b0 + 1 < nrows) { r0[128] = d1; r0[128 + 8] = d3; }
         }
 
         bool finish = whole;
@@ -686,15 +719,13 @@ void exl3_gemv_kernel(const GemvParams P)
             finish = s_last != 0;
             if (finish)
             {
+                // only the first contributor can have started before this block (its second slot)
+                const int first_slot = 2 * i_first + (blk * G > split.begin(i_first) ? 1 : 0);
                 for (int idx = t; idx < nrows * 128; idx += GEMV_THREADS)
                 {
-                    float sum = 0.f;
-                    for (int i = i_first; i <= i_last; ++i)       // ascending k: deterministic
-                    {
-                        const int iu0 = (int) ((long) U * i / ncta);
-                        const int slot = 2 * i + (blk * G > iu0 ? 1 : 0);
-                        sum += __ldcg(slots + (size_t) slot * m * 128 + idx);
-                    }
+                    float sum = __ldcg(slots + (size_t) first_slot * m * 128 + idx);
+                    for (int i = i_first + 1; i <= i_last; ++i)       // ascending k: deterministic
+                        sum += __ldcg(slots + (size_t) (2 * i) * m * 128 + idx);
                     part[idx] = sum;
                 }
             }
@@ -747,7 +778,7 @@ void exl3_gemv_kernel(const GemvParams P)
         }
         useg += g1 - g0;
     }
-    cp_async_wait(0);
+    cp_async_wait_n<0>();
 }
 
 typedef void (*gemv_fn)(const GemvParams);

@@ -227,8 +227,8 @@ def run_gpu(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": "llama3-8b-shaped decode step, batch 1, EXL3 4.0 bpw x32 layers + 6 bpw lm_head, one CUDA graph",
-                   "l2": "inputs larger than L2 (3.89 GB of weights streamed per step)",
+        "config": {"workload": "llama3-8b-shaped decode step, batch 1, EXL3 4.0 bpw x%d layers + 6 bpw lm_head, one CUDA graph" % LAYERS,
+                   "l2": "inputs larger than L2 (%.2f GB of weights streamed per step)" % (bytes_step / 1e9),
                    "replicas": world},
         "e2e": {"value": round(tok_s_e2e, 2), "unit": UNIT,
                 "h2d_bytes_per_step": host_x.numel() * 2, "d2h_bytes_per_step": host_logits.numel() * 2},
@@ -302,7 +302,7 @@ def run_reference(args):
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(sec_step * 1e3, 1), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "llama3-8b-shaped decode step, batch 1, EXL3 4.0 bpw x32 layers + 6 bpw lm_head",
+        "config": {"workload": "llama3-8b-shaped decode step, batch 1, EXL3 4.0 bpw x%d layers + 6 bpw lm_head" % LAYERS,
                    "note": "CPU reconstruct-then-matmul; the reference ships no CPU code for this codebook, "
                            "so the timed code is the CPU restatement (oracle port)"},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
@@ -314,12 +314,16 @@ def run_reference(args):
 
 
 def main():
+    global LAYERS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=LAYERS,
+                    help="layers of the stack (default: the full 32; fewer only for a small profiler capture)")
     args = ap.parse_args()
+    LAYERS = args.layers
     if args.impl == "reference":
         if args.steps > 5:
             args.steps = 5                 # each step is seconds of CPU work

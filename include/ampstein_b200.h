@@ -103,12 +103,13 @@ int amp_exl3_gemv(const void* x, const void* trellis, void* c, const void* suh, 
 
 /*
  * Same with a fixed number of CTAs (split, 1..1024: the work is cut into that many equal
- * ranges) and cp.async ring depth per warp (stages, 1..4); 0 = choose. The counterpart of the
+ * ranges) and number of 64-row groups of the transformed input held in shared memory at a time
+ * (xgroups, a multiple of 4 up to 128; smaller values force more chunks); 0 = choose. The counterpart of the
  * reference's force_shape_idx / force_num_sms arguments (Q/exl3_gemm.cu:114-127), used by
  * tuning and tests.
  */
 int amp_exl3_gemv_cfg(const void* x, const void* trellis, void* c, const void* suh, const void* svh,
-                      int m, int k, int n, int K, int cb, int c_fp32, int split, int stages,
+                      int m, int k, int n, int K, int cb, int c_fp32, int split, int xgroups,
                       cudaStream_t stream);
 
 /*

@@ -102,16 +102,16 @@ def test_had_r_128_bit_exact(amp, oracle):
     assert np.array_equal(host16(t), oracle.had_hf(x, pre=pre).view(np.uint16))
 
 
-def run_gemm(amp, trellis, suh, svh, x, cb, fp32=False, split=0, stages=0):
+def run_gemm(amp, trellis, suh, svh, x, cb, fp32=False, split=0, xgroups=0):
     from ampstein_b200 import _lib
     m, k = x.shape
     n = trellis.shape[1] * 16
     K = trellis.shape[2] // 16
     out = torch.full((m, n), float("nan"), dtype=torch.float32 if fp32 else torch.float16, device="cuda")
     t, s, v, xx = dev(trellis), dev(suh), dev(svh), dev(x)
-    if split or stages:
+    if split or xgroups:
         _lib.call("amp_exl3_gemv_cfg", xx.data_ptr(), t.data_ptr(), out.data_ptr(), s.data_ptr(), v.data_ptr(),
-                  m, k, n, K, cb, int(fp32), split, stages, torch.cuda.current_stream().cuda_stream)
+                  m, k, n, K, cb, int(fp32), split, xgroups, torch.cuda.current_stream().cuda_stream)
     else:
         amp.exl3_gemm(xx, t, out, s, v, mul1=(cb == 2), mcg=(cb == 1))
     torch.cuda.synchronize()
@@ -137,19 +137,19 @@ def test_gemv_batch_sizes(amp, oracle, m):
     check_close(run_gemm(amp, trellis, suh, svh, x, 0, fp32=True), ref)
 
 
-@pytest.mark.parametrize("split,stages", [(1, 1), (1, 3), (2, 2), (3, 2), (5, 1), (8, 2), (8, 4), (37, 3), (72, 2), (148, 3)])
-def test_gemv_splits_and_ring_depths(amp, oracle, split, stages):
+@pytest.mark.parametrize("split,xgroups", [(1, 0), (1, 4), (2, 8), (3, 0), (5, 4), (8, 12), (8, 0), (37, 4), (72, 0), (148, 4)])
+def test_gemv_splits_and_chunk_sizes(amp, oracle, split, xgroups):
     # k = 2304 = 36 groups x 2 column blocks = 72 units: one CTA walking both blocks, ragged
     # ranges that start and end inside a block, one unit per CTA, more CTAs than units
     trellis, suh, svh, x = make_linear(2304, 256, 4, seed=5000, m=2)
     ref = oracle.linear(x, trellis, suh, svh, 0, fp32_out=True)
-    check_close(run_gemm(amp, trellis, suh, svh, x, 0, split=split, stages=stages), ref)
+    check_close(run_gemm(amp, trellis, suh, svh, x, 0, split=split, xgroups=xgroups), ref)
 
 
 def test_gemv_split_larger_than_blocks(amp, oracle):
     trellis, suh, svh, x = make_linear(256, 128, 5, seed=5100, m=1)
     ref = oracle.linear(x, trellis, suh, svh, 0, fp32_out=True)
-    check_close(run_gemm(amp, trellis, suh, svh, x, 0, split=8, stages=2), ref)
+    check_close(run_gemm(amp, trellis, suh, svh, x, 0, split=8, xgroups=4), ref)
 
 
 def test_config1_single_layer_4096(amp, oracle):
@@ -173,7 +173,7 @@ def test_shared_blocks_large_batch_chunks(amp, oracle, m):
     trellis, suh, svh, x = make_linear(6144, 384, 4, seed=5200 + m, m=m)
     ref = oracle.linear(x, trellis, suh, svh, 0, fp32_out=True)
     check_close(run_gemm(amp, trellis, suh, svh, x, 0), ref)
-    check_close(run_gemm(amp, trellis, suh, svh, x, 0, split=11, stages=2), ref)
+    check_close(run_gemm(amp, trellis, suh, svh, x, 0, split=11, xgroups=4), ref)
 
 
 def test_mgemm_multi_and_sliced(amp, oracle):
