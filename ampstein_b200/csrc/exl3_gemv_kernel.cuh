@@ -13,19 +13,20 @@
 //    in a small global scratch area, summed in ascending-k order so results are bitwise
 //    reproducible). Nobody waits: there is no spin, no lock and no grid-wide barrier (the
 //    reference needs two grid.sync()s, an A_had scratch tensor and a lock buffer).
-//  * Inside the CTA each of the eight warps owns one 16-column tile column of the block and
-//    walks every unit of the range: the warps stay in step (no imbalance inside a CTA, nothing
-//    to reduce between warps), a warp's unit is only 1024 weights, so small matrices still
-//    spread evenly, and a thread needs eight fp32 accumulators, which leaves room for four
-//    CTAs (32 warps) per SM -- the decode is bound by instruction issue, so warps in flight
-//    are what hides its latencies.
+//  * A CTA is four warps; each owns two adjacent 16-column tile columns of the block and walks
+//    every unit of the range: the warps stay in step (no imbalance inside a CTA, nothing to
+//    reduce between warps), a warp's unit is only 2048 weights, so small matrices still spread
+//    evenly, and the per-unit bookkeeping (ring, cursors, activations) is shared by two tiles.
+//    The decode is bound by the issue rate of the integer pipes (about 0.72 instructions per
+//    clock and scheduler whatever the occupancy), so three such CTAs per SM are enough.
 //  * Packed trellis words are streamed global -> shared with 16-byte cp.async copies into
-//    per-warp rings (a slot = one unit = four tiles of one tile column, 128*K bytes). Bulk
+//    per-warp rings (a slot = one unit = four tile rows of two tiles, 256*K bytes). Bulk
 //    (TMA) copies were measured and rejected for this access pattern: one warp sustains only
 //    about one bulk copy per 1000 cycles whatever the ring depth, so the small row pieces of
 //    a column block cap the kernel near 1.4 TB/s, while cp.async streams at the full HBM
-//    rate. The copies are issued before the kernel waits for its predecessor (programmatic
-//    dependent launch), so a layer's weight stream starts under the previous layer's tail.
+//    rate. With programmatic dependent launch (optional) the copies are issued before the
+//    kernel waits for its predecessor, and a CTA releases the dependents when its decode is
+//    done.
 //  * Decode stays in registers. The decoded weights are the A operand of mma.sync.m16n8k16
 //    (16 output columns x 16 k-slots) and the activations the B operand (k-slots x 8 batch
 //    rows), so a batch of up to 8 costs one MMA per 128 weights. For codebooks 0/1 the final
@@ -45,8 +46,9 @@
 
 namespace amp {
 
-constexpr int GEMV_THREADS = 256;
-constexpr int GEMV_WARPS = 8;                  // one per 16-column tile column of a 128-column block
+constexpr int GEMV_NT = 2;                     // 16-column tile columns per warp
+constexpr int GEMV_WARPS = 8 / GEMV_NT;        // the warps of a CTA cover one 128-column block
+constexpr int GEMV_THREADS = 32 * GEMV_WARPS;
 constexpr int GEMV_XCHUNK_MAX = 8192;          // most rows of x~ held in shared memory at a time
 
 // Grouped expert GEMV (fused decode MoE): the kernel's slices are expert runs described by a
@@ -99,12 +101,12 @@ struct GemvParams
     GemvMoe moe;                // grouped-expert modes only
 };
 
-// A ring slot holds one unit of one warp: four tiles (one per tile row of the 64-row group),
-// each padded by 32 bytes so that the four tile rows start in different banks.
-__host__ __device__ constexpr int gemv_row_pitch(int K) { return 32 * K + 32; }      // bytes per tile inside a slot
+// A ring slot holds one unit of one warp: four tile rows (the 64-row group) of GEMV_NT adjacent
+// tiles, each row padded by 32 bytes so that the four rows start in different banks.
+__host__ __device__ constexpr int gemv_row_pitch(int K) { return GEMV_NT * 32 * K + 32; }   // bytes per tile row inside a slot
 __host__ __device__ constexpr int gemv_slot_bytes(int K) { return 4 * gemv_row_pitch(K); }
-// ring depth per warp: enough bytes in flight per SM (depth-1 slots x 32 warps) to cover the HBM latency
-__host__ __device__ constexpr int gemv_stages(int K) { return K <= 2 ? 8 : (K <= 4 ? 6 : 4); }
+// ring depth per warp: enough bytes in flight per SM (depth-1 slots x 24 warps) to cover the HBM latency
+__host__ __device__ constexpr int gemv_stages(int K) { return K <= 2 ? 6 : (K <= 5 ? 5 : 4); }
 
 // byte offsets inside dynamic shared memory
 struct GemvSmem
@@ -128,10 +130,15 @@ __host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int xgrou
     return L;
 }
 
+__device__ __forceinline__ void lds128(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d)
+{
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
+}
+
 __device__ __forceinline__ uint32_t lds32(uint32_t addr)
 {
     uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
     return v;
 }
 
@@ -144,13 +151,13 @@ __device__ __forceinline__ void load_chunk_s(uint32_t addr, uint32_t (&w)[K])
         #pragma unroll
         for (int i = 0; i < K / 4; ++i)
             asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3]) : "r"(addr + 16 * i));
+                         : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3]) : "r"(addr + 16 * i) : "memory");
     }
     else if constexpr (K % 2 == 0)
     {
         #pragma unroll
         for (int i = 0; i < K / 2; ++i)
-            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w[2 * i]), "=r"(w[2 * i + 1]) : "r"(addr + 8 * i));
+            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w[2 * i]), "=r"(w[2 * i + 1]) : "r"(addr + 8 * i) : "memory");
     }
     else
     {
@@ -247,12 +254,13 @@ __device__ __forceinline__ void decode_mma_r(const uint32_t (&w)[K], uint32_t pr
     for (int j = 0; j < 8; ++j) a[j] = a_word<CB>(s[j]);
 #endif
 #ifdef AMP_LAB_NOMMA
+    // keep the decoded words alive without issuing anything
+    asm volatile("" :: "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]));
+#elif defined(AMP_LAB_HALFMMA)
     #pragma unroll
     for (int mb = 0; mb < MB; ++mb)
-    {
-        uint32_t u = a[0] ^ a[1] ^ a[2] ^ a[3] ^ a[4] ^ a[5] ^ a[6] ^ a[7] ^ xb[mb][2 * R];
-        acc0[mb][0] += __uint_as_float(u);
-    }
+        mma_16816(acc0[mb], a[0], a[4], a[1], a[5], xb[mb][2 * R], xb[mb][2 * R + 1]);
+    asm volatile("" :: "r"(a[2]), "r"(a[6]), "r"(a[3]), "r"(a[7]));
 #else
     #pragma unroll
     for (int mb = 0; mb < MB; ++mb)
@@ -298,7 +306,7 @@ __device__ __forceinline__ float moe_act_gate(int act, bool gated, float g, floa
 }
 
 #ifndef AMP_GEMV_MINBLOCKS
-#define AMP_GEMV_MINBLOCKS 4
+#define AMP_GEMV_MINBLOCKS 6
 #endif
 
 __device__ __forceinline__ void cp_async16_s(uint32_t dst, const void* src)
@@ -329,7 +337,7 @@ struct GemvSplit
 // run x projection, input rows gathered by token).  MODE 2: grouped expert down (input = the
 // activation of the run's gate/up rows, computed on the fly).
 template <int K, int CB, int MB, int MODE = 0>
-__global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 2))
+__global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 4))
 void exl3_gemv_kernel(const GemvParams P)
 {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -345,7 +353,9 @@ void exl3_gemv_kernel(const GemvParams P)
     constexpr int RP = gemv_row_pitch(K);
     constexpr int SLOT = gemv_slot_bytes(K);
     constexpr int TILE_BYTES = 32 * K;
-    constexpr int PIECES = 8 * K;                      // 16-byte pieces of a unit (four tiles of 2K pieces)
+    constexpr int NT = GEMV_NT;
+    constexpr int ROWP = NT * 2 * K;                   // 16-byte pieces per tile row of a unit
+    constexpr int PIECES = 4 * ROWP;                   // ... and per unit
     constexpr int NP = (PIECES + 31) / 32;             // copy instructions per unit and lane
 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -360,15 +370,11 @@ void exl3_gemv_kernel(const GemvParams P)
     if constexpr (MODE != 0)
     {
         // the run table is the previous kernel's output: nothing can be fetched before it exists
-        if (P.pdl) { pdl_launch_dependents(); pdl_wait(); }
+        if (P.pdl) pdl_wait();
     }
     const int U = (MODE == 0 ? P.blocks : P.moe.runs[0] * nproj * nbw) * G;
     const int cta = blockIdx.x, ncta = min((int) gridDim.x, U);    // never more ranges than units
-    if (cta >= ncta)
-    {
-        if (MODE == 0 && P.pdl) { pdl_launch_dependents(); pdl_wait(); }
-        return;
-    }
+    if (cta >= ncta) return;                           // an exited CTA counts as having released its dependents
     GemvSplit split;
     split.q = U / ncta;
     split.r = U - split.q * ncta;
@@ -377,7 +383,7 @@ void exl3_gemv_kernel(const GemvParams P)
     const uint32_t ring_s = smem_u32(smem + L.ring) + warp * (S * SLOT);      // this warp's ring
 
     // ---- weight stream: a cursor walks the range's units; piece p = lane + 32 j of a unit is
-    // 16 bytes of tile row p / 2K ----
+    // 16 bytes of tile row p / ROWP ----
     int iu = u0;                                       // next unit to fetch
     int iblk = iu / G, ig = iu - iblk * G;
     uint32_t islot = 0;                                // byte offset of the next slot to fill
@@ -387,8 +393,8 @@ void exl3_gemv_kernel(const GemvParams P)
     #pragma unroll
     for (int j = 0; j < NP; ++j)
     {
-        const int p = lane + 32 * j, row = p / (2 * K);
-        idst[j] = ring_s + row * RP + (p - row * 2 * K) * 16;
+        const int p = lane + 32 * j, row = p / ROWP;
+        idst[j] = ring_s + row * RP + (p - row * ROWP) * 16;
         isrc[j] = nullptr;
     }
 
@@ -410,13 +416,13 @@ void exl3_gemv_kernel(const GemvParams P)
             stride = P.t_stride ? P.t_stride[slice] : P.width;
         }
         const size_t irow = (size_t) (stride >> 4) * TILE_BYTES;          // bytes between tile rows
-        const unsigned char* base = tr + (size_t) (nb * 8 + warp) * TILE_BYTES + (size_t) (4 * g) * irow;
+        const unsigned char* base = tr + (size_t) (nb * 8 + warp * NT) * TILE_BYTES + (size_t) (4 * g) * irow;
         istep = 4 * irow;
         #pragma unroll
         for (int j = 0; j < NP; ++j)
         {
-            const int p = lane + 32 * j, row = p / (2 * K);
-            isrc[j] = base + (size_t) row * irow + (p - row * 2 * K) * 16;
+            const int p = lane + 32 * j, row = p / ROWP;
+            isrc[j] = base + (size_t) row * irow + (p - row * ROWP) * 16;
         }
     };
 
@@ -449,25 +455,27 @@ void exl3_gemv_kernel(const GemvParams P)
         if (islot == S * SLOT) islot = 0;
     };
 
+#ifdef AMP_LAB_WAITFIRST
+    if (MODE == 0 && P.pdl) pdl_wait();
+#endif
     // the weight stream does not depend on the previous kernel: start it before anything else
     if (iu < u1) set_block(iblk, ig);
     #pragma unroll
     for (int j = 0; j < S - 1; ++j) issue();
     if constexpr (MODE == 0)
     {
-        if (P.pdl)
-        {
-            pdl_launch_dependents();                   // the next kernel may start its own weight stream
-            pdl_wait();                                // x is the previous kernel's output
-        }
+#ifndef AMP_LAB_WAITFIRST
+        if (P.pdl) pdl_wait();                         // x is the previous kernel's output
+#endif
     }
 
     // per-lane constants of the consume side
     int xrow[MB];                                      // word offset of this lane's batch row in xd
     #pragma unroll
     for (int mb = 0; mb < MB; ++mb) xrow[mb] = min(mb * 8 + gq, m - 1) * XPITCH + pq * 4;
-    const uint32_t w_off = ring_s + pq * RP + gq * K * 4;                             // this lane's K words of a tile
+    const uint32_t w_off = ring_s + pq * RP + gq * K * 4;                             // this lane's K words of the first tile
     const uint32_t p_off = ring_s + pq * RP + ((gq * K + 8 * K - 1) % (8 * K)) * 4;   // the word before them (ring)
+    const uint32_t xd_s = smem_u32(xd);
 
     uint32_t cslot = 0;                                // byte offset of the next slot to consume
     int useg = u0;
@@ -510,13 +518,15 @@ void exl3_gemv_kernel(const GemvParams P)
             else cbase += (size_t) slice * m * P.width * (P.c_fp32 ? 4 : 2);
         }
 
-        float acc0[MB][4], acc1[MB][4];                // this warp's 16 columns x this lane's batch rows
+        float acc0[NT][MB][4], acc1[NT][MB][4];        // this warp's tile columns x this lane's batch rows
         #pragma unroll
-        for (int mb = 0; mb < MB; ++mb)
-        {
-            acc0[mb][0] = acc0[mb][1] = acc0[mb][2] = acc0[mb][3] = 0.f;
-            acc1[mb][0] = acc1[mb][1] = acc1[mb][2] = acc1[mb][3] = 0.f;
-        }
+        for (int nt = 0; nt < NT; ++nt)
+            #pragma unroll
+            for (int mb = 0; mb < MB; ++mb)
+            {
+                acc0[nt][mb][0] = acc0[nt][mb][1] = acc0[nt][mb][2] = acc0[nt][mb][3] = 0.f;
+                acc1[nt][mb][0] = acc1[nt][mb][1] = acc1[nt][mb][2] = acc1[nt][mb][3] = 0.f;
+            }
         float xsum[MB][2];                             // cb 2 only: sum of x~ over the segment's rows, batch rows 2pq, 2pq+1
         #pragma unroll
         for (int mb = 0; mb < MB; ++mb) xsum[mb][0] = xsum[mb][1] = 0.f;
@@ -634,41 +644,49 @@ void exl3_gemv_kernel(const GemvParams P)
             }
 
             // every warp walks the chunk's units c0 .. cg1-1
-            const uint32_t* xq = xd + (c0 - cg0) * 64;
-            for (int g = c0; g < cg1; ++g, xq += 64)
+            uint32_t xaddr = xd_s + (c0 - cg0) * 256;   // shared address of the unit's x~ (64 words a group)
+            for (int n = cg1 - c0; n > 0; --n, xaddr += 256)
             {
                 cp_async_wait_n<S - 2>();               // the unit has landed (this lane's pieces)
                 __syncwarp();                           // ... and every other lane's; the slot consumed last is free
                 issue();
 
-                // duplicated activations of this lane's tile (rows 16*pq .. +15 of the group): four
+                // duplicated activations of this lane's tile row (rows 16*pq .. +15 of the group): four
                 // 16-byte loads. Batch rows >= m do not exist: row m-1 is read instead (their MMA
                 // columns are never stored).
                 uint32_t xb[MB][16];
                 #pragma unroll
                 for (int mb = 0; mb < MB; ++mb)
-                {
-                    const uint32_t* xp = xq + xrow[mb];
                     #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                    {
-                        uint4 v = *reinterpret_cast<const uint4*>(xp + i * 16);
-                        xb[mb][4 * i] = v.x; xb[mb][4 * i + 1] = v.y; xb[mb][4 * i + 2] = v.z; xb[mb][4 * i + 3] = v.w;
-                    }
-                }
+                        lds128(xaddr + xrow[mb] * 4 + i * 64, xb[mb][4 * i], xb[mb][4 * i + 1], xb[mb][4 * i + 2], xb[mb][4 * i + 3]);
 
-                uint32_t w[K];
-                load_chunk_s<K>(w_off + cslot, w);
-                const uint32_t prev = lds32(p_off + cslot);
-                decode_mma_r<K, CB, MB, 0>(w, prev, xb, acc0, acc1);
-                decode_mma_r<K, CB, MB, 1>(w, prev, xb, acc0, acc1);
-                decode_mma_r<K, CB, MB, 2>(w, prev, xb, acc0, acc1);
-                decode_mma_r<K, CB, MB, 3>(w, prev, xb, acc0, acc1);
+                uint32_t w[NT][K], prev[NT];
+                #pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                {
+                    load_chunk_s<K>(w_off + cslot + nt * TILE_BYTES, w[nt]);
+                    prev[nt] = lds32(p_off + cslot + nt * TILE_BYTES);
+                }
+                #pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                {
+                    decode_mma_r<K, CB, MB, 0>(w[nt], prev[nt], xb, acc0[nt], acc1[nt]);
+                    decode_mma_r<K, CB, MB, 1>(w[nt], prev[nt], xb, acc0[nt], acc1[nt]);
+                    decode_mma_r<K, CB, MB, 2>(w[nt], prev[nt], xb, acc0[nt], acc1[nt]);
+                    decode_mma_r<K, CB, MB, 3>(w[nt], prev[nt], xb, acc0[nt], acc1[nt]);
+                }
 
                 cslot += SLOT;
                 if (cslot == S * SLOT) cslot = 0;
             }
         }
+
+        // The CTA has decoded its last unit: let the next kernel's CTAs be scheduled. They take
+        // the places of CTAs that leave and start their weight stream while this grid exchanges
+        // its partial sums. (Releasing them any earlier fills the SMs with CTAs of kernels that
+        // cannot run yet and pushes this grid's own work into a second wave.)
+        if (P.pdl && useg + (g1 - g0) >= u1) pdl_launch_dependents();
 
         // ---- segment done: every lane holds final sums of this CTA's rows for its columns ----
         const bool whole = (g0 == 0 && g1 == G);       // this CTA owns every row of the block
@@ -679,10 +697,12 @@ void exl3_gemv_kernel(const GemvParams P)
         const int my_slot = 2 * cta + (blk * G > u0 ? 1 : 0);
         float* dst = whole ? part : slots + (size_t) my_slot * m * 128;
         #pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+        #pragma unroll
         for (int mb = 0; mb < MB; ++mb)
         {
-            float d0 = acc0[mb][0] + acc1[mb][0], d1 = acc0[mb][1] + acc1[mb][1];
-            float d2 = acc0[mb][2] + acc1[mb][2], d3 = acc0[mb][3] + acc1[mb][3];
+            float d0 = acc0[nt][mb][0] + acc1[nt][mb][0], d1 = acc0[nt][mb][1] + acc1[nt][mb][1];
+            float d2 = acc0[nt][mb][2] + acc1[nt][mb][2], d3 = acc0[nt][mb][3] + acc1[nt][mb][3];
             if constexpr (CB == 2)
             {
                 // w = raw * k_inv + k_bias  ->  sum x*w = k_inv * sum x*raw + k_bias * sum x
@@ -692,7 +712,7 @@ void exl3_gemv_kernel(const GemvParams P)
                 d2 = d2 * kinv + xsum[mb][0] * kbias; d3 = d3 * kinv + xsum[mb][1] * kbias;
             }
             const int b0 = mb * 8 + 2 * pq;
-            float* r0 = dst + b0 * 128 + warp * 16 + gq;
+            float* r0 = dst + b0 * 128 + (warp * NT + nt) * 16 + gq;
             if (b0 < nrows) { r0[0] = d0; r0[8] = d2; }
             if (b0 + 1 < nrows) { r0[128] = d1; r0[128 + 8] = d3; }
         }
