@@ -64,5 +64,36 @@ def build(force=False, verbose=False):
     return LIB
 
 
+GLUE_SRC = os.path.join(HERE, "csrc_torch", "torch_glue.cpp")
+GLUE = os.path.join(HERE, "_torch_glue.so")
+
+
+def build_torch_glue(force=False):
+    """Builds ampstein_b200/_torch_glue.so: the libtorch C++ layer with the reference's at::Tensor
+    signatures over the C ABI (plain g++, linked against the installed libtorch and the library
+    above)."""
+    build()
+    if not force and os.path.exists(GLUE) and os.path.getmtime(GLUE) >= max(
+            os.path.getmtime(GLUE_SRC), os.path.getmtime(os.path.join(HERE, "..", "include", "ampstein_b200.h"))):
+        return GLUE
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension as ce
+    inc = ce.include_paths("cuda") + [sysconfig.get_paths()["include"]]
+    libdirs = ce.library_paths("cuda")
+    cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-DTORCH_EXTENSION_NAME=_torch_glue",
+           "-DTORCH_API_INCLUDE_EXTENSION_H", "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)]
+    cmd += ["-I" + p for p in inc] + [GLUE_SRC, "-o", GLUE]
+    cmd += ["-L" + p for p in libdirs] + ["-L" + HERE, "-lampstein_b200", "-lc10", "-lc10_cuda", "-ltorch_cpu",
+                                          "-ltorch_cuda", "-ltorch", "-ltorch_python", "-lcudart",
+                                          "-Wl,-rpath,$ORIGIN"] + ["-Wl,-rpath," + p for p in libdirs]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("torch glue build failed:\n%s\n%s" % (r.stdout, r.stderr[-4000:]))
+    return GLUE
+
+
 if __name__ == "__main__":
     print(build(force="-f" in sys.argv, verbose="-v" in sys.argv))
+    if "--glue" in sys.argv:
+        print(build_torch_glue(force="-f" in sys.argv))

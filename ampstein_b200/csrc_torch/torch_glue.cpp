@@ -1,0 +1,266 @@
+// libtorch host layer over the C ABI: the functions the reference's binding file links against,
+// with the reference's own C++ signatures (global namespace, at::Tensor arguments), implemented by
+// unpacking the tensors and calling libampstein_b200.so. Linking this object in place of the
+// reference's exl3 kernel library leaves src/torch/amp_torch.cpp unchanged.
+//
+// Signatures replaced (declarations in the reference at src/torch/amp_torch.cpp):
+//   exl3_gemm              :3775-3787      exl3_mgemm            :3841-3864
+//   reconstruct            :3832-3839      reconstruct_had_slice :11071-11081
+//   had_r_128              :11062-11069    exl3_moe_coop         :3739-3771
+// Error convention: argument and launch errors throw c10::Error (TORCH_CHECK), which every
+// binding of the reference catches and turns into a script exception (:224-236).
+//
+// The same functions are exposed as the Python module ampstein_b200._torch_glue so that the tests
+// can drive this layer with torch tensors (compile with -DAMP_NO_PYBIND to leave the module out).
+#ifndef AMP_NO_PYBIND
+#include <torch/extension.h>
+#else
+#include <ATen/ATen.h>
+#endif
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda_runtime.h>
+
+#include "../../include/ampstein_b200.h"
+
+namespace {
+
+void check_rc(int rc, const char* what)
+{
+    if (rc == 0) return;
+    if (rc < 0) TORCH_CHECK(false, what, ": ", amp_b200_last_error());
+    TORCH_CHECK(false, what, ": CUDA error ", rc, " (", cudaGetErrorString((cudaError_t) rc), ") ", amp_b200_last_error());
+}
+
+int codebook(bool mcg, bool mul1)
+{
+    TORCH_CHECK(!(mcg && mul1), "mcg and mul1 are exclusive");
+    return mul1 ? 2 : (mcg ? 1 : 0);
+}
+
+int bits_of(const at::Tensor& trellis, const char* who)
+{
+    TORCH_CHECK(trellis.dim() == 3 && trellis.scalar_type() == at::kShort, who, ": trellis must be int16 (k/16, n/16, 16K)");
+    TORCH_CHECK(trellis.is_contiguous(), who, ": trellis must be contiguous");
+    const int64_t w = trellis.size(2);
+    TORCH_CHECK(w % 16 == 0 && w / 16 >= 1 && w / 16 <= 8, who, ": unsupported EXL3 bitrate");
+    return (int) (w / 16);
+}
+
+int bits_of(float K, const char* who)
+{
+    TORCH_CHECK(K == (float) (int) K && K >= 1.f && K <= 8.f, who, ": unsupported EXL3 bitrate ", K, " (integer 1..8)");
+    return (int) K;
+}
+
+const void* opt_ptr(const c10::optional<at::Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+
+cudaStream_t stream_of(const at::Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+
+void same_device(const at::Tensor& a, const at::Tensor& b, const char* who)
+{
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.get_device() == b.get_device(), who, ": tensors must live on one CUDA device");
+}
+
+}  // namespace
+
+// C (m, n) = A (m, k) through the quantized weight B. Returns the kernel family used: 90 for the
+// decode kernel (the reference's GEMV index), 100 for the tensor-core prefill kernel.
+int exl3_gemm(const at::Tensor& A, const at::Tensor& B, at::Tensor& C, const c10::optional<at::Tensor>& suh,
+              const c10::optional<at::Tensor>& A_had, const c10::optional<at::Tensor>& svh, int force_shape_idx,
+              bool mcg, bool mul1, int force_num_sms)
+{
+    (void) force_shape_idx; (void) force_num_sms;
+    const c10::cuda::CUDAGuard guard(A.device());
+    same_device(A, B, "exl3_gemm"); same_device(A, C, "exl3_gemm");
+    const int K = bits_of(B, "exl3_gemm");
+    TORCH_CHECK(A.dim() == 2 && C.dim() == 2 && A.is_contiguous() && C.is_contiguous(), "exl3_gemm: A and C must be contiguous 2-D");
+    TORCH_CHECK(A.scalar_type() == at::kHalf || A.scalar_type() == at::kBFloat16, "exl3_gemm: A must be float16 (or bfloat16)");
+    TORCH_CHECK(C.scalar_type() == at::kHalf || C.scalar_type() == at::kFloat, "exl3_gemm: C must be float16 or float32");
+    TORCH_CHECK(suh.has_value() && svh.has_value(), "exl3_gemm: suh and svh are required");
+    TORCH_CHECK(suh->scalar_type() == at::kHalf && svh->scalar_type() == at::kHalf, "exl3_gemm: suh, svh must be float16");
+    const int64_t m = A.size(0), k = A.size(1), n = C.size(1);
+    TORCH_CHECK(B.size(0) * 16 == k && B.size(1) * 16 == n && C.size(0) == m, "exl3_gemm: shape mismatch");
+    TORCH_CHECK(suh->numel() == k && svh->numel() == n, "exl3_gemm: suh / svh length mismatch");
+    if (A_had.has_value() && A_had->defined())
+        TORCH_CHECK(A_had->scalar_type() == at::kHalf && A_had->numel() >= A.numel() && A_had->is_contiguous(),
+                    "exl3_gemm: A_had must be contiguous float16 of A's size");
+    if (m == 0 || n == 0) return 0;
+    const bool bf16 = A.scalar_type() == at::kBFloat16;
+    auto fn = bf16 ? amp_exl3_gemm_bf16 : amp_exl3_gemm;
+    check_rc(fn(A.data_ptr(), B.data_ptr(), C.data_ptr(), suh->data_ptr(), const_cast<void*>(opt_ptr(A_had)), svh->data_ptr(),
+                (int) m, (int) k, (int) n, K, codebook(mcg, mul1), C.scalar_type() == at::kFloat ? 1 : 0, stream_of(A)),
+             "exl3_gemm");
+    return m <= 16 ? 90 : 100;
+}
+
+// Several weights (or equal-width column slices) against one shared input. B / suh / svh are int64
+// device pointer tables. The routed forms of the reference (indices / weights) belong to its
+// token-sorted MoE path and are not part of this library.
+int exl3_mgemm(const at::Tensor& A, const at::Tensor& B, at::Tensor& C, const at::Tensor& suh, const at::Tensor& A_had,
+               const at::Tensor& svh, const c10::optional<at::Tensor>& indices, const c10::optional<at::Tensor>& weights,
+               float K, int force_shape_idx, uint32_t mcg_mult, uint32_t mul1_mult, int min_index, int max_index,
+               int force_num_sms, int num_tokens, const c10::optional<at::Tensor>& size_n_list,
+               const c10::optional<at::Tensor>& c_ptrs, const c10::optional<at::Tensor>& n_stride_list,
+               const c10::optional<at::Tensor>& had_src_list, int num_had_src)
+{
+    (void) force_shape_idx; (void) force_num_sms; (void) min_index; (void) max_index; (void) num_tokens;
+    const c10::cuda::CUDAGuard guard(A.device());
+    TORCH_CHECK(!indices.has_value() && !weights.has_value(), "exl3_mgemm: routed (indices / weights) form is not supported");
+    same_device(A, B, "exl3_mgemm"); same_device(A, C, "exl3_mgemm");
+    TORCH_CHECK(B.scalar_type() == at::kLong && suh.scalar_type() == at::kLong && svh.scalar_type() == at::kLong,
+                "exl3_mgemm: B, suh, svh must be int64 pointer tables");
+    TORCH_CHECK(A.scalar_type() == at::kHalf && A.is_contiguous() && A.dim() == 3 && A.size(0) == 1, "exl3_mgemm: A must be contiguous float16 (1, m, k)");
+    TORCH_CHECK(C.dim() == 3 && C.is_contiguous() && (C.scalar_type() == at::kHalf || C.scalar_type() == at::kFloat),
+                "exl3_mgemm: C must be contiguous (num, m, n) float16 or float32");
+    const int bits = bits_of(K, "exl3_mgemm");
+    const int64_t num = C.size(0), m = C.size(1), width = C.size(2), k = A.size(2);
+    TORCH_CHECK(A.size(1) == m, "exl3_mgemm: row count of A and C differ");
+    TORCH_CHECK(B.numel() >= num && svh.numel() >= num, "exl3_mgemm: pointer tables shorter than the matrix count");
+    const void* cp = nullptr; const void* ns = nullptr; const void* hs = nullptr;
+    if (size_n_list.has_value())
+    {
+        // every entry must equal C.size(2): the slices of one launch share one width
+        TORCH_CHECK(c_ptrs.has_value(), "exl3_mgemm: size_n_list requires c_ptrs");
+        TORCH_CHECK(size_n_list->scalar_type() == at::kInt && c_ptrs->scalar_type() == at::kLong, "exl3_mgemm: size_n_list int32, c_ptrs int64");
+        TORCH_CHECK(c_ptrs->numel() == num && size_n_list->numel() == num, "exl3_mgemm: slice tables do not match C");
+        cp = c_ptrs->data_ptr();
+    }
+    if (had_src_list.has_value())
+    {
+        TORCH_CHECK(size_n_list.has_value() && c_ptrs.has_value() && n_stride_list.has_value(),
+                    "exl3_mgemm: sliced mode requires size_n_list, c_ptrs and n_stride_list");
+        TORCH_CHECK(had_src_list->scalar_type() == at::kInt && n_stride_list->scalar_type() == at::kInt, "exl3_mgemm: had_src_list / n_stride_list must be int32");
+        TORCH_CHECK(had_src_list->numel() >= num && n_stride_list->numel() >= num, "exl3_mgemm: had_src_list / n_stride_list must have one entry per slice");
+        TORCH_CHECK(num_had_src > 0 && suh.numel() >= num_had_src, "exl3_mgemm: suh must hold one entry per source");
+        ns = n_stride_list->data_ptr();
+        hs = had_src_list->data_ptr();
+    }
+    else
+    {
+        TORCH_CHECK(!n_stride_list.has_value(), "exl3_mgemm: n_stride_list requires had_src_list");
+        TORCH_CHECK(suh.numel() >= num, "exl3_mgemm: suh table shorter than the matrix count");
+    }
+    const int cb = mul1_mult ? 2 : (mcg_mult ? 1 : 0);
+    check_rc(amp_exl3_mgemm(A.data_ptr(), B.data_ptr(), C.data_ptr(), suh.data_ptr(), A_had.defined() ? A_had.data_ptr() : nullptr,
+                            svh.data_ptr(), (int) num, (int) m, (int) k, (int) width, bits, cb, C.scalar_type() == at::kFloat ? 1 : 0,
+                            cp, ns, hs, num_had_src, stream_of(A)),
+             "exl3_mgemm");
+    return 90;
+}
+
+void reconstruct(at::Tensor unpacked, at::Tensor packed, float K_, bool mcg, bool mul1)
+{
+    const c10::cuda::CUDAGuard guard(unpacked.device());
+    same_device(unpacked, packed, "reconstruct");
+    const int K = bits_of(packed, "reconstruct");
+    TORCH_CHECK(bits_of(K_, "reconstruct") == K, "reconstruct: K does not match the trellis");
+    TORCH_CHECK(unpacked.scalar_type() == at::kHalf && unpacked.dim() == 2 && unpacked.is_contiguous(), "reconstruct: unpacked must be contiguous float16 (k, n)");
+    const int64_t k = packed.size(0) * 16, n = packed.size(1) * 16;
+    TORCH_CHECK(unpacked.size(0) == k && unpacked.size(1) == n, "reconstruct: shape mismatch");
+    if (k == 0 || n == 0) return;
+    check_rc(amp_exl3_reconstruct(unpacked.data_ptr(), packed.data_ptr(), (int) k, (int) n, K, codebook(mcg, mul1), 0, (int) n, stream_of(unpacked)),
+             "reconstruct");
+}
+
+void reconstruct_had_slice(at::Tensor unpacked, at::Tensor packed, at::Tensor suh, at::Tensor svh, float K_, bool mcg, bool mul1,
+                           int64_t n_offset)
+{
+    const c10::cuda::CUDAGuard guard(unpacked.device());
+    same_device(unpacked, packed, "reconstruct_had_slice");
+    const int K = bits_of(packed, "reconstruct_had_slice");
+    TORCH_CHECK(bits_of(K_, "reconstruct_had_slice") == K, "reconstruct_had_slice: K does not match the trellis");
+    TORCH_CHECK(unpacked.scalar_type() == at::kHalf && unpacked.dim() == 2 && unpacked.is_contiguous(), "reconstruct_had_slice: unpacked must be contiguous float16");
+    TORCH_CHECK(suh.scalar_type() == at::kHalf && svh.scalar_type() == at::kHalf, "reconstruct_had_slice: suh, svh must be float16");
+    const int64_t k = packed.size(0) * 16, n = packed.size(1) * 16, n_out = unpacked.size(1);
+    TORCH_CHECK(unpacked.size(0) == k && n_offset >= 0 && n_offset + n_out <= n, "reconstruct_had_slice: slice outside the weight");
+    TORCH_CHECK(suh.numel() == k && svh.numel() >= n_out, "reconstruct_had_slice: suh / svh length mismatch");
+    if (k == 0 || n_out == 0) return;
+    check_rc(amp_exl3_reconstruct_had(unpacked.data_ptr(), packed.data_ptr(), suh.data_ptr(), svh.data_ptr(), (int) k, (int) n, K,
+                                      codebook(mcg, mul1), (int) n_offset, (int) n_out, stream_of(unpacked)),
+             "reconstruct_had_slice");
+}
+
+void had_r_128(const at::Tensor& input, const at::Tensor& output, const c10::optional<at::Tensor>& pre_scale,
+               const c10::optional<at::Tensor>& post_scale, const float scale)
+{
+    const c10::cuda::CUDAGuard guard(input.device());
+    same_device(input, output, "had_r_128");
+    TORCH_CHECK(input.dim() >= 1 && input.is_contiguous() && output.is_contiguous() && input.numel() == output.numel(), "had_r_128: contiguous tensors of one size");
+    TORCH_CHECK(input.scalar_type() == output.scalar_type() && (input.scalar_type() == at::kHalf || input.scalar_type() == at::kFloat),
+                "had_r_128: float16 or float32, same type in and out");
+    const int64_t cols = input.size(-1), rows = cols ? input.numel() / cols : 0;
+    TORCH_CHECK(cols % 128 == 0, "had_r_128: last dimension must be a multiple of 128");
+    for (const auto* s : { &pre_scale, &post_scale })
+        if (s->has_value() && (*s)->defined())
+            TORCH_CHECK((*s)->scalar_type() == at::kHalf && (*s)->numel() == cols, "had_r_128: scales must be float16 of the row length");
+    if (rows == 0) return;
+    check_rc(amp_had_r_128(input.data_ptr(), output.data_ptr(), opt_ptr(pre_scale), opt_ptr(post_scale), rows, (int) cols,
+                           input.scalar_type() == at::kFloat ? 1 : 0, scale, stream_of(input)),
+             "had_r_128");
+}
+
+// Fused decode MoE. had_g / had_u / act_out are scratch of the reference's kernels that this
+// implementation does not need (accepted, untouched); per-expert bit tables are not supported.
+void exl3_moe_coop(const at::Tensor& x, const at::Tensor& sel, const at::Tensor& rw, int min_expert, int max_expert, int Hi,
+                   const at::Tensor& g_trellis, const at::Tensor& g_suh, const at::Tensor& g_svh,
+                   const at::Tensor& u_trellis, const at::Tensor& u_suh, const at::Tensor& u_svh,
+                   const at::Tensor& d_trellis, const at::Tensor& d_suh, const at::Tensor& d_svh,
+                   const c10::optional<at::Tensor>& g_bias, const c10::optional<at::Tensor>& u_bias, const c10::optional<at::Tensor>& d_bias,
+                   float Kg, float Ku, float Kd, bool mcg, bool mul1, int act, float act_limit, bool gated,
+                   at::Tensor& had_g, at::Tensor& had_u, at::Tensor& gu_g, at::Tensor& gu_u, at::Tensor& act_out, at::Tensor& d_out,
+                   at::Tensor& ctr, at::Tensor& out, const c10::optional<at::Tensor>& sh_out, const c10::optional<at::Tensor>& sh_gate_w,
+                   const c10::optional<at::Tensor>& bits_g, const c10::optional<at::Tensor>& bits_u, const c10::optional<at::Tensor>& bits_d)
+{
+    (void) had_g; (void) had_u; (void) act_out;
+    const c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(!bits_g.has_value() && !bits_u.has_value() && !bits_d.has_value(), "exl3_moe_coop: per-expert bit tables are not supported");
+    TORCH_CHECK(x.dim() == 2 && x.scalar_type() == at::kHalf && x.stride(1) == 1, "exl3_moe_coop: x must be float16 (bsz, H)");
+    TORCH_CHECK(sel.scalar_type() == at::kLong && rw.scalar_type() == at::kHalf && sel.is_contiguous() && rw.is_contiguous() &&
+                sel.dim() == 2 && sel.sizes() == rw.sizes() && sel.size(0) == x.size(0), "exl3_moe_coop: sel int64 / rw float16 (bsz, topk)");
+    for (const at::Tensor* t : { &g_trellis, &g_suh, &g_svh, &u_trellis, &u_suh, &u_svh, &d_trellis, &d_suh, &d_svh })
+        TORCH_CHECK(t->scalar_type() == at::kLong && t->is_cuda(), "exl3_moe_coop: expert tables must be int64 device pointer tables");
+    TORCH_CHECK(!gated || Kg == Ku, "exl3_moe_coop: gate and up must share one bitrate");
+    TORCH_CHECK(d_out.scalar_type() == at::kFloat && d_out.dim() >= 1 && out.scalar_type() == at::kFloat && out.dim() >= 2 && out.stride(-1) == 1,
+                "exl3_moe_coop: d_out and out must be float32");
+    TORCH_CHECK(gu_g.scalar_type() == gu_u.scalar_type() && (gu_g.scalar_type() == at::kFloat || gu_g.scalar_type() == at::kHalf) && gu_g.dim() >= 1,
+                "exl3_moe_coop: gu scratch must be float32 or float16 (slots, I)");
+    TORCH_CHECK(ctr.scalar_type() == at::kInt, "exl3_moe_coop: ctr must be int32");
+
+    amp_moe_coop_args a = {};
+    a.x = x.data_ptr(); a.x_stride = (int) x.stride(0);
+    a.sel = sel.data_ptr(); a.rw = rw.data_ptr();
+    a.bsz = (int) x.size(0); a.topk = (int) sel.size(1);
+    a.H = (int) x.size(1); a.Hi = Hi; a.I = (int) gu_u.size(-1); a.Ho = (int) d_out.size(-1); a.H_out = (int) out.size(-1);
+    a.min_expert = min_expert; a.max_expert = max_expert; a.n_local = (int) u_trellis.numel();
+    a.g_trellis = g_trellis.data_ptr(); a.g_suh = g_suh.data_ptr(); a.g_svh = g_svh.data_ptr();
+    a.u_trellis = u_trellis.data_ptr(); a.u_suh = u_suh.data_ptr(); a.u_svh = u_svh.data_ptr();
+    a.d_trellis = d_trellis.data_ptr(); a.d_suh = d_suh.data_ptr(); a.d_svh = d_svh.data_ptr();
+    a.g_bias = opt_ptr(g_bias); a.u_bias = opt_ptr(u_bias); a.d_bias = opt_ptr(d_bias);
+    a.Kgu = bits_of(Ku, "exl3_moe_coop"); a.Kd = bits_of(Kd, "exl3_moe_coop");
+    a.cb = codebook(mcg, mul1); a.act = act; a.act_limit = act_limit; a.gated = gated ? 1 : 0;
+    a.gu_g = gu_g.data_ptr(); a.gu_u = gu_u.data_ptr(); a.gu_f32 = gu_g.scalar_type() == at::kFloat ? 1 : 0;
+    a.d_out = d_out.data_ptr(); a.ctr = (int*) ctr.data_ptr();
+    a.slots_max = (int) std::min(std::min(gu_g.numel(), gu_u.numel()) / std::max(a.I, 1), d_out.numel() / std::max(a.Ho, 1));
+    TORCH_CHECK(a.bsz <= out.size(-2), "exl3_moe_coop: batch exceeds the output tensor");
+    TORCH_CHECK(ctr.numel() >= amp_exl3_moe_coop_ctr_len(a.slots_max), "exl3_moe_coop: ctr too short for the scratch's slot count");
+    a.out = out.data_ptr(); a.out_stride = (int) out.stride(-2);
+    a.sh_out = opt_ptr(sh_out); a.sh_gate_w = opt_ptr(sh_gate_w);
+    check_rc(amp_exl3_moe_coop(&a, stream_of(x)), "exl3_moe_coop");
+}
+
+int64_t exl3_moe_coop_ctr_len(int64_t slots_max) { return amp_exl3_moe_coop_ctr_len(slots_max); }
+
+#ifndef AMP_NO_PYBIND
+PYBIND11_MODULE(_torch_glue, m)
+{
+    m.doc() = "reference-signature C++ layer of ampstein_b200 (for tests)";
+    m.def("exl3_gemm", &exl3_gemm);
+    m.def("exl3_mgemm", &exl3_mgemm);
+    m.def("reconstruct", &reconstruct);
+    m.def("reconstruct_had_slice", &reconstruct_had_slice);
+    m.def("had_r_128", &had_r_128);
+    m.def("exl3_moe_coop", &exl3_moe_coop);
+    m.def("exl3_moe_coop_ctr_len", &exl3_moe_coop_ctr_len);
+}
+#endif
