@@ -169,6 +169,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     if (A.force_split > 0) ncta = A.force_split;
     if (ncta > units) ncta = units;
     if (ncta > GEMV_MAX_CTAS) ncta = GEMV_MAX_CTAS;
+    if (A.ws_counters && ncta > A.ws_max_ctas) ncta = A.ws_max_ctas;
     AMP_REQUIRE(ncta >= 1, "exl3_gemv: empty problem");
 
     // a range of `per` units starting anywhere needs per + 1 groups of x~ (chunks start at an
@@ -192,7 +193,8 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     P.m = m; P.k = k; P.c_fp32 = A.c_fp32; P.xgroups = xgroups; P.pdl = g_pdl;
     P.blocks = (int) col_blocks;
     P.moe = A.moe;
-    if (int rc = workspace_region(dev, &P.counters, &P.scratch)) return rc;
+    if (A.ws_counters) { P.counters = A.ws_counters; P.scratch = A.ws_scratch; }
+    else if (int rc = workspace_region(dev, &P.counters, &P.scratch)) return rc;
     {
         // address of the status word, looked up once per device
         static int* status_ptr[64] = {};
@@ -242,6 +244,52 @@ AMP_API int amp_exl3_gemv_cfg(const void* x, const void* trellis, void* c, const
                               cudaStream_t stream)
 {
     return launch_gemv(direct(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, split, xgroups), stream);
+}
+
+// ---- allocation-free variant ----------------------------------------------------------------
+// The decode GEMV with its arrival counters and partial-sum slots in a fixed array of the module
+// instead of the lazily allocated per-device workspace. Limits: m <= 4, n <= 131072 (1024 column
+// blocks), at most 512 CTAs. The counters must be zero when a call starts: they are zero when the
+// module is loaded and every launch leaves them zero; the slots need no initial value. All calls
+// on a device share the one array, so two calls that overlap on the GPU (different streams, graph
+// branches) race on it.
+constexpr int GEMV_STATIC_MAX_BLOCKS = 1024;
+constexpr int GEMV_STATIC_MAX_CTAS = 512;
+constexpr int GEMV_STATIC_MAX_M = 4;
+constexpr size_t GEMV_STATIC_COUNTER_BYTES = GEMV_STATIC_MAX_BLOCKS * sizeof(int);
+constexpr size_t GEMV_STATIC_SLOT_BYTES = (size_t) GEMV_STATIC_MAX_CTAS * 2 * GEMV_STATIC_MAX_M * 128 * sizeof(float);
+static __device__ __align__(256) unsigned char g_gemv_static_ws[GEMV_STATIC_COUNTER_BYTES + GEMV_STATIC_SLOT_BYTES];   // 2 MB + 4 KB
+
+AMP_API int amp_exl3_gemv_static(const void* x, const void* trellis, void* c, const void* suh, const void* svh,
+                                 int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream)
+{
+    AMP_REQUIRE(m >= 1 && m <= GEMV_STATIC_MAX_M, "exl3_gemv_static: m must be 1..%d (got %d); larger batches need amp_exl3_gemv",
+                GEMV_STATIC_MAX_M, m);
+    AMP_REQUIRE(n > 0 && n % 128 == 0 && n / 128 <= GEMV_STATIC_MAX_BLOCKS,
+                "exl3_gemv_static: n must be a multiple of 128 up to %d (got %d); wider matrices need amp_exl3_gemv",
+                GEMV_STATIC_MAX_BLOCKS * 128, n);
+    int dev = 0;
+    if (cudaError_t e = cudaGetDevice(&dev)) return cuda_rc(e, "cudaGetDevice");
+    // set-up, once per device: the address of this device's copy of the array
+    static unsigned char* ws_ptr[64] = {};
+    static std::mutex mu;
+    unsigned char* ws;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        unsigned char*& slot = ws_ptr[dev & 63];
+        if (!slot)
+        {
+            unsigned char* ptr = nullptr;
+            if (cudaError_t e = cudaGetSymbolAddress((void**) &ptr, g_gemv_static_ws)) return cuda_rc(e, "exl3_gemv_static: symbol address");
+            slot = ptr;
+        }
+        ws = slot;
+    }
+    GemvLaunch A = direct(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, 0, 0);
+    A.ws_counters = (int*) ws;
+    A.ws_scratch = (float*) (ws + GEMV_STATIC_COUNTER_BYTES);
+    A.ws_max_ctas = GEMV_STATIC_MAX_CTAS;
+    return launch_gemv(A, stream);
 }
 
 // Reads and clears the GEMV status word of the current device (synchronises the device).

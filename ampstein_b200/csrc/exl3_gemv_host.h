@@ -15,6 +15,9 @@ struct GemvLaunch
     int mode;            // 0 dense / bundle, 1 grouped gate+up, 2 grouped down
     int max_slices;      // grouped modes: most slices the run table can describe (slices = the expected count)
     GemvMoe moe;
+    int* ws_counters;    // caller-provided arrival counters / partial-sum slots instead of the
+    float* ws_scratch;   // per-device workspace (both or neither); ws_max_ctas bounds the CTA count
+    int ws_max_ctas;
 };
 
 int launch_gemv(const GemvLaunch& A, cudaStream_t stream);

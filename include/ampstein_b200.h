@@ -102,6 +102,20 @@ int amp_exl3_gemv(const void* x, const void* trellis, void* c, const void* suh, 
                   int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream);
 
 /*
+ * The decode kernel without any device allocation, ever: its arrival counters and partial-sum
+ * slots live in a fixed 2 MB array inside the library instead of the lazily allocated workspace.
+ * This entry point has no counterpart in the reference. Limits: m = 1..4, n <= 131072 (a multiple
+ * of 128), k a multiple of 128; anything larger is refused with a negative return and a message.
+ * The first call on a device looks up the array's address (cudaGetSymbolAddress), so it should
+ * come before any stream capture; later calls only launch. Every call on a device uses the same
+ * array: calls that overlap on the GPU (other streams, parallel graph branches) race on it and
+ * must be serialised by the caller. The counters in the array are zero when the library is
+ * loaded and each launch leaves them zero; nothing else needs initialising.
+ */
+int amp_exl3_gemv_static(const void* x, const void* trellis, void* c, const void* suh, const void* svh,
+                         int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream);
+
+/*
  * Same with a fixed number of CTAs (split, 1..1024: the work is cut into that many equal
  * ranges) and number of 64-row groups of the transformed input held in shared memory at a time
  * (xgroups, a multiple of 4 up to 128; smaller values force more chunks); 0 = choose. The counterpart of the
