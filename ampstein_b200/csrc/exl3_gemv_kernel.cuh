@@ -99,14 +99,18 @@ struct GemvParams
     int* counters;              // [blocks] arrival counters, zero between launches
     int* status;                // device status word (the kernel has no waits that can run out; kept for the ABI)
     GemvMoe moe;                // grouped-expert modes only
+#ifdef AMP_LAB_STAMP
+    unsigned long long* stamps; // [gridDim.x][4] globaltimer at entry, x~ ready, decode done, exit
+#endif
 };
 
 // A ring slot holds one unit of one warp: four tile rows (the 64-row group) of GEMV_NT adjacent
 // tiles, each row padded by 32 bytes so that the four rows start in different banks.
 __host__ __device__ constexpr int gemv_row_pitch(int K) { return GEMV_NT * 32 * K + 32; }   // bytes per tile row inside a slot
 __host__ __device__ constexpr int gemv_slot_bytes(int K) { return 4 * gemv_row_pitch(K); }
-// ring depth per warp: enough bytes in flight per SM (depth-1 slots x 24 warps) to cover the HBM latency
-__host__ __device__ constexpr int gemv_stages(int K) { return K <= 2 ? 6 : (K <= 5 ? 5 : 4); }
+// ring depth per warp: deep enough that a layer-sized matrix is requested almost whole when the
+// grid starts (a CTA's range is then 4-30 units), so HBM streams from the first microsecond on
+__host__ __device__ constexpr int gemv_stages(int K) { return K <= 4 ? 8 : (K <= 6 ? 6 : 5); }
 
 // byte offsets inside dynamic shared memory
 struct GemvSmem
@@ -273,6 +277,18 @@ __device__ __forceinline__ void decode_mma_r(const uint32_t (&w)[K], uint32_t pr
 #endif
 }
 
+#ifdef AMP_LAB_STAMP
+__device__ __forceinline__ unsigned long long lab_now()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define LAB_STAMP(i) do { if (threadIdx.x == 0) P.stamps[blockIdx.x * 4 + (i)] = lab_now(); } while (0)
+#else
+#define LAB_STAMP(i) do { } while (0)
+#endif
+
 __device__ __forceinline__ void pdl_launch_dependents()
 {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -306,7 +322,7 @@ __device__ __forceinline__ float moe_act_gate(int act, bool gated, float g, floa
 }
 
 #ifndef AMP_GEMV_MINBLOCKS
-#define AMP_GEMV_MINBLOCKS 6
+#define AMP_GEMV_MINBLOCKS 4
 #endif
 
 __device__ __forceinline__ void cp_async16_s(uint32_t dst, const void* src)
@@ -358,6 +374,12 @@ void exl3_gemv_kernel(const GemvParams P)
     constexpr int PIECES = 4 * ROWP;                   // ... and per unit
     constexpr int NP = (PIECES + 31) / 32;             // copy instructions per unit and lane
 
+    LAB_STAMP(0);
+    // Dependent launch: the next kernel's CTAs may be scheduled from now on. The launch asks for
+    // so much shared memory that an SM holds exactly this grid's share of CTAs, so they only move
+    // in as CTAs of this grid leave -- one for one, which keeps the next grid evenly spread --
+    // and start their weight stream under this grid's partial-sum exchange.
+    if (P.pdl) pdl_launch_dependents();
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int gq = lane >> 2, pq = lane & 3;
     const int m = P.m, k = P.k;
@@ -455,19 +477,29 @@ void exl3_gemv_kernel(const GemvParams P)
         if (islot == S * SLOT) islot = 0;
     };
 
-#ifdef AMP_LAB_WAITFIRST
-    if (MODE == 0 && P.pdl) pdl_wait();
-#endif
-    // the weight stream does not depend on the previous kernel: start it before anything else
-    if (iu < u1) set_block(iblk, ig);
-    #pragma unroll
-    for (int j = 0; j < S - 1; ++j) issue();
+    // the two lines of svh this CTA may need at the very end are pulled into L2 now
     if constexpr (MODE == 0)
     {
-#ifndef AMP_LAB_WAITFIRST
-        if (P.pdl) pdl_wait();                         // x is the previous kernel's output
-#endif
+        if (t < 2)
+        {
+            const int slice0 = iblk / nbw;
+            const __half* svh0 = P.tables ? reinterpret_cast<const __half*>(P.t_svh[slice0]) : P.svh;
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(svh0 + (size_t) (iblk - slice0 * nbw) * 128 + t * 64));
+        }
     }
+
+    // The weight stream does not depend on the previous kernel. With dependent launch it starts
+    // before the wait for that kernel; otherwise right behind the loads of the first x~ pass
+    // (those are tiny and must not queue behind the weight burst of the whole grid).
+    if (iu < u1) set_block(iblk, ig);
+    bool started = false;
+    if (MODE != 0 || P.pdl)
+    {
+        #pragma unroll
+        for (int j = 0; j < S - 1; ++j) issue();
+        started = true;
+    }
+    bool waited = false;                               // MODE 0 waits for its predecessor inside the first x~ pass
 
     // per-lane constants of the consume side
     int xrow[MB];                                      // word offset of this lane's batch row in xd
@@ -541,6 +573,77 @@ void exl3_gemv_kernel(const GemvParams P)
             // x~ = fp16(H(x * suh) / sqrt(128)), stored duplicated ((v, v) per word) and in the
             // order the B fragments are read: word = group*64 + (row%16 / 4)*16 + (row%64 / 16)*4 + row%4.
             // Tasks (batch row b, 128-row block jb) go round the warps.
+            // transform one task's four values per lane and store them; b, jb name the task
+            auto had_store = [&](int b, int jb, float h0, float h1, float h2, float h3)
+            {
+                warp_had128(h0, h1, h2, h3, lane);
+                const __half2 o01 = __floats2half2_rn(h0 * kRScale, h1 * kRScale);
+                const __half2 o23 = __floats2half2_rn(h2 * kRScale, h3 * kRScale);
+                const uint32_t u01 = *reinterpret_cast<const uint32_t*>(&o01);
+                const uint32_t u23 = *reinterpret_cast<const uint32_t*>(&o23);
+                uint4 d;
+                d.x = __byte_perm(u01, u01, 0x1010); d.y = __byte_perm(u01, u01, 0x3232);
+                d.z = __byte_perm(u23, u23, 0x1010); d.w = __byte_perm(u23, u23, 0x3232);
+                const int r = jb * 128 + lane * 4;      // row inside the chunk
+                const int word = (r >> 6) * 64 + ((r & 15) >> 2) * 16 + ((r & 63) >> 4) * 4;
+                *reinterpret_cast<uint4*>(xd + b * XPITCH + word) = d;
+                if constexpr (CB == 2)
+                {
+                    // sum of the rounded x~ over each 64-row group (lanes 0-15 / 16-31), fixed order
+                    float sg = (__low2float(o01) + __high2float(o01)) + (__low2float(o23) + __high2float(o23));
+                    #pragma unroll
+                    for (int i = 1; i < 16; i <<= 1) sg += __shfl_xor_sync(0xffffffffu, sg, i);
+                    if ((lane & 15) == 0) gsum[b * XG + 2 * jb + (lane >> 4)] = sg;
+                }
+            };
+            if constexpr (MODE == 0)
+            {
+                // up to four tasks per pass: all their loads are in flight before the first
+                // transform (at grid start a load takes a microsecond), and the weight stream is
+                // started right behind the first pass's loads
+                int b = 0, jb = warp;
+                while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
+                do
+                {
+                    constexpr int TB = 4;
+                    half4 vx[TB], vs[TB];
+                    int tb[TB], tj[TB];
+                    #pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                    {
+                        tb[i] = b; tj[i] = jb;
+                        if (b < nrows)
+                        {
+                            vs[i] = *reinterpret_cast<const half4*>(suh + (size_t) cg0 * 64 + (size_t) jb * 128 + lane * 4);
+                            jb += GEMV_WARPS;
+                            while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
+                        }
+                        else tb[i] = -1;
+                    }
+                    // suh belongs to the weights; x is the previous kernel's output
+                    if (!waited) { if (P.pdl) pdl_wait(); waited = true; }
+                    #pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                        if (tb[i] >= 0)
+                            vx[i] = *reinterpret_cast<const half4*>(P.x + (size_t) tb[i] * k + (size_t) cg0 * 64 + (size_t) tj[i] * 128 + lane * 4);
+                    if (!started)
+                    {
+                        #pragma unroll
+                        for (int j = 0; j < S - 1; ++j) issue();
+                        started = true;
+                    }
+                    #pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                    {
+                        if (tb[i] < 0) continue;
+                        half4 v = vx[i];
+                        v.x = __hmul2(v.x, vs[i].x);
+                        v.y = __hmul2(v.y, vs[i].y);
+                        had_store(tb[i], tj[i], __low2float(v.x), __high2float(v.x), __low2float(v.y), __high2float(v.y));
+                    }
+                } while (b < nrows);
+            }
+            else
             {
                 int b = 0, jb = warp;
                 while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
@@ -603,31 +706,14 @@ void exl3_gemv_kernel(const GemvParams P)
                         half4 sc = *reinterpret_cast<const half4*>(suh + col);
                         h0 *= __low2float(sc.x); h1 *= __high2float(sc.x); h2 *= __low2float(sc.y); h3 *= __high2float(sc.y);
                     }
-                    warp_had128(h0, h1, h2, h3, lane);
-                    const __half2 o01 = __floats2half2_rn(h0 * kRScale, h1 * kRScale);
-                    const __half2 o23 = __floats2half2_rn(h2 * kRScale, h3 * kRScale);
-                    const uint32_t u01 = *reinterpret_cast<const uint32_t*>(&o01);
-                    const uint32_t u23 = *reinterpret_cast<const uint32_t*>(&o23);
-                    uint4 d;
-                    d.x = __byte_perm(u01, u01, 0x1010); d.y = __byte_perm(u01, u01, 0x3232);
-                    d.z = __byte_perm(u23, u23, 0x1010); d.w = __byte_perm(u23, u23, 0x3232);
-                    const int r = jb * 128 + lane * 4;      // row inside the chunk
-                    const int word = (r >> 6) * 64 + ((r & 15) >> 2) * 16 + ((r & 63) >> 4) * 4;
-                    *reinterpret_cast<uint4*>(xd + b * XPITCH + word) = d;
-                    if constexpr (CB == 2)
-                    {
-                        // sum of the rounded x~ over each 64-row group (lanes 0-15 / 16-31), fixed order
-                        float sg = (__low2float(o01) + __high2float(o01)) + (__low2float(o23) + __high2float(o23));
-                        #pragma unroll
-                        for (int i = 1; i < 16; i <<= 1) sg += __shfl_xor_sync(0xffffffffu, sg, i);
-                        if ((lane & 15) == 0) gsum[b * XG + 2 * jb + (lane >> 4)] = sg;
-                    }
+                    had_store(b, jb, h0, h1, h2, h3);
                     jb += GEMV_WARPS;
                     while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
                 }
             }
             __syncthreads();
 
+            if (useg == u0 && cg0 == (g0 & ~1)) LAB_STAMP(1);
             const int c0 = max(cg0, g0);                // first group of the chunk that belongs to the range
             if constexpr (CB == 2)
             {
@@ -682,11 +768,8 @@ void exl3_gemv_kernel(const GemvParams P)
             }
         }
 
-        // The CTA has decoded its last unit: let the next kernel's CTAs be scheduled. They take
-        // the places of CTAs that leave and start their weight stream while this grid exchanges
-        // its partial sums. (Releasing them any earlier fills the SMs with CTAs of kernels that
-        // cannot run yet and pushes this grid's own work into a second wave.)
-        if (P.pdl && useg + (g1 - g0) >= u1) pdl_launch_dependents();
+
+        if (useg + (g1 - g0) >= u1) LAB_STAMP(2);
 
         // ---- segment done: every lane holds final sums of this CTA's rows for its columns ----
         const bool whole = (g0 == 0 && g1 == G);       // this CTA owns every row of the block
@@ -799,6 +882,7 @@ void exl3_gemv_kernel(const GemvParams P)
         useg += g1 - g0;
     }
     cp_async_wait_n<0>();
+    LAB_STAMP(3);
 }
 
 typedef void (*gemv_fn)(const GemvParams);

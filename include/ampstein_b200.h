@@ -195,9 +195,8 @@ int amp_exl3_moe_coop(const amp_moe_coop_args* args, cudaStream_t stream);
 long amp_exl3_moe_coop_ctr_len(long slots_max);
 
 /*
- * Programmatic dependent launch of the decode kernels (default off: measured slower than plain
- * stream order inside CUDA graphs on B200): each kernel starts its weight stream before waiting
- * for the kernel in front of it. Returns the previous setting.
+ * Programmatic dependent launch of the decode kernels (default on): each kernel starts its
+ * weight stream before waiting for the kernel in front of it. Returns the previous setting.
  * The reference has no counterpart (it launches cooperative kernels back to back).
  */
 int amp_exl3_set_pdl(int enable);
