@@ -5,6 +5,7 @@
 #include "host_common.h"
 #include "exl3_gemv_host.h"
 #include <mutex>
+#include <cstdlib>
 
 namespace amp {
 
@@ -83,6 +84,9 @@ static int workspace_region(int dev, int** counters, float** scratch)
 // dependent grid piles up on the SMs that drain first and the chain runs 10 % slower than
 // without dependent launch; with the padding it runs 3 % faster (B200, inside CUDA graphs).
 int g_pdl = 1;
+int g_cluster = 1;        // cluster form of the partial-sum exchange (lab switch: AMP_LAB_NOCLUSTER=1 in the environment)
+// (with more than 16 units per CTA the grid of 8 x blocks CTAs is too coarse: measured slower)
+constexpr int GEMV_CLUSTER = 8, GEMV_CLUSTER_MAX_M = 4, GEMV_CLUSTER_MAX_UNITS = 16;
 
 int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
 {
@@ -167,6 +171,20 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
         if (S >= 1) ncta = col_blocks * S;
         else { ncta = (long) D.sms * ctas_per_sm; while (ncta > D.sms && units / ncta < 4) ncta -= D.sms; }
     }
+    // Layer-sized single matrices at small batch: one cluster of eight CTAs per column block. The
+    // partial sums then travel through distributed shared memory and a cluster barrier (about a
+    // microsecond) instead of global memory, a fence, an atomic and a read-back (about three).
+    int cluster = 0;
+    {
+        static int env_checked = 0;
+        if (!env_checked) { env_checked = 1; if (getenv("AMP_LAB_NOCLUSTER")) g_cluster = 0; }
+    }
+    if (!A.mode && !A.ws_counters && A.force_split == 0 && A.force_xgroups == 0 && m <= GEMV_CLUSTER_MAX_M && G % GEMV_CLUSTER == 0 &&
+        G / GEMV_CLUSTER >= 2 && G / GEMV_CLUSTER <= GEMV_CLUSTER_MAX_UNITS && col_blocks * GEMV_CLUSTER <= (long) D.sms * ctas_per_sm && g_cluster)
+    {
+        cluster = GEMV_CLUSTER;
+        ncta = col_blocks * GEMV_CLUSTER;
+    }
     if (A.force_split > 0) ncta = A.force_split;
     if (ncta > units) ncta = units;
     if (ncta > GEMV_MAX_CTAS) ncta = GEMV_MAX_CTAS;
@@ -182,7 +200,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
         const long need = (per + 1 + 3) / 4 * 4;
         if (need < xgroups) xgroups = (int) need;
     }
-    L = gemv_smem_layout(K, m, xgroups);
+    L = gemv_smem_layout(K, m, xgroups, cluster);
     // Ask for enough shared memory that exactly ctas_per_sm CTAs fit on an SM. The grid is sized
     // for that many; if an SM could take one more, a dependent grid that starts while this one
     // drains would pile four CTAs on the SMs that free up first and leave others with two.
@@ -190,6 +208,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     {
         const int fit_one_more = smem_per_sm / (ctas_per_sm + 1) - 1024;      // largest size of which ctas_per_sm + 1 fit
         if (smem_bytes <= fit_one_more) smem_bytes = fit_one_more + 16;
+        if (smem_bytes > D.smem_optin) smem_bytes = D.smem_optin;
     }
     if (cudaError_t e = ensure_smem(fn, smem_bytes, dev)) return cuda_rc(e, "exl3_gemv smem attribute");
 
@@ -199,7 +218,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     P.t_trellis = A.t_trellis; P.t_suh = A.t_suh; P.t_svh = A.t_svh; P.t_c = A.t_c;
     P.t_stride = A.t_stride; P.t_src = A.t_src;
     P.tables = A.tables; P.width = A.width; P.stride = A.stride;
-    P.m = m; P.k = k; P.c_fp32 = A.c_fp32; P.xgroups = xgroups; P.pdl = g_pdl;
+    P.m = m; P.k = k; P.c_fp32 = A.c_fp32; P.xgroups = xgroups; P.pdl = g_pdl; P.cluster = cluster;
     P.blocks = (int) col_blocks;
     P.moe = A.moe;
     if (A.ws_counters) { P.counters = A.ws_counters; P.scratch = A.ws_scratch; }
@@ -218,11 +237,22 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int nattr = 0;
+    if (g_pdl)
+    {
+        attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+        ++nattr;
+    }
+    if (cluster)
+    {
+        attr[nattr].id = cudaLaunchAttributeClusterDimension;
+        attr[nattr].val.clusterDim.x = cluster; attr[nattr].val.clusterDim.y = 1; attr[nattr].val.clusterDim.z = 1;
+        ++nattr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = g_pdl ? 1 : 0;
+    cfg.numAttrs = nattr;
     return cuda_rc(cudaLaunchKernelEx(&cfg, fn, P), "exl3_gemv launch");
 }
 

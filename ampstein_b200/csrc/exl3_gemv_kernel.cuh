@@ -94,6 +94,7 @@ struct GemvParams
     int c_fp32;
     int xgroups;                // 64-row groups of x~ held in shared memory at a time (multiple of 4)
     int pdl;                    // launched with programmatic stream serialization
+    int cluster;                // 0, or CTAs per thread-block cluster: one cluster = one column block (MODE 0)
     int blocks;                 // column blocks in total (slices * width / 128)
     float* scratch;             // [gridDim.x][2][m][128] partial sums of blocks shared between CTAs
     int* counters;              // [blocks] arrival counters, zero between launches
@@ -115,14 +116,14 @@ __host__ __device__ constexpr int gemv_stages(int K) { return K <= 4 ? 8 : (K <=
 // byte offsets inside dynamic shared memory
 struct GemvSmem
 {
-    int part, xd, gsum, ring, total;
+    int part, xd, gsum, ring, xchg, total;
 };
 
 // 32-bit words per batch row of the duplicated x~ (+16 keeps fragment loads conflict-free)
 __host__ __device__ constexpr int gemv_xpitch(int xgroups) { return xgroups * 64 + 16; }
 
 // xrows: rows of x~ / partial sums kept (the batch size m)
-__host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int xgroups)
+__host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int xgroups, int cluster = 0)
 {
     GemvSmem L;
     L.part = 0;                                             // [xrows][128] fp32: the finished block
@@ -130,7 +131,8 @@ __host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int xgrou
     L.gsum = L.xd + xrows * gemv_xpitch(xgroups) * 4;       // [xrows][xgroups] fp32 (codebook 2: sum of x~ per group)
     L.ring = L.gsum + xrows * xgroups * 4;
     L.ring = (L.ring + 127) & ~127;
-    L.total = L.ring + GEMV_WARPS * gemv_stages(K) * gemv_slot_bytes(K);
+    L.xchg = L.ring + GEMV_WARPS * gemv_stages(K) * gemv_slot_bytes(K);   // [cluster][xrows][128] fp32, filled by the cluster's CTAs
+    L.total = L.xchg + cluster * xrows * 128 * 4;
     return L;
 }
 
@@ -277,6 +279,32 @@ __device__ __forceinline__ void decode_mma_r(const uint32_t (&w)[K], uint32_t pr
 #endif
 }
 
+// thread-block cluster helpers: rank of this CTA, address of a shared-memory location in another
+// CTA of the cluster, a store there, and the cluster-wide barrier (release / acquire)
+__device__ __forceinline__ uint32_t cluster_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t cluster_map(uint32_t saddr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+
+__device__ __forceinline__ void cluster_st_f32(uint32_t addr, float v)
+{
+    asm volatile("st.shared::cluster.f32 [%0], %1;" :: "r"(addr), "f"(v) : "memory");
+}
+
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 #ifdef AMP_LAB_STAMP
 __device__ __forceinline__ unsigned long long lab_now()
 {
@@ -357,7 +385,7 @@ __global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 4))
 void exl3_gemv_kernel(const GemvParams P)
 {
     extern __shared__ __align__(128) unsigned char smem[];
-    const GemvSmem L = gemv_smem_layout(K, P.m, P.xgroups);
+    const GemvSmem L = gemv_smem_layout(K, P.m, P.xgroups, P.cluster);
     const int XPITCH = gemv_xpitch(P.xgroups);
     const int XG = P.xgroups;
     float* part = reinterpret_cast<float*>(smem + L.part);
@@ -779,6 +807,10 @@ void exl3_gemv_kernel(const GemvParams P)
         float* slots = P.scratch;                      // [cta][2][m][128]
         const int my_slot = 2 * cta + (blk * G > u0 ? 1 : 0);
         float* dst = whole ? part : slots + (size_t) my_slot * m * 128;
+        // cluster form: the partial goes straight into the shared memory of the cluster's first CTA
+        const bool clustered = (MODE == 0) && P.cluster > 0;
+        uint32_t xdst = 0;
+        if (clustered) xdst = cluster_map(smem_u32(smem + L.xchg), 0) + cluster_rank() * (m * 128 * 4);
         #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
         #pragma unroll
@@ -795,13 +827,37 @@ void exl3_gemv_kernel(const GemvParams P)
                 d2 = d2 * kinv + xsum[mb][0] * kbias; d3 = d3 * kinv + xsum[mb][1] * kbias;
             }
             const int b0 = mb * 8 + 2 * pq;
+            if (clustered)
+            {
+                const uint32_t r0 = xdst + (b0 * 128 + (warp * NT + nt) * 16 + gq) * 4;
+                if (b0 < nrows) { cluster_st_f32(r0, d0); cluster_st_f32(r0 + 32, d2); }
+                if (b0 + 1 < nrows) { cluster_st_f32(r0 + 512, d1); cluster_st_f32(r0 + 512 + 32, d3); }
+                continue;
+            }
             float* r0 = dst + b0 * 128 + (warp * NT + nt) * 16 + gq;
             if (b0 < nrows) { r0[0] = d0; r0[8] = d2; }
             if (b0 + 1 < nrows) { r0[128] = d1; r0[128 + 8] = d3; }
         }
 
         bool finish = whole;
-        if (!whole)
+        if (clustered)
+        {
+            // every CTA of the cluster has delivered its partial when the barrier completes; the
+            // first CTA adds them in rank order (= ascending k) and finishes the block
+            cluster_sync_all();
+            finish = cluster_rank() == 0;
+            if (finish)
+            {
+                const float* xc = reinterpret_cast<const float*>(smem + L.xchg);
+                for (int idx = t; idx < nrows * 128; idx += GEMV_THREADS)
+                {
+                    float sum = xc[idx];
+                    for (int r = 1; r < P.cluster; ++r) sum += xc[r * m * 128 + idx];
+                    part[idx] = sum;
+                }
+            }
+        }
+        else if (!whole)
         {
             // publish the partial, then count arrivals: the last contributor finishes the block.
             // One thread fences after the block-wide barrier (the fence is cumulative over the

@@ -45,7 +45,11 @@ def test_static_scratch_matches_allocating_entry_point_twice_in_a_row(amp, oracl
         first = run("amp_exl3_gemv_static", xx, t, s, v, m, k, n, K)
         second = run("amp_exl3_gemv_static", xx, t, s, v, m, k, n, K)
         torch.cuda.synchronize()
-        assert torch.equal(first, ref) and torch.equal(second, ref)
+        # the two entry points may cut the rows into different ranges (different fp32 summation
+        # order), so they agree to fp16 rounding; the same entry point twice agrees bit for bit
+        assert torch.equal(first, second)
+        scale = ref.float().abs().max()
+        assert float((first.float() - ref.float()).abs().max() / scale) < 2e-3
         want = oracle.linear(x, trellis, suh, svh, 0, fp32_out=True)
         err = np.max(np.abs(first.float().cpu().numpy() - want)) / np.max(np.abs(want))
         assert err < 1e-2                  # max relative error against the fp32-accumulated oracle
