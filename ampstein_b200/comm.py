@@ -151,7 +151,9 @@ class P2PComm:
 
     # ---- operations ------------------------------------------------------------------------
 
-    def allreduce(self, x, rank=None):
+    def allreduce(self, x, rank=None, out=None):
+        """Sum of every rank's x, returned as a new tensor (or written into `out`, a contiguous
+        fp16 tensor of x's size on the same device, for callers that keep fixed buffers)."""
         if rank is None:
             rank = self.rank
         if rank is None or not (0 <= rank < self.N):
@@ -166,7 +168,11 @@ class P2PComm:
             raise ValueError("comm.allreduce: x must be contiguous fp16 on the rank's device, "
                              "n % 8 == 0, n <= cap")
         n = x.numel()
-        out = torch.empty_like(x)
+        if out is None:
+            out = torch.empty_like(x)
+        elif not (isinstance(out, torch.Tensor) and out.is_cuda and out.dtype == torch.float16 and out.is_contiguous()
+                  and out.numel() == n and out.device == x.device):
+            raise ValueError("comm.allreduce: out must be a contiguous fp16 tensor of x's size on x's device")
         bufs, ctls = self._bufs[rank]
         with torch.cuda.device(x.device):
             self.backend.launch(x.data_ptr(), out.data_ptr(), bufs, ctls, rank, self.N, n, self.cap,

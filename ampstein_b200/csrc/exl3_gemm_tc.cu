@@ -8,45 +8,63 @@
 // every 16-row slab) and its reconstruct + cuBLAS path (torch_exl3_gemm_recon,
 // src/torch/amp_torch.cpp:11148-11230, which writes the whole fp16 weight to global memory first).
 //
-// One CTA = 512 tokens x 128 output columns. Per 64-row k step:
-//   * all eight warps copy the x~ tile (512 x 64 fp16, four 128-row sub-tiles) with cp.async
-//     into the canonical K-major 128-byte-swizzled layout, and the step's packed trellis words
-//     (4 tile rows x 8 tiles) into a staging area;
-//   * they decode the 8192 weights (bit-exact codebook values) straight into the swizzled
-//     K-major B tile (128 columns x 64 k): each decoded weight is used for 512 tokens;
-//   * one thread issues 16 tcgen05.mma (M128 x N128 x K16, fp16 in, fp32 accumulate) into four
-//     128-column accumulators in tensor memory and commits them to an mbarrier that frees the
-//     stage. Two stages: the copies and the decode of step i+1 run under the MMAs of step i.
+// One CTA = 512 tokens x 128 output columns, k walked in steps of 64. Three roles, 18 warps:
+//   * warp 0, one thread: fetches the x~ tile of a step (four 128 x 64 boxes) with TMA straight
+//     into the canonical K-major 128-byte-swizzled layout (two stages); a stage is refilled the
+//     moment the MMAs that read it have completed.
+//   * warp 1, one thread: issues the step's 16 tcgen05.mma (M128 x N128 x K16, fp16 in, fp32
+//     accumulate) into four 128-column accumulators in tensor memory as soon as the x~ tile has
+//     landed and the weight tile is decoded, and commits them to the barriers that free the
+//     stages. It does nothing else: with fetch and issue in one thread the tensor pipe idled
+//     two thirds of the time.
+//   * warps 2-17 decode, in two groups of eight that take alternate k steps: warp w of a group
+//     owns tile column w of the 128-column block; a lane streams its 32 weights' packed words
+//     through its own cp.async ring (several k steps deep: the words come from HBM exactly once
+//     and a step lasts about half a microsecond), cuts the windows with compile-time shifts,
+//     forms the exact fp16 codebook values and writes them as 16-byte pieces into the swizzled
+//     K-major B tile (three stages): each decoded weight serves 512 tokens.
+//   * mbarriers tie the roles together: TMA completion (bytes), "B tile decoded" (one arrival per
+//     decode warp of the group), and tcgen05.commit arrivals that free an A stage and a B stage.
 // Epilogue: accumulators -> registers (tcgen05.ld) -> shared memory, then the same warp-level
 // 128-point Hadamard, svh scale and rounding as the decode kernels, coalesced stores.
 //
-// Tensor-pipe bound by design (2 * M * k * n flops); the decode costs about a sixteenth of an
-// instruction per MAC at 512 tokens per decoded weight. Every wait on an mbarrier is bounded;
-// on expiry the status word is set and the CTA still frees its tensor memory.
-#include "exl3_common.cuh"
+// Tensor-pipe bound by design (2 * M * k * n flops). Every wait on an mbarrier is bounded; on
+// expiry the status word is set, every role leaves its loop and the CTA still frees its tensor
+// memory.
+#include "exl3_gemv_kernel.cuh"
 #include "host_common.h"
+#include <cuda.h>
 
 namespace amp {
 
-constexpr int TC_THREADS = 256;
+constexpr int TC_DECODE_WARPS = 16;           // two groups of eight that take alternate k steps
+constexpr int TC_THREADS = 32 * (2 + TC_DECODE_WARPS);     // warp 0 fetches, warp 1 issues the MMAs, the rest decode
 constexpr int TC_BM = 128;            // tokens per sub-tile (UMMA M)
 constexpr int TC_SUB = 4;             // sub-tiles per CTA
 constexpr int TC_BN = 128;            // output columns per CTA (UMMA N)
 constexpr int TC_BK = 64;             // k per step (one 128-byte swizzle row)
-constexpr int TC_A_BYTES = TC_SUB * TC_BM * TC_BK * 2;     // 65536
+constexpr int TC_A_SLOTS = 2, TC_B_STAGES = 3;
+constexpr int TC_A_BYTES = TC_SUB * TC_BM * TC_BK * 2;     // one slot = the x~ tile of one k step: 65536
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;              // 16384
-constexpr int TC_STAGES = 2;
+// packed trellis words travel through per-lane cp.async rings this many k steps deep (the words
+// come from HBM exactly once: the ring must cover the HBM latency, a step is ~0.5 us)
+__host__ __device__ constexpr int tc_p_stages(int K) { return K <= 4 ? 4 : 3; }        // per decode group: every other step
+__host__ __device__ constexpr int tc_smem_bytes(int K)
+{
+    return 1024 + TC_A_SLOTS * TC_A_BYTES + TC_B_STAGES * TC_B_BYTES + TC_DECODE_WARPS * tc_p_stages(K) * 128 * K;
+}
 constexpr unsigned TC_SPIN_LIMIT = 1u << 22;   // try_wait polls before a wait is declared lost
 
-__host__ __device__ constexpr int tc_packed_bytes(int K) { return 4 * 8 * 32 * K; }      // 4 tile rows x 8 tiles
-__host__ __device__ constexpr int tc_stage_bytes(int K) { return TC_A_BYTES + TC_B_BYTES + tc_packed_bytes(K); }
-__host__ __device__ constexpr int tc_smem_bytes(int K) { return 1024 + TC_STAGES * tc_stage_bytes(K); }
-
 __device__ int g_tc_status;
+#ifdef AMP_LAB_TCSTAMP
+__device__ long long g_tc_dbg[64 * 8];
+#define TC_STAMP(i, j) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (i) < 64) g_tc_dbg[(i) * 8 + (j)] = clock64(); } while (0)
+#else
+#define TC_STAMP(i, j) do { } while (0)
+#endif
 
 struct TcParams
 {
-    const __half* xh;           // (M, k) rotated input
     const uint16_t* trellis;    // (k/16, n/16, 16K)
     const __half* svh;          // (n)
     void* c;                    // (M, n) fp16 or fp32
@@ -82,36 +100,87 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar)
                  :: "r"(smem_u32(bar)) : "memory");
 }
 
-__device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, int src_bytes)
+// one 2-D box of the x~ tensor map -> shared memory (no multicast), completion counted on bar
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
 {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(smem_u32(dst)), "l"(src), "r"(src_bytes) : "memory");
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+
+// 4K bytes of one lane, global -> this lane's ring slot, widest cp.async the alignment allows
+template <int K>
+__device__ __forceinline__ void cp_async_chunk(uint32_t dst, const unsigned char* src)
+{
+    if constexpr (K % 4 == 0)
+    {
+        #pragma unroll
+        for (int i = 0; i < K / 4; ++i)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst + 16 * i), "l"(src + 16 * i) : "memory");
+    }
+    else if constexpr (K % 2 == 0)
+    {
+        #pragma unroll
+        for (int i = 0; i < K / 2; ++i)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" :: "r"(dst + 8 * i), "l"(src + 8 * i) : "memory");
+    }
+    else
+    {
+        #pragma unroll
+        for (int i = 0; i < K; ++i)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(dst + 4 * i), "l"(src + 4 * i) : "memory");
+    }
+}
+
+// two states -> two exact fp16 weights packed (a in the low half), bit-identical to the reference
+template <int CB>
+__device__ __forceinline__ uint32_t weights2(uint32_t sa, uint32_t sb)
+{
+    if constexpr (CB == 2)
+    {
+        const uint32_t raw = __byte_perm(cb2_raw(sa), cb2_raw(sb), 0x5410);
+        const __half2 kinv = __half2half2(__ushort_as_half((unsigned short) 0x1eee));
+        const __half2 kbias = __half2half2(__ushort_as_half((unsigned short) 0xc931));
+        const __half2 w = __hfma2(*reinterpret_cast<const __half2*>(&raw), kinv, kbias);
+        return *reinterpret_cast<const uint32_t*>(&w);
+    }
+    else
+    {
+        const uint32_t ya = cb_halves<CB>(sa), yb = cb_halves<CB>(sb);
+        const uint32_t lo = __byte_perm(ya, yb, 0x5410), hi = __byte_perm(ya, yb, 0x7632);
+        const __half2 w = __hadd2(*reinterpret_cast<const __half2*>(&lo), *reinterpret_cast<const __half2*>(&hi));
+        return *reinterpret_cast<const uint32_t*>(&w);
+    }
 }
 
 template <int K, int CB>
 __global__ __launch_bounds__(TC_THREADS, 1)
-void exl3_gemm_tc_kernel(const TcParams P)
+void exl3_gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const TcParams P)
 {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment is required by the swizzled layout
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
-    __shared__ uint64_t bar_free[TC_STAGES];
-    __shared__ uint64_t bar_done;
+    __shared__ uint64_t a_full[TC_A_SLOTS], a_free[TC_A_SLOTS], b_full[TC_B_STAGES], b_free[TC_B_STAGES], bar_done;
     __shared__ uint32_t s_tmem;
-    __shared__ int s_bad;
+    __shared__ volatile int s_bad;
 
-    constexpr int STAGE = tc_stage_bytes(K);
-    constexpr int TW = 8 * K;                          // words per trellis tile
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int nb = blockIdx.x, mb = blockIdx.y;
     const int m0 = mb * (TC_SUB * TC_BM);
     const int rows = min(TC_SUB * TC_BM, P.M - m0);    // valid token rows of this CTA
+    const int nsub = (rows + TC_BM - 1) / TC_BM;        // sub-tiles that hold any of them
     const int ksteps = P.k / TC_BK;
     const size_t tiles_n = (size_t) P.n >> 4;
 
     if (t == 0)
     {
-        mbar_init(&bar_free[0], 1);
-        mbar_init(&bar_free[1], 1);
+        for (int i = 0; i < TC_A_SLOTS; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_free[i], 1); }
+        for (int i = 0; i < TC_B_STAGES; ++i) { mbar_init(&b_full[i], TC_DECODE_WARPS / 2); mbar_init(&b_free[i], 1); }
         mbar_init(&bar_done, 1);
         fence_mbar_init();
         s_bad = 0;
@@ -127,123 +196,159 @@ void exl3_gemm_tc_kernel(const TcParams P)
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
 
-    auto stage_a = [&](int s) { return smem + s * STAGE; };
-    auto stage_b = [&](int s) { return smem + s * STAGE + TC_A_BYTES; };
-    auto stage_p = [&](int s) { return smem + s * STAGE + TC_A_BYTES + TC_B_BYTES; };
-
-    // x~ tile (rows beyond M read as zero) and packed trellis words of k step i into stage s
-    auto issue_loads = [&](int i, int s)
-    {
-        unsigned char* a = stage_a(s);
-        for (int c = t; c < TC_SUB * TC_BM * 8; c += TC_THREADS)
-        {
-            const int r = c >> 3, ch = c & 7;                 // row inside the CTA tile, 16-byte chunk
-            const int sub = r >> 7, rr = r & 127;
-            const int ok = (r < rows) ? 16 : 0;
-            const __half* src = P.xh + (size_t) (m0 + (ok ? r : 0)) * P.k + (size_t) i * TC_BK + ch * 8;
-            cp_async16_zfill(a + sub * (TC_BM * 128) + sw128(rr, ch), src, ok);
-        }
-        unsigned char* p = stage_p(s);
-        constexpr int ROWP = 8 * 32 * K;                        // bytes of one tile row (8 tiles)
-        for (int c = t; c < 4 * ROWP / 16; c += TC_THREADS)
-        {
-            const int row = c / (ROWP / 16), off = (c - row * (ROWP / 16)) * 16;
-            const unsigned char* src = reinterpret_cast<const unsigned char*>(P.trellis)
-                                     + ((size_t) (4 * i + row) * tiles_n + (size_t) nb * 8) * (32 * K) + off;
-            cp_async16_zfill(p + row * ROWP + off, src, 16);
-        }
-        cp_async_commit();
-    };
+    unsigned char* a_base = smem;
+    unsigned char* b_base = smem + TC_A_SLOTS * TC_A_BYTES;
 
     bool ok = true;
     auto wait_bar = [&](uint64_t* bar, uint32_t parity)
     {
         if (!ok) return;
         bool done = false;
-        for (unsigned spin = 0; spin < TC_SPIN_LIMIT && !done; ++spin) done = mbar_try_wait(bar, parity);
+        for (unsigned spin = 0; spin < TC_SPIN_LIMIT && !done; ++spin)
+        {
+            done = mbar_try_wait(bar, parity);
+            if (!done && (spin & 1023) == 1023 && s_bad) break;      // another role gave up: leave too
+        }
         if (!done) { ok = false; s_bad = 1; }
     };
 
-    // instruction descriptor: D fp32, A/B fp16, both K-major, N = 128, M = 128
-    constexpr uint32_t IDESC = (1u << 4) | ((uint32_t) (TC_BN >> 3) << 17) | ((uint32_t) (TC_BM >> 4) << 24);
-
-    issue_loads(0, 0);
-    for (int i = 0; i < ksteps; ++i)
+    if (warp == 0)
     {
-        const int s = i & 1;
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();                                 // stage s holds x~ and the packed words of step i
-
-        // decode 4 x 8 trellis tiles into the B tile: warp w takes tile column w, rows 0..3
+        // ---- fetch: one thread keeps both x~ stages full ----
+        if (lane == 0)
         {
-            const uint32_t* packed = reinterpret_cast<const uint32_t*>(stage_p(s));
-            unsigned char* b = stage_b(s);
-            #pragma unroll
-            for (int kt = 0; kt < 4; ++kt)
+            for (int i = 0; i < ksteps && ok; ++i)
             {
-                const uint32_t* ring = packed + (kt * 8 + warp) * TW;
-                uint32_t st[8];
-                #pragma unroll
-                for (int j = 0; j < 8; ++j) st[j] = window_rt<K>(ring, lane * 8 + j);
-                // positions (0,1) rows (2p, 2p+1), (2,3) rows (2p+8, 2p+9) of column c; (4..7) the same for column c+8
-                const int p2 = (lane & 3) * 2, cc = lane >> 2;
-                #pragma unroll
-                for (int h = 0; h < 4; ++h)
-                {
-                    const __half w0 = decode_state<CB>(st[2 * h]), w1 = decode_state<CB>(st[2 * h + 1]);
-                    const int ncol = warp * 16 + cc + 8 * (h >> 1);
-                    const int kk = kt * 16 + p2 + 8 * (h & 1);
-                    *reinterpret_cast<__half2*>(b + sw128(ncol, kk >> 3) + (kk & 7) * 2) = __halves2half2(w0, w1);
-                }
+                const int s = i % TC_A_SLOTS;
+                // the stage is free once the MMAs of step i - 2 have read it
+                if (i >= TC_A_SLOTS) wait_bar(&a_free[s], (uint32_t) (((i / TC_A_SLOTS) - 1) & 1));
+                if (!ok) break;
+                mbar_expect_tx(&a_full[s], (uint32_t) nsub * TC_BM * TC_BK * 2);
+                for (int sub = 0; sub < nsub; ++sub)
+                    tma_load_2d(smem_u32(a_base + s * TC_A_BYTES + sub * (TC_BM * 128)), &xmap, i * TC_BK, m0 + sub * TC_BM, &a_full[s]);
             }
         }
-        // make the generic-proxy writes (cp.async data, decoded tile) visible to the tensor core
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-
-        if (t == 0)
+        __syncwarp();
+    }
+    else if (warp == 1)
+    {
+        // ---- MMA issue: one thread, nothing else on its plate ----
+        if (lane == 0)
         {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a0 = smem_u32(stage_a(s)), b0 = smem_u32(stage_b(s));
-            #pragma unroll
-            for (int sub = 0; sub < TC_SUB; ++sub)
-                #pragma unroll
-                for (int kk = 0; kk < TC_BK / 16; ++kk)
-                    umma_f16(tmem + sub * TC_BN, make_desc(a0 + sub * (TC_BM * 128) + kk * 32),
-                             make_desc(b0 + kk * 32), IDESC, (i > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(&bar_free[s]);                  // arrives when these MMAs have read the stage
-            if (i == ksteps - 1) umma_commit(&bar_done);
+            // instruction descriptor: D fp32, A/B fp16, both K-major, N = 128, M = 128
+            constexpr uint32_t IDESC = (1u << 4) | ((uint32_t) (TC_BN >> 3) << 17) | ((uint32_t) (TC_BM >> 4) << 24);
+            const uint64_t da0 = make_desc(smem_u32(a_base)), db0 = make_desc(smem_u32(b_base));
+            for (int i = 0; i < ksteps && ok; ++i)
+            {
+                const int sa = i % TC_A_SLOTS, sb = i % TC_B_STAGES;
+                TC_STAMP(i, 0);
+                wait_bar(&a_full[sa], (uint32_t) ((i / TC_A_SLOTS) & 1));
+                TC_STAMP(i, 1);
+                wait_bar(&b_full[sb], (uint32_t) ((i / TC_B_STAGES) & 1));
+                TC_STAMP(i, 2);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // descriptors advance by byte offset >> 4 in their low (address) field
+                const uint64_t da = da0 + (uint64_t) ((sa * TC_A_BYTES) >> 4), db = db0 + (uint64_t) ((sb * TC_B_BYTES) >> 4);
+                for (int sub = 0; sub < nsub; ++sub)
+                    #pragma unroll
+                    for (int kk = 0; kk < TC_BK / 16; ++kk)
+                        umma_f16(tmem + sub * TC_BN, da + (uint64_t) ((sub * (TC_BM * 128) + kk * 32) >> 4),
+                                 db + (uint64_t) ((kk * 32) >> 4), IDESC, (i > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&a_free[sa]);                   // arrive when these MMAs have read their operands
+                umma_commit(&b_free[sb]);
+                if (i == ksteps - 1) umma_commit(&bar_done);
+                TC_STAMP(i, 3);
+            }
         }
-
-        // the other stage is free once the MMAs of step i-1 have completed: refill it for step i+1
-        if (i + 1 < ksteps)
+        __syncwarp();
+    }
+    else
+    {
+        // ---- decode warps ----
+        const int dw = (warp - 2) & 7;                     // tile column of the 128-column block
+        const int grp = (warp - 2) >> 3;                   // this warp's steps: grp, grp + 2, ...
+        const int gq = lane >> 2, pq = lane & 3;           // 32-weight piece of the tile, tile row of the step
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(P.trellis)
+                                 + ((size_t) pq * tiles_n + (size_t) nb * 8 + dw) * (32 * K) + gq * (4 * K);
+        const size_t step_bytes = (size_t) 4 * tiles_n * (32 * K);
+        // this lane's ring: slot s at pring + s * SLOT (a warp's lanes side by side inside a slot); a
+        // lane only ever reads what it copied itself
+        constexpr int PS = tc_p_stages(K);
+        constexpr int SLOT = 32 * 4 * K;
+        const uint32_t pring = smem_u32(smem + TC_A_SLOTS * TC_A_BYTES + TC_B_STAGES * TC_B_BYTES)
+                             + (uint32_t) ((warp - 2) * PS * SLOT + lane * 4 * K);
+        #pragma unroll
+        for (int j = 0; j < PS - 1; ++j)
         {
-            if (i >= 1) wait_bar(&bar_free[s ^ 1], (uint32_t) (((i - 1) >> 1) & 1));
-            issue_loads(i + 1, s ^ 1);
+            if (grp + 2 * j < ksteps) cp_async_chunk<K>(pring + j * SLOT, src + (size_t) (grp + 2 * j) * step_bytes);
+            cp_async_commit();
+        }
+        int pslot = 0;
+        for (int i = grp; i < ksteps && ok; i += 2)
+        {
+            cp_async_wait_n<PS - 2>();                  // this lane's words of step i have landed
+            uint32_t w[K];
+            load_chunk_s<K>(pring + pslot * SLOT, w);
+            {
+                // refill the slot read in this warp's previous step with the words of its step PS - 1 ahead
+                const int nxt = i + 2 * (PS - 1), nslot = (pslot == 0) ? PS - 1 : pslot - 1;
+                if (nxt < ksteps) cp_async_chunk<K>(pring + nslot * SLOT, src + (size_t) nxt * step_bytes);
+                cp_async_commit();
+                if (++pslot == PS) pslot = 0;
+            }
+            // the word in front of this lane's piece: the last word of the lane four below (ring)
+            const uint32_t prev = __shfl_sync(0xffffffffu, w[K - 1], (lane + 28) & 31);
+
+            // 32 weights: columns gq and gq+8 of the tile, k rows 0..15 of tile row pq
+            uint32_t colA[8], colB[8];                     // packed pairs (k, k+1): words 0-3 = k 0..7, 4-7 = k 8..15
+            auto decode_r = [&](auto rtag)
+            {
+                constexpr int R = decltype(rtag)::value;
+                uint32_t s[8];
+                states8<K, R>(w, prev, s);
+                colA[R] = weights2<CB>(s[0], s[1]);     colA[4 + R] = weights2<CB>(s[2], s[3]);
+                colB[R] = weights2<CB>(s[4], s[5]);     colB[4 + R] = weights2<CB>(s[6], s[7]);
+            };
+            decode_r(std::integral_constant<int, 0>()); decode_r(std::integral_constant<int, 1>());
+            decode_r(std::integral_constant<int, 2>()); decode_r(std::integral_constant<int, 3>());
+
+            const int sb = i % TC_B_STAGES;
+            if (i >= TC_B_STAGES) wait_bar(&b_free[sb], (uint32_t) (((i / TC_B_STAGES) - 1) & 1));
+            if (!ok) break;
+            unsigned char* b = b_base + sb * TC_B_BYTES;
+            const int ncol = dw * 16 + gq;
+            *reinterpret_cast<uint4*>(b + sw128(ncol, 2 * pq)) = make_uint4(colA[0], colA[1], colA[2], colA[3]);
+            *reinterpret_cast<uint4*>(b + sw128(ncol, 2 * pq + 1)) = make_uint4(colA[4], colA[5], colA[6], colA[7]);
+            *reinterpret_cast<uint4*>(b + sw128(ncol + 8, 2 * pq)) = make_uint4(colB[0], colB[1], colB[2], colB[3]);
+            *reinterpret_cast<uint4*>(b + sw128(ncol + 8, 2 * pq + 1)) = make_uint4(colB[4], colB[5], colB[6], colB[7]);
+            // make the generic-proxy writes visible to the tensor core, then one arrival per warp
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&b_full[sb]);
         }
     }
 
     // ---- epilogue ----
-    wait_bar(&bar_done, 0);
+    if (warp >= 2) wait_bar(&bar_done, 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
-    const bool all_ok = ok && !s_bad;
+    const bool all_ok = !s_bad;
 
     float* tile = reinterpret_cast<float*>(smem);        // [128][132] fp32, reuses the pipeline stages
     constexpr int TP = 132;
-    for (int sub = 0; sub < TC_SUB; ++sub)
+    const int ew = warp - 2;                             // epilogue warp 0..15 (warps 0 and 1 only keep the barriers company)
+    for (int sub = 0; sub < nsub; ++sub)
     {
-        if (sub * TC_BM >= rows) break;
-        if (all_ok)
+        if (all_ok && warp >= 2)
         {
-            // warp w reads tensor-memory lanes 32*(w%4).. (token rows), columns 64*(w/4)..+63 of this accumulator
-            const int lrow = 32 * (warp & 3) + lane;
-            #pragma unroll
-            for (int half = 0; half < 2; ++half)
+            // a warp may read the tensor-memory lanes 32*(warp%4)..+31 (token rows); the two warps
+            // of a lane group split the 128 columns of this accumulator
+            const int lg = warp & 3, ch = ew >> 2;          // lane group, 32-column quarter of this accumulator
+            const int lrow = 32 * lg + lane;
             {
-                const int col0 = 64 * (warp >> 2) + 32 * half;
-                const uint32_t taddr = tmem + ((uint32_t) (32 * (warp & 3)) << 16) + (uint32_t) (sub * TC_BN + col0);
+                const int col0 = 32 * ch;
+                const uint32_t taddr = tmem + ((uint32_t) (32 * lg) << 16) + (uint32_t) (sub * TC_BN + col0);
                 uint32_t v[32];
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -261,10 +366,10 @@ void exl3_gemm_tc_kernel(const TcParams P)
             }
         }
         __syncthreads();
-        if (all_ok)
+        if (all_ok && warp >= 2)
         {
             const half4 sv = reinterpret_cast<const half4*>(P.svh + (size_t) nb * 128)[lane];
-            for (int r = warp; r < TC_BM; r += TC_THREADS / 32)
+            for (int r = ew; r < TC_BM; r += TC_DECODE_WARPS)
             {
                 const int grow = m0 + sub * TC_BM + r;
                 if (grow >= P.M) break;
@@ -297,12 +402,30 @@ void exl3_gemm_tc_kernel(const TcParams P)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(512u) : "memory");
 }
 
-typedef void (*tc_fn)(const TcParams);
+typedef void (*tc_fn)(const CUtensorMap, const TcParams);
 
 #define AMP_TC_ROW(cb) { exl3_gemm_tc_kernel<1, cb>, exl3_gemm_tc_kernel<2, cb>, exl3_gemm_tc_kernel<3, cb>, exl3_gemm_tc_kernel<4, cb>, \
                          exl3_gemm_tc_kernel<5, cb>, exl3_gemm_tc_kernel<6, cb>, exl3_gemm_tc_kernel<7, cb>, exl3_gemm_tc_kernel<8, cb> }
 static const tc_fn k_tc[3][8] = { AMP_TC_ROW(0), AMP_TC_ROW(1), AMP_TC_ROW(2) };
 #undef AMP_TC_ROW
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda)
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static encode_tiled_fn encode_tiled()
+{
+    static encode_tiled_fn fn = nullptr;
+    if (!fn)
+    {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (encode_tiled_fn) p;
+    }
+    return fn;
+}
 
 // x~ (M, k) fp16 already rotated -> C. Called by amp_exl3_gemm for m > 16.
 int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh, int M, int k, int n,
@@ -316,10 +439,26 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
     int dev = 0;
     if (cudaError_t e = cudaGetDevice(&dev)) return cuda_rc(e, "cudaGetDevice");
     tc_fn fn = k_tc[cb][K - 1];
-    const int smem = tc_smem_bytes(K);
-    if (cudaError_t e = ensure_smem(fn, smem, dev)) return cuda_rc(e, "exl3_gemm smem attribute");
+    const int smem_bytes = tc_smem_bytes(K);
+    if (cudaError_t e = ensure_smem(fn, smem_bytes, dev)) return cuda_rc(e, "exl3_gemm smem attribute");
+
+    // tensor map of x~: inner dimension k, outer M; boxes of 64 x 128 elements, 128-byte swizzle;
+    // rows beyond M read as zero
+    encode_tiled_fn enc = encode_tiled();
+    if (!enc) return fail(AMP_E_UNSUPPORTED, "exl3_gemm: cuTensorMapEncodeTiled is not available in this driver");
+    CUtensorMap xmap;
+    {
+        const cuuint64_t dims[2] = { (cuuint64_t) k, (cuuint64_t) M };
+        const cuuint64_t strides[1] = { (cuuint64_t) k * 2 };
+        const cuuint32_t box[2] = { (cuuint32_t) TC_BK, (cuuint32_t) TC_BM };
+        const cuuint32_t estr[2] = { 1, 1 };
+        const CUresult r = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(xh), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(AMP_E_ARG, "exl3_gemm: tensor map for the rotated input was refused (CUresult %d)", (int) r);
+    }
     TcParams P;
-    P.xh = (const __half*) xh; P.trellis = (const uint16_t*) trellis; P.svh = (const __half*) svh; P.c = c;
+    P.trellis = (const uint16_t*) trellis; P.svh = (const __half*) svh; P.c = c;
     P.M = M; P.k = k; P.n = n; P.c_fp32 = c_fp32;
     {
         static int* status_ptr[64] = {};
@@ -331,7 +470,7 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
     const long mblocks = ((long) M + TC_SUB * TC_BM - 1) / (TC_SUB * TC_BM);
     AMP_REQUIRE(mblocks <= 65535, "exl3_gemm: too many rows");
     dim3 grid(n / 128, (unsigned) mblocks);
-    fn<<<grid, TC_THREADS, smem, stream>>>(P);
+    fn<<<grid, TC_THREADS, smem_bytes, stream>>>(xmap, P);
     return cuda_rc(cudaGetLastError(), "exl3_gemm_tc launch");
 }
 
@@ -349,3 +488,10 @@ AMP_API int amp_exl3_gemm_status(int* out)
     if (out) *out = v;
     return 0;
 }
+
+#ifdef AMP_LAB_TCSTAMP
+AMP_API int amp_lab_tc_dbg(long long* out)
+{
+    return (int) cudaMemcpyFromSymbol(out, g_tc_dbg, sizeof(long long) * 64 * 8);
+}
+#endif

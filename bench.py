@@ -8,7 +8,13 @@ pattern is a valid stream); svh carries random signs scaled so that chained acti
 O(1) in fp16 without extra kernels. A step streams 3.89 GB of packed weights, far more than the
 126 MB L2, so no cache flush is needed between steps.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--mode tp|replicas]
+
+With N > 1 GPUs (one process per GPU under torchrun) the same stack is decoded tensor-parallel, as
+the reference shards it: q|k|v and gate|up column-parallel, o and down row-parallel, each followed
+by the fp16 all-reduce of the hidden state over NVLink (this library's kernel, inside the graph);
+lm_head is split by vocabulary. All ranks decode the same token, so the work is fixed as N grows
+(strong scaling). `--mode replicas` runs N independent copies of the 1-GPU step instead.
 
 One JSON line on stdout (rank 0). `--impl reference` times the CPU restatement of the
 reference's reconstruct-then-matmul path (the reference has no CPU code of its own for this
@@ -96,23 +102,40 @@ class ClockSampler:
 # the GPU arm
 # ------------------------------------------------------------------------------------------
 
-def build_stack(torch, device, seed):
-    """Distinct synthetic tensors for every linear of the stack (3.9 GB)."""
+def tp_shapes(rank, world):
+    """(name, in, out, in of the unsharded matrix) of one layer and the lm_head for a rank of a
+    tensor-parallel group: column-parallel q/k/v/gate/up, row-parallel o/down (reference:
+    src/ucode/ampstein/models.uc:527-562), lm_head by blocks of 128 vocabulary entries."""
+    layer = []
+    for name, k, n in LAYER_LINEARS:
+        if name in ("o", "down"):
+            layer.append((name, k // world, n, k))
+        else:
+            layer.append((name, k, n // world, k))
+    blocks = VOCAB // 128
+    b0, b1 = blocks * rank // world, blocks * (rank + 1) // world
+    return layer, (HIDDEN, (b1 - b0) * 128)
+
+
+def build_stack(torch, device, seed, shapes=None):
+    """Distinct synthetic tensors for every linear of the stack (3.9 GB in all)."""
     from ampstein_b200.models import LinearEXL3
     g = torch.Generator(device=device)
     g.manual_seed(seed)
+    layer_shapes = [(name, k, n, k) for name, k, n in LAYER_LINEARS] if shapes is None else shapes[0]
+    head_shape = (HIDDEN, VOCAB) if shapes is None else shapes[1]
 
-    def make(k, n, K):
+    def make(k, n, K, k_full=None):
         trellis = torch.randint(-32768, 32768, (k // 16, n // 16, 16 * K), dtype=torch.int16,
                                 device=device, generator=g)
         sgn = lambda c: (torch.randint(0, 2, (c,), device=device, generator=g).to(torch.float16) * 2 - 1)
         suh = sgn(k)
         # decoded weights have std 1.2437: keep chained activations at unit scale
-        svh = sgn(n) * (1.0 / (1.2437 * math.sqrt(k)))
+        svh = sgn(n) * (1.0 / (1.2437 * math.sqrt(k_full or k)))
         return LinearEXL3(trellis, suh, svh.to(torch.float16))
 
-    layers = [{name: make(k, n, K_LAYER) for name, k, n in LAYER_LINEARS} for _ in range(LAYERS)]
-    head = make(HIDDEN, VOCAB, K_HEAD)
+    layers = [{name: make(k, n, K_LAYER, kf) for name, k, n, kf in layer_shapes} for _ in range(LAYERS)]
+    head = make(head_shape[0], head_shape[1], K_HEAD)
     return layers, head
 
 
@@ -134,13 +157,25 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=device)
 
     m = 1
-    layers, head = build_stack(torch, device, seed=1234 + rank)
+    tp = world if (world > 1 and args.mode == "tp") else 1
+    if tp > 1 and ((HIDDEN // tp) % 128 or (KV // tp) % 128 or (FFN // tp) % 128):
+        raise SystemExit("bench.py: the stack does not shard %d ways in multiples of 128" % tp)
+    shapes = tp_shapes(rank, tp) if tp > 1 else None
+    layers, head = build_stack(torch, device, seed=1234 + rank, shapes=shapes)
+    vocab_local = head.out_features
     f16 = dict(dtype=torch.float16, device=device)
     h_in = torch.empty((1, m, HIDDEN), **f16)
-    bufs = {"q": torch.empty((1, m, HIDDEN), **f16), "k": torch.empty((1, m, KV), **f16),
-            "v": torch.empty((1, m, KV), **f16), "a": torch.empty((1, m, HIDDEN), **f16),
-            "gu": torch.empty((2, m, FFN), **f16), "h": torch.empty((1, m, HIDDEN), **f16),
-            "logits": torch.empty((m, VOCAB), **f16)}
+    bufs = {"q": torch.empty((1, m, HIDDEN // tp), **f16), "k": torch.empty((1, m, KV // tp), **f16),
+            "v": torch.empty((1, m, KV // tp), **f16), "a": torch.empty((1, m, HIDDEN), **f16),
+            "gu": torch.empty((2, m, FFN // tp), **f16), "h": torch.empty((1, m, HIDDEN), **f16),
+            "logits": torch.empty((m, vocab_local), **f16)}
+    comm = None
+    if tp > 1:
+        # partial sums of the row-parallel o / down, all-reduced over NVLink inside the graph
+        from ampstein_b200.comm import P2PComm
+        bufs["a_part"] = torch.empty((1, m, HIDDEN), **f16)
+        bufs["h_part"] = torch.empty((1, m, HIDDEN), **f16)
+        comm = P2PComm.from_process_group(cap=m * HIDDEN)
     # the reference's decode step runs q|k|v as one sliced bundle and gate|up as one stacked bundle
     # (src/ucode/ampstein/graphdec.uc:163-210): four launches per layer
     qkv = [Sliced([L["q"], L["k"], L["v"]], [bufs["q"], bufs["k"], bufs["v"]]) for L in layers]
@@ -152,16 +187,24 @@ def run_gpu(args):
         n = 0
         for i, L in enumerate(layers):
             qkv[i].run(x)
-            L["o"].forward(bufs["q"][0], bufs["a"][0])    # attention itself is outside the path
-            gu[i].run(bufs["a"])
-            L["down"].forward(bufs["gu"][0], bufs["h"][0])
+            if comm is None:
+                L["o"].forward(bufs["q"][0], bufs["a"][0])    # attention itself is outside the path
+                gu[i].run(bufs["a"])
+                L["down"].forward(bufs["gu"][0], bufs["h"][0])
+                n += 4
+            else:
+                L["o"].forward(bufs["q"][0], bufs["a_part"][0])
+                comm.allreduce(bufs["a_part"], out=bufs["a"])
+                gu[i].run(bufs["a"])
+                L["down"].forward(bufs["gu"][0], bufs["h_part"][0])
+                comm.allreduce(bufs["h_part"], out=bufs["h"])
+                n += 6
             x = bufs["h"]
-            n += 4
         head.forward(x[0], bufs["logits"])
         launches[0] = n + 1
 
     host_x = torch.randn((m, HIDDEN), dtype=torch.float16).pin_memory()
-    host_logits = torch.empty((m, VOCAB), dtype=torch.float16).pin_memory()
+    host_logits = torch.empty((m, vocab_local), dtype=torch.float16).pin_memory()
     h_in.copy_(host_x.view(1, m, HIDDEN))
     graph = DecodeGraph(step, warmup=2)
     stream = graph.stream
@@ -209,12 +252,24 @@ def run_gpu(args):
     if not torch.isfinite(logits).all() or float(logits.abs().max()) == 0.0:
         raise SystemExit("bench.py: step produced non-finite or all-zero logits")
 
+    comm_status = 0
+    if comm is not None:
+        comm_status = comm.status()
+        t = torch.tensor([comm_status], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        comm_status = int(t.item())
+        if comm_status:
+            raise SystemExit("bench.py: an all-reduce gave up waiting for a peer (status %d)" % comm_status)
     if rank != 0:
         return
     ms_step = ms / args.steps
-    tok_s = world * m * 1000.0 / ms_step
-    tok_s_e2e = world * m * 1000.0 / (ms_e2e / args.steps)
-    bytes_step = algorithmic_bytes(m)
+    # tensor parallel: every rank decodes the same token; replicas: one token per rank
+    streams = 1 if tp > 1 else world
+    tok_s = streams * m * 1000.0 / ms_step
+    tok_s_e2e = streams * m * 1000.0 / (ms_e2e / args.steps)
+    gemv_launches = 4 * LAYERS + 1
+    # per GPU: a rank streams 1/tp of the weights (+ the unsharded vectors)
+    bytes_step = algorithmic_bytes(m) if tp == 1 else algorithmic_bytes(m) // tp
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -225,11 +280,12 @@ def run_gpu(args):
     line = {
         "metric": METRIC, "value": round(tok_s, 2), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "higher_is_better": True, "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
         "config": {"workload": "llama3-8b-shaped decode step, batch 1, EXL3 4.0 bpw x%d layers + 6 bpw lm_head, one CUDA graph" % LAYERS,
-                   "l2": "inputs larger than L2 (%.2f GB of weights streamed per step)" % (bytes_step / 1e9),
-                   "replicas": world},
+                   "l2": "inputs larger than L2 (%.2f GB of weights streamed per step and GPU)" % (bytes_step / 1e9),
+                   "parallelism": ("tp%d: column-parallel q|k|v, gate|up; row-parallel o, down + fp16 all-reduce (%d per step) over NVLink; lm_head by vocabulary"
+                                   % (tp, 2 * LAYERS)) if tp > 1 else ("replicas x%d" % world)},
         "e2e": {"value": round(tok_s_e2e, 2), "unit": UNIT,
                 "h2d_bytes_per_step": host_x.numel() * 2, "d2h_bytes_per_step": host_logits.numel() * 2},
         "gpu_launches": launches[0] * args.steps,
@@ -237,11 +293,11 @@ def run_gpu(args):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4),
                      "peak_source": "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback",
-                     "kernel": "exl3_gemv_kernel", "bytes_per_launch": bytes_step // launches[0],
-                     "launches_per_step": launches[0],
+                     "kernel": "exl3_gemv_kernel", "bytes_per_launch": bytes_step // gemv_launches,
+                     "launches_per_step": gemv_launches, "per": "gpu",
                      # DRAM bytes per launch: dram__bytes_read + write of an ncu capture of the four
                      # layer shapes came to 1.004 x the algorithmic bytes (traffic scales with the weights)
-                     "traffic": int(1.004 * bytes_step) // launches[0],
+                     "traffic": int(1.004 * bytes_step) // gemv_launches,
                      "traffic_source": "ncu capture on a 2-layer stack, scaled by weight bytes"},
     }
     if world == 1:
@@ -323,6 +379,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--mode", default="tp", choices=["tp", "replicas"],
+                    help="with --gpus N > 1: tensor-parallel decode of one stack (default) or N independent replicas")
     ap.add_argument("--layers", type=int, default=LAYERS,
                     help="layers of the stack (default: the full 32; fewer only for a small profiler capture)")
     args = ap.parse_args()
