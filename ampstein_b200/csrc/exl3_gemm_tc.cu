@@ -1,7 +1,7 @@
 // Prefill GEMM: C (M, n) = x~ (M, k) @ W_hat (k, n) -> Hadamard -> * svh, with W_hat decoded from
 // the trellis on the fly into shared memory and multiplied on the 5th-generation tensor cores
 // (tcgen05.mma, accumulators in tensor memory). x~ = fp16(H(x * suh) / sqrt(128)) is produced by
-// the Hadamard kernel into the caller's A_had scratch first.
+// the rotation kernel (had_tiled_kernel) into the caller's A_had scratch first.
 //
 // Replaces, for m > 16, the reference's trellis-decode GEMM (exl3_gemm_kernel,
 // vendor/exl3/exllamav3_ext/quant/exl3_gemm_kernel.cuh:8-80, mma.sync, re-decoding the weights for
@@ -9,9 +9,11 @@
 // src/torch/amp_torch.cpp:11148-11230, which writes the whole fp16 weight to global memory first).
 //
 // One CTA = 512 tokens x 128 output columns, k walked in steps of 64. Three roles, 18 warps:
-//   * warp 0, one thread: fetches the x~ tile of a step (four 128 x 64 boxes) with TMA straight
-//     into the canonical K-major 128-byte-swizzled layout (two stages); a stage is refilled the
-//     moment the MMAs that read it have completed.
+//   * warp 0, one thread: fetches the x~ tile of a step with four bulk (TMA) copies of 16 KB. The
+//     rotation kernel has already written x~ k-step-major with the 128-byte swizzle applied, so a
+//     128-token x 64-k box is contiguous in global memory and lands in the canonical K-major
+//     layout as it is (two stages); a stage is refilled the moment the MMAs that read it have
+//     completed.
 //   * warp 1, one thread: issues the step's 16 tcgen05.mma (M128 x N128 x K16, fp16 in, fp32
 //     accumulate) into four 128-column accumulators in tensor memory as soon as the x~ tile has
 //     landed and the weight tile is decoded, and commits them to the barriers that free the
@@ -33,7 +35,6 @@
 // memory.
 #include "exl3_gemv_kernel.cuh"
 #include "host_common.h"
-#include <cuda.h>
 
 namespace amp {
 
@@ -65,10 +66,12 @@ __device__ long long g_tc_dbg[64 * 8];
 
 struct TcParams
 {
+    const unsigned char* xt;    // rotated input, k-step-major and pre-swizzled (had_tiled_kernel): [k/64][M][128 bytes]
     const uint16_t* trellis;    // (k/16, n/16, 16K)
     const __half* svh;          // (n)
     void* c;                    // (M, n) fp16 or fp32
     int M, k, n, c_fp32;
+    int sub;                    // 128-token sub-tiles per CTA: 4, or fewer when the grid would leave SMs idle
     int* status;
 };
 
@@ -98,14 +101,6 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                  :: "r"(smem_u32(bar)) : "memory");
-}
-
-// one 2-D box of the x~ tensor map -> shared memory (no multicast), completion counted on bar
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
@@ -160,7 +155,7 @@ __device__ __forceinline__ uint32_t weights2(uint32_t sa, uint32_t sb)
 
 template <int K, int CB>
 __global__ __launch_bounds__(TC_THREADS, 1)
-void exl3_gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const TcParams P)
+void exl3_gemm_tc_kernel(const TcParams P)
 {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment is required by the swizzled layout
@@ -171,8 +166,8 @@ void exl3_gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const TcParam
 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int nb = blockIdx.x, mb = blockIdx.y;
-    const int m0 = mb * (TC_SUB * TC_BM);
-    const int rows = min(TC_SUB * TC_BM, P.M - m0);    // valid token rows of this CTA
+    const int m0 = mb * (P.sub * TC_BM);
+    const int rows = min(P.sub * TC_BM, P.M - m0);     // valid token rows of this CTA
     const int nsub = (rows + TC_BM - 1) / TC_BM;        // sub-tiles that hold any of them
     const int ksteps = P.k / TC_BK;
     const size_t tiles_n = (size_t) P.n >> 4;
@@ -223,9 +218,14 @@ void exl3_gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const TcParam
                 // the stage is free once the MMAs of step i - 2 have read it
                 if (i >= TC_A_SLOTS) wait_bar(&a_free[s], (uint32_t) (((i / TC_A_SLOTS) - 1) & 1));
                 if (!ok) break;
-                mbar_expect_tx(&a_full[s], (uint32_t) nsub * TC_BM * TC_BK * 2);
+                // a 128-token box of this k step is one contiguous run of 128-byte rows: one bulk copy
+                // each (the rows of a ragged last box that do not exist are not copied; their
+                // accumulator rows are never stored)
+                mbar_expect_tx(&a_full[s], (uint32_t) rows * 128);
+                const unsigned char* src = P.xt + (((size_t) i * P.M + m0) << 7);
                 for (int sub = 0; sub < nsub; ++sub)
-                    tma_load_2d(smem_u32(a_base + s * TC_A_BYTES + sub * (TC_BM * 128)), &xmap, i * TC_BK, m0 + sub * TC_BM, &a_full[s]);
+                    bulk_g2s(a_base + s * TC_A_BYTES + sub * (TC_BM * 128), src + ((size_t) sub * TC_BM << 7),
+                             (uint32_t) min(TC_BM, rows - sub * TC_BM) * 128, &a_full[s]);
             }
         }
         __syncwarp();
@@ -402,32 +402,14 @@ void exl3_gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const TcParam
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(512u) : "memory");
 }
 
-typedef void (*tc_fn)(const CUtensorMap, const TcParams);
+typedef void (*tc_fn)(const TcParams);
 
 #define AMP_TC_ROW(cb) { exl3_gemm_tc_kernel<1, cb>, exl3_gemm_tc_kernel<2, cb>, exl3_gemm_tc_kernel<3, cb>, exl3_gemm_tc_kernel<4, cb>, \
                          exl3_gemm_tc_kernel<5, cb>, exl3_gemm_tc_kernel<6, cb>, exl3_gemm_tc_kernel<7, cb>, exl3_gemm_tc_kernel<8, cb> }
 static const tc_fn k_tc[3][8] = { AMP_TC_ROW(0), AMP_TC_ROW(1), AMP_TC_ROW(2) };
 #undef AMP_TC_ROW
 
-// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda)
-typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static encode_tiled_fn encode_tiled()
-{
-    static encode_tiled_fn fn = nullptr;
-    if (!fn)
-    {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = (encode_tiled_fn) p;
-    }
-    return fn;
-}
-
-// x~ (M, k) fp16 already rotated -> C. Called by amp_exl3_gemm for m > 16.
+// tiled x~ (launch_had_tiled) -> C. Called by amp_exl3_gemm for m > 16.
 int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh, int M, int k, int n,
                    int K, int cb, int c_fp32, cudaStream_t stream)
 {
@@ -442,23 +424,8 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
     const int smem_bytes = tc_smem_bytes(K);
     if (cudaError_t e = ensure_smem(fn, smem_bytes, dev)) return cuda_rc(e, "exl3_gemm smem attribute");
 
-    // tensor map of x~: inner dimension k, outer M; boxes of 64 x 128 elements, 128-byte swizzle;
-    // rows beyond M read as zero
-    encode_tiled_fn enc = encode_tiled();
-    if (!enc) return fail(AMP_E_UNSUPPORTED, "exl3_gemm: cuTensorMapEncodeTiled is not available in this driver");
-    CUtensorMap xmap;
-    {
-        const cuuint64_t dims[2] = { (cuuint64_t) k, (cuuint64_t) M };
-        const cuuint64_t strides[1] = { (cuuint64_t) k * 2 };
-        const cuuint32_t box[2] = { (cuuint32_t) TC_BK, (cuuint32_t) TC_BM };
-        const cuuint32_t estr[2] = { 1, 1 };
-        const CUresult r = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(xh), dims, strides, box, estr,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail(AMP_E_ARG, "exl3_gemm: tensor map for the rotated input was refused (CUresult %d)", (int) r);
-    }
     TcParams P;
-    P.trellis = (const uint16_t*) trellis; P.svh = (const __half*) svh; P.c = c;
+    P.xt = (const unsigned char*) xh; P.trellis = (const uint16_t*) trellis; P.svh = (const __half*) svh; P.c = c;
     P.M = M; P.k = k; P.n = n; P.c_fp32 = c_fp32;
     {
         static int* status_ptr[64] = {};
@@ -467,10 +434,17 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
             if (cudaError_t e = cudaGetSymbolAddress((void**) &sp, g_tc_status)) return cuda_rc(e, "status symbol");
         P.status = sp;
     }
-    const long mblocks = ((long) M + TC_SUB * TC_BM - 1) / (TC_SUB * TC_BM);
+    // 512 tokens per CTA amortise the decode best; with few column blocks that leaves most SMs
+    // idle, so the token tile shrinks until the grid covers the device
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int sub = TC_SUB;
+    while (sub > 1 && (long) (n / 128) * (((long) M + sub * TC_BM - 1) / (sub * TC_BM)) < (long) sms * 4 / 5) sub >>= 1;
+    P.sub = sub;
+    const long mblocks = ((long) M + sub * TC_BM - 1) / (sub * TC_BM);
     AMP_REQUIRE(mblocks <= 65535, "exl3_gemm: too many rows");
     dim3 grid(n / 128, (unsigned) mblocks);
-    fn<<<grid, TC_THREADS, smem_bytes, stream>>>(xmap, P);
+    fn<<<grid, TC_THREADS, smem_bytes, stream>>>(P);
     return cuda_rc(cudaGetLastError(), "exl3_gemm_tc launch");
 }
 

@@ -352,6 +352,7 @@ AMP_API int amp_exl3_set_pdl(int enable)
 namespace amp {
 int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh, int M, int k, int n,
                    int K, int cb, int c_fp32, cudaStream_t stream);
+int launch_had_tiled(const void* in, void* out, const void* pre, long M, int k, int bf16, cudaStream_t stream);
 }
 extern "C" int amp_had_r_128(const void* in, void* out, const void* pre, const void* post,
                              long rows, int cols, int dtype, float scale, cudaStream_t stream);
@@ -369,7 +370,7 @@ static int gemm_any(const void* A, int a_bf16, const void* trellis, void* C, con
         return launch_gemv(direct(A, trellis, C, suh, svh, m, k, n, K, cb, c_fp32, 0, 0), stream);
     AMP_REQUIRE(A_had, "exl3_gemm: A_had scratch (same shape as A, fp16) is required above 16 rows");
     AMP_REQUIRE(A && suh && k > 0 && k % 128 == 0, "exl3_gemm: bad input");
-    if (int rc = amp_had_r_128(A, A_had, suh, nullptr, m, k, a_bf16 ? 2 : 0, 1.0f, stream)) return rc;
+    if (int rc = launch_had_tiled(A, A_had, suh, m, k, a_bf16, stream)) return rc;
     return launch_gemm_tc(A_had, trellis, C, svh, m, k, n, K, cb, c_fp32, stream);
 }
 

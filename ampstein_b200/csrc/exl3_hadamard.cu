@@ -105,6 +105,62 @@ void had_r_128_kernel(const void* __restrict__ in, void* __restrict__ out,
     }
 }
 
+// Rotated prefill activations in the layout the tensor-core GEMM fetches them in: x~ =
+// fp16(H(x * suh) / sqrt(128)) of an (M, k) matrix, stored k-step-major -- [k / 64][M] rows of 64
+// halves (128 bytes) -- with the 16-byte pieces of a row already XOR-swizzled by (row & 7). A
+// 128-token x 64-k box is then 16 KB of contiguous global memory that one bulk copy drops into
+// shared memory in the K-major 128-byte-swizzled form the MMA descriptors expect. Same arithmetic
+// as the plain kernels above (fp16 input: scaled in fp16; bf16 input: scaled in fp32).
+template <bool BF16>
+__global__ __launch_bounds__(256)
+void had_tiled_kernel(const void* __restrict__ in, __half* __restrict__ out, const __half* __restrict__ pre,
+                      long chunks, int chunks_per_row, long M, float r_scale)
+{
+    const int lane = threadIdx.x & 31;
+    const long chunk = (long) blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (chunk >= chunks) return;
+    const long row = chunk / chunks_per_row;
+    const int cb = (int) (chunk - row * chunks_per_row);
+    const half4 s = reinterpret_cast<const half4*>(pre)[cb * 32 + lane];
+    float h0, h1, h2, h3;
+    if constexpr (BF16)
+    {
+        const uint2 raw = reinterpret_cast<const uint2*>(in)[chunk * 32 + lane];
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        h0 = __low2float(a) * __low2float(s.x); h1 = __high2float(a) * __high2float(s.x);
+        h2 = __low2float(b) * __low2float(s.y); h3 = __high2float(b) * __high2float(s.y);
+    }
+    else
+    {
+        half4 v = reinterpret_cast<const half4*>(in)[chunk * 32 + lane];
+        v.x = __hmul2(v.x, s.x);
+        v.y = __hmul2(v.y, s.y);
+        h0 = __low2float(v.x); h1 = __high2float(v.x); h2 = __low2float(v.y); h3 = __high2float(v.y);
+    }
+    warp_had128(h0, h1, h2, h3, lane);
+    half4 o;
+    o.x = __floats2half2_rn(h0 * r_scale, h1 * r_scale);
+    o.y = __floats2half2_rn(h2 * r_scale, h3 * r_scale);
+    // lane l holds k = 128 cb + 4l .. +3: k step 2 cb + l / 16, 16-byte piece (l % 16) / 2, half of the piece l % 2
+    const long kstep = 2 * cb + (lane >> 4);
+    const int piece = ((lane & 15) >> 1) ^ (int) (row & 7);
+    unsigned char* dst = reinterpret_cast<unsigned char*>(out) + ((kstep * M + row) << 7) + (piece << 4) + ((lane & 1) << 3);
+    *reinterpret_cast<half4*>(dst) = o;
+}
+
+// (M, k) fp16 or bf16 -> tiled x~ (M * k halves). Internal to the prefill path.
+int launch_had_tiled(const void* in, void* out, const void* pre, long M, int k, int bf16, cudaStream_t stream)
+{
+    AMP_REQUIRE(in && out && pre && M > 0 && k > 0 && k % 128 == 0, "exl3_gemm: bad arguments to the input rotation");
+    AMP_REQUIRE(((uintptr_t) in & 7) == 0 && ((uintptr_t) out & 15) == 0 && ((uintptr_t) pre & 7) == 0, "exl3_gemm: misaligned pointer");
+    const long chunks = M * (k / 128);
+    const long blocks = (chunks + 7) / 8;
+    AMP_REQUIRE(blocks <= 0x7fffffffL, "exl3_gemm: too many rows");
+    if (bf16) had_tiled_kernel<true><<<(unsigned) blocks, 256, 0, stream>>>(in, (__half*) out, (const __half*) pre, chunks, k / 128, M, kRScale);
+    else had_tiled_kernel<false><<<(unsigned) blocks, 256, 0, stream>>>(in, (__half*) out, (const __half*) pre, chunks, k / 128, M, kRScale);
+    return cuda_rc(cudaGetLastError(), "exl3_gemm input rotation");
+}
+
 }  // namespace amp
 
 using namespace amp;
