@@ -69,7 +69,8 @@ int amp_had_r_128(const void* in, void* out, const void* pre, const void* post,
  * EXL3 linear, any m: C (m, n) fp16 (c_fp32 = 0) or fp32 (c_fp32 = 1) = A (m, k) fp16 through
  * the quantized weight. suh and svh are required. k and n multiples of 128. Up to 16 rows run on
  * the decode kernel; more rows on the tensor-core (tcgen05) prefill kernel, which needs A_had:
- * the reference's scratch argument, fp16, same shape as A (it receives the rotated input).
+ * the reference's scratch argument, m * k halves, 16-byte aligned (it receives the rotated input
+ * in an internal tiled order; its contents mean nothing to the caller).
  * Replaces: exl3_gemm, Q/exl3_gemm.cu:114-349 (binding torch.exl3_gemm,
  * src/torch/amp_torch.cpp:11250-11293), including its GEMV dispatch Q/exl3_gemv.cu:92-184, and,
  * above 144 rows, the reconstruct + cuBLAS path of torch.exl3_gemm_recon
