@@ -119,8 +119,8 @@ class DecodeGraph:
     after warm-up runs, then replays it: one host->device crossing per step, as the reference's
     graphdec does. Everything the step touches must exist before capture."""
 
-    def __init__(self, step_fn, warmup=3):
-        self.stream = torch.cuda.Stream()
+    def __init__(self, step_fn, warmup=3, stream=None):
+        self.stream = stream if stream is not None else torch.cuda.Stream()
         with torch.cuda.stream(self.stream):
             for _ in range(warmup):
                 step_fn()

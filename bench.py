@@ -182,7 +182,8 @@ def run_gpu(args):
     gu = [Multi([L["gate"], L["up"]], bufs["gu"]) for L in layers]
     launches = [0]
 
-    def step():
+    def step(stub=False):
+        # stub: the all-reduces replaced by local copies (to price the exchange)
         x = h_in
         n = 0
         for i, L in enumerate(layers):
@@ -194,14 +195,21 @@ def run_gpu(args):
                 n += 4
             else:
                 L["o"].forward(bufs["q"][0], bufs["a_part"][0])
-                comm.allreduce(bufs["a_part"], out=bufs["a"])
+                if stub:
+                    bufs["a"].copy_(bufs["a_part"])
+                else:
+                    comm.allreduce(bufs["a_part"], out=bufs["a"])
                 gu[i].run(bufs["a"])
                 L["down"].forward(bufs["gu"][0], bufs["h_part"][0])
-                comm.allreduce(bufs["h_part"], out=bufs["h"])
+                if stub:
+                    bufs["h"].copy_(bufs["h_part"])
+                else:
+                    comm.allreduce(bufs["h_part"], out=bufs["h"])
                 n += 6
             x = bufs["h"]
         head.forward(x[0], bufs["logits"])
-        launches[0] = n + 1
+        if not stub:
+            launches[0] = n + 1
 
     host_x = torch.randn((m, HIDDEN), dtype=torch.float16).pin_memory()
     host_logits = torch.empty((m, vocab_local), dtype=torch.float16).pin_memory()
@@ -246,6 +254,12 @@ def run_gpu(args):
     ms = timed(resident_step, args.steps)
     ms_e2e = timed(e2e_step, args.steps)
     t1 = time.time()
+    ms_stub = None
+    if comm is not None:
+        # the same graph with every all-reduce replaced by a local copy: the difference is what
+        # the exchange costs (values diverge between ranks here; only the time is used)
+        stub_graph = DecodeGraph(lambda: step(stub=True), warmup=1, stream=stream)
+        ms_stub = timed(stub_graph.replay, args.steps)
     clocks = sampler.stop(t0, t1) if sampler else None
 
     logits = host_logits.float()
@@ -300,6 +314,11 @@ def run_gpu(args):
                      "traffic": int(1.004 * bytes_step) // gemv_launches,
                      "traffic_source": "ncu capture on a 2-layer stack, scaled by weight bytes"},
     }
+    if ms_stub is not None:
+        line["allreduce"] = {"per_step": 2 * LAYERS, "bytes": m * HIDDEN * 2,
+                             "ms_per_step_without": round(ms_stub / args.steps, 4),
+                             "share_of_step": round(max(0.0, 1.0 - ms_stub / ms), 4),
+                             "us_each": round(max(0.0, ms - ms_stub) / args.steps / (2 * LAYERS) * 1e3, 2)}
     if world == 1:
         line["cpu_baseline"] = cpu_baseline()
     print(json.dumps(line), flush=True)
