@@ -9,6 +9,7 @@ O(1) in fp16 without extra kernels. A step streams 3.89 GB of packed weights, fa
 126 MB L2, so no cache flush is needed between steps.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--mode tp|replicas]
+    python bench.py --workload prefill | --workload moe [--tokens 1|4|16]      (secondary, one GPU)
 
 With N > 1 GPUs (one process per GPU under torchrun) the same stack is decoded tensor-parallel, as
 the reference shards it: q|k|v and gate|up column-parallel, o and down row-parallel, each followed
@@ -325,6 +326,145 @@ def run_gpu(args):
 
 
 # ------------------------------------------------------------------------------------------
+# secondary workloads (one GPU): the prefill GEMM and the fused decode MoE
+# ------------------------------------------------------------------------------------------
+
+def _peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        return {}
+
+
+def run_prefill(args):
+    """One decoder layer's seven linears at M = 2048 tokens, bf16 activations, mixed bit widths
+    (attention K=5, gate/up K=3, down K=4): the tensor-core (tcgen05) trellis-decode GEMM,
+    including the input rotation kernel. One step = the seven GEMMs."""
+    import torch
+    import ampstein_b200 as amp
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the path has no CPU fallback)")
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    M = 2048
+    bits = {"q": 5, "k": 5, "v": 5, "o": 5, "gate": 3, "up": 3, "down": 4}
+    ops = []
+    for name, k, n in LAYER_LINEARS:
+        K = bits[name]
+        t = torch.randint(-32768, 32768, (k // 16, n // 16, 16 * K), dtype=torch.int16, device=dev, generator=g)
+        sgn = lambda c: (torch.randint(0, 2, (c,), device=dev, generator=g).to(torch.float16) * 2 - 1)
+        svh = (sgn(n) * (1.0 / (1.2437 * math.sqrt(k)))).to(torch.float16)
+        x = torch.randn((M, k), device=dev, generator=g).to(torch.bfloat16)
+        ops.append((x, t, torch.empty((M, n), dtype=torch.float16, device=dev), sgn(k), svh))
+    flops = sum(2.0 * M * k * n for _, k, n in LAYER_LINEARS)
+
+    def step():
+        for x, t, y, suh, svh in ops:
+            amp.exl3_gemm(x, t, y, suh, svh)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    t0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop(t0, time.time())
+    ms = e0.elapsed_time(e1) / args.steps
+    if not all(torch.isfinite(o[2].float()).all() for o in ops):
+        raise SystemExit("bench.py: prefill produced non-finite outputs")
+    peaks = _peaks()
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    tf = flops / ms / 1e9
+    print(json.dumps({
+        "metric": "prefill TFLOP/s (one 8B-shaped layer, M=2048, EXL3 K=5/3/4)", "value": round(tf, 1), "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "prefill: 7 linears of one llama3-8b-shaped layer, M=2048 bf16 tokens, K=5 attention / 3 gate,up / 4 down",
+                   "l2": "operands of a step: 0.23 GB (weights read once per GEMM)"},
+        "gpu_launches": 14 * args.steps, "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(tf / peak, 4),
+                     "peak_source": "measured burst (MEASURED_PEAKS.json)" if "bf16_tflops" in peaks else "fallback",
+                     "kernel": "exl3_gemm_tc_kernel", "traffic": None}}), flush=True)
+
+
+def run_moe(args):
+    """Fused decode MoE: 128 experts 2048 -> 768 -> 2048 at K=3, top-8 routing from fp32 router
+    logits ~ N(0,1), T tokens per step (--tokens 1, 4 or 16). Eight different routings are
+    captured in one CUDA graph so that successive layers hit different experts; one step = one
+    MoE layer."""
+    import numpy as np
+    import torch
+    import ampstein_b200 as amp
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the path has no CPU fallback)")
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+    E, Hi, I, Ho, K, topk, T = 128, 2048, 768, 2048, 3, 8, args.tokens
+    tr = lambda k, n: torch.randint(-32768, 32768, (k // 16, n // 16, 16 * K), dtype=torch.int16, device=dev, generator=g)
+    sg = lambda c, s=1.0: ((torch.randint(0, 2, (c,), device=dev, generator=g).to(torch.float16) * 2 - 1) * s).to(torch.float16)
+    ex = [dict(g=(tr(Hi, I), sg(Hi), sg(I, 1 / (1.2437 * math.sqrt(Hi)))), u=(tr(Hi, I), sg(Hi), sg(I, 1 / (1.2437 * math.sqrt(Hi)))),
+               d=(tr(I, Ho), sg(I), sg(Ho, 1 / (1.2437 * math.sqrt(I))))) for _ in range(E)]
+    tab = lambda key, i: amp.ptr_array([e[key][i].data_ptr() for e in ex])
+    slots = T * topk
+    cfg = dict(g_trellis=tab("g", 0), g_suh=tab("g", 1), g_svh=tab("g", 2), u_trellis=tab("u", 0), u_suh=tab("u", 1), u_svh=tab("u", 2),
+               d_trellis=tab("d", 0), d_suh=tab("d", 1), d_svh=tab("d", 2),
+               gu_g=torch.zeros(slots, I, dtype=torch.float16, device=dev), gu_u=torch.zeros(slots, I, dtype=torch.float16, device=dev),
+               d_out=torch.zeros(slots, Ho, dtype=torch.float32, device=dev),
+               ctr=torch.zeros(amp.moe_coop_ctr_len(slots), dtype=torch.int32, device=dev),
+               out=torch.zeros(T, Hi, dtype=torch.float32, device=dev), Hi=Hi, Kg=K, Ku=K, Kd=K, act=0, act_limit=0.0)
+    sets = []
+    for _ in range(8):
+        w, sel = torch.topk(torch.randn(T, E, device=dev, generator=g), topk, dim=1)
+        sets.append((torch.randn(T, Hi, device=dev, generator=g).to(torch.float16), sel.contiguous(),
+                     torch.softmax(w, 1).to(torch.float16).contiguous()))
+    distinct = float(np.mean([len(torch.unique(s[1])) for s in sets]))
+    for x, sel, rw in sets:
+        amp.moe_coop(x, sel, rw, cfg)
+    torch.cuda.synchronize()
+    gr, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(st), torch.cuda.graph(gr, stream=st):
+        for x, sel, rw in sets:
+            amp.moe_coop(x, sel, rw, cfg)
+    for _ in range(max(args.warmup, 3)):
+        gr.replay()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    t0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        gr.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop(t0, time.time())
+    us = e0.elapsed_time(e1) * 1e3 / (args.steps * len(sets))
+    if not torch.isfinite(cfg["out"]).all():
+        raise SystemExit("bench.py: MoE produced non-finite outputs")
+    byt = distinct * 3 * Hi * I * K // 8
+    peaks = _peaks()
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    gbs = byt / us / 1e3
+    print(json.dumps({
+        "metric": "fused decode MoE layer time (128 experts, top-8, K=3)", "value": round(us, 2), "unit": "us/layer",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(us * len(sets) / 1e3, 4),
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "moe decode: 128 experts 2048->768->2048 K=3, top-8, %d token(s), 8 routings per graph" % T,
+                   "distinct_experts_per_layer": round(distinct, 1),
+                   "l2": "expert weights in total 226 MB (larger than L2); each layer touches %.1f MB" % (byt / 1e6)},
+        "gpu_launches": 4 * len(sets) * args.steps, "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
+                     "peak_source": "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback",
+                     "kernel": "exl3_gemv_kernel (grouped modes)", "bytes_per_launch": int(byt) // 2, "traffic": None}}), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
 # CPU legs (the oracle as the timed thing: allowed only here)
 # ------------------------------------------------------------------------------------------
 
@@ -400,6 +540,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--mode", default="tp", choices=["tp", "replicas"],
                     help="with --gpus N > 1: tensor-parallel decode of one stack (default) or N independent replicas")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "moe"],
+                    help="decode (default, the headline step) or a secondary one-GPU workload: the prefill GEMM / the fused decode MoE")
+    ap.add_argument("--tokens", type=int, default=1, choices=[1, 4, 16], help="tokens per step of --workload moe")
     ap.add_argument("--layers", type=int, default=LAYERS,
                     help="layers of the stack (default: the full 32; fewer only for a small profiler capture)")
     args = ap.parse_args()
@@ -409,6 +552,10 @@ def main():
             args.steps = 5                 # each step is seconds of CPU work
         args.warmup = min(args.warmup, 1)
         run_reference(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
+    elif args.workload == "moe":
+        run_moe(args)
     else:
         run_gpu(args)
 
