@@ -180,6 +180,32 @@ class P2PComm:
                                 torch.cuda.current_stream(x.device).cuda_stream)
         return out
 
+    def linear_allreduce(self, lin, x, out, rank=None):
+        """Row-parallel EXL3 linear with the all-reduce fused into its kernel: out (m, n) fp16 =
+        sum over ranks of lin(x). `lin` is a models.LinearEXL3 holding this rank's row shard; x
+        (m, k_local) fp16, m <= 16, m * n <= cap. Equivalent to lin.forward followed by
+        allreduce (same bits), without the extra launch."""
+        from . import _lib
+        rank = self.rank if rank is None else rank
+        if rank is None or not (0 <= rank < self.N):
+            raise ValueError("expected (lin, x, out, rank)")
+        m = x.shape[0]
+        n = lin.out_features
+        ok = (x.is_cuda and x.dtype == torch.float16 and x.is_contiguous() and x.dim() == 2
+              and x.shape[1] == lin.in_features and 1 <= m <= 16 and m * n <= self.cap
+              and out.is_cuda and out.dtype == torch.float16 and out.is_contiguous() and out.numel() == m * n
+              and out.device == x.device and lin.bias is None)
+        if not ok:
+            raise ValueError("comm.linear_allreduce: x (m <= 16, k) and out (m, n) must be contiguous fp16 on the "
+                             "rank's device, m * n <= cap, no bias")
+        bufs, ctls = self._bufs[rank]
+        cb = 2 if lin.mul1 else (1 if lin.mcg else 0)
+        with torch.cuda.device(x.device):
+            _lib.call("amp_exl3_gemv_allreduce", x.data_ptr(), lin.trellis.data_ptr(), out.data_ptr(),
+                      lin.suh.data_ptr(), lin.svh.data_ptr(), m, lin.in_features, n, lin.K, cb,
+                      bufs, ctls, rank, self.N, self.cap, torch.cuda.current_stream(x.device).cuda_stream)
+        return out
+
     def status(self, rank=None):
         """Non-zero when a bounded wait for a peer ran out since the last query."""
         rank = self.rank if rank is None else rank

@@ -60,8 +60,10 @@ __device__ int g_tc_status;
 #ifdef AMP_LAB_TCSTAMP
 __device__ long long g_tc_dbg[64 * 8];
 #define TC_STAMP(i, j) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (i) < 64) g_tc_dbg[(i) * 8 + (j)] = clock64(); } while (0)
+#define TC_STAMP_D(i, j) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (i) < 64 && (warp == 2 || warp == 10) && lane == 0) g_tc_dbg[(i) * 8 + (j)] = clock64(); } while (0)
 #else
 #define TC_STAMP(i, j) do { } while (0)
+#define TC_STAMP_D(i, j) do { } while (0)
 #endif
 
 struct TcParams
@@ -287,6 +289,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
         int pslot = 0;
         for (int i = grp; i < ksteps && ok; i += 2)
         {
+            TC_STAMP_D(i, 4);
             cp_async_wait_n<PS - 2>();                  // this lane's words of step i have landed
             uint32_t w[K];
             load_chunk_s<K>(pring + pslot * SLOT, w);
@@ -314,7 +317,9 @@ void exl3_gemm_tc_kernel(const TcParams P)
             decode_r(std::integral_constant<int, 2>()); decode_r(std::integral_constant<int, 3>());
 
             const int sb = i % TC_B_STAGES;
+            TC_STAMP_D(i, 5);
             if (i >= TC_B_STAGES) wait_bar(&b_free[sb], (uint32_t) (((i / TC_B_STAGES) - 1) & 1));
+            TC_STAMP_D(i, 6);
             if (!ok) break;
             unsigned char* b = b_base + sb * TC_B_BYTES;
             const int ncol = dw * 16 + gq;
@@ -326,6 +331,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&b_full[sb]);
+            TC_STAMP_D(i, 7);
         }
     }
 

@@ -221,6 +221,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     P.m = m; P.k = k; P.c_fp32 = A.c_fp32; P.xgroups = xgroups; P.pdl = g_pdl; P.cluster = cluster;
     P.blocks = (int) col_blocks;
     P.moe = A.moe;
+    P.ar = A.ar;
     if (A.ws_counters) { P.counters = A.ws_counters; P.scratch = A.ws_scratch; }
     else if (int rc = workspace_region(dev, &P.counters, &P.scratch)) return rc;
     {
@@ -283,6 +284,29 @@ AMP_API int amp_exl3_gemv_cfg(const void* x, const void* trellis, void* c, const
                               cudaStream_t stream)
 {
     return launch_gemv(direct(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, split, xgroups), stream);
+}
+
+// ---- row-parallel linear with the tensor-parallel all-reduce fused into its epilogue ----
+// out (m, n) fp16 = sum over the N ranks of this rank's x (m, k_local) through its row shard of
+// the weight. bufs / ctls: the communicator's buffers exactly as amp_comm_allreduce_fp16 takes
+// them (zero-filled once, sized by amp_comm_buffer_bytes(N, cap)); m * n <= cap. All ranks must
+// issue the same sequence of all-reduce and fused calls.
+AMP_API int amp_exl3_gemv_allreduce(const void* x, const void* trellis, void* out, const void* suh, const void* svh,
+                                    int m, int k, int n, int K, int cb, void* const* bufs, int* const* ctls,
+                                    int rank, int N, long cap, cudaStream_t stream)
+{
+    AMP_REQUIRE(N >= 2 && N <= COMM_MAXN && rank >= 0 && rank < N, "exl3_gemv_allreduce: bad rank / world size (2..%d ranks)", COMM_MAXN);
+    AMP_REQUIRE(bufs && ctls, "exl3_gemv_allreduce: null buffer table");
+    AMP_REQUIRE(cap > 0 && cap % 8 == 0 && (long) m * n <= cap, "exl3_gemv_allreduce: m * n exceeds the communicator's capacity");
+    GemvLaunch A = direct(x, trellis, out, suh, svh, m, k, n, K, cb, 0, 0, 0);
+    for (int p = 0; p < N; ++p)
+    {
+        AMP_REQUIRE(bufs[p] && ctls[p], "exl3_gemv_allreduce: null buffer of rank %d", p);
+        A.ar.buf[p] = (uint2*) bufs[p];
+    }
+    A.ar.ctl = ctls[rank];
+    A.ar.rank = rank; A.ar.N = N; A.ar.wcap = cap / 2;
+    return launch_gemv(A, stream);
 }
 
 // ---- allocation-free variant ----------------------------------------------------------------

@@ -18,6 +18,7 @@ struct GemvLaunch
     int* ws_counters;    // caller-provided arrival counters / partial-sum slots instead of the
     float* ws_scratch;   // per-device workspace (both or neither); ws_max_ctas bounds the CTA count
     int ws_max_ctas;
+    GemvAr ar;           // fused tensor-parallel all-reduce of the output (ar.N == 0: none)
 };
 
 int launch_gemv(const GemvLaunch& A, cudaStream_t stream);

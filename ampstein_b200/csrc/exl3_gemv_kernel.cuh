@@ -43,6 +43,7 @@
 // per weight, i.e. ~30 weights per clock per SM).
 #pragma once
 #include "exl3_common.cuh"
+#include "comm_ll.cuh"
 
 namespace amp {
 
@@ -70,6 +71,18 @@ struct GemvMoe
     float* d_out;               // (slots, Ho) fp32 down outputs (after svh and bias)
     int Hi, I, Ho;
     int act; float act_limit; int gated;
+};
+
+// Fused tensor-parallel all-reduce (row-parallel linears): the CTA that finishes a column block
+// pushes the block's fp16 partial straight into every peer's all-reduce buffer and gathers the
+// peers' partials of the same block, so the exchange starts while other blocks still decode and
+// needs no launch of its own. Same buffers, layout and sequence protocol as the stand-alone kernel.
+struct GemvAr
+{
+    uint2* buf[COMM_MAXN];      // every rank's buffer as this process addresses it
+    int* ctl;                   // this rank's control block
+    int rank, N;                // N == 0: no exchange
+    long wcap;                  // LL words per (slot, sender) = cap / 2
 };
 
 struct GemvParams
@@ -100,6 +113,7 @@ struct GemvParams
     int* counters;              // [blocks] arrival counters, zero between launches
     int* status;                // device status word (the kernel has no waits that can run out; kept for the ABI)
     GemvMoe moe;                // grouped-expert modes only
+    GemvAr ar;                  // MODE 0, fp16 output only
 #ifdef AMP_LAB_STAMP
     unsigned long long* stamps; // [gridDim.x][4] globaltimer at entry, x~ ready, decode done, exit
 #endif
@@ -931,7 +945,55 @@ void exl3_gemv_kernel(const GemvParams P)
                     half4 o;
                     o.x = __hmul2(__floats2half2_rn(h0, h1), sv.x);
                     o.y = __hmul2(__floats2half2_rn(h2, h3), sv.y);
+                    if constexpr (MODE == 0)
+                    {
+                        if (P.ar.N)
+                        {
+                            // this lane's four halves are one unit of the all-reduce payload (m, stride):
+                            // push it to every peer, then add up the peers' units in rank order
+                            const uint32_t seq = (uint32_t) (*(volatile int*) &P.ar.ctl[0] + 1);
+                            const long unit = ((long) b * stride + (long) nb * 128 + lane * 4) >> 2;
+                            const long slot_off = (long) (seq & 1) * P.ar.N * P.ar.wcap;
+                            const uint2 mine = *reinterpret_cast<const uint2*>(&o);
+                            for (int p = 0; p < P.ar.N; ++p)
+                                if (p != P.ar.rank)
+                                    st_ll2(P.ar.buf[p] + slot_off + (long) P.ar.rank * P.ar.wcap + 2 * unit, mine.x, mine.y, seq);
+                            uint2* srcs[COMM_MAXN];
+                            #pragma unroll
+                            for (int p = 0; p < COMM_MAXN; ++p)
+                                srcs[p] = (p < P.ar.N) ? P.ar.buf[P.ar.rank] + slot_off + (long) p * P.ar.wcap + 2 * unit : nullptr;
+                            uint32_t d[COMM_MAXN][2];
+                            unsigned budget = COMM_SPIN_LIMIT;
+                            if (!gather_unit(srcs, &mine, P.ar.rank, P.ar.N, seq, d, budget)) atomicExch(P.ar.ctl + COMM_MAXB, 1);
+                            float acc[4] = { 0.f, 0.f, 0.f, 0.f };
+                            #pragma unroll
+                            for (int p = 0; p < COMM_MAXN; ++p)         // rank order, fp32, one rounding
+                                if (p < P.ar.N) acc4(acc, d[p][0], d[p][1]);
+                            o.x = __floats2half2_rn(acc[0], acc[1]);
+                            o.y = __floats2half2_rn(acc[2], acc[3]);
+                        }
+                    }
                     reinterpret_cast<half4*>(reinterpret_cast<__half*>(cbase) + (size_t) b * stride + (size_t) nb * 128)[lane] = o;
+                }
+            }
+            if constexpr (MODE == 0)
+            {
+                if (P.ar.N)
+                {
+                    // one arrival per finished column block; the last one closes the call (the
+                    // sequence number advances once every block of this rank has been gathered)
+                    __syncthreads();
+                    if (t == 0)
+                    {
+                        const int seq = *(volatile int*) &P.ar.ctl[0] + 1;
+                        __threadfence();
+                        if (atomicAdd(&P.ar.ctl[1], 1) == P.blocks - 1)
+                        {
+                            P.ar.ctl[1] = 0;
+                            __threadfence();
+                            *(volatile int*) &P.ar.ctl[0] = seq;
+                        }
+                    }
                 }
             }
         }

@@ -184,7 +184,7 @@ def run_gpu(args):
     launches = [0]
 
     def step(stub=False):
-        # stub: the all-reduces replaced by local copies (to price the exchange)
+        # stub: the row-parallel linears without their all-reduce (to price the exchange)
         x = h_in
         n = 0
         for i, L in enumerate(layers):
@@ -195,18 +195,22 @@ def run_gpu(args):
                 L["down"].forward(bufs["gu"][0], bufs["h"][0])
                 n += 4
             else:
-                L["o"].forward(bufs["q"][0], bufs["a_part"][0])
                 if stub:
-                    bufs["a"].copy_(bufs["a_part"])
-                else:
+                    L["o"].forward(bufs["q"][0], bufs["a"][0])
+                elif args.unfused:
+                    L["o"].forward(bufs["q"][0], bufs["a_part"][0])
                     comm.allreduce(bufs["a_part"], out=bufs["a"])
-                gu[i].run(bufs["a"])
-                L["down"].forward(bufs["gu"][0], bufs["h_part"][0])
-                if stub:
-                    bufs["h"].copy_(bufs["h_part"])
                 else:
+                    comm.linear_allreduce(L["o"], bufs["q"][0], bufs["a"][0])
+                gu[i].run(bufs["a"])
+                if stub:
+                    L["down"].forward(bufs["gu"][0], bufs["h"][0])
+                elif args.unfused:
+                    L["down"].forward(bufs["gu"][0], bufs["h_part"][0])
                     comm.allreduce(bufs["h_part"], out=bufs["h"])
-                n += 6
+                else:
+                    comm.linear_allreduce(L["down"], bufs["gu"][0], bufs["h"][0])
+                n += 6 if args.unfused else 4
             x = bufs["h"]
         head.forward(x[0], bufs["logits"])
         if not stub:
@@ -257,8 +261,8 @@ def run_gpu(args):
     t1 = time.time()
     ms_stub = None
     if comm is not None:
-        # the same graph with every all-reduce replaced by a local copy: the difference is what
-        # the exchange costs (values diverge between ranks here; only the time is used)
+        # the same graph without the exchange: the difference is what the all-reduces cost
+        # (values diverge between ranks here; only the time is used)
         stub_graph = DecodeGraph(lambda: step(stub=True), warmup=1, stream=stream)
         ms_stub = timed(stub_graph.replay, args.steps)
     clocks = sampler.stop(t0, t1) if sampler else None
@@ -299,8 +303,8 @@ def run_gpu(args):
         "data": "synthetic",
         "config": {"workload": "llama3-8b-shaped decode step, batch 1, EXL3 4.0 bpw x%d layers + 6 bpw lm_head, one CUDA graph" % LAYERS,
                    "l2": "inputs larger than L2 (%.2f GB of weights streamed per step and GPU)" % (bytes_step / 1e9),
-                   "parallelism": ("tp%d: column-parallel q|k|v, gate|up; row-parallel o, down + fp16 all-reduce (%d per step) over NVLink; lm_head by vocabulary"
-                                   % (tp, 2 * LAYERS)) if tp > 1 else ("replicas x%d" % world)},
+                   "parallelism": ("tp%d: column-parallel q|k|v, gate|up; row-parallel o, down with the fp16 all-reduce (%d per step) over NVLink %s; lm_head by vocabulary"
+                                   % (tp, 2 * LAYERS, "as separate launches" if args.unfused else "fused into the GEMV epilogue")) if tp > 1 else ("replicas x%d" % world)},
         "e2e": {"value": round(tok_s_e2e, 2), "unit": UNIT,
                 "h2d_bytes_per_step": host_x.numel() * 2, "d2h_bytes_per_step": host_logits.numel() * 2},
         "gpu_launches": launches[0] * args.steps,
@@ -540,6 +544,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--mode", default="tp", choices=["tp", "replicas"],
                     help="with --gpus N > 1: tensor-parallel decode of one stack (default) or N independent replicas")
+    ap.add_argument("--unfused", action="store_true",
+                    help="tensor-parallel mode: separate all-reduce launches instead of the GEMV's fused exchange")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "moe"],
                     help="decode (default, the headline step) or a secondary one-GPU workload: the prefill GEMM / the fused decode MoE")
     ap.add_argument("--tokens", type=int, default=1, choices=[1, 4, 16], help="tokens per step of --workload moe")

@@ -230,6 +230,22 @@ int amp_exl3_gemv_status(int* out);
 int amp_comm_allreduce_fp16(const void* x, void* out, void* const* bufs, int* const* ctls,
                             int rank, int N, long n, long cap, int mode, int blocks,
                             cudaStream_t stream);
+/*
+ * Row-parallel EXL3 linear of tensor-parallel decode with the all-reduce fused into the kernel:
+ * out (m, n) fp16 on every rank = sum over ranks of (this rank's x (m, k) through its row shard of
+ * the weight), m <= 16, m * n <= cap. The CTA that finishes a 128-column block pushes the block's
+ * fp16 partial into every peer's buffer and adds up the peers' partials of that block (fp32, rank
+ * order, one rounding: bit-identical on all ranks, and identical to amp_exl3_gemv followed by
+ * amp_comm_allreduce_fp16), so the exchange overlaps the rest of the decode and costs no launch.
+ * bufs / ctls, rank, N, cap: exactly as for amp_comm_allreduce_fp16, whose buffers, layout and
+ * sequence protocol it shares (calls of both kinds may be mixed; all ranks must issue the same
+ * sequence). Waits on peers are bounded (amp_comm_status).
+ * Replaces the pair exl3_gemm + comm.allreduce after o_proj / down_proj,
+ * src/ucode/ampstein/qwen35_tp.uc:356,368; the reference has no fused form.
+ */
+int amp_exl3_gemv_allreduce(const void* x, const void* trellis, void* out, const void* suh, const void* svh,
+                            int m, int k, int n, int K, int cb, void* const* bufs, int* const* ctls,
+                            int rank, int N, long cap, cudaStream_t stream);
 long amp_comm_buffer_bytes(int N, long cap);
 long amp_comm_ctl_bytes(void);
 int amp_comm_blocks(int N, long n);

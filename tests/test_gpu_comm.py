@@ -113,3 +113,46 @@ def test_wait_for_a_missing_peer_runs_out_and_reports():
     y = (out.float() + 1).sum().item()                   # the context still works
     assert np.isfinite(y)
     comm.close()
+
+
+def test_fused_linear_allreduce_matches_gemv_then_allreduce(oracle):
+    """Row-parallel linear with the exchange fused into the GEMV epilogue: bit-identical to the
+    plain GEMV followed by the stand-alone all-reduce on every rank, equal to the oracle's
+    rank-order sum of the fp16 partials, and mixable with plain all-reduce calls on the same
+    communicator (shared sequence numbers). Covers the cluster and the global form of the
+    partial-sum exchange and batches 1 and 3."""
+    if ngpu() < 2:
+        pytest.skip("needs at least two GPUs")
+    from conftest import make_linear
+    from ampstein_b200.comm import p2p_comm
+    from ampstein_b200.models import LinearEXL3
+    for N in sorted({2, min(ngpu(), 8)}):
+        comm = p2p_comm(list(range(N)), 3 * 1024)
+        for call, (k_local, n, m) in enumerate([(1024, 512, 1), (256, 1024, 3), (1024, 512, 1), (2048, 256, 2)]):
+            shards = [make_linear(k_local, n, 4, seed=8800 + 10 * call + r, m=m) for r in range(N)]
+            lins, xs = [], []
+            for r, (trellis, suh, svh, x) in enumerate(shards):
+                d = "cuda:%d" % r
+                svh = (svh.astype(np.float32) / 40.0).astype(np.float16)
+                shards[r] = (trellis, suh, svh, x)
+                lins.append(LinearEXL3(torch.from_numpy(trellis.view(np.int16)).to(d), torch.from_numpy(suh).to(d),
+                                       torch.from_numpy(svh).to(d)))
+                xs.append(torch.from_numpy(x).to(d))
+            # reference on the GPU: plain GEMV per rank, then the stand-alone all-reduce
+            parts = [lins[r].forward(xs[r]) for r in range(N)]
+            plain = [comm.allreduce(parts[r].view(-1), r) for r in range(N)]
+            fused = [torch.empty((m, n), dtype=torch.float16, device="cuda:%d" % r) for r in range(N)]
+            for r in range(N):
+                comm.linear_allreduce(lins[r], xs[r], fused[r], r)
+            for r in range(N):
+                torch.cuda.synchronize(r)
+            for r in range(N):
+                assert torch.equal(fused[r].view(-1).cpu(), plain[r].cpu()), (N, call, r)
+            # oracle: fp16 partials of every shard, summed in fp32 in rank order, rounded once
+            oparts = [oracle.linear(x, t, s, v, 0, fp32_out=False).reshape(-1) for (t, s, v, x) in shards]
+            want = oracle.allreduce_fp16(oparts).astype(np.float32)
+            got = fused[0].view(-1).float().cpu().numpy()
+            assert np.max(np.abs(got - want)) / np.max(np.abs(want)) < 1e-2      # max relative error
+        for r in range(N):
+            assert comm.status(r) == 0
+        comm.close()
