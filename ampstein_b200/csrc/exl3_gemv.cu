@@ -5,7 +5,6 @@
 #include "host_common.h"
 #include "exl3_gemv_host.h"
 #include <mutex>
-#include <cstdlib>
 
 namespace amp {
 
@@ -84,7 +83,7 @@ static int workspace_region(int dev, int** counters, float** scratch)
 // dependent grid piles up on the SMs that drain first and the chain runs 10 % slower than
 // without dependent launch; with the padding it runs 3 % faster (B200, inside CUDA graphs).
 int g_pdl = 1;
-int g_cluster = 1;        // cluster form of the partial-sum exchange (lab switch: AMP_LAB_NOCLUSTER=1 in the environment)
+int g_cluster = 1;        // cluster form of the partial-sum exchange
 // (with more than 16 units per CTA the grid of 8 x blocks CTAs is too coarse: measured slower)
 constexpr int GEMV_CLUSTER = 8, GEMV_CLUSTER_MAX_M = 4, GEMV_CLUSTER_MAX_UNITS = 16;
 
@@ -175,10 +174,6 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     // partial sums then travel through distributed shared memory and a cluster barrier (about a
     // microsecond) instead of global memory, a fence, an atomic and a read-back (about three).
     int cluster = 0;
-    {
-        static int env_checked = 0;
-        if (!env_checked) { env_checked = 1; if (getenv("AMP_LAB_NOCLUSTER")) g_cluster = 0; }
-    }
     if (!A.mode && !A.ws_counters && A.force_split == 0 && A.force_xgroups == 0 && m <= GEMV_CLUSTER_MAX_M && G % GEMV_CLUSTER == 0 &&
         G / GEMV_CLUSTER >= 2 && G / GEMV_CLUSTER <= GEMV_CLUSTER_MAX_UNITS && col_blocks * GEMV_CLUSTER <= (long) D.sms * ctas_per_sm && g_cluster)
     {
