@@ -159,7 +159,9 @@ def test_config1_single_layer_4096(amp, oracle):
     check_close(run_gemm(amp, trellis, suh, svh, x, 0), ref)
 
 
-@pytest.mark.parametrize("k,n,K", [(4096, 1024, 4), (4096, 14336, 4), (14336, 4096, 4), (4096, 2048, 6), (5120, 6144, 5)])
+@pytest.mark.parametrize("k,n,K", [(4096, 1024, 4), (4096, 14336, 4), (14336, 4096, 4), (4096, 2048, 6), (5120, 6144, 5),
+                                   # shards of the tensor-parallel stack (8 and 4 ways): short k, narrow n
+                                   (512, 4096, 4), (1792, 4096, 4), (4096, 768, 4), (3584, 4096, 4), (1024, 4096, 4)])
 def test_llama_shapes(amp, oracle, k, n, K):
     trellis, suh, svh, x = make_linear(k, n, K, seed=k + n + K, m=1)
     ref = oracle.linear(x, trellis, suh, svh, 0, fp32_out=True)
