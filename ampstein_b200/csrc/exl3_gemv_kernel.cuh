@@ -363,8 +363,11 @@ __device__ __forceinline__ float moe_act_gate(int act, bool gated, float g, floa
     return x * u;
 }
 
+#ifndef AMP_GEMV_TB
+#define AMP_GEMV_TB 6               // x~ tasks whose loads are in flight together (per warp and pass)
+#endif
 #ifndef AMP_GEMV_MINBLOCKS
-#define AMP_GEMV_MINBLOCKS 4
+#define AMP_GEMV_MINBLOCKS 3
 #endif
 
 __device__ __forceinline__ void cp_async16_s(uint32_t dst, const void* src)
@@ -395,7 +398,7 @@ struct GemvSplit
 // run x projection, input rows gathered by token).  MODE 2: grouped expert down (input = the
 // activation of the run's gate/up rows, computed on the fly).
 template <int K, int CB, int MB, int MODE = 0>
-__global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 4))
+__global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 3))
 void exl3_gemv_kernel(const GemvParams P)
 {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -640,14 +643,14 @@ void exl3_gemv_kernel(const GemvParams P)
             };
             if constexpr (MODE == 0)
             {
-                // up to four tasks per pass: all their loads are in flight before the first
+                // up to six tasks per pass: all their loads are in flight before the first
                 // transform (at grid start a load takes a microsecond), and the weight stream is
                 // started right behind the first pass's loads
                 int b = 0, jb = warp;
                 while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
                 do
                 {
-                    constexpr int TB = 4;
+                    constexpr int TB = AMP_GEMV_TB;
                     half4 vx[TB], vs[TB];
                     int tb[TB], tj[TB];
                     #pragma unroll
