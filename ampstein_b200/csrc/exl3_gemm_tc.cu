@@ -408,12 +408,324 @@ void exl3_gemm_tc_kernel(const TcParams P)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(512u) : "memory");
 }
 
+// ------------------------------------------------------------------------------------------
+// Pair form: two CTAs of a cluster (two SMs) work on 512 tokens x 256 columns with
+// tcgen05.mma.cta_group::2 (M = 256: 128 token rows per CTA; N = 256: each CTA decodes 128 of the
+// columns into its own shared memory and the tensor cores of both SMs read both halves). Per flop
+// a CTA then fetches half the x~ bytes and its MMAs read half the operand bytes from shared
+// memory, which is what bounds the single-CTA kernel above.
+//
+// Roles per CTA as above; differences:
+//   * only the first CTA of the pair issues MMAs; its commits arrive on the stage barriers of
+//     BOTH CTAs (one tcgen05.commit per barrier, the peer's through its cluster address);
+//   * the peer's warp 1 relays "my x~ stage has landed" to the first CTA's a_peer barrier, and the
+//     decode warps of both CTAs arrive on the first CTA's b_full barrier (16 arrivals);
+//   * tensor memory is allocated and freed by warp 0 of both CTAs with the cta_group::2 forms.
+// ------------------------------------------------------------------------------------------
+constexpr int T2_SUB = 2;                                  // 128-token sub-tiles per CTA
+constexpr int T2_A_SLOTS = 3, T2_B_STAGES = 4;
+constexpr int T2_A_BYTES = T2_SUB * TC_BM * TC_BK * 2;     // 32768
+constexpr int T2_B_BYTES = 128 * TC_BK * 2;                // this CTA's half of the 256-column B tile: 16384
+__host__ __device__ constexpr int tc2_smem_bytes(int K)
+{
+    return 1024 + T2_A_SLOTS * T2_A_BYTES + T2_B_STAGES * T2_B_BYTES + TC_DECODE_WARPS * tc_p_stages(K) * 128 * K;
+}
+
+__device__ __forceinline__ uint32_t cluster_addr(const void* p, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+    return r;
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_bar) : "memory");
+}
+
+__device__ __forceinline__ void umma2_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        :: "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+
+__device__ __forceinline__ void umma2_commit(uint32_t cluster_bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(cluster_bar) : "memory");
+}
+
+__device__ __forceinline__ void cluster_barrier()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int K, int CB>
+__global__ __launch_bounds__(TC_THREADS, 1)
+void exl3_gemm_tc2_kernel(const TcParams P)
+{
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
+    __shared__ uint64_t a_land[T2_A_SLOTS], a_peer[T2_A_SLOTS], a_free[T2_A_SLOTS], b_full[T2_B_STAGES], b_free[T2_B_STAGES], bar_done;
+    __shared__ uint32_t s_tmem;
+    __shared__ volatile int s_bad;
+
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    uint32_t crank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
+    const bool leader = crank == 0;
+    const int nb = blockIdx.x >> 1, mb = blockIdx.y;       // 256-column block, 512-token block of the pair
+    const int m0 = mb * (2 * T2_SUB * TC_BM) + (int) crank * (T2_SUB * TC_BM);
+    const int rows = max(0, min(T2_SUB * TC_BM, P.M - m0));         // valid token rows of this CTA (the peer may have none)
+    const int nsub = (rows + TC_BM - 1) / TC_BM;
+    const int rows_lead = min(T2_SUB * TC_BM, P.M - mb * (2 * T2_SUB * TC_BM));
+    const int nsub_mma = (rows_lead + TC_BM - 1) / TC_BM;           // sub-tiles the pair multiplies (the first CTA's count)
+    const int ksteps = P.k / TC_BK;
+    const size_t tiles_n = (size_t) P.n >> 4;
+
+    if (t == 0)
+    {
+        for (int i = 0; i < T2_A_SLOTS; ++i) { mbar_init(&a_land[i], 1); mbar_init(&a_peer[i], 1); mbar_init(&a_free[i], 1); }
+        for (int i = 0; i < T2_B_STAGES; ++i) { mbar_init(&b_full[i], TC_DECODE_WARPS); mbar_init(&b_free[i], 1); }
+        mbar_init(&bar_done, 1);
+        fence_mbar_init();
+        s_bad = 0;
+    }
+    __syncwarp();
+    if (warp == 0)
+    {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&s_tmem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_barrier();                                     // both CTAs' barriers exist before anyone arrives remotely
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    unsigned char* a_base = smem;
+    unsigned char* b_base = smem + T2_A_SLOTS * T2_A_BYTES;
+
+    bool ok = true;
+    auto wait_bar = [&](uint64_t* bar, uint32_t parity)
+    {
+        if (!ok) return;
+        bool done = false;
+        for (unsigned spin = 0; spin < TC_SPIN_LIMIT && !done; ++spin)
+        {
+            done = mbar_try_wait(bar, parity);
+            if (!done && (spin & 1023) == 1023 && s_bad) break;
+        }
+        if (!done) { ok = false; s_bad = 1; }
+    };
+
+    if (warp == 0)
+    {
+        // ---- fetch ----
+        if (lane == 0)
+        {
+            for (int i = 0; i < ksteps && ok; ++i)
+            {
+                const int s = i % T2_A_SLOTS;
+                if (i >= T2_A_SLOTS) wait_bar(&a_free[s], (uint32_t) (((i / T2_A_SLOTS) - 1) & 1));
+                if (!ok) break;
+                mbar_expect_tx(&a_land[s], (uint32_t) rows * 128);
+                const unsigned char* src = P.xt + (((size_t) i * P.M + m0) << 7);
+                for (int sub = 0; sub < nsub; ++sub)
+                    bulk_g2s(a_base + s * T2_A_BYTES + sub * (TC_BM * 128), src + ((size_t) sub * TC_BM << 7),
+                             (uint32_t) min(TC_BM, rows - sub * TC_BM) * 128, &a_land[s]);
+            }
+        }
+        __syncwarp();
+    }
+    else if (warp == 1)
+    {
+        if (lane == 0)
+        {
+            if (leader)
+            {
+                // ---- MMA issue for the pair ----
+                // instruction descriptor: D fp32, A/B fp16, both K-major, N = 256, M = 256 (pair)
+                constexpr uint32_t IDESC = (1u << 4) | ((uint32_t) (256 >> 3) << 17) | ((uint32_t) (256 >> 4) << 24);
+                const uint64_t da0 = make_desc(smem_u32(a_base)), db0 = make_desc(smem_u32(b_base));
+                for (int i = 0; i < ksteps && ok; ++i)
+                {
+                    const int sa = i % T2_A_SLOTS, sb = i % T2_B_STAGES;
+                    wait_bar(&a_land[sa], (uint32_t) ((i / T2_A_SLOTS) & 1));
+                    wait_bar(&a_peer[sa], (uint32_t) ((i / T2_A_SLOTS) & 1));
+                    wait_bar(&b_full[sb], (uint32_t) ((i / T2_B_STAGES) & 1));
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = da0 + (uint64_t) ((sa * T2_A_BYTES) >> 4), db = db0 + (uint64_t) ((sb * T2_B_BYTES) >> 4);
+                    for (int sub = 0; sub < nsub_mma; ++sub)
+                        #pragma unroll
+                        for (int kk = 0; kk < TC_BK / 16; ++kk)
+                            umma2_f16(tmem + sub * 256, da + (uint64_t) ((sub * (TC_BM * 128) + kk * 32) >> 4),
+                                      db + (uint64_t) ((kk * 32) >> 4), IDESC, (i > 0 || kk > 0) ? 1u : 0u);
+                    // the stages are free in BOTH CTAs once these MMAs have read them
+                    umma2_commit(cluster_addr(&a_free[sa], 0)); umma2_commit(cluster_addr(&a_free[sa], 1));
+                    umma2_commit(cluster_addr(&b_free[sb], 0)); umma2_commit(cluster_addr(&b_free[sb], 1));
+                    if (i == ksteps - 1) { umma2_commit(cluster_addr(&bar_done, 0)); umma2_commit(cluster_addr(&bar_done, 1)); }
+                }
+            }
+            else
+            {
+                // ---- relay: tell the first CTA that this CTA's x~ stage has landed ----
+                for (int i = 0; i < ksteps && ok; ++i)
+                {
+                    const int sa = i % T2_A_SLOTS;
+                    wait_bar(&a_land[sa], (uint32_t) ((i / T2_A_SLOTS) & 1));
+                    if (!ok) break;
+                    mbar_arrive_cluster(cluster_addr(&a_peer[sa], 0));
+                }
+            }
+        }
+        __syncwarp();
+    }
+    else
+    {
+        // ---- decode warps: this CTA's 128 columns of the pair's 256 ----
+        const int dw = (warp - 2) & 7;
+        const int grp = (warp - 2) >> 3;
+        const int gq = lane >> 2, pq = lane & 3;
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(P.trellis)
+                                 + ((size_t) pq * tiles_n + (size_t) nb * 16 + crank * 8 + dw) * (32 * K) + gq * (4 * K);
+        const size_t step_bytes = (size_t) 4 * tiles_n * (32 * K);
+        constexpr int PS = tc_p_stages(K);
+        constexpr int SLOT = 32 * 4 * K;
+        const uint32_t pring = smem_u32(smem + T2_A_SLOTS * T2_A_BYTES + T2_B_STAGES * T2_B_BYTES)
+                             + (uint32_t) ((warp - 2) * PS * SLOT + lane * 4 * K);
+        #pragma unroll
+        for (int j = 0; j < PS - 1; ++j)
+        {
+            if (grp + 2 * j < ksteps) cp_async_chunk<K>(pring + j * SLOT, src + (size_t) (grp + 2 * j) * step_bytes);
+            cp_async_commit();
+        }
+        int pslot = 0;
+        for (int i = grp; i < ksteps && ok; i += 2)
+        {
+            cp_async_wait_n<PS - 2>();
+            uint32_t w[K];
+            load_chunk_s<K>(pring + pslot * SLOT, w);
+            {
+                const int nxt = i + 2 * (PS - 1), nslot = (pslot == 0) ? PS - 1 : pslot - 1;
+                if (nxt < ksteps) cp_async_chunk<K>(pring + nslot * SLOT, src + (size_t) nxt * step_bytes);
+                cp_async_commit();
+                if (++pslot == PS) pslot = 0;
+            }
+            const uint32_t prev = __shfl_sync(0xffffffffu, w[K - 1], (lane + 28) & 31);
+            uint32_t colA[8], colB[8];
+            auto decode_r = [&](auto rtag)
+            {
+                constexpr int R = decltype(rtag)::value;
+                uint32_t s[8];
+                states8<K, R>(w, prev, s);
+                colA[R] = weights2<CB>(s[0], s[1]);     colA[4 + R] = weights2<CB>(s[2], s[3]);
+                colB[R] = weights2<CB>(s[4], s[5]);     colB[4 + R] = weights2<CB>(s[6], s[7]);
+            };
+            decode_r(std::integral_constant<int, 0>()); decode_r(std::integral_constant<int, 1>());
+            decode_r(std::integral_constant<int, 2>()); decode_r(std::integral_constant<int, 3>());
+
+            const int sb = i % T2_B_STAGES;
+            if (i >= T2_B_STAGES) wait_bar(&b_free[sb], (uint32_t) (((i / T2_B_STAGES) - 1) & 1));
+            if (!ok) break;
+            unsigned char* b = b_base + sb * T2_B_BYTES;
+            const int ncol = dw * 16 + gq;
+            *reinterpret_cast<uint4*>(b + sw128(ncol, 2 * pq)) = make_uint4(colA[0], colA[1], colA[2], colA[3]);
+            *reinterpret_cast<uint4*>(b + sw128(ncol, 2 * pq + 1)) = make_uint4(colA[4], colA[5], colA[6], colA[7]);
+            *reinterpret_cast<uint4*>(b + sw128(ncol + 8, 2 * pq)) = make_uint4(colB[0], colB[1], colB[2], colB[3]);
+            *reinterpret_cast<uint4*>(b + sw128(ncol + 8, 2 * pq + 1)) = make_uint4(colB[4], colB[5], colB[6], colB[7]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(cluster_addr(&b_full[sb], 0));     // the first CTA counts both CTAs' warps
+        }
+    }
+
+    // ---- epilogue: each CTA stores its own 256 tokens x 256 columns ----
+    if (warp >= 2) wait_bar(&bar_done, 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    __syncthreads();
+    const bool all_ok = !s_bad;
+
+    float* tile = reinterpret_cast<float*>(smem);        // [128][132] fp32, reuses the pipeline stages
+    constexpr int TP = 132;
+    const int ew = warp - 2;
+    for (int sub = 0; sub < nsub; ++sub)
+    for (int hb = 0; hb < 2; ++hb)                       // the two 128-column Hadamard blocks of the pair's 256 columns
+    {
+        if (all_ok && warp >= 2)
+        {
+            const int lg = warp & 3, ch = ew >> 2;
+            const int lrow = 32 * lg + lane;
+            const int col0 = 32 * ch;
+            const uint32_t taddr = tmem + ((uint32_t) (32 * lg) << 16) + (uint32_t) (sub * 256 + hb * 128 + col0);
+            uint32_t v[32];
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                  "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                  "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                  "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                : "r"(taddr) : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            #pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<uint4*>(tile + lrow * TP + col0 + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        }
+        __syncthreads();
+        if (all_ok && warp >= 2)
+        {
+            const size_t cblk = (size_t) nb * 256 + (size_t) hb * 128;
+            const half4 sv = reinterpret_cast<const half4*>(P.svh + cblk)[lane];
+            for (int r = ew; r < TC_BM; r += TC_DECODE_WARPS)
+            {
+                const int grow = m0 + sub * TC_BM + r;
+                if (grow >= P.M) break;
+                const float4 v = *reinterpret_cast<const float4*>(tile + r * TP + lane * 4);
+                float h0 = v.x, h1 = v.y, h2 = v.z, h3 = v.w;
+                warp_had128(h0, h1, h2, h3, lane);
+                h0 *= kRScale; h1 *= kRScale; h2 *= kRScale; h3 *= kRScale;
+                if (P.c_fp32)
+                {
+                    float4 o = make_float4(h0 * __low2float(sv.x), h1 * __high2float(sv.x),
+                                           h2 * __low2float(sv.y), h3 * __high2float(sv.y));
+                    reinterpret_cast<float4*>(reinterpret_cast<float*>(P.c) + (size_t) grow * P.n + cblk)[lane] = o;
+                }
+                else
+                {
+                    half4 o;
+                    o.x = __hmul2(__floats2half2_rn(h0, h1), sv.x);
+                    o.y = __hmul2(__floats2half2_rn(h2, h3), sv.y);
+                    reinterpret_cast<half4*>(reinterpret_cast<__half*>(P.c) + (size_t) grow * P.n + cblk)[lane] = o;
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    if (t == 0 && !all_ok) atomicExch(P.status, 1);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_barrier();                                     // neither CTA leaves while the other may still use its memory
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(512u) : "memory");
+}
+
 typedef void (*tc_fn)(const TcParams);
 
 #define AMP_TC_ROW(cb) { exl3_gemm_tc_kernel<1, cb>, exl3_gemm_tc_kernel<2, cb>, exl3_gemm_tc_kernel<3, cb>, exl3_gemm_tc_kernel<4, cb>, \
                          exl3_gemm_tc_kernel<5, cb>, exl3_gemm_tc_kernel<6, cb>, exl3_gemm_tc_kernel<7, cb>, exl3_gemm_tc_kernel<8, cb> }
 static const tc_fn k_tc[3][8] = { AMP_TC_ROW(0), AMP_TC_ROW(1), AMP_TC_ROW(2) };
 #undef AMP_TC_ROW
+#define AMP_TC2_ROW(cb) { exl3_gemm_tc2_kernel<1, cb>, exl3_gemm_tc2_kernel<2, cb>, exl3_gemm_tc2_kernel<3, cb>, exl3_gemm_tc2_kernel<4, cb>, \
+                          exl3_gemm_tc2_kernel<5, cb>, exl3_gemm_tc2_kernel<6, cb>, exl3_gemm_tc2_kernel<7, cb>, exl3_gemm_tc2_kernel<8, cb> }
+static const tc_fn k_tc2[3][8] = { AMP_TC2_ROW(0), AMP_TC2_ROW(1), AMP_TC2_ROW(2) };
+#undef AMP_TC2_ROW
+int g_tc_pair = 1;        // pair (cta_group::2) form: 0 never, 1 where it fills the device, 2 whenever n % 256 == 0
 
 // tiled x~ (launch_had_tiled) -> C. Called by amp_exl3_gemm for m > 16.
 int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh, int M, int k, int n,
@@ -440,10 +752,33 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
             if (cudaError_t e = cudaGetSymbolAddress((void**) &sp, g_tc_status)) return cuda_rc(e, "status symbol");
         P.status = sp;
     }
-    // 512 tokens per CTA amortise the decode best; with few column blocks that leaves most SMs
-    // idle, so the token tile shrinks until the grid covers the device
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // pair form (two CTAs per 512 tokens x 256 columns) when the shape fills the device with it
+    if (g_tc_pair && n % 256 == 0 && (M > 256 || g_tc_pair == 2))
+    {
+        const long pairs = (long) (n / 256) * (((long) M + 511) / 512);
+        if ((2 * pairs >= (long) sms * 4 / 5 || g_tc_pair == 2) && ((long) M + 511) / 512 <= 65535)
+        {
+            tc_fn fn2 = k_tc2[cb][K - 1];
+            const int smem2 = tc2_smem_bytes(K);
+            if (cudaError_t e = ensure_smem(fn2, smem2, dev)) return cuda_rc(e, "exl3_gemm smem attribute");
+            P.sub = T2_SUB;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned) (2 * (n / 256)), (unsigned) (((long) M + 511) / 512), 1);
+            cfg.blockDim = dim3(TC_THREADS, 1, 1);
+            cfg.dynamicSmemBytes = smem2;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            return cuda_rc(cudaLaunchKernelEx(&cfg, fn2, P), "exl3_gemm_tc2 launch");
+        }
+    }
+    // single-CTA form: 512 tokens per CTA amortise the decode best; with few column blocks that
+    // leaves most SMs idle, so the token tile shrinks until the grid covers the device
     int sub = TC_SUB;
     while (sub > 1 && (long) (n / 128) * (((long) M + sub * TC_BM - 1) / (sub * TC_BM)) < (long) sms * 4 / 5) sub >>= 1;
     P.sub = sub;
@@ -475,3 +810,13 @@ AMP_API int amp_lab_tc_dbg(long long* out)
     return (int) cudaMemcpyFromSymbol(out, g_tc_dbg, sizeof(long long) * 64 * 8);
 }
 #endif
+
+// Chooses between the single-CTA and the pair (cta_group::2) form of the prefill GEMM: 0 = never
+// the pair form, 1 = where it fills the device (default), 2 = whenever n is a multiple of 256
+// (tests). Returns the previous setting.
+AMP_API int amp_exl3_set_gemm_pair(int mode)
+{
+    const int old = g_tc_pair;
+    g_tc_pair = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
+    return old;
+}

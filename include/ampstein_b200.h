@@ -88,6 +88,13 @@ int amp_exl3_gemm_bf16(const void* A, const void* trellis, void* C, const void* 
                        const void* svh, int m, int k, int n, int K, int cb, int c_fp32,
                        cudaStream_t stream);
 
+/*
+ * Form of the prefill GEMM: 0 = one CTA per tile only, 1 = CTA pairs (tcgen05 cta_group::2, 512
+ * tokens x 256 columns per pair) where that fills the device (default), 2 = pairs whenever n is
+ * a multiple of 256 (for tests). Returns the previous setting. No counterpart in the reference.
+ */
+int amp_exl3_set_gemm_pair(int mode);
+
 /* Reads and clears the prefill GEMM's status word (non-zero: a bounded wait on a tensor-core
  * completion barrier ran out). Synchronises; diagnostics only. */
 int amp_exl3_gemm_status(int* out);
