@@ -8,6 +8,10 @@
 // every 16-row slab) and its reconstruct + cuBLAS path (torch_exl3_gemm_recon,
 // src/torch/amp_torch.cpp:11148-11230, which writes the whole fp16 weight to global memory first).
 //
+// Two kernels. The pair form (exl3_gemm_tc2_kernel, second half of this file: two SMs per 512 x 256
+// tile with cta_group::2) runs wherever n is a multiple of 256 and the grid fills the device; the
+// single-CTA form below covers narrow weights and short batches.
+//
 // One CTA = 512 tokens x 128 output columns, k walked in steps of 64. Three roles, 18 warps:
 //   * warp 0, one thread: fetches the x~ tile of a step with four bulk (TMA) copies of 16 KB. The
 //     rotation kernel has already written x~ k-step-major with the 128-byte swizzle applied, so a
@@ -208,6 +212,14 @@ void exl3_gemm_tc_kernel(const TcParams P)
         }
         if (!done) { ok = false; s_bad = 1; }
     };
+    // a whole warp waits: one lane polls (32 lanes polling one mbarrier word serialise in the
+    // shared-memory pipe and delay every other thread's barrier operations), the rest take its word
+    auto wait_bar_warp = [&](uint64_t* bar, uint32_t parity)
+    {
+        if (lane == 0) wait_bar(bar, parity);
+        __syncwarp();
+        ok = __shfl_sync(0xffffffffu, (int) ok, 0) != 0;
+    };
 
     if (warp == 0)
     {
@@ -318,7 +330,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
 
             const int sb = i % TC_B_STAGES;
             TC_STAMP_D(i, 5);
-            if (i >= TC_B_STAGES) wait_bar(&b_free[sb], (uint32_t) (((i / TC_B_STAGES) - 1) & 1));
+            if (i >= TC_B_STAGES) wait_bar_warp(&b_free[sb], (uint32_t) (((i / TC_B_STAGES) - 1) & 1));
             TC_STAMP_D(i, 6);
             if (!ok) break;
             unsigned char* b = b_base + sb * TC_B_BYTES;
@@ -336,7 +348,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
     }
 
     // ---- epilogue ----
-    if (warp >= 2) wait_bar(&bar_done, 0);
+    if (warp >= 2 && lane == 0) wait_bar(&bar_done, 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
     const bool all_ok = !s_bad;
@@ -410,26 +422,38 @@ void exl3_gemm_tc_kernel(const TcParams P)
 
 // ------------------------------------------------------------------------------------------
 // Pair form: two CTAs of a cluster (two SMs) work on 512 tokens x 256 columns with
-// tcgen05.mma.cta_group::2 (M = 256: 128 token rows per CTA; N = 256: each CTA decodes 128 of the
-// columns into its own shared memory and the tensor cores of both SMs read both halves). Per flop
-// a CTA then fetches half the x~ bytes and its MMAs read half the operand bytes from shared
-// memory, which is what bounds the single-CTA kernel above.
+// tcgen05.mma.cta_group::2 (M = 256: 128 token rows per CTA and sub-tile; N = 256: each CTA decodes
+// 128 of the columns into its own shared memory and the tensor cores of both SMs read both
+// halves). Per flop a CTA fetches half the x~ bytes and decodes half the weights of the single-CTA
+// kernel above, and one issuing thread feeds two SMs.
 //
-// Roles per CTA as above; differences:
-//   * only the first CTA of the pair issues MMAs; its commits arrive on the stage barriers of
-//     BOTH CTAs (one tcgen05.commit per barrier, the peer's through its cluster address);
-//   * the peer's warp 1 relays "my x~ stage has landed" to the first CTA's a_peer barrier, and the
-//     decode warps of both CTAs arrive on the first CTA's b_full barrier (16 arrivals);
+// Roles per CTA as above. What a cycle-stamped lab build showed, and the structure that follows:
+//   * the thread that issues the MMAs is the critical resource: every barrier operation of that
+//     thread costs a few hundred cycles through the busy shared-memory pipe. So a stage holds the
+//     x~ tile AND the weight tile of a k step and is freed by ONE tcgen05.commit that arrives in
+//     both CTAs; the thread waits on two local barriers per step and polls the next step's
+//     barriers (non-blocking) before it issues this step's MMAs, so that the answer is there when
+//     it comes round;
+//   * decode warps arrive on a barrier of their own CTA. A remote arrival with cluster-scope
+//     release from a warp that has cp.async copies in flight took ~2000 cycles (the release waits
+//     for the copies); one relay thread per pair (the peer's warp 1, which has nothing in flight)
+//     tells the first CTA "my x~ and my columns are ready" with a single remote arrival per step;
+//   * one lane of a decode warp polls for the free stage, the other 31 take its word;
 //   * tensor memory is allocated and freed by warp 0 of both CTAs with the cta_group::2 forms.
 // ------------------------------------------------------------------------------------------
 constexpr int T2_SUB = 2;                                  // 128-token sub-tiles per CTA
-constexpr int T2_A_SLOTS = 3, T2_B_STAGES = 4;
-constexpr int T2_A_BYTES = T2_SUB * TC_BM * TC_BK * 2;     // 32768
+constexpr int T2_A_BYTES = T2_SUB * TC_BM * TC_BK * 2;     // x~ of one k step, this CTA's 256 tokens: 32768
 constexpr int T2_B_BYTES = 128 * TC_BK * 2;                // this CTA's half of the 256-column B tile: 16384
+// A stage holds the x~ tile and the decoded weight tile of one k step and is freed by ONE commit.
+// Four stages where the packed-word rings leave room, three above 5 bits per weight.
+__host__ __device__ constexpr int t2_stages(int K) { return K <= 5 ? 4 : 3; }
+__host__ __device__ constexpr int t2_p_stages(int K) { return K <= 4 ? 4 : 3; }
 __host__ __device__ constexpr int tc2_smem_bytes(int K)
 {
-    return 1024 + T2_A_SLOTS * T2_A_BYTES + T2_B_STAGES * T2_B_BYTES + TC_DECODE_WARPS * tc_p_stages(K) * 128 * K;
+    return 1024 + t2_stages(K) * (T2_A_BYTES + T2_B_BYTES) + TC_DECODE_WARPS * t2_p_stages(K) * 128 * K;
 }
+static_assert(tc2_smem_bytes(5) <= 232448 && tc2_smem_bytes(8) <= 232448 && tc2_smem_bytes(4) <= 232448, "pair kernel stages must fit 227 KB");
+constexpr int T2_MAX_STAGES = 4;
 
 __device__ __forceinline__ uint32_t cluster_addr(const void* p, uint32_t rank)
 {
@@ -452,9 +476,19 @@ __device__ __forceinline__ void umma2_f16(uint32_t tmem_d, uint64_t da, uint64_t
         :: "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 
-__device__ __forceinline__ void umma2_commit(uint32_t cluster_bar)
+// Arrives, once every tcgen05.mma issued so far by this thread has completed, on the barrier at
+// this shared-memory offset in BOTH CTAs of the pair. One instruction (an arrival multicast, not a
+// load); AMP_T2_TWO_COMMITS selects two unicast commits instead (measured 4-5 % slower: the
+// issuing thread's instruction stream is the critical resource of this kernel).
+__device__ __forceinline__ void umma2_commit_both(uint64_t* bar)
 {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(cluster_bar) : "memory");
+#ifndef AMP_T2_TWO_COMMITS
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 :: "r"(smem_u32(bar)), "h"((unsigned short) 3) : "memory");
+#else
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(cluster_addr(bar, 0)) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(cluster_addr(bar, 1)) : "memory");
+#endif
 }
 
 __device__ __forceinline__ void cluster_barrier()
@@ -468,9 +502,16 @@ void exl3_gemm_tc2_kernel(const TcParams P)
 {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
-    __shared__ uint64_t a_land[T2_A_SLOTS], a_peer[T2_A_SLOTS], a_free[T2_A_SLOTS], b_full[T2_B_STAGES], b_free[T2_B_STAGES], bar_done;
+    // a_land: this CTA's x~ bytes of a stage have landed; b_full: this CTA's eight decode warps of
+    // the step have published their columns. In the first CTA a_land also counts one arrival from
+    // the peer's relay thread, sent when BOTH of the peer's barriers have completed, so the issuing
+    // thread learns about all four operand pieces from two local barriers and the pair exchanges
+    // one remote arrival per step. st_free: the MMAs that read the stage have completed (one
+    // commit, both CTAs).
+    __shared__ uint64_t a_land[T2_MAX_STAGES], b_full[T2_MAX_STAGES], st_free[T2_MAX_STAGES], bar_done;
     __shared__ uint32_t s_tmem;
     __shared__ volatile int s_bad;
+    constexpr int S = t2_stages(K);
 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     uint32_t crank;
@@ -487,8 +528,12 @@ void exl3_gemm_tc2_kernel(const TcParams P)
 
     if (t == 0)
     {
-        for (int i = 0; i < T2_A_SLOTS; ++i) { mbar_init(&a_land[i], 1); mbar_init(&a_peer[i], 1); mbar_init(&a_free[i], 1); }
-        for (int i = 0; i < T2_B_STAGES; ++i) { mbar_init(&b_full[i], TC_DECODE_WARPS); mbar_init(&b_free[i], 1); }
+        for (int i = 0; i < S; ++i)
+        {
+            mbar_init(&a_land[i], leader ? 2 : 1);
+            mbar_init(&b_full[i], TC_DECODE_WARPS / 2);
+            mbar_init(&st_free[i], 1);
+        }
         mbar_init(&bar_done, 1);
         fence_mbar_init();
         s_bad = 0;
@@ -506,7 +551,7 @@ void exl3_gemm_tc2_kernel(const TcParams P)
     const uint32_t tmem = s_tmem;
 
     unsigned char* a_base = smem;
-    unsigned char* b_base = smem + T2_A_SLOTS * T2_A_BYTES;
+    unsigned char* b_base = smem + S * T2_A_BYTES;
 
     bool ok = true;
     auto wait_bar = [&](uint64_t* bar, uint32_t parity)
@@ -520,22 +565,46 @@ void exl3_gemm_tc2_kernel(const TcParams P)
         }
         if (!done) { ok = false; s_bad = 1; }
     };
+    // a whole warp waits: one lane polls (32 lanes polling one mbarrier word serialise in the
+    // shared-memory pipe and delay every other thread's barrier operations), the rest take its word
+    auto wait_bar_warp = [&](uint64_t* bar, uint32_t parity)
+    {
+        if (lane == 0) wait_bar(bar, parity);
+        __syncwarp();
+        ok = __shfl_sync(0xffffffffu, (int) ok, 0) != 0;
+    };
+    // the same with cluster-scope acquire: for the barrier the peer CTA arrives on
+    auto wait_bar_cluster = [&](uint64_t* bar, uint32_t parity)
+    {
+        if (!ok) return;
+        bool done = false;
+        for (unsigned spin = 0; spin < TC_SPIN_LIMIT && !done; ++spin)
+        {
+            uint32_t r;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(r) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+            done = r != 0;
+            if (!done && (spin & 1023) == 1023 && s_bad) break;
+        }
+        if (!done) { ok = false; s_bad = 1; }
+    };
 
     if (warp == 0)
     {
         // ---- fetch ----
         if (lane == 0)
         {
+            int s = 0; uint32_t ph = 1;                    // stage, parity of "freed for the (use)-th time" - first pass needs no wait
             for (int i = 0; i < ksteps && ok; ++i)
             {
-                const int s = i % T2_A_SLOTS;
-                if (i >= T2_A_SLOTS) wait_bar(&a_free[s], (uint32_t) (((i / T2_A_SLOTS) - 1) & 1));
+                if (i >= S) wait_bar(&st_free[s], ph);
                 if (!ok) break;
                 mbar_expect_tx(&a_land[s], (uint32_t) rows * 128);
                 const unsigned char* src = P.xt + (((size_t) i * P.M + m0) << 7);
                 for (int sub = 0; sub < nsub; ++sub)
                     bulk_g2s(a_base + s * T2_A_BYTES + sub * (TC_BM * 128), src + ((size_t) sub * TC_BM << 7),
                              (uint32_t) min(TC_BM, rows - sub * TC_BM) * 128, &a_land[s]);
+                if (++s == S) { s = 0; ph ^= 1; }
             }
         }
         __syncwarp();
@@ -546,39 +615,63 @@ void exl3_gemm_tc2_kernel(const TcParams P)
         {
             if (leader)
             {
-                // ---- MMA issue for the pair ----
+                // ---- MMA issue for the pair: per k step two waits, the MMAs, one commit ----
                 // instruction descriptor: D fp32, A/B fp16, both K-major, N = 256, M = 256 (pair)
                 constexpr uint32_t IDESC = (1u << 4) | ((uint32_t) (256 >> 3) << 17) | ((uint32_t) (256 >> 4) << 24);
                 const uint64_t da0 = make_desc(smem_u32(a_base)), db0 = make_desc(smem_u32(b_base));
+                int s = 0; uint32_t ph = 0;
+                uint32_t ra = 0, rb = 0;                   // this step's barriers were seen complete by the look-ahead poll
                 for (int i = 0; i < ksteps && ok; ++i)
                 {
-                    const int sa = i % T2_A_SLOTS, sb = i % T2_B_STAGES;
-                    wait_bar(&a_land[sa], (uint32_t) ((i / T2_A_SLOTS) & 1));
-                    wait_bar(&a_peer[sa], (uint32_t) ((i / T2_A_SLOTS) & 1));
-                    wait_bar(&b_full[sb], (uint32_t) ((i / T2_B_STAGES) & 1));
+                    TC_STAMP(i, 0);
+                    if (!ra) wait_bar_cluster(&a_land[s], ph);
+                    TC_STAMP(i, 1);
+                    if (!rb) wait_bar(&b_full[s], ph);
+                    TC_STAMP(i, 2);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t da = da0 + (uint64_t) ((sa * T2_A_BYTES) >> 4), db = db0 + (uint64_t) ((sb * T2_B_BYTES) >> 4);
-                    for (int sub = 0; sub < nsub_mma; ++sub)
+                    // Look-ahead: a non-blocking poll of the NEXT step's barriers, issued before this
+                    // step's MMAs so that the answers (a few hundred cycles through the busy
+                    // shared-memory pipe) arrive while the MMAs are being issued. The decode warps and
+                    // the fetch run stages ahead, so the answer is almost always yes and the blocking
+                    // waits above are skipped.
+                    {
+                        const int s2 = (s + 1 == S) ? 0 : s + 1;
+                        const uint32_t ph2 = (s + 1 == S) ? ph ^ 1 : ph;
+                        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                                     : "=r"(ra) : "r"(smem_u32(&a_land[s2])), "r"(ph2) : "memory");
+                        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                                     : "=r"(rb) : "r"(smem_u32(&b_full[s2])), "r"(ph2) : "memory");
+                    }
+                    const uint64_t da = da0 + (uint64_t) ((s * T2_A_BYTES) >> 4), db = db0 + (uint64_t) ((s * T2_B_BYTES) >> 4);
+                    const uint32_t acc = i > 0 ? 1u : 0u;
+                    umma2_f16(tmem, da, db, IDESC, acc);
+                    #pragma unroll
+                    for (int kk = 1; kk < TC_BK / 16; ++kk) umma2_f16(tmem, da + (uint64_t) (kk * 2), db + (uint64_t) (kk * 2), IDESC, 1u);
+                    if (nsub_mma > 1)
+                    {
+                        const uint64_t da1 = da + (uint64_t) ((TC_BM * 128) >> 4);
+                        umma2_f16(tmem + 256, da1, db, IDESC, acc);
                         #pragma unroll
-                        for (int kk = 0; kk < TC_BK / 16; ++kk)
-                            umma2_f16(tmem + sub * 256, da + (uint64_t) ((sub * (TC_BM * 128) + kk * 32) >> 4),
-                                      db + (uint64_t) ((kk * 32) >> 4), IDESC, (i > 0 || kk > 0) ? 1u : 0u);
-                    // the stages are free in BOTH CTAs once these MMAs have read them
-                    umma2_commit(cluster_addr(&a_free[sa], 0)); umma2_commit(cluster_addr(&a_free[sa], 1));
-                    umma2_commit(cluster_addr(&b_free[sb], 0)); umma2_commit(cluster_addr(&b_free[sb], 1));
-                    if (i == ksteps - 1) { umma2_commit(cluster_addr(&bar_done, 0)); umma2_commit(cluster_addr(&bar_done, 1)); }
+                        for (int kk = 1; kk < TC_BK / 16; ++kk) umma2_f16(tmem + 256, da1 + (uint64_t) (kk * 2), db + (uint64_t) (kk * 2), IDESC, 1u);
+                    }
+                    umma2_commit_both(&st_free[s]);        // the stage is free in BOTH CTAs once these MMAs have read it
+                    if (i == ksteps - 1) umma2_commit_both(&bar_done);
+                    TC_STAMP(i, 3);
+                    if (++s == S) { s = 0; ph ^= 1; }
                 }
             }
             else
             {
-                // ---- relay: tell the first CTA that this CTA's x~ stage has landed ----
+                // ---- relay: tell the first CTA that this CTA's halves of the stage are ready ----
+                int s = 0; uint32_t ph = 0;
                 for (int i = 0; i < ksteps && ok; ++i)
                 {
-                    const int sa = i % T2_A_SLOTS;
-                    wait_bar(&a_land[sa], (uint32_t) ((i / T2_A_SLOTS) & 1));
+                    wait_bar(&a_land[s], ph);
+                    wait_bar(&b_full[s], ph);
                     if (!ok) break;
-                    mbar_arrive_cluster(cluster_addr(&a_peer[sa], 0));
+                    mbar_arrive_cluster(cluster_addr(&a_land[s], 0));
+                    if (++s == S) { s = 0; ph ^= 1; }
                 }
             }
         }
@@ -593,10 +686,9 @@ void exl3_gemm_tc2_kernel(const TcParams P)
         const unsigned char* src = reinterpret_cast<const unsigned char*>(P.trellis)
                                  + ((size_t) pq * tiles_n + (size_t) nb * 16 + crank * 8 + dw) * (32 * K) + gq * (4 * K);
         const size_t step_bytes = (size_t) 4 * tiles_n * (32 * K);
-        constexpr int PS = tc_p_stages(K);
+        constexpr int PS = t2_p_stages(K);
         constexpr int SLOT = 32 * 4 * K;
-        const uint32_t pring = smem_u32(smem + T2_A_SLOTS * T2_A_BYTES + T2_B_STAGES * T2_B_BYTES)
-                             + (uint32_t) ((warp - 2) * PS * SLOT + lane * 4 * K);
+        const uint32_t pring = smem_u32(smem + S * (T2_A_BYTES + T2_B_BYTES)) + (uint32_t) ((warp - 2) * PS * SLOT + lane * 4 * K);
         #pragma unroll
         for (int j = 0; j < PS - 1; ++j)
         {
@@ -606,15 +698,10 @@ void exl3_gemm_tc2_kernel(const TcParams P)
         int pslot = 0;
         for (int i = grp; i < ksteps && ok; i += 2)
         {
-            cp_async_wait_n<PS - 2>();
+            TC_STAMP_D(i, 4);
             uint32_t w[K];
+            cp_async_wait_n<PS - 2>();
             load_chunk_s<K>(pring + pslot * SLOT, w);
-            {
-                const int nxt = i + 2 * (PS - 1), nslot = (pslot == 0) ? PS - 1 : pslot - 1;
-                if (nxt < ksteps) cp_async_chunk<K>(pring + nslot * SLOT, src + (size_t) nxt * step_bytes);
-                cp_async_commit();
-                if (++pslot == PS) pslot = 0;
-            }
             const uint32_t prev = __shfl_sync(0xffffffffu, w[K - 1], (lane + 28) & 31);
             uint32_t colA[8], colB[8];
             auto decode_r = [&](auto rtag)
@@ -628,8 +715,10 @@ void exl3_gemm_tc2_kernel(const TcParams P)
             decode_r(std::integral_constant<int, 0>()); decode_r(std::integral_constant<int, 1>());
             decode_r(std::integral_constant<int, 2>()); decode_r(std::integral_constant<int, 3>());
 
-            const int sb = i % T2_B_STAGES;
-            if (i >= T2_B_STAGES) wait_bar(&b_free[sb], (uint32_t) (((i / T2_B_STAGES) - 1) & 1));
+            const int sb = i % S;
+            TC_STAMP_D(i, 5);
+            if (i >= S) wait_bar_warp(&st_free[sb], (uint32_t) (((i / S) - 1) & 1));
+            TC_STAMP_D(i, 6);
             if (!ok) break;
             unsigned char* b = b_base + sb * T2_B_BYTES;
             const int ncol = dw * 16 + gq;
@@ -639,12 +728,22 @@ void exl3_gemm_tc2_kernel(const TcParams P)
             *reinterpret_cast<uint4*>(b + sw128(ncol + 8, 2 * pq + 1)) = make_uint4(colB[4], colB[5], colB[6], colB[7]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(cluster_addr(&b_full[sb], 0));     // the first CTA counts both CTAs' warps
+            if (lane == 0) mbar_arrive(&b_full[sb]);
+            TC_STAMP_D(i, 7);
+            {
+                // refill the slot read in this warp's previous step with the words of its step PS - 1
+                // ahead. Issued after the arrival: the arrival's release must not find this warp's
+                // newest copies still on their way from HBM.
+                const int nxt = i + 2 * (PS - 1), nslot = (pslot == 0) ? PS - 1 : pslot - 1;
+                if (nxt < ksteps) cp_async_chunk<K>(pring + nslot * SLOT, src + (size_t) nxt * step_bytes);
+                cp_async_commit();
+                if (++pslot == PS) pslot = 0;
+            }
         }
     }
 
     // ---- epilogue: each CTA stores its own 256 tokens x 256 columns ----
-    if (warp >= 2) wait_bar(&bar_done, 0);
+    if (warp >= 2 && lane == 0) wait_bar(&bar_done, 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
     const bool all_ok = !s_bad;
