@@ -518,10 +518,11 @@ void exl3_gemm_tc2_kernel(const TcParams P)
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
     const bool leader = crank == 0;
     const int nb = blockIdx.x >> 1, mb = blockIdx.y;       // 256-column block, 512-token block of the pair
-    const int m0 = mb * (2 * T2_SUB * TC_BM) + (int) crank * (T2_SUB * TC_BM);
-    const int rows = max(0, min(T2_SUB * TC_BM, P.M - m0));         // valid token rows of this CTA (the peer may have none)
+    const int cta_rows = P.sub * TC_BM;                    // token rows per CTA: 256, or 128 for short grids
+    const int m0 = mb * (2 * cta_rows) + (int) crank * cta_rows;
+    const int rows = max(0, min(cta_rows, P.M - m0));               // valid token rows of this CTA (the peer may have none)
     const int nsub = (rows + TC_BM - 1) / TC_BM;
-    const int rows_lead = min(T2_SUB * TC_BM, P.M - mb * (2 * T2_SUB * TC_BM));
+    const int rows_lead = min(cta_rows, P.M - mb * (2 * cta_rows));
     const int nsub_mma = (rows_lead + TC_BM - 1) / TC_BM;           // sub-tiles the pair multiplies (the first CTA's count)
     const int ksteps = P.k / TC_BK;
     const size_t tiles_n = (size_t) P.n >> 4;
@@ -854,17 +855,23 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     // pair form (two CTAs per 512 tokens x 256 columns) when the shape fills the device with it
-    if (g_tc_pair && n % 256 == 0 && (M > 256 || g_tc_pair == 2))
+    if (g_tc_pair && n % 256 == 0 && (M > 256 || g_tc_pair >= 2))
     {
-        const long pairs = (long) (n / 256) * (((long) M + 511) / 512);
-        if ((2 * pairs >= (long) sms * 4 / 5 || g_tc_pair == 2) && ((long) M + 511) / 512 <= 65535)
+        // 256 token rows per CTA. Measured on 148 SMs: the pair form wins from about half a device
+        // of CTAs upwards (M = 512, n = 14336: 112 CTAs, 0.087 ms against 0.153 ms); below that
+        // (k and v projections: 32 CTAs) the single-CTA form with 128-token tiles is faster, and
+        // pairs of 128-token CTAs (mode 3) never were.
+        const int psub = g_tc_pair == 3 ? 1 : T2_SUB;
+        const long mblk = ((long) M + 256 * psub - 1) / (256 * psub);
+        const long pairs = (long) (n / 256) * mblk;
+        if ((2 * pairs > (long) sms / 2 || g_tc_pair >= 2) && mblk <= 65535)
         {
             tc_fn fn2 = k_tc2[cb][K - 1];
             const int smem2 = tc2_smem_bytes(K);
             if (cudaError_t e = ensure_smem(fn2, smem2, dev)) return cuda_rc(e, "exl3_gemm smem attribute");
-            P.sub = T2_SUB;
+            P.sub = psub;
             cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3((unsigned) (2 * (n / 256)), (unsigned) (((long) M + 511) / 512), 1);
+            cfg.gridDim = dim3((unsigned) (2 * (n / 256)), (unsigned) mblk, 1);
             cfg.blockDim = dim3(TC_THREADS, 1, 1);
             cfg.dynamicSmemBytes = smem2;
             cfg.stream = stream;
@@ -911,11 +918,12 @@ AMP_API int amp_lab_tc_dbg(long long* out)
 #endif
 
 // Chooses between the single-CTA and the pair (cta_group::2) form of the prefill GEMM: 0 = never
-// the pair form, 1 = where it fills the device (default), 2 = whenever n is a multiple of 256
+// the pair form, 1 = by shape (default: pairs of 256-token CTAs from half a device of CTAs upwards,
+// single CTAs below that), 2 / 3 = pairs of 256- / 128-token CTAs whenever n is a multiple of 256
 // (tests). Returns the previous setting.
 AMP_API int amp_exl3_set_gemm_pair(int mode)
 {
     const int old = g_tc_pair;
-    g_tc_pair = mode < 0 ? 0 : (mode > 2 ? 2 : mode);
+    g_tc_pair = mode < 0 ? 0 : (mode > 3 ? 3 : mode);
     return old;
 }

@@ -241,16 +241,18 @@ def test_prefill_gemm_tensor_core(amp, oracle, m, k, n, K, cb):
     check_close(got32, ref)
 
 
+@pytest.mark.parametrize("mode", [2, 3])
 @pytest.mark.parametrize("m,k,n,K,cb", [(600, 256, 256, 4, 0), (257, 512, 512, 3, 0), (1024, 384, 256, 5, 1),
-                                        (100, 128, 256, 6, 2), (513, 256, 512, 8, 0)])
-def test_prefill_gemm_cta_pairs(amp, oracle, m, k, n, K, cb):
-    """The pair form (two CTAs per 512 tokens x 256 columns, tcgen05 cta_group::2), forced for
-    small shapes: ragged token counts, a second CTA with few or no rows, several k steps."""
+                                        (100, 128, 256, 6, 2), (513, 256, 512, 8, 0), (129, 1024, 256, 7, 0)])
+def test_prefill_gemm_cta_pairs(amp, oracle, m, k, n, K, cb, mode):
+    """The pair form (two CTAs per 512 or 256 tokens x 256 columns, tcgen05 cta_group::2), forced
+    for small shapes: ragged token counts, a second CTA with few or no rows, several k steps,
+    three- and four-stage pipelines (bit widths above and below 6)."""
     from ampstein_b200 import _lib
     trellis, suh, svh, x = make_linear(k, n, K, seed=7400 + m + K, m=m)
     svh = (svh.astype(np.float32) / (1.2437 * np.sqrt(k))).astype(np.float16)
     ref = oracle.linear(x, trellis, suh, svh, cb, fp32_out=True)
-    old = _lib.lib().amp_exl3_set_gemm_pair(2)
+    old = _lib.lib().amp_exl3_set_gemm_pair(mode)
     try:
         got = run_gemm(amp, trellis, suh, svh, x, cb)
         assert gemm_status() == 0
