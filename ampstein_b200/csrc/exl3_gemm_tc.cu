@@ -435,9 +435,9 @@ void exl3_gemm_tc_kernel(const TcParams P)
 //     barriers (non-blocking) before it issues this step's MMAs, so that the answer is there when
 //     it comes round;
 //   * decode warps arrive on a barrier of their own CTA. A remote arrival with cluster-scope
-//     release from a warp that has cp.async copies in flight took ~2000 cycles (the release waits
-//     for the copies); one relay thread per pair (the peer's warp 1, which has nothing in flight)
-//     tells the first CTA "my x~ and my columns are ready" with a single remote arrival per step;
+//     release took 1000-2000 cycles (it waits for what the SM has in flight); one relay thread per
+//     pair (the peer's warp 1) tells the first CTA "my x~ and my columns are ready" with a single,
+//     relaxed remote arrival per step (see mbar_arrive_cluster);
 //   * one lane of a decode warp polls for the free stage, the other 31 take its word;
 //   * tensor memory is allocated and freed by warp 0 of both CTAs with the cta_group::2 forms.
 // ------------------------------------------------------------------------------------------
@@ -462,9 +462,23 @@ __device__ __forceinline__ uint32_t cluster_addr(const void* p, uint32_t rank)
     return r;
 }
 
+// The relay's arrival on the first CTA's barrier. Relaxed on purpose: with release semantics at
+// cluster scope this one instruction took well over a thousand cycles (it waits for everything the
+// SM has in flight), and since the relay thread sends one per k step, in order, it set the pace of
+// the whole pair: 690 -> 793 TFLOP/s on a 4096 x 4096 weight when it was relaxed. What the arrival
+// publishes is already in place when it is sent: the x~ bytes were written by the bulk copy whose
+// completion the relay observed with an acquire, the weight tile by warps that each ran
+// fence.proxy.async and a releasing arrive on the barrier the relay acquired; both live in this
+// SM's shared memory, which is read in place by the pair's tensor cores and cached nowhere.
+// AMP_T2_RELEASE_RELAY selects the releasing form. A test runs the benchmark's shapes twelve
+// times and requires bit-identical results.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
 {
+#ifdef AMP_T2_RELEASE_RELAY
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_bar) : "memory");
+#else
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_bar) : "memory");
+#endif
 }
 
 __device__ __forceinline__ void umma2_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate)
@@ -574,15 +588,18 @@ void exl3_gemm_tc2_kernel(const TcParams P)
         __syncwarp();
         ok = __shfl_sync(0xffffffffu, (int) ok, 0) != 0;
     };
-    // the same with cluster-scope acquire: for the barrier the peer CTA arrives on
-    auto wait_bar_cluster = [&](uint64_t* bar, uint32_t parity)
+    // The three single threads that drive the pipeline (fetch, MMA issue, relay) poll without
+    // parking: a thread parked in try_wait was seen to sleep on for up to ~1000 cycles after an
+    // arrival that came from the tensor core, a bulk copy or the other CTA. Cluster-scope acquire,
+    // since those arrivals may come from the peer.
+    auto wait_bar_spin = [&](uint64_t* bar, uint32_t parity)
     {
         if (!ok) return;
         bool done = false;
         for (unsigned spin = 0; spin < TC_SPIN_LIMIT && !done; ++spin)
         {
             uint32_t r;
-            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                          : "=r"(r) : "r"(smem_u32(bar)), "r"(parity) : "memory");
             done = r != 0;
             if (!done && (spin & 1023) == 1023 && s_bad) break;
@@ -598,7 +615,7 @@ void exl3_gemm_tc2_kernel(const TcParams P)
             int s = 0; uint32_t ph = 1;                    // stage, parity of "freed for the (use)-th time" - first pass needs no wait
             for (int i = 0; i < ksteps && ok; ++i)
             {
-                if (i >= S) wait_bar(&st_free[s], ph);
+                if (i >= S) wait_bar_spin(&st_free[s], ph);
                 if (!ok) break;
                 mbar_expect_tx(&a_land[s], (uint32_t) rows * 128);
                 const unsigned char* src = P.xt + (((size_t) i * P.M + m0) << 7);
@@ -625,9 +642,9 @@ void exl3_gemm_tc2_kernel(const TcParams P)
                 for (int i = 0; i < ksteps && ok; ++i)
                 {
                     TC_STAMP(i, 0);
-                    if (!ra) wait_bar_cluster(&a_land[s], ph);
+                    if (!ra) wait_bar_spin(&a_land[s], ph);
                     TC_STAMP(i, 1);
-                    if (!rb) wait_bar(&b_full[s], ph);
+                    if (!rb) wait_bar_spin(&b_full[s], ph);
                     TC_STAMP(i, 2);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -668,8 +685,8 @@ void exl3_gemm_tc2_kernel(const TcParams P)
                 int s = 0; uint32_t ph = 0;
                 for (int i = 0; i < ksteps && ok; ++i)
                 {
-                    wait_bar(&a_land[s], ph);
-                    wait_bar(&b_full[s], ph);
+                    wait_bar_spin(&a_land[s], ph);
+                    wait_bar_spin(&b_full[s], ph);
                     if (!ok) break;
                     mbar_arrive_cluster(cluster_addr(&a_land[s], 0));
                     if (++s == S) { s = 0; ph ^= 1; }

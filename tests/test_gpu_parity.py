@@ -264,6 +264,51 @@ def test_prefill_gemm_cta_pairs(amp, oracle, m, k, n, K, cb, mode):
         _lib.lib().amp_exl3_set_gemm_pair(old)
 
 
+@pytest.mark.parametrize("k,n,K", [(4096, 4096, 5), (14336, 4096, 4), (4096, 14336, 3)])
+def test_prefill_gemm_bench_shapes_repeatable(amp, k, n, K):
+    """The benchmark's prefill shapes (2048 tokens) through the default dispatch, i.e. the pair
+    form: twelve launches must agree bit for bit (the two CTAs of a pair hand stages to each other
+    through shared-memory barriers; a hand-off that came too early would show as a difference
+    between launches), the single-CTA form must agree within rounding, and both must agree with
+    "reconstruct, then an fp32 matmul of the rotated input" computed by other kernels."""
+    from ampstein_b200 import _lib
+    m = 2048
+    g = torch.Generator(device="cuda").manual_seed(9100 + K)
+    t = torch.randint(-32768, 32767, (k // 16, n // 16, 16 * K), dtype=torch.int16, device="cuda", generator=g)
+    suh = (torch.randint(0, 2, (k,), device="cuda", generator=g) * 2 - 1).to(torch.float16)
+    svh = ((torch.randint(0, 2, (n,), device="cuda", generator=g) * 2 - 1) / (1.2437 * np.sqrt(k))).to(torch.float16)
+    x = torch.randn((m, k), device="cuda", generator=g).to(torch.float16)
+    outs = []
+    for _ in range(12):
+        y = torch.empty((m, n), dtype=torch.float16, device="cuda")
+        amp.exl3_gemm(x, t, y, suh, svh)
+        outs.append(y)
+    torch.cuda.synchronize()
+    assert gemm_status() == 0
+    for y in outs[1:]:
+        assert torch.equal(y, outs[0])
+    old = _lib.lib().amp_exl3_set_gemm_pair(0)
+    try:
+        y1 = torch.empty((m, n), dtype=torch.float16, device="cuda")
+        amp.exl3_gemm(x, t, y1, suh, svh)
+        torch.cuda.synchronize()
+    finally:
+        _lib.lib().amp_exl3_set_gemm_pair(old)
+    assert gemm_status() == 0
+    # other kernels: rotation of the input, reconstruct of the weight, fp32 matmul, rotation of the output
+    xt = torch.empty_like(x)
+    amp.had_r_128(x, xt, pre_scale=suh)
+    w = torch.empty((k, n), dtype=torch.float16, device="cuda")
+    amp.exl3_reconstruct(w, t, K)
+    acc = xt.float() @ w.float()
+    ref = torch.empty_like(acc)
+    amp.had_r_128(acc, ref, post_scale=svh)
+    ref = ref.cpu().numpy()
+    check_close(outs[0].float().cpu().numpy(), ref)
+    check_close(y1.float().cpu().numpy(), ref)
+    check_close(y1.float().cpu().numpy(), outs[0].float().cpu().numpy())
+
+
 def test_prefill_gemm_bf16_activations(amp, oracle):
     """bf16 activations (the prefill configuration): the oracle consumes the bf16 values exactly,
     with the fp32 input scale the bf16 form uses."""
