@@ -481,15 +481,6 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
 #endif
 }
 
-__device__ __forceinline__ void umma2_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
-        :: "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-
 // Arrives, once every tcgen05.mma issued so far by this thread has completed, on the barrier at
 // this shared-memory offset in BOTH CTAs of the pair. One instruction (an arrival multicast, not a
 // load); AMP_T2_TWO_COMMITS selects two unicast commits instead (measured 4-5 % slower: the
@@ -504,6 +495,59 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar)
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(cluster_addr(bar, 1)) : "memory");
 #endif
 }
+
+// One k step of the issuing thread as a single instruction sequence: the non-blocking polls of
+// the NEXT step's two barriers go out first, then the step's MMAs (four per 128-token sub-tile,
+// k = 16 each: the descriptors advance by 32 bytes = 2 units), and only then are the polls'
+// predicates turned into values. Written as one asm block because a predicate cannot leave one:
+// with the polls in blocks of their own the thread sat out each poll's round trip through the
+// shared-memory pipe before it issued the first MMA.
+#define AMP_UMMA2(d, a, b, p) "tcgen05.mma.cta_group::2.kind::f16 [" d "], " a ", " b ", %5, {%10, %10, %10, %10, %10, %10, %10, %10}, " p ";\n\t"
+#define AMP_UMMA2_HEAD \
+        "{\n\t" \
+        ".reg .pred pa, pb, pacc, pone;\n\t" \
+        ".reg .b64 a1, a2, a3, b1, b2, b3, c0, c1, c2, c3;\n\t" \
+        ".reg .b32 t1;\n\t" \
+        "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 pa, [%7], %9;\n\t" \
+        "mbarrier.test_wait.parity.shared::cta.b64 pb, [%8], %9;\n\t" \
+        "setp.ne.b32 pacc, %6, 0;\n\t" \
+        "setp.eq.b32 pone, %10, 0;\n\t" \
+        "add.u64 a1, %3, 2;\n\t"  "add.u64 a2, %3, 4;\n\t"  "add.u64 a3, %3, 6;\n\t" \
+        "add.u64 b1, %4, 2;\n\t"  "add.u64 b2, %4, 4;\n\t"  "add.u64 b3, %4, 6;\n\t" \
+        AMP_UMMA2("%2", "%3", "%4", "pacc") AMP_UMMA2("%2", "a1", "b1", "pone") \
+        AMP_UMMA2("%2", "a2", "b2", "pone") AMP_UMMA2("%2", "a3", "b3", "pone")
+#define AMP_UMMA2_SUB1 \
+        "add.u32 t1, %2, 256;\n\t" \
+        "add.u64 c0, %3, %11;\n\t" "add.u64 c1, a1, %11;\n\t" "add.u64 c2, a2, %11;\n\t" "add.u64 c3, a3, %11;\n\t" \
+        AMP_UMMA2("t1", "c0", "%4", "pacc") AMP_UMMA2("t1", "c1", "b1", "pone") \
+        AMP_UMMA2("t1", "c2", "b2", "pone") AMP_UMMA2("t1", "c3", "b3", "pone")
+#define AMP_UMMA2_TAIL \
+        "selp.u32 %0, 1, 0, pa;\n\t" \
+        "selp.u32 %1, 1, 0, pb;\n\t" \
+        "}"
+template <bool TWO_SUBS>
+__device__ __forceinline__ void umma2_step(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate,
+                                           uint32_t next_a_bar, uint32_t next_b_bar, uint32_t next_parity,
+                                           uint32_t& next_a_ready, uint32_t& next_b_ready)
+{
+    const uint64_t sub_desc = (uint64_t) ((TC_BM * 128) >> 4);     // second sub-tile of the x~ stage, in descriptor units
+    if constexpr (TWO_SUBS)
+        asm volatile(AMP_UMMA2_HEAD AMP_UMMA2_SUB1 AMP_UMMA2_TAIL
+            : "=r"(next_a_ready), "=r"(next_b_ready)
+            : "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(next_a_bar), "r"(next_b_bar), "r"(next_parity),
+              "r"(0u), "l"(sub_desc)
+            : "memory");
+    else
+        asm volatile(AMP_UMMA2_HEAD AMP_UMMA2_TAIL
+            : "=r"(next_a_ready), "=r"(next_b_ready)
+            : "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(next_a_bar), "r"(next_b_bar), "r"(next_parity),
+              "r"(0u), "l"(sub_desc)
+            : "memory");
+}
+#undef AMP_UMMA2
+#undef AMP_UMMA2_HEAD
+#undef AMP_UMMA2_SUB1
+#undef AMP_UMMA2_TAIL
 
 __device__ __forceinline__ void cluster_barrier()
 {
@@ -648,30 +692,16 @@ void exl3_gemm_tc2_kernel(const TcParams P)
                     TC_STAMP(i, 2);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    // Look-ahead: a non-blocking poll of the NEXT step's barriers, issued before this
-                    // step's MMAs so that the answers (a few hundred cycles through the busy
-                    // shared-memory pipe) arrive while the MMAs are being issued. The decode warps and
-                    // the fetch run stages ahead, so the answer is almost always yes and the blocking
-                    // waits above are skipped.
+                    // Look-ahead: the NEXT step's barriers are polled (non-blocking) in the same
+                    // instruction sequence as this step's MMAs. The decode warps and the fetch run
+                    // stages ahead, so the answer is almost always yes and the waits above are skipped.
                     {
                         const int s2 = (s + 1 == S) ? 0 : s + 1;
                         const uint32_t ph2 = (s + 1 == S) ? ph ^ 1 : ph;
-                        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                                     : "=r"(ra) : "r"(smem_u32(&a_land[s2])), "r"(ph2) : "memory");
-                        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                                     : "=r"(rb) : "r"(smem_u32(&b_full[s2])), "r"(ph2) : "memory");
-                    }
-                    const uint64_t da = da0 + (uint64_t) ((s * T2_A_BYTES) >> 4), db = db0 + (uint64_t) ((s * T2_B_BYTES) >> 4);
-                    const uint32_t acc = i > 0 ? 1u : 0u;
-                    umma2_f16(tmem, da, db, IDESC, acc);
-                    #pragma unroll
-                    for (int kk = 1; kk < TC_BK / 16; ++kk) umma2_f16(tmem, da + (uint64_t) (kk * 2), db + (uint64_t) (kk * 2), IDESC, 1u);
-                    if (nsub_mma > 1)
-                    {
-                        const uint64_t da1 = da + (uint64_t) ((TC_BM * 128) >> 4);
-                        umma2_f16(tmem + 256, da1, db, IDESC, acc);
-                        #pragma unroll
-                        for (int kk = 1; kk < TC_BK / 16; ++kk) umma2_f16(tmem + 256, da1 + (uint64_t) (kk * 2), db + (uint64_t) (kk * 2), IDESC, 1u);
+                        const uint64_t da = da0 + (uint64_t) ((s * T2_A_BYTES) >> 4), db = db0 + (uint64_t) ((s * T2_B_BYTES) >> 4);
+                        const uint32_t acc = i > 0 ? 1u : 0u;
+                        if (nsub_mma > 1) umma2_step<true>(tmem, da, db, IDESC, acc, smem_u32(&a_land[s2]), smem_u32(&b_full[s2]), ph2, ra, rb);
+                        else              umma2_step<false>(tmem, da, db, IDESC, acc, smem_u32(&a_land[s2]), smem_u32(&b_full[s2]), ph2, ra, rb);
                     }
                     umma2_commit_both(&st_free[s]);        // the stage is free in BOTH CTAs once these MMAs have read it
                     if (i == ksteps - 1) umma2_commit_both(&bar_done);
