@@ -901,17 +901,17 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
     }
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    // pair form (two CTAs per 512 tokens x 256 columns) when the shape fills the device with it
+    // pair form (two CTAs per 256-column block) for every weight it can tile and more than 256 tokens
     if (g_tc_pair && n % 256 == 0 && (M > 256 || g_tc_pair >= 2))
     {
-        // 256 token rows per CTA. Measured on 148 SMs: the pair form wins from about half a device
-        // of CTAs upwards (M = 512, n = 14336: 112 CTAs, 0.087 ms against 0.153 ms); below that
-        // (k and v projections: 32 CTAs) the single-CTA form with 128-token tiles is faster, and
-        // pairs of 128-token CTAs (mode 3) never were.
-        const int psub = g_tc_pair == 3 ? 1 : T2_SUB;
+        // 256 token rows per CTA amortise the decode best, but a pair's k loop takes about as long
+        // with 128: where the 128-row grid still fits one wave of CTA pairs it halves the time
+        // (measured: 2048 x 4096 x 1024 0.080 -> 0.068 ms, 1024 x 4096 x 4096 0.073 -> 0.060 ms,
+        // against 0.082 / 0.084 ms for the single-CTA form), beyond one wave it doubles the waves.
+        const long pairs128 = (long) (n / 256) * (((long) M + 255) / 256);
+        const int psub = g_tc_pair == 3 ? 1 : (g_tc_pair == 2 ? T2_SUB : (pairs128 <= sms / 2 ? 1 : T2_SUB));
         const long mblk = ((long) M + 256 * psub - 1) / (256 * psub);
-        const long pairs = (long) (n / 256) * mblk;
-        if ((2 * pairs > (long) sms / 2 || g_tc_pair >= 2) && mblk <= 65535)
+        if (mblk <= 65535)
         {
             tc_fn fn2 = k_tc2[cb][K - 1];
             const int smem2 = tc2_smem_bytes(K);
@@ -965,9 +965,9 @@ AMP_API int amp_lab_tc_dbg(long long* out)
 #endif
 
 // Chooses between the single-CTA and the pair (cta_group::2) form of the prefill GEMM: 0 = never
-// the pair form, 1 = by shape (default: pairs of 256-token CTAs from half a device of CTAs upwards,
-// single CTAs below that), 2 / 3 = pairs of 256- / 128-token CTAs whenever n is a multiple of 256
-// (tests). Returns the previous setting.
+// the pair form, 1 = by shape (default: pairs whenever n is a multiple of 256 and M > 256, 128-token
+// CTAs while that grid fits one wave, 256-token CTAs beyond), 2 / 3 = pairs of 256- / 128-token
+// CTAs whenever n is a multiple of 256 (tests). Returns the previous setting.
 AMP_API int amp_exl3_set_gemm_pair(int mode)
 {
     const int old = g_tc_pair;
