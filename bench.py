@@ -394,7 +394,7 @@ def run_prefill(args):
         "gpu_launches": 14 * args.steps, "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(tf / peak, 4),
                      "peak_source": "measured burst (MEASURED_PEAKS.json)" if "bf16_tflops" in peaks else "fallback",
-                     "kernel": "exl3_gemm_tc_kernel", "traffic": None}}), flush=True)
+                     "kernel": "exl3_gemm_tc2_kernel", "traffic": None}}), flush=True)
 
 
 def run_moe(args):
