@@ -454,6 +454,13 @@ __host__ __device__ constexpr int tc2_smem_bytes(int K)
 }
 static_assert(tc2_smem_bytes(5) <= 232448 && tc2_smem_bytes(8) <= 232448 && tc2_smem_bytes(4) <= 232448, "pair kernel stages must fit 227 KB");
 constexpr int T2_MAX_STAGES = 4;
+// MMA-issuing threads in the first CTA: one per 128-token sub-tile (each with its own accumulator),
+// in warps 1 and 18, so that the two instruction streams run on different schedulers
+#ifndef AMP_T2_ISSUERS
+#define AMP_T2_ISSUERS 2
+#endif
+constexpr int T2_ISSUERS = AMP_T2_ISSUERS;
+constexpr int T2_THREADS = TC_THREADS + (T2_ISSUERS > 1 ? 32 : 0);
 
 __device__ __forceinline__ uint32_t cluster_addr(const void* p, uint32_t rank)
 {
@@ -496,18 +503,17 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar)
 #endif
 }
 
-// One k step of the issuing thread as a single instruction sequence: the non-blocking polls of
-// the NEXT step's two barriers go out first, then the step's MMAs (four per 128-token sub-tile,
-// k = 16 each: the descriptors advance by 32 bytes = 2 units), and only then are the polls'
-// predicates turned into values. Written as one asm block because a predicate cannot leave one:
+// One k step of one sub-tile as a single instruction sequence: the non-blocking polls of the NEXT
+// step's two barriers go out first, then the four MMAs of the 128-token sub-tile (k = 16 each:
+// the descriptors advance by 32 bytes = 2 units), and only then are the polls' predicates turned
+// into values. Written as one asm block because a predicate cannot leave one:
 // with the polls in blocks of their own the thread sat out each poll's round trip through the
 // shared-memory pipe before it issued the first MMA.
 #define AMP_UMMA2(d, a, b, p) "tcgen05.mma.cta_group::2.kind::f16 [" d "], " a ", " b ", %5, {%10, %10, %10, %10, %10, %10, %10, %10}, " p ";\n\t"
 #define AMP_UMMA2_HEAD \
         "{\n\t" \
         ".reg .pred pa, pb, pacc, pone;\n\t" \
-        ".reg .b64 a1, a2, a3, b1, b2, b3, c0, c1, c2, c3;\n\t" \
-        ".reg .b32 t1;\n\t" \
+        ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t" \
         "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 pa, [%7], %9;\n\t" \
         "mbarrier.test_wait.parity.shared::cta.b64 pb, [%8], %9;\n\t" \
         "setp.ne.b32 pacc, %6, 0;\n\t" \
@@ -516,37 +522,21 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar)
         "add.u64 b1, %4, 2;\n\t"  "add.u64 b2, %4, 4;\n\t"  "add.u64 b3, %4, 6;\n\t" \
         AMP_UMMA2("%2", "%3", "%4", "pacc") AMP_UMMA2("%2", "a1", "b1", "pone") \
         AMP_UMMA2("%2", "a2", "b2", "pone") AMP_UMMA2("%2", "a3", "b3", "pone")
-#define AMP_UMMA2_SUB1 \
-        "add.u32 t1, %2, 256;\n\t" \
-        "add.u64 c0, %3, %11;\n\t" "add.u64 c1, a1, %11;\n\t" "add.u64 c2, a2, %11;\n\t" "add.u64 c3, a3, %11;\n\t" \
-        AMP_UMMA2("t1", "c0", "%4", "pacc") AMP_UMMA2("t1", "c1", "b1", "pone") \
-        AMP_UMMA2("t1", "c2", "b2", "pone") AMP_UMMA2("t1", "c3", "b3", "pone")
 #define AMP_UMMA2_TAIL \
         "selp.u32 %0, 1, 0, pa;\n\t" \
         "selp.u32 %1, 1, 0, pb;\n\t" \
         "}"
-template <bool TWO_SUBS>
 __device__ __forceinline__ void umma2_step(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate,
                                            uint32_t next_a_bar, uint32_t next_b_bar, uint32_t next_parity,
                                            uint32_t& next_a_ready, uint32_t& next_b_ready)
 {
-    const uint64_t sub_desc = (uint64_t) ((TC_BM * 128) >> 4);     // second sub-tile of the x~ stage, in descriptor units
-    if constexpr (TWO_SUBS)
-        asm volatile(AMP_UMMA2_HEAD AMP_UMMA2_SUB1 AMP_UMMA2_TAIL
-            : "=r"(next_a_ready), "=r"(next_b_ready)
-            : "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(next_a_bar), "r"(next_b_bar), "r"(next_parity),
-              "r"(0u), "l"(sub_desc)
-            : "memory");
-    else
-        asm volatile(AMP_UMMA2_HEAD AMP_UMMA2_TAIL
-            : "=r"(next_a_ready), "=r"(next_b_ready)
-            : "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(next_a_bar), "r"(next_b_bar), "r"(next_parity),
-              "r"(0u), "l"(sub_desc)
-            : "memory");
+    asm volatile(AMP_UMMA2_HEAD AMP_UMMA2_TAIL
+        : "=r"(next_a_ready), "=r"(next_b_ready)
+        : "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(next_a_bar), "r"(next_b_bar), "r"(next_parity), "r"(0u)
+        : "memory");
 }
 #undef AMP_UMMA2
 #undef AMP_UMMA2_HEAD
-#undef AMP_UMMA2_SUB1
 #undef AMP_UMMA2_TAIL
 
 __device__ __forceinline__ void cluster_barrier()
@@ -555,7 +545,7 @@ __device__ __forceinline__ void cluster_barrier()
 }
 
 template <int K, int CB>
-__global__ __launch_bounds__(TC_THREADS, 1)
+__global__ __launch_bounds__(T2_THREADS, 1)
 void exl3_gemm_tc2_kernel(const TcParams P)
 {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -591,9 +581,9 @@ void exl3_gemm_tc2_kernel(const TcParams P)
         {
             mbar_init(&a_land[i], leader ? 2 : 1);
             mbar_init(&b_full[i], TC_DECODE_WARPS / 2);
-            mbar_init(&st_free[i], 1);
+            mbar_init(&st_free[i], T2_ISSUERS);
         }
-        mbar_init(&bar_done, 1);
+        mbar_init(&bar_done, T2_ISSUERS);
         fence_mbar_init();
         s_bad = 0;
     }
@@ -671,45 +661,54 @@ void exl3_gemm_tc2_kernel(const TcParams P)
         }
         __syncwarp();
     }
-    else if (warp == 1)
+    else if (warp == 1 || warp == 18)
     {
+        // ---- MMA issue for the pair: per k step two waits, four MMAs per sub-tile, one commit ----
+        // `which` = the sub-tile (and accumulator) this thread owns; with one issuer it owns both
+        auto issue_loop = [&](const int which)
+        {
+            // instruction descriptor: D fp32, A/B fp16, both K-major, N = 256, M = 256 (pair)
+            constexpr uint32_t IDESC = (1u << 4) | ((uint32_t) (256 >> 3) << 17) | ((uint32_t) (256 >> 4) << 24);
+            constexpr uint32_t SUB_DESC = (TC_BM * 128) >> 4;
+            const uint64_t da0 = make_desc(smem_u32(a_base)), db0 = make_desc(smem_u32(b_base));
+            const bool has0 = T2_ISSUERS == 1 || which == 0;                       // this thread multiplies sub-tile 0
+            const bool has1 = (T2_ISSUERS == 1 || which == 1) && nsub_mma > 1;     // ... sub-tile 1
+            int s = 0; uint32_t ph = 0;
+            uint32_t ra = 0, rb = 0;                       // this step's barriers were seen complete by the look-ahead poll
+            for (int i = 0; i < ksteps && ok; ++i)
+            {
+                if (which == 0) TC_STAMP(i, 0);
+                if (!ra) wait_bar_spin(&a_land[s], ph);
+                if (which == 0) TC_STAMP(i, 1);
+                if (!rb) wait_bar_spin(&b_full[s], ph);
+                if (which == 0) TC_STAMP(i, 2);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // Look-ahead: the NEXT step's barriers are polled (non-blocking) in the same
+                // instruction sequence as this step's MMAs. The decode warps and the fetch run
+                // stages ahead, so the answer is almost always yes and the waits above are skipped.
+                const int s2 = (s + 1 == S) ? 0 : s + 1;
+                const uint32_t ph2 = (s + 1 == S) ? ph ^ 1 : ph;
+                const uint64_t da = da0 + (uint64_t) ((s * T2_A_BYTES) >> 4), db = db0 + (uint64_t) ((s * T2_B_BYTES) >> 4);
+                const uint32_t acc = i > 0 ? 1u : 0u;
+                const uint32_t na = smem_u32(&a_land[s2]), nbar = smem_u32(&b_full[s2]);
+                ra = rb = 0;
+                if (has0) umma2_step(tmem, da, db, IDESC, acc, na, nbar, ph2, ra, rb);
+                if (has1) umma2_step(tmem + 256, da + SUB_DESC, db, IDESC, acc, na, nbar, ph2, ra, rb);
+                umma2_commit_both(&st_free[s]);            // the stage is free in BOTH CTAs once every issuer's MMAs have read it
+                if (i == ksteps - 1) umma2_commit_both(&bar_done);
+                if (which == 0) TC_STAMP(i, 3);
+                if (++s == S) { s = 0; ph ^= 1; }
+            }
+        };
         if (lane == 0)
         {
             if (leader)
             {
-                // ---- MMA issue for the pair: per k step two waits, the MMAs, one commit ----
-                // instruction descriptor: D fp32, A/B fp16, both K-major, N = 256, M = 256 (pair)
-                constexpr uint32_t IDESC = (1u << 4) | ((uint32_t) (256 >> 3) << 17) | ((uint32_t) (256 >> 4) << 24);
-                const uint64_t da0 = make_desc(smem_u32(a_base)), db0 = make_desc(smem_u32(b_base));
-                int s = 0; uint32_t ph = 0;
-                uint32_t ra = 0, rb = 0;                   // this step's barriers were seen complete by the look-ahead poll
-                for (int i = 0; i < ksteps && ok; ++i)
-                {
-                    TC_STAMP(i, 0);
-                    if (!ra) wait_bar_spin(&a_land[s], ph);
-                    TC_STAMP(i, 1);
-                    if (!rb) wait_bar_spin(&b_full[s], ph);
-                    TC_STAMP(i, 2);
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    // Look-ahead: the NEXT step's barriers are polled (non-blocking) in the same
-                    // instruction sequence as this step's MMAs. The decode warps and the fetch run
-                    // stages ahead, so the answer is almost always yes and the waits above are skipped.
-                    {
-                        const int s2 = (s + 1 == S) ? 0 : s + 1;
-                        const uint32_t ph2 = (s + 1 == S) ? ph ^ 1 : ph;
-                        const uint64_t da = da0 + (uint64_t) ((s * T2_A_BYTES) >> 4), db = db0 + (uint64_t) ((s * T2_B_BYTES) >> 4);
-                        const uint32_t acc = i > 0 ? 1u : 0u;
-                        if (nsub_mma > 1) umma2_step<true>(tmem, da, db, IDESC, acc, smem_u32(&a_land[s2]), smem_u32(&b_full[s2]), ph2, ra, rb);
-                        else              umma2_step<false>(tmem, da, db, IDESC, acc, smem_u32(&a_land[s2]), smem_u32(&b_full[s2]), ph2, ra, rb);
-                    }
-                    umma2_commit_both(&st_free[s]);        // the stage is free in BOTH CTAs once these MMAs have read it
-                    if (i == ksteps - 1) umma2_commit_both(&bar_done);
-                    TC_STAMP(i, 3);
-                    if (++s == S) { s = 0; ph ^= 1; }
-                }
+                if (warp == 1) issue_loop(0);
+                else if (T2_ISSUERS > 1) issue_loop(1);
             }
-            else
+            else if (warp == 1)
             {
                 // ---- relay: tell the first CTA that this CTA's halves of the stage are ready ----
                 int s = 0; uint32_t ph = 0;
@@ -791,7 +790,8 @@ void exl3_gemm_tc2_kernel(const TcParams P)
     }
 
     // ---- epilogue: each CTA stores its own 256 tokens x 256 columns ----
-    if (warp >= 2 && lane == 0) wait_bar(&bar_done, 0);
+    const bool dec_warp = warp >= 2 && warp < 2 + TC_DECODE_WARPS;
+    if (dec_warp && lane == 0) wait_bar(&bar_done, 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     __syncthreads();
     const bool all_ok = !s_bad;
@@ -802,7 +802,7 @@ void exl3_gemm_tc2_kernel(const TcParams P)
     for (int sub = 0; sub < nsub; ++sub)
     for (int hb = 0; hb < 2; ++hb)                       // the two 128-column Hadamard blocks of the pair's 256 columns
     {
-        if (all_ok && warp >= 2)
+        if (all_ok && dec_warp)
         {
             const int lg = warp & 3, ch = ew >> 2;
             const int lrow = 32 * lg + lane;
@@ -824,7 +824,7 @@ void exl3_gemm_tc2_kernel(const TcParams P)
                 *reinterpret_cast<uint4*>(tile + lrow * TP + col0 + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
         }
         __syncthreads();
-        if (all_ok && warp >= 2)
+        if (all_ok && dec_warp)
         {
             const size_t cblk = (size_t) nb * 256 + (size_t) hb * 128;
             const half4 sv = reinterpret_cast<const half4*>(P.svh + cblk)[lane];
@@ -919,7 +919,7 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
             P.sub = psub;
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((unsigned) (2 * (n / 256)), (unsigned) mblk, 1);
-            cfg.blockDim = dim3(TC_THREADS, 1, 1);
+            cfg.blockDim = dim3(T2_THREADS, 1, 1);
             cfg.dynamicSmemBytes = smem2;
             cfg.stream = stream;
             cudaLaunchAttribute attr[1];
