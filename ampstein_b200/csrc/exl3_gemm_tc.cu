@@ -572,6 +572,7 @@ void exl3_gemm_tc2_kernel(const TcParams P)
     const int nsub = (rows + TC_BM - 1) / TC_BM;
     const int rows_lead = min(cta_rows, P.M - mb * (2 * cta_rows));
     const int nsub_mma = (rows_lead + TC_BM - 1) / TC_BM;           // sub-tiles the pair multiplies (the first CTA's count)
+    const int n_issuers = (T2_ISSUERS > 1 && nsub_mma > 1) ? 2 : 1;   // threads that issue MMAs and commit (same value in both CTAs)
     const int ksteps = P.k / TC_BK;
     const size_t tiles_n = (size_t) P.n >> 4;
 
@@ -581,9 +582,9 @@ void exl3_gemm_tc2_kernel(const TcParams P)
         {
             mbar_init(&a_land[i], leader ? 2 : 1);
             mbar_init(&b_full[i], TC_DECODE_WARPS / 2);
-            mbar_init(&st_free[i], T2_ISSUERS);
+            mbar_init(&st_free[i], n_issuers);
         }
-        mbar_init(&bar_done, T2_ISSUERS);
+        mbar_init(&bar_done, n_issuers);
         fence_mbar_init();
         s_bad = 0;
     }
@@ -671,8 +672,8 @@ void exl3_gemm_tc2_kernel(const TcParams P)
             constexpr uint32_t IDESC = (1u << 4) | ((uint32_t) (256 >> 3) << 17) | ((uint32_t) (256 >> 4) << 24);
             constexpr uint32_t SUB_DESC = (TC_BM * 128) >> 4;
             const uint64_t da0 = make_desc(smem_u32(a_base)), db0 = make_desc(smem_u32(b_base));
-            const bool has0 = T2_ISSUERS == 1 || which == 0;                       // this thread multiplies sub-tile 0
-            const bool has1 = (T2_ISSUERS == 1 || which == 1) && nsub_mma > 1;     // ... sub-tile 1
+            const bool has0 = which == 0;                                          // this thread multiplies sub-tile 0
+            const bool has1 = (n_issuers == 1 || which == 1) && nsub_mma > 1;      // ... sub-tile 1
             int s = 0; uint32_t ph = 0;
             uint32_t ra = 0, rb = 0;                       // this step's barriers were seen complete by the look-ahead poll
             for (int i = 0; i < ksteps && ok; ++i)
@@ -706,7 +707,7 @@ void exl3_gemm_tc2_kernel(const TcParams P)
             if (leader)
             {
                 if (warp == 1) issue_loop(0);
-                else if (T2_ISSUERS > 1) issue_loop(1);
+                else if (n_issuers > 1) issue_loop(1);
             }
             else if (warp == 1)
             {
