@@ -439,6 +439,9 @@ void exl3_gemm_tc_kernel(const TcParams P)
 //     pair (the peer's warp 1) tells the first CTA "my x~ and my columns are ready" with a single,
 //     relaxed remote arrival per step (see mbar_arrive_cluster);
 //   * one lane of a decode warp polls for the free stage, the other 31 take its word;
+//   * two threads issue the MMAs, one per 128-token sub-tile (each sub-tile has its own
+//     accumulator, so the two streams need no order between them); both commit on the stage's
+//     barrier, which therefore counts two arrivals where a CTA has two sub-tiles;
 //   * tensor memory is allocated and freed by warp 0 of both CTAs with the cta_group::2 forms.
 // ------------------------------------------------------------------------------------------
 constexpr int T2_SUB = 2;                                  // 128-token sub-tiles per CTA
