@@ -905,8 +905,11 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
     }
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    // pair form (two CTAs per 256-column block) for every weight it can tile and more than 256 tokens
-    if (g_tc_pair && n % 256 == 0 && (M > 256 || g_tc_pair >= 2))
+    // pair form (two CTAs per 256-column block) for every weight it can tile. That includes
+    // batches of 17..256 tokens, where the second CTA of a pair may hold no token at all and only
+    // contributes its half of the decode: 64 tokens x 14336 x 4096 0.198 -> 0.134 ms, 256 tokens x
+    // 4096 x 14336 0.128 -> 0.059 ms against the single-CTA form.
+    if (g_tc_pair && n % 256 == 0)
     {
         // 256 token rows per CTA amortise the decode best, but a pair's k loop takes about as long
         // with 128: where the 128-row grid still fits one wave of CTA pairs it halves the time
@@ -969,9 +972,9 @@ AMP_API int amp_lab_tc_dbg(long long* out)
 #endif
 
 // Chooses between the single-CTA and the pair (cta_group::2) form of the prefill GEMM: 0 = never
-// the pair form, 1 = by shape (default: pairs whenever n is a multiple of 256 and M > 256, 128-token
-// CTAs while that grid fits one wave, 256-token CTAs beyond), 2 / 3 = pairs of 256- / 128-token
-// CTAs whenever n is a multiple of 256 (tests). Returns the previous setting.
+// the pair form, 1 = by shape (default: pairs whenever n is a multiple of 256, 128-token CTAs while
+// that grid fits one wave, 256-token CTAs beyond), 2 / 3 = pairs of 256- / 128-token CTAs whenever
+// n is a multiple of 256 (tests). Returns the previous setting.
 AMP_API int amp_exl3_set_gemm_pair(int mode)
 {
     const int old = g_tc_pair;

@@ -90,8 +90,8 @@ int amp_exl3_gemm_bf16(const void* A, const void* trellis, void* C, const void* 
 
 /*
  * Form of the prefill GEMM: 0 = one CTA per tile only, 1 = by shape (default: CTA pairs with
- * tcgen05 cta_group::2 whenever n is a multiple of 256 and m > 256: 256 tokens x 256 columns per
- * pair while that grid fits one wave, 512 tokens beyond; single CTAs otherwise), 2 / 3 = pairs of
+ * tcgen05 cta_group::2 whenever n is a multiple of 256: 256 tokens x 256 columns per pair while
+ * that grid fits one wave, 512 tokens beyond; single CTAs otherwise), 2 / 3 = pairs of
  * 512 / 256 tokens whenever n is a multiple of 256 (for tests). Returns the previous setting. No
  * counterpart in the reference.
  */
