@@ -38,6 +38,7 @@
 // expiry the status word is set, every role leaves its loop and the CTA still frees its tensor
 // memory.
 #include "exl3_gemv_kernel.cuh"
+#include "exl3_gemv_host.h"
 #include "host_common.h"
 
 namespace amp {
@@ -651,6 +652,10 @@ void exl3_gemm_tc2_kernel(const TcParams P)
         if (lane == 0)
         {
             int s = 0; uint32_t ph = 1;                    // stage, parity of "freed for the (use)-th time" - first pass needs no wait
+            // launched as a programmatic dependent of the rotation kernel: everything up to here
+            // (tensor-memory allocation, barriers, the decode warps' first weight copies) ran under
+            // that kernel; its output is read from here on
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int i = 0; i < ksteps && ok; ++i)
             {
                 if (i >= S) wait_bar_spin(&st_free[s], ph);
@@ -929,11 +934,13 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
             cfg.blockDim = dim3(T2_THREADS, 1, 1);
             cfg.dynamicSmemBytes = smem2;
             cfg.stream = stream;
-            cudaLaunchAttribute attr[1];
+            cudaLaunchAttribute attr[2];
             attr[0].id = cudaLaunchAttributeClusterDimension;
             attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[1].val.programmaticStreamSerializationAllowed = 1;
             cfg.attrs = attr;
-            cfg.numAttrs = 1;
+            cfg.numAttrs = g_pdl ? 2 : 1;
             return cuda_rc(cudaLaunchKernelEx(&cfg, fn2, P), "exl3_gemm_tc2 launch");
         }
     }

@@ -116,6 +116,10 @@ __global__ __launch_bounds__(256)
 void had_tiled_kernel(const void* __restrict__ in, __half* __restrict__ out, const __half* __restrict__ pre,
                       long chunks, int chunks_per_row, long M, float r_scale)
 {
+    // the GEMM that consumes this kernel's output may be scheduled from now on: it allocates its
+    // tensor memory and starts its weight stream under this kernel, and waits (griddepcontrol.wait
+    // in its fetch thread) before it reads the first rotated row
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const long chunk = (long) blockIdx.x * 8 + (threadIdx.x >> 5);
     if (chunk >= chunks) return;
