@@ -433,8 +433,8 @@ void exl3_gemm_tc_kernel(const TcParams P)
 //     thread costs a few hundred cycles through the busy shared-memory pipe. So a stage holds the
 //     x~ tile AND the weight tile of a k step and is freed by ONE tcgen05.commit that arrives in
 //     both CTAs; the thread waits on two local barriers per step and polls the next step's
-//     barriers (non-blocking) before it issues this step's MMAs, so that the answer is there when
-//     it comes round;
+//     barriers (non-blocking) before it issues this step's MMAs, so that the answer is there by
+//     the time it reaches that step;
 //   * decode warps arrive on a barrier of their own CTA. A remote arrival with cluster-scope
 //     release took 1000-2000 cycles (it waits for what the SM has in flight); one relay thread per
 //     pair (the peer's warp 1) tells the first CTA "my x~ and my columns are ready" with a single,
@@ -511,7 +511,7 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar)
 // step's two barriers go out first, then the four MMAs of the 128-token sub-tile (k = 16 each:
 // the descriptors advance by 32 bytes = 2 units), and only then are the polls' predicates turned
 // into values. Written as one asm block because a predicate cannot leave one:
-// with the polls in blocks of their own the thread sat out each poll's round trip through the
+// with the polls in blocks of their own the thread sat out each poll's latency through the
 // shared-memory pipe before it issued the first MMA.
 #define AMP_UMMA2(d, a, b, p) "tcgen05.mma.cta_group::2.kind::f16 [" d "], " a ", " b ", %5, {%10, %10, %10, %10, %10, %10, %10, %10}, " p ";\n\t"
 #define AMP_UMMA2_HEAD \
