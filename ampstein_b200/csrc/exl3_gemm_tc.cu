@@ -805,12 +805,16 @@ void exl3_gemm_tc2_kernel(const TcParams P)
     __syncthreads();
     const bool all_ok = !s_bad;
 
-    float* tile = reinterpret_cast<float*>(smem);        // [128][132] fp32, reuses the pipeline stages
+    // two [128][132] fp32 tiles in the pipeline's stages, used alternately: a warp that has
+    // finished the rows of one pass goes straight on to unload the next accumulator block into
+    // the other tile, one block-wide barrier per pass
     constexpr int TP = 132;
     const int ew = warp - 2;
+    int pass = 0;
     for (int sub = 0; sub < nsub; ++sub)
-    for (int hb = 0; hb < 2; ++hb)                       // the two 128-column Hadamard blocks of the pair's 256 columns
+    for (int hb = 0; hb < 2; ++hb, ++pass)               // the two 128-column Hadamard blocks of the pair's 256 columns
     {
+        float* tile = reinterpret_cast<float*>(smem) + (pass & 1) * (TC_BM * TP);
         if (all_ok && dec_warp)
         {
             const int lg = warp & 3, ch = ew >> 2;
@@ -860,7 +864,6 @@ void exl3_gemm_tc2_kernel(const TcParams P)
                 }
             }
         }
-        __syncthreads();
     }
 
     if (t == 0 && !all_ok) atomicExch(P.status, 1);
