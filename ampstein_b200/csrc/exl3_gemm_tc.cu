@@ -62,14 +62,6 @@ __host__ __device__ constexpr int tc_smem_bytes(int K)
 constexpr unsigned TC_SPIN_LIMIT = 1u << 22;   // try_wait polls before a wait is declared lost
 
 __device__ int g_tc_status;
-#ifdef AMP_LAB_TCSTAMP
-__device__ long long g_tc_dbg[64 * 8];
-#define TC_STAMP(i, j) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (i) < 64) g_tc_dbg[(i) * 8 + (j)] = clock64(); } while (0)
-#define TC_STAMP_D(i, j) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (i) < 64 && (warp == 2 || warp == 10) && lane == 0) g_tc_dbg[(i) * 8 + (j)] = clock64(); } while (0)
-#else
-#define TC_STAMP(i, j) do { } while (0)
-#define TC_STAMP_D(i, j) do { } while (0)
-#endif
 
 struct TcParams
 {
@@ -256,11 +248,8 @@ void exl3_gemm_tc_kernel(const TcParams P)
             for (int i = 0; i < ksteps && ok; ++i)
             {
                 const int sa = i % TC_A_SLOTS, sb = i % TC_B_STAGES;
-                TC_STAMP(i, 0);
                 wait_bar(&a_full[sa], (uint32_t) ((i / TC_A_SLOTS) & 1));
-                TC_STAMP(i, 1);
                 wait_bar(&b_full[sb], (uint32_t) ((i / TC_B_STAGES) & 1));
-                TC_STAMP(i, 2);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // descriptors advance by byte offset >> 4 in their low (address) field
@@ -273,7 +262,6 @@ void exl3_gemm_tc_kernel(const TcParams P)
                 umma_commit(&a_free[sa]);                   // arrive when these MMAs have read their operands
                 umma_commit(&b_free[sb]);
                 if (i == ksteps - 1) umma_commit(&bar_done);
-                TC_STAMP(i, 3);
             }
         }
         __syncwarp();
@@ -302,7 +290,6 @@ void exl3_gemm_tc_kernel(const TcParams P)
         int pslot = 0;
         for (int i = grp; i < ksteps && ok; i += 2)
         {
-            TC_STAMP_D(i, 4);
             cp_async_wait_n<PS - 2>();                  // this lane's words of step i have landed
             uint32_t w[K];
             load_chunk_s<K>(pring + pslot * SLOT, w);
@@ -330,9 +317,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
             decode_r(std::integral_constant<int, 2>()); decode_r(std::integral_constant<int, 3>());
 
             const int sb = i % TC_B_STAGES;
-            TC_STAMP_D(i, 5);
             if (i >= TC_B_STAGES) wait_bar_warp(&b_free[sb], (uint32_t) (((i / TC_B_STAGES) - 1) & 1));
-            TC_STAMP_D(i, 6);
             if (!ok) break;
             unsigned char* b = b_base + sb * TC_B_BYTES;
             const int ncol = dw * 16 + gq;
@@ -344,7 +329,6 @@ void exl3_gemm_tc_kernel(const TcParams P)
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&b_full[sb]);
-            TC_STAMP_D(i, 7);
         }
     }
 
@@ -686,11 +670,8 @@ void exl3_gemm_tc2_kernel(const TcParams P)
             uint32_t ra = 0, rb = 0;                       // this step's barriers were seen complete by the look-ahead poll
             for (int i = 0; i < ksteps && ok; ++i)
             {
-                if (which == 0) TC_STAMP(i, 0);
                 if (!ra) wait_bar_spin(&a_land[s], ph);
-                if (which == 0) TC_STAMP(i, 1);
                 if (!rb) wait_bar_spin(&b_full[s], ph);
-                if (which == 0) TC_STAMP(i, 2);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // Look-ahead: the NEXT step's barriers are polled (non-blocking) in the same
@@ -706,7 +687,6 @@ void exl3_gemm_tc2_kernel(const TcParams P)
                 if (has1) umma2_step(tmem + 256, da + SUB_DESC, db, IDESC, acc, na, nbar, ph2, ra, rb);
                 umma2_commit_both(&st_free[s]);            // the stage is free in BOTH CTAs once every issuer's MMAs have read it
                 if (i == ksteps - 1) umma2_commit_both(&bar_done);
-                if (which == 0) TC_STAMP(i, 3);
                 if (++s == S) { s = 0; ph ^= 1; }
             }
         };
@@ -754,7 +734,6 @@ void exl3_gemm_tc2_kernel(const TcParams P)
         int pslot = 0;
         for (int i = grp; i < ksteps && ok; i += 2)
         {
-            TC_STAMP_D(i, 4);
             uint32_t w[K];
             cp_async_wait_n<PS - 2>();
             load_chunk_s<K>(pring + pslot * SLOT, w);
@@ -772,9 +751,7 @@ void exl3_gemm_tc2_kernel(const TcParams P)
             decode_r(std::integral_constant<int, 2>()); decode_r(std::integral_constant<int, 3>());
 
             const int sb = i % S;
-            TC_STAMP_D(i, 5);
             if (i >= S) wait_bar_warp(&st_free[sb], (uint32_t) (((i / S) - 1) & 1));
-            TC_STAMP_D(i, 6);
             if (!ok) break;
             unsigned char* b = b_base + sb * T2_B_BYTES;
             const int ncol = dw * 16 + gq;
@@ -785,7 +762,6 @@ void exl3_gemm_tc2_kernel(const TcParams P)
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&b_full[sb]);
-            TC_STAMP_D(i, 7);
             {
                 // refill the slot read in this warp's previous step with the words of its step PS - 1
                 // ahead. Issued after the arrival: the arrival's release must not find this warp's
@@ -974,12 +950,6 @@ AMP_API int amp_exl3_gemm_status(int* out)
     return 0;
 }
 
-#ifdef AMP_LAB_TCSTAMP
-AMP_API int amp_lab_tc_dbg(long long* out)
-{
-    return (int) cudaMemcpyFromSymbol(out, g_tc_dbg, sizeof(long long) * 64 * 8);
-}
-#endif
 
 // Chooses between the single-CTA and the pair (cta_group::2) form of the prefill GEMM: 0 = never
 // the pair form, 1 = by shape (default: pairs whenever n is a multiple of 256, 128-token CTAs while

@@ -2,6 +2,7 @@
 // C-ABI entry points amp_exl3_gemv and amp_exl3_gemm (the launcher the reference's exl3_gemm,
 // vendor/exl3/exllamav3_ext/quant/exl3_gemm.cu:114-349, maps onto).
 #include "exl3_gemv_kernel.cuh"
+#include "exl3_gemv_tc.cuh"
 #include "host_common.h"
 #include "exl3_gemv_host.h"
 #include <mutex>
@@ -39,6 +40,22 @@ static gemv_fn gemv_kernel_for(int K, int cb, int MB, int mode)
         case 6: return gemv_kernel_k6(cb, MB, mode);
         case 7: return gemv_kernel_k7(cb, MB, mode);
         case 8: return gemv_kernel_k8(cb, MB, mode);
+    }
+    return nullptr;
+}
+
+static gemv_fn gemv_tc_kernel_for(int K, int cb, int ar)
+{
+    switch (K)
+    {
+        case 1: return gemv_tc_kernel_k1(cb, ar);
+        case 2: return gemv_tc_kernel_k2(cb, ar);
+        case 3: return gemv_tc_kernel_k3(cb, ar);
+        case 4: return gemv_tc_kernel_k4(cb, ar);
+        case 5: return gemv_tc_kernel_k5(cb, ar);
+        case 6: return gemv_tc_kernel_k6(cb, ar);
+        case 7: return gemv_tc_kernel_k7(cb, ar);
+        case 8: return gemv_tc_kernel_k8(cb, ar);
     }
     return nullptr;
 }
@@ -84,6 +101,11 @@ static int workspace_region(int dev, int** counters, float** scratch)
 // without dependent launch; with the padding it runs 3 % faster (B200, inside CUDA graphs).
 int g_pdl = 1;
 int g_cluster = 1;        // cluster form of the partial-sum exchange
+// 1: dense / bundle launches of up to eight rows run on the tensor-memory kernel
+// (exl3_gemv_tc.cuh) instead of the mma.sync kernel. Off by default: measured slower on B200 (its
+// hand-over of decoded weights to the tensor core costs more instructions than the eight issue
+// cycles per mma.sync it saves); kept for A/B runs (amp_exl3_set_gemv_tc).
+int g_gemv_tc = 0;
 // (with more than 16 units per CTA the grid of 8 x blocks CTAs is too coarse: measured slower)
 constexpr int GEMV_CLUSTER = 8, GEMV_CLUSTER_MAX_M = 4, GEMV_CLUSTER_MAX_UNITS = 16;
 
@@ -119,7 +141,8 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     const DevInfo& D = dev_info(dev);
 
     const int MB = m <= 8 ? 1 : 2;
-    gemv_fn fn = gemv_kernel_for(K, A.cb, MB, A.mode);
+    const bool tc = !A.mode && m <= TCV_MAX_M && g_gemv_tc;
+    gemv_fn fn = tc ? gemv_tc_kernel_for(K, A.cb, A.ar.N != 0) : gemv_kernel_for(K, A.cb, MB, A.mode);
     if (!fn) return fail(AMP_E_UNSUPPORTED, "exl3_gemv: no kernel for K=%d cb=%d", K, A.cb);
 
     // x~ rows resident at a time: at most 16 KB of shared memory (whole segments for small
@@ -137,13 +160,17 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
                     "exl3_gemv: xgroups must be a multiple of 4, at most %d", GEMV_XCHUNK_MAX / 64);
         xcap = A.force_xgroups;
     }
+    // tensor-memory kernel: x~ in chunks of four 64-row groups (two 128-row transforms), two buffers
+    const int tc_xg = G < 4 ? G : 4;
     GemvSmem L = gemv_smem_layout(K, m, xcap);
+    if (tc) L.total = tcv_smem_layout(K, m, tc_xg).total;
     AMP_REQUIRE(L.total <= D.smem_optin, "exl3_gemv: shared memory layout does not fit (%d bytes)", L.total);
     const int smem_per_sm = D.smem_optin + 1024;                       // opt-in limit excludes 1 KB per CTA
     // CTAs per SM: the decode is bound by the rate of the integer pipes, not by latency, so
     // three 4-warp CTAs per SM run as fast as six (measured) and halve the partial sums that
     // have to be exchanged
-    const int reg_ctas = (MB == 1 ? 3 : 4);
+    // (the tensor-memory kernel: four CTAs of 128 tensor-memory columns fill an SM's 512)
+    const int reg_ctas = tc ? 4 : (MB == 1 ? 3 : 4);
     int ctas_per_sm = smem_per_sm / (L.total + 1024);
     if (ctas_per_sm > reg_ctas) ctas_per_sm = reg_ctas;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
@@ -196,6 +223,11 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
         if (need < xgroups) xgroups = (int) need;
     }
     L = gemv_smem_layout(K, m, xgroups, cluster);
+    if (tc)
+    {
+        xgroups = tc_xg;
+        L.total = tcv_smem_layout(K, m, tc_xg, cluster).total;
+    }
     // Ask for enough shared memory that exactly ctas_per_sm CTAs fit on an SM. The grid is sized
     // for that many; if an SM could take one more, a dependent grid that starts while this one
     // drains would pile four CTAs on the SMs that free up first and leave others with two.
@@ -230,7 +262,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned) ncta, 1, 1);
-    cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
+    cfg.blockDim = dim3(tc ? TCV_THREADS : GEMV_THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -358,6 +390,15 @@ AMP_API int amp_exl3_gemv_status(int* out)
     if (cudaError_t e = cudaMemcpyToSymbol(g_gemv_status, &zero, sizeof(int))) return cuda_rc(e, "status clear");
     if (out) *out = v;
     return 0;
+}
+
+// Tensor-memory form of the decode GEMV for dense / bundle launches of up to eight rows (off by
+// default: the mma.sync kernel is faster). Returns the old setting.
+AMP_API int amp_exl3_set_gemv_tc(int enable)
+{
+    const int old = g_gemv_tc;
+    g_gemv_tc = enable ? 1 : 0;
+    return old;
 }
 
 // Programmatic dependent launch of the decode kernels (on by default): returns the old setting.

@@ -1,6 +1,7 @@
 // Kernel instances of the trellis-decode GEMV for one bitrate; compiled once per K with
 // -DAMP_GEMV_K=<1..8> so the eight translation units build in parallel.
 #include "exl3_gemv_kernel.cuh"
+#include "exl3_gemv_tc.cuh"
 
 #ifndef AMP_GEMV_K
 #error "compile with -DAMP_GEMV_K=<bits>"
@@ -28,6 +29,19 @@ gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB, int mode)
     if (cb < 0 || cb > 2 || MB < 1 || MB > 2 || mode < 0 || mode > 2) return nullptr;
     if (mode) return MB == 1 ? moe[cb][mode - 1] : nullptr;
     return fn[cb][MB - 1];
+}
+
+// tensor-memory form (dense / bundle launches of up to eight rows)
+gemv_fn AMP_CAT(gemv_tc_kernel_k, AMP_GEMV_K)(int cb, int ar)
+{
+    static const gemv_fn fn[3][2] =
+    {
+        { exl3_gemv_tc_kernel<AMP_GEMV_K, 0, 0>, exl3_gemv_tc_kernel<AMP_GEMV_K, 0, 1> },
+        { exl3_gemv_tc_kernel<AMP_GEMV_K, 1, 0>, exl3_gemv_tc_kernel<AMP_GEMV_K, 1, 1> },
+        { exl3_gemv_tc_kernel<AMP_GEMV_K, 2, 0>, exl3_gemv_tc_kernel<AMP_GEMV_K, 2, 1> },
+    };
+    if (cb < 0 || cb > 2) return nullptr;
+    return fn[cb][ar ? 1 : 0];
 }
 
 }  // namespace amp

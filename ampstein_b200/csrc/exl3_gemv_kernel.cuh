@@ -114,9 +114,6 @@ struct GemvParams
     int* status;                // device status word (the kernel has no waits that can run out; kept for the ABI)
     GemvMoe moe;                // grouped-expert modes only
     GemvAr ar;                  // MODE 0, fp16 output only
-#ifdef AMP_LAB_STAMP
-    unsigned long long* stamps; // [gridDim.x][4] globaltimer at entry, x~ ready, decode done, exit
-#endif
 };
 
 // A ring slot holds one unit of one warp: four tile rows (the 64-row group) of GEMV_NT adjacent
@@ -265,23 +262,9 @@ __device__ __forceinline__ void decode_mma_r(const uint32_t (&w)[K], uint32_t pr
                                              float (&acc0)[MB][4], float (&acc1)[MB][4])
 {
     uint32_t s[8], a[8];
-#ifdef AMP_LAB_NODECODE
-    #pragma unroll
-    for (int j = 0; j < 8; ++j) a[j] = w[R % K] + j + prev;
-#else
     states8<K, R>(w, prev, s);
     #pragma unroll
     for (int j = 0; j < 8; ++j) a[j] = a_word<CB>(s[j]);
-#endif
-#ifdef AMP_LAB_NOMMA
-    // keep the decoded words alive without issuing anything
-    asm volatile("" :: "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]));
-#elif defined(AMP_LAB_HALFMMA)
-    #pragma unroll
-    for (int mb = 0; mb < MB; ++mb)
-        mma_16816(acc0[mb], a[0], a[4], a[1], a[5], xb[mb][2 * R], xb[mb][2 * R + 1]);
-    asm volatile("" :: "r"(a[2]), "r"(a[6]), "r"(a[3]), "r"(a[7]));
-#else
     #pragma unroll
     for (int mb = 0; mb < MB; ++mb)
     {
@@ -290,7 +273,6 @@ __device__ __forceinline__ void decode_mma_r(const uint32_t (&w)[K], uint32_t pr
         mma_16816(acc0[mb], a[0], a[4], a[1], a[5], xb[mb][2 * R], xb[mb][2 * R + 1]);
         mma_16816(acc1[mb], a[2], a[6], a[3], a[7], xb[mb][2 * R + 8], xb[mb][2 * R + 9]);
     }
-#endif
 }
 
 // thread-block cluster helpers: rank of this CTA, address of a shared-memory location in another
@@ -319,17 +301,6 @@ __device__ __forceinline__ void cluster_sync_all()
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-#ifdef AMP_LAB_STAMP
-__device__ __forceinline__ unsigned long long lab_now()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define LAB_STAMP(i) do { if (threadIdx.x == 0) P.stamps[blockIdx.x * 4 + (i)] = lab_now(); } while (0)
-#else
-#define LAB_STAMP(i) do { } while (0)
-#endif
 
 __device__ __forceinline__ void pdl_launch_dependents()
 {
@@ -419,7 +390,6 @@ void exl3_gemv_kernel(const GemvParams P)
     constexpr int PIECES = 4 * ROWP;                   // ... and per unit
     constexpr int NP = (PIECES + 31) / 32;             // copy instructions per unit and lane
 
-    LAB_STAMP(0);
     // Dependent launch: the next kernel's CTAs may be scheduled from now on. The launch asks for
     // so much shared memory that an SM holds exactly this grid's share of CTAs, so they only move
     // in as CTAs of this grid leave -- one for one, which keeps the next grid evenly spread --
@@ -497,11 +467,7 @@ void exl3_gemv_kernel(const GemvParams P)
     // step with the unit index.
     auto issue = [&]()
     {
-#ifndef AMP_LAB_NOLOAD
         if (iu < u1)
-#else
-        if (iu < 0)
-#endif
         {
             #pragma unroll
             for (int j = 0; j < NP; ++j)
@@ -758,7 +724,6 @@ void exl3_gemv_kernel(const GemvParams P)
             }
             __syncthreads();
 
-            if (useg == u0 && cg0 == (g0 & ~1)) LAB_STAMP(1);
             const int c0 = max(cg0, g0);                // first group of the chunk that belongs to the range
             if constexpr (CB == 2)
             {
@@ -814,7 +779,6 @@ void exl3_gemv_kernel(const GemvParams P)
         }
 
 
-        if (useg + (g1 - g0) >= u1) LAB_STAMP(2);
 
         // ---- segment done: every lane holds final sums of this CTA's rows for its columns ----
         const bool whole = (g0 == 0 && g1 == G);       // this CTA owns every row of the block
@@ -1003,7 +967,6 @@ void exl3_gemv_kernel(const GemvParams P)
         useg += g1 - g0;
     }
     cp_async_wait_n<0>();
-    LAB_STAMP(3);
 }
 
 typedef void (*gemv_fn)(const GemvParams);

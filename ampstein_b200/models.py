@@ -44,6 +44,51 @@ class LinearEXL3:
         return self.trellis.numel() * 2
 
 
+def split_n(total, unit, weights):
+    """Cut `total` (a multiple of `unit`) into per-rank [start, length] ranges proportional to
+    `weights` by largest remainder (reference: src/ucode/ampstein/qwen35_tp.uc:40-72)."""
+    n, tot = total // unit, float(sum(weights))
+    cnt, rem, used = [], [], 0
+    for g, w in enumerate(weights):
+        exact = n * w / tot
+        c = int(exact)
+        cnt.append(c)
+        rem.append((exact - c, g))
+        used += c
+    rem.sort(key=lambda a: (-a[0], a[1]))
+    k = 0
+    while used < n:
+        cnt[rem[k % len(weights)][1]] += 1
+        k += 1
+        used += 1
+    out, at = [], 0
+    for c in cnt:
+        out.append((at * unit, c * unit))
+        at += c
+    return out
+
+
+def cols(lin, ranges):
+    """Column-parallel shard: output columns ([start, length] pairs, 256-aligned) concatenated;
+    suh whole, svh sliced (reference: models.uc cols(), :537-545)."""
+    for n0, w in ranges:
+        if n0 % 16 or w % 16:
+            raise ValueError("models.cols: ranges must be multiples of 16 columns")
+    tr = torch.cat([lin.trellis[:, n0 // 16:(n0 + w) // 16] for n0, w in ranges], dim=1).contiguous()
+    svh = torch.cat([lin.svh[n0:n0 + w] for n0, w in ranges]).contiguous()
+    return LinearEXL3(tr, lin.suh, svh, mul1=lin.mul1, mcg=lin.mcg)
+
+
+def rows(lin, k0, klen):
+    """Row-parallel shard: input rows [k0, k0 + klen), 128-aligned, with the matching suh slice
+    and the whole svh; the shards' outputs SUM to the full product (reference: models.uc rows(),
+    :547-562)."""
+    if k0 % 128 or klen % 128 or k0 + klen > lin.in_features:
+        raise ValueError("models.rows: range [%d, %d] not 128-aligned/in bounds" % (k0, klen))
+    tr = lin.trellis[k0 // 16:(k0 + klen) // 16].clone()
+    return LinearEXL3(tr, lin.suh[k0:k0 + klen].clone(), lin.svh, mul1=lin.mul1, mcg=lin.mcg)
+
+
 def _bundle_check(linears):
     a = linears[0]
     for i, w in enumerate(linears[1:], 1):

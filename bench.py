@@ -549,10 +549,15 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "moe"],
                     help="decode (default, the headline step) or a secondary one-GPU workload: the prefill GEMM / the fused decode MoE")
     ap.add_argument("--tokens", type=int, default=1, choices=[1, 4, 16], help="tokens per step of --workload moe")
+    ap.add_argument("--tmem-gemv", action="store_true",
+                    help="A/B: run the decode GEMVs on the tensor-memory (tcgen05) kernel instead of the mma.sync kernel")
     ap.add_argument("--layers", type=int, default=LAYERS,
                     help="layers of the stack (default: the full 32; fewer only for a small profiler capture)")
     args = ap.parse_args()
     LAYERS = args.layers
+    if args.tmem_gemv and args.impl != "reference":
+        from ampstein_b200 import _lib
+        _lib.lib().amp_exl3_set_gemv_tc(1)
     if args.impl == "reference":
         if args.steps > 5:
             args.steps = 5                 # each step is seconds of CPU work

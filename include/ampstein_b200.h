@@ -212,9 +212,20 @@ long amp_exl3_moe_coop_ctr_len(long slots_max);
 int amp_exl3_set_pdl(int enable);
 
 /*
+ * Which kernel serves dense and bundle GEMV launches of up to eight rows: 0 (default) the
+ * register-operand mma.sync kernel, 1 the tensor-memory kernel (decoded weights written to tensor
+ * memory with tcgen05.st, dot products by tcgen05.mma with the weights as the A operand). Both
+ * give the same results to rounding; the mma.sync kernel is the faster one on B200 and always
+ * serves 9..16 rows and the grouped expert modes. For A/B measurements. Returns the previous
+ * setting. The reference has no counterpart (its kernels use mma.sync only,
+ * Q/exl3_gemv_kernel.cuh:396-397).
+ */
+int amp_exl3_set_gemv_tc(int enable);
+
+/*
  * Reads and clears the current device's GEMV status word (non-zero = a kernel reported an
- * internal error). The decode kernels contain no spin-waits, so it stays zero; it is kept so
- * that tests can assert it. Synchronises; not for the hot path.
+ * internal error: a bounded wait on one of the tensor-memory kernel's hand-over barriers ran out).
+ * Synchronises; not for the hot path.
  */
 int amp_exl3_gemv_status(int* out);
 

@@ -1,0 +1,94 @@
+// C-ABI shim around the UNMODIFIED reference GEMM / GEMV / fused decode MoE entry points
+// (vendored exllamav3 under the reference tree's vendor/exl3/exllamav3_ext/quant/), compiled from
+// where they lie by Makefile.ref into oracle/_ref/libexl3_ref_gemm.so. Test infrastructure: a
+// second oracle for the GPU tests and the bar the benchmarks time this library against on the
+// same B200. Raw device pointers in, wrapped into at::Tensor views without copying. The
+// reference's tensor-parallel all-reduce kernel is left out on purpose: its wait ends in a trap.
+#include <ATen/ATen.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cstdint>
+#include <cstdio>
+#include <exception>
+
+// reference entry points (global namespace): quant/exl3_gemm.cuh, quant/exl3_moe_coop.cuh
+int exl3_gemm(const at::Tensor& A, const at::Tensor& B, at::Tensor& C, const c10::optional<at::Tensor>& suh,
+              const c10::optional<at::Tensor>& A_had, const c10::optional<at::Tensor>& svh, int force_shape_idx,
+              bool mcg, bool mul1, int force_num_sms);
+
+void exl3_moe_coop(const at::Tensor& x, const at::Tensor& sel, const at::Tensor& rw, int min_expert, int max_expert, int Hi,
+                   const at::Tensor& g_trellis, const at::Tensor& g_suh, const at::Tensor& g_svh,
+                   const at::Tensor& u_trellis, const at::Tensor& u_suh, const at::Tensor& u_svh,
+                   const at::Tensor& d_trellis, const at::Tensor& d_suh, const at::Tensor& d_svh,
+                   const c10::optional<at::Tensor>& g_bias, const c10::optional<at::Tensor>& u_bias,
+                   const c10::optional<at::Tensor>& d_bias, float Kg, float Ku, float Kd, bool mcg, bool mul1, int act,
+                   float act_limit, bool gated, at::Tensor& had_g, at::Tensor& had_u, at::Tensor& gu_g, at::Tensor& gu_u,
+                   at::Tensor& act_out, at::Tensor& d_out, at::Tensor& ctr, at::Tensor& out,
+                   const c10::optional<at::Tensor>& sh_out, const c10::optional<at::Tensor>& sh_gate_w,
+                   const c10::optional<at::Tensor>& bits_g, const c10::optional<at::Tensor>& bits_u,
+                   const c10::optional<at::Tensor>& bits_d);
+
+static at::Tensor view(void* p, at::IntArrayRef shape, at::ScalarType t, int dev)
+{
+    return at::from_blob(p, shape, at::TensorOptions().dtype(t).device(at::kCUDA, dev));
+}
+
+// C = had(A * suh) @ W -> had(.) * svh through the reference's dispatch (GEMV kernel, int8 GEMV
+// or the block-pipelined GEMM, autotuned on first use). Returns the reference's shape index
+// (90 = its GEMV kernel) or -1 on an exception. a_had: scratch, same shape as x.
+extern "C" int ref_exl3_gemm(void* x, void* trellis, void* c, void* suh, void* a_had, void* svh,
+                             int m, int k, int n, int K, int cb, int c_fp32, int dev)
+{
+    try
+    {
+        c10::cuda::CUDAGuard guard(dev);
+        auto A = view(x, {m, k}, at::kHalf, dev);
+        auto B = view(trellis, {k / 16, n / 16, 16 * K}, at::kShort, dev);
+        auto C = view(c, {m, n}, c_fp32 ? at::kFloat : at::kHalf, dev);
+        c10::optional<at::Tensor> su = view(suh, {k}, at::kHalf, dev);
+        c10::optional<at::Tensor> ah = view(a_had, {m, k}, at::kHalf, dev);
+        c10::optional<at::Tensor> sv = view(svh, {n}, at::kHalf, dev);
+        return exl3_gemm(A, B, C, su, ah, sv, -1, cb == 1, cb == 2, 0);
+    }
+    catch (const std::exception& e) { fprintf(stderr, "ref_shim: %s\n", e.what()); return -1; }
+}
+
+struct ref_moe_args
+{
+    void* x; int bsz; int H; int x_stride;
+    void* sel; void* rw; int topk;
+    int experts; int Hi, I, Ho;
+    void* tables[9];            // g_trellis, g_suh, g_svh, u_*, d_* : int64 device arrays (experts entries)
+    int K; int cb; int act; float act_limit; int gated;
+    void* had_g; void* had_u; void* gu_g; void* gu_u; void* act_out; void* d_out;   // fp16 scratch (slots_max rows), d_out fp32
+    int slots_max; int rows_max;
+    void* ctr; long ctr_len;
+    void* out; int H_out;
+};
+
+extern "C" int ref_exl3_moe_coop(const ref_moe_args* a, int dev)
+{
+    try
+    {
+        c10::cuda::CUDAGuard guard(dev);
+        auto x = view(a->x, {a->bsz, a->H}, at::kHalf, dev);
+        auto sel = view(a->sel, {a->bsz, a->topk}, at::kLong, dev);
+        auto rw = view(a->rw, {a->bsz, a->topk}, at::kHalf, dev);
+        at::Tensor t[9];
+        for (int i = 0; i < 9; ++i) t[i] = view(a->tables[i], {a->experts}, at::kLong, dev);
+        auto had_g = view(a->had_g, {a->slots_max, a->Hi}, at::kHalf, dev);
+        auto had_u = view(a->had_u, {a->slots_max, a->Hi}, at::kHalf, dev);
+        auto gu_g = view(a->gu_g, {a->slots_max, a->I}, at::kHalf, dev);
+        auto gu_u = view(a->gu_u, {a->slots_max, a->I}, at::kHalf, dev);
+        auto act_out = view(a->act_out, {a->slots_max, a->I}, at::kHalf, dev);
+        auto d_out = view(a->d_out, {a->slots_max, a->Ho}, at::kFloat, dev);
+        auto ctr = view(a->ctr, {a->ctr_len}, at::kInt, dev);
+        auto out = view(a->out, {a->rows_max, a->H_out}, at::kFloat, dev);
+        c10::optional<at::Tensor> none;
+        exl3_moe_coop(x, sel, rw, -1, -1, a->Hi, t[0], t[1], t[2], t[3], t[4], t[5], t[6], t[7], t[8],
+                      none, none, none, (float) a->K, (float) a->K, (float) a->K, a->cb == 1, a->cb == 2, a->act,
+                      a->act_limit, a->gated != 0, had_g, had_u, gu_g, gu_u, act_out, d_out, ctr, out,
+                      none, none, none, none, none);
+        return 0;
+    }
+    catch (const std::exception& e) { fprintf(stderr, "ref_shim: %s\n", e.what()); return -1; }
+}
