@@ -9,15 +9,19 @@ O(1) in fp16 without extra kernels. A step streams 3.89 GB of packed weights, fa
 126 MB L2, so no cache flush is needed between steps.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--mode tp|replicas]
-    python bench.py --workload prefill | --workload moe [--tokens 1|4|16]      (secondary, one GPU)
+    python bench.py --workload tp5 [--batch 1|8]       (the 64-layer 5-bit tensor-parallel stack)
+    python bench.py --workload prefill | moe [--tokens 1|4|16] | issue        (secondary, one GPU)
 
-With N > 1 GPUs (one process per GPU under torchrun) the same stack is decoded tensor-parallel, as
-the reference shards it: q|k|v and gate|up column-parallel, o and down row-parallel, each followed
+With N > 1 GPUs (one process per GPU under torchrun) the stack is decoded tensor-parallel, as the
+reference shards it: q|k|v and gate|up column-parallel, o and down row-parallel, each followed
 by the fp16 all-reduce of the hidden state over NVLink (this library's kernel, inside the graph);
 lm_head is split by vocabulary. All ranks decode the same token, so the work is fixed as N grows
-(strong scaling). `--mode replicas` runs N independent copies of the 1-GPU step instead.
+(strong scaling). Before timing, every rank checks the fused o_proj / down_proj of layer 0 against
+the fp32 rank-order sum (rounded once) of the gathered partial products. `--mode replicas` runs N
+independent copies of the 1-GPU step instead.
 
-One JSON line on stdout (rank 0). `--impl reference` times the CPU restatement of the
+One JSON line on stdout (rank 0). The `--steps` block is repeated until at least a second has
+been timed and the median block is reported. `--impl reference` times the CPU restatement of the
 reference's reconstruct-then-matmul path (the reference has no CPU code of its own for this
 codebook) on the host cores, on a bounded sample of the same workload.
 """
@@ -36,25 +40,50 @@ sys.path.insert(0, ROOT)
 METRIC = "decode tok/s (8B-shape EXL3 4bpw stack)"
 UNIT = "tok/s"
 
-HIDDEN, KV, FFN, VOCAB, LAYERS = 4096, 1024, 14336, 128256, 32
-K_LAYER, K_HEAD = 4, 6
-# (name, in, out) of one layer, in launch order
-LAYER_LINEARS = [("q", HIDDEN, HIDDEN), ("k", HIDDEN, KV), ("v", HIDDEN, KV), ("o", HIDDEN, HIDDEN),
-                 ("gate", HIDDEN, FFN), ("up", HIDDEN, FFN), ("down", FFN, HIDDEN)]
+# hidden, q width, kv width, ffn, vocabulary (0: no lm_head), layers, bits per weight (layers, head)
+STACKS = {
+    "decode": dict(name="llama3-8b-shaped", hidden=4096, q=4096, kv=1024, ffn=14336, vocab=128256, layers=32, K=4, K_head=6),
+    "tp5": dict(name="64-layer dense 5 bpw (hidden 5120)", hidden=5120, q=6144, kv=1024, ffn=25600, vocab=0, layers=64, K=5, K_head=0),
+}
+MIN_TIMED_S = 1.0
 
 
-def algorithmic_bytes(m=1):
-    """Bytes a step must move: packed weights + suh/svh + activations in and out (no scratch)."""
+def layer_linears(S, rank=0, world=1):
+    """(name, in, out, in of the unsharded matrix) of one layer for a rank of a tensor-parallel
+    group: column-parallel q/k/v/gate/up, row-parallel o/down (reference:
+    src/ucode/ampstein/models.uc:527-562); attention by kv head (128 wide), the MLP in 256-column
+    units by largest remainder (src/ucode/ampstein/qwen35_tp.uc:40-79)."""
+    from ampstein_b200.models import split_n
+    h, q, kv, ffn = S["hidden"], S["q"], S["kv"], S["ffn"]
+    if world == 1:
+        fl = ffn
+    else:
+        if (kv // 128) % world or (q // 128) % world:
+            raise SystemExit("bench.py: %d kv heads do not split %d ways" % (kv // 128, world))
+        fl = split_n(ffn, 256, [1] * world)[rank][1]
+    ql, kl = q // world, kv // world
+    return [("q", h, ql, h), ("k", h, kl, h), ("v", h, kl, h), ("o", ql, h, q),
+            ("gate", h, fl, h), ("up", h, fl, h), ("down", fl, h, ffn)]
+
+
+def head_shape(S, rank=0, world=1):
+    if not S["vocab"]:
+        return None
+    blocks = S["vocab"] // 128
+    b0, b1 = blocks * rank // world, blocks * (rank + 1) // world
+    return (S["hidden"], (b1 - b0) * 128)
+
+
+def algorithmic_bytes(S, m=1, rank=0, world=1):
+    """Bytes a step must move on one GPU: packed weights + suh/svh + activations in and out."""
     total = 0
-    for _, k, n in LAYER_LINEARS:
-        total += k * n * K_LAYER // 8 + 2 * (k + n) + 2 * m * (k + n)
-    total *= LAYERS
-    total += HIDDEN * VOCAB * K_HEAD // 8 + 2 * (HIDDEN + VOCAB) + 2 * m * (HIDDEN + VOCAB)
+    for _, k, n, _ in layer_linears(S, rank, world):
+        total += k * n * S["K"] // 8 + 2 * (k + n) + 2 * m * (k + n)
+    total *= S["layers"]
+    hs = head_shape(S, rank, world)
+    if hs:
+        total += hs[0] * hs[1] * S["K_head"] // 8 + 2 * (hs[0] + hs[1]) + 2 * m * (hs[0] + hs[1])
     return total
-
-
-def total_weights():
-    return LAYERS * sum(k * n for _, k, n in LAYER_LINEARS) + HIDDEN * VOCAB
 
 
 # ------------------------------------------------------------------------------------------
@@ -99,32 +128,50 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(rows)}
 
 
-# ------------------------------------------------------------------------------------------
-# the GPU arm
-# ------------------------------------------------------------------------------------------
+def _peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        return {}
 
-def tp_shapes(rank, world):
-    """(name, in, out, in of the unsharded matrix) of one layer and the lm_head for a rank of a
-    tensor-parallel group: column-parallel q/k/v/gate/up, row-parallel o/down (reference:
-    src/ucode/ampstein/models.uc:527-562), lm_head by blocks of 128 vocabulary entries."""
-    layer = []
-    for name, k, n in LAYER_LINEARS:
-        if name in ("o", "down"):
-            layer.append((name, k // world, n, k))
+
+def timed_blocks(torch, fn, steps, stream=None, barrier=None, reduce_max=None, min_s=MIN_TIMED_S, max_blocks=400):
+    """Runs blocks of `steps` calls of fn, each bracketed by CUDA events on `stream`, until at
+    least min_s seconds have been timed; returns (median block ms, blocks, total ms)."""
+    stream = stream or torch.cuda.current_stream()
+    times = []
+    total = 0.0
+    while total < min_s * 1e3 and len(times) < max_blocks:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if barrier:
+            barrier()
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+        if barrier:
+            barrier()
         else:
-            layer.append((name, k, n // world, k))
-    blocks = VOCAB // 128
-    b0, b1 = blocks * rank // world, blocks * (rank + 1) // world
-    return layer, (HIDDEN, (b1 - b0) * 128)
+            torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if reduce_max:
+            ms = reduce_max(ms)              # the same value on every rank: all ranks stop together
+        times.append(ms)
+        total += ms
+    times.sort()
+    return times[len(times) // 2], len(times), total
 
 
-def build_stack(torch, device, seed, shapes=None):
-    """Distinct synthetic tensors for every linear of the stack (3.9 GB in all)."""
+# ------------------------------------------------------------------------------------------
+# the decode arm (1 GPU, replicas, or tensor parallel)
+# ------------------------------------------------------------------------------------------
+
+def build_stack(torch, device, seed, S, rank=0, world=1):
+    """Distinct synthetic tensors for every linear of the stack."""
     from ampstein_b200.models import LinearEXL3
     g = torch.Generator(device=device)
     g.manual_seed(seed)
-    layer_shapes = [(name, k, n, k) for name, k, n in LAYER_LINEARS] if shapes is None else shapes[0]
-    head_shape = (HIDDEN, VOCAB) if shapes is None else shapes[1]
 
     def make(k, n, K, k_full=None):
         trellis = torch.randint(-32768, 32768, (k // 16, n // 16, 16 * K), dtype=torch.int16,
@@ -135,12 +182,14 @@ def build_stack(torch, device, seed, shapes=None):
         svh = sgn(n) * (1.0 / (1.2437 * math.sqrt(k_full or k)))
         return LinearEXL3(trellis, suh, svh.to(torch.float16))
 
-    layers = [{name: make(k, n, K_LAYER, kf) for name, k, n, kf in layer_shapes} for _ in range(LAYERS)]
-    head = make(head_shape[0], head_shape[1], K_HEAD)
+    shapes = layer_linears(S, rank, world)
+    layers = [{name: make(k, n, S["K"], kf) for name, k, n, kf in shapes} for _ in range(S["layers"])]
+    hs = head_shape(S, rank, world)
+    head = make(hs[0], hs[1], S["K_head"]) if hs else None
     return layers, head
 
 
-def run_gpu(args):
+def run_decode(args, S):
     import torch
     import ampstein_b200  # noqa: F401  (raises if the CUDA library is missing)
     from ampstein_b200.models import DecodeGraph, Multi, Sliced
@@ -157,26 +206,24 @@ def run_gpu(args):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
 
-    m = 1
+    m = args.batch
+    H = S["hidden"]
     tp = world if (world > 1 and args.mode == "tp") else 1
-    if tp > 1 and ((HIDDEN // tp) % 128 or (KV // tp) % 128 or (FFN // tp) % 128):
-        raise SystemExit("bench.py: the stack does not shard %d ways in multiples of 128" % tp)
-    shapes = tp_shapes(rank, tp) if tp > 1 else None
-    layers, head = build_stack(torch, device, seed=1234 + rank, shapes=shapes)
-    vocab_local = head.out_features
+    shapes = {name: (k, n) for name, k, n, _ in layer_linears(S, rank if tp > 1 else 0, tp)}
+    layers, head = build_stack(torch, device, 1234 + rank, S, rank if tp > 1 else 0, tp)
     f16 = dict(dtype=torch.float16, device=device)
-    h_in = torch.empty((1, m, HIDDEN), **f16)
-    bufs = {"q": torch.empty((1, m, HIDDEN // tp), **f16), "k": torch.empty((1, m, KV // tp), **f16),
-            "v": torch.empty((1, m, KV // tp), **f16), "a": torch.empty((1, m, HIDDEN), **f16),
-            "gu": torch.empty((2, m, FFN // tp), **f16), "h": torch.empty((1, m, HIDDEN), **f16),
-            "logits": torch.empty((m, vocab_local), **f16)}
+    h_in = torch.empty((1, m, H), **f16)
+    bufs = {"q": torch.empty((1, m, shapes["q"][1]), **f16), "k": torch.empty((1, m, shapes["k"][1]), **f16),
+            "v": torch.empty((1, m, shapes["v"][1]), **f16), "a": torch.empty((1, m, H), **f16),
+            "gu": torch.empty((2, m, shapes["gate"][1]), **f16), "h": torch.empty((1, m, H), **f16)}
+    out_buf = torch.empty((m, head.out_features), **f16) if head else bufs["h"][0]
     comm = None
     if tp > 1:
         # partial sums of the row-parallel o / down, all-reduced over NVLink inside the graph
         from ampstein_b200.comm import P2PComm
-        bufs["a_part"] = torch.empty((1, m, HIDDEN), **f16)
-        bufs["h_part"] = torch.empty((1, m, HIDDEN), **f16)
-        comm = P2PComm.from_process_group(cap=m * HIDDEN)
+        bufs["a_part"] = torch.empty((1, m, H), **f16)
+        bufs["h_part"] = torch.empty((1, m, H), **f16)
+        comm = P2PComm.from_process_group(cap=m * H)
     # the reference's decode step runs q|k|v as one sliced bundle and gate|up as one stacked bundle
     # (src/ucode/ampstein/graphdec.uc:163-210): four launches per layer
     qkv = [Sliced([L["q"], L["k"], L["v"]], [bufs["q"], bufs["k"], bufs["v"]]) for L in layers]
@@ -189,124 +236,144 @@ def run_gpu(args):
         n = 0
         for i, L in enumerate(layers):
             qkv[i].run(x)
-            if comm is None:
-                L["o"].forward(bufs["q"][0], bufs["a"][0])    # attention itself is outside the path
-                gu[i].run(bufs["a"])
-                L["down"].forward(bufs["gu"][0], bufs["h"][0])
-                n += 4
+            if comm is None or stub:
+                L["o"].forward(bufs["q"][0], bufs["a"][0])        # attention itself is outside the path
+            elif args.unfused:
+                L["o"].forward(bufs["q"][0], bufs["a_part"][0])
+                comm.allreduce(bufs["a_part"], out=bufs["a"])
             else:
-                if stub:
-                    L["o"].forward(bufs["q"][0], bufs["a"][0])
-                elif args.unfused:
-                    L["o"].forward(bufs["q"][0], bufs["a_part"][0])
-                    comm.allreduce(bufs["a_part"], out=bufs["a"])
-                else:
-                    comm.linear_allreduce(L["o"], bufs["q"][0], bufs["a"][0])
-                gu[i].run(bufs["a"])
-                if stub:
-                    L["down"].forward(bufs["gu"][0], bufs["h"][0])
-                elif args.unfused:
-                    L["down"].forward(bufs["gu"][0], bufs["h_part"][0])
-                    comm.allreduce(bufs["h_part"], out=bufs["h"])
-                else:
-                    comm.linear_allreduce(L["down"], bufs["gu"][0], bufs["h"][0])
-                n += 6 if args.unfused else 4
+                comm.linear_allreduce(L["o"], bufs["q"][0], bufs["a"][0])
+            gu[i].run(bufs["a"])
+            if comm is None or stub:
+                L["down"].forward(bufs["gu"][0], bufs["h"][0])
+            elif args.unfused:
+                L["down"].forward(bufs["gu"][0], bufs["h_part"][0])
+                comm.allreduce(bufs["h_part"], out=bufs["h"])
+            else:
+                comm.linear_allreduce(L["down"], bufs["gu"][0], bufs["h"][0])
+            n += 6 if (comm is not None and args.unfused and not stub) else 4
             x = bufs["h"]
-        head.forward(x[0], bufs["logits"])
+        if head:
+            head.forward(x[0], out_buf)
+            n += 1
         if not stub:
-            launches[0] = n + 1
+            launches[0] = n
 
-    host_x = torch.randn((m, HIDDEN), dtype=torch.float16).pin_memory()
-    host_logits = torch.empty((m, vocab_local), dtype=torch.float16).pin_memory()
-    h_in.copy_(host_x.view(1, m, HIDDEN))
-    graph = DecodeGraph(step, warmup=2)
-    stream = graph.stream
+    host_x = torch.randn((m, H), dtype=torch.float16).pin_memory()
+    host_out = torch.empty(tuple(out_buf.shape), dtype=torch.float16).pin_memory()
+    h_in.copy_(host_x.view(1, m, H))
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        with torch.cuda.stream(stream):
-            e0.record(stream)
-            for _ in range(steps):
-                fn()
-            e1.record(stream)
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if dist is not None:
-            t = torch.tensor([ms], device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+    def reduce_max(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    allreduce_check = None
+    if comm is not None:
+        # Parity of the exchange, once before timing: the fused row-parallel linears of layer 0 must
+        # equal, bit for bit and on every rank, the fp32 rank-order sum (rounded once) of the ranks'
+        # fp16 partial products; so must the stand-alone all-reduce.
+        gen = torch.Generator(device=device)
+        gen.manual_seed(99 + rank)
+        ok = True
+        for name in ("o", "down"):
+            xin = torch.randn((m, shapes[name][0]), device=device, generator=gen).to(torch.float16)
+            part = torch.empty((m, H), **f16)
+            layers[0][name].forward(xin, part)
+            gathered = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(gathered, part)
+            acc = gathered[0].float()
+            for p in gathered[1:]:
+                acc = acc + p.float()
+            want = acc.to(torch.float16)
+            fused = torch.empty((m, H), **f16)
+            comm.linear_allreduce(layers[0][name], xin, fused)
+            sep = torch.empty((1, m, H), **f16)
+            comm.allreduce(part.view(1, m, H), out=sep)
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(fused, want) and torch.equal(sep[0], want)
+        flag = torch.tensor([1 if ok else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) != 1:
+            raise SystemExit("bench.py: the all-reduce of layer 0 differs from the fp32 rank-order sum of the partial products")
+        allreduce_check = "exact"
+
+    graph = DecodeGraph(step, warmup=2)
+    stream = graph.stream
 
     def resident_step():
         graph.replay()
 
     def e2e_step():
-        h_in.copy_(host_x.view(1, m, HIDDEN), non_blocking=True)
+        h_in.copy_(host_x.view(1, m, H), non_blocking=True)
         graph.replay()
-        host_logits.copy_(bufs["logits"], non_blocking=True)
+        host_out.copy_(out_buf, non_blocking=True)
 
     with torch.cuda.stream(stream):
         for _ in range(max(args.warmup, 3)):
             e2e_step()
+    barrier()
     sampler = ClockSampler(local) if rank == 0 else None
     t0 = time.time()
-    ms = timed(resident_step, args.steps)
-    ms_e2e = timed(e2e_step, args.steps)
+    ms, nblk, tot = timed_blocks(torch, resident_step, args.steps, stream, barrier, reduce_max)
+    ms_e2e, _, _ = timed_blocks(torch, e2e_step, args.steps, stream, barrier, reduce_max)
     t1 = time.time()
     ms_stub = None
     if comm is not None:
         # the same graph without the exchange: the difference is what the all-reduces cost
         # (values diverge between ranks here; only the time is used)
         stub_graph = DecodeGraph(lambda: step(stub=True), warmup=1, stream=stream)
-        ms_stub = timed(stub_graph.replay, args.steps)
+        ms_stub, _, _ = timed_blocks(torch, stub_graph.replay, args.steps, stream, barrier, reduce_max)
     clocks = sampler.stop(t0, t1) if sampler else None
 
-    logits = host_logits.float()
-    if not torch.isfinite(logits).all() or float(logits.abs().max()) == 0.0:
-        raise SystemExit("bench.py: step produced non-finite or all-zero logits")
+    res = host_out.float()
+    if not torch.isfinite(res).all() or float(res.abs().max()) == 0.0:
+        raise SystemExit("bench.py: step produced non-finite or all-zero outputs")
 
-    comm_status = 0
     if comm is not None:
-        comm_status = comm.status()
-        t = torch.tensor([comm_status], device=device)
+        t = torch.tensor([comm.status()], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        comm_status = int(t.item())
-        if comm_status:
-            raise SystemExit("bench.py: an all-reduce gave up waiting for a peer (status %d)" % comm_status)
+        if int(t.item()):
+            raise SystemExit("bench.py: an all-reduce gave up waiting for a peer (status %d)" % int(t.item()))
+
+    per_shape = None
+    if world == 1 and args.workload == "decode" and not args.no_secondary:
+        per_shape = per_shape_us(torch, layers, head, bufs, h_in, out_buf, qkv, gu, stream)
     if rank != 0:
         return
     ms_step = ms / args.steps
-    # tensor parallel: every rank decodes the same token; replicas: one token per rank
+    # tensor parallel: every rank decodes the same tokens; replicas: one batch per rank
     streams = 1 if tp > 1 else world
     tok_s = streams * m * 1000.0 / ms_step
     tok_s_e2e = streams * m * 1000.0 / (ms_e2e / args.steps)
-    gemv_launches = 4 * LAYERS + 1
-    # per GPU: a rank streams 1/tp of the weights (+ the unsharded vectors)
-    bytes_step = algorithmic_bytes(m) if tp == 1 else algorithmic_bytes(m) // tp
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except (OSError, ValueError):
-        pass
+    gemv_launches = 4 * S["layers"] + (1 if head else 0)
+    bytes_step = algorithmic_bytes(S, m, 0, tp)
+    peaks = _peaks()
     peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = bytes_step / (ms_step * 1e-3) / 1e9
+    metric = METRIC if args.workload == "decode" else "decode tok/s (64-layer 5 bpw tensor-parallel stack, hidden 5120)"
+    wl = "%s decode step, batch %d, EXL3 %d bpw x%d layers%s, one CUDA graph" % (
+        S["name"], m, S["K"], S["layers"], (" + %d bpw lm_head" % S["K_head"]) if head else "")
     line = {
-        "metric": METRIC, "value": round(tok_s, 2), "unit": UNIT, "n_gpus": world,
+        "metric": metric, "value": round(tok_s, 2), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4),
         "higher_is_better": True, "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": "llama3-8b-shaped decode step, batch 1, EXL3 4.0 bpw x%d layers + 6 bpw lm_head, one CUDA graph" % LAYERS,
+        "config": {"workload": wl,
                    "l2": "inputs larger than L2 (%.2f GB of weights streamed per step and GPU)" % (bytes_step / 1e9),
-                   "parallelism": ("tp%d: column-parallel q|k|v, gate|up; row-parallel o, down with the fp16 all-reduce (%d per step) over NVLink %s; lm_head by vocabulary"
-                                   % (tp, 2 * LAYERS, "as separate launches" if args.unfused else "fused into the GEMV epilogue")) if tp > 1 else ("replicas x%d" % world)},
+                   "parallelism": ("tp%d: column-parallel q|k|v, gate|up; row-parallel o, down with the fp16 all-reduce (%d per step) over NVLink %s%s"
+                                   % (tp, 2 * S["layers"], "as separate launches" if args.unfused else "fused into the GEMV epilogue",
+                                      "; lm_head by vocabulary" if head else "")) if tp > 1 else ("replicas x%d" % world),
+                   "timing": "median of %d blocks of %d steps (%.2f s timed)" % (nblk, args.steps, tot / 1e3)},
         "e2e": {"value": round(tok_s_e2e, 2), "unit": UNIT,
-                "h2d_bytes_per_step": host_x.numel() * 2, "d2h_bytes_per_step": host_logits.numel() * 2},
+                "h2d_bytes_per_step": host_x.numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2},
         "gpu_launches": launches[0] * args.steps,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
@@ -320,97 +387,120 @@ def run_gpu(args):
                      "traffic_source": "ncu capture on a 2-layer stack, scaled by weight bytes"},
     }
     if ms_stub is not None:
-        line["allreduce"] = {"per_step": 2 * LAYERS, "bytes": m * HIDDEN * 2,
+        line["allreduce"] = {"per_step": 2 * S["layers"], "bytes": m * H * 2,
                              "ms_per_step_without": round(ms_stub / args.steps, 4),
                              "share_of_step": round(max(0.0, 1.0 - ms_stub / ms), 4),
-                             "us_each": round(max(0.0, ms - ms_stub) / args.steps / (2 * LAYERS) * 1e3, 2)}
-    if world == 1:
+                             "us_each": round(max(0.0, ms - ms_stub) / args.steps / (2 * S["layers"]) * 1e3, 2)}
+        line["allreduce_check"] = allreduce_check
+    if per_shape:
+        line["per_shape_us"] = per_shape
+    if world == 1 and args.workload == "decode":
         line["cpu_baseline"] = cpu_baseline()
+        if not args.no_secondary:
+            line["secondary"] = secondary()
     print(json.dumps(line), flush=True)
 
 
+def per_shape_us(torch, layers, head, bufs, h_in, out_buf, qkv, gu, stream):
+    """Time of each of the layer's four launches (and the lm_head) on their own: one CUDA graph per
+    shape that runs the launch of every layer in turn (distinct weights, larger than L2), so that
+    the step reads as the sum of its launches."""
+    from ampstein_b200.models import DecodeGraph
+    n = len(layers)
+    progs = {
+        "q|k|v": lambda: [qkv[i].run(h_in) for i in range(n)],
+        "o": lambda: [L["o"].forward(bufs["q"][0], bufs["a"][0]) for L in layers],
+        "gate|up": lambda: [gu[i].run(bufs["a"]) for i in range(n)],
+        "down": lambda: [L["down"].forward(bufs["gu"][0], bufs["h"][0]) for L in layers],
+    }
+    out = {}
+    for name, fn in progs.items():
+        g = DecodeGraph(fn, warmup=1, stream=stream)
+        ms, _, _ = timed_blocks(torch, g.replay, 8, stream, min_s=0.1)
+        out[name] = round(ms / 8 / n * 1e3, 2)
+    total = sum(out.values()) * n
+    if head:
+        g = DecodeGraph(lambda: head.forward(bufs["h"][0], out_buf), warmup=1, stream=stream)
+        ms, _, _ = timed_blocks(torch, g.replay, 8, stream, min_s=0.1)
+        out["lm_head"] = round(ms / 8 * 1e3, 2)
+        total += out["lm_head"]
+    out["sum_per_step_ms"] = round(total / 1e3, 4)
+    return out
+
+
 # ------------------------------------------------------------------------------------------
-# secondary workloads (one GPU): the prefill GEMM and the fused decode MoE
+# secondary workloads (one GPU): the prefill GEMM, the fused decode MoE, the issue microbenchmark
 # ------------------------------------------------------------------------------------------
 
-def _peaks():
-    try:
-        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except (OSError, ValueError):
-        return {}
+LAYER_8B = [("q", 4096, 4096), ("k", 4096, 1024), ("v", 4096, 1024), ("o", 4096, 4096),
+            ("gate", 4096, 14336), ("up", 4096, 14336), ("down", 14336, 4096)]
 
 
-def run_prefill(args):
+def measure_prefill(steps, warmup):
     """One decoder layer's seven linears at M = 2048 tokens, bf16 activations, mixed bit widths
     (attention K=5, gate/up K=3, down K=4): the tensor-core (tcgen05) trellis-decode GEMM,
     including the input rotation kernel. One step = the seven GEMMs."""
     import torch
     import ampstein_b200 as amp
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device (the path has no CPU fallback)")
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev)
     g.manual_seed(7)
     M = 2048
     bits = {"q": 5, "k": 5, "v": 5, "o": 5, "gate": 3, "up": 3, "down": 4}
     ops = []
-    for name, k, n in LAYER_LINEARS:
+    for name, k, n in LAYER_8B:
         K = bits[name]
         t = torch.randint(-32768, 32768, (k // 16, n // 16, 16 * K), dtype=torch.int16, device=dev, generator=g)
         sgn = lambda c: (torch.randint(0, 2, (c,), device=dev, generator=g).to(torch.float16) * 2 - 1)
         svh = (sgn(n) * (1.0 / (1.2437 * math.sqrt(k)))).to(torch.float16)
         x = torch.randn((M, k), device=dev, generator=g).to(torch.bfloat16)
         ops.append((x, t, torch.empty((M, n), dtype=torch.float16, device=dev), sgn(k), svh))
-    flops = sum(2.0 * M * k * n for _, k, n in LAYER_LINEARS)
+    flops = sum(2.0 * M * k * n for _, k, n in LAYER_8B)
 
     def step():
         for x, t, y, suh, svh in ops:
             amp.exl3_gemm(x, t, y, suh, svh)
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step()
     torch.cuda.synchronize()
     sampler = ClockSampler(0)
     t0 = time.time()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
+    ms_blk, nblk, _ = timed_blocks(torch, step, steps, min_s=0.5)
     clocks = sampler.stop(t0, time.time())
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = ms_blk / steps
     if not all(torch.isfinite(o[2].float()).all() for o in ops):
         raise SystemExit("bench.py: prefill produced non-finite outputs")
     peaks = _peaks()
     peak = float(peaks.get("bf16_tflops", 1590.0))
     tf = flops / ms / 1e9
-    print(json.dumps({
+    return {
         "metric": "prefill TFLOP/s (one 8B-shaped layer, M=2048, EXL3 K=5/3/4)", "value": round(tf, 1), "unit": "TFLOP/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4),
+        "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3), "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "prefill: 7 linears of one llama3-8b-shaped layer, M=2048 bf16 tokens, K=5 attention / 3 gate,up / 4 down",
-                   "l2": "operands of a step: 0.23 GB (weights read once per GEMM)"},
-        "gpu_launches": 14 * args.steps, "clocks": clocks,
+                   "l2": "operands of a step: 0.23 GB (weights read once per GEMM)",
+                   "timing": "median of %d blocks of %d steps" % (nblk, steps)},
+        "gpu_launches": 14 * steps, "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(tf / peak, 4),
                      "peak_source": "measured burst (MEASURED_PEAKS.json)" if "bf16_tflops" in peaks else "fallback",
-                     "kernel": "exl3_gemm_tc2_kernel", "traffic": None}}), flush=True)
+                     "kernel": "exl3_gemm_tc2_kernel", "traffic": None}}
 
 
-def run_moe(args):
+MOE_LAUNCHES = 4           # kernels per fused MoE layer: run table, gate|up, down, combine
+
+
+def measure_moe(steps, warmup, T):
     """Fused decode MoE: 128 experts 2048 -> 768 -> 2048 at K=3, top-8 routing from fp32 router
-    logits ~ N(0,1), T tokens per step (--tokens 1, 4 or 16). Eight different routings are
-    captured in one CUDA graph so that successive layers hit different experts; one step = one
-    MoE layer."""
+    logits ~ N(0,1), T tokens per step. Eight different routings are captured in one CUDA graph so
+    that successive layers hit different experts; one step = one MoE layer."""
     import numpy as np
     import torch
     import ampstein_b200 as amp
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device (the path has no CPU fallback)")
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev)
     g.manual_seed(11)
-    E, Hi, I, Ho, K, topk, T = 128, 2048, 768, 2048, 3, 8, args.tokens
+    E, Hi, I, Ho, K, topk = 128, 2048, 768, 2048, 3, 8
     tr = lambda k, n: torch.randint(-32768, 32768, (k // 16, n // 16, 16 * K), dtype=torch.int16, device=dev, generator=g)
     sg = lambda c, s=1.0: ((torch.randint(0, 2, (c,), device=dev, generator=g).to(torch.float16) * 2 - 1) * s).to(torch.float16)
     ex = [dict(g=(tr(Hi, I), sg(Hi), sg(I, 1 / (1.2437 * math.sqrt(Hi)))), u=(tr(Hi, I), sg(Hi), sg(I, 1 / (1.2437 * math.sqrt(Hi)))),
@@ -436,72 +526,114 @@ def run_moe(args):
     with torch.cuda.stream(st), torch.cuda.graph(gr, stream=st):
         for x, sel, rw in sets:
             amp.moe_coop(x, sel, rw, cfg)
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         gr.replay()
     torch.cuda.synchronize()
     sampler = ClockSampler(0)
     t0 = time.time()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        gr.replay()
-    e1.record()
-    torch.cuda.synchronize()
+    ms_blk, _, _ = timed_blocks(torch, gr.replay, steps, min_s=0.3)
     clocks = sampler.stop(t0, time.time())
-    us = e0.elapsed_time(e1) * 1e3 / (args.steps * len(sets))
+    us = ms_blk * 1e3 / (steps * len(sets))
     if not torch.isfinite(cfg["out"]).all():
         raise SystemExit("bench.py: MoE produced non-finite outputs")
     byt = distinct * 3 * Hi * I * K // 8
     peaks = _peaks()
     peak = float(peaks.get("hbm_gbs", 6650.0))
     gbs = byt / us / 1e3
-    print(json.dumps({
+    return {
         "metric": "fused decode MoE layer time (128 experts, top-8, K=3)", "value": round(us, 2), "unit": "us/layer",
-        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(us * len(sets) / 1e3, 4),
+        "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3), "ms_per_step": round(us * len(sets) / 1e3, 4),
         "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "moe decode: 128 experts 2048->768->2048 K=3, top-8, %d token(s), 8 routings per graph" % T,
                    "distinct_experts_per_layer": round(distinct, 1),
                    "l2": "expert weights in total 226 MB (larger than L2); each layer touches %.1f MB" % (byt / 1e6)},
-        "gpu_launches": 4 * len(sets) * args.steps, "clocks": clocks,
+        "gpu_launches": MOE_LAUNCHES * len(sets) * steps, "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
                      "peak_source": "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback",
-                     "kernel": "exl3_gemv_kernel (grouped modes)", "bytes_per_launch": int(byt) // 2, "traffic": None}}), flush=True)
+                     "kernel": "exl3_gemv_kernel (grouped modes)", "bytes_per_launch": int(byt) // 2, "traffic": None}}
+
+
+def measure_issue():
+    """Cycles one SM scheduler needs per 8 decoded weights and lane (K = 4 decode mix) with the dot
+    product fed by two mma.sync, by one tcgen05.st, not at all, and for the two mma.sync alone."""
+    import ctypes
+    from ampstein_b200 import _lib
+    names = ["decode + 2 mma.sync m16n8k16", "decode + tcgen05.st (8 registers)", "decode + checksum (4 lop3)", "2 mma.sync only"]
+    table = {}
+    for v, name in enumerate(names):
+        row = {}
+        for w in (1, 2, 3, 4, 6, 8):
+            c = ctypes.c_float(0)
+            _lib.call("amp_diag_issue_cycles", v, w, ctypes.byref(c))
+            row[str(w)] = round(c.value, 2)
+        table[name] = row
+    return table
+
+
+def secondary():
+    """The other configurations, measured in the same run so that the record holds them."""
+    out = {}
+    p = measure_prefill(10, 3)
+    out["prefill"] = {k: p[k] for k in ("metric", "value", "unit", "ms_per_step", "roofline", "clocks")}
+    for T in (1, 4, 16):
+        r = measure_moe(20, 3, T)
+        out["moe_T%d" % T] = {"metric": r["metric"], "value": r["value"], "unit": r["unit"],
+                              "distinct_experts": r["config"]["distinct_experts_per_layer"],
+                              "roofline": r["roofline"], "clocks": r["clocks"]}
+    return out
 
 
 # ------------------------------------------------------------------------------------------
 # CPU legs (the oracle as the timed thing: allowed only here)
 # ------------------------------------------------------------------------------------------
 
+HEAD_SLICE = 8192          # lm_head columns in the CPU sample (of 128256)
+
+
 def cpu_sample_seconds(repeats=1):
-    """One layer of the stack (7 linears, 218 M weights) through the CPU restatement of
-    reconstruct-then-matmul; returns (seconds per layer, threads)."""
+    """One layer of the 8B stack (7 linears at 4 bits, 218 M weights) and a 8192-column slice of
+    the 6-bit lm_head (33.6 M weights) through the CPU restatement of reconstruct-then-matmul;
+    returns (seconds per layer, seconds per head slice, threads)."""
     import numpy as np
     from oracle import exl3_oracle as o
+    S = STACKS["decode"]
     rng = np.random.default_rng(0)
-    mats = []
-    for _, k, n in LAYER_LINEARS:
-        trellis = rng.integers(0, 65536, size=(k // 16, n // 16, 16 * K_LAYER), dtype=np.uint16)
+
+    def mat(k, n, K):
+        trellis = rng.integers(0, 65536, size=(k // 16, n // 16, 16 * K), dtype=np.uint16)
         suh = rng.choice(np.array([-1.0, 1.0], np.float16), k)
         svh = rng.choice(np.array([-1.0, 1.0], np.float16), n)
-        x = rng.standard_normal((1, k)).astype(np.float16)
-        mats.append((x, trellis, suh, svh))
-    best = None
+        return (rng.standard_normal((1, k)).astype(np.float16), trellis, suh, svh)
+
+    mats = [mat(k, n, S["K"]) for _, k, n in LAYER_8B]
+    headm = mat(S["hidden"], HEAD_SLICE, S["K_head"])
+    best_l = best_h = None
     for _ in range(repeats):
         t = time.time()
         for x, trellis, suh, svh in mats:
             o.linear(x, trellis, suh, svh, 0)
-        dt = time.time() - t
-        best = dt if best is None else min(best, dt)
-    return best, o.num_threads()
+        dl = time.time() - t
+        t = time.time()
+        o.linear(*headm, 0)
+        dh = time.time() - t
+        best_l = dl if best_l is None else min(best_l, dl)
+        best_h = dh if best_h is None else min(best_h, dh)
+    return best_l, best_h, o.num_threads()
+
+
+def cpu_step_seconds(sec_layer, sec_head):
+    S = STACKS["decode"]
+    return sec_layer * S["layers"] + sec_head * (S["vocab"] / HEAD_SLICE)
+
+
+CPU_SAMPLE = ("one of 32 layers (7 linears at 4 bits, 218M weights) and 8192 of the 128256 lm_head columns at 6 bits, "
+              "reconstructed and multiplied; step = 32 x layer + 15.66 x head slice")
 
 
 def cpu_baseline(repeats=2):
-    sec_layer, threads = cpu_sample_seconds(repeats)
-    layer_weights = sum(k * n for _, k, n in LAYER_LINEARS)
-    sec_step = sec_layer * total_weights() / layer_weights
-    return {"value": round(1.0 / sec_step, 5), "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": "one of 32 layers (7 linears, 218M weights) reconstructed and multiplied, "
-                      "best of %d, scaled by weight count to the full step" % repeats}
+    sl, sh, threads = cpu_sample_seconds(repeats)
+    return {"value": round(1.0 / cpu_step_seconds(sl, sh), 5), "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": CPU_SAMPLE + ", best of %d" % repeats}
 
 
 def run_reference(args):
@@ -514,21 +646,19 @@ def run_reference(args):
     t0 = time.time()
     for _ in range(args.steps):
         t_all.append(cpu_sample_seconds(1))
-    sec_layer = sum(t for t, _ in t_all) / len(t_all)
-    threads = t_all[0][1]
-    layer_weights = sum(k * n for _, k, n in LAYER_LINEARS)
-    sec_step = sec_layer * total_weights() / layer_weights
+    sec_step = cpu_step_seconds(sum(t[0] for t in t_all) / len(t_all), sum(t[1] for t in t_all) / len(t_all))
+    threads = t_all[0][2]
     val = round(1.0 / sec_step, 5)
+    S = STACKS["decode"]
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT,
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(sec_step * 1e3, 1), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "llama3-8b-shaped decode step, batch 1, EXL3 4.0 bpw x%d layers + 6 bpw lm_head" % LAYERS,
+        "config": {"workload": "%s decode step, batch 1, EXL3 %d bpw x%d layers + %d bpw lm_head" % (S["name"], S["K"], S["layers"], S["K_head"]),
                    "note": "CPU reconstruct-then-matmul; the reference ships no CPU code for this codebook, "
                            "so the timed code is the CPU restatement (oracle port)"},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": "each step = one of 32 layers (7 linears, 218M weights), scaled by weight count"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": "each step = " + CPU_SAMPLE},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": round(time.time() - t0, 1),
     }
@@ -536,7 +666,6 @@ def run_reference(args):
 
 
 def main():
-    global LAYERS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -546,15 +675,20 @@ def main():
                     help="with --gpus N > 1: tensor-parallel decode of one stack (default) or N independent replicas")
     ap.add_argument("--unfused", action="store_true",
                     help="tensor-parallel mode: separate all-reduce launches instead of the GEMV's fused exchange")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "moe"],
-                    help="decode (default, the headline step) or a secondary one-GPU workload: the prefill GEMM / the fused decode MoE")
+    ap.add_argument("--workload", default="decode", choices=["decode", "tp5", "prefill", "moe", "issue"],
+                    help="decode (default, the headline step), tp5 (the 64-layer 5-bit tensor-parallel stack), or a secondary "
+                         "one-GPU workload: the prefill GEMM / the fused decode MoE / the issue-rate microbenchmark")
+    ap.add_argument("--batch", type=int, default=1, help="tokens per decode step (decode / tp5 workloads), 1..16")
     ap.add_argument("--tokens", type=int, default=1, choices=[1, 4, 16], help="tokens per step of --workload moe")
     ap.add_argument("--tmem-gemv", action="store_true",
                     help="A/B: run the decode GEMVs on the tensor-memory (tcgen05) kernel instead of the mma.sync kernel")
-    ap.add_argument("--layers", type=int, default=LAYERS,
-                    help="layers of the stack (default: the full 32; fewer only for a small profiler capture)")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="decode workload on one GPU: skip the per-shape and secondary measurements (profiler captures)")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="layers of the stack (default: the full stack; fewer only for a small profiler capture)")
     args = ap.parse_args()
-    LAYERS = args.layers
+    if not 1 <= args.batch <= 16:
+        raise SystemExit("bench.py: --batch must be 1..16")
     if args.tmem_gemv and args.impl != "reference":
         from ampstein_b200 import _lib
         _lib.lib().amp_exl3_set_gemv_tc(1)
@@ -563,12 +697,23 @@ def main():
             args.steps = 5                 # each step is seconds of CPU work
         args.warmup = min(args.warmup, 1)
         run_reference(args)
-    elif args.workload == "prefill":
-        run_prefill(args)
-    elif args.workload == "moe":
-        run_moe(args)
-    else:
-        run_gpu(args)
+        return
+    if args.workload in ("prefill", "moe", "issue"):
+        import torch
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py: no CUDA device (the path has no CPU fallback)")
+        if args.workload == "prefill":
+            print(json.dumps(measure_prefill(args.steps, args.warmup)), flush=True)
+        elif args.workload == "moe":
+            print(json.dumps(measure_moe(args.steps, args.warmup, args.tokens)), flush=True)
+        else:
+            print(json.dumps({"metric": "scheduler cycles per 8 decoded weights and lane (K=4 mix)", "unit": "cycles",
+                              "by_warps_per_scheduler": measure_issue()}), flush=True)
+        return
+    S = dict(STACKS[args.workload])
+    if args.layers:
+        S["layers"] = args.layers
+    run_decode(args, S)
 
 
 if __name__ == "__main__":

@@ -223,6 +223,15 @@ int amp_exl3_set_pdl(int enable);
 int amp_exl3_set_gemv_tc(int enable);
 
 /*
+ * Measurement aid behind `python bench.py --workload issue` (not part of the hot path): cycles one
+ * SM scheduler needs per 8 decoded weights and lane for the decode kernel's K = 4 instruction mix
+ * when the dot product is fed by two mma.sync (variant 0), by one tcgen05.st into tensor memory
+ * (1), not at all (2: checksum), or for the two mma.sync alone (3), at 1..8 resident warps per
+ * scheduler. Synchronises and allocates its own buffers. The reference has no counterpart.
+ */
+int amp_diag_issue_cycles(int variant, int warps_per_scheduler, float* cycles_per_iter);
+
+/*
  * Reads and clears the current device's GEMV status word (non-zero = a kernel reported an
  * internal error: a bounded wait on one of the tensor-memory kernel's hand-over barriers ran out).
  * Synchronises; not for the hot path.

@@ -15,6 +15,13 @@ int exl3_gemm(const at::Tensor& A, const at::Tensor& B, at::Tensor& C, const c10
               const c10::optional<at::Tensor>& A_had, const c10::optional<at::Tensor>& svh, int force_shape_idx,
               bool mcg, bool mul1, int force_num_sms);
 
+int exl3_mgemm(const at::Tensor& A, const at::Tensor& B, at::Tensor& C, const at::Tensor& suh, const at::Tensor& A_had,
+               const at::Tensor& svh, const c10::optional<at::Tensor>& indices, const c10::optional<at::Tensor>& weights,
+               float K, int force_shape_idx, uint32_t mcg_mult, uint32_t mul1_mult, int min_index, int max_index,
+               int force_num_sms, int num_tokens, const c10::optional<at::Tensor>& size_n_list,
+               const c10::optional<at::Tensor>& c_ptrs, const c10::optional<at::Tensor>& n_stride_list,
+               const c10::optional<at::Tensor>& had_src_list, int num_had_src);
+
 void exl3_moe_coop(const at::Tensor& x, const at::Tensor& sel, const at::Tensor& rw, int min_expert, int max_expert, int Hi,
                    const at::Tensor& g_trellis, const at::Tensor& g_suh, const at::Tensor& g_svh,
                    const at::Tensor& u_trellis, const at::Tensor& u_suh, const at::Tensor& u_svh,
@@ -26,6 +33,16 @@ void exl3_moe_coop(const at::Tensor& x, const at::Tensor& sel, const at::Tensor&
                    const c10::optional<at::Tensor>& sh_out, const c10::optional<at::Tensor>& sh_gate_w,
                    const c10::optional<at::Tensor>& bits_g, const c10::optional<at::Tensor>& bits_u,
                    const c10::optional<at::Tensor>& bits_d);
+
+// The reference's exl3_gemm.cu refers to Graph::record_param (its graph.cu needs Python.h and is
+// not part of the reference's own build either: torch.so leaves the symbol to lazy binding, and it
+// is only reached with a non-null graph, which neither the reference nor this shim passes).
+// Loading through ctypes binds eagerly, so the symbol gets a body that reports the call.
+#include "graph.cuh"
+void Graph::record_param(void*, int, int, int)
+{
+    fprintf(stderr, "ref_shim: Graph::record_param called (no graph recording in this build)\n");
+}
 
 static at::Tensor view(void* p, at::IntArrayRef shape, at::ScalarType t, int dev)
 {
@@ -48,6 +65,36 @@ extern "C" int ref_exl3_gemm(void* x, void* trellis, void* c, void* suh, void* a
         c10::optional<at::Tensor> ah = view(a_had, {m, k}, at::kHalf, dev);
         c10::optional<at::Tensor> sv = view(svh, {n}, at::kHalf, dev);
         return exl3_gemm(A, B, C, su, ah, sv, -1, cb == 1, cb == 2, 0);
+    }
+    catch (const std::exception& e) { fprintf(stderr, "ref_shim: %s\n", e.what()); return -1; }
+}
+
+// Bundles exactly as the reference's torch.mgemm binding passes them (src/torch/amp_torch.cpp:
+// 10193-10322): x (1, m, k); device int64 pointer tables with `num` entries; C (num, m, width);
+// A_had (num_src, m, k) scratch; the four option tables are null for a stacked bundle.
+extern "C" int ref_exl3_mgemm(void* x, void* b_ptrs, void* c, void* suh_ptrs, void* a_had, void* svh_ptrs,
+                              int num, int num_src, int m, int k, int width, int K, int cb,
+                              void* size_n_list, void* c_ptrs, void* n_stride_list, void* had_src_list, int dev)
+{
+    try
+    {
+        c10::cuda::CUDAGuard guard(dev);
+        auto A = view(x, {1, m, k}, at::kHalf, dev);
+        auto B = view(b_ptrs, {num}, at::kLong, dev);
+        auto C = view(c, {num, m, width}, at::kHalf, dev);
+        auto su = view(suh_ptrs, {num_src}, at::kLong, dev);
+        auto ah = view(a_had, {num_src, m, k}, at::kHalf, dev);
+        auto sv = view(svh_ptrs, {num}, at::kLong, dev);
+        c10::optional<at::Tensor> none, snl, cp, nsl, hsl;
+        if (c_ptrs)
+        {
+            snl = view(size_n_list, {num}, at::kInt, dev);
+            cp = view(c_ptrs, {num}, at::kLong, dev);
+            nsl = view(n_stride_list, {num}, at::kInt, dev);
+            hsl = view(had_src_list, {num}, at::kInt, dev);
+        }
+        return exl3_mgemm(A, B, C, su, ah, sv, none, none, (float) K, -1, cb == 1 ? 1u : 0u, cb == 2 ? 1u : 0u,
+                          -1, -1, 0, 1, snl, cp, nsl, hsl, c_ptrs ? num_src : 0);
     }
     catch (const std::exception& e) { fprintf(stderr, "ref_shim: %s\n", e.what()); return -1; }
 }
