@@ -21,6 +21,9 @@ SIGNATURES = {
     "amp_had_r_128": [_vp, _vp, _vp, _vp, _l, _i, _i, _f, _vp],
     "amp_exl3_gemv": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "amp_exl3_gemv_allreduce": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, ctypes.c_long, _vp],
+    "amp_exl3_gemv_push": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, ctypes.c_long, _vp],
+    "amp_exl3_gemv_gathered": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, ctypes.c_long, _vp],
+    "amp_exl3_mgemm_gathered": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, ctypes.c_long, _vp],
     "amp_exl3_gemv_static": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "amp_exl3_gemv_cfg": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "amp_exl3_gemv_status": [ctypes.POINTER(ctypes.c_int)],

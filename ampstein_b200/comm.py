@@ -206,6 +206,69 @@ class P2PComm:
                       bufs, ctls, rank, self.N, self.cap, torch.cuda.current_stream(x.device).cuda_stream)
         return out
 
+    # ---- split exchange: push in the producer, gather in the consumer's prologue ----
+
+    def linear_push(self, lin, x, rank=None):
+        """Row-parallel EXL3 linear whose result is not written anywhere: every finished column
+        block is pushed, as this rank's fp16 partial, into every rank's buffer. The next launch on
+        this communicator must be a gathered one (gathered_linear / gathered_bundle) on every
+        rank; it consumes the sum."""
+        from . import _lib
+        rank = self.rank if rank is None else rank
+        if rank is None or not (0 <= rank < self.N):
+            raise ValueError("expected (lin, x, rank)")
+        m, n = x.shape[0], lin.out_features
+        ok = (x.is_cuda and x.dtype == torch.float16 and x.is_contiguous() and x.dim() == 2
+              and x.shape[1] == lin.in_features and 1 <= m <= 16 and m * n <= self.cap and lin.bias is None)
+        if not ok:
+            raise ValueError("comm.linear_push: x (m <= 16, k) must be contiguous fp16 on the rank's device, "
+                             "m * n <= cap, no bias")
+        bufs, ctls = self._bufs[rank]
+        cb = 2 if lin.mul1 else (1 if lin.mcg else 0)
+        with torch.cuda.device(x.device):
+            _lib.call("amp_exl3_gemv_push", x.data_ptr(), lin.trellis.data_ptr(), lin.suh.data_ptr(), lin.svh.data_ptr(),
+                      m, lin.in_features, n, lin.K, cb, bufs, ctls, rank, self.N, self.cap,
+                      torch.cuda.current_stream(x.device).cuda_stream)
+
+    def gathered_linear(self, lin, out, rank=None):
+        """out (m, n) = lin(all-reduced input): the input (m, k) is the sum of the partials the
+        ranks pushed with their last linear_push, added up inside the kernel's input rotation."""
+        from . import _lib
+        rank = self.rank if rank is None else rank
+        m, n = out.shape[0], lin.out_features
+        if not (out.is_cuda and out.is_contiguous() and out.dim() == 2 and out.shape[1] == n and 1 <= m <= 16
+                and out.dtype in (torch.float16, torch.float32) and m * lin.in_features <= self.cap and lin.bias is None):
+            raise ValueError("comm.gathered_linear: out must be a contiguous (m <= 16, n) fp16/fp32 CUDA tensor, m * k <= cap")
+        buf, ctl = self._local[rank]
+        cb = 2 if lin.mul1 else (1 if lin.mcg else 0)
+        with torch.cuda.device(out.device):
+            _lib.call("amp_exl3_gemv_gathered", lin.trellis.data_ptr(), out.data_ptr(), lin.suh.data_ptr(), lin.svh.data_ptr(),
+                      m, lin.in_features, n, lin.K, cb, int(out.dtype == torch.float32), buf, ctl, self.N, self.cap,
+                      torch.cuda.current_stream(out.device).cuda_stream)
+        return out
+
+    def gathered_bundle(self, bundle, m, rank=None):
+        """A models.Multi or models.Sliced bundle run on the all-reduced input (see
+        gathered_linear); writes the bundle's own output buffers."""
+        from . import _lib
+        rank = self.rank if rank is None else rank
+        a = bundle.linears[0]
+        if not (1 <= m <= 16 and m * a.in_features <= self.cap):
+            raise ValueError("comm.gathered_bundle: m <= 16 and m * k <= cap")
+        buf, ctl = self._local[rank]
+        cb = 2 if a.mul1 else (1 if a.mcg else 0)
+        opts = getattr(bundle, "opts", None)
+        if opts is None:
+            C, num, width = bundle.out, len(bundle.linears), a.out_features
+            cp = ns = hs = None
+        else:
+            C, num, width = bundle.carrier, bundle.slices, bundle.width
+            cp, ns, hs = opts["c_ptrs"].data_ptr(), opts["n_stride_list"].data_ptr(), opts["had_src_list"].data_ptr()
+        with torch.cuda.device(C.device):
+            _lib.call("amp_exl3_mgemm_gathered", bundle.B.data_ptr(), C.data_ptr(), bundle.suh.data_ptr(), bundle.svh.data_ptr(),
+                      num, m, a.in_features, width, a.K, cb, 0, cp, ns, hs, buf, ctl, self.N, self.cap,
+                      torch.cuda.current_stream(C.device).cuda_stream)
+
     def status(self, rank=None):
         """Non-zero when a bounded wait for a peer ran out since the last query."""
         rank = self.rank if rank is None else rank

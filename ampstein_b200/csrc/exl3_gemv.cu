@@ -28,18 +28,18 @@ static DevInfo& dev_info(int dev)
     return d;
 }
 
-static gemv_fn gemv_kernel_for(int K, int cb, int MB, int mode)
+static gemv_fn gemv_kernel_for(int K, int cb, int MB, int mode, int gin)
 {
     switch (K)
     {
-        case 1: return gemv_kernel_k1(cb, MB, mode);
-        case 2: return gemv_kernel_k2(cb, MB, mode);
-        case 3: return gemv_kernel_k3(cb, MB, mode);
-        case 4: return gemv_kernel_k4(cb, MB, mode);
-        case 5: return gemv_kernel_k5(cb, MB, mode);
-        case 6: return gemv_kernel_k6(cb, MB, mode);
-        case 7: return gemv_kernel_k7(cb, MB, mode);
-        case 8: return gemv_kernel_k8(cb, MB, mode);
+        case 1: return gemv_kernel_k1(cb, MB, mode, gin);
+        case 2: return gemv_kernel_k2(cb, MB, mode, gin);
+        case 3: return gemv_kernel_k3(cb, MB, mode, gin);
+        case 4: return gemv_kernel_k4(cb, MB, mode, gin);
+        case 5: return gemv_kernel_k5(cb, MB, mode, gin);
+        case 6: return gemv_kernel_k6(cb, MB, mode, gin);
+        case 7: return gemv_kernel_k7(cb, MB, mode, gin);
+        case 8: return gemv_kernel_k8(cb, MB, mode, gin);
     }
     return nullptr;
 }
@@ -118,7 +118,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     AMP_REQUIRE(k > 0 && A.width > 0 && k % 128 == 0 && A.width % 128 == 0 && A.stride % 128 == 0,
                 "exl3_gemv: k and n must be multiples of 128");
     AMP_REQUIRE(A.slices >= 1 && (long) A.slices * (A.width / 128) <= 0x7fffffffL, "exl3_gemv: bad slice count");
-    AMP_REQUIRE(A.mode || (A.x && ((uintptr_t) A.x & 7) == 0), "exl3_gemv: x must be a non-null 8-byte aligned pointer");
+    AMP_REQUIRE(A.mode || A.arin.N || (A.x && ((uintptr_t) A.x & 7) == 0), "exl3_gemv: x must be a non-null 8-byte aligned pointer");
     if (A.mode)
     {
         AMP_REQUIRE(A.moe.runs && A.max_slices >= 1, "exl3_moe: run table missing");
@@ -141,8 +141,8 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     const DevInfo& D = dev_info(dev);
 
     const int MB = m <= 8 ? 1 : 2;
-    const bool tc = !A.mode && m <= TCV_MAX_M && g_gemv_tc;
-    gemv_fn fn = tc ? gemv_tc_kernel_for(K, A.cb, A.ar.N != 0) : gemv_kernel_for(K, A.cb, MB, A.mode);
+    const bool tc = !A.mode && m <= TCV_MAX_M && g_gemv_tc && !A.arin.N && !A.ar.push_only;
+    gemv_fn fn = tc ? gemv_tc_kernel_for(K, A.cb, A.ar.N != 0) : gemv_kernel_for(K, A.cb, MB, A.mode, A.arin.N != 0);
     if (!fn) return fail(AMP_E_UNSUPPORTED, "exl3_gemv: no kernel for K=%d cb=%d", K, A.cb);
 
     // x~ rows resident at a time: at most 16 KB of shared memory (whole segments for small
@@ -222,7 +222,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
         const long need = (per + 1 + 3) / 4 * 4;
         if (need < xgroups) xgroups = (int) need;
     }
-    L = gemv_smem_layout(K, m, xgroups, cluster);
+    L = gemv_smem_layout(K, m, xgroups, cluster, A.arin.N != 0);
     if (tc)
     {
         xgroups = tc_xg;
@@ -249,6 +249,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     P.blocks = (int) col_blocks;
     P.moe = A.moe;
     P.ar = A.ar;
+    P.arin = A.arin;
     if (A.ws_counters) { P.counters = A.ws_counters; P.scratch = A.ws_scratch; }
     else if (int rc = workspace_region(dev, &P.counters, &P.scratch)) return rc;
     {
@@ -333,6 +334,69 @@ AMP_API int amp_exl3_gemv_allreduce(const void* x, const void* trellis, void* ou
     }
     A.ar.ctl = ctls[rank];
     A.ar.rank = rank; A.ar.N = N; A.ar.wcap = cap / 2;
+    return launch_gemv(A, stream);
+}
+
+// ---- split exchange: the producer only pushes, the consumer gathers in its x~ prologue ----
+// amp_exl3_gemv_push: a row-parallel linear whose finished column blocks are pushed, as fp16
+// partials, into every rank's all-reduce buffer (this rank's included); nothing waits and no output
+// tensor is written. The launch that consumes the sum (amp_exl3_gemv_gathered /
+// amp_exl3_mgemm_gathered) adds the ranks' partials up while it rotates its input.
+AMP_API int amp_exl3_gemv_push(const void* x, const void* trellis, const void* suh, const void* svh,
+                               int m, int k, int n, int K, int cb, void* const* bufs, int* const* ctls,
+                               int rank, int N, long cap, cudaStream_t stream)
+{
+    AMP_REQUIRE(N >= 2 && N <= COMM_MAXN && rank >= 0 && rank < N, "exl3_gemv_push: bad rank / world size (2..%d ranks)", COMM_MAXN);
+    AMP_REQUIRE(bufs && ctls, "exl3_gemv_push: null buffer table");
+    AMP_REQUIRE(cap > 0 && cap % 8 == 0 && (long) m * n <= cap, "exl3_gemv_push: m * n exceeds the communicator's capacity");
+    // the kernel never writes through `c` in this mode; the pointer only has to pass the checks
+    GemvLaunch A = direct(x, trellis, (void*) x, suh, svh, m, k, n, K, cb, 0, 0, 0);
+    for (int p = 0; p < N; ++p)
+    {
+        AMP_REQUIRE(bufs[p] && ctls[p], "exl3_gemv_push: null buffer of rank %d", p);
+        A.ar.buf[p] = (uint2*) bufs[p];
+    }
+    A.ar.ctl = ctls[rank];
+    A.ar.rank = rank; A.ar.N = N; A.ar.wcap = cap / 2; A.ar.push_only = 1;
+    return launch_gemv(A, stream);
+}
+
+static int arin_fill(GemvLaunch& A, const void* buf, int* ctl, int N, long cap, int m, int k)
+{
+    AMP_REQUIRE(N >= 2 && N <= COMM_MAXN && buf && ctl, "exl3_gemv_gathered: bad communicator arguments (2..%d ranks)", COMM_MAXN);
+    AMP_REQUIRE(cap > 0 && cap % 8 == 0 && (long) m * k <= cap, "exl3_gemv_gathered: m * k exceeds the communicator's capacity");
+    A.arin.buf = (const uint2*) buf; A.arin.ctl = ctl; A.arin.N = N; A.arin.wcap = cap / 2;
+    return 0;
+}
+
+// c (m, n) = the linear of the all-reduced input: x (m, k) is the sum of the partials the ranks
+// pushed with their last amp_exl3_gemv_push on this communicator (payload (m, k)); buf / ctl are
+// THIS rank's buffer and control block.
+AMP_API int amp_exl3_gemv_gathered(const void* trellis, void* c, const void* suh, const void* svh,
+                                   int m, int k, int n, int K, int cb, int c_fp32,
+                                   const void* buf, int* ctl, int N, long cap, cudaStream_t stream)
+{
+    GemvLaunch A = direct(nullptr, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, 0, 0);
+    if (int rc = arin_fill(A, buf, ctl, N, cap, m, k)) return rc;
+    return launch_gemv(A, stream);
+}
+
+// the bundle form (amp_exl3_mgemm's tables) with the gathered input
+AMP_API int amp_exl3_mgemm_gathered(const void* trellis_ptrs, void* C, const void* suh_ptrs, const void* svh_ptrs,
+                                    int num, int m, int k, int width, int K, int cb, int c_fp32,
+                                    const void* c_ptrs, const void* n_stride_list, const void* had_src_list,
+                                    const void* buf, int* ctl, int N, long cap, cudaStream_t stream)
+{
+    if (num == 0 || m == 0) return 0;
+    AMP_REQUIRE(num > 0, "exl3_mgemm_gathered: negative matrix count");
+    GemvLaunch A = {};
+    A.c = C;
+    A.t_trellis = (const long long*) trellis_ptrs; A.t_suh = (const long long*) suh_ptrs;
+    A.t_svh = (const long long*) svh_ptrs; A.t_c = (const long long*) c_ptrs;
+    A.t_stride = (const int*) n_stride_list; A.t_src = (const int*) had_src_list;
+    A.tables = 1; A.slices = num; A.width = width; A.stride = width;
+    A.m = m; A.k = k; A.K = K; A.cb = cb; A.c_fp32 = c_fp32;
+    if (int rc = arin_fill(A, buf, ctl, N, cap, m, k)) return rc;
     return launch_gemv(A, stream);
 }
 

@@ -19,6 +19,7 @@ struct GemvLaunch
     float* ws_scratch;   // per-device workspace (both or neither); ws_max_ctas bounds the CTA count
     int ws_max_ctas;
     GemvAr ar;           // fused tensor-parallel all-reduce of the output (ar.N == 0: none)
+    GemvArIn arin;       // the input is gathered from the communicator's buffer (arin.N == 0: plain x)
 };
 
 int launch_gemv(const GemvLaunch& A, cudaStream_t stream);

@@ -12,8 +12,15 @@
 
 namespace amp {
 
-gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB, int mode)
+gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB, int mode, int gin)
 {
+    // input gathered from the all-reduce buffers (split exchange)
+    static const gemv_fn fng[3][2] =
+    {
+        { exl3_gemv_kernel<AMP_GEMV_K, 0, 1, 0, 1>, exl3_gemv_kernel<AMP_GEMV_K, 0, 2, 0, 1> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 1, 1, 0, 1>, exl3_gemv_kernel<AMP_GEMV_K, 1, 2, 0, 1> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 0, 1>, exl3_gemv_kernel<AMP_GEMV_K, 2, 2, 0, 1> },
+    };
     static const gemv_fn fn[3][2] =
     {
         { exl3_gemv_kernel<AMP_GEMV_K, 0, 1>, exl3_gemv_kernel<AMP_GEMV_K, 0, 2> },
@@ -27,8 +34,8 @@ gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB, int mode)
         { exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 1>, exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 2> },
     };
     if (cb < 0 || cb > 2 || MB < 1 || MB > 2 || mode < 0 || mode > 2) return nullptr;
-    if (mode) return MB == 1 ? moe[cb][mode - 1] : nullptr;
-    return fn[cb][MB - 1];
+    if (mode) return (MB == 1 && !gin) ? moe[cb][mode - 1] : nullptr;
+    return gin ? fng[cb][MB - 1] : fn[cb][MB - 1];
 }
 
 // tensor-memory form (dense / bundle launches of up to eight rows)

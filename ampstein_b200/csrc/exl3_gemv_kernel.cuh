@@ -83,6 +83,21 @@ struct GemvAr
     int* ctl;                   // this rank's control block
     int rank, N;                // N == 0: no exchange
     long wcap;                  // LL words per (slot, sender) = cap / 2
+    int push_only;              // 1: push the partial to every rank (this one included) and do not
+                                // gather: the consumer adds the ranks' partials up (GemvArIn)
+};
+
+// Input side of the split exchange: the (m, k) input of this launch is the all-reduce of the
+// partials that the ranks' previous launches pushed (GemvAr::push_only): every x value is
+// gathered from this rank's own buffer (N flag-in-data words per unit of four values), added up in
+// fp32 in rank order and rounded once -- the bits the stand-alone all-reduce would have written --
+// inside the x~ prologue, while this launch's weight stream is already in flight.
+struct GemvArIn
+{
+    const uint2* buf;           // this rank's buffer
+    int* ctl;                   // this rank's control block
+    int N;                      // N == 0: plain input
+    long wcap;
 };
 
 struct GemvParams
@@ -114,6 +129,7 @@ struct GemvParams
     int* status;                // device status word (the kernel has no waits that can run out; kept for the ABI)
     GemvMoe moe;                // grouped-expert modes only
     GemvAr ar;                  // MODE 0, fp16 output only
+    GemvArIn arin;              // MODE 0: x is gathered from the communicator's buffer
 };
 
 // A ring slot holds one unit of one warp: four tile rows (the 64-row group) of GEMV_NT adjacent
@@ -127,14 +143,15 @@ __host__ __device__ constexpr int gemv_stages(int K) { return K <= 4 ? 8 : (K <=
 // byte offsets inside dynamic shared memory
 struct GemvSmem
 {
-    int part, xd, gsum, ring, xchg, total;
+    int part, xd, gsum, ring, xchg, stage, total;
 };
 
 // 32-bit words per batch row of the duplicated x~ (+16 keeps fragment loads conflict-free)
 __host__ __device__ constexpr int gemv_xpitch(int xgroups) { return xgroups * 64 + 16; }
 
 // xrows: rows of x~ / partial sums kept (the batch size m)
-__host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int xgroups, int cluster = 0)
+// stage: reserve room for the gathered input of one chunk (split exchange), fp16 [xrows][xgroups * 64]
+__host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int xgroups, int cluster = 0, int stage = 0)
 {
     GemvSmem L;
     L.part = 0;                                             // [xrows][128] fp32: the finished block
@@ -143,7 +160,8 @@ __host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int xgrou
     L.ring = L.gsum + xrows * xgroups * 4;
     L.ring = (L.ring + 127) & ~127;
     L.xchg = L.ring + GEMV_WARPS * gemv_stages(K) * gemv_slot_bytes(K);   // [cluster][xrows][128] fp32, filled by the cluster's CTAs
-    L.total = L.xchg + cluster * xrows * 128 * 4;
+    L.stage = L.xchg + cluster * xrows * 128 * 4;
+    L.total = L.stage + (stage ? xrows * xgroups * 128 : 0);
     return L;
 }
 
@@ -365,15 +383,64 @@ struct GemvSplit
     }
 };
 
+// All-reduced input of one x~ chunk (split exchange) into a staging area: `total` units of four
+// values, `upr` units per batch row starting at unit `first` of each row. A unit is the N ranks'
+// flag-in-data words; U units per thread are in flight at a time: all their words are loaded at
+// once, the ones not yet there are polled with a bound, then fp32 sum in rank order and one
+// rounding -- the stand-alone all-reduce's arithmetic.
+template <int U, int NMAX>
+__device__ __forceinline__ void gather_chunk(half4* stage, const uint2* gbase, int N, long wcap, uint32_t seq, int* ctl,
+                                             int total, int upr, long row_units, long first, int t)
+{
+    for (int u = t; u < total; u += U * GEMV_THREADS)
+    {
+        uint32_t v[U][NMAX][4];
+        const uint2* src[U];
+        #pragma unroll
+        for (int i = 0; i < U; ++i)
+        {
+            const int ui = u + i * GEMV_THREADS;
+            if (ui >= total) continue;
+            const int b = ui / upr;
+            src[i] = gbase + 2 * ((long) b * row_units + first + (ui - b * upr));
+            #pragma unroll
+            for (int p = 0; p < NMAX; ++p)
+                if (p < N) ld_ll2_once(src[i] + (long) p * wcap, v[i][p]);
+        }
+        #pragma unroll
+        for (int i = 0; i < U; ++i)
+        {
+            const int ui = u + i * GEMV_THREADS;
+            if (ui >= total) continue;
+            unsigned budget = COMM_SPIN_LIMIT;
+            float acc[4] = { 0.f, 0.f, 0.f, 0.f };
+            #pragma unroll
+            for (int p = 0; p < NMAX; ++p)
+            {
+                if (p >= N) continue;
+                uint32_t d0 = v[i][p][0], d1 = v[i][p][2];
+                if (v[i][p][1] != seq || v[i][p][3] != seq)
+                    if (!ld_ll2(src[i] + (long) p * wcap, seq, &d0, &d1, budget)) { atomicExch(ctl + COMM_MAXB, 1); d0 = d1 = 0; }
+                acc4(acc, d0, d1);
+            }
+            half4 r;
+            r.x = __floats2half2_rn(acc[0], acc[1]);
+            r.y = __floats2half2_rn(acc[2], acc[3]);
+            stage[ui] = r;
+        }
+    }
+}
+
 // MODE 0: one matrix or a bundle sharing one input.  MODE 1: grouped expert gate/up (slice = expert
 // run x projection, input rows gathered by token).  MODE 2: grouped expert down (input = the
 // activation of the run's gate/up rows, computed on the fly).
-template <int K, int CB, int MB, int MODE = 0>
+// GIN: MODE 0 instance whose input is gathered from the all-reduce buffers (GemvArIn)
+template <int K, int CB, int MB, int MODE = 0, int GIN = 0>
 __global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 3))
 void exl3_gemv_kernel(const GemvParams P)
 {
     extern __shared__ __align__(128) unsigned char smem[];
-    const GemvSmem L = gemv_smem_layout(K, P.m, P.xgroups, P.cluster);
+    const GemvSmem L = gemv_smem_layout(K, P.m, P.xgroups, P.cluster, GIN);
     const int XPITCH = gemv_xpitch(P.xgroups);
     const int XG = P.xgroups;
     float* part = reinterpret_cast<float*>(smem + L.part);
@@ -607,7 +674,7 @@ void exl3_gemv_kernel(const GemvParams P)
                     if ((lane & 15) == 0) gsum[b * XG + 2 * jb + (lane >> 4)] = sg;
                 }
             };
-            if constexpr (MODE == 0)
+            if constexpr (MODE == 0 && !GIN)
             {
                 // up to six tasks per pass: all their loads are in flight before the first
                 // transform (at grid start a load takes a microsecond), and the weight stream is
@@ -656,6 +723,29 @@ void exl3_gemv_kernel(const GemvParams P)
             }
             else
             {
+                if constexpr (MODE == 0)
+                {
+                    // Gathered input (split exchange): the whole CTA adds up the ranks' partials of this
+                    // chunk's rows, two units per thread in flight, into a staging area. The local
+                    // producer has completed (stream order / the wait for the predecessor), so its
+                    // sequence number is final; the peers' words may still be on their way.
+                    if (!waited) { if (P.pdl) pdl_wait(); waited = true; }
+                    const uint32_t seq_in = (uint32_t) *(volatile int*) &P.arin.ctl[0];
+                    const uint2* gbase = P.arin.buf + (long) (seq_in & 1) * P.arin.N * P.arin.wcap;
+                    half4* stage = reinterpret_cast<half4*>(smem + L.stage);
+                    const int upr = nblk * 32;                      // units per batch row in this chunk
+                    const long first = (long) cg0 * 16, row_units = k >> 2;
+                    if (P.arin.N <= 2) gather_chunk<4, 2>(stage, gbase, P.arin.N, P.arin.wcap, seq_in, P.arin.ctl, nrows * upr, upr, row_units, first, t);
+                    else if (P.arin.N <= 4) gather_chunk<2, 4>(stage, gbase, P.arin.N, P.arin.wcap, seq_in, P.arin.ctl, nrows * upr, upr, row_units, first, t);
+                    else gather_chunk<1, COMM_MAXN>(stage, gbase, P.arin.N, P.arin.wcap, seq_in, P.arin.ctl, nrows * upr, upr, row_units, first, t);
+                    if (!started)
+                    {
+                        #pragma unroll
+                        for (int j = 0; j < S - 1; ++j) issue();
+                        started = true;
+                    }
+                    __syncthreads();
+                }
                 int b = 0, jb = warp;
                 while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
                 while (b < nrows)
@@ -664,8 +754,8 @@ void exl3_gemv_kernel(const GemvParams P)
                     float h0, h1, h2, h3;
                     if constexpr (MODE == 0)
                     {
-                        half4 v = *reinterpret_cast<const half4*>(P.x + (size_t) b * k + col);
                         half4 sc = *reinterpret_cast<const half4*>(suh + col);
+                        half4 v = reinterpret_cast<const half4*>(smem + L.stage)[b * (nblk * 32) + jb * 32 + lane];
                         v.x = __hmul2(v.x, sc.x);
                         v.y = __hmul2(v.y, sc.y);
                         h0 = __low2float(v.x); h1 = __high2float(v.x); h2 = __low2float(v.y); h3 = __high2float(v.y);
@@ -923,8 +1013,9 @@ void exl3_gemv_kernel(const GemvParams P)
                             const long slot_off = (long) (seq & 1) * P.ar.N * P.ar.wcap;
                             const uint2 mine = *reinterpret_cast<const uint2*>(&o);
                             for (int p = 0; p < P.ar.N; ++p)
-                                if (p != P.ar.rank)
+                                if (p != P.ar.rank || P.ar.push_only)
                                     st_ll2(P.ar.buf[p] + slot_off + (long) P.ar.rank * P.ar.wcap + 2 * unit, mine.x, mine.y, seq);
+                            if (P.ar.push_only) continue;           // the consumer adds the partials up
                             uint2* srcs[COMM_MAXN];
                             #pragma unroll
                             for (int p = 0; p < COMM_MAXN; ++p)
@@ -973,7 +1064,7 @@ typedef void (*gemv_fn)(const GemvParams);
 
 // one lookup function per K, defined by the per-K translation units: (cb, MB, mode) -> kernel
 // (grouped-expert modes exist for MB == 1 only: a run holds at most eight rows)
-#define AMP_GEMV_LOOKUP_DECL(K) gemv_fn gemv_kernel_k##K(int cb, int MB, int mode);
+#define AMP_GEMV_LOOKUP_DECL(K) gemv_fn gemv_kernel_k##K(int cb, int MB, int mode, int gin);
 AMP_GEMV_LOOKUP_DECL(1) AMP_GEMV_LOOKUP_DECL(2) AMP_GEMV_LOOKUP_DECL(3) AMP_GEMV_LOOKUP_DECL(4)
 AMP_GEMV_LOOKUP_DECL(5) AMP_GEMV_LOOKUP_DECL(6) AMP_GEMV_LOOKUP_DECL(7) AMP_GEMV_LOOKUP_DECL(8)
 #undef AMP_GEMV_LOOKUP_DECL

@@ -16,9 +16,10 @@ With N > 1 GPUs (one process per GPU under torchrun) the stack is decoded tensor
 reference shards it: q|k|v and gate|up column-parallel, o and down row-parallel, each followed
 by the fp16 all-reduce of the hidden state over NVLink (this library's kernel, inside the graph);
 lm_head is split by vocabulary. All ranks decode the same token, so the work is fixed as N grows
-(strong scaling). Before timing, every rank checks the fused o_proj / down_proj of layer 0 against
-the fp32 rank-order sum (rounded once) of the gathered partial products. `--mode replicas` runs N
-independent copies of the 1-GPU step instead.
+(strong scaling). Before timing, every rank checks the exchange after o_proj / down_proj of layer 0
+against the fp32 rank-order sum (rounded once) of the gathered partial products. `--exchange` picks
+its form: fused into the producer (default), split between producer and consumer, or a launch of
+its own. `--mode replicas` runs N independent copies of the 1-GPU step instead.
 
 One JSON line on stdout (rank 0). The `--steps` block is repeated until at least a second has
 been timed and the median block is reported. `--impl reference` times the CPU restatement of the
@@ -230,31 +231,51 @@ def run_decode(args, S):
     gu = [Multi([L["gate"], L["up"]], bufs["gu"]) for L in layers]
     launches = [0]
 
+    exchange = args.exchange if comm is not None else None
+
     def step(stub=False):
         # stub: the row-parallel linears without their all-reduce (to price the exchange)
         x = h_in
         n = 0
+        mode = None if stub else exchange
+        pushed = False                                   # split: the hidden state is still in the exchange buffers
+        last = len(layers) - 1
         for i, L in enumerate(layers):
-            qkv[i].run(x)
-            if comm is None or stub:
+            if pushed:
+                comm.gathered_bundle(qkv[i], m)
+            else:
+                qkv[i].run(x)
+            if mode is None:
                 L["o"].forward(bufs["q"][0], bufs["a"][0])        # attention itself is outside the path
-            elif args.unfused:
+                gu[i].run(bufs["a"])
+            elif mode == "separate":
                 L["o"].forward(bufs["q"][0], bufs["a_part"][0])
                 comm.allreduce(bufs["a_part"], out=bufs["a"])
-            else:
+                gu[i].run(bufs["a"])
+            elif mode == "fused":
                 comm.linear_allreduce(L["o"], bufs["q"][0], bufs["a"][0])
-            gu[i].run(bufs["a"])
-            if comm is None or stub:
+                gu[i].run(bufs["a"])
+            else:
+                comm.linear_push(L["o"], bufs["q"][0])
+                comm.gathered_bundle(gu[i], m)
+            pushed = False
+            if mode is None:
                 L["down"].forward(bufs["gu"][0], bufs["h"][0])
-            elif args.unfused:
+            elif mode == "separate":
                 L["down"].forward(bufs["gu"][0], bufs["h_part"][0])
                 comm.allreduce(bufs["h_part"], out=bufs["h"])
+            elif mode == "fused" or (i == last and head is None):
+                comm.linear_allreduce(L["down"], bufs["gu"][0], bufs["h"][0])     # (split: the step's output must exist)
             else:
-                comm.linear_allreduce(L["down"], bufs["gu"][0], bufs["h"][0])
-            n += 6 if (comm is not None and args.unfused and not stub) else 4
+                comm.linear_push(L["down"], bufs["gu"][0])
+                pushed = True
+            n += 6 if mode == "separate" else 4
             x = bufs["h"]
         if head:
-            head.forward(x[0], out_buf)
+            if pushed:
+                comm.gathered_linear(head, out_buf)
+            else:
+                head.forward(x[0], out_buf)
             n += 1
         if not stub:
             launches[0] = n
@@ -297,8 +318,14 @@ def run_decode(args, S):
             comm.linear_allreduce(layers[0][name], xin, fused)
             sep = torch.empty((1, m, H), **f16)
             comm.allreduce(part.view(1, m, H), out=sep)
+            # split form: push, then a consumer that gathers; the consumer applied to `want` must agree
+            comm.linear_push(layers[0][name], xin)
+            got = torch.empty((m, shapes["q"][1]), **f16)
+            comm.gathered_linear(layers[0]["q"], got)
+            ref = torch.empty_like(got)
+            layers[0]["q"].forward(want, ref)
             torch.cuda.synchronize()
-            ok = ok and torch.equal(fused, want) and torch.equal(sep[0], want)
+            ok = ok and torch.equal(fused, want) and torch.equal(sep[0], want) and torch.equal(got, ref)
         flag = torch.tensor([1 if ok else 0], device=device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if int(flag.item()) != 1:
@@ -369,7 +396,8 @@ def run_decode(args, S):
         "config": {"workload": wl,
                    "l2": "inputs larger than L2 (%.2f GB of weights streamed per step and GPU)" % (bytes_step / 1e9),
                    "parallelism": ("tp%d: column-parallel q|k|v, gate|up; row-parallel o, down with the fp16 all-reduce (%d per step) over NVLink %s%s"
-                                   % (tp, 2 * S["layers"], "as separate launches" if args.unfused else "fused into the GEMV epilogue",
+                                   % (tp, 2 * S["layers"], {"separate": "as separate launches", "fused": "fused into the GEMV epilogue",
+                                                              "split": "pushed from the GEMV epilogue and gathered in the consuming GEMV's prologue"}[args.exchange],
                                       "; lm_head by vocabulary" if head else "")) if tp > 1 else ("replicas x%d" % world),
                    "timing": "median of %d blocks of %d steps (%.2f s timed)" % (nblk, args.steps, tot / 1e3)},
         "e2e": {"value": round(tok_s_e2e, 2), "unit": UNIT,
@@ -673,8 +701,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--mode", default="tp", choices=["tp", "replicas"],
                     help="with --gpus N > 1: tensor-parallel decode of one stack (default) or N independent replicas")
-    ap.add_argument("--unfused", action="store_true",
-                    help="tensor-parallel mode: separate all-reduce launches instead of the GEMV's fused exchange")
+    ap.add_argument("--exchange", default="fused", choices=["split", "fused", "separate"],
+                    help="tensor-parallel mode: how the all-reduce after o / down runs. fused (default): push and gather in the "
+                         "producing GEMV's epilogue; split: the producer only pushes its partial, the consuming GEMV adds the ranks' "
+                         "partials up in its prologue (measured slower); separate: a stand-alone all-reduce launch")
     ap.add_argument("--workload", default="decode", choices=["decode", "tp5", "prefill", "moe", "issue"],
                     help="decode (default, the headline step), tp5 (the 64-layer 5-bit tensor-parallel stack), or a secondary "
                          "one-GPU workload: the prefill GEMM / the fused decode MoE / the issue-rate microbenchmark")

@@ -275,6 +275,30 @@ int amp_comm_allreduce_fp16(const void* x, void* out, void* const* bufs, int* co
 int amp_exl3_gemv_allreduce(const void* x, const void* trellis, void* out, const void* suh, const void* svh,
                             int m, int k, int n, int K, int cb, void* const* bufs, int* const* ctls,
                             int rank, int N, long cap, cudaStream_t stream);
+/*
+ * The same exchange split between producer and consumer, so that no kernel waits for a peer
+ * while its own rank could move on: amp_exl3_gemv_push is the row-parallel linear whose finished
+ * 128-column blocks are pushed as fp16 partials into EVERY rank's buffer (its own included) and
+ * which writes no output tensor; the launch that consumes the all-reduced hidden state
+ * (amp_exl3_gemv_gathered, or amp_exl3_mgemm_gathered for a q|k|v or gate|up bundle) has no x
+ * argument: it adds the ranks' partials up (fp32, rank order, one rounding: the bits
+ * amp_comm_allreduce_fp16 would give) while it rotates its input, with its weight stream already
+ * in flight. buf / ctl of the gathered forms are THIS rank's buffer and control block; the
+ * payload is (m, k) of the consumer = (m, n) of the producer, m * k <= cap. A push must be
+ * followed by exactly one gathering launch on every rank before the next call on the
+ * communicator. Waits are bounded (amp_comm_status). The reference has no counterpart: its
+ * all-reduce is a kernel of its own between the two (src/ucode/ampstein/qwen35_tp.uc:356,368).
+ */
+int amp_exl3_gemv_push(const void* x, const void* trellis, const void* suh, const void* svh,
+                       int m, int k, int n, int K, int cb, void* const* bufs, int* const* ctls,
+                       int rank, int N, long cap, cudaStream_t stream);
+int amp_exl3_gemv_gathered(const void* trellis, void* c, const void* suh, const void* svh,
+                           int m, int k, int n, int K, int cb, int c_fp32,
+                           const void* buf, int* ctl, int N, long cap, cudaStream_t stream);
+int amp_exl3_mgemm_gathered(const void* trellis_ptrs, void* C, const void* suh_ptrs, const void* svh_ptrs,
+                            int num, int m, int k, int width, int K, int cb, int c_fp32,
+                            const void* c_ptrs, const void* n_stride_list, const void* had_src_list,
+                            const void* buf, int* ctl, int N, long cap, cudaStream_t stream);
 long amp_comm_buffer_bytes(int N, long cap);
 long amp_comm_ctl_bytes(void);
 int amp_comm_blocks(int N, long n);

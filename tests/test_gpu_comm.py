@@ -156,3 +156,78 @@ def test_fused_linear_allreduce_matches_gemv_then_allreduce(oracle):
         for r in range(N):
             assert comm.status(r) == 0
         comm.close()
+
+
+def test_split_exchange_push_then_gather_in_the_consumer(oracle):
+    """The exchange split between producer and consumer: every rank's row-parallel linear only
+    pushes its partial (linear_push); the next linear / bundle adds the ranks' partials up inside
+    its input rotation (gathered_linear / gathered_bundle). The consumer's output must equal, bit
+    for bit, the same linear applied to the stand-alone all-reduce of the partials; plain and fused
+    all-reduce calls on the same communicator stay in step. Batches 1 and 3, a stacked and a
+    sliced bundle as consumers."""
+    if ngpu() < 2:
+        pytest.skip("needs at least two GPUs")
+    from conftest import make_linear
+    from ampstein_b200.comm import p2p_comm
+    from ampstein_b200.models import LinearEXL3, Multi, Sliced
+
+    def lin_on(k, n, seed, d, scale=40.0):
+        t, su, sv, _ = make_linear(k, n, 4, seed=seed)
+        sv = (sv.astype(np.float32) / scale).astype(np.float16)
+        return LinearEXL3(torch.from_numpy(t.view(np.int16)).to(d), torch.from_numpy(su).to(d), torch.from_numpy(sv).to(d))
+
+    for N in sorted({2, min(ngpu(), 8)}):
+        hidden = 512
+        comm = p2p_comm(list(range(N)), 3 * hidden)
+        for call, (k_local, m) in enumerate([(1024, 1), (256, 3), (2048, 2)]):
+            prod, xs, cons, bund, sl = [], [], [], [], []
+            for r in range(N):
+                d = "cuda:%d" % r
+                prod.append(lin_on(k_local, hidden, 9000 + 10 * call + r, d))
+                xs.append(torch.randn((m, k_local), generator=torch.Generator().manual_seed(call * 10 + r)).to(torch.float16).to(d))
+                cons.append(lin_on(hidden, 384, 9100 + call, d, 30.0))                       # the same consumer on every rank
+                g, u = lin_on(hidden, 256, 9200 + call, d, 30.0), lin_on(hidden, 256, 9300 + call, d, 30.0)
+                bund.append(Multi([g, u], torch.empty((2, m, 256), dtype=torch.float16, device=d)))
+                q, kk = lin_on(hidden, 512, 9400 + call, d, 30.0), lin_on(hidden, 128, 9500 + call, d, 30.0)
+                sl.append(Sliced([q, kk], [torch.empty((1, m, 512), dtype=torch.float16, device=d),
+                                           torch.empty((1, m, 128), dtype=torch.float16, device=d)]))
+            # the all-reduced hidden state by the stand-alone path
+            parts = [prod[r].forward(xs[r]) for r in range(N)]
+            summed = [comm.allreduce(parts[r].view(-1), r).view(m, hidden) for r in range(N)]
+            for consumer in ("linear", "multi", "sliced"):
+                for r in range(N):
+                    comm.linear_push(prod[r], xs[r], r)
+                outs, want = [], []
+                for r in range(N):
+                    d = "cuda:%d" % r
+                    if consumer == "linear":
+                        y = torch.full((m, 384), float("nan"), dtype=torch.float16, device=d)
+                        comm.gathered_linear(cons[r], y, r)
+                        outs.append([y])
+                        want.append([cons[r].forward(summed[r])])
+                    elif consumer == "multi":
+                        bund[r].out.fill_(float("nan"))
+                        comm.gathered_bundle(bund[r], m, r)
+                        outs.append([bund[r].out.clone()])
+                        bund[r].run(summed[r].view(1, m, hidden))
+                        want.append([bund[r].out.clone()])
+                    else:
+                        comm.gathered_bundle(sl[r], m, r)
+                        outs.append([o.clone() for o in sl[r].outs])
+                        sl[r].run(summed[r].view(1, m, hidden))
+                        want.append([o.clone() for o in sl[r].outs])
+                for r in range(N):
+                    torch.cuda.synchronize(r)
+                for r in range(N):
+                    for a, b in zip(outs[r], want[r]):
+                        assert torch.equal(a.cpu(), b.cpu()), (N, call, consumer, r)
+                # a fused call in between keeps the sequence numbers of all call kinds in step
+                fused = [torch.empty((m, hidden), dtype=torch.float16, device="cuda:%d" % r) for r in range(N)]
+                for r in range(N):
+                    comm.linear_allreduce(prod[r], xs[r], fused[r], r)
+                for r in range(N):
+                    torch.cuda.synchronize(r)
+                    assert torch.equal(fused[r].cpu(), summed[r].cpu())
+        for r in range(N):
+            assert comm.status(r) == 0
+        comm.close()
