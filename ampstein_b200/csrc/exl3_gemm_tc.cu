@@ -40,6 +40,7 @@
 #include "exl3_gemv_kernel.cuh"
 #include "exl3_gemv_host.h"
 #include "host_common.h"
+#include <mutex>
 
 namespace amp {
 
@@ -881,7 +882,11 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
     P.xt = (const unsigned char*) xh; P.trellis = (const uint16_t*) trellis; P.svh = (const __half*) svh; P.c = c;
     P.M = M; P.k = k; P.n = n; P.c_fp32 = c_fp32;
     {
+        // address of the status word, looked up once per device (under a lock: two host threads
+        // may make their first launch on a device at the same time)
         static int* status_ptr[64] = {};
+        static std::mutex status_mu;
+        std::lock_guard<std::mutex> lock(status_mu);
         int*& sp = status_ptr[dev & 63];
         if (!sp)
             if (cudaError_t e = cudaGetSymbolAddress((void**) &sp, g_tc_status)) return cuda_rc(e, "status symbol");

@@ -253,8 +253,11 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     if (A.ws_counters) { P.counters = A.ws_counters; P.scratch = A.ws_scratch; }
     else if (int rc = workspace_region(dev, &P.counters, &P.scratch)) return rc;
     {
-        // address of the status word, looked up once per device
+        // address of the status word, looked up once per device (under a lock: two host threads
+        // may make their first launch on a device at the same time)
         static int* status_ptr[64] = {};
+        static std::mutex status_mu;
+        std::lock_guard<std::mutex> lock(status_mu);
         int*& sp = status_ptr[dev & 63];
         if (!sp)
             if (cudaError_t e = cudaGetSymbolAddress((void**) &sp, g_gemv_status)) return cuda_rc(e, "status symbol");

@@ -41,6 +41,38 @@ void had_r_128_bf16_kernel(const __nv_bfloat16* __restrict__ in, __half* __restr
     reinterpret_cast<half4*>(out)[chunk * 32 + lane] = o;
 }
 
+// fp32 rows in, fp16 rows out (the form the reference's GEMM epilogue uses on its fp32
+// accumulators, had_fh_r_128_inner, vendor/exl3/exllamav3_ext/quant/hadamard_inner.cuh:216-279):
+// fp32 pre-scale and transform, one rounding to fp16, fp16 post-scale
+__global__ __launch_bounds__(256)
+void had_r_128_fh_kernel(const float* __restrict__ in, __half* __restrict__ out,
+                         const __half* __restrict__ pre, const __half* __restrict__ post,
+                         long chunks, int chunks_per_row, float r_scale)
+{
+    const int lane = threadIdx.x & 31;
+    const long chunk = (long) blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (chunk >= chunks) return;
+    const int cb = (int) (chunk % chunks_per_row);
+    const float4 v = reinterpret_cast<const float4*>(in)[chunk * 32 + lane];
+    float h0 = v.x, h1 = v.y, h2 = v.z, h3 = v.w;
+    if (pre)
+    {
+        half4 s = reinterpret_cast<const half4*>(pre)[cb * 32 + lane];
+        h0 *= __low2float(s.x); h1 *= __high2float(s.x); h2 *= __low2float(s.y); h3 *= __high2float(s.y);
+    }
+    warp_had128(h0, h1, h2, h3, lane);
+    half4 o;
+    o.x = __floats2half2_rn(h0 * r_scale, h1 * r_scale);
+    o.y = __floats2half2_rn(h2 * r_scale, h3 * r_scale);
+    if (post)
+    {
+        half4 s = reinterpret_cast<const half4*>(post)[cb * 32 + lane];
+        o.x = __hmul2(o.x, s.x);
+        o.y = __hmul2(o.y, s.y);
+    }
+    reinterpret_cast<half4*>(out)[chunk * 32 + lane] = o;
+}
+
 template <bool F32>
 __global__ __launch_bounds__(256)
 void had_r_128_kernel(const void* __restrict__ in, void* __restrict__ out,
@@ -169,23 +201,25 @@ int launch_had_tiled(const void* in, void* out, const void* pre, long M, int k, 
 
 using namespace amp;
 
-// dtype: 0 = fp16 in/out, 1 = fp32 in/out, 2 = bf16 in / fp16 out. pre / post: fp16 vectors of
+// dtype: 0 = fp16 in/out, 1 = fp32 in/out, 2 = bf16 in / fp16 out, 3 = fp32 in / fp16 out. pre / post: fp16 vectors of
 // `cols` values or null.
 AMP_API int amp_had_r_128(const void* in, void* out, const void* pre, const void* post,
                              long rows, int cols, int dtype, float scale, cudaStream_t stream)
 {
-    AMP_REQUIRE(dtype >= 0 && dtype <= 2, "had_r_128: unsupported datatype");
+    AMP_REQUIRE(dtype >= 0 && dtype <= 3, "had_r_128: unsupported datatype");
     AMP_REQUIRE(rows >= 0 && cols >= 0 && cols % 128 == 0, "had_r_128: columns must be divisible by 128");
     if (rows == 0 || cols == 0) return 0;
     AMP_REQUIRE(in && out, "had_r_128: null pointer");
-    const uintptr_t amask = dtype == 1 ? 15 : 7;
-    AMP_REQUIRE(((uintptr_t) in & amask) == 0 && ((uintptr_t) out & amask) == 0, "had_r_128: misaligned pointer");
+    const uintptr_t imask = (dtype == 1 || dtype == 3) ? 15 : 7, omask = dtype == 1 ? 15 : 7;
+    AMP_REQUIRE(((uintptr_t) in & imask) == 0 && ((uintptr_t) out & omask) == 0, "had_r_128: misaligned pointer");
     AMP_REQUIRE(((uintptr_t) pre & 7) == 0 && ((uintptr_t) post & 7) == 0, "had_r_128: misaligned scale vector");
     const long chunks = rows * (cols / 128);
     const long blocks = (chunks + 7) / 8;
     AMP_REQUIRE(blocks <= 0x7fffffffL, "had_r_128: too many rows");
     const float rs = scale * kRScale;
-    if (dtype == 2)
+    if (dtype == 3)
+        had_r_128_fh_kernel<<<(unsigned) blocks, 256, 0, stream>>>((const float*) in, (__half*) out, (const __half*) pre, (const __half*) post, chunks, cols / 128, rs);
+    else if (dtype == 2)
         had_r_128_bf16_kernel<<<(unsigned) blocks, 256, 0, stream>>>((const __nv_bfloat16*) in, (__half*) out, (const __half*) pre, (const __half*) post, chunks, cols / 128, rs);
     else if (dtype)
         had_r_128_kernel<true><<<(unsigned) blocks, 256, 0, stream>>>(in, out, (const __half*) pre, (const __half*) post, chunks, cols / 128, rs);

@@ -81,13 +81,18 @@ def exl3_reconstruct_had(unpacked, packed, suh, svh, K, mul1=False, mcg=False, n
 
 def had_r_128(input, output, pre_scale=None, post_scale=None, scale=1.0):
     """output = blockwise H128(input [* pre_scale]) * scale / sqrt(128) [* post_scale]; fp16 or
-    fp32, may run in place (reference: had_r_128, .../quant/hadamard.cu:125-207)."""
+    fp32, may run in place; an fp32 input with an fp16 output runs the transform in fp32 and
+    rounds once (reference: had_r_128, .../quant/hadamard.cu:125-207; the mixed form is
+    had_fh_r_128_inner, .../quant/hadamard_inner.cuh:216-279)."""
     ts = [input, output] + [t for t in (pre_scale, post_scale) if t is not None]
     _check_cuda("had_r_128", *ts)
     if input.shape != output.shape or input.dim() != 2:
         raise ValueError("had_r_128: input and output must be 2-D and of one shape")
-    if input.dtype != output.dtype or input.dtype not in (torch.float16, torch.float32):
+    mixed = input.dtype == torch.float32 and output.dtype == torch.float16
+    if (input.dtype != output.dtype and not mixed) or input.dtype not in (torch.float16, torch.float32):
         raise TypeError("had_r_128: unsupported datatype")
+    if mixed and input.data_ptr() == output.data_ptr():
+        raise ValueError("had_r_128: the fp32 -> fp16 form cannot run in place")
     rows, cols = input.shape
     if cols % 128:
         raise ValueError("had_r_128: columns must be divisible by 128")
@@ -98,7 +103,7 @@ def had_r_128(input, output, pre_scale=None, post_scale=None, scale=1.0):
         _lib.call("amp_had_r_128", input.data_ptr(), output.data_ptr(),
                   pre_scale.data_ptr() if pre_scale is not None else None,
                   post_scale.data_ptr() if post_scale is not None else None,
-                  rows, cols, 1 if input.dtype == torch.float32 else 0, float(scale), _stream(input))
+                  rows, cols, 3 if mixed else (1 if input.dtype == torch.float32 else 0), float(scale), _stream(input))
     return output
 
 

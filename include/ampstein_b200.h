@@ -58,8 +58,9 @@ int amp_exl3_reconstruct_had(void* unpacked, const void* trellis, const void* su
 
 /*
  * Blockwise 128-point Hadamard of a (rows, cols) matrix, out = H(in [* pre]) * scale/sqrt(128)
- * [* post]; in place allowed. dtype 0 = fp16, 1 = fp32, 2 = bf16 in / fp16 out (not in place).
- * pre / post: fp16 (cols) or NULL.
+ * [* post]; in place allowed. dtype 0 = fp16, 1 = fp32, 2 = bf16 in / fp16 out, 3 = fp32 in / fp16
+ * out (2 and 3 not in place; 3 is the form the reference applies to fp32 accumulators,
+ * had_fh_r_128_inner, Q/hadamard_inner.cuh:216-279). pre / post: fp16 (cols) or NULL.
  * Replaces: had_r_128, Q/hadamard.cu:125-207.
  */
 int amp_had_r_128(const void* in, void* out, const void* pre, const void* post,
@@ -103,7 +104,7 @@ int amp_exl3_gemm_status(int* out);
 
 /*
  * The decode-batch kernel on its own, m = 1..16. The first call on a device allocates a
- * per-device workspace (about 70 MB: arrival counters and partial-sum slots) and must
+ * per-device workspace (64 MB + 256 KB: four regions of arrival counters and partial-sum slots) and must
  * therefore come before any stream capture; later calls allocate nothing.
  * Replaces: exl3_gemv_kernel / exl3_gemv_try_launch, Q/exl3_gemv_kernel.cuh:186-482,
  * Q/exl3_gemv.cu:92-184.
@@ -149,6 +150,8 @@ int amp_exl3_gemv_cfg(const void* x, const void* trellis, void* c, const void* s
  * and not used.
  * Replaces: exl3_mgemm, Q/exl3_gemm.cu:351-735 (binding torch.mgemm,
  * src/torch/amp_torch.cpp:10193-10322; bundle builders src/ucode/ampstein/models.uc:338-432).
+ * size_n_list of the reference's signature has no counterpart here: every slice is `width` columns
+ * wide (the reference's caller cuts matrices into equal slices, src/ucode/ampstein/models.uc:373-398).
  */
 int amp_exl3_mgemm(const void* x, const void* trellis_ptrs, void* C, const void* suh_ptrs,
                    void* A_had, const void* svh_ptrs, int num, int m, int k, int width,

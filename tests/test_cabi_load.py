@@ -44,7 +44,7 @@ def test_bad_arguments_return_codes_without_a_gpu():
     assert L.amp_exl3_gemv(p, p, p, p, p, 1, 64, 128, 4, 0, 0, None) < 0
     assert L.amp_exl3_gemv(p, p, p, None, p, 1, 128, 128, 4, 0, 0, None) < 0
     # Hadamard: bad dtype / columns
-    assert L.amp_had_r_128(p, p, None, None, 1, 128, 3, 1.0, None) < 0
+    assert L.amp_had_r_128(p, p, None, None, 1, 128, 4, 1.0, None) < 0
     assert L.amp_had_r_128(p, p, None, None, 1, 100, 0, 1.0, None) < 0
     # empty problems are a no-op
     assert L.amp_exl3_reconstruct(p, p, 0, 128, 4, 0, 0, 128, None) == 0

@@ -96,6 +96,12 @@ def test_had_r_128_bit_exact(amp, oracle):
     outf = torch.empty((5, 256), dtype=torch.float32, device="cuda")
     amp.had_r_128(dev(xf), outf, None, dev(post[:256]))
     assert np.array_equal(outf.cpu().numpy(), oracle.had_ff(xf, post=post[:256]))
+    # fp32 in, fp16 out: transform in fp32, one rounding, fp16 post-scale
+    outh = torch.empty((5, 256), dtype=torch.float16, device="cuda")
+    amp.had_r_128(dev(xf), outh, None, dev(post[:256]))
+    assert np.array_equal(host16(outh), oracle.had_fh(xf, post=post[:256]).view(np.uint16))
+    amp.had_r_128(dev(xf), outh)
+    assert np.array_equal(host16(outh), oracle.had_fh(xf).view(np.uint16))
     # in place
     t = dev(x)
     amp.had_r_128(t, t, dev(pre), None)
