@@ -43,7 +43,7 @@ SIGNATURES = {
     "amp_comm_ipc_close": [_vp],
     "amp_comm_free": [_vp],
     "amp_exl3_moe_coop": [_vp, _vp],
-    "amp_exl3_moe_coop_ctr_len": [_l],
+    "amp_exl3_moe_coop_ctr_len": [_l, _l, _l, _l],
     "amp_exl3_gemm_bf16": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "amp_exl3_gemm_status": [ctypes.POINTER(ctypes.c_int)],
     "amp_exl3_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],

@@ -60,36 +60,51 @@ static gemv_fn gemv_tc_kernel_for(int K, int cb, int ar)
     return nullptr;
 }
 
-// Per-device workspace of the decode kernels: arrival counters and partial-sum slots for column
-// blocks whose rows are shared between CTAs. Allocated on the first launch on a device (like
-// the reference's DevCtx lock buffer, vendor/exl3/exllamav3_ext/quant/exl3_devctx.cu:81-94), so
-// the first call on a device must come before stream capture. Launches rotate through
-// GEMV_REGIONS independent regions, so kernels that overlap on the GPU (other streams, graph
-// branches) do not share counters as long as fewer than GEMV_REGIONS are in flight.
-constexpr int GEMV_REGIONS = 4;
+// Workspace of the decode kernels: arrival counters and partial-sum slots for column blocks whose
+// rows are shared between CTAs. One region per (device, stream), allocated on the first launch on
+// that stream (like the reference's DevCtx lock buffer,
+// vendor/exl3/exllamav3_ext/quant/exl3_devctx.cu:81-94), so the first call on a stream must come
+// before any capture on it. Launches on one stream never use their region at the same time (a
+// launch touches it only after its predecessor has completed), and launches that overlap on the
+// GPU run on different streams (a side stream for the shared expert, parallel graph branches), so
+// they never share counters. Beyond GEMV_MAX_STREAMS streams per device regions are shared again.
+constexpr int GEMV_MAX_STREAMS = 16;
 constexpr int GEMV_MAX_BLOCKS = 16384;                       // column blocks per launch
 constexpr int GEMV_MAX_CTAS = 1024;
 constexpr size_t GEMV_COUNTER_BYTES = GEMV_MAX_BLOCKS * sizeof(int);
 constexpr size_t GEMV_SCRATCH_BYTES = (size_t) GEMV_MAX_CTAS * 2 * 16 * 128 * sizeof(float);
 constexpr size_t GEMV_REGION_BYTES = GEMV_COUNTER_BYTES + GEMV_SCRATCH_BYTES;
 
-struct Workspace { unsigned char* base = nullptr; unsigned seq = 0; };
+struct Workspace { cudaStream_t stream[GEMV_MAX_STREAMS]; unsigned char* base[GEMV_MAX_STREAMS]; int n = 0; };
 
-static int workspace_region(int dev, int** counters, float** scratch)
+static int workspace_region(int dev, cudaStream_t stream, int** counters, float** scratch)
 {
     static Workspace ws[64];
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
     Workspace& W = ws[dev & 63];
-    if (!W.base)
+    int idx = -1;
+    for (int i = 0; i < W.n; ++i)
+        if (W.stream[i] == stream) { idx = i; break; }
+    if (idx < 0 && W.n == GEMV_MAX_STREAMS) idx = (int) (((uintptr_t) stream >> 4) % GEMV_MAX_STREAMS);
+    if (idx < 0 && W.n > 0)
+    {
+        // a stream that is being captured cannot allocate: it borrows the first region (its launches
+        // then share counters with that stream's; warm the stream up before capture to avoid it)
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) idx = 0;
+    }
+    if (idx < 0)
     {
         void* p = nullptr;
-        if (cudaError_t e = cudaMalloc(&p, GEMV_REGION_BYTES * GEMV_REGIONS)) return cuda_rc(e, "exl3_gemv workspace");
-        if (cudaError_t e = cudaMemset(p, 0, GEMV_REGION_BYTES * GEMV_REGIONS)) return cuda_rc(e, "exl3_gemv workspace clear");
+        if (cudaError_t e = cudaMalloc(&p, GEMV_REGION_BYTES)) return cuda_rc(e, "exl3_gemv workspace");
+        if (cudaError_t e = cudaMemset(p, 0, GEMV_COUNTER_BYTES)) return cuda_rc(e, "exl3_gemv workspace clear");
         if (cudaError_t e = cudaDeviceSynchronize()) return cuda_rc(e, "exl3_gemv workspace sync");
-        W.base = (unsigned char*) p;
+        idx = W.n++;
+        W.stream[idx] = stream;
+        W.base[idx] = (unsigned char*) p;
     }
-    unsigned char* r = W.base + (size_t) (W.seq++ % GEMV_REGIONS) * GEMV_REGION_BYTES;
+    unsigned char* r = W.base[idx];
     *counters = (int*) r;
     *scratch = (float*) (r + GEMV_COUNTER_BYTES);
     return 0;
@@ -207,6 +222,15 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
         cluster = GEMV_CLUSTER;
         ncta = col_blocks * GEMV_CLUSTER;
     }
+    // Grouped launch for one token: the picks are known to be at most max_slices one-row runs, so
+    // the same form applies with the largest cluster that divides the row groups and fits the device
+    if (A.mode && A.moe.inline_runs && g_cluster)
+        for (int c = GEMV_CLUSTER; c >= 2 && !cluster; --c)
+            if (G % c == 0 && G / c >= 2 && col_blocks * c <= (long) D.sms * ctas_per_sm)
+            {
+                cluster = c;
+                ncta = col_blocks * c;
+            }
     if (A.force_split > 0) ncta = A.force_split;
     if (ncta > units) ncta = units;
     if (ncta > GEMV_MAX_CTAS) ncta = GEMV_MAX_CTAS;
@@ -251,7 +275,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     P.ar = A.ar;
     P.arin = A.arin;
     if (A.ws_counters) { P.counters = A.ws_counters; P.scratch = A.ws_scratch; }
-    else if (int rc = workspace_region(dev, &P.counters, &P.scratch)) return rc;
+    else if (int rc = workspace_region(dev, stream, &P.counters, &P.scratch)) return rc;
     {
         // address of the status word, looked up once per device (under a lock: two host threads
         // may make their first launch on a device at the same time)

@@ -71,7 +71,102 @@ struct GemvMoe
     float* d_out;               // (slots, Ho) fp32 down outputs (after svh and bias)
     int Hi, I, Ho;
     int act; float act_limit; int gated;
+    // routing, read on the device
+    const long long* sel; const __half* rw; int bsz;
+    int min_expert, max_expert, n_local;
+    int inline_runs;            // one token: every CTA derives the run table from sel / rw itself
+    // routing-weighted sum of a token's slot outputs, done by whichever CTA delivers the last of the
+    // token's picks for a 128-column chunk (MODE 2)
+    const int* need;            // [bsz] active local picks per token (inline_runs: derived in the kernel)
+    int* done;                  // [bsz][Ho / 128] arrivals, zero between calls
+    float* out; int out_stride, H_out;
+    const float* sh_out; const __half* sh_gate_w;
 };
+
+struct MoeSlot { int row, local; float w; bool active; };
+
+// one (token, pick) slot of the routing: the local expert index and weight, or inactive (weight
+// zero, expert outside this shard's range or tables)
+__device__ __forceinline__ MoeSlot moe_slot(const long long* sel, const __half* rw, int topk,
+                                            int min_expert, int max_expert, int n_local, int s)
+{
+    MoeSlot si;
+    si.row = s / topk;
+    long long e = sel[s];
+    si.w = __half2float(rw[s]);
+    bool ok = si.w != 0.0f;
+    if (min_expert >= 0)
+    {
+        ok = ok && e >= min_expert && e < max_expert;
+        e -= min_expert;
+    }
+    ok = ok && e >= 0 && e < n_local;
+    si.local = ok ? (int) e : 0;
+    si.active = ok;
+    return si;
+}
+
+// out[row, chunk] = sum over the row's active picks, in pick order, of weight * d_out[slot] (+ the
+// shared expert's output, optionally gated by sigmoid(x . w)): one warp, four columns per lane.
+// Reference: exl3_moe_coop_b_kernel's last-arrival epilogue, exl3_moe_coop_kernel.cuh:848-999.
+__device__ __forceinline__ void moe_combine_chunk(const GemvMoe& M, int row, int chunk, int lane)
+{
+    const int col = chunk * 128 + lane * 4;
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+    for (int k0 = 0; k0 < M.topk; k0 += 8)               // pick order: deterministic
+    {
+        // lane i < 8 reads pick k0 + i of the routing; then all eight slot rows are requested
+        // before the first is added (the loads would otherwise form a chain of L2 round trips)
+        MoeSlot mine; mine.active = false; mine.w = 0.f;
+        if (lane < 8 && k0 + lane < M.topk)
+            mine = moe_slot(M.sel, M.rw, M.topk, M.min_expert, M.max_expert, M.n_local, row * M.topk + k0 + lane);
+        const unsigned act = __ballot_sync(0xffffffffu, mine.active);
+        float4 v[8];
+        #pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if ((act >> i) & 1)
+                v[i] = __ldcg(reinterpret_cast<const float4*>(M.d_out + (size_t) (row * M.topk + k0 + i) * M.Ho + col));
+        #pragma unroll
+        for (int i = 0; i < 8; ++i)
+        {
+            const float w = __shfl_sync(0xffffffffu, mine.w, i);
+            if (!((act >> i) & 1)) continue;
+            o0 = __fadd_rn(o0, __fmul_rn(w, v[i].x)); o1 = __fadd_rn(o1, __fmul_rn(w, v[i].y));
+            o2 = __fadd_rn(o2, __fmul_rn(w, v[i].z)); o3 = __fadd_rn(o3, __fmul_rn(w, v[i].w));
+        }
+    }
+    if (M.sh_out)
+    {
+        float gv = 1.0f;
+        if (M.sh_gate_w)
+        {
+            const __half* xr = M.x + (size_t) row * M.x_stride;
+            float dot = 0.0f;
+            for (int i = lane * 2; i < M.H; i += 64)
+            {
+                const __half2 xv = *reinterpret_cast<const __half2*>(xr + i);
+                const __half2 wv = *reinterpret_cast<const __half2*>(M.sh_gate_w + i);
+                dot += __low2float(xv) * __low2float(wv) + __high2float(xv) * __high2float(wv);
+            }
+            #pragma unroll
+            for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            gv = 1.0f / (1.0f + __expf(-dot));
+        }
+        const float* sh = M.sh_out + (size_t) row * M.H + col;
+        if (col + 0 < M.H) o0 += gv * sh[0];
+        if (col + 1 < M.H) o1 += gv * sh[1];
+        if (col + 2 < M.H) o2 += gv * sh[2];
+        if (col + 3 < M.H) o3 += gv * sh[3];
+    }
+    float* dst = M.out + (size_t) row * M.out_stride + col;
+    if (col + 3 < M.H_out) *reinterpret_cast<float4*>(dst) = make_float4(o0, o1, o2, o3);
+    else
+    {
+        if (col + 0 < M.H_out) dst[0] = o0;
+        if (col + 1 < M.H_out) dst[1] = o1;
+        if (col + 2 < M.H_out) dst[2] = o2;
+    }
+}
 
 // Fused tensor-parallel all-reduce (row-parallel linears): the CTA that finishes a column block
 // pushes the block's fp16 partial straight into every peer's all-reduce buffer and gathers the
@@ -122,7 +217,7 @@ struct GemvParams
     int c_fp32;
     int xgroups;                // 64-row groups of x~ held in shared memory at a time (multiple of 4)
     int pdl;                    // launched with programmatic stream serialization
-    int cluster;                // 0, or CTAs per thread-block cluster: one cluster = one column block (MODE 0)
+    int cluster;                // 0, or CTAs per thread-block cluster: one cluster = one column block
     int blocks;                 // column blocks in total (slices * width / 128)
     float* scratch;             // [gridDim.x][2][m][128] partial sums of blocks shared between CTAs
     int* counters;              // [blocks] arrival counters, zero between launches
@@ -461,7 +556,11 @@ void exl3_gemv_kernel(const GemvParams P)
     // so much shared memory that an SM holds exactly this grid's share of CTAs, so they only move
     // in as CTAs of this grid leave -- one for one, which keeps the next grid evenly spread --
     // and start their weight stream under this grid's partial-sum exchange.
-    if (P.pdl) pdl_launch_dependents();
+    // The gate/up launch of the grouped mode (MODE 1) needs the routing (or the run table built from
+    // it) before anything else and releases its dependents only once that has arrived, so that
+    // the down launch (MODE 2), which starts under it, may read the same without a wait of its own.
+    if constexpr (MODE == 1) { if (P.pdl) { pdl_wait(); pdl_launch_dependents(); } }
+    else if (P.pdl) pdl_launch_dependents();
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int gq = lane >> 2, pq = lane & 3;
     const int m = P.m, k = P.k;
@@ -471,18 +570,58 @@ void exl3_gemv_kernel(const GemvParams P)
     // Work = (column block, group) units in block-major order, cut into equal contiguous ranges:
     // every CTA decodes the same number of weights (+-1 group) whatever the shape.
     const int nproj = (MODE == 1 && P.moe.gated) ? 2 : 1;
+    const int* runs = P.moe.runs;                      // [0] run count, [1] active slots, then the runs
+    __shared__ int s_runs[2 + 16 * MOE_RUN_INTS];
+    int inline_active = 0;
     if constexpr (MODE != 0)
     {
-        // the run table is the previous kernel's output: nothing can be fetched before it exists
-        if (P.pdl) pdl_wait();
+        if (P.moe.inline_runs)
+        {
+            // one token: its active picks, in pick order, are the runs (one row each); lane i of
+            // the first warp reads pick i
+            if (t < 32)
+            {
+                MoeSlot si; si.active = false; si.local = 0;
+                if (t < P.moe.topk)
+                    si = moe_slot(P.moe.sel, P.moe.rw, P.moe.topk, P.moe.min_expert, P.moe.max_expert, P.moe.n_local, t);
+                const unsigned act = __ballot_sync(0xffffffffu, si.active);
+                if (si.active)
+                {
+                    int* rec = s_runs + 2 + __popc(act & ((1u << t) - 1u)) * MOE_RUN_INTS;
+                    rec[0] = si.local; rec[1] = 1; rec[2] = t; rec[3] = 0;
+                }
+                if (t == 0) s_runs[0] = s_runs[1] = __popc(act);
+            }
+            __syncthreads();
+            runs = s_runs;
+            inline_active = s_runs[0];
+        }
     }
-    const int U = (MODE == 0 ? P.blocks : P.moe.runs[0] * nproj * nbw) * G;
+    const int U = (MODE == 0 ? P.blocks : runs[0] * nproj * nbw) * G;
     const int cta = blockIdx.x, ncta = min((int) gridDim.x, U);    // never more ranges than units
+    if constexpr (MODE == 2)
+    {
+        // a single token without any local pick: nobody will deliver a slot, the row is still due
+        if (P.moe.inline_runs && inline_active == 0 && cta == 0)
+            for (int c = warp; c < (P.moe.Ho >> 7); c += GEMV_WARPS) moe_combine_chunk(P.moe, 0, c, lane);
+    }
     if (cta >= ncta) return;                           // an exited CTA counts as having released its dependents
     GemvSplit split;
     split.q = U / ncta;
     split.r = U - split.q * ncta;
-    const int u0 = split.begin(cta), u1 = split.begin(cta + 1);
+    int u0 = split.begin(cta), u1 = split.begin(cta + 1);
+    if constexpr (MODE != 0)
+    {
+        if (P.cluster)
+        {
+            // cluster form of a grouped launch (one token): the grid holds a cluster per column
+            // block of every pick; the clusters of picks that turn out inactive leave as a whole
+            const int cblk = cta / P.cluster, per = G / P.cluster;
+            if (cblk * G >= U) return;
+            u0 = cblk * G + (cta - cblk * P.cluster) * per;
+            u1 = u0 + per;
+        }
+    }
 
     const uint32_t ring_s = smem_u32(smem + L.ring) + warp * (S * SLOT);      // this warp's ring
 
@@ -510,7 +649,7 @@ void exl3_gemv_kernel(const GemvParams P)
         if constexpr (MODE != 0)
         {
             const int run = slice / nproj, proj = (MODE == 2) ? 2 : (P.moe.gated ? slice - run * nproj : 1);
-            const int expert = P.moe.runs[2 + run * MOE_RUN_INTS];
+            const int expert = runs[2 + run * MOE_RUN_INTS];
             tr = reinterpret_cast<const unsigned char*>(P.moe.trellis[proj][expert]);
             stride = P.width;
         }
@@ -577,7 +716,7 @@ void exl3_gemv_kernel(const GemvParams P)
         for (int j = 0; j < S - 1; ++j) issue();
         started = true;
     }
-    bool waited = false;                               // MODE 0 waits for its predecessor inside the first x~ pass
+    bool waited = (MODE == 1);                         // MODE 0 / 2 wait for their predecessor inside the first x~ pass
 
     // per-lane constants of the consume side
     int xrow[MB];                                      // word offset of this lane's batch row in xd
@@ -606,7 +745,7 @@ void exl3_gemv_kernel(const GemvParams P)
         if constexpr (MODE != 0)
         {
             const int run = slice / nproj, proj = (MODE == 2) ? 2 : (P.moe.gated ? slice - run * nproj : 1);
-            const int* rec = P.moe.runs + 2 + run * MOE_RUN_INTS;
+            const int* rec = runs + 2 + run * MOE_RUN_INTS;
             const int expert = rec[0];
             nrows = rec[1];
             run_slots = reinterpret_cast<const unsigned char*>(rec + 2);
@@ -615,6 +754,8 @@ void exl3_gemv_kernel(const GemvParams P)
             if (P.moe.bias[proj]) bias = reinterpret_cast<const __half*>(P.moe.bias[proj][expert]);
             cbase = reinterpret_cast<unsigned char*>(MODE == 2 ? P.moe.d_out : P.moe.gu[proj]);
             stride = P.width;
+            // the expert's output scales are needed at the very end: pull their lines into L2 now
+            if (t < 2) asm volatile("prefetch.global.L2 [%0];" :: "l"(svh + (size_t) nb * 128 + t * 64));
             #pragma unroll
             for (int mb = 0; mb < MB; ++mb) xrow[mb] = min(mb * 8 + gq, nrows - 1) * XPITCH + pq * 4;
         }
@@ -782,6 +923,8 @@ void exl3_gemv_kernel(const GemvParams P)
                         }
                         else
                         {
+                            // the gate / up outputs are the previous launch's
+                            if (!waited) { if (P.pdl) pdl_wait(); waited = true; }
                             float4 u4, g4;
                             if (P.moe.gu_f32)
                             {
@@ -879,7 +1022,7 @@ void exl3_gemv_kernel(const GemvParams P)
         const int my_slot = 2 * cta + (blk * G > u0 ? 1 : 0);
         float* dst = whole ? part : slots + (size_t) my_slot * m * 128;
         // cluster form: the partial goes straight into the shared memory of the cluster's first CTA
-        const bool clustered = (MODE == 0) && P.cluster > 0;
+        const bool clustered = P.cluster > 0;
         uint32_t xdst = 0;
         if (clustered) xdst = cluster_map(smem_u32(smem + L.xchg), 0) + cluster_rank() * (m * 128 * 4);
         #pragma unroll
@@ -989,6 +1132,28 @@ void exl3_gemv_kernel(const GemvParams P)
                         oh.x = __floats2half2_rn(o.x, o.y);
                         oh.y = __floats2half2_rn(o.z, o.w);
                         reinterpret_cast<half4*>(reinterpret_cast<__half*>(cbase) + (size_t) run_slots[b] * stride + (size_t) nb * 128)[lane] = oh;
+                    }
+                    if constexpr (MODE == 2)
+                    {
+                        // this slot's part of the token's output chunk is delivered: whoever delivers
+                        // the last of the token's picks adds them up (pick order) and writes the row
+                        const int row = run_slots[b] / P.moe.topk;
+                        int* cnt = P.moe.done + row * (P.moe.Ho >> 7) + nb;
+                        __syncwarp();
+                        int last = 0;
+                        if (lane == 0)
+                        {
+                            __threadfence();
+                            const int need = P.moe.inline_runs ? inline_active : P.moe.need[row];
+                            if (atomicAdd(cnt, 1) == need - 1)
+                            {
+                                *cnt = 0;                            // zero again for the next call
+                                __threadfence();
+                                last = 1;
+                            }
+                        }
+                        last = __shfl_sync(0xffffffffu, last, 0);
+                        if (last) moe_combine_chunk(P.moe, row, nb, lane);
                     }
                 }
                 else if (P.c_fp32)

@@ -6,12 +6,17 @@
 // kernels exl3_moe_coop_kernel.cuh:667-999). Organisation here:
 //   1. moe_prep_kernel     sorts the active (token, pick) slots by expert and cuts them into runs
 //                          of at most eight slots of one expert (a run's slots are the batch rows
-//                          of one MMA, so an expert's weights are decoded once per run)
+//                          of one MMA, so an expert's weights are decoded once per run), and counts
+//                          every token's active picks. Skipped for a single token: the two GEMV
+//                          launches then derive the (one row per pick) table from the routing.
 //   2. grouped GEMV mode 1 gate and up of every run through the decode GEMV kernel (input rows
 //                          gathered by token, rotated in the prologue), fp32 outputs per slot
-//   3. grouped GEMV mode 2 down of every run; its prologue computes act(gate, up) * d_suh on the fly
-//   4. moe_combine_kernel  per token: sum of routing weight * slot output in pick order, plus the
-//                          shared expert (optionally sigmoid-gated), fp32 output row
+//   3. grouped GEMV mode 2 down of every run; its prologue computes act(gate, up) * d_suh on the
+//                          fly; the warp that delivers the last of a token's picks for a 128-column
+//                          chunk adds them up (routing weight * slot output in pick order, plus the
+//                          shared expert, optionally sigmoid-gated) and writes the fp32 output row
+// All counters live in the caller's ctr scratch (zero before the first call, left zero by every
+// call), so calls on different streams with different scratch do not interfere.
 // The arithmetic per element follows the reference's epilogues (fp32 scales, fp32 Hadamard,
 // one rounding to fp16 at each GEMV input).
 #include "exl3_gemv_host.h"
@@ -20,41 +25,26 @@
 
 namespace amp {
 
-struct SlotInfo { int row, local; float w; bool active; };
-
-__device__ __forceinline__ SlotInfo moe_slot(const long long* sel, const __half* rw, int topk,
-                                             int min_expert, int max_expert, int s)
-{
-    SlotInfo si;
-    si.row = s / topk;
-    long long e = sel[s];
-    si.w = __half2float(rw[s]);
-    bool ok = si.w != 0.0f;
-    if (min_expert >= 0)
-    {
-        ok = ok && e >= min_expert && e < max_expert;
-        e -= min_expert;
-    }
-    si.local = ok ? (int) e : 0;
-    si.active = ok;
-    return si;
-}
-
-// One block. Active slots ranked by (local expert, slot), then cut into runs.
+// One block. Active slots ranked by (local expert, slot), then cut into runs; per token the
+// number of active picks (the down launch counts arrivals against it); a token without any local
+// pick gets its output row here (nobody else will write it).
 __global__ __launch_bounds__(256)
-void moe_prep_kernel(const long long* sel, const __half* rw, int bsz, int topk, int min_expert,
-                     int max_expert, int n_local, int* runs, int pdl)
+void moe_prep_kernel(const GemvMoe M, int* runs, int* need, int pdl)
 {
     __shared__ int s_local[256];
     __shared__ short s_order[256];
+    __shared__ int s_need[256];
     __shared__ int s_active;
-    const int t = threadIdx.x, slots = bsz * topk;
-    if (pdl) { pdl_launch_dependents(); pdl_wait(); }
+    const int t = threadIdx.x, slots = M.bsz * M.topk;
+    if (pdl) { pdl_wait(); pdl_launch_dependents(); }
     if (t == 0) s_active = 0;
+    if (t < M.bsz) s_need[t] = 0;
+    __syncthreads();
     if (t < slots)
     {
-        SlotInfo si = moe_slot(sel, rw, topk, min_expert, max_expert, t);
-        s_local[t] = (si.active && si.local < n_local) ? si.local : -1;
+        const MoeSlot si = moe_slot(M.sel, M.rw, M.topk, M.min_expert, M.max_expert, M.n_local, t);
+        s_local[t] = si.active ? si.local : -1;
+        if (si.active) atomicAdd(&s_need[si.row], 1);
     }
     __syncthreads();
     const int my_e = t < slots ? s_local[t] : -1;
@@ -71,6 +61,7 @@ void moe_prep_kernel(const long long* sel, const __half* rw, int bsz, int topk, 
         atomicAdd(&s_active, 1);
     }
     __syncthreads();
+    if (t < M.bsz) need[t] = s_need[t];
     if (t == 0)
     {
         const int n_active = s_active;
@@ -92,70 +83,12 @@ void moe_prep_kernel(const long long* sel, const __half* rw, int bsz, int topk, 
         runs[0] = n_runs;
         runs[1] = n_active;
     }
-}
-
-struct CombineParams
-{
-    const __half* x; int x_stride, H;
-    const long long* sel; const __half* rw; int bsz, topk, min_expert, max_expert, n_local;
-    const float* d_out; int Ho, H_out;
-    float* out; int out_stride;
-    const float* sh_out; const __half* sh_gate_w;
-    int pdl;
-};
-
-// one warp per (token row, 128-column chunk)
-__global__ __launch_bounds__(256)
-void moe_combine_kernel(const CombineParams p)
-{
-    if (p.pdl) { pdl_launch_dependents(); pdl_wait(); }
-    const int lane = threadIdx.x & 31;
-    const int item = blockIdx.x * 8 + (threadIdx.x >> 5);
-    const int chunks = p.Ho / 128;
-    if (item >= p.bsz * chunks) return;
-    const int row = item / chunks, chunk = item - row * chunks;
-    const int col = chunk * 128 + lane * 4;
-
-    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-    for (int k = 0; k < p.topk; ++k)                      // pick order: deterministic
+    // rows nobody will deliver a slot for
+    const int lane = t & 31, chunks = M.Ho >> 7;
+    for (int item = t >> 5; item < M.bsz * chunks; item += 8)
     {
-        const int s = row * p.topk + k;
-        const SlotInfo si = moe_slot(p.sel, p.rw, p.topk, p.min_expert, p.max_expert, s);
-        if (!si.active || si.local >= p.n_local) continue;
-        const float4 v = __ldcg(reinterpret_cast<const float4*>(p.d_out + (size_t) s * p.Ho + col));
-        o0 = __fadd_rn(o0, __fmul_rn(si.w, v.x)); o1 = __fadd_rn(o1, __fmul_rn(si.w, v.y));
-        o2 = __fadd_rn(o2, __fmul_rn(si.w, v.z)); o3 = __fadd_rn(o3, __fmul_rn(si.w, v.w));
-    }
-    if (p.sh_out)
-    {
-        float gv = 1.0f;
-        if (p.sh_gate_w)
-        {
-            const __half* xr = p.x + (size_t) row * p.x_stride;
-            float dot = 0.0f;
-            for (int i = lane * 2; i < p.H; i += 64)
-            {
-                const __half2 xv = *reinterpret_cast<const __half2*>(xr + i);
-                const __half2 wv = *reinterpret_cast<const __half2*>(p.sh_gate_w + i);
-                dot += __low2float(xv) * __low2float(wv) + __high2float(xv) * __high2float(wv);
-            }
-            #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            gv = 1.0f / (1.0f + __expf(-dot));
-        }
-        const float* sh = p.sh_out + (size_t) row * p.H + col;
-        if (col + 0 < p.H) o0 += gv * sh[0];
-        if (col + 1 < p.H) o1 += gv * sh[1];
-        if (col + 2 < p.H) o2 += gv * sh[2];
-        if (col + 3 < p.H) o3 += gv * sh[3];
-    }
-    float* dst = p.out + (size_t) row * p.out_stride + col;
-    if (col + 3 < p.H_out) *reinterpret_cast<float4*>(dst) = make_float4(o0, o1, o2, o3);
-    else
-    {
-        if (col + 0 < p.H_out) dst[0] = o0;
-        if (col + 1 < p.H_out) dst[1] = o1;
-        if (col + 2 < p.H_out) dst[2] = o2;
+        const int row = item / chunks;
+        if (s_need[row] == 0) moe_combine_chunk(M, row, item - row * chunks, lane);
     }
 }
 
@@ -178,9 +111,12 @@ static cudaError_t launch_small(void (*kernel)(Args...), int grid, cudaStream_t 
 
 using namespace amp;
 
-AMP_API long amp_exl3_moe_coop_ctr_len(long slots_max)
+// run table (2 + 4 ints per slot), active picks per token, arrivals per (token, 128-column chunk
+// of the down output)
+AMP_API long amp_exl3_moe_coop_ctr_len(long slots_max, long rows_max, long I, long Ho)
 {
-    return 2 + slots_max * MOE_RUN_INTS;
+    (void) I;
+    return 2 + slots_max * MOE_RUN_INTS + rows_max * (1 + Ho / 128);
 }
 
 AMP_API int amp_exl3_moe_coop(const amp_moe_coop_args* a, cudaStream_t stream)
@@ -201,14 +137,14 @@ AMP_API int amp_exl3_moe_coop(const amp_moe_coop_args* a, cudaStream_t stream)
                 "exl3_moe_coop: pointer tables missing");
     AMP_REQUIRE(!a->gated || (a->g_trellis && a->g_suh && a->g_svh), "exl3_moe_coop: gate tables missing");
     AMP_REQUIRE(a->gu_g && a->gu_u && a->d_out && a->ctr, "exl3_moe_coop: scratch missing");
+    AMP_REQUIRE(a->ctr_len >= amp_exl3_moe_coop_ctr_len(a->slots_max, a->bsz, a->I, a->Ho), "exl3_moe_coop: counter scratch too small");
     AMP_REQUIRE(a->min_expert < 0 || a->max_expert - a->min_expert <= a->n_local, "exl3_moe_coop: expert range exceeds tables");
     AMP_REQUIRE(!a->sh_out || a->H_out == a->H, "exl3_moe_coop: shared expert output width must match the routed output");
     AMP_REQUIRE(!a->sh_gate_w || a->H % 2 == 0, "exl3_moe_coop: shared gate width");
 
     int* runs = a->ctr;
-    if (cudaError_t e = launch_small(moe_prep_kernel, 1, stream, (const long long*) a->sel, (const __half*) a->rw,
-                                     a->bsz, a->topk, a->min_expert, a->max_expert, a->n_local, runs, g_pdl))
-        return cuda_rc(e, "moe_prep launch");
+    int* need = a->ctr + 2 + a->slots_max * MOE_RUN_INTS;
+    int* done = need + a->bsz;
 
     GemvLaunch L = {};
     L.moe.runs = runs;
@@ -220,7 +156,19 @@ AMP_API int amp_exl3_moe_coop(const amp_moe_coop_args* a, cudaStream_t stream)
     L.moe.gu[0] = a->gu_g; L.moe.gu[1] = a->gu_u; L.moe.gu_f32 = a->gu_f32 ? 1 : 0; L.moe.d_out = (float*) a->d_out;
     L.moe.Hi = a->Hi; L.moe.I = a->I; L.moe.Ho = a->Ho;
     L.moe.act = a->act; L.moe.act_limit = a->act_limit; L.moe.gated = a->gated ? 1 : 0;
+    L.moe.sel = (const long long*) a->sel; L.moe.rw = (const __half*) a->rw; L.moe.bsz = a->bsz;
+    L.moe.min_expert = a->min_expert; L.moe.max_expert = a->max_expert; L.moe.n_local = a->n_local;
+    L.moe.need = need; L.moe.done = done;
+    L.moe.out = (float*) a->out; L.moe.out_stride = a->out_stride; L.moe.H_out = a->H_out;
+    L.moe.sh_out = (const float*) a->sh_out; L.moe.sh_gate_w = a->sh_out ? (const __half*) a->sh_gate_w : nullptr;
+    // one token with at most 16 picks: the kernels derive the (trivial) run table themselves and
+    // the sorting launch is not needed
+    L.moe.inline_runs = (a->bsz == 1 && a->topk <= 16) ? 1 : 0;
     L.m = 8; L.cb = a->cb; L.c_fp32 = 1;
+
+    if (!L.moe.inline_runs)
+        if (cudaError_t e = launch_small(moe_prep_kernel, 1, stream, L.moe, runs, need, g_pdl))
+            return cuda_rc(e, "moe_prep launch");
 
     // gate + up: slices = runs x projections, k = Hi, width = I
     const int nproj = a->gated ? 2 : 1;
@@ -228,20 +176,8 @@ AMP_API int amp_exl3_moe_coop(const amp_moe_coop_args* a, cudaStream_t stream)
     L.slices = slots * nproj; L.max_slices = slots * nproj;          // at most one run per slot
     if (int rc = launch_gemv(L, stream)) return rc;
 
-    // down: slices = runs, k = I, width = Ho
+    // down: slices = runs, k = I, width = Ho; its finishing CTAs also do the routing-weighted sum
     L.mode = 2; L.k = a->I; L.width = a->Ho; L.stride = a->Ho; L.K = a->Kd;
     L.slices = slots; L.max_slices = slots;
-    if (int rc = launch_gemv(L, stream)) return rc;
-
-    CombineParams C;
-    C.x = (const __half*) a->x; C.x_stride = a->x_stride; C.H = a->H;
-    C.sel = (const long long*) a->sel; C.rw = (const __half*) a->rw; C.bsz = a->bsz; C.topk = a->topk;
-    C.min_expert = a->min_expert; C.max_expert = a->max_expert; C.n_local = a->n_local;
-    C.d_out = (const float*) a->d_out; C.Ho = a->Ho; C.H_out = a->H_out;
-    C.out = (float*) a->out; C.out_stride = a->out_stride;
-    C.sh_out = (const float*) a->sh_out; C.sh_gate_w = a->sh_out ? (const __half*) a->sh_gate_w : nullptr;
-    C.pdl = g_pdl;
-    const int items = a->bsz * (a->Ho / 128);
-    if (cudaError_t e = launch_small(moe_combine_kernel, (items + 7) / 8, stream, C)) return cuda_rc(e, "moe_combine launch");
-    return 0;
+    return launch_gemv(L, stream);
 }

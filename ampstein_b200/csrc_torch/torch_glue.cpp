@@ -240,16 +240,20 @@ void exl3_moe_coop(const at::Tensor& x, const at::Tensor& sel, const at::Tensor&
     a.Kgu = bits_of(Ku, "exl3_moe_coop"); a.Kd = bits_of(Kd, "exl3_moe_coop");
     a.cb = codebook(mcg, mul1); a.act = act; a.act_limit = act_limit; a.gated = gated ? 1 : 0;
     a.gu_g = gu_g.data_ptr(); a.gu_u = gu_u.data_ptr(); a.gu_f32 = gu_g.scalar_type() == at::kFloat ? 1 : 0;
-    a.d_out = d_out.data_ptr(); a.ctr = (int*) ctr.data_ptr();
+    a.d_out = d_out.data_ptr(); a.ctr = (int*) ctr.data_ptr(); a.ctr_len = (long) ctr.numel();
     a.slots_max = (int) std::min(std::min(gu_g.numel(), gu_u.numel()) / std::max(a.I, 1), d_out.numel() / std::max(a.Ho, 1));
     TORCH_CHECK(a.bsz <= out.size(-2), "exl3_moe_coop: batch exceeds the output tensor");
-    TORCH_CHECK(ctr.numel() >= amp_exl3_moe_coop_ctr_len(a.slots_max), "exl3_moe_coop: ctr too short for the scratch's slot count");
+    TORCH_CHECK(ctr.numel() >= amp_exl3_moe_coop_ctr_len(a.slots_max, a.bsz, a.I, a.Ho), "exl3_moe_coop: ctr too short for the scratch's slot count");
     a.out = out.data_ptr(); a.out_stride = (int) out.stride(-2);
     a.sh_out = opt_ptr(sh_out); a.sh_gate_w = opt_ptr(sh_gate_w);
     check_rc(amp_exl3_moe_coop(&a, stream_of(x)), "exl3_moe_coop");
 }
 
-int64_t exl3_moe_coop_ctr_len(int64_t slots_max) { return amp_exl3_moe_coop_ctr_len(slots_max); }
+// same arguments as the reference's exl3_moe_coop_ctr_len (vendor/exl3/exllamav3_ext/quant/exl3_moe_coop.cuh:164-167)
+int64_t exl3_moe_coop_ctr_len(int64_t slots_max, int64_t bsz_max, int64_t I, int64_t Ho)
+{
+    return amp_exl3_moe_coop_ctr_len(slots_max, bsz_max, I, Ho);
+}
 
 #ifndef AMP_NO_PYBIND
 PYBIND11_MODULE(_torch_glue, m)

@@ -224,14 +224,19 @@ class _MoeArgs(__import__("ctypes").Structure):
         ("Kgu", _c.c_int), ("Kd", _c.c_int), ("cb", _c.c_int), ("act", _c.c_int),
         ("act_limit", _c.c_float), ("gated", _c.c_int),
         ("gu_g", _c.c_void_p), ("gu_u", _c.c_void_p), ("gu_f32", _c.c_int), ("d_out", _c.c_void_p),
-        ("ctr", _c.c_void_p), ("slots_max", _c.c_int),
+        ("ctr", _c.c_void_p), ("ctr_len", _c.c_long), ("slots_max", _c.c_int),
         ("out", _c.c_void_p), ("out_stride", _c.c_int),
         ("sh_out", _c.c_void_p), ("sh_gate_w", _c.c_void_p),
     ]
 
 
-def moe_coop_ctr_len(slots_max):
-    return int(_lib.lib().amp_exl3_moe_coop_ctr_len(int(slots_max)))
+def moe_coop_ctr_len(slots_max, rows_max=None, I=0, Ho=None):
+    """int32 entries of the `ctr` scratch (reference: exl3_moe_coop_ctr_len,
+    .../quant/exl3_moe_coop.cuh:164-167). Without rows_max / Ho an upper bound is returned (one
+    token per slot, outputs up to 16384 wide)."""
+    rows_max = slots_max if rows_max is None else rows_max
+    Ho = 16384 if Ho is None else Ho
+    return int(_lib.lib().amp_exl3_moe_coop_ctr_len(int(slots_max), int(rows_max), int(I), int(Ho)))
 
 
 def moe_coop(x, sel, rw, cfg, sh_out=None):
@@ -276,7 +281,7 @@ def moe_coop(x, sel, rw, cfg, sh_out=None):
     bsz, topk = sel.shape
     if bsz > out.shape[-2]:
         raise ValueError("exl3_moe_coop: batch exceeds the scratch")
-    if cfg["ctr"].numel() < moe_coop_ctr_len(slots_max):
+    if cfg["ctr"].numel() < moe_coop_ctr_len(slots_max, bsz, I, Ho):
         raise ValueError("exl3_moe_coop: counter scratch too small")
     if sh_out is not None:
         _check_cuda("moe_coop", sh_out)
@@ -296,7 +301,7 @@ def moe_coop(x, sel, rw, cfg, sh_out=None):
     a.Kgu, a.Kd, a.cb = int(Ku), int(Kd), _cb(mul1, mcg)
     a.act, a.act_limit, a.gated = int(cfg.get("act", 0)), float(cfg.get("act_limit", 0.0)), int(gated)
     a.gu_g, a.gu_u, a.gu_f32, a.d_out = p(cfg["gu_g"]), p(cfg["gu_u"]), int(gu_dt == torch.float32), p(cfg["d_out"])
-    a.ctr, a.slots_max = p(cfg["ctr"]), slots_max
+    a.ctr, a.ctr_len, a.slots_max = p(cfg["ctr"]), cfg["ctr"].numel(), slots_max
     a.out, a.out_stride = p(out), out.stride(-2)
     a.sh_out = p(sh_out)
     a.sh_gate_w = p(cfg.get("sh_gate_w"))

@@ -515,7 +515,9 @@ def measure_prefill(steps, warmup):
                      "kernel": "exl3_gemm_tc2_kernel", "traffic": None}}
 
 
-MOE_LAUNCHES = 4           # kernels per fused MoE layer: run table, gate|up, down, combine
+def moe_launches(T):
+    """kernels per fused MoE layer: (run table for more than one token,) gate|up, down"""
+    return 2 if T == 1 else 3
 
 
 def measure_moe(steps, warmup, T):
@@ -539,7 +541,7 @@ def measure_moe(steps, warmup, T):
                d_trellis=tab("d", 0), d_suh=tab("d", 1), d_svh=tab("d", 2),
                gu_g=torch.zeros(slots, I, dtype=torch.float16, device=dev), gu_u=torch.zeros(slots, I, dtype=torch.float16, device=dev),
                d_out=torch.zeros(slots, Ho, dtype=torch.float32, device=dev),
-               ctr=torch.zeros(amp.moe_coop_ctr_len(slots), dtype=torch.int32, device=dev),
+               ctr=torch.zeros(amp.moe_coop_ctr_len(slots, T, I, Ho), dtype=torch.int32, device=dev),
                out=torch.zeros(T, Hi, dtype=torch.float32, device=dev), Hi=Hi, Kg=K, Ku=K, Kd=K, act=0, act_limit=0.0)
     sets = []
     for _ in range(8):
@@ -547,10 +549,11 @@ def measure_moe(steps, warmup, T):
         sets.append((torch.randn(T, Hi, device=dev, generator=g).to(torch.float16), sel.contiguous(),
                      torch.softmax(w, 1).to(torch.float16).contiguous()))
     distinct = float(np.mean([len(torch.unique(s[1])) for s in sets]))
-    for x, sel, rw in sets:
-        amp.moe_coop(x, sel, rw, cfg)
-    torch.cuda.synchronize()
     gr, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(st):                       # (the stream's workspace is created here, before capture)
+        for x, sel, rw in sets:
+            amp.moe_coop(x, sel, rw, cfg)
+    torch.cuda.synchronize()
     with torch.cuda.stream(st), torch.cuda.graph(gr, stream=st):
         for x, sel, rw in sets:
             amp.moe_coop(x, sel, rw, cfg)
@@ -575,7 +578,7 @@ def measure_moe(steps, warmup, T):
         "config": {"workload": "moe decode: 128 experts 2048->768->2048 K=3, top-8, %d token(s), 8 routings per graph" % T,
                    "distinct_experts_per_layer": round(distinct, 1),
                    "l2": "expert weights in total 226 MB (larger than L2); each layer touches %.1f MB" % (byt / 1e6)},
-        "gpu_launches": MOE_LAUNCHES * len(sets) * steps, "clocks": clocks,
+        "gpu_launches": moe_launches(T) * len(sets) * steps, "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
                      "peak_source": "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback",
                      "kernel": "exl3_gemv_kernel (grouped modes)", "bytes_per_launch": int(byt) // 2, "traffic": None}}

@@ -104,8 +104,9 @@ int amp_exl3_gemm_status(int* out);
 
 /*
  * The decode-batch kernel on its own, m = 1..16. The first call on a device allocates a
- * per-device workspace (64 MB + 256 KB: four regions of arrival counters and partial-sum slots) and must
- * therefore come before any stream capture; later calls allocate nothing.
+ * workspace for the stream it is issued on (16 MB + 64 KB of arrival counters and partial-sum slots per
+ * stream and device, so that launches overlapping on different streams never share counters) and must
+ * therefore come before any capture on that stream; later calls on the stream allocate nothing.
  * Replaces: exl3_gemv_kernel / exl3_gemv_try_launch, Q/exl3_gemv_kernel.cuh:186-482,
  * Q/exl3_gemv.cu:92-184.
  */
@@ -162,6 +163,8 @@ int amp_exl3_mgemm(const void* x, const void* trellis_ptrs, void* C, const void*
  * Fused decode-shaped MoE: out[row] = sum over the row's active picks of rw * expert(x[row]),
  * expert = down(act(gate(x), up(x))), plus an optional shared-expert term. Up to 256
  * (token, pick) slots per call. Routing (sel, rw) is read on the device; nothing synchronises.
+ * Three launches (run table, gate|up, down: the CTA that delivers the last of a token's picks for
+ * an output chunk also does the routing-weighted sum), two for a single token.
  * Replaces: exl3_moe_coop, Q/exl3_moe_coop.cu:309-371 and its parameter block MoeCoopParams,
  * Q/exl3_moe_coop.cuh:21-83 (binding torch.moe_coop, src/torch/amp_torch.cpp:7852-7934). Fields
  * keep the reference's names and meaning; scratch the new kernels do not need (had_g, had_u,
@@ -193,7 +196,9 @@ typedef struct amp_moe_coop_args
     void* gu_g; void* gu_u;     /* (slots_max, I) fp32 (gu_f32 = 1) or fp16 (gu_f32 = 0) */
     int gu_f32;
     void* d_out;                /* (slots_max, Ho) fp32 */
-    int* ctr;                   /* int32, amp_exl3_moe_coop_ctr_len(slots_max) entries: the run table */
+    int* ctr;                   /* int32 scratch, zero-filled once: run table, active picks per token, arrivals per
+                                   (token, 128-column output chunk); the kernels leave the arrivals zero */
+    long ctr_len;               /* entries in ctr, >= amp_exl3_moe_coop_ctr_len(slots_max, bsz, I, Ho) */
     int slots_max;
     void* out;                  /* (bsz, H_out) fp32, row stride out_stride */
     int out_stride;
@@ -203,9 +208,11 @@ typedef struct amp_moe_coop_args
 
 int amp_exl3_moe_coop(const amp_moe_coop_args* args, cudaStream_t stream);
 
-/* Length (int32 entries) of the ctr scratch for slots_max slots. Replaces
- * exl3_moe_coop_ctr_len, Q/exl3_moe_coop.cuh:164-167. */
-long amp_exl3_moe_coop_ctr_len(long slots_max);
+/* Length (int32 entries) of the ctr scratch for up to slots_max (token, pick) slots and rows_max
+ * tokens: 2 + 4 * slots_max + rows_max * (1 + Ho / 128). Same arguments as the reference's
+ * exl3_moe_coop_ctr_len, Q/exl3_moe_coop.cuh:164-167 (I is not needed here); never longer than
+ * the reference's figure when I >= 384. */
+long amp_exl3_moe_coop_ctr_len(long slots_max, long rows_max, long I, long Ho);
 
 /*
  * Programmatic dependent launch of the decode kernels (default on): each kernel starts its

@@ -159,3 +159,40 @@ def test_moe_config4_shapes_one_token(amp, oracle):
     amp.moe_coop(dev(x), dev(sel), dev(rw), cfg)
     torch.cuda.synchronize()
     check(cfg["out"][:1].cpu().numpy(), oracle.moe_coop(x, sel, rw, ex))
+
+
+def test_moe_and_a_plain_gemv_on_two_streams_at_once(amp, oracle):
+    """The reference runs the shared expert's linears on a side stream while moe_coop runs
+    (src/ucode/ampstein/glm5.uc:970,998): launches that overlap on the GPU must not share arrival
+    counters. Many rounds of a fused MoE on one stream and plain GEMVs (shapes whose column blocks
+    are shared between CTAs) on another, all results checked."""
+    from test_gpu_parity import check_close
+    E, Hi, I, Ho, K, topk, T = 16, 512, 256, 512, 3, 4, 4
+    ex = make_experts(E, Hi, I, Ho, K, seed=1300)
+    rng = np.random.default_rng(13)
+    x = rng.standard_normal((T, Hi)).astype(np.float16)
+    logits = rng.standard_normal((T, E)).astype(np.float32)
+    sel = np.argsort(-logits, axis=1)[:, :topk].astype(np.int64)
+    rw = np.full((T, topk), 1.0 / topk, np.float16)
+    cfg = build_cfg(amp, ex, Hi, I, Ho, Hi, K, 16, topk)
+    ref_moe = oracle.moe_coop(x, sel, rw, ex)
+    trellis, suh, svh, xg = make_linear(4096, 1024, 4, seed=1301, m=2)
+    ref_lin = oracle.linear(xg, trellis, suh, svh, 0, fp32_out=True)
+    t, su, sv, xgd = dev(trellis), dev(suh), dev(svh), dev(xg)
+    xd, seld, rwd = dev(x), dev(sel), dev(rw)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = [torch.empty((2, 1024), dtype=torch.float16, device="cuda") for _ in range(24)]
+    moe_outs = []
+    torch.cuda.synchronize()
+    for i in range(24):
+        with torch.cuda.stream(s1):
+            amp.moe_coop(xd, seld, rwd, cfg)
+            if i % 6 == 5:
+                moe_outs.append(cfg["out"][:T].clone())
+        with torch.cuda.stream(s2):
+            amp.exl3_gemm(xgd, t, outs[i], su, sv)
+    torch.cuda.synchronize()
+    for o in outs:
+        check_close(o.cpu().numpy(), ref_lin)
+    for o in moe_outs:
+        check(o.cpu().numpy(), ref_moe)

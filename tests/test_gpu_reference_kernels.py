@@ -124,10 +124,11 @@ def test_fused_moe_agrees(amp, oracle, T, E, Hi, I, Ho, K, topk):
 
 def graph_time_us(fn_list, reps=20):
     """Average time of one call when the calls of fn_list run back to back inside one CUDA graph."""
-    for f in fn_list:
-        f()
-    torch.cuda.synchronize()
     g, s = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for f in fn_list:
+            f()
+    torch.cuda.synchronize()
     with torch.cuda.stream(s), torch.cuda.graph(g, stream=s):
         for f in fn_list:
             f()
