@@ -28,6 +28,7 @@ SIGNATURES = {
     "amp_exl3_gemv_cfg": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "amp_exl3_gemv_status": [ctypes.POINTER(ctypes.c_int)],
     "amp_exl3_mgemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
+    "amp_exl3_mgemm_bf16": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
     "amp_exl3_set_pdl": [_i],
     "amp_exl3_set_gemv_tc": [_i],
     "amp_diag_issue_cycles": [_i, _i, ctypes.POINTER(ctypes.c_float)],

@@ -70,10 +70,50 @@ struct TcParams
     const uint16_t* trellis;    // (k/16, n/16, 16K)
     const __half* svh;          // (n)
     void* c;                    // (M, n) fp16 or fp32
-    int M, k, n, c_fp32;
+    int M, k, n, c_fp32;        // n: row width of the trellis / output (bundle: columns per slice)
     int sub;                    // 128-token sub-tiles per CTA: 4, or fewer when the grid would leave SMs idle
     int* status;
+    // bundle (tables == 1): several matrices or equal-width column slices in one grid, identified
+    // by device pointer tables with one entry per slice, exactly as the decode kernel's table mode
+    int tables;
+    const long long* t_trellis;
+    const long long* t_svh;
+    const long long* t_c;       // may be null: outputs stacked in c as (slices, M, n)
+    const int* t_stride;        // may be null: row width = n
+    const int* t_src;           // may be null: rotated input of slice i is source i
 };
+
+// What one CTA (pair) works on: its weight, scales, output, rotated input and column block
+struct TcSlice
+{
+    const unsigned char* trellis;
+    const __half* svh;
+    unsigned char* c;
+    const unsigned char* xt;
+    int n_row;                  // row width of trellis and output
+    int nb;                     // column block (of BW columns) inside the slice
+};
+
+template <int BW>
+__device__ __forceinline__ TcSlice tc_slice(const TcParams& P, int nbg)
+{
+    TcSlice s;
+    s.trellis = reinterpret_cast<const unsigned char*>(P.trellis);
+    s.svh = P.svh; s.c = reinterpret_cast<unsigned char*>(P.c); s.xt = P.xt; s.n_row = P.n; s.nb = nbg;
+    if (P.tables)
+    {
+        const int bps = P.n / BW, slice = nbg / bps;
+        s.nb = nbg - slice * bps;
+        s.trellis = reinterpret_cast<const unsigned char*>(P.t_trellis[slice]);
+        s.svh = reinterpret_cast<const __half*>(P.t_svh[slice]);
+        s.n_row = P.t_stride ? P.t_stride[slice] : P.n;
+        s.c = P.t_c ? reinterpret_cast<unsigned char*>(P.t_c[slice])
+                    : reinterpret_cast<unsigned char*>(P.c) + (size_t) slice * P.M * P.n * (P.c_fp32 ? 4 : 2);
+        const int src = P.t_src ? P.t_src[slice] : slice;
+        s.xt = P.xt + (size_t) src * P.M * P.k * 2;
+    }
+    return s;
+}
 
 // K-major, 128-byte swizzle, rows of 128 bytes: byte offset of (row, 16-byte chunk)
 __device__ __forceinline__ uint32_t sw128(int row, int chunk)
@@ -165,12 +205,13 @@ void exl3_gemm_tc_kernel(const TcParams P)
     __shared__ volatile int s_bad;
 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const int nb = blockIdx.x, mb = blockIdx.y;
+    const TcSlice W = tc_slice<TC_BN>(P, blockIdx.x);
+    const int nb = W.nb, mb = blockIdx.y;
     const int m0 = mb * (P.sub * TC_BM);
     const int rows = min(P.sub * TC_BM, P.M - m0);     // valid token rows of this CTA
     const int nsub = (rows + TC_BM - 1) / TC_BM;        // sub-tiles that hold any of them
     const int ksteps = P.k / TC_BK;
-    const size_t tiles_n = (size_t) P.n >> 4;
+    const size_t tiles_n = (size_t) W.n_row >> 4;
 
     if (t == 0)
     {
@@ -230,7 +271,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
                 // each (the rows of a ragged last box that do not exist are not copied; their
                 // accumulator rows are never stored)
                 mbar_expect_tx(&a_full[s], (uint32_t) rows * 128);
-                const unsigned char* src = P.xt + (((size_t) i * P.M + m0) << 7);
+                const unsigned char* src = W.xt + (((size_t) i * P.M + m0) << 7);
                 for (int sub = 0; sub < nsub; ++sub)
                     bulk_g2s(a_base + s * TC_A_BYTES + sub * (TC_BM * 128), src + ((size_t) sub * TC_BM << 7),
                              (uint32_t) min(TC_BM, rows - sub * TC_BM) * 128, &a_full[s]);
@@ -273,8 +314,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
         const int dw = (warp - 2) & 7;                     // tile column of the 128-column block
         const int grp = (warp - 2) >> 3;                   // this warp's steps: grp, grp + 2, ...
         const int gq = lane >> 2, pq = lane & 3;           // 32-weight piece of the tile, tile row of the step
-        const unsigned char* src = reinterpret_cast<const unsigned char*>(P.trellis)
-                                 + ((size_t) pq * tiles_n + (size_t) nb * 8 + dw) * (32 * K) + gq * (4 * K);
+        const unsigned char* src = W.trellis + ((size_t) pq * tiles_n + (size_t) nb * 8 + dw) * (32 * K) + gq * (4 * K);
         const size_t step_bytes = (size_t) 4 * tiles_n * (32 * K);
         // this lane's ring: slot s at pring + s * SLOT (a warp's lanes side by side inside a slot); a
         // lane only ever reads what it copied itself
@@ -372,7 +412,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
         __syncthreads();
         if (all_ok && warp >= 2)
         {
-            const half4 sv = reinterpret_cast<const half4*>(P.svh + (size_t) nb * 128)[lane];
+            const half4 sv = reinterpret_cast<const half4*>(W.svh + (size_t) nb * 128)[lane];
             for (int r = ew; r < TC_BM; r += TC_DECODE_WARPS)
             {
                 const int grow = m0 + sub * TC_BM + r;
@@ -385,14 +425,14 @@ void exl3_gemm_tc_kernel(const TcParams P)
                 {
                     float4 o = make_float4(h0 * __low2float(sv.x), h1 * __high2float(sv.x),
                                            h2 * __low2float(sv.y), h3 * __high2float(sv.y));
-                    reinterpret_cast<float4*>(reinterpret_cast<float*>(P.c) + (size_t) grow * P.n + (size_t) nb * 128)[lane] = o;
+                    reinterpret_cast<float4*>(reinterpret_cast<float*>(W.c) + (size_t) grow * W.n_row + (size_t) nb * 128)[lane] = o;
                 }
                 else
                 {
                     half4 o;
                     o.x = __hmul2(__floats2half2_rn(h0, h1), sv.x);
                     o.y = __hmul2(__floats2half2_rn(h2, h3), sv.y);
-                    reinterpret_cast<half4*>(reinterpret_cast<__half*>(P.c) + (size_t) grow * P.n + (size_t) nb * 128)[lane] = o;
+                    reinterpret_cast<half4*>(reinterpret_cast<__half*>(W.c) + (size_t) grow * W.n_row + (size_t) nb * 128)[lane] = o;
                 }
             }
         }
@@ -554,7 +594,8 @@ void exl3_gemm_tc2_kernel(const TcParams P)
     uint32_t crank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
     const bool leader = crank == 0;
-    const int nb = blockIdx.x >> 1, mb = blockIdx.y;       // 256-column block, 512-token block of the pair
+    const TcSlice W = tc_slice<256>(P, blockIdx.x >> 1);
+    const int nb = W.nb, mb = blockIdx.y;                  // 256-column block, 512-token block of the pair
     const int cta_rows = P.sub * TC_BM;                    // token rows per CTA: 256, or 128 for short grids
     const int m0 = mb * (2 * cta_rows) + (int) crank * cta_rows;
     const int rows = max(0, min(cta_rows, P.M - m0));               // valid token rows of this CTA (the peer may have none)
@@ -563,7 +604,7 @@ void exl3_gemm_tc2_kernel(const TcParams P)
     const int nsub_mma = (rows_lead + TC_BM - 1) / TC_BM;           // sub-tiles the pair multiplies (the first CTA's count)
     const int n_issuers = (T2_ISSUERS > 1 && nsub_mma > 1) ? 2 : 1;   // threads that issue MMAs and commit (same value in both CTAs)
     const int ksteps = P.k / TC_BK;
-    const size_t tiles_n = (size_t) P.n >> 4;
+    const size_t tiles_n = (size_t) W.n_row >> 4;
 
     if (t == 0)
     {
@@ -646,7 +687,7 @@ void exl3_gemm_tc2_kernel(const TcParams P)
                 if (i >= S) wait_bar_spin(&st_free[s], ph);
                 if (!ok) break;
                 mbar_expect_tx(&a_land[s], (uint32_t) rows * 128);
-                const unsigned char* src = P.xt + (((size_t) i * P.M + m0) << 7);
+                const unsigned char* src = W.xt + (((size_t) i * P.M + m0) << 7);
                 for (int sub = 0; sub < nsub; ++sub)
                     bulk_g2s(a_base + s * T2_A_BYTES + sub * (TC_BM * 128), src + ((size_t) sub * TC_BM << 7),
                              (uint32_t) min(TC_BM, rows - sub * TC_BM) * 128, &a_land[s]);
@@ -720,8 +761,7 @@ void exl3_gemm_tc2_kernel(const TcParams P)
         const int dw = (warp - 2) & 7;
         const int grp = (warp - 2) >> 3;
         const int gq = lane >> 2, pq = lane & 3;
-        const unsigned char* src = reinterpret_cast<const unsigned char*>(P.trellis)
-                                 + ((size_t) pq * tiles_n + (size_t) nb * 16 + crank * 8 + dw) * (32 * K) + gq * (4 * K);
+        const unsigned char* src = W.trellis + ((size_t) pq * tiles_n + (size_t) nb * 16 + crank * 8 + dw) * (32 * K) + gq * (4 * K);
         const size_t step_bytes = (size_t) 4 * tiles_n * (32 * K);
         constexpr int PS = t2_p_stages(K);
         constexpr int SLOT = 32 * 4 * K;
@@ -817,7 +857,7 @@ void exl3_gemm_tc2_kernel(const TcParams P)
         if (all_ok && dec_warp)
         {
             const size_t cblk = (size_t) nb * 256 + (size_t) hb * 128;
-            const half4 sv = reinterpret_cast<const half4*>(P.svh + cblk)[lane];
+            const half4 sv = reinterpret_cast<const half4*>(W.svh + cblk)[lane];
             for (int r = ew; r < TC_BM; r += TC_DECODE_WARPS)
             {
                 const int grow = m0 + sub * TC_BM + r;
@@ -830,14 +870,14 @@ void exl3_gemm_tc2_kernel(const TcParams P)
                 {
                     float4 o = make_float4(h0 * __low2float(sv.x), h1 * __high2float(sv.x),
                                            h2 * __low2float(sv.y), h3 * __high2float(sv.y));
-                    reinterpret_cast<float4*>(reinterpret_cast<float*>(P.c) + (size_t) grow * P.n + cblk)[lane] = o;
+                    reinterpret_cast<float4*>(reinterpret_cast<float*>(W.c) + (size_t) grow * W.n_row + cblk)[lane] = o;
                 }
                 else
                 {
                     half4 o;
                     o.x = __hmul2(__floats2half2_rn(h0, h1), sv.x);
                     o.y = __hmul2(__floats2half2_rn(h2, h3), sv.y);
-                    reinterpret_cast<half4*>(reinterpret_cast<__half*>(P.c) + (size_t) grow * P.n + cblk)[lane] = o;
+                    reinterpret_cast<half4*>(reinterpret_cast<__half*>(W.c) + (size_t) grow * W.n_row + cblk)[lane] = o;
                 }
             }
         }
@@ -863,15 +903,20 @@ static const tc_fn k_tc2[3][8] = { AMP_TC2_ROW(0), AMP_TC2_ROW(1), AMP_TC2_ROW(2
 #undef AMP_TC2_ROW
 int g_tc_pair = 1;        // pair (cta_group::2) form: 0 never, 1 where it fills the device, 2 whenever n % 256 == 0
 
-// tiled x~ (launch_had_tiled) -> C. Called by amp_exl3_gemm for m > 16.
+// tiled x~ (launch_had_tiled) -> C. Called by amp_exl3_gemm for m > 16, and by amp_exl3_mgemm
+// with T set: then `n` is the width of one slice, the grid covers T->num slices, and trellis / svh
+// (and c when T->c is given) are ignored in favour of the tables.
 int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh, int M, int k, int n,
-                   int K, int cb, int c_fp32, cudaStream_t stream)
+                   int K, int cb, int c_fp32, cudaStream_t stream, const TcTables* T)
 {
-    AMP_REQUIRE(xh && trellis && c && svh, "exl3_gemm: null pointer");
+    AMP_REQUIRE(xh && (T || (trellis && c && svh)), "exl3_gemm: null pointer");
+    AMP_REQUIRE(!T || (T->num >= 1 && T->trellis && T->svh && (T->c || c)), "exl3_mgemm: pointer tables are required");
     AMP_REQUIRE(K >= 1 && K <= 8 && cb >= 0 && cb <= 2, "exl3_gemm: unsupported bitrate / codebook");
     AMP_REQUIRE(M >= 1 && k % 128 == 0 && n % 128 == 0 && k > 0 && n > 0, "exl3_gemm: k and n must be multiples of 128");
     AMP_REQUIRE(((uintptr_t) xh & 15) == 0 && ((uintptr_t) trellis & 15) == 0 && ((uintptr_t) c & 15) == 0 &&
                 ((uintptr_t) svh & 7) == 0, "exl3_gemm: misaligned pointer");
+    const long slices = T ? T->num : 1;
+    AMP_REQUIRE(slices * (n / 128) <= 0x3fffffffL, "exl3_gemm: too many column blocks");
     int dev = 0;
     if (cudaError_t e = cudaGetDevice(&dev)) return cuda_rc(e, "cudaGetDevice");
     tc_fn fn = k_tc[cb][K - 1];
@@ -881,6 +926,9 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
     TcParams P;
     P.xt = (const unsigned char*) xh; P.trellis = (const uint16_t*) trellis; P.svh = (const __half*) svh; P.c = c;
     P.M = M; P.k = k; P.n = n; P.c_fp32 = c_fp32;
+    P.tables = T ? 1 : 0;
+    P.t_trellis = T ? T->trellis : nullptr; P.t_svh = T ? T->svh : nullptr; P.t_c = T ? T->c : nullptr;
+    P.t_stride = T ? T->stride : nullptr; P.t_src = T ? T->src : nullptr;
     {
         // address of the status word, looked up once per device (under a lock: two host threads
         // may make their first launch on a device at the same time)
@@ -904,7 +952,7 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
         // with 128: where the 128-row grid still fits one wave of CTA pairs it halves the time
         // (measured: 2048 x 4096 x 1024 0.080 -> 0.068 ms, 1024 x 4096 x 4096 0.073 -> 0.060 ms,
         // against 0.082 / 0.084 ms for the single-CTA form), beyond one wave it doubles the waves.
-        const long pairs128 = (long) (n / 256) * (((long) M + 255) / 256);
+        const long pairs128 = slices * (n / 256) * (((long) M + 255) / 256);
         const int psub = g_tc_pair == 3 ? 1 : (g_tc_pair == 2 ? T2_SUB : (pairs128 <= sms / 2 ? 1 : T2_SUB));
         const long mblk = ((long) M + 256 * psub - 1) / (256 * psub);
         if (mblk <= 65535)
@@ -914,7 +962,7 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
             if (cudaError_t e = ensure_smem(fn2, smem2, dev)) return cuda_rc(e, "exl3_gemm smem attribute");
             P.sub = psub;
             cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3((unsigned) (2 * (n / 256)), (unsigned) mblk, 1);
+            cfg.gridDim = dim3((unsigned) (2 * slices * (n / 256)), (unsigned) mblk, 1);
             cfg.blockDim = dim3(T2_THREADS, 1, 1);
             cfg.dynamicSmemBytes = smem2;
             cfg.stream = stream;
@@ -931,11 +979,11 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
     // single-CTA form: 512 tokens per CTA amortise the decode best; with few column blocks that
     // leaves most SMs idle, so the token tile shrinks until the grid covers the device
     int sub = TC_SUB;
-    while (sub > 1 && (long) (n / 128) * (((long) M + sub * TC_BM - 1) / (sub * TC_BM)) < (long) sms * 4 / 5) sub >>= 1;
+    while (sub > 1 && slices * (n / 128) * (((long) M + sub * TC_BM - 1) / (sub * TC_BM)) < (long) sms * 4 / 5) sub >>= 1;
     P.sub = sub;
     const long mblocks = ((long) M + sub * TC_BM - 1) / (sub * TC_BM);
     AMP_REQUIRE(mblocks <= 65535, "exl3_gemm: too many rows");
-    dim3 grid(n / 128, (unsigned) mblocks);
+    dim3 grid((unsigned) (slices * (n / 128)), (unsigned) mblocks);
     fn<<<grid, TC_THREADS, smem_bytes, stream>>>(P);
     return cuda_rc(cudaGetLastError(), "exl3_gemm_tc launch");
 }

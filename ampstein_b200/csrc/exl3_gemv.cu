@@ -500,11 +500,6 @@ AMP_API int amp_exl3_set_pdl(int enable)
     return old;
 }
 
-namespace amp {
-int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh, int M, int k, int n,
-                   int K, int cb, int c_fp32, cudaStream_t stream);
-int launch_had_tiled(const void* in, void* out, const void* pre, long M, int k, int bf16, cudaStream_t stream);
-}
 extern "C" int amp_had_r_128(const void* in, void* out, const void* pre, const void* post,
                              long rows, int cols, int dtype, float scale, cudaStream_t stream);
 
@@ -547,15 +542,29 @@ AMP_API int amp_exl3_gemm_bf16(const void* A, const void* trellis, void* C, cons
 // them (int64 device arrays). num entries in trellis_ptrs / svh_ptrs (and c_ptrs, n_stride_list,
 // had_src_list when given); suh_ptrs has one entry per source (num_had_src, or num when
 // had_src_list is null). Outputs go to c_ptrs[i] with row width n_stride_list[i], or stacked
-// into C as (num, m, width) when c_ptrs is null. m <= 16.
-AMP_API int amp_exl3_mgemm(const void* x, const void* trellis_ptrs, void* C, const void* suh_ptrs,
-                           void* A_had, const void* svh_ptrs, int num, int m, int k, int width,
-                           int K, int cb, int c_fp32, const void* c_ptrs, const void* n_stride_list,
-                           const void* had_src_list, int num_had_src, cudaStream_t stream)
+// into C as (num, m, width) when c_ptrs is null. Up to 16 rows run on the decode kernel (A_had
+// unused); more rows take the tensor-core path as ONE grid over all slices: the rotated input of
+// every source is written into A_had ((sources, m, k) fp16, required), then the bundle form of the
+// prefill GEMM runs over num * width columns.
+static int mgemm_any(const void* x, int x_bf16, const void* trellis_ptrs, void* C, const void* suh_ptrs,
+                     void* A_had, const void* svh_ptrs, int num, int m, int k, int width,
+                     int K, int cb, int c_fp32, const void* c_ptrs, const void* n_stride_list,
+                     const void* had_src_list, int num_had_src, cudaStream_t stream)
 {
-    (void) A_had; (void) num_had_src;
     if (num == 0 || m == 0) return 0;
-    AMP_REQUIRE(num > 0, "exl3_mgemm: negative matrix count");
+    AMP_REQUIRE(num > 0 && m > 0, "exl3_mgemm: negative matrix or row count");
+    if (m > 16 || x_bf16)
+    {
+        AMP_REQUIRE(x && trellis_ptrs && suh_ptrs && svh_ptrs && (C || c_ptrs), "exl3_mgemm: pointer tables are required");
+        AMP_REQUIRE(A_had, "exl3_mgemm: A_had scratch ((sources, m, k) fp16) is required above 16 rows");
+        AMP_REQUIRE(!had_src_list || num_had_src >= 1, "exl3_mgemm: num_had_src missing");
+        const int sources = had_src_list ? num_had_src : num;
+        if (int rc = launch_had_tiled(x, A_had, nullptr, m, k, x_bf16, stream, (const long long*) suh_ptrs, sources)) return rc;
+        TcTables T;
+        T.num = num; T.trellis = (const long long*) trellis_ptrs; T.svh = (const long long*) svh_ptrs;
+        T.c = (const long long*) c_ptrs; T.stride = (const int*) n_stride_list; T.src = (const int*) had_src_list;
+        return launch_gemm_tc(A_had, nullptr, C, nullptr, m, k, width, K, cb, c_fp32, stream, &T);
+    }
     GemvLaunch A = {};
     A.x = x; A.c = C;
     A.t_trellis = (const long long*) trellis_ptrs; A.t_suh = (const long long*) suh_ptrs;
@@ -564,4 +573,24 @@ AMP_API int amp_exl3_mgemm(const void* x, const void* trellis_ptrs, void* C, con
     A.tables = 1; A.slices = num; A.width = width; A.stride = width;
     A.m = m; A.k = k; A.K = K; A.cb = cb; A.c_fp32 = c_fp32;
     return launch_gemv(A, stream);
+}
+
+AMP_API int amp_exl3_mgemm(const void* x, const void* trellis_ptrs, void* C, const void* suh_ptrs,
+                           void* A_had, const void* svh_ptrs, int num, int m, int k, int width,
+                           int K, int cb, int c_fp32, const void* c_ptrs, const void* n_stride_list,
+                           const void* had_src_list, int num_had_src, cudaStream_t stream)
+{
+    return mgemm_any(x, 0, trellis_ptrs, C, suh_ptrs, A_had, svh_ptrs, num, m, k, width, K, cb, c_fp32,
+                     c_ptrs, n_stride_list, had_src_list, num_had_src, stream);
+}
+
+// Same with bf16 activations (any row count takes the tensor-core path; the reference's bundle is
+// fp16 only, vendor/exl3/exllamav3_ext/quant/exl3_gemm.cu:429).
+AMP_API int amp_exl3_mgemm_bf16(const void* x, const void* trellis_ptrs, void* C, const void* suh_ptrs,
+                                void* A_had, const void* svh_ptrs, int num, int m, int k, int width,
+                                int K, int cb, int c_fp32, const void* c_ptrs, const void* n_stride_list,
+                                const void* had_src_list, int num_had_src, cudaStream_t stream)
+{
+    return mgemm_any(x, 1, trellis_ptrs, C, suh_ptrs, A_had, svh_ptrs, num, m, k, width, K, cb, c_fp32,
+                     c_ptrs, n_stride_list, had_src_list, num_had_src, stream);
 }

@@ -24,6 +24,24 @@ struct GemvLaunch
 
 int launch_gemv(const GemvLaunch& A, cudaStream_t stream);
 
+// Device pointer tables of a bundle for the prefill GEMM (one entry per slice, as exl3_mgemm takes them)
+struct TcTables
+{
+    int num;
+    const long long* trellis; const long long* svh;
+    const long long* c;          // may be null: outputs stacked (num, M, width)
+    const int* stride;           // may be null: row width = slice width
+    const int* src;              // may be null: rotated input i belongs to slice i
+};
+
+// rotated inputs -> outputs on the tensor cores (m > 16); T: bundle form
+int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh, int M, int k, int n,
+                   int K, int cb, int c_fp32, cudaStream_t stream, const TcTables* T = nullptr);
+// (M, k) fp16 / bf16 -> rotated, k-step-major, swizzled x~; pre_table: `sources` device pointers to
+// the scale vectors, one x~ of M * k halves per source written back to back
+int launch_had_tiled(const void* in, void* out, const void* pre, long M, int k, int bf16, cudaStream_t stream,
+                     const long long* pre_table = nullptr, int sources = 1);
+
 extern int g_pdl;
 
 }  // namespace amp

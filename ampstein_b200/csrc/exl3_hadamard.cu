@@ -146,8 +146,14 @@ void had_r_128_kernel(const void* __restrict__ in, void* __restrict__ out,
 template <bool BF16>
 __global__ __launch_bounds__(256)
 void had_tiled_kernel(const void* __restrict__ in, __half* __restrict__ out, const __half* __restrict__ pre,
-                      long chunks, int chunks_per_row, long M, float r_scale)
+                      const long long* __restrict__ pre_table, long chunks, int chunks_per_row, long M, float r_scale)
 {
+    // bundle: blockIdx.y = source; each source has its own scale vector and its own x~
+    if (pre_table)
+    {
+        pre = reinterpret_cast<const __half*>(pre_table[blockIdx.y]);
+        out += (size_t) blockIdx.y * (size_t) chunks * 128;
+    }
     // the GEMM that consumes this kernel's output may be scheduled from now on: it allocates its
     // tensor memory and starts its weight stream under this kernel, and waits (griddepcontrol.wait
     // in its fetch thread) before it reads the first rotated row
@@ -185,15 +191,18 @@ void had_tiled_kernel(const void* __restrict__ in, __half* __restrict__ out, con
 }
 
 // (M, k) fp16 or bf16 -> tiled x~ (M * k halves). Internal to the prefill path.
-int launch_had_tiled(const void* in, void* out, const void* pre, long M, int k, int bf16, cudaStream_t stream)
+int launch_had_tiled(const void* in, void* out, const void* pre, long M, int k, int bf16, cudaStream_t stream,
+                     const long long* pre_table, int sources)
 {
-    AMP_REQUIRE(in && out && pre && M > 0 && k > 0 && k % 128 == 0, "exl3_gemm: bad arguments to the input rotation");
+    AMP_REQUIRE(in && out && (pre || pre_table) && M > 0 && k > 0 && k % 128 == 0, "exl3_gemm: bad arguments to the input rotation");
     AMP_REQUIRE(((uintptr_t) in & 7) == 0 && ((uintptr_t) out & 15) == 0 && ((uintptr_t) pre & 7) == 0, "exl3_gemm: misaligned pointer");
+    AMP_REQUIRE(sources >= 1 && sources <= 65535, "exl3_mgemm: source count out of range");
     const long chunks = M * (k / 128);
     const long blocks = (chunks + 7) / 8;
     AMP_REQUIRE(blocks <= 0x7fffffffL, "exl3_gemm: too many rows");
-    if (bf16) had_tiled_kernel<true><<<(unsigned) blocks, 256, 0, stream>>>(in, (__half*) out, (const __half*) pre, chunks, k / 128, M, kRScale);
-    else had_tiled_kernel<false><<<(unsigned) blocks, 256, 0, stream>>>(in, (__half*) out, (const __half*) pre, chunks, k / 128, M, kRScale);
+    const dim3 grid((unsigned) blocks, pre_table ? (unsigned) sources : 1u);
+    if (bf16) had_tiled_kernel<true><<<grid, 256, 0, stream>>>(in, (__half*) out, (const __half*) pre, pre_table, chunks, k / 128, M, kRScale);
+    else had_tiled_kernel<false><<<grid, 256, 0, stream>>>(in, (__half*) out, (const __half*) pre, pre_table, chunks, k / 128, M, kRScale);
     return cuda_rc(cudaGetLastError(), "exl3_gemm input rotation");
 }
 

@@ -165,13 +165,15 @@ def mgemm(x, B_ptrs, C, suh_ptrs, A_had, svh_ptrs, K, mcg, mul1, opts=None):
     src/torch/amp_torch.cpp:10193-10322). x (1, m, k) fp16; B_ptrs / suh_ptrs / svh_ptrs int64
     CUDA pointer tables; C (num, m, n) stacked output. opts selects sliced mode:
     {size_n_list, c_ptrs, n_stride_list, had_src_list, num_had_src}; C is then only a
-    (num_slices, m, width) descriptor. A_had is accepted and unused. Returns C."""
+    (num_slices, m, width) descriptor. Up to 16 rows A_had is unused; above (one tensor-core grid
+    over all slices) it must be a (sources, m, k) fp16 scratch, sources = num_had_src or num. x may
+    be bfloat16 (tensor-core path at any row count; not in the reference). Returns C."""
     for name, t in (("B_ptrs", B_ptrs), ("suh_ptrs", suh_ptrs), ("svh_ptrs", svh_ptrs)):
         if not isinstance(t, torch.Tensor) or t.dtype != torch.int64 or not t.is_cuda:
             raise TypeError("mgemm: %s must be an int64 CUDA tensor" % name)
     _check_cuda("mgemm", x, C)
-    if x.dtype != torch.float16 or C.dtype not in (torch.float16, torch.float32):
-        raise TypeError("mgemm: x must be float16, C float16 or float32")
+    if x.dtype not in (torch.float16, torch.bfloat16) or C.dtype not in (torch.float16, torch.float32):
+        raise TypeError("mgemm: x must be float16 (or bfloat16), C float16 or float32")
     if x.dim() != 3 or x.shape[0] != 1 or C.dim() != 3:
         raise ValueError("mgemm: x must be (1, m, k) and C (num, m, n)")
     if float(K) != int(K) or not (1 <= int(K) <= 8):
@@ -199,8 +201,18 @@ def mgemm(x, B_ptrs, C, suh_ptrs, A_had, svh_ptrs, K, mcg, mul1, opts=None):
             raise ValueError("mgemm: slice tables do not match C")
     if B_ptrs.numel() < num or svh_ptrs.numel() < num:
         raise ValueError("mgemm: pointer tables shorter than the matrix count")
+    bf16 = x.dtype == torch.bfloat16
+    if m > 16 or bf16:
+        sources = num_had_src if had_src is not None else num
+        if A_had is None:
+            raise ValueError("mgemm: A_had scratch is required above 16 rows")
+        _check_cuda("mgemm", A_had)
+        if A_had.dtype != torch.float16 or not A_had.is_contiguous() or A_had.numel() < sources * m * k:
+            raise ValueError("mgemm: A_had must be a contiguous float16 tensor of (sources, m, k)")
+        if not x.is_contiguous():
+            raise ValueError("mgemm: x must be contiguous")
     with torch.cuda.device(x.device):
-        _lib.call("amp_exl3_mgemm", x.data_ptr(), B_ptrs.data_ptr(), C.data_ptr(), suh_ptrs.data_ptr(),
+        _lib.call("amp_exl3_mgemm_bf16" if bf16 else "amp_exl3_mgemm", x.data_ptr(), B_ptrs.data_ptr(), C.data_ptr(), suh_ptrs.data_ptr(),
                   A_had.data_ptr() if A_had is not None else None, svh_ptrs.data_ptr(), num, m, k, width,
                   int(K), _cb(mul1, mcg), 1 if C.dtype == torch.float32 else 0,
                   c_ptrs.data_ptr() if c_ptrs is not None else None,

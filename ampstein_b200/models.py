@@ -109,9 +109,13 @@ class Multi:
         self.suh = exl3.ptr_array([w.suh.data_ptr() for w in linears], dev)
         self.svh = exl3.ptr_array([w.svh.data_ptr() for w in linears], dev)
 
-    def run(self, x):
+    def run(self, x, a_had=None):
+        """a_had: (num, m, k) fp16 scratch, needed above 16 rows (allocated here if missing)"""
         a = self.linears[0]
-        return exl3.mgemm(x, self.B, self.out, self.suh, None, self.svh, a.K, a.mcg, a.mul1)
+        m = x.shape[1]
+        if a_had is None and (m > 16 or x.dtype == torch.bfloat16):
+            a_had = torch.empty((len(self.linears), m, a.in_features), dtype=torch.float16, device=x.device)
+        return exl3.mgemm(x, self.B, self.out, self.suh, a_had, self.svh, a.K, a.mcg, a.mul1)
 
 
 class Sliced:
@@ -153,9 +157,13 @@ class Sliced:
         # descriptor only: (num_slices, m, width); the data goes through c_ptrs
         self.carrier = torch.empty((len(t), m, width), dtype=torch.float16, device=dev)
 
-    def run(self, x):
+    def run(self, x, a_had=None):
+        """a_had: (linears, m, k) fp16 scratch, needed above 16 rows (allocated here if missing)"""
         a = self.linears[0]
-        exl3.mgemm(x, self.B, self.carrier, self.suh, None, self.svh, a.K, a.mcg, a.mul1, self.opts)
+        m = x.shape[1]
+        if a_had is None and (m > 16 or x.dtype == torch.bfloat16):
+            a_had = torch.empty((len(self.linears), m, a.in_features), dtype=torch.float16, device=x.device)
+        exl3.mgemm(x, self.B, self.carrier, self.suh, a_had, self.svh, a.K, a.mcg, a.mul1, self.opts)
         return self.outs
 
 

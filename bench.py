@@ -464,30 +464,48 @@ LAYER_8B = [("q", 4096, 4096), ("k", 4096, 1024), ("v", 4096, 1024), ("o", 4096,
             ("gate", 4096, 14336), ("up", 4096, 14336), ("down", 14336, 4096)]
 
 
-def measure_prefill(steps, warmup):
+def measure_prefill(steps, warmup, bundles=True):
     """One decoder layer's seven linears at M = 2048 tokens, bf16 activations, mixed bit widths
     (attention K=5, gate/up K=3, down K=4): the tensor-core (tcgen05) trellis-decode GEMM,
-    including the input rotation kernel. One step = the seven GEMMs."""
+    including the input rotation kernels. q|k|v and gate|up run as bundles (one grid each, the
+    reference's mgemm with its sliced / stacked tables) unless bundles is False; one step = the
+    layer's seven GEMMs."""
     import torch
     import ampstein_b200 as amp
+    from ampstein_b200.models import LinearEXL3, Multi, Sliced
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev)
     g.manual_seed(7)
     M = 2048
     bits = {"q": 5, "k": 5, "v": 5, "o": 5, "gate": 3, "up": 3, "down": 4}
-    ops = []
+    lin, xs, ys = {}, {}, {}
     for name, k, n in LAYER_8B:
         K = bits[name]
         t = torch.randint(-32768, 32768, (k // 16, n // 16, 16 * K), dtype=torch.int16, device=dev, generator=g)
         sgn = lambda c: (torch.randint(0, 2, (c,), device=dev, generator=g).to(torch.float16) * 2 - 1)
         svh = (sgn(n) * (1.0 / (1.2437 * math.sqrt(k)))).to(torch.float16)
-        x = torch.randn((M, k), device=dev, generator=g).to(torch.bfloat16)
-        ops.append((x, t, torch.empty((M, n), dtype=torch.float16, device=dev), sgn(k), svh))
+        lin[name] = LinearEXL3(t, sgn(k), svh)
+        xs[name] = torch.randn((1, M, k), device=dev, generator=g).to(torch.bfloat16)
+        ys[name] = torch.empty((1, M, n), dtype=torch.float16, device=dev)
     flops = sum(2.0 * M * k * n for _, k, n in LAYER_8B)
+    gu_out = torch.empty((2, M, 14336), dtype=torch.float16, device=dev)
+    qkv = Sliced([lin["q"], lin["k"], lin["v"]], [ys["q"], ys["k"], ys["v"]])
+    gu = Multi([lin["gate"], lin["up"]], gu_out)
+    had3 = torch.empty((3, M, 4096), dtype=torch.float16, device=dev)
+
+    def single(name):
+        w = lin[name]
+        amp.exl3_gemm(xs[name][0], w.trellis, ys[name][0], w.suh, w.svh)
 
     def step():
-        for x, t, y, suh, svh in ops:
-            amp.exl3_gemm(x, t, y, suh, svh)
+        if bundles:
+            qkv.run(xs["q"], had3)
+            single("o")
+            gu.run(xs["gate"], had3)
+        else:
+            for name in ("q", "k", "v", "o", "gate", "up"):
+                single(name)
+        single("down")
 
     for _ in range(max(warmup, 3)):
         step()
@@ -497,19 +515,22 @@ def measure_prefill(steps, warmup):
     ms_blk, nblk, _ = timed_blocks(torch, step, steps, min_s=0.5)
     clocks = sampler.stop(t0, time.time())
     ms = ms_blk / steps
-    if not all(torch.isfinite(o[2].float()).all() for o in ops):
+    outs = [ys[n] for n in ("q", "k", "v", "o", "down")] + ([gu_out] if bundles else [ys["gate"], ys["up"]])
+    if not all(torch.isfinite(o.float()).all() for o in outs):
         raise SystemExit("bench.py: prefill produced non-finite outputs")
     peaks = _peaks()
     peak = float(peaks.get("bf16_tflops", 1590.0))
     tf = flops / ms / 1e9
+    launches = 8 if bundles else 14
     return {
         "metric": "prefill TFLOP/s (one 8B-shaped layer, M=2048, EXL3 K=5/3/4)", "value": round(tf, 1), "unit": "TFLOP/s",
         "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3), "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "prefill: 7 linears of one llama3-8b-shaped layer, M=2048 bf16 tokens, K=5 attention / 3 gate,up / 4 down",
+                   "launches": "q|k|v and gate|up as bundles (one grid each), o and down single" if bundles else "seven separate GEMMs",
                    "l2": "operands of a step: 0.23 GB (weights read once per GEMM)",
                    "timing": "median of %d blocks of %d steps" % (nblk, steps)},
-        "gpu_launches": 14 * steps, "clocks": clocks,
+        "gpu_launches": launches * steps, "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(tf / peak, 4),
                      "peak_source": "measured burst (MEASURED_PEAKS.json)" if "bf16_tflops" in peaks else "fallback",
                      "kernel": "exl3_gemm_tc2_kernel", "traffic": None}}
@@ -582,6 +603,48 @@ def measure_moe(steps, warmup, T):
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
                      "peak_source": "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback",
                      "kernel": "exl3_gemv_kernel (grouped modes)", "bytes_per_launch": int(byt) // 2, "traffic": None}}
+
+
+def measure_gemv(steps, warmup, shape, m, tmem=False):
+    """One decode GEMV shape on its own (k x n at K bits, m rows): as many distinct copies of the
+    matrix as it takes to exceed L2 twice over, one launch per copy, all in one CUDA graph."""
+    import torch
+    import ampstein_b200 as amp
+    from ampstein_b200.models import DecodeGraph
+    k, n, K = shape
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    wbytes = k * n * K // 8
+    copies = max(1, min(64, -(-2 * 126 * 2 ** 20 // wbytes)))
+    mats = [torch.randint(-32768, 32768, (k // 16, n // 16, 16 * K), dtype=torch.int16, device=dev, generator=g) for _ in range(copies)]
+    sgn = lambda c: (torch.randint(0, 2, (c,), device=dev, generator=g).to(torch.float16) * 2 - 1)
+    suh, svh = sgn(k), (sgn(n) / (1.2437 * math.sqrt(k))).to(torch.float16)
+    x = torch.randn((m, k), device=dev, generator=g).to(torch.float16)
+    y = torch.empty((m, n), dtype=torch.float16, device=dev)
+    graph = DecodeGraph(lambda: [amp.exl3_gemm(x, t, y, suh, svh) for t in mats], warmup=max(warmup, 3))
+    sampler = ClockSampler(0)
+    t0 = time.time()
+    ms_blk, nblk, _ = timed_blocks(torch, graph.replay, steps, graph.stream, min_s=0.3)
+    clocks = sampler.stop(t0, time.time())
+    us = ms_blk * 1e3 / (steps * copies)
+    if not torch.isfinite(y.float()).all():
+        raise SystemExit("bench.py: GEMV produced non-finite outputs")
+    byt = wbytes + 2 * (k + n) + 2 * m * (k + n)
+    peaks = _peaks()
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    gbs = byt / us / 1e3
+    return {
+        "metric": "decode GEMV time (%dx%d, K=%d, m=%d)" % (k, n, K, m), "value": round(us, 2), "unit": "us/launch",
+        "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3), "ms_per_step": round(us * copies / 1e3, 4),
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "one GEMV shape, %d distinct weight copies per graph (%.0f MB, larger than L2)" % (copies, copies * wbytes / 1e6),
+                   "kernel_form": "tensor memory (tcgen05)" if tmem else "mma.sync",
+                   "timing": "median of %d blocks of %d graph replays" % (nblk, steps)},
+        "gpu_launches": copies * steps, "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
+                     "peak_source": "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback",
+                     "kernel": "exl3_gemv_tc_kernel" if tmem else "exl3_gemv_kernel", "bytes_per_launch": byt, "traffic": None}}
 
 
 def measure_issue():
@@ -708,13 +771,17 @@ def main():
                     help="tensor-parallel mode: how the all-reduce after o / down runs. fused (default): push and gather in the "
                          "producing GEMV's epilogue; split: the producer only pushes its partial, the consuming GEMV adds the ranks' "
                          "partials up in its prologue (measured slower); separate: a stand-alone all-reduce launch")
-    ap.add_argument("--workload", default="decode", choices=["decode", "tp5", "prefill", "moe", "issue"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "tp5", "prefill", "moe", "gemv", "issue"],
                     help="decode (default, the headline step), tp5 (the 64-layer 5-bit tensor-parallel stack), or a secondary "
-                         "one-GPU workload: the prefill GEMM / the fused decode MoE / the issue-rate microbenchmark")
+                         "one-GPU workload: the prefill GEMM / the fused decode MoE / one GEMV shape (--shape) / the "
+                         "issue-rate microbenchmark")
+    ap.add_argument("--shape", default="4096x229376x4", help="--workload gemv: k x n x K (rows, columns, bits per weight)")
     ap.add_argument("--batch", type=int, default=1, help="tokens per decode step (decode / tp5 workloads), 1..16")
     ap.add_argument("--tokens", type=int, default=1, choices=[1, 4, 16], help="tokens per step of --workload moe")
     ap.add_argument("--tmem-gemv", action="store_true",
                     help="A/B: run the decode GEMVs on the tensor-memory (tcgen05) kernel instead of the mma.sync kernel")
+    ap.add_argument("--separate", action="store_true",
+                    help="--workload prefill: seven separate GEMM calls instead of the q|k|v and gate|up bundles")
     ap.add_argument("--no-secondary", action="store_true",
                     help="decode workload on one GPU: skip the per-shape and secondary measurements (profiler captures)")
     ap.add_argument("--layers", type=int, default=0,
@@ -731,14 +798,21 @@ def main():
         args.warmup = min(args.warmup, 1)
         run_reference(args)
         return
-    if args.workload in ("prefill", "moe", "issue"):
+    if args.workload in ("prefill", "moe", "gemv", "issue"):
         import torch
         if not torch.cuda.is_available():
             raise SystemExit("bench.py: no CUDA device (the path has no CPU fallback)")
         if args.workload == "prefill":
-            print(json.dumps(measure_prefill(args.steps, args.warmup)), flush=True)
+            print(json.dumps(measure_prefill(args.steps, args.warmup, not args.separate)), flush=True)
         elif args.workload == "moe":
             print(json.dumps(measure_moe(args.steps, args.warmup, args.tokens)), flush=True)
+        elif args.workload == "gemv":
+            try:
+                shape = tuple(int(v) for v in args.shape.lower().split("x"))
+                assert len(shape) == 3 and shape[0] % 128 == 0 and shape[1] % 128 == 0 and 1 <= shape[2] <= 8
+            except (ValueError, AssertionError):
+                raise SystemExit("bench.py: --shape must be KxNxBITS with k, n multiples of 128 and 1..8 bits")
+            print(json.dumps(measure_gemv(args.steps, args.warmup, shape, args.batch, args.tmem_gemv)), flush=True)
         else:
             print(json.dumps({"metric": "scheduler cycles per 8 decoded weights and lane (K=4 mix)", "unit": "cycles",
                               "by_warps_per_scheduler": measure_issue()}), flush=True)

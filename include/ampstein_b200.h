@@ -147,8 +147,10 @@ int amp_exl3_gemv_cfg(const void* x, const void* trellis, void* c, const void* s
  *                                     to its source, NULL = identity
  *   c_ptrs[num] + n_stride_list[num]  per-slice output pointer and row width of the matrix it
  *                                     belongs to; both NULL = outputs stacked in C (num, m, width)
- * All slices share k, K, the codebook and the width (a multiple of 128). A_had is accepted
- * and not used.
+ * All slices share k, K, the codebook and the width (a multiple of 128). Up to 16 rows run on the
+ * decode kernel and A_had is not used; more rows run as ONE tensor-core grid over all slices and
+ * A_had ((sources, m, k) fp16, sources = num_had_src or num) is required: the rotated input of
+ * every source is written there first.
  * Replaces: exl3_mgemm, Q/exl3_gemm.cu:351-735 (binding torch.mgemm,
  * src/torch/amp_torch.cpp:10193-10322; bundle builders src/ucode/ampstein/models.uc:338-432).
  * size_n_list of the reference's signature has no counterpart here: every slice is `width` columns
@@ -158,6 +160,12 @@ int amp_exl3_mgemm(const void* x, const void* trellis_ptrs, void* C, const void*
                    void* A_had, const void* svh_ptrs, int num, int m, int k, int width,
                    int K, int cb, int c_fp32, const void* c_ptrs, const void* n_stride_list,
                    const void* had_src_list, int num_had_src, cudaStream_t stream);
+/* The same with bf16 activations (any row count takes the tensor-core path). No counterpart in the
+ * reference, whose bundle checks for fp16 (Q/exl3_gemm.cu:429). */
+int amp_exl3_mgemm_bf16(const void* x, const void* trellis_ptrs, void* C, const void* suh_ptrs,
+                        void* A_had, const void* svh_ptrs, int num, int m, int k, int width,
+                        int K, int cb, int c_fp32, const void* c_ptrs, const void* n_stride_list,
+                        const void* had_src_list, int num_had_src, cudaStream_t stream);
 
 /*
  * Fused decode-shaped MoE: out[row] = sum over the row's active picks of rw * expert(x[row]),

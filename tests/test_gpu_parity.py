@@ -214,6 +214,49 @@ def test_mgemm_multi_and_sliced(amp, oracle):
         check_close(o[0].cpu().numpy(), oracle.linear(x, t, su, sv, 0, fp32_out=True))
 
 
+@pytest.mark.parametrize("m,bf16", [(40, False), (300, False), (130, True)])
+def test_mgemm_bundles_above_16_rows(amp, oracle, m, bf16):
+    """The same bundles at prefill row counts: one tensor-core grid over all slices (pair form
+    for widths that are multiples of 256, single-CTA form for 128). Checked against the oracle and,
+    bit for bit, against separate exl3_gemm calls (same rotation, same tiles)."""
+    from ampstein_b200.models import LinearEXL3, Multi, Sliced
+    k = 512
+    rng = np.random.default_rng(78 + m)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    xt = torch.from_numpy(x).cuda().to(torch.bfloat16 if bf16 else torch.float16)
+    x = xt.float().cpu().numpy().astype(np.float16)   # what the kernel sees (bf16 values are exact in fp16 here)
+    xd = xt.reshape(1, m, k)
+
+    def lin(n, seed, K=4):
+        trellis, suh, svh, _ = make_linear(k, n, K, seed=seed)
+        return (trellis, suh, svh), LinearEXL3(dev(trellis), dev(suh), dev(svh))
+
+    def separate(w, n):
+        y = torch.empty((m, n), dtype=torch.float16, device="cuda")
+        amp.exl3_gemm(xt, w.trellis, y, w.suh, w.svh)
+        return y
+
+    (g_np, g), (u_np, u) = lin(768, 11, 3), lin(768, 12, 3)
+    out = torch.full((2, m, 768), float("nan"), dtype=torch.float16, device="cuda")
+    Multi([g, u], out).run(xd)
+    torch.cuda.synchronize()
+    for i, ((t, su, sv), w) in enumerate(((g_np, g), (u_np, u))):
+        check_close(out[i].cpu().numpy(), oracle.linear(x, t, su, sv, 0, fp32_out=True))
+        assert torch.equal(out[i], separate(w, 768))
+
+    for widths in ((1024, 256, 256), (384, 128, 128)):
+        parts = [lin(n, 20 + i + n) for i, n in enumerate(widths)]
+        outs = [torch.full((1, m, n), float("nan"), dtype=torch.float16, device="cuda") for n in widths]
+        sl = Sliced([p[1] for p in parts], outs)
+        assert sl.width == min(widths)
+        sl.run(xd)
+        torch.cuda.synchronize()
+        for o, ((t, su, sv), w), n in zip(outs, parts, widths):
+            check_close(o[0].cpu().numpy(), oracle.linear(x, t, su, sv, 0, fp32_out=True))
+            assert torch.equal(o[0], separate(w, n))
+    assert gemm_status() == 0
+
+
 def test_gemm_more_than_16_rows(amp, oracle):
     trellis, suh, svh, x = make_linear(256, 256, 3, seed=6000, m=37)
     ref = oracle.linear(x, trellis, suh, svh, 1, fp32_out=True)
