@@ -73,6 +73,7 @@ struct TcParams
     int M, k, n, c_fp32;        // n: row width of the trellis / output (bundle: columns per slice)
     int sub;                    // 128-token sub-tiles per CTA: 4, or fewer when the grid would leave SMs idle
     int* status;
+    int relay_release;          // pair form: the relay's remote arrival releases at cluster scope (slower; default relaxed)
     // bundle (tables == 1): several matrices or equal-width column slices in one grid, identified
     // by device pointer tables with one entry per slice, exactly as the decode kernel's table mode
     int tables;
@@ -506,15 +507,15 @@ __device__ __forceinline__ uint32_t cluster_addr(const void* p, uint32_t rank)
 // completion the relay observed with an acquire, the weight tile by warps that each ran
 // fence.proxy.async and a releasing arrive on the barrier the relay acquired; both live in this
 // SM's shared memory, which is read in place by the pair's tensor cores and cached nowhere.
-// AMP_T2_RELEASE_RELAY selects the releasing form. A test runs the benchmark's shapes twelve
-// times and requires bit-identical results.
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
+// This leans on a property of the hardware, not on a rule of the PTX memory model: on paper the
+// relay's acquire of its own barriers and the first CTA's acquire of this arrival are only
+// chained into one causality order if the arrival releases (or a fence.acq_rel.cluster stands in
+// front of it). `release` selects that form at run time (amp_exl3_set_gemm_relay_release); a test
+// runs the benchmark's shapes in both forms, twelve launches each, and requires identical bits.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar, int release)
 {
-#ifdef AMP_T2_RELEASE_RELAY
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_bar) : "memory");
-#else
-    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_bar) : "memory");
-#endif
+    if (release) asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_bar) : "memory");
+    else asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_bar) : "memory");
 }
 
 // Arrives, once every tcgen05.mma issued so far by this thread has completed, on the barrier at
@@ -748,7 +749,7 @@ void exl3_gemm_tc2_kernel(const TcParams P)
                     wait_bar_spin(&a_land[s], ph);
                     wait_bar_spin(&b_full[s], ph);
                     if (!ok) break;
-                    mbar_arrive_cluster(cluster_addr(&a_land[s], 0));
+                    mbar_arrive_cluster(cluster_addr(&a_land[s], 0), P.relay_release);
                     if (++s == S) { s = 0; ph ^= 1; }
                 }
             }
@@ -901,6 +902,7 @@ static const tc_fn k_tc[3][8] = { AMP_TC_ROW(0), AMP_TC_ROW(1), AMP_TC_ROW(2) };
                           exl3_gemm_tc2_kernel<5, cb>, exl3_gemm_tc2_kernel<6, cb>, exl3_gemm_tc2_kernel<7, cb>, exl3_gemm_tc2_kernel<8, cb> }
 static const tc_fn k_tc2[3][8] = { AMP_TC2_ROW(0), AMP_TC2_ROW(1), AMP_TC2_ROW(2) };
 #undef AMP_TC2_ROW
+int g_tc_relay_release = 0;
 int g_tc_pair = 1;        // pair (cta_group::2) form: 0 never, 1 where it fills the device, 2 whenever n % 256 == 0
 
 // tiled x~ (launch_had_tiled) -> C. Called by amp_exl3_gemm for m > 16, and by amp_exl3_mgemm
@@ -927,6 +929,7 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
     P.xt = (const unsigned char*) xh; P.trellis = (const uint16_t*) trellis; P.svh = (const __half*) svh; P.c = c;
     P.M = M; P.k = k; P.n = n; P.c_fp32 = c_fp32;
     P.tables = T ? 1 : 0;
+    P.relay_release = g_tc_relay_release;
     P.t_trellis = T ? T->trellis : nullptr; P.t_svh = T ? T->svh : nullptr; P.t_c = T ? T->c : nullptr;
     P.t_stride = T ? T->stride : nullptr; P.t_src = T ? T->src : nullptr;
     {
@@ -1008,6 +1011,15 @@ AMP_API int amp_exl3_gemm_status(int* out)
 // the pair form, 1 = by shape (default: pairs whenever n is a multiple of 256, 128-token CTAs while
 // that grid fits one wave, 256-token CTAs beyond), 2 / 3 = pairs of 256- / 128-token CTAs whenever
 // n is a multiple of 256 (tests). Returns the previous setting.
+// The pair form's remote arrival: 0 = relaxed (default), 1 = release at cluster scope (what the PTX
+// memory model asks for on paper; measured 10-15 % slower). Returns the previous setting.
+AMP_API int amp_exl3_set_gemm_relay_release(int enable)
+{
+    const int old = g_tc_relay_release;
+    g_tc_relay_release = enable ? 1 : 0;
+    return old;
+}
+
 AMP_API int amp_exl3_set_gemm_pair(int mode)
 {
     const int old = g_tc_pair;

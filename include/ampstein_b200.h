@@ -97,6 +97,13 @@ int amp_exl3_gemm_bf16(const void* A, const void* trellis, void* C, const void* 
  * counterpart in the reference.
  */
 int amp_exl3_set_gemm_pair(int mode);
+/*
+ * Pair form only: the one remote mbarrier arrival per k step that tells the first CTA of a pair that
+ * the second CTA's operands are ready is `relaxed` by default; 1 selects `release.cluster`, the form
+ * the PTX memory model asks for on paper (slower; results are identical, which a test checks).
+ * Returns the previous setting. No counterpart in the reference.
+ */
+int amp_exl3_set_gemm_relay_release(int enable);
 
 /* Reads and clears the prefill GEMM's status word (non-zero: a bounded wait on a tensor-core
  * completion barrier ran out). Synchronises; diagnostics only. */

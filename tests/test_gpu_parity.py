@@ -336,6 +336,16 @@ def test_prefill_gemm_bench_shapes_repeatable(amp, k, n, K):
     assert gemm_status() == 0
     for y in outs[1:]:
         assert torch.equal(y, outs[0])
+    # the releasing form of the pair's remote arrival must give the same bits as the relaxed default
+    prev = _lib.lib().amp_exl3_set_gemm_relay_release(1)
+    try:
+        for _ in range(12):
+            y = torch.empty((m, n), dtype=torch.float16, device="cuda")
+            amp.exl3_gemm(x, t, y, suh, svh)
+            assert torch.equal(y, outs[0])
+    finally:
+        _lib.lib().amp_exl3_set_gemm_relay_release(prev)
+    assert gemm_status() == 0
     old = _lib.lib().amp_exl3_set_gemm_pair(0)
     try:
         y1 = torch.empty((m, n), dtype=torch.float16, device="cuda")
