@@ -124,6 +124,38 @@ int g_gemv_tc = 0;
 // (with more than 16 units per CTA the grid of 8 x blocks CTAs is too coarse: measured slower)
 constexpr int GEMV_CLUSTER = 8, GEMV_CLUSTER_MAX_M = 4, GEMV_CLUSTER_MAX_UNITS = 16;
 
+// x~ = fp16(H(x * suh) / sqrt(128)) of every source, (sources, m, k) fp16 row-major: one warp per
+// 128 values, the arithmetic of the GEMV kernel's own prologue (fp16 scale, fp32 butterfly, one
+// rounding). Runs right before a GEMV of five or more rows, which then only copies x~ into
+// fragment order instead of rotating all rows of its range in every CTA.
+__global__ __launch_bounds__(256)
+void gemv_prerotate_kernel(const __half* __restrict__ x, __half* __restrict__ out, const __half* __restrict__ suh,
+                           const long long* __restrict__ t_suh, int m, int k, int pdl)
+{
+    // the GEMV behind this launch may start its weight stream now; it waits for this grid before it
+    // reads x~, and this grid waits for the producer of x
+    if (pdl) pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int per_row = k >> 7;
+    const int task = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (task >= m * per_row) return;
+    const int b = task / per_row, jb = task - b * per_row;
+    if (t_suh) suh = reinterpret_cast<const __half*>(t_suh[blockIdx.y]);
+    const half4 sc = *reinterpret_cast<const half4*>(suh + (size_t) jb * 128 + lane * 4);
+    if (pdl) pdl_wait();
+    half4 v = *reinterpret_cast<const half4*>(x + (size_t) b * k + (size_t) jb * 128 + lane * 4);
+    v.x = __hmul2(v.x, sc.x);
+    v.y = __hmul2(v.y, sc.y);
+    float h0 = __low2float(v.x), h1 = __high2float(v.x), h2 = __low2float(v.y), h3 = __high2float(v.y);
+    warp_had128(h0, h1, h2, h3, lane);
+    half4 o;
+    o.x = __floats2half2_rn(h0 * kRScale, h1 * kRScale);
+    o.y = __floats2half2_rn(h2 * kRScale, h3 * kRScale);
+    *reinterpret_cast<half4*>(out + ((size_t) blockIdx.y * m + b) * k + (size_t) jb * 128 + lane * 4) = o;
+}
+
+constexpr int GEMV_PREROTATE_MIN_M = 5;
+
 int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
 {
     const int m = A.m, k = A.k, K = A.K;
@@ -157,18 +189,33 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
 
     const int MB = m <= 8 ? 1 : 2;
     const bool tc = !A.mode && m <= TCV_MAX_M && g_gemv_tc && !A.arin.N && !A.ar.push_only;
-    gemv_fn fn = tc ? gemv_tc_kernel_for(K, A.cb, A.ar.N != 0) : gemv_kernel_for(K, A.cb, MB, A.mode, A.arin.N != 0);
+    // five rows or more with a scratch for the rotated input: rotate once, in a launch of its own
+    const bool prerot = !tc && !A.mode && !A.arin.N && m >= GEMV_PREROTATE_MIN_M && A.x_rot && A.x;
+    gemv_fn fn = tc ? gemv_tc_kernel_for(K, A.cb, A.ar.N != 0) : gemv_kernel_for(K, A.cb, MB, A.mode, A.arin.N ? 1 : (prerot ? 2 : 0));
     if (!fn) return fail(AMP_E_UNSUPPORTED, "exl3_gemv: no kernel for K=%d cb=%d", K, A.cb);
 
     // x~ rows resident at a time: at most 16 KB of shared memory (whole segments for small
     // batches, so the main loop rarely meets a block-wide barrier); shrunk below to what a
     // CTA's range needs
     const int G = k / 64;
-    int xcap = (16 * 1024 / (m * 4)) / 64;
-    xcap &= ~3;
-    if (xcap > GEMV_XCHUNK_MAX / 64) xcap = GEMV_XCHUNK_MAX / 64;
-    if (xcap > (G + 3) / 4 * 4) xcap = (G + 3) / 4 * 4;
-    if (xcap < 4) xcap = 4;
+    const int smem_per_sm = D.smem_optin + 1024;                       // opt-in limit excludes 1 KB per CTA
+    const int reg_ctas = tc ? 4 : (m <= 8 ? 3 : 4);                    // CTAs per SM the register budget allows
+    auto xcap_for = [&](int kb)
+    {
+        int c = (kb * 1024 / (m * 4)) / 64;
+        c &= ~3;
+        if (c > GEMV_XCHUNK_MAX / 64) c = GEMV_XCHUNK_MAX / 64;
+        if (c > (G + 3) / 4 * 4) c = (G + 3) / 4 * 4;
+        return c < 4 ? 4 : c;
+    };
+    int xcap = xcap_for(16);
+    if (m > 4)
+    {
+        // several batch rows: twice the x~ budget (half as many block-wide x~ passes per range)
+        // where that does not cost a resident CTA
+        const int big = xcap_for(32);
+        if (smem_per_sm / (gemv_smem_layout(K, m, big).total + 1024) >= reg_ctas) xcap = big;
+    }
     if (A.force_xgroups > 0)
     {
         AMP_REQUIRE(A.force_xgroups % 4 == 0 && A.force_xgroups <= GEMV_XCHUNK_MAX / 64,
@@ -180,12 +227,10 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     GemvSmem L = gemv_smem_layout(K, m, xcap);
     if (tc) L.total = tcv_smem_layout(K, m, tc_xg).total;
     AMP_REQUIRE(L.total <= D.smem_optin, "exl3_gemv: shared memory layout does not fit (%d bytes)", L.total);
-    const int smem_per_sm = D.smem_optin + 1024;                       // opt-in limit excludes 1 KB per CTA
     // CTAs per SM: the decode is bound by the rate of the integer pipes, not by latency, so
     // three 4-warp CTAs per SM run as fast as six (measured) and halve the partial sums that
     // have to be exchanged
     // (the tensor-memory kernel: four CTAs of 128 tensor-memory columns fill an SM's 512)
-    const int reg_ctas = tc ? 4 : (MB == 1 ? 3 : 4);
     int ctas_per_sm = smem_per_sm / (L.total + 1024);
     if (ctas_per_sm > reg_ctas) ctas_per_sm = reg_ctas;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
@@ -286,6 +331,26 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
         if (!sp)
             if (cudaError_t e = cudaGetSymbolAddress((void**) &sp, g_gemv_status)) return cuda_rc(e, "status symbol");
         P.status = sp;
+    }
+
+    if (prerot)
+    {
+        const int sources = A.tables ? (A.num_src > 0 ? A.num_src : A.slices) : 1;
+        AMP_REQUIRE(sources >= 1 && sources <= 65535, "exl3_gemv: source count out of range");
+        AMP_REQUIRE(((uintptr_t) A.x_rot & 7) == 0, "exl3_gemv: A_had must be 8-byte aligned");
+        cudaLaunchConfig_t pc = {};
+        pc.gridDim = dim3((unsigned) (((long) m * (k / 128) + 7) / 8), (unsigned) sources, 1);
+        pc.blockDim = dim3(256, 1, 1);
+        pc.stream = stream;
+        cudaLaunchAttribute pa[1];
+        pa[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        pa[0].val.programmaticStreamSerializationAllowed = 1;
+        pc.attrs = pa;
+        pc.numAttrs = g_pdl ? 1 : 0;
+        if (cudaError_t e = cudaLaunchKernelEx(&pc, gemv_prerotate_kernel, (const __half*) A.x, (__half*) A.x_rot, (const __half*) A.suh,
+                                               A.tables ? A.t_suh : (const long long*) nullptr, m, k, g_pdl))
+            return cuda_rc(e, "exl3_gemv input rotation launch");
+        P.x = (const __half*) A.x_rot;
     }
 
     cudaLaunchConfig_t cfg = {};
@@ -503,8 +568,9 @@ AMP_API int amp_exl3_set_pdl(int enable)
 extern "C" int amp_had_r_128(const void* in, void* out, const void* pre, const void* post,
                              long rows, int cols, int dtype, float scale, cudaStream_t stream);
 
-// C = had(A*suh) @ W_hat -> had(.)*svh for any m. Up to 16 rows run on the decode kernel (A_had is
-// then unused: the input transform lives in the kernel's prologue); more rows take the
+// C = had(A*suh) @ W_hat -> had(.)*svh for any m. Up to 16 rows run on the decode kernel (the input
+// transform lives in the kernel's prologue up to four rows; from five rows on, when A_had is given,
+// a small launch of its own rotates the input into A_had once); more rows take the
 // tensor-core path: x~ is written into A_had (same shape as A, fp16: required) by the Hadamard
 // kernel and the tcgen05 GEMM consumes it. a_bf16: A holds bf16 instead of fp16 (m > 16 only).
 static int gemm_any(const void* A, int a_bf16, const void* trellis, void* C, const void* suh, void* A_had,
@@ -513,7 +579,11 @@ static int gemm_any(const void* A, int a_bf16, const void* trellis, void* C, con
     AMP_REQUIRE(m >= 0, "exl3_gemm: negative m");
     if (m == 0) return 0;
     if (m <= 16 && !a_bf16)
-        return launch_gemv(direct(A, trellis, C, suh, svh, m, k, n, K, cb, c_fp32, 0, 0), stream);
+    {
+        GemvLaunch L = direct(A, trellis, C, suh, svh, m, k, n, K, cb, c_fp32, 0, 0);
+        L.x_rot = A_had;                               // optional: used from five rows up
+        return launch_gemv(L, stream);
+    }
     AMP_REQUIRE(A_had, "exl3_gemm: A_had scratch (same shape as A, fp16) is required above 16 rows");
     AMP_REQUIRE(A && suh && k > 0 && k % 128 == 0, "exl3_gemm: bad input");
     if (int rc = launch_had_tiled(A, A_had, suh, m, k, a_bf16, stream)) return rc;
@@ -572,6 +642,8 @@ static int mgemm_any(const void* x, int x_bf16, const void* trellis_ptrs, void* 
     A.t_stride = (const int*) n_stride_list; A.t_src = (const int*) had_src_list;
     A.tables = 1; A.slices = num; A.width = width; A.stride = width;
     A.m = m; A.k = k; A.K = K; A.cb = cb; A.c_fp32 = c_fp32;
+    A.num_src = had_src_list ? num_had_src : num;
+    A.x_rot = A.num_src >= 1 ? A_had : nullptr;                     // optional: used from five rows up
     return launch_gemv(A, stream);
 }
 

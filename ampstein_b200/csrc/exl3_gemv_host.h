@@ -20,6 +20,8 @@ struct GemvLaunch
     int ws_max_ctas;
     GemvAr ar;           // fused tensor-parallel all-reduce of the output (ar.N == 0: none)
     GemvArIn arin;       // the input is gathered from the communicator's buffer (arin.N == 0: plain x)
+    void* x_rot;         // optional scratch, (sources, m, k) fp16: with five rows or more the input is rotated
+    int num_src;         // once by a launch of its own instead of by every CTA (sources: 1, or the bundle's)
 };
 
 int launch_gemv(const GemvLaunch& A, cudaStream_t stream);

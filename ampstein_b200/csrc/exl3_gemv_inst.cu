@@ -21,6 +21,13 @@ gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB, int mode, int gin)
         { exl3_gemv_kernel<AMP_GEMV_K, 1, 1, 0, 1>, exl3_gemv_kernel<AMP_GEMV_K, 1, 2, 0, 1> },
         { exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 0, 1>, exl3_gemv_kernel<AMP_GEMV_K, 2, 2, 0, 1> },
     };
+    // input already rotated (batches of five rows and more)
+    static const gemv_fn fnr[3][2] =
+    {
+        { exl3_gemv_kernel<AMP_GEMV_K, 0, 1, 0, 2>, exl3_gemv_kernel<AMP_GEMV_K, 0, 2, 0, 2> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 1, 1, 0, 2>, exl3_gemv_kernel<AMP_GEMV_K, 1, 2, 0, 2> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 0, 2>, exl3_gemv_kernel<AMP_GEMV_K, 2, 2, 0, 2> },
+    };
     static const gemv_fn fn[3][2] =
     {
         { exl3_gemv_kernel<AMP_GEMV_K, 0, 1>, exl3_gemv_kernel<AMP_GEMV_K, 0, 2> },
@@ -35,7 +42,7 @@ gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB, int mode, int gin)
     };
     if (cb < 0 || cb > 2 || MB < 1 || MB > 2 || mode < 0 || mode > 2) return nullptr;
     if (mode) return (MB == 1 && !gin) ? moe[cb][mode - 1] : nullptr;
-    return gin ? fng[cb][MB - 1] : fn[cb][MB - 1];
+    return gin == 2 ? fnr[cb][MB - 1] : (gin ? fng[cb][MB - 1] : fn[cb][MB - 1]);
 }
 
 // tensor-memory form (dense / bundle launches of up to eight rows)

@@ -529,13 +529,14 @@ __device__ __forceinline__ void gather_chunk(half4* stage, const uint2* gbase, i
 // MODE 0: one matrix or a bundle sharing one input.  MODE 1: grouped expert gate/up (slice = expert
 // run x projection, input rows gathered by token).  MODE 2: grouped expert down (input = the
 // activation of the run's gate/up rows, computed on the fly).
-// GIN: MODE 0 instance whose input is gathered from the all-reduce buffers (GemvArIn)
+// GIN: MODE 0 instances with another input side. 1: the input is gathered from the all-reduce
+// buffers (GemvArIn). 2: the input arrives already rotated (several batch rows, gemv_prerotate_kernel).
 template <int K, int CB, int MB, int MODE = 0, int GIN = 0>
 __global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 3))
 void exl3_gemv_kernel(const GemvParams P)
 {
     extern __shared__ __align__(128) unsigned char smem[];
-    const GemvSmem L = gemv_smem_layout(K, P.m, P.xgroups, P.cluster, GIN);
+    const GemvSmem L = gemv_smem_layout(K, P.m, P.xgroups, P.cluster, GIN == 1);
     const int XPITCH = gemv_xpitch(P.xgroups);
     const int XG = P.xgroups;
     float* part = reinterpret_cast<float*>(smem + L.part);
@@ -742,6 +743,7 @@ void exl3_gemv_kernel(const GemvParams P)
         int stride = P.stride;
         int nrows = m;                                 // batch rows of this segment
         const unsigned char* run_slots = nullptr;      // grouped modes: the run's slot indices
+        const __half* xrot = P.x;                      // GIN == 2: this slice's rotated input
         if constexpr (MODE != 0)
         {
             const int run = slice / nproj, proj = (MODE == 2) ? 2 : (P.moe.gated ? slice - run * nproj : 1);
@@ -762,6 +764,7 @@ void exl3_gemv_kernel(const GemvParams P)
         else if (P.tables)
         {
             const int src = P.t_src ? P.t_src[slice] : slice;
+            if constexpr (GIN == 2) xrot = P.x + (size_t) src * m * k;
             suh = reinterpret_cast<const __half*>(P.t_suh[src]);
             svh = reinterpret_cast<const __half*>(P.t_svh[slice]);
             stride = P.t_stride ? P.t_stride[slice] : P.width;
@@ -792,12 +795,9 @@ void exl3_gemv_kernel(const GemvParams P)
             // x~ = fp16(H(x * suh) / sqrt(128)), stored duplicated ((v, v) per word) and in the
             // order the B fragments are read: word = group*64 + (row%16 / 4)*16 + (row%64 / 16)*4 + row%4.
             // Tasks (batch row b, 128-row block jb) go round the warps.
-            // transform one task's four values per lane and store them; b, jb name the task
-            auto had_store = [&](int b, int jb, float h0, float h1, float h2, float h3)
+            // store one task's four rotated values per lane; b, jb name the task
+            auto frag_store = [&](int b, int jb, const __half2 o01, const __half2 o23)
             {
-                warp_had128(h0, h1, h2, h3, lane);
-                const __half2 o01 = __floats2half2_rn(h0 * kRScale, h1 * kRScale);
-                const __half2 o23 = __floats2half2_rn(h2 * kRScale, h3 * kRScale);
                 const uint32_t u01 = *reinterpret_cast<const uint32_t*>(&o01);
                 const uint32_t u23 = *reinterpret_cast<const uint32_t*>(&o23);
                 uint4 d;
@@ -815,7 +815,49 @@ void exl3_gemv_kernel(const GemvParams P)
                     if ((lane & 15) == 0) gsum[b * XG + 2 * jb + (lane >> 4)] = sg;
                 }
             };
-            if constexpr (MODE == 0 && !GIN)
+            auto had_store = [&](int b, int jb, float h0, float h1, float h2, float h3)
+            {
+                warp_had128(h0, h1, h2, h3, lane);
+                frag_store(b, jb, __floats2half2_rn(h0 * kRScale, h1 * kRScale), __floats2half2_rn(h2 * kRScale, h3 * kRScale));
+            };
+            if constexpr (MODE == 0 && GIN == 2)
+            {
+                // The input arrives rotated (fp16 x~ of every source, written by gemv_prerotate_kernel
+                // right before this launch): only the copy into fragment order is left, eight tasks
+                // per pass. With several batch rows the rotation would otherwise be repeated by every
+                // CTA for all rows of its range.
+                if (!waited) { if (P.pdl) pdl_wait(); waited = true; }
+                int b = 0, jb = warp;
+                while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
+                do
+                {
+                    constexpr int TB = 8;
+                    half4 vx[TB];
+                    int tb[TB], tj[TB];
+                    #pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                    {
+                        tb[i] = b; tj[i] = jb;
+                        if (b < nrows)
+                        {
+                            vx[i] = *reinterpret_cast<const half4*>(xrot + (size_t) b * k + (size_t) cg0 * 64 + (size_t) jb * 128 + lane * 4);
+                            jb += GEMV_WARPS;
+                            while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
+                        }
+                        else tb[i] = -1;
+                    }
+                    if (!started)
+                    {
+                        #pragma unroll
+                        for (int j = 0; j < S - 1; ++j) issue();
+                        started = true;
+                    }
+                    #pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                        if (tb[i] >= 0) frag_store(tb[i], tj[i], vx[i].x, vx[i].y);
+                } while (b < nrows);
+            }
+            else if constexpr (MODE == 0 && GIN == 0)
             {
                 // up to six tasks per pass: all their loads are in flight before the first
                 // transform (at grid start a load takes a microsecond), and the weight stream is
@@ -866,7 +908,7 @@ void exl3_gemv_kernel(const GemvParams P)
             {
                 if constexpr (MODE == 0)
                 {
-                    // Gathered input (split exchange): the whole CTA adds up the ranks' partials of this
+                    // (GIN == 1) Gathered input (split exchange): the whole CTA adds up the ranks' partials of this
                     // chunk's rows, two units per thread in flight, into a staging area. The local
                     // producer has completed (stream order / the wait for the predecessor), so its
                     // sequence number is final; the peers' words may still be on their way.
@@ -1092,14 +1134,27 @@ void exl3_gemv_kernel(const GemvParams P)
             finish = s_last != 0;
             if (finish)
             {
-                // only the first contributor can have started before this block (its second slot)
+                // only the first contributor can have started before this block (its second slot).
+                // Four values per thread and up to eight contributors' loads in flight at a time
+                // (one after the other they are a chain of L2 round trips on the critical path of
+                // the launch); the adds stay in ascending k order: deterministic.
                 const int first_slot = 2 * i_first + (blk * G > split.begin(i_first) ? 1 : 0);
-                for (int idx = t; idx < nrows * 128; idx += GEMV_THREADS)
+                const size_t pitch = (size_t) 2 * m * 128;               // floats between consecutive contributors' slots
+                for (int idx = 4 * t; idx < nrows * 128; idx += 4 * GEMV_THREADS)
                 {
-                    float sum = __ldcg(slots + (size_t) first_slot * m * 128 + idx);
-                    for (int i = i_first + 1; i <= i_last; ++i)       // ascending k: deterministic
-                        sum += __ldcg(slots + (size_t) (2 * i) * m * 128 + idx);
-                    part[idx] = sum;
+                    float4 sum = __ldcg(reinterpret_cast<const float4*>(slots + (size_t) first_slot * m * 128 + idx));
+                    const float* src = slots + (size_t) (i_first + 1) * pitch + idx;
+                    for (int i = i_first + 1; i <= i_last; i += 8, src += 8 * pitch)
+                    {
+                        float4 v[8];
+                        #pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (i + j <= i_last) v[j] = __ldcg(reinterpret_cast<const float4*>(src + j * pitch));
+                        #pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (i + j <= i_last) { sum.x += v[j].x; sum.y += v[j].y; sum.z += v[j].z; sum.w += v[j].w; }
+                    }
+                    *reinterpret_cast<float4*>(part + idx) = sum;
                 }
             }
         }

@@ -130,7 +130,8 @@ def exl3_gemm(A, B, C, suh, svh, mul1=False, mcg=False):
     bf16 = A.dtype == torch.bfloat16
     # the binding allocates the input-rotation scratch per call, as the reference's does
     # (src/torch/amp_torch.cpp:11282); the decode kernel (<= 16 rows) does not need it
-    A_had = torch.empty(A.shape, dtype=torch.float16, device=A.device) if (m > 16 or bf16) else None
+    # (from five rows on it lets the input be rotated once instead of by every CTA)
+    A_had = torch.empty(A.shape, dtype=torch.float16, device=A.device) if (m >= 5 or bf16) else None
     with torch.cuda.device(A.device):
         _lib.call("amp_exl3_gemm_bf16" if bf16 else "amp_exl3_gemm", A.data_ptr(), B.data_ptr(), C.data_ptr(),
                   suh.data_ptr(), A_had.data_ptr() if A_had is not None else None, svh.data_ptr(), m, k, n, K,
@@ -165,8 +166,9 @@ def mgemm(x, B_ptrs, C, suh_ptrs, A_had, svh_ptrs, K, mcg, mul1, opts=None):
     src/torch/amp_torch.cpp:10193-10322). x (1, m, k) fp16; B_ptrs / suh_ptrs / svh_ptrs int64
     CUDA pointer tables; C (num, m, n) stacked output. opts selects sliced mode:
     {size_n_list, c_ptrs, n_stride_list, had_src_list, num_had_src}; C is then only a
-    (num_slices, m, width) descriptor. Up to 16 rows A_had is unused; above (one tensor-core grid
-    over all slices) it must be a (sources, m, k) fp16 scratch, sources = num_had_src or num. x may
+    (num_slices, m, width) descriptor. A_had is a (sources, m, k) fp16 scratch, sources =
+    num_had_src or num: unused up to 4 rows, optional up to 16 (when given, the input is rotated once
+    by a launch of its own), required above (one tensor-core grid over all slices). x may
     be bfloat16 (tensor-core path at any row count; not in the reference). Returns C."""
     for name, t in (("B_ptrs", B_ptrs), ("suh_ptrs", suh_ptrs), ("svh_ptrs", svh_ptrs)):
         if not isinstance(t, torch.Tensor) or t.dtype != torch.int64 or not t.is_cuda:
@@ -202,7 +204,7 @@ def mgemm(x, B_ptrs, C, suh_ptrs, A_had, svh_ptrs, K, mcg, mul1, opts=None):
     if B_ptrs.numel() < num or svh_ptrs.numel() < num:
         raise ValueError("mgemm: pointer tables shorter than the matrix count")
     bf16 = x.dtype == torch.bfloat16
-    if m > 16 or bf16:
+    if m > 16 or bf16 or (m >= 5 and A_had is not None):
         sources = num_had_src if had_src is not None else num
         if A_had is None:
             raise ValueError("mgemm: A_had scratch is required above 16 rows")

@@ -110,10 +110,10 @@ class Multi:
         self.svh = exl3.ptr_array([w.svh.data_ptr() for w in linears], dev)
 
     def run(self, x, a_had=None):
-        """a_had: (num, m, k) fp16 scratch, needed above 16 rows (allocated here if missing)"""
+        """a_had: (num, m, k) fp16 scratch, used from five rows up (allocated here if missing)"""
         a = self.linears[0]
         m = x.shape[1]
-        if a_had is None and (m > 16 or x.dtype == torch.bfloat16):
+        if a_had is None and (m >= 5 or x.dtype == torch.bfloat16):
             a_had = torch.empty((len(self.linears), m, a.in_features), dtype=torch.float16, device=x.device)
         return exl3.mgemm(x, self.B, self.out, self.suh, a_had, self.svh, a.K, a.mcg, a.mul1)
 
@@ -158,10 +158,10 @@ class Sliced:
         self.carrier = torch.empty((len(t), m, width), dtype=torch.float16, device=dev)
 
     def run(self, x, a_had=None):
-        """a_had: (linears, m, k) fp16 scratch, needed above 16 rows (allocated here if missing)"""
+        """a_had: (linears, m, k) fp16 scratch, used from five rows up (allocated here if missing)"""
         a = self.linears[0]
         m = x.shape[1]
-        if a_had is None and (m > 16 or x.dtype == torch.bfloat16):
+        if a_had is None and (m >= 5 or x.dtype == torch.bfloat16):
             a_had = torch.empty((len(self.linears), m, a.in_features), dtype=torch.float16, device=x.device)
         exl3.mgemm(x, self.B, self.carrier, self.suh, a_had, self.svh, a.K, a.mcg, a.mul1, self.opts)
         return self.outs

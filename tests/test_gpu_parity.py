@@ -257,6 +257,47 @@ def test_mgemm_bundles_above_16_rows(amp, oracle, m, bf16):
     assert gemm_status() == 0
 
 
+@pytest.mark.parametrize("m,K,cb", [(5, 4, 0), (8, 5, 0), (8, 3, 2), (13, 4, 1), (16, 6, 0)])
+def test_rows_5_to_16_with_and_without_the_rotation_scratch(amp, oracle, m, K, cb):
+    """From five rows on, exl3_gemm with A_had rotates the input once in a launch of its own; without
+    A_had every CTA rotates its rows. Same arithmetic: the results must agree bit for bit, for a
+    single matrix and for a sliced bundle, and match the oracle."""
+    from ampstein_b200 import _lib
+    from ampstein_b200.models import LinearEXL3, Sliced
+    k, n = 1536, 1024
+    trellis, suh, svh, x = make_linear(k, n, K, seed=6100 + m + K, m=m)
+    t, su, sv, xx = dev(trellis), dev(suh), dev(svh), dev(x)
+    st = torch.cuda.current_stream().cuda_stream
+    outs = []
+    for scratch in (None, torch.empty((m, k), dtype=torch.float16, device="cuda")):
+        y = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+        _lib.call("amp_exl3_gemm", xx.data_ptr(), t.data_ptr(), y.data_ptr(), su.data_ptr(),
+                  scratch.data_ptr() if scratch is not None else None, sv.data_ptr(), m, k, n, K, cb, 0, st)
+        outs.append(y)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
+    check_close(outs[1].cpu().numpy(), oracle.linear(x, trellis, suh, svh, cb, fp32_out=True))
+
+    widths = (512, 256, 256)
+    parts = []
+    for i, w in enumerate(widths):
+        tr, s_u, s_v, _ = make_linear(k, w, K, seed=6200 + i + m)
+        parts.append(((tr, s_u, s_v), LinearEXL3(dev(tr), dev(s_u), dev(s_v), mul1=(cb == 2), mcg=(cb == 1))))
+    xd = xx.reshape(1, m, k)
+    res = []
+    for scratch in (False, True):
+        o = [torch.full((1, m, w), float("nan"), dtype=torch.float16, device="cuda") for w in widths]
+        sl = Sliced([p[1] for p in parts], o)
+        a = sl.linears[0]
+        amp.mgemm(xd, sl.B, sl.carrier, sl.suh, torch.empty((3, m, k), dtype=torch.float16, device="cuda") if scratch else None,
+                  sl.svh, a.K, a.mcg, a.mul1, sl.opts)
+        res.append(o)
+    torch.cuda.synchronize()
+    for o0, o1, ((tr, s_u, s_v), _) in zip(res[0], res[1], parts):
+        assert torch.equal(o0, o1)
+        check_close(o1[0].cpu().numpy(), oracle.linear(x, tr, s_u, s_v, cb, fp32_out=True))
+
+
 def test_gemm_more_than_16_rows(amp, oracle):
     trellis, suh, svh, x = make_linear(256, 256, 3, seed=6000, m=37)
     ref = oracle.linear(x, trellis, suh, svh, 1, fp32_out=True)
