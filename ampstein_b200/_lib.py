@@ -33,6 +33,7 @@ SIGNATURES = {
     "amp_exl3_set_gemv_tc": [_i],
     "amp_diag_issue_cycles": [_i, _i, ctypes.POINTER(ctypes.c_float)],
     "amp_exl3_set_gemm_pair": [_i],
+    "amp_exl3_set_int8_gemv": [_i, _i],
     "amp_exl3_set_gemm_relay_release": [_i],
     "amp_comm_allreduce_fp16": [_vp, _vp, _vp, _vp, _i, _i, _l, _l, _i, _i, _vp],
     "amp_comm_buffer_bytes": [_i, _l],

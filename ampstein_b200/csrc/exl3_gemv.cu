@@ -5,6 +5,7 @@
 #include "exl3_gemv_tc.cuh"
 #include "host_common.h"
 #include "exl3_gemv_host.h"
+#include <cstdlib>
 #include <mutex>
 
 namespace amp {
@@ -156,6 +157,18 @@ void gemv_prerotate_kernel(const __half* __restrict__ x, __half* __restrict__ ou
 
 constexpr int GEMV_PREROTATE_MIN_M = 5;
 
+// Int8-activation form of the one-row GEMV for mul1 (codebook 2) tensors, as the reference's
+// EXL3_INT8_GEMV switch (vendor/exl3/exllamav3_ext/quant/exl3_gemv_int8.cu:20-52): 0 = off, 2 = plain
+// int8 (the reference's default). Its mode 1 (int8 + residual pass) is not implemented: the fp16
+// kernel, which is more precise than either, runs instead. The environment variables are read once.
+static int int8_env(const char* name, int fallback)
+{
+    const char* e = getenv(name);
+    return e ? atoi(e) : fallback;
+}
+int g_int8_gemv = int8_env("EXL3_INT8_GEMV", 2);
+int g_int8_max_k = int8_env("EXL3_INT8_GEMV_MAX_K", 6);
+
 int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
 {
     const int m = A.m, k = A.k, K = A.K;
@@ -191,7 +204,9 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     const bool tc = !A.mode && m <= TCV_MAX_M && g_gemv_tc && !A.arin.N && !A.ar.push_only;
     // five rows or more with a scratch for the rotated input: rotate once, in a launch of its own
     const bool prerot = !tc && !A.mode && !A.arin.N && m >= GEMV_PREROTATE_MIN_M && A.x_rot && A.x;
-    gemv_fn fn = tc ? gemv_tc_kernel_for(K, A.cb, A.ar.N != 0) : gemv_kernel_for(K, A.cb, MB, A.mode, A.arin.N ? 1 : (prerot ? 2 : 0));
+    const bool i8 = !tc && !A.mode && !A.arin.N && A.cb == 2 && m == 1 && g_int8_gemv == 2 && K <= g_int8_max_k;
+    gemv_fn fn = tc ? gemv_tc_kernel_for(K, A.cb, A.ar.N != 0)
+                    : gemv_kernel_for(K, i8 ? 3 : A.cb, MB, A.mode, A.arin.N ? 1 : (prerot ? 2 : 0));
     if (!fn) return fail(AMP_E_UNSUPPORTED, "exl3_gemv: no kernel for K=%d cb=%d", K, A.cb);
 
     // x~ rows resident at a time: at most 16 KB of shared memory (whole segments for small
@@ -396,6 +411,17 @@ AMP_API int amp_exl3_gemv(const void* x, const void* trellis, void* c, const voi
                           int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream)
 {
     return launch_gemv(direct(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, 0, 0), stream);
+}
+
+// 0 = the mul1 one-row GEMV runs the fp16 kernel, 2 = int8 activations (the reference's
+// EXL3_INT8_GEMV modes; 1 is accepted and means 0 here). max_k > 0 also sets the highest bit width
+// that takes the int8 form (EXL3_INT8_GEMV_MAX_K). Returns the previous mode.
+AMP_API int amp_exl3_set_int8_gemv(int mode, int max_k)
+{
+    const int old = g_int8_gemv;
+    g_int8_gemv = mode == 2 ? 2 : 0;
+    if (max_k > 0) g_int8_max_k = max_k > 8 ? 8 : max_k;
+    return old;
 }
 
 // tuning / test hook: fixed CTA count (split) and x~ chunk size (xgroups); 0 = choose

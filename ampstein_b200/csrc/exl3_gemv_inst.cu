@@ -40,6 +40,8 @@ gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB, int mode, int gin)
         { exl3_gemv_kernel<AMP_GEMV_K, 1, 1, 1>, exl3_gemv_kernel<AMP_GEMV_K, 1, 1, 2> },
         { exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 1>, exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 2> },
     };
+    // cb 3 = the mul1 codebook with int8 activations: one batch row, plain launches only
+    if (cb == 3) return (MB == 1 && !mode && !gin) ? exl3_gemv_kernel<AMP_GEMV_K, 3, 1> : nullptr;
     if (cb < 0 || cb > 2 || MB < 1 || MB > 2 || mode < 0 || mode > 2) return nullptr;
     if (mode) return (MB == 1 && !gin) ? moe[cb][mode - 1] : nullptr;
     return gin == 2 ? fnr[cb][MB - 1] : (gin ? fng[cb][MB - 1] : fn[cb][MB - 1]);

@@ -238,7 +238,7 @@ __host__ __device__ constexpr int gemv_stages(int K) { return K <= 4 ? 8 : (K <=
 // byte offsets inside dynamic shared memory
 struct GemvSmem
 {
-    int part, xd, gsum, ring, xchg, stage, total;
+    int part, xd, gsum, qs, ring, xchg, stage, total;
 };
 
 // 32-bit words per batch row of the duplicated x~ (+16 keeps fragment loads conflict-free)
@@ -252,7 +252,8 @@ __host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int xgrou
     L.part = 0;                                             // [xrows][128] fp32: the finished block
     L.xd = L.part + xrows * 128 * 4;                        // [xrows][XPITCH] duplicated fp16 pairs
     L.gsum = L.xd + xrows * gemv_xpitch(xgroups) * 4;       // [xrows][xgroups] fp32 (codebook 2: sum of x~ per group)
-    L.ring = L.gsum + xrows * xgroups * 4;
+    L.qs = L.gsum + xrows * xgroups * 4;                    // [xrows][xgroups] fp32 (int8 activations: scale of the group's 128-row block)
+    L.ring = L.qs + xrows * xgroups * 4;
     L.ring = (L.ring + 127) & ~127;
     L.xchg = L.ring + GEMV_WARPS * gemv_stages(K) * gemv_slot_bytes(K);   // [cluster][xrows][128] fp32, filled by the cluster's CTAs
     L.stage = L.xchg + cluster * xrows * 128 * 4;
@@ -335,7 +336,7 @@ __device__ __forceinline__ uint32_t hi16_fma(uint32_t r)
 // When K divides 16, windows 16/K positions apart are exactly 16 bits apart, so one 32-bit
 // word cut from the stream holds two states (high and low half): one funnel shift serves two
 // weights. Other bitrates cut each window on its own (shift on the ALU, mask on the FMA pipe).
-template <int K, int R>
+template <int K, int R, bool FMA = true>
 __device__ __forceinline__ void states8(const uint32_t (&w)[K], uint32_t prev, uint32_t (&s)[8])
 {
     if constexpr (K == 4 || K == 8)
@@ -352,17 +353,17 @@ __device__ __forceinline__ void states8(const uint32_t (&w)[K], uint32_t prev, u
             uint32_t r;
             if (sh == 0) r = w[j1];
             else r = __funnelshift_r(w[j1], j1 == 0 ? prev : w[j1 > 0 ? j1 - 1 : 0], sh);
-            s[j] = ((AMP_GEMV_HI_FMA_MASK >> pair) & 1) ? hi16_fma(r) : (r >> 16);
-            s[j + D] = ((AMP_GEMV_LO_FMA_MASK >> pair) & 1) ? lo16_fma(r) : (r & 0xffffu);
+            s[j] = (FMA && ((AMP_GEMV_HI_FMA_MASK >> pair) & 1)) ? hi16_fma(r) : (r >> 16);
+            s[j + D] = (FMA && ((AMP_GEMV_LO_FMA_MASK >> pair) & 1)) ? lo16_fma(r) : (r & 0xffffu);
             ++pair;
         }
     }
     else
     {
-        s[0] = window_ct<K, R * 8 + 0, K>(w, prev); s[1] = window_ct<K, R * 8 + 1, K>(w, prev);
-        s[2] = window_ct<K, R * 8 + 2, K>(w, prev); s[3] = window_ct<K, R * 8 + 3, K>(w, prev);
-        s[4] = window_ct<K, R * 8 + 4, K>(w, prev); s[5] = window_ct<K, R * 8 + 5, K>(w, prev);
-        s[6] = window_ct<K, R * 8 + 6, K>(w, prev); s[7] = window_ct<K, R * 8 + 7, K>(w, prev);
+        s[0] = window_ct<K, R * 8 + 0, K, FMA>(w, prev); s[1] = window_ct<K, R * 8 + 1, K, FMA>(w, prev);
+        s[2] = window_ct<K, R * 8 + 2, K, FMA>(w, prev); s[3] = window_ct<K, R * 8 + 3, K, FMA>(w, prev);
+        s[4] = window_ct<K, R * 8 + 4, K, FMA>(w, prev); s[5] = window_ct<K, R * 8 + 5, K, FMA>(w, prev);
+        s[6] = window_ct<K, R * 8 + 6, K, FMA>(w, prev); s[7] = window_ct<K, R * 8 + 7, K, FMA>(w, prev);
     }
 }
 
@@ -386,6 +387,35 @@ __device__ __forceinline__ void decode_mma_r(const uint32_t (&w)[K], uint32_t pr
         mma_16816(acc0[mb], a[0], a[4], a[1], a[5], xb[mb][2 * R], xb[mb][2 * R + 1]);
         mma_16816(acc1[mb], a[2], a[6], a[3], a[7], xb[mb][2 * R + 8], xb[mb][2 * R + 9]);
     }
+}
+
+// u8 x s8 dot product with int32 accumulation
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Int8-activation form for the mul1 codebook (reference: exl3_gemv_int8_kernel.cuh:19-47): the
+// weight is affine in the byte sum of s * M, so dp4a of the product against the activation's int8
+// code replicated into four bytes is bytesum * code, accumulated exactly. xs[r] = the replicated
+// code of tile row r; a0 / a1: columns gq and gq + 8 of the tile (two chains each). The multiply
+// and the dp4a both run on the FMA-heavy pipe, so the field extraction stays on the ALU.
+template <int K, int R>
+__device__ __forceinline__ void decode_dp4a_r(const uint32_t (&w)[K], uint32_t prev, const uint32_t (&xs)[16],
+                                              int (&a0)[2], int (&a1)[2])
+{
+    uint32_t s[8];
+    states8<K, R, false>(w, prev, s);
+    a0[0] = dp4a_us(s[0] * 0x83DCD12Du, xs[2 * R], a0[0]);
+    a0[1] = dp4a_us(s[2] * 0x83DCD12Du, xs[2 * R + 8], a0[1]);
+    a1[0] = dp4a_us(s[4] * 0x83DCD12Du, xs[2 * R], a1[0]);
+    a1[1] = dp4a_us(s[6] * 0x83DCD12Du, xs[2 * R + 8], a1[1]);
+    a0[0] = dp4a_us(s[1] * 0x83DCD12Du, xs[2 * R + 1], a0[0]);
+    a0[1] = dp4a_us(s[3] * 0x83DCD12Du, xs[2 * R + 9], a0[1]);
+    a1[0] = dp4a_us(s[5] * 0x83DCD12Du, xs[2 * R + 1], a1[0]);
+    a1[1] = dp4a_us(s[7] * 0x83DCD12Du, xs[2 * R + 9], a1[1]);
 }
 
 // thread-block cluster helpers: rank of this CTA, address of a shared-memory location in another
@@ -542,6 +572,7 @@ void exl3_gemv_kernel(const GemvParams P)
     float* part = reinterpret_cast<float*>(smem + L.part);
     uint32_t* xd = reinterpret_cast<uint32_t*>(smem + L.xd);
     float* gsum = reinterpret_cast<float*>(smem + L.gsum);
+    float* qs = reinterpret_cast<float*>(smem + L.qs);
     __shared__ int s_last;
 
     constexpr int S = gemv_stages(K);
@@ -798,6 +829,35 @@ void exl3_gemv_kernel(const GemvParams P)
             // store one task's four rotated values per lane; b, jb name the task
             auto frag_store = [&](int b, int jb, const __half2 o01, const __half2 o23)
             {
+                if constexpr (CB == 3)
+                {
+                    // int8 activations: one scale per 128-row block (this warp's task), codes
+                    // replicated into the four bytes of the word the fp16 pair would occupy
+                    const float v0 = __low2float(o01), v1 = __high2float(o01), v2 = __low2float(o23), v3 = __high2float(o23);
+                    float mx = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+                    #pragma unroll
+                    for (int i = 16; i > 0; i >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, i));
+                    const float inv = mx > 0.0f ? __fdiv_rn(127.0f, mx) : 0.0f;
+                    const int i0 = __float2int_rn(v0 * inv), i1 = __float2int_rn(v1 * inv);
+                    const int i2 = __float2int_rn(v2 * inv), i3 = __float2int_rn(v3 * inv);
+                    uint4 d;
+                    d.x = (uint32_t) (i0 & 0xff) * 0x01010101u; d.y = (uint32_t) (i1 & 0xff) * 0x01010101u;
+                    d.z = (uint32_t) (i2 & 0xff) * 0x01010101u; d.w = (uint32_t) (i3 & 0xff) * 0x01010101u;
+                    const int r = jb * 128 + lane * 4;
+                    const int word = (r >> 6) * 64 + ((r & 15) >> 2) * 16 + ((r & 63) >> 4) * 4;
+                    *reinterpret_cast<uint4*>(xd + b * XPITCH + word) = d;
+                    // per 64-row group (lanes 0-15 / 16-31): the dequantised sum of the codes and the scale
+                    int si = (i0 + i1) + (i2 + i3);
+                    #pragma unroll
+                    for (int i = 1; i < 16; i <<= 1) si += __shfl_xor_sync(0xffffffffu, si, i);
+                    if ((lane & 15) == 0)
+                    {
+                        const float q = __fdiv_rn(mx, 127.0f);
+                        gsum[b * XG + 2 * jb + (lane >> 4)] = q * (float) si;
+                        qs[b * XG + 2 * jb + (lane >> 4)] = q;
+                    }
+                    return;
+                }
                 const uint32_t u01 = *reinterpret_cast<const uint32_t*>(&o01);
                 const uint32_t u23 = *reinterpret_cast<const uint32_t*>(&o23);
                 uint4 d;
@@ -1000,7 +1060,7 @@ void exl3_gemv_kernel(const GemvParams P)
             __syncthreads();
 
             const int c0 = max(cg0, g0);                // first group of the chunk that belongs to the range
-            if constexpr (CB == 2)
+            if constexpr (CB == 2 || CB == 3)
             {
                 #pragma unroll
                 for (int mb = 0; mb < MB; ++mb)
@@ -1039,13 +1099,33 @@ void exl3_gemv_kernel(const GemvParams P)
                     load_chunk_s<K>(w_off + cslot + nt * TILE_BYTES, w[nt]);
                     prev[nt] = lds32(p_off + cslot + nt * TILE_BYTES);
                 }
-                #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
+                if constexpr (CB == 3)
                 {
-                    decode_mma_r<K, CB, MB, 0>(w[nt], prev[nt], xb, acc0[nt], acc1[nt]);
-                    decode_mma_r<K, CB, MB, 1>(w[nt], prev[nt], xb, acc0[nt], acc1[nt]);
-                    decode_mma_r<K, CB, MB, 2>(w[nt], prev[nt], xb, acc0[nt], acc1[nt]);
-                    decode_mma_r<K, CB, MB, 3>(w[nt], prev[nt], xb, acc0[nt], acc1[nt]);
+                    // int8 activations (one batch row): exact integer sums over the unit, scaled by
+                    // the unit's block scale into the fp32 sums of the segment
+                    const float q = qs[(c0 - cg0) + (cg1 - c0 - n)];
+                    #pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                    {
+                        int a0[2] = { 0, 0 }, a1[2] = { 0, 0 };
+                        decode_dp4a_r<K, 0>(w[nt], prev[nt], xb[0], a0, a1);
+                        decode_dp4a_r<K, 1>(w[nt], prev[nt], xb[0], a0, a1);
+                        decode_dp4a_r<K, 2>(w[nt], prev[nt], xb[0], a0, a1);
+                        decode_dp4a_r<K, 3>(w[nt], prev[nt], xb[0], a0, a1);
+                        acc0[nt][0][0] = fmaf(q, (float) (a0[0] + a0[1]), acc0[nt][0][0]);
+                        acc0[nt][0][2] = fmaf(q, (float) (a1[0] + a1[1]), acc0[nt][0][2]);
+                    }
+                }
+                else
+                {
+                    #pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                    {
+                        decode_mma_r<K, CB, MB, 0>(w[nt], prev[nt], xb, acc0[nt], acc1[nt]);
+                        decode_mma_r<K, CB, MB, 1>(w[nt], prev[nt], xb, acc0[nt], acc1[nt]);
+                        decode_mma_r<K, CB, MB, 2>(w[nt], prev[nt], xb, acc0[nt], acc1[nt]);
+                        decode_mma_r<K, CB, MB, 3>(w[nt], prev[nt], xb, acc0[nt], acc1[nt]);
+                    }
                 }
 
                 cslot += SLOT;
@@ -1081,6 +1161,18 @@ void exl3_gemv_kernel(const GemvParams P)
                 const float kbias = __half2float(__ushort_as_half((unsigned short) 0xc931));
                 d0 = d0 * kinv + xsum[mb][0] * kbias; d1 = d1 * kinv + xsum[mb][1] * kbias;
                 d2 = d2 * kinv + xsum[mb][0] * kbias; d3 = d3 * kinv + xsum[mb][1] * kbias;
+            }
+            if constexpr (CB == 3)
+            {
+                // the four lanes of a column hold the sums of their tile rows: add them up (fixed
+                // order), then sum x*w = k_inv * sum x*bytesum + (1024 k_inv + k_bias) * sum x
+                const float kinv = __half2float(__ushort_as_half((unsigned short) 0x1eee));
+                const float kbias = __half2float(__ushort_as_half((unsigned short) 0xc931));
+                d0 += __shfl_xor_sync(0xffffffffu, d0, 1); d2 += __shfl_xor_sync(0xffffffffu, d2, 1);
+                d0 += __shfl_xor_sync(0xffffffffu, d0, 2); d2 += __shfl_xor_sync(0xffffffffu, d2, 2);
+                const float aff = fmaf(1024.0f, kinv, kbias);
+                d0 = d0 * kinv + xsum[mb][0] * aff; d2 = d2 * kinv + xsum[mb][0] * aff;
+                d1 = d3 = 0.0f;
             }
             const int b0 = mb * 8 + 2 * pq;
             if (clustered)

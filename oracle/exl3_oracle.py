@@ -162,6 +162,21 @@ def linear(x, trellis, suh, svh, cb=0, fp32_out=False, what=None):
     return o32 if fp32_out else o16.view(np.float16)
 
 
+def linear_int8(x, trellis, suh, svh, fp32_out=False):
+    """The mul1 (cb 2) linear with int8-quantised rotated activations, one scale per 128 rows of k
+    (the arithmetic of the int8-activation GEMV). Returns fp16 (m,n), or fp32 when fp32_out."""
+    xx = _h(x)
+    m, k = xx.shape
+    t = _h(trellis)
+    kk, n, K = trellis_dims(t)
+    assert kk == k
+    o16 = np.empty((m, n), np.uint16)
+    o32 = np.empty((m, n), np.float32)
+    rc = lib().exl3o_linear_int8(_p16(xx), _p16(t), _p16(_h(suh)), _p16(_h(svh)), m, k, n, K, _p16(o16), _p32(o32))
+    assert rc == 0, rc
+    return o32 if fp32_out else o16.view(np.float16)
+
+
 def matmul_f32(a, w):
     aa, ww = _h(a), _h(w)
     m, k = aa.shape

@@ -29,3 +29,20 @@ def oracle():
     from oracle import exl3_oracle
     exl3_oracle.lib()
     return exl3_oracle
+
+
+@pytest.fixture(autouse=True)
+def _fp16_mul1_gemv_by_default():
+    """The one-row GEMV of mul1 tensors takes the int8-activation form by default (as the
+    reference). The parity tests compare the fp16 kernels against the fp32-accumulated oracle, so
+    the switch is off unless a test turns it on (the int8 tests do, and compare against the int8
+    restatement)."""
+    try:
+        from ampstein_b200 import _lib
+        L = _lib.lib()
+    except Exception:
+        yield
+        return
+    old = L.amp_exl3_set_int8_gemv(0, 0)
+    yield
+    L.amp_exl3_set_int8_gemv(old, 0)

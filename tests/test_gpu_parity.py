@@ -298,6 +298,44 @@ def test_rows_5_to_16_with_and_without_the_rotation_scratch(amp, oracle, m, K, c
         check_close(o1[0].cpu().numpy(), oracle.linear(x, tr, s_u, s_v, cb, fp32_out=True))
 
 
+@pytest.mark.parametrize("k,n,K", [(256, 128, 4), (1024, 768, 3), (4096, 1024, 4), (1536, 512, 5), (2048, 256, 6), (512, 384, 1),
+                                   (14336, 512, 4)])
+def test_int8_activation_gemv_mul1(amp, oracle, k, n, K):
+    """One row, mul1 codebook, int8 switch on: the kernel quantises the rotated input per 128 rows of
+    k and sums bytesum * code exactly, so it must agree closely with the CPU restatement of that
+    arithmetic (1e-4 of the largest output: fp32 summation order is all that differs) and stay
+    within the reference's figure for this form against the fp32-accumulated linear (relative
+    rms < 1e-2; src/torch/amp_torch.cpp:12974-12981 quotes ~8e-3). Bit widths above the limit, two
+    rows and the switch set to 0 take the fp16 kernel."""
+    from ampstein_b200 import _lib
+    trellis, suh, svh, x = make_linear(k, n, K, seed=9300 + K + n, m=2)
+    t, su, sv = dev(trellis), dev(suh), dev(svh)
+    x1 = x[:1]
+    ref8 = oracle.linear_int8(x1, trellis, suh, svh, fp32_out=True)
+    ref = oracle.linear(x1, trellis, suh, svh, 2, fp32_out=True)
+
+    def run(xx, mode, max_k=6):
+        old = _lib.lib().amp_exl3_set_int8_gemv(mode, max_k)
+        try:
+            y = torch.full((xx.shape[0], n), float("nan"), dtype=torch.float32, device="cuda")
+            amp.exl3_gemm(dev(xx), t, y, su, sv, mul1=True)
+            torch.cuda.synchronize()
+            return y.cpu().numpy()
+        finally:
+            _lib.lib().amp_exl3_set_int8_gemv(old, 6)
+
+    got = run(x1, 2)
+    assert np.all(np.isfinite(got))
+    assert np.max(np.abs(got - ref8)) / np.max(np.abs(ref8)) < 1e-4
+    rms = np.sqrt(np.mean((got.astype(np.float64) - ref) ** 2) / np.mean(ref.astype(np.float64) ** 2))
+    assert 1e-4 < rms < 1e-2, rms                                  # really the int8 form, and within its figure
+    fp = run(x1, 0)
+    check_close(fp, ref)                                           # switch off: the fp16 kernel
+    assert np.array_equal(run(x1, 2, max_k=K - 1), fp) if K > 1 else True    # above the bit-width limit
+    both = run(x, 2)                                               # two rows: fp16 kernel
+    check_close(both, oracle.linear(x, trellis, suh, svh, 2, fp32_out=True))
+
+
 def test_gemm_more_than_16_rows(amp, oracle):
     trellis, suh, svh, x = make_linear(256, 256, 3, seed=6000, m=37)
     ref = oracle.linear(x, trellis, suh, svh, 1, fp32_out=True)

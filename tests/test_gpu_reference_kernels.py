@@ -53,6 +53,36 @@ def test_gemm_dispatch_agrees(amp, oracle, k, n, K, m):
     assert e_ref < 1e-2 and e_mine < 1e-2 and e_pair < 1e-2, (shape_idx, e_ref, e_mine, e_pair)
 
 
+@pytest.mark.parametrize("k,n,K", [(4096, 4096, 4), (4096, 1024, 3), (14336, 4096, 4), (2048, 1024, 6)])
+def test_int8_gemv_next_to_the_reference_int8_kernel(amp, oracle, k, n, K):
+    """mul1 codebook, one row: the reference's dispatcher takes its int8-activation GEMV by default
+    (exl3_gemm.cu:188-196); so does this library. Both quantise the activations (with different
+    scale granularity), so they are compared through the fp32-accumulated oracle: each within
+    relative rms 1e-2 of it, and of each other."""
+    from ampstein_b200 import _lib
+    trellis, suh, svh, x = make_linear(k, n, K, seed=3 * k + n + K, m=1)
+    svh = (svh.astype(np.float32) / np.sqrt(k)).astype(np.float16)
+    t, su, sv, xx = dev(trellis), dev(suh), dev(svh), dev(x)
+    ref_out = torch.full((1, n), float("nan"), dtype=torch.float16, device="cuda")
+    a_had = torch.empty_like(xx)
+    ref_kernels.gemm(xx, t, ref_out, su, sv, a_had, cb=2)
+    mine = torch.full((1, n), float("nan"), dtype=torch.float16, device="cuda")
+    old = _lib.lib().amp_exl3_set_int8_gemv(2, 6)
+    try:
+        amp.exl3_gemm(xx, t, mine, su, sv, mul1=True)
+        torch.cuda.synchronize()
+    finally:
+        _lib.lib().amp_exl3_set_int8_gemv(old, 6)
+    cpu = oracle.linear(x, trellis, suh, svh, 2, fp32_out=True).astype(np.float64)
+
+    def rms(a, b):
+        return np.sqrt(np.mean((a.astype(np.float64) - b) ** 2) / np.mean(b ** 2))
+
+    e_ref, e_mine = rms(ref_out.cpu().numpy(), cpu), rms(mine.cpu().numpy(), cpu)
+    e_pair = rms(mine.cpu().numpy(), ref_out.cpu().numpy().astype(np.float64))
+    assert e_ref < 1.2e-2 and e_mine < 1e-2 and e_pair < 1.6e-2, (e_ref, e_mine, e_pair)
+
+
 def moe_case(T, E, Hi, I, Ho, K, topk, seed):
     from test_gpu_moe import make_experts
     ex = make_experts(E, Hi, I, Ho, K, seed=seed)
@@ -174,6 +204,27 @@ def test_timing_table(amp):
                          weight_mb=round(k * n * K / 8e6, 1)))
         del ls
         torch.cuda.empty_cache()
+
+    # mul1 codebook, one row: both libraries take their int8-activation GEMV
+    from ampstein_b200 import _lib as _amp_lib
+    old_i8 = _amp_lib.lib().amp_exl3_set_int8_gemv(2, 6)
+    try:
+        for name, k, n, K in [("o 4096x4096 K4 mul1 (int8 activations)", 4096, 4096, 4), ("down 14336x4096 K4 mul1 (int8 activations)", 14336, 4096, 4),
+                              ("lm_head 4096x128256 K6 mul1 (int8 activations)", 4096, 128256, 6)]:
+            nset = 2 if k * n > 2e8 else max(2, int(3e8 // (k * n * K // 8)))
+            ls = [lin(k, n, K) for _ in range(nset)]
+            x = torch.randn((1, k), device="cuda", generator=g).to(torch.float16)
+            y = torch.empty((1, n), dtype=torch.float16, device="cuda")
+            a_had = torch.empty_like(x)
+            ours = graph_time_us([lambda L=L: amp.exl3_gemm(x, L.trellis, y, L.suh, L.svh, mul1=True) for L in ls])
+            idx = ref_kernels.gemm(x, ls[0].trellis, y, ls[0].suh, ls[0].svh, a_had, cb=2)
+            ref = graph_time_us([lambda L=L: ref_kernels.gemm(x, L.trellis, y, L.suh, L.svh, a_had, cb=2) for L in ls])
+            rows.append(dict(case=name, ours_us=round(ours, 2), reference_us=round(ref, 2), reference_kernel=idx,
+                             weight_mb=round(k * n * K / 8e6, 1)))
+            del ls
+            torch.cuda.empty_cache()
+    finally:
+        _amp_lib.lib().amp_exl3_set_int8_gemv(old_i8, 6)
 
     # prefill: the layer's four shapes at 2048 fp16 tokens. At this row count the reference does not
     # run its trellis GEMM but reconstructs the original-basis weight (its reconstruct_had kernel)

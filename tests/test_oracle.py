@@ -264,3 +264,20 @@ def test_oracle_matches_reference_fixture(oracle, path):
         assert np.array_equal(got.view(np.uint32), z["out"].view(np.uint32))
     else:
         raise AssertionError("unknown fixture kind " + kind)
+
+
+def test_int8_activation_linear_against_the_fp_linear(oracle):
+    """The int8-activation restatement (mul1 codebook, one scale per 128 rows of k) deviates from the
+    fp32-accumulated linear by the quantisation of the activations only: a few 1e-3 relative rms
+    (the reference quotes ~8e-3 for its per-slice scales), and is exact for an input whose rotated
+    form is exactly representable (all zeros)."""
+    import numpy as np
+    from conftest import make_linear
+    for K in (2, 4, 6):
+        trellis, suh, svh, x = make_linear(512, 256, K, seed=40 + K, m=3)
+        a = oracle.linear(x, trellis, suh, svh, 2, fp32_out=True).astype(np.float64)
+        b = oracle.linear_int8(x, trellis, suh, svh, fp32_out=True).astype(np.float64)
+        rms = np.sqrt(np.mean((a - b) ** 2) / np.mean(a ** 2))
+        assert 1e-4 < rms < 1e-2, rms
+    z = oracle.linear_int8(np.zeros((1, 512), np.float16), trellis, suh, svh, fp32_out=True)
+    assert np.all(z == 0)
