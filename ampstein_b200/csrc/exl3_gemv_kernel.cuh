@@ -1227,26 +1227,26 @@ void exl3_gemv_kernel(const GemvParams P)
             if (finish)
             {
                 // only the first contributor can have started before this block (its second slot).
-                // Four values per thread and up to eight contributors' loads in flight at a time
-                // (one after the other they are a chain of L2 round trips on the critical path of
-                // the launch); the adds stay in ascending k order: deterministic.
+                // Four contributors' loads are in flight at a time (one after the other they are a
+                // chain of L2 round trips on the critical path of the launch; wider forms cost the
+                // main loop registers); the adds stay in ascending k order: deterministic.
                 const int first_slot = 2 * i_first + (blk * G > split.begin(i_first) ? 1 : 0);
                 const size_t pitch = (size_t) 2 * m * 128;               // floats between consecutive contributors' slots
-                for (int idx = 4 * t; idx < nrows * 128; idx += 4 * GEMV_THREADS)
+                for (int idx = t; idx < nrows * 128; idx += GEMV_THREADS)
                 {
-                    float4 sum = __ldcg(reinterpret_cast<const float4*>(slots + (size_t) first_slot * m * 128 + idx));
+                    float sum = __ldcg(slots + (size_t) first_slot * m * 128 + idx);
                     const float* src = slots + (size_t) (i_first + 1) * pitch + idx;
-                    for (int i = i_first + 1; i <= i_last; i += 8, src += 8 * pitch)
+                    for (int i = i_first + 1; i <= i_last; i += 4, src += 4 * pitch)
                     {
-                        float4 v[8];
+                        float v[4];
                         #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            if (i + j <= i_last) v[j] = __ldcg(reinterpret_cast<const float4*>(src + j * pitch));
+                        for (int j = 0; j < 4; ++j)
+                            if (i + j <= i_last) v[j] = __ldcg(src + j * pitch);
                         #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            if (i + j <= i_last) { sum.x += v[j].x; sum.y += v[j].y; sum.z += v[j].z; sum.w += v[j].w; }
+                        for (int j = 0; j < 4; ++j)
+                            if (i + j <= i_last) sum += v[j];
                     }
-                    *reinterpret_cast<float4*>(part + idx) = sum;
+                    part[idx] = sum;
                 }
             }
         }

@@ -334,6 +334,23 @@ def test_int8_activation_gemv_mul1(amp, oracle, k, n, K):
     assert np.array_equal(run(x1, 2, max_k=K - 1), fp) if K > 1 else True    # above the bit-width limit
     both = run(x, 2)                                               # two rows: fp16 kernel
     check_close(both, oracle.linear(x, trellis, suh, svh, 2, fp32_out=True))
+    if k == 1024:
+        # a sliced bundle of mul1 linears at one row takes the int8 form too
+        from ampstein_b200.models import LinearEXL3, Sliced
+        parts = []
+        for i, w in enumerate((512, 256, 256)):
+            tr, s_u, s_v, _ = make_linear(k, w, K, seed=9400 + i)
+            parts.append(((tr, s_u, s_v), LinearEXL3(dev(tr), dev(s_u), dev(s_v), mul1=True)))
+        outs = [torch.full((1, 1, w), float("nan"), dtype=torch.float16, device="cuda") for w in (512, 256, 256)]
+        old = _lib.lib().amp_exl3_set_int8_gemv(2, 6)
+        try:
+            Sliced([p[1] for p in parts], outs).run(dev(x1).reshape(1, 1, k))
+            torch.cuda.synchronize()
+        finally:
+            _lib.lib().amp_exl3_set_int8_gemv(old, 6)
+        for o, ((tr, s_u, s_v), _) in zip(outs, parts):
+            r8 = oracle.linear_int8(x1, tr, s_u, s_v, fp32_out=True)
+            assert np.max(np.abs(o[0].float().cpu().numpy() - r8)) / np.max(np.abs(r8)) < 1e-3      # fp16 output rounding
 
 
 def test_gemm_more_than_16_rows(amp, oracle):
