@@ -9,6 +9,7 @@ from .exl3 import (  # noqa: F401
     exl3_gemm,
     exl3_gemm_recon,
     exl3_reconstruct,
+    exl3_reconstruct_batch,
     exl3_reconstruct_had,
     had_r_128,
     mgemm,
@@ -17,4 +18,4 @@ from .exl3 import (  # noqa: F401
     ptr_array,
 )
 
-__all__ = ["exl3_gemm", "exl3_gemm_recon", "exl3_reconstruct", "exl3_reconstruct_had", "had_r_128", "mgemm", "moe_coop", "moe_coop_ctr_len", "ptr_array"]
+__all__ = ["exl3_gemm", "exl3_gemm_recon", "exl3_reconstruct", "exl3_reconstruct_batch", "exl3_reconstruct_had", "had_r_128", "mgemm", "moe_coop", "moe_coop_ctr_len", "ptr_array"]

@@ -32,6 +32,8 @@ SIGNATURES = {
     "amp_exl3_set_pdl": [_i],
     "amp_exl3_set_gemv_tc": [_i],
     "amp_diag_issue_cycles": [_i, _i, ctypes.POINTER(ctypes.c_float)],
+    "amp_exl3_reconstruct_batch": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "amp_exl3_reconstruct_had_batch": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "amp_exl3_set_gemm_pair": [_i],
     "amp_exl3_set_int8_gemv": [_i, _i],
     "amp_exl3_set_gemm_relay_release": [_i],

@@ -81,6 +81,10 @@ struct GemvMoe
     int* done;                  // [bsz][Ho / 128] arrivals, zero between calls
     float* out; int out_stride, H_out;
     const float* sh_out; const __half* sh_gate_w;
+    // mixed bit widths: per-expert widths of gate / up / down (uint8, indexed by local expert), or
+    // null for one width. A launch then works on the runs whose expert has the launch's width.
+    const unsigned char* bits[3];
+    int first_down;             // MODE 2: this launch also writes the row of a single token without any pick
 };
 
 struct MoeSlot { int row, local; float w; bool active; };
@@ -629,12 +633,41 @@ void exl3_gemv_kernel(const GemvParams P)
             inline_active = s_runs[0];
         }
     }
-    const int U = (MODE == 0 ? P.blocks : runs[0] * nproj * nbw) * G;
+    // mixed bit widths: the runs this launch works on (those whose expert has this instance's width)
+    __shared__ unsigned char s_sel[256];
+    __shared__ int s_nsel;
+    bool filtered = false;
+    int nruns = 0;
+    if constexpr (MODE != 0)
+    {
+        nruns = runs[0];
+        const unsigned char* bits = P.moe.bits[MODE == 2 ? 2 : 1];
+        if (bits)
+        {
+            filtered = true;
+            if (t < 32)
+            {
+                int count = 0;
+                for (int base = 0; base < nruns; base += 32)
+                {
+                    const int r = base + t;
+                    const bool hit = r < nruns && bits[runs[2 + r * MOE_RUN_INTS]] == K;
+                    const unsigned m32 = __ballot_sync(0xffffffffu, hit);
+                    if (hit) s_sel[count + __popc(m32 & ((1u << t) - 1u))] = (unsigned char) r;
+                    count += __popc(m32);
+                }
+                if (t == 0) s_nsel = count;
+            }
+            __syncthreads();
+            nruns = s_nsel;
+        }
+    }
+    const int U = (MODE == 0 ? P.blocks : nruns * nproj * nbw) * G;
     const int cta = blockIdx.x, ncta = min((int) gridDim.x, U);    // never more ranges than units
     if constexpr (MODE == 2)
     {
         // a single token without any local pick: nobody will deliver a slot, the row is still due
-        if (P.moe.inline_runs && inline_active == 0 && cta == 0)
+        if (P.moe.inline_runs && inline_active == 0 && cta == 0 && P.moe.first_down)
             for (int c = warp; c < (P.moe.Ho >> 7); c += GEMV_WARPS) moe_combine_chunk(P.moe, 0, c, lane);
     }
     if (cta >= ncta) return;                           // an exited CTA counts as having released its dependents
@@ -680,7 +713,8 @@ void exl3_gemv_kernel(const GemvParams P)
         int stride = P.stride;
         if constexpr (MODE != 0)
         {
-            const int run = slice / nproj, proj = (MODE == 2) ? 2 : (P.moe.gated ? slice - run * nproj : 1);
+            const int srun = slice / nproj, proj = (MODE == 2) ? 2 : (P.moe.gated ? slice - srun * nproj : 1);
+            const int run = filtered ? s_sel[srun] : srun;
             const int expert = runs[2 + run * MOE_RUN_INTS];
             tr = reinterpret_cast<const unsigned char*>(P.moe.trellis[proj][expert]);
             stride = P.width;
@@ -777,7 +811,8 @@ void exl3_gemv_kernel(const GemvParams P)
         const __half* xrot = P.x;                      // GIN == 2: this slice's rotated input
         if constexpr (MODE != 0)
         {
-            const int run = slice / nproj, proj = (MODE == 2) ? 2 : (P.moe.gated ? slice - run * nproj : 1);
+            const int srun = slice / nproj, proj = (MODE == 2) ? 2 : (P.moe.gated ? slice - srun * nproj : 1);
+            const int run = filtered ? s_sel[srun] : srun;
             const int* rec = runs + 2 + run * MOE_RUN_INTS;
             const int expert = rec[0];
             nrows = rec[1];

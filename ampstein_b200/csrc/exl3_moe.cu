@@ -130,7 +130,7 @@ AMP_API int amp_exl3_moe_coop(const amp_moe_coop_args* a, cudaStream_t stream)
     AMP_REQUIRE(a->Hi % 128 == 0 && a->I % 128 == 0 && a->Ho % 128 == 0 && a->H_out <= a->Ho,
                 "exl3_moe_coop: Hi/I/Ho shape");
     AMP_REQUIRE(a->H % 4 == 0 && a->H <= a->Hi, "exl3_moe_coop: H/Hi shape");
-    AMP_REQUIRE(a->Kgu >= 1 && a->Kgu <= 8 && a->Kd >= 1 && a->Kd <= 8, "exl3_moe_coop: K out of range");
+    AMP_REQUIRE((a->g_bits && a->u_bits && a->d_bits) || (a->Kgu >= 1 && a->Kgu <= 8 && a->Kd >= 1 && a->Kd <= 8), "exl3_moe_coop: K out of range");
     AMP_REQUIRE(a->cb >= 0 && a->cb <= 2, "exl3_moe_coop: codebook index out of range");
     AMP_REQUIRE(a->act >= 0 && a->act <= 3, "exl3_moe_coop: unknown activation");
     AMP_REQUIRE(a->u_trellis && a->u_suh && a->u_svh && a->d_trellis && a->d_suh && a->d_svh,
@@ -165,6 +165,17 @@ AMP_API int amp_exl3_moe_coop(const amp_moe_coop_args* a, cudaStream_t stream)
     // the sorting launch is not needed
     L.moe.inline_runs = (a->bsz == 1 && a->topk <= 16) ? 1 : 0;
     L.m = 8; L.cb = a->cb; L.c_fp32 = 1;
+    const bool mixed = a->g_bits || a->u_bits || a->d_bits;
+    if (mixed)
+    {
+        AMP_REQUIRE(a->g_bits && a->u_bits && a->d_bits, "exl3_moe_coop: give all three bit width tables or none");
+        AMP_REQUIRE(a->kmask_gu > 0 && a->kmask_gu < 256 && a->kmask_d > 0 && a->kmask_d < 256,
+                    "exl3_moe_coop: kmask_gu / kmask_d must name the bit widths (1..8) that occur in the tables");
+        L.moe.bits[0] = (const unsigned char*) a->g_bits; L.moe.bits[1] = (const unsigned char*) a->u_bits;
+        L.moe.bits[2] = (const unsigned char*) a->d_bits;
+    }
+    const int mask_gu = mixed ? a->kmask_gu : (1 << (a->Kgu - 1));
+    const int mask_d = mixed ? a->kmask_d : (1 << (a->Kd - 1));
 
     if (!L.moe.inline_runs)
         if (cudaError_t e = launch_small(moe_prep_kernel, 1, stream, L.moe, runs, need, g_pdl))
@@ -172,12 +183,26 @@ AMP_API int amp_exl3_moe_coop(const amp_moe_coop_args* a, cudaStream_t stream)
 
     // gate + up: slices = runs x projections, k = Hi, width = I
     const int nproj = a->gated ? 2 : 1;
-    L.mode = 1; L.k = a->Hi; L.width = a->I; L.stride = a->I; L.K = a->Kgu;
+    // (mixed bit widths: one launch per width that occurs; each works on the runs of its width)
+    L.mode = 1; L.k = a->Hi; L.width = a->I; L.stride = a->I;
     L.slices = slots * nproj; L.max_slices = slots * nproj;          // at most one run per slot
-    if (int rc = launch_gemv(L, stream)) return rc;
+    for (int K = 1; K <= 8; ++K)
+        if (mask_gu & (1 << (K - 1)))
+        {
+            L.K = K;
+            if (int rc = launch_gemv(L, stream)) return rc;
+        }
 
     // down: slices = runs, k = I, width = Ho; its finishing CTAs also do the routing-weighted sum
-    L.mode = 2; L.k = a->I; L.width = a->Ho; L.stride = a->Ho; L.K = a->Kd;
+    L.mode = 2; L.k = a->I; L.width = a->Ho; L.stride = a->Ho;
     L.slices = slots; L.max_slices = slots;
-    return launch_gemv(L, stream);
+    L.moe.first_down = 1;
+    for (int K = 1; K <= 8; ++K)
+        if (mask_d & (1 << (K - 1)))
+        {
+            L.K = K;
+            if (int rc = launch_gemv(L, stream)) return rc;
+            L.moe.first_down = 0;
+        }
+    return 0;
 }

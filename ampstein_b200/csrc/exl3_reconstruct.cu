@@ -20,8 +20,15 @@ namespace amp {
 template <int K, int CB>
 __global__ __launch_bounds__(256)
 void reconstruct_kernel(__half* __restrict__ out, const uint16_t* __restrict__ trellis,
-                        int tiles_n, int tile_n_offset, int n_out)
+                        int tiles_n, int tile_n_offset, int n_out, const long long* __restrict__ t_trellis, size_t mat_elems)
 {
+    // batch form: blockIdx.z = matrix; the trellis comes from a device pointer table and the
+    // outputs are stacked
+    if (t_trellis)
+    {
+        trellis = reinterpret_cast<const uint16_t*>(t_trellis[blockIdx.z]);
+        out += (size_t) blockIdx.z * mat_elems;
+    }
     constexpr int TW = 8 * K;                 // uint32 words per tile
     __shared__ __align__(16) uint32_t s_packed[8 * TW];
     __shared__ __align__(16) __half s_tile[16][128 + 8];
@@ -70,8 +77,16 @@ template <int K, int CB>
 __global__ __launch_bounds__(256)
 void reconstruct_had_kernel(__half* __restrict__ out, const uint16_t* __restrict__ trellis,
                             const __half* __restrict__ suh, const __half* __restrict__ svh,
-                            int tiles_n, int tile_n_offset, int n_out)
+                            int tiles_n, int tile_n_offset, int n_out, const long long* __restrict__ t_trellis,
+                            const long long* __restrict__ t_suh, const long long* __restrict__ t_svh, size_t mat_elems)
 {
+    if (t_trellis)
+    {
+        trellis = reinterpret_cast<const uint16_t*>(t_trellis[blockIdx.z]);
+        suh = reinterpret_cast<const __half*>(t_suh[blockIdx.z]);
+        svh = reinterpret_cast<const __half*>(t_svh[blockIdx.z]);
+        out += (size_t) blockIdx.z * mat_elems;
+    }
     constexpr int TW = 8 * K;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half* st = reinterpret_cast<__half*>(smem_raw);                       // [128][128] swizzled
@@ -161,8 +176,9 @@ void reconstruct_had_kernel(__half* __restrict__ out, const uint16_t* __restrict
     }
 }
 
-typedef void (*recon_fn)(__half*, const uint16_t*, int, int, int);
-typedef void (*recon_had_fn)(__half*, const uint16_t*, const __half*, const __half*, int, int, int);
+typedef void (*recon_fn)(__half*, const uint16_t*, int, int, int, const long long*, size_t);
+typedef void (*recon_had_fn)(__half*, const uint16_t*, const __half*, const __half*, int, int, int,
+                             const long long*, const long long*, const long long*, size_t);
 
 #define AMP_ROW(T, cb) { T<1, cb>, T<2, cb>, T<3, cb>, T<4, cb>, T<5, cb>, T<6, cb>, T<7, cb>, T<8, cb> }
 static const recon_fn k_recon[3][8] = { AMP_ROW(reconstruct_kernel, 0), AMP_ROW(reconstruct_kernel, 1), AMP_ROW(reconstruct_kernel, 2) };
@@ -194,8 +210,24 @@ AMP_API int amp_exl3_reconstruct(void* unpacked, const void* trellis, int k, int
     AMP_REQUIRE(k / 16 <= 65535, "reconstruct: k too large");
     dim3 grid(n_out / 128, k / 16);
     k_recon[cb][K - 1]<<<grid, 256, 0, stream>>>((__half*) unpacked, (const uint16_t*) trellis,
-                                                 n / 16, n_offset / 16, n_out);
+                                                 n / 16, n_offset / 16, n_out, nullptr, 0);
     return cuda_rc(cudaGetLastError(), "amp_exl3_reconstruct");
+}
+
+// `batch` whole matrices of one shape in one launch: unpacked (batch, k, n) fp16 contiguous,
+// packed_ptrs a DEVICE array of int64 trellis addresses (rotated basis, as amp_exl3_reconstruct)
+AMP_API int amp_exl3_reconstruct_batch(void* unpacked, const void* packed_ptrs, int batch, int k, int n, int K, int cb,
+                                       cudaStream_t stream)
+{
+    AMP_REQUIRE(batch >= 0 && batch <= 65535, "reconstruct_batch: batch out of range");
+    if (batch == 0 || k == 0 || n == 0) return 0;
+    AMP_REQUIRE(packed_ptrs, "reconstruct_batch: null pointer table");
+    if (int rc = check_common(unpacked, unpacked, k, n, K, cb, 0, n)) return rc;
+    AMP_REQUIRE(k / 16 <= 65535, "reconstruct: k too large");
+    dim3 grid(n / 128, k / 16, batch);
+    k_recon[cb][K - 1]<<<grid, 256, 0, stream>>>((__half*) unpacked, nullptr, n / 16, 0, n,
+                                                 (const long long*) packed_ptrs, (size_t) k * n);
+    return cuda_rc(cudaGetLastError(), "amp_exl3_reconstruct_batch");
 }
 
 AMP_API int amp_exl3_reconstruct_had(void* unpacked, const void* trellis, const void* suh, const void* svh,
@@ -215,6 +247,28 @@ AMP_API int amp_exl3_reconstruct_had(void* unpacked, const void* trellis, const 
     if (cudaError_t e = ensure_smem(fn, smem, dev)) return cuda_rc(e, "reconstruct_had smem");
     dim3 grid(n_out / 128, k / 128);
     fn<<<grid, 256, smem, stream>>>((__half*) unpacked, (const uint16_t*) trellis, (const __half*) suh,
-                                    (const __half*) svh, n / 16, n_offset / 16, n_out);
+                                    (const __half*) svh, n / 16, n_offset / 16, n_out, nullptr, nullptr, nullptr, 0);
     return cuda_rc(cudaGetLastError(), "amp_exl3_reconstruct_had");
+}
+
+// `batch` whole matrices of one shape into the original basis in one launch; packed_ptrs / suh_ptrs
+// / svh_ptrs are DEVICE arrays of int64 addresses (trellis, k-length suh, n-length svh per matrix)
+AMP_API int amp_exl3_reconstruct_had_batch(void* unpacked, const void* packed_ptrs, const void* suh_ptrs, const void* svh_ptrs,
+                                           int batch, int k, int n, int K, int cb, cudaStream_t stream)
+{
+    AMP_REQUIRE(batch >= 0 && batch <= 65535, "reconstruct_had_batch: batch out of range");
+    if (batch == 0 || k == 0 || n == 0) return 0;
+    AMP_REQUIRE(packed_ptrs && suh_ptrs && svh_ptrs, "reconstruct_had_batch: null pointer table");
+    if (int rc = check_common(unpacked, unpacked, k, n, K, cb, 0, n)) return rc;
+    AMP_REQUIRE(k % 128 == 0, "reconstruct_had_batch: K dimension must be divisible by 128");
+    AMP_REQUIRE(k / 128 <= 65535, "reconstruct_had: k too large");
+    const int smem = 128 * 128 * 2 + 64 * 8 * K * 4;
+    recon_had_fn fn = k_recon_had[cb][K - 1];
+    int dev = 0;
+    if (cudaError_t e = cudaGetDevice(&dev)) return cuda_rc(e, "cudaGetDevice");
+    if (cudaError_t e = ensure_smem(fn, smem, dev)) return cuda_rc(e, "reconstruct_had smem");
+    dim3 grid(n / 128, k / 128, batch);
+    fn<<<grid, 256, smem, stream>>>((__half*) unpacked, nullptr, nullptr, nullptr, n / 16, 0, n,
+                                    (const long long*) packed_ptrs, (const long long*) suh_ptrs, (const long long*) svh_ptrs, (size_t) k * n);
+    return cuda_rc(cudaGetLastError(), "amp_exl3_reconstruct_had_batch");
 }

@@ -14,6 +14,8 @@
 // can drive this layer with torch tensors (compile with -DAMP_NO_PYBIND to leave the module out).
 #ifndef AMP_NO_PYBIND
 #include <torch/extension.h>
+#include <map>
+#include <mutex>
 #else
 #include <ATen/ATen.h>
 #endif
@@ -214,7 +216,6 @@ void exl3_moe_coop(const at::Tensor& x, const at::Tensor& sel, const at::Tensor&
 {
     (void) had_g; (void) had_u; (void) act_out;
     const c10::cuda::CUDAGuard guard(x.device());
-    TORCH_CHECK(!bits_g.has_value() && !bits_u.has_value() && !bits_d.has_value(), "exl3_moe_coop: per-expert bit tables are not supported");
     TORCH_CHECK(x.dim() == 2 && x.scalar_type() == at::kHalf && x.stride(1) == 1, "exl3_moe_coop: x must be float16 (bsz, H)");
     TORCH_CHECK(sel.scalar_type() == at::kLong && rw.scalar_type() == at::kHalf && sel.is_contiguous() && rw.is_contiguous() &&
                 sel.dim() == 2 && sel.sizes() == rw.sizes() && sel.size(0) == x.size(0), "exl3_moe_coop: sel int64 / rw float16 (bsz, topk)");
@@ -246,6 +247,37 @@ void exl3_moe_coop(const at::Tensor& x, const at::Tensor& sel, const at::Tensor&
     TORCH_CHECK(ctr.numel() >= amp_exl3_moe_coop_ctr_len(a.slots_max, a.bsz, a.I, a.Ho), "exl3_moe_coop: ctr too short for the scratch's slot count");
     a.out = out.data_ptr(); a.out_stride = (int) out.stride(-2);
     a.sh_out = opt_ptr(sh_out); a.sh_gate_w = opt_ptr(sh_gate_w);
+    if (bits_g.has_value() || bits_u.has_value() || bits_d.has_value())
+    {
+        // mixed bit widths: the C ABI wants to know which widths occur; the tables are static, so
+        // they are read back once per table (keyed by address) and remembered
+        TORCH_CHECK(bits_g.has_value() && bits_u.has_value() && bits_d.has_value(), "exl3_moe_coop: give all three bit width tables or none");
+        for (const at::Tensor* t : { &bits_g.value(), &bits_u.value(), &bits_d.value() })
+            TORCH_CHECK(t->scalar_type() == at::kByte && t->is_cuda() && t->is_contiguous() && t->numel() >= a.n_local,
+                        "exl3_moe_coop: bit width tables must be contiguous uint8 device tensors with one entry per expert");
+        static std::mutex mu;
+        static std::map<std::pair<const void*, int>, int> masks;
+        auto mask_of = [&](const at::Tensor& t)
+        {
+            std::lock_guard<std::mutex> lock(mu);
+            const auto key = std::make_pair((const void*) t.data_ptr(), a.n_local);
+            auto it = masks.find(key);
+            if (it != masks.end()) return it->second;
+            const at::Tensor h = t.narrow(0, 0, a.n_local).cpu();
+            int m = 0;
+            for (int i = 0; i < a.n_local; ++i)
+            {
+                const int K = h.data_ptr<uint8_t>()[i];
+                TORCH_CHECK(K >= 1 && K <= 8, "exl3_moe_coop: bit widths must be 1..8");
+                m |= 1 << (K - 1);
+            }
+            masks[key] = m;
+            return m;
+        };
+        a.g_bits = bits_g->data_ptr(); a.u_bits = bits_u->data_ptr(); a.d_bits = bits_d->data_ptr();
+        a.kmask_gu = mask_of(*bits_u); a.kmask_d = mask_of(*bits_d);
+        if (gated) TORCH_CHECK(mask_of(*bits_g) == a.kmask_gu, "exl3_moe_coop: gate and up of an expert must share a bit width");
+    }
     check_rc(amp_exl3_moe_coop(&a, stream_of(x)), "exl3_moe_coop");
 }
 

@@ -79,6 +79,34 @@ def exl3_reconstruct_had(unpacked, packed, suh, svh, K, mul1=False, mcg=False, n
     return unpacked
 
 
+def exl3_reconstruct_batch(unpacked, packed_ptrs, K, mul1=False, mcg=False, suh_ptrs=None, svh_ptrs=None):
+    """Dequantize B matrices of one shape in one launch into unpacked (B, k, n) fp16; packed_ptrs is
+    an int64 CUDA tensor of trellis addresses. With suh_ptrs / svh_ptrs the original-basis form
+    (reference: reconstruct_batch / reconstruct_had_batch,
+    vendor/exl3/exllamav3_ext/quant/reconstruct.cu:512-626)."""
+    _check_cuda("exl3_reconstruct_batch", unpacked, packed_ptrs)
+    if unpacked.dtype != torch.float16 or unpacked.dim() != 3:
+        raise TypeError("exl3_reconstruct_batch: unpacked must be 3-D float16")
+    if float(K) != int(K) or not (1 <= int(K) <= 8):
+        raise ValueError("exl3_reconstruct_batch: unsupported EXL3 bitrate %s" % K)
+    tables = [packed_ptrs] + [t for t in (suh_ptrs, svh_ptrs) if t is not None]
+    if (suh_ptrs is None) != (svh_ptrs is None):
+        raise TypeError("exl3_reconstruct_batch: suh_ptrs and svh_ptrs go together")
+    B, k, n = unpacked.shape
+    for t in tables:
+        _check_cuda("exl3_reconstruct_batch", t)
+        if t.dtype != torch.int64 or t.numel() < B:
+            raise ValueError("exl3_reconstruct_batch: pointer tables must be int64 with one entry per matrix")
+    with torch.cuda.device(unpacked.device):
+        if suh_ptrs is None:
+            _lib.call("amp_exl3_reconstruct_batch", unpacked.data_ptr(), packed_ptrs.data_ptr(), B, k, n, int(K),
+                      _cb(mul1, mcg), _stream(unpacked))
+        else:
+            _lib.call("amp_exl3_reconstruct_had_batch", unpacked.data_ptr(), packed_ptrs.data_ptr(), suh_ptrs.data_ptr(),
+                      svh_ptrs.data_ptr(), B, k, n, int(K), _cb(mul1, mcg), _stream(unpacked))
+    return unpacked
+
+
 def had_r_128(input, output, pre_scale=None, post_scale=None, scale=1.0):
     """output = blockwise H128(input [* pre_scale]) * scale / sqrt(128) [* post_scale]; fp16 or
     fp32, may run in place; an fp32 input with an fp16 output runs the transform in fp32 and
@@ -241,6 +269,8 @@ class _MoeArgs(__import__("ctypes").Structure):
         ("ctr", _c.c_void_p), ("ctr_len", _c.c_long), ("slots_max", _c.c_int),
         ("out", _c.c_void_p), ("out_stride", _c.c_int),
         ("sh_out", _c.c_void_p), ("sh_gate_w", _c.c_void_p),
+        ("g_bits", _c.c_void_p), ("u_bits", _c.c_void_p), ("d_bits", _c.c_void_p),
+        ("kmask_gu", _c.c_int), ("kmask_d", _c.c_int),
     ]
 
 
@@ -260,7 +290,8 @@ def moe_coop(x, sel, rw, cfg, sh_out=None):
     parts under the reference's keys: int64 pointer tables g_trellis g_suh g_svh u_* d_*, scratch
     gu_g gu_u d_out ctr out, numbers Hi Kg Ku Kd act act_limit min_expert max_expert, booleans
     mcg mul1 (had_g, had_u, act_out are accepted and unused; optional g_bias u_bias d_bias tables,
-    sh_gate_w, gated)."""
+    sh_gate_w, gated; optional uint8 tables g_bits u_bits d_bits for experts of different bit
+    widths, in which case Kg Ku Kd are not used)."""
     import ctypes
     if not isinstance(cfg, dict):
         raise TypeError("moe_coop: cfg must be an object")
@@ -319,6 +350,26 @@ def moe_coop(x, sel, rw, cfg, sh_out=None):
     a.out, a.out_stride = p(out), out.stride(-2)
     a.sh_out = p(sh_out)
     a.sh_gate_w = p(cfg.get("sh_gate_w"))
+    if any(cfg.get(n) is not None for n in ("g_bits", "u_bits", "d_bits")):
+        # mixed bit widths: uint8 tables, one entry per expert. The widths that occur are read once
+        # (the tables are static) and kept in the cfg object.
+        for n in ("g_bits", "u_bits", "d_bits"):
+            t = cfg.get(n)
+            if not isinstance(t, torch.Tensor) or t.dtype != torch.uint8 or not t.is_cuda or not t.is_contiguous() \
+                    or t.numel() < a.n_local:
+                raise TypeError("exl3_moe_coop: give all three bit width tables (contiguous uint8 CUDA, one entry per expert) or none")
+        if "_kmask" not in cfg:
+            if gated and not torch.equal(cfg["g_bits"][:a.n_local], cfg["u_bits"][:a.n_local]):
+                raise ValueError("exl3_moe_coop: gate and up of an expert must share a bit width")
+            masks = []
+            for n in ("u_bits", "d_bits"):
+                ks = torch.unique(cfg[n][:a.n_local]).tolist()
+                if not ks or min(ks) < 1 or max(ks) > 8:
+                    raise ValueError("exl3_moe_coop: bit widths must be 1..8")
+                masks.append(sum(1 << (int(k) - 1) for k in ks))
+            cfg["_kmask"] = tuple(masks)
+        a.g_bits, a.u_bits, a.d_bits = p(cfg["g_bits"]), p(cfg["u_bits"]), p(cfg["d_bits"])
+        a.kmask_gu, a.kmask_d = cfg["_kmask"]
     with torch.cuda.device(x.device):
         _lib.call("amp_exl3_moe_coop", ctypes.byref(a), _stream(x))
     return None

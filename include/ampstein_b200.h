@@ -57,6 +57,18 @@ int amp_exl3_reconstruct_had(void* unpacked, const void* trellis, const void* su
                              cudaStream_t stream);
 
 /*
+ * Batch forms: `batch` whole matrices of one shape in one launch. unpacked (batch, k, n) fp16
+ * contiguous; packed_ptrs (and suh_ptrs / svh_ptrs) are DEVICE arrays of int64 addresses, one per
+ * matrix. n a multiple of 128; k a multiple of 16 (rotated basis) or 128 (original basis).
+ * Replaces: reconstruct_batch / reconstruct_had_batch, Q/reconstruct.cu:512-626 (kernels :102-139,
+ * :381-429).
+ */
+int amp_exl3_reconstruct_batch(void* unpacked, const void* packed_ptrs, int batch, int k, int n, int K, int cb,
+                               cudaStream_t stream);
+int amp_exl3_reconstruct_had_batch(void* unpacked, const void* packed_ptrs, const void* suh_ptrs, const void* svh_ptrs,
+                                   int batch, int k, int n, int K, int cb, cudaStream_t stream);
+
+/*
  * Blockwise 128-point Hadamard of a (rows, cols) matrix, out = H(in [* pre]) * scale/sqrt(128)
  * [* post]; in place allowed. dtype 0 = fp16, 1 = fp32, 2 = bf16 in / fp16 out, 3 = fp32 in / fp16
  * out (2 and 3 not in place; 3 is the form the reference applies to fp32 accumulators,
@@ -234,6 +246,13 @@ typedef struct amp_moe_coop_args
     int out_stride;
     const void* sh_out;         /* nullable: (bsz, H) fp32 shared-expert output */
     const void* sh_gate_w;      /* nullable: (H) fp16, gate = sigmoid(x . w) */
+    /* mixed bit widths (nullable, all three or none): uint8 device tables indexed by local expert;
+     * gate and up of an expert share one width (g_bits[e] == u_bits[e]). kmask_gu / kmask_d: bit K-1
+     * set for every width K that occurs in u_bits / d_bits (host values: the tables are static, the
+     * caller reads them once); Kgu / Kd are ignored then. One pair of launches per width.
+     * Reference: g_bits / u_bits / d_bits of MoeCoopParams, Q/exl3_moe_coop.cuh:46-50. */
+    const void* g_bits; const void* u_bits; const void* d_bits;
+    int kmask_gu, kmask_d;
 } amp_moe_coop_args;
 
 int amp_exl3_moe_coop(const amp_moe_coop_args* args, cudaStream_t stream);

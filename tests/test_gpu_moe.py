@@ -161,6 +161,38 @@ def test_moe_config4_shapes_one_token(amp, oracle):
     check(cfg["out"][:1].cpu().numpy(), oracle.moe_coop(x, sel, rw, ex))
 
 
+@pytest.mark.parametrize("T", [1, 5])
+def test_moe_experts_of_different_bit_widths(amp, oracle, T):
+    """Mixed packs (the reference's g_bits / u_bits / d_bits tables, exl3_moe_coop.cuh:46-50): every
+    expert's gate|up and down have their own bit width; one pair of launches per width that occurs,
+    each working on the runs of its width. One token (tables built in the kernel, cluster form) and
+    several; a token whose picks all fall on one width; the second call reuses the cached masks."""
+    E, Hi, I, Ho, topk = 8, 256, 256, 256, 3
+    kgu = [3, 4, 4, 3, 5, 4, 3, 5]
+    kd = [4, 4, 2, 2, 4, 6, 6, 2]
+    ex = []
+    for e in range(E):
+        def one(k, n, K, s):
+            t, su, sv, _ = make_linear(k, n, K, seed=1500 + s)
+            sv = (sv.astype(np.float32) / (1.2437 * np.sqrt(k))).astype(np.float16)
+            return (t, su, sv)
+        ex.append({"gate": one(Hi, I, kgu[e], 3 * e), "up": one(Hi, I, kgu[e], 3 * e + 1), "down": one(I, Ho, kd[e], 3 * e + 2)})
+    rng = np.random.default_rng(15 + T)
+    x = rng.standard_normal((T, Hi)).astype(np.float16)
+    sel = np.stack([rng.permutation(E)[:topk] for _ in range(T)]).astype(np.int64)
+    sel[0] = [1, 2, 5]                                   # gate|up all 4 bits
+    rw = rng.uniform(0.2, 0.6, (T, topk)).astype(np.float16)
+    bits = lambda v: torch.tensor(v, dtype=torch.uint8, device="cuda")
+    cfg = build_cfg(amp, ex, Hi, I, Ho, Hi, 0, 8, topk, g_bits=bits(kgu), u_bits=bits(kgu), d_bits=bits(kd))
+    ref = oracle.moe_coop(x, sel, rw, ex)
+    for _ in range(2):
+        cfg["out"].fill_(float("nan"))
+        amp.moe_coop(dev(x), dev(sel), dev(rw), cfg)
+        torch.cuda.synchronize()
+        check(cfg["out"][:T].cpu().numpy(), ref)
+    assert cfg["_kmask"] == (0b11100, 0b101010)
+
+
 def test_moe_and_a_plain_gemv_on_two_streams_at_once(amp, oracle):
     """The reference runs the shared expert's linears on a side stream while moe_coop runs
     (src/ucode/ampstein/glm5.uc:970,998): launches that overlap on the GPU must not share arrival

@@ -67,6 +67,22 @@ def test_reconstruct_4096_bit_exact_and_slices(amp, oracle):
     assert np.array_equal(host16(sl), ref[:, 1024:1280])
 
 
+@pytest.mark.parametrize("K,cb", [(2, 0), (4, 2), (5, 1)])
+def test_reconstruct_batch_forms_bit_exact(amp, oracle, K, cb):
+    """Three matrices of one shape in one launch, rotated and original basis, against the oracle."""
+    mats = [make_linear(256, 384, K, seed=2500 + 7 * K + i) for i in range(3)]
+    keep = [(dev(t), dev(su), dev(sv)) for t, su, sv, _ in mats]
+    ptrs = [amp.ptr_array([k[i].data_ptr() for k in keep]) for i in range(3)]
+    out = torch.full((3, 256, 384), float("nan"), dtype=torch.float16, device="cuda")
+    amp.exl3_reconstruct_batch(out, ptrs[0], K, mul1=(cb == 2), mcg=(cb == 1))
+    for i, (t, _, _, _) in enumerate(mats):
+        assert np.array_equal(host16(out[i]), oracle.reconstruct(t, cb).view(np.uint16))
+    out.fill_(float("nan"))
+    amp.exl3_reconstruct_batch(out, ptrs[0], K, mul1=(cb == 2), mcg=(cb == 1), suh_ptrs=ptrs[1], svh_ptrs=ptrs[2])
+    for i, (t, su, sv, _) in enumerate(mats):
+        assert np.array_equal(host16(out[i]), oracle.reconstruct_had(t, su, sv, cb).view(np.uint16))
+
+
 @pytest.mark.parametrize("K,cb", [(1, 0), (3, 2), (4, 0), (5, 1), (6, 0), (8, 2)])
 def test_reconstruct_had_bit_exact(amp, oracle, K, cb):
     trellis, suh, svh, _ = make_linear(256, 384, K, seed=2000 + K)
@@ -360,6 +376,62 @@ def test_gemm_more_than_16_rows(amp, oracle):
     # the many-rows operator of the reference (exl3_gemm_recon) returns a new tensor
     y = amp.exl3_gemm_recon(dev(x), dev(trellis), dev(suh), dev(svh), 3, mcg=True)
     check_close(y.cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("rows", [200, 1100])
+def test_gemm_recon_next_to_gemm(amp, oracle, rows):
+    """The many-rows operator against the in-place operator on the same input, at the two row
+    counts the reference's test uses for its two sub-paths (tests/exl3_recon.uc:38-52: within
+    relative rms 5e-3 of each other), and both against the oracle."""
+    k, n, K = 512, 768, 4
+    trellis, suh, svh, x = make_linear(k, n, K, seed=6300 + rows, m=rows)
+    t, su, sv, xx = dev(trellis), dev(suh), dev(svh), dev(x)
+    y = torch.empty((rows, n), dtype=torch.float16, device="cuda")
+    amp.exl3_gemm(xx, t, y, su, sv)
+    z = amp.exl3_gemm_recon(xx, t, su, sv, K)
+    torch.cuda.synchronize()
+    assert gemm_status() == 0
+    a, b = y.float().cpu().numpy().astype(np.float64), z.float().cpu().numpy().astype(np.float64)
+    assert np.sqrt(np.mean((a - b) ** 2) / np.mean(a ** 2)) < 5e-3
+    check_close(b, oracle.linear(x, trellis, suh, svh, 0, fp32_out=True))
+
+
+@pytest.mark.parametrize("m", [1, 3])
+def test_chain_of_layers_against_the_oracle_chain(amp, oracle, m):
+    """Four layers of q|k|v (sliced bundle) -> o -> gate|up (stacked bundle) -> down, every output
+    feeding the next linear as in the decode graph (the reference's tests/exl3_stack.uc chains 16
+    layers of 7 linears). The oracle runs the same chain on its own intermediates; rounding
+    differences pass through eight linears per path, so the bound is 1e-2 relative rms at the end and
+    per layer."""
+    from ampstein_b200.models import LinearEXL3, Multi, Sliced
+    H, KV, I, K, layers = 512, 128, 1024, 4, 4
+    rng = np.random.default_rng(64 + m)
+    x = rng.standard_normal((m, H)).astype(np.float16)
+
+    def lin(k, n, seed):
+        tr, su, sv, _ = make_linear(k, n, K, seed=seed)
+        sv = (sv.astype(np.float32) / (1.2437 * np.sqrt(k))).astype(np.float16)      # keep activations O(1)
+        return (tr, su, sv), LinearEXL3(dev(tr), dev(su), dev(sv))
+
+    h_ref, h = x, dev(x).reshape(1, m, H)
+    for layer in range(layers):
+        s0 = 7000 + 10 * layer
+        (q_np, q), (k_np, kk), (v_np, v) = lin(H, H, s0), lin(H, KV, s0 + 1), lin(H, KV, s0 + 2)
+        (o_np, o), (g_np, g), (u_np, u), (d_np, d) = lin(H, H, s0 + 3), lin(H, I, s0 + 4), lin(H, I, s0 + 5), lin(I, H, s0 + 6)
+        outs = [torch.empty((1, m, n), dtype=torch.float16, device="cuda") for n in (H, KV, KV)]
+        Sliced([q, kk, v], outs).run(h)
+        a = o.forward(outs[0][0])                                   # attention stands in as the identity on q
+        gu = torch.empty((2, m, I), dtype=torch.float16, device="cuda")
+        Multi([g, u], gu).run(a.reshape(1, m, H))
+        h = d.forward(gu[0]).reshape(1, m, H)                        # (the activation is not part of this path)
+        r = oracle.linear(h_ref, *q_np, 0)
+        r = oracle.linear(r, *o_np, 0)
+        r = oracle.linear(r, *g_np, 0)
+        h_ref = oracle.linear(r, *d_np, 0)
+        torch.cuda.synchronize()
+        got, ref = h[0].float().cpu().numpy().astype(np.float64), h_ref.astype(np.float64)
+        assert np.all(np.isfinite(got))
+        assert np.sqrt(np.mean((got - ref) ** 2) / np.mean(ref ** 2)) < 1e-2, layer
 
 
 def gemm_status():
