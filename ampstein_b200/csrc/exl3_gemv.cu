@@ -224,10 +224,11 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
         return c < 4 ? 4 : c;
     };
     int xcap = xcap_for(16);
-    if (m > 4)
+    if (m > 4 && !A.mode)
     {
         // several batch rows: twice the x~ budget (half as many block-wide x~ passes per range)
-        // where that does not cost a resident CTA
+        // where that does not cost a resident CTA (not for the grouped modes: their runs mostly hold
+        // one or two rows, and the single-token form also needs room for the cluster exchange)
         const int big = xcap_for(32);
         if (smem_per_sm / (gemv_smem_layout(K, m, big).total + 1024) >= reg_ctas) xcap = big;
     }
