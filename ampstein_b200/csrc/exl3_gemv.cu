@@ -201,12 +201,19 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     const DevInfo& D = dev_info(dev);
 
     const int MB = m <= 8 ? 1 : 2;
-    const bool tc = !A.mode && m <= TCV_MAX_M && g_gemv_tc && !A.arin.N && !A.ar.push_only;
+    const bool tc = !A.mode && m <= TCV_MAX_M && g_gemv_tc && !A.arin.N && !A.ar.push_only && !A.x2;
     // five rows or more with a scratch for the rotated input: rotate once, in a launch of its own
-    const bool prerot = !tc && !A.mode && !A.arin.N && m >= GEMV_PREROTATE_MIN_M && A.x_rot && A.x;
-    const bool i8 = !tc && !A.mode && !A.arin.N && A.cb == 2 && m == 1 && g_int8_gemv == 2 && K <= g_int8_max_k;
+    const bool fused_norm = A.norm_w != nullptr;
+    const bool fused_act = A.x2 != nullptr && !fused_norm;
+    AMP_REQUIRE(!fused_act || (!A.mode && !A.arin.N && !A.tables && ((uintptr_t) A.x2 & 7) == 0),
+                "exl3_gemv: the fused activation takes two plain 8-byte aligned inputs");
+    AMP_REQUIRE(!fused_norm || (!A.mode && !A.arin.N && A.x && A.x2 && A.y && A.y != A.x && A.y != A.x2 &&
+                                (((uintptr_t) A.x2 | (uintptr_t) A.norm_w | (uintptr_t) A.y) & 7) == 0),
+                "exl3_gemv: the fused norm takes x, residual, weight and a separate output for the residual stream, 8-byte aligned");
+    const bool prerot = !tc && !A.mode && !A.arin.N && !fused_act && !fused_norm && m >= GEMV_PREROTATE_MIN_M && A.x_rot && A.x;
+    const bool i8 = !tc && !A.mode && !A.arin.N && !fused_act && !fused_norm && A.cb == 2 && m == 1 && g_int8_gemv == 2 && K <= g_int8_max_k;
     gemv_fn fn = tc ? gemv_tc_kernel_for(K, A.cb, A.ar.N != 0)
-                    : gemv_kernel_for(K, i8 ? 3 : A.cb, MB, A.mode, A.arin.N ? 1 : (prerot ? 2 : 0));
+                    : gemv_kernel_for(K, i8 ? 3 : A.cb, MB, A.mode, A.arin.N ? 1 : (fused_norm ? 4 : (fused_act ? 3 : (prerot ? 2 : 0))));
     if (!fn) return fail(AMP_E_UNSUPPORTED, "exl3_gemv: no kernel for K=%d cb=%d", K, A.cb);
 
     // x~ rows resident at a time: at most 16 KB of shared memory (whole segments for small
@@ -335,6 +342,8 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     P.moe = A.moe;
     P.ar = A.ar;
     P.arin = A.arin;
+    P.x2 = (const __half*) A.x2;
+    P.norm_w = (const __half*) A.norm_w; P.y = (__half*) A.y; P.eps = A.eps;
     if (A.ws_counters) { P.counters = A.ws_counters; P.scratch = A.ws_scratch; }
     else if (int rc = workspace_region(dev, stream, &P.counters, &P.scratch)) return rc;
     {
@@ -423,6 +432,53 @@ AMP_API int amp_exl3_set_int8_gemv(int mode, int max_k)
     g_int8_gemv = mode == 2 ? 2 : 0;
     if (max_k > 0) g_int8_max_k = max_k > 8 ? 8 : max_k;
     return old;
+}
+
+// Down projection with the gated activation in its prologue: c (m, n) = linear(silu(gate) * up),
+// gate / up (m, k) fp16. One launch instead of silu_mul followed by exl3_gemm; the activation is
+// formed in fp32 and rounded to fp16 exactly as the stand-alone kernel does it, so the result is
+// that of the two-step sequence. m <= 16.
+AMP_API int amp_exl3_gemv_silu_mul(const void* gate, const void* up, const void* trellis, void* c, const void* suh, const void* svh,
+                                   int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream)
+{
+    AMP_REQUIRE(gate && up, "exl3_gemv_silu_mul: null input");
+    GemvLaunch A = direct(gate, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, 0, 0);
+    A.x2 = up;
+    return launch_gemv(A, stream);
+}
+
+// Linear behind the fused residual add + RMSNorm of the decode step: y (m, k) = fp16(x + res) (the
+// updated residual stream), c (m, n) = linear(fp16(y * rsqrt(mean(y^2) + eps)) * norm_w). One launch
+// instead of rms_norm_res followed by exl3_gemm (the final norm in front of the lm_head). y must not
+// alias x or res. m <= 16.
+AMP_API int amp_exl3_gemv_rms_norm_res(const void* x, const void* res, const void* norm_w, float eps, void* y,
+                                       const void* trellis, void* c, const void* suh, const void* svh,
+                                       int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream)
+{
+    AMP_REQUIRE(x && res && norm_w && y, "exl3_gemv_rms_norm_res: null input");
+    GemvLaunch A = direct(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, 0, 0);
+    A.x2 = res; A.norm_w = norm_w; A.y = y; A.eps = eps;
+    return launch_gemv(A, stream);
+}
+
+// The bundle form (amp_exl3_mgemm's tables; q|k|v or gate|up behind rms_norm_res), m <= 16
+AMP_API int amp_exl3_mgemm_rms_norm_res(const void* x, const void* res, const void* norm_w, float eps, void* y,
+                                        const void* trellis_ptrs, void* C, const void* suh_ptrs, const void* svh_ptrs,
+                                        int num, int m, int k, int width, int K, int cb, int c_fp32,
+                                        const void* c_ptrs, const void* n_stride_list, const void* had_src_list, cudaStream_t stream)
+{
+    if (num == 0 || m == 0) return 0;
+    AMP_REQUIRE(num > 0 && m >= 1 && m <= 16, "exl3_mgemm_rms_norm_res: 1..16 rows");
+    AMP_REQUIRE(x && res && norm_w && y, "exl3_mgemm_rms_norm_res: null input");
+    GemvLaunch A = {};
+    A.x = x; A.c = C;
+    A.t_trellis = (const long long*) trellis_ptrs; A.t_suh = (const long long*) suh_ptrs;
+    A.t_svh = (const long long*) svh_ptrs; A.t_c = (const long long*) c_ptrs;
+    A.t_stride = (const int*) n_stride_list; A.t_src = (const int*) had_src_list;
+    A.tables = 1; A.slices = num; A.width = width; A.stride = width;
+    A.m = m; A.k = k; A.K = K; A.cb = cb; A.c_fp32 = c_fp32;
+    A.x2 = res; A.norm_w = norm_w; A.y = y; A.eps = eps;
+    return launch_gemv(A, stream);
 }
 
 // tuning / test hook: fixed CTA count (split) and x~ chunk size (xgroups); 0 = choose

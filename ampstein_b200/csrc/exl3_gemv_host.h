@@ -20,6 +20,11 @@ struct GemvLaunch
     int ws_max_ctas;
     GemvAr ar;           // fused tensor-parallel all-reduce of the output (ar.N == 0: none)
     GemvArIn arin;       // the input is gathered from the communicator's buffer (arin.N == 0: plain x)
+    const void* x2;      // non-null: the input is silu(x) * x2 (x = gate, x2 = up), formed in the kernel's prologue;
+                         // with norm_w: the residual contribution, input = RMSNorm(x + x2) * norm_w
+    const void* norm_w;  // RMSNorm weight (k) fp16
+    void* y;             // (m, k) fp16: receives fp16(x + x2), the updated residual stream (must not alias x)
+    float eps;
     void* x_rot;         // optional scratch, (sources, m, k) fp16: with five rows or more the input is rotated
     int num_src;         // once by a launch of its own instead of by every CTA (sources: 1, or the bundle's)
 };

@@ -28,6 +28,20 @@ gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB, int mode, int gin)
         { exl3_gemv_kernel<AMP_GEMV_K, 1, 1, 0, 2>, exl3_gemv_kernel<AMP_GEMV_K, 1, 2, 0, 2> },
         { exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 0, 2>, exl3_gemv_kernel<AMP_GEMV_K, 2, 2, 0, 2> },
     };
+    // input = silu(gate) * up, formed in the prologue
+    static const gemv_fn fna[3][2] =
+    {
+        { exl3_gemv_kernel<AMP_GEMV_K, 0, 1, 0, 3>, exl3_gemv_kernel<AMP_GEMV_K, 0, 2, 0, 3> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 1, 1, 0, 3>, exl3_gemv_kernel<AMP_GEMV_K, 1, 2, 0, 3> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 0, 3>, exl3_gemv_kernel<AMP_GEMV_K, 2, 2, 0, 3> },
+    };
+    // input = RMSNorm(x + residual) * w, formed in the prologue
+    static const gemv_fn fnn[3][2] =
+    {
+        { exl3_gemv_kernel<AMP_GEMV_K, 0, 1, 0, 4>, exl3_gemv_kernel<AMP_GEMV_K, 0, 2, 0, 4> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 1, 1, 0, 4>, exl3_gemv_kernel<AMP_GEMV_K, 1, 2, 0, 4> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 0, 4>, exl3_gemv_kernel<AMP_GEMV_K, 2, 2, 0, 4> },
+    };
     static const gemv_fn fn[3][2] =
     {
         { exl3_gemv_kernel<AMP_GEMV_K, 0, 1>, exl3_gemv_kernel<AMP_GEMV_K, 0, 2> },
@@ -44,7 +58,8 @@ gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB, int mode, int gin)
     if (cb == 3) return (MB == 1 && !mode && !gin) ? exl3_gemv_kernel<AMP_GEMV_K, 3, 1> : nullptr;
     if (cb < 0 || cb > 2 || MB < 1 || MB > 2 || mode < 0 || mode > 2) return nullptr;
     if (mode) return (MB == 1 && !gin) ? moe[cb][mode - 1] : nullptr;
-    return gin == 2 ? fnr[cb][MB - 1] : (gin ? fng[cb][MB - 1] : fn[cb][MB - 1]);
+    if (gin == 4) return fnn[cb][MB - 1];
+    return gin == 3 ? fna[cb][MB - 1] : (gin == 2 ? fnr[cb][MB - 1] : (gin ? fng[cb][MB - 1] : fn[cb][MB - 1]));
 }
 
 // tensor-memory form (dense / bundle launches of up to eight rows)

@@ -229,6 +229,11 @@ struct GemvParams
     GemvMoe moe;                // grouped-expert modes only
     GemvAr ar;                  // MODE 0, fp16 output only
     GemvArIn arin;              // MODE 0: x is gathered from the communicator's buffer
+    const __half* x2;           // GIN == 3: the input is act(x, x2) = silu(x) * x2 (x = gate, x2 = up), rounded to fp16
+                                // GIN == 4: the residual contribution added to x before the norm
+    const __half* norm_w;       // GIN == 4: RMSNorm weight (k)
+    __half* y;                  // GIN == 4: updated residual stream fp16(x + x2), (m, k), written by the first CTA
+    float eps;
 };
 
 // A ring slot holds one unit of one warp: four tile rows (the 64-row group) of GEMV_NT adjacent
@@ -560,11 +565,76 @@ __device__ __forceinline__ void gather_chunk(half4* stage, const uint2* gbase, i
     }
 }
 
+// The last arriver's sum of a column block's partials (slots [cta][2][m][128] fp32; contributor i's
+// partial sits in slot 2 i, the first contributor's in first_slot), added in ascending k order into
+// part: deterministic. Kept out of line so that its registers are not the main loop's. One batch row:
+// four contributors' loads in flight per thread (one after the other they are a chain of L2 round
+// trips on the critical path of the launch). Several rows: a thread would walk rows x contributors
+// round trips, so the partials are staged through the x~ area (free at this point) with 16-byte
+// asynchronous copies, as many contributors per batch as it holds, all in flight at once, and the
+// adds run from shared memory in the same order.
+static __device__ __forceinline__ void gemv_reduce_partials_body(float* part, const float* slots, const float* stage, uint32_t stage_s, int stage_bytes,
+                                                                 int m, int nrows, int i_first, int i_last, int first_slot, int t)
+{
+    if (nrows >= 2)
+    {
+        const int pieces = nrows * 32;                         // 16-byte pieces of one partial
+        const int cap = stage_bytes / (pieces * 16);           // contributors per batch (>= 2)
+        for (int c0 = i_first; c0 <= i_last; c0 += cap)
+        {
+            const int nb = min(cap, i_last - c0 + 1);
+            for (int e = t; e < nb * pieces; e += GEMV_THREADS)
+            {
+                const int ci = e / pieces, pc = e - ci * pieces, i = c0 + ci;
+                cp_async16_s(stage_s + e * 16, slots + (size_t) (i == i_first ? first_slot : 2 * i) * m * 128 + pc * 4);
+            }
+            cp_async_commit();
+            cp_async_wait_n<0>();
+            __syncthreads();
+            for (int idx = t; idx < nrows * 128; idx += GEMV_THREADS)
+            {
+                float sum = (c0 == i_first) ? stage[idx] : part[idx];
+                for (int ci = (c0 == i_first) ? 1 : 0; ci < nb; ++ci) sum += stage[ci * nrows * 128 + idx];
+                part[idx] = sum;
+            }
+            __syncthreads();
+        }
+        return;
+    }
+    const size_t pitch = (size_t) 2 * m * 128;                 // floats between consecutive contributors' slots
+    for (int idx = t; idx < nrows * 128; idx += GEMV_THREADS)
+    {
+        float sum = __ldcg(slots + (size_t) first_slot * m * 128 + idx);
+        const float* src = slots + (size_t) (i_first + 1) * pitch + idx;
+        for (int i = i_first + 1; i <= i_last; i += 8, src += 8 * pitch)
+        {
+            float v[8];
+            #pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (i + j <= i_last) v[j] = __ldcg(src + j * pitch);
+            #pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (i + j <= i_last) sum += v[j];
+        }
+        part[idx] = sum;
+    }
+}
+
+// (out of line for the dense launches, whose main loop is the register-critical one; in line for the
+// grouped modes, where the call's own register needs cost the single-token path more than it saves)
+static __device__ __noinline__ void gemv_reduce_partials(float* part, const float* slots, const float* stage, uint32_t stage_s, int stage_bytes,
+                                                         int m, int nrows, int i_first, int i_last, int first_slot, int t)
+{
+    gemv_reduce_partials_body(part, slots, stage, stage_s, stage_bytes, m, nrows, i_first, i_last, first_slot, t);
+}
+
 // MODE 0: one matrix or a bundle sharing one input.  MODE 1: grouped expert gate/up (slice = expert
 // run x projection, input rows gathered by token).  MODE 2: grouped expert down (input = the
 // activation of the run's gate/up rows, computed on the fly).
 // GIN: MODE 0 instances with another input side. 1: the input is gathered from the all-reduce
 // buffers (GemvArIn). 2: the input arrives already rotated (several batch rows, gemv_prerotate_kernel).
+// 3: the input is silu(x) * x2 of two vectors (the gated activation in front of a down projection).
+// 4: the input is RMSNorm(x + x2) * norm_w (residual add and norm in front of q|k|v, gate|up, lm_head).
 template <int K, int CB, int MB, int MODE = 0, int GIN = 0>
 __global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 3))
 void exl3_gemv_kernel(const GemvParams P)
@@ -784,6 +854,53 @@ void exl3_gemv_kernel(const GemvParams P)
     }
     bool waited = (MODE == 1);                         // MODE 0 / 2 wait for their predecessor inside the first x~ pass
 
+    // GIN == 4: the input is RMSNorm(x + x2) * norm_w (reference: amp_rms_norm_res_kernel,
+    // src/torch/amp_kernels.cu:279-360: y = fp16(x + r); n = fp16(y * rsqrt(mean(y^2) + eps)) * w in
+    // fp16). Every CTA needs the row's sum of squares, so every CTA reads the whole row once (it is
+    // L2 resident) while its weight stream is in flight; the first CTA also writes y.
+    __shared__ float s_scale[16];
+    if constexpr (GIN == 4)
+    {
+        __shared__ float s_red[16][GEMV_WARPS];
+        if (!started)
+        {
+            #pragma unroll
+            for (int j = 0; j < S - 1; ++j) issue();
+            started = true;
+        }
+        if (!waited) { if (P.pdl) pdl_wait(); waited = true; }
+        const int cnt = k >> 2;
+        for (int b = 0; b < m; ++b)
+        {
+            const __half* xr = P.x + (size_t) b * k;
+            const __half* rr = P.x2 + (size_t) b * k;
+            float acc = 0.0f;
+            for (int c = t; c < cnt; c += GEMV_THREADS)
+            {
+                const half4 xv = reinterpret_cast<const half4*>(xr)[c], rv = reinterpret_cast<const half4*>(rr)[c];
+                half4 h;
+                h.x = __floats2half2_rn(__low2float(xv.x) + __low2float(rv.x), __high2float(xv.x) + __high2float(rv.x));
+                h.y = __floats2half2_rn(__low2float(xv.y) + __low2float(rv.y), __high2float(xv.y) + __high2float(rv.y));
+                if (cta == 0) reinterpret_cast<half4*>(P.y + (size_t) b * k)[c] = h;
+                const float2 v0 = __half22float2(h.x), v1 = __half22float2(h.y);
+                acc += v0.x * v0.x + v0.y * v0.y;
+                acc += v1.x * v1.x + v1.y * v1.y;
+            }
+            #pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) s_red[b][warp] = acc;
+        }
+        __syncthreads();
+        if (t < m)
+        {
+            float total = 0.0f;
+            #pragma unroll
+            for (int i = 0; i < GEMV_WARPS; ++i) total += s_red[t][i];
+            s_scale[t] = rsqrtf(total / (float) k + P.eps);
+        }
+        __syncthreads();
+    }
+
     // per-lane constants of the consume side
     int xrow[MB];                                      // word offset of this lane's batch row in xd
     #pragma unroll
@@ -950,6 +1067,102 @@ void exl3_gemv_kernel(const GemvParams P)
                     #pragma unroll
                     for (int i = 0; i < TB; ++i)
                         if (tb[i] >= 0) frag_store(tb[i], tj[i], vx[i].x, vx[i].y);
+                } while (b < nrows);
+            }
+            else if constexpr (MODE == 0 && GIN == 3)
+            {
+                // The input is the gated activation of two vectors, computed here instead of by a
+                // kernel of its own between the gate|up bundle and this launch: a = fp16(silu(g) * u)
+                // in fp32 exactly as the stand-alone kernel forms it (reference: amp_silu_mul_kernel,
+                // src/torch/amp_kernels.cu:235-251), then the usual fp16 scale and rotation.
+                int b = 0, jb = warp;
+                while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
+                do
+                {
+                    constexpr int TB = 4;
+                    half4 vg[TB], vu[TB], vs[TB];
+                    int tb[TB], tj[TB];
+                    #pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                    {
+                        tb[i] = b; tj[i] = jb;
+                        if (b < nrows)
+                        {
+                            vs[i] = *reinterpret_cast<const half4*>(suh + (size_t) cg0 * 64 + (size_t) jb * 128 + lane * 4);
+                            jb += GEMV_WARPS;
+                            while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
+                        }
+                        else tb[i] = -1;
+                    }
+                    if (!waited) { if (P.pdl) pdl_wait(); waited = true; }
+                    #pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                        if (tb[i] >= 0)
+                        {
+                            const size_t off = (size_t) tb[i] * k + (size_t) cg0 * 64 + (size_t) tj[i] * 128 + lane * 4;
+                            vg[i] = *reinterpret_cast<const half4*>(P.x + off);
+                            vu[i] = *reinterpret_cast<const half4*>(P.x2 + off);
+                        }
+                    if (!started)
+                    {
+                        #pragma unroll
+                        for (int j = 0; j < S - 1; ++j) issue();
+                        started = true;
+                    }
+                    #pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                    {
+                        if (tb[i] < 0) continue;
+                        auto act1 = [](float gf, float uf) { return (gf / (1.0f + __expf(-gf))) * uf; };
+                        half4 v;
+                        v.x = __floats2half2_rn(act1(__low2float(vg[i].x), __low2float(vu[i].x)), act1(__high2float(vg[i].x), __high2float(vu[i].x)));
+                        v.y = __floats2half2_rn(act1(__low2float(vg[i].y), __low2float(vu[i].y)), act1(__high2float(vg[i].y), __high2float(vu[i].y)));
+                        v.x = __hmul2(v.x, vs[i].x);
+                        v.y = __hmul2(v.y, vs[i].y);
+                        had_store(tb[i], tj[i], __low2float(v.x), __high2float(v.x), __low2float(v.y), __high2float(v.y));
+                    }
+                } while (b < nrows);
+            }
+            else if constexpr (MODE == 0 && GIN == 4)
+            {
+                // normalised input: n = fp16(fp16(x + r) * scale) * w (fp16), then the usual scale and rotation
+                int b = 0, jb = warp;
+                while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
+                do
+                {
+                    constexpr int TB = 3;
+                    half4 vg[TB], vu[TB], vs[TB], vw[TB];
+                    int tb[TB], tj[TB];
+                    #pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                    {
+                        tb[i] = b; tj[i] = jb;
+                        if (b < nrows)
+                        {
+                            const size_t col = (size_t) cg0 * 64 + (size_t) jb * 128 + lane * 4;
+                            vs[i] = *reinterpret_cast<const half4*>(suh + col);
+                            vw[i] = *reinterpret_cast<const half4*>(P.norm_w + col);
+                            vg[i] = *reinterpret_cast<const half4*>(P.x + (size_t) b * k + col);
+                            vu[i] = *reinterpret_cast<const half4*>(P.x2 + (size_t) b * k + col);
+                            jb += GEMV_WARPS;
+                            while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
+                        }
+                        else tb[i] = -1;
+                    }
+                    #pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                    {
+                        if (tb[i] < 0) continue;
+                        const float sc = s_scale[tb[i]];
+                        half4 h, v;
+                        h.x = __floats2half2_rn(__low2float(vg[i].x) + __low2float(vu[i].x), __high2float(vg[i].x) + __high2float(vu[i].x));
+                        h.y = __floats2half2_rn(__low2float(vg[i].y) + __low2float(vu[i].y), __high2float(vg[i].y) + __high2float(vu[i].y));
+                        v.x = __hmul2(__floats2half2_rn(__low2float(h.x) * sc, __high2float(h.x) * sc), vw[i].x);
+                        v.y = __hmul2(__floats2half2_rn(__low2float(h.y) * sc, __high2float(h.y) * sc), vw[i].y);
+                        v.x = __hmul2(v.x, vs[i].x);
+                        v.y = __hmul2(v.y, vs[i].y);
+                        had_store(tb[i], tj[i], __low2float(v.x), __high2float(v.x), __low2float(v.y), __high2float(v.y));
+                    }
                 } while (b < nrows);
             }
             else if constexpr (MODE == 0 && GIN == 0)
@@ -1261,27 +1474,31 @@ void exl3_gemv_kernel(const GemvParams P)
             finish = s_last != 0;
             if (finish)
             {
-                // only the first contributor can have started before this block (its second slot).
-                // Four contributors' loads are in flight at a time (one after the other they are a
-                // chain of L2 round trips on the critical path of the launch; wider forms cost the
-                // main loop registers); the adds stay in ascending k order: deterministic.
+                // only the first contributor can have started before this block (its second slot)
                 const int first_slot = 2 * i_first + (blk * G > split.begin(i_first) ? 1 : 0);
-                const size_t pitch = (size_t) 2 * m * 128;               // floats between consecutive contributors' slots
-                for (int idx = t; idx < nrows * 128; idx += GEMV_THREADS)
+                if constexpr (MODE == 0)
+                    gemv_reduce_partials(part, slots, reinterpret_cast<const float*>(xd), xd_s, m * XPITCH * 4, m, nrows,
+                                         i_first, i_last, first_slot, t);
+                else
                 {
-                    float sum = __ldcg(slots + (size_t) first_slot * m * 128 + idx);
-                    const float* src = slots + (size_t) (i_first + 1) * pitch + idx;
-                    for (int i = i_first + 1; i <= i_last; i += 4, src += 4 * pitch)
+                    // grouped modes: the plain form (runs mostly hold one or two rows)
+                    const size_t pitch = (size_t) 2 * m * 128;
+                    for (int idx = t; idx < nrows * 128; idx += GEMV_THREADS)
                     {
-                        float v[4];
-                        #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (i + j <= i_last) v[j] = __ldcg(src + j * pitch);
-                        #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (i + j <= i_last) sum += v[j];
+                        float sum = __ldcg(slots + (size_t) first_slot * m * 128 + idx);
+                        const float* src = slots + (size_t) (i_first + 1) * pitch + idx;
+                        for (int i = i_first + 1; i <= i_last; i += 4, src += 4 * pitch)
+                        {
+                            float v[4];
+                            #pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                if (i + j <= i_last) v[j] = __ldcg(src + j * pitch);
+                            #pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                if (i + j <= i_last) sum += v[j];
+                        }
+                        part[idx] = sum;
                     }
-                    part[idx] = sum;
                 }
             }
         }

@@ -167,6 +167,93 @@ def exl3_gemm(A, B, C, suh, svh, mul1=False, mcg=False):
     return C
 
 
+def exl3_gemm_silu_mul(gate, up, B, C, suh, svh, mul1=False, mcg=False):
+    """C = linear(silu(gate) * up) in ONE launch: the gated activation of the decode step
+    (reference: torch.silu_mul followed by torch.exl3_gemm, src/ucode/ampstein/graphdec.uc:205-217)
+    folded into the input side of the down projection. gate / up (m, k) fp16 with m <= 16; the rest
+    as exl3_gemm. Returns C."""
+    _check_cuda("exl3_gemm_silu_mul", gate, up, B, C, suh, svh)
+    k, n, K = _trellis_dims("exl3_gemm_silu_mul", B)
+    if gate.dtype != torch.float16 or up.dtype != torch.float16 or suh.dtype != torch.float16 or svh.dtype != torch.float16:
+        raise TypeError("exl3_gemm_silu_mul: gate, up, suh and svh must be float16")
+    if C.dtype not in (torch.float16, torch.float32):
+        raise TypeError("exl3_gemm_silu_mul: C must be float16 or float32")
+    if gate.shape != up.shape or gate.shape[-1] != k or C.shape[-1] != n:
+        raise ValueError("exl3_gemm_silu_mul: incompatible shapes")
+    m = gate.numel() // k
+    if not 1 <= m <= 16:
+        raise ValueError("exl3_gemm_silu_mul: 1..16 rows (larger batches: silu_mul, then exl3_gemm)")
+    if C.numel() != m * n or suh.numel() != k or svh.numel() != n:
+        raise ValueError("exl3_gemm_silu_mul: incompatible shapes")
+    with torch.cuda.device(gate.device):
+        _lib.call("amp_exl3_gemv_silu_mul", gate.data_ptr(), up.data_ptr(), B.data_ptr(), C.data_ptr(), suh.data_ptr(),
+                  svh.data_ptr(), m, k, n, K, _cb(mul1, mcg), 1 if C.dtype == torch.float32 else 0, _stream(gate))
+    return C
+
+
+def _norm_args(name, x, res, norm_w, y):
+    _check_cuda(name, x, res, norm_w, y)
+    if any(t.dtype != torch.float16 for t in (x, res, norm_w, y)):
+        raise TypeError("%s: x, res, norm_w and y must be float16" % name)
+    if x.shape != res.shape or x.shape != y.shape or norm_w.numel() != x.shape[-1]:
+        raise ValueError("%s: x, res and y must have one shape, norm_w one value per column" % name)
+    if y.data_ptr() in (x.data_ptr(), res.data_ptr()):
+        raise ValueError("%s: y must not alias x or res" % name)
+
+
+def exl3_gemm_rms_norm_res(x, res, norm_w, eps, y, B, C, suh, svh, mul1=False, mcg=False):
+    """y = fp16(x + res) (the updated residual stream) and C = linear(RMSNorm(y) * norm_w) in ONE
+    launch (reference: torch.rms_norm_res followed by torch.exl3_gemm, e.g. the final norm in front
+    of the lm_head, src/ucode/ampstein/graphdec.uc:219-231). x, res, y (m, k) fp16 with m <= 16; y
+    must be a buffer of its own. Returns C."""
+    _norm_args("exl3_gemm_rms_norm_res", x, res, norm_w, y)
+    _check_cuda("exl3_gemm_rms_norm_res", B, C, suh, svh)
+    k, n, K = _trellis_dims("exl3_gemm_rms_norm_res", B)
+    if C.dtype not in (torch.float16, torch.float32) or suh.dtype != torch.float16 or svh.dtype != torch.float16:
+        raise TypeError("exl3_gemm_rms_norm_res: C must be float16 or float32, suh and svh float16")
+    m = x.numel() // k
+    if x.shape[-1] != k or not 1 <= m <= 16 or C.numel() != m * n or suh.numel() != k or svh.numel() != n:
+        raise ValueError("exl3_gemm_rms_norm_res: incompatible shapes (1..16 rows)")
+    with torch.cuda.device(x.device):
+        _lib.call("amp_exl3_gemv_rms_norm_res", x.data_ptr(), res.data_ptr(), norm_w.data_ptr(), float(eps), y.data_ptr(),
+                  B.data_ptr(), C.data_ptr(), suh.data_ptr(), svh.data_ptr(), m, k, n, K, _cb(mul1, mcg),
+                  1 if C.dtype == torch.float32 else 0, _stream(x))
+    return C
+
+
+def mgemm_rms_norm_res(x, res, norm_w, eps, y, B_ptrs, C, suh_ptrs, svh_ptrs, K, mcg, mul1, opts=None):
+    """The bundle form: y = fp16(x + res), then every matrix / slice of the bundle applied to
+    RMSNorm(y) * norm_w in ONE launch (reference: torch.rms_norm_res followed by the q|k|v or gate|up
+    mgemm, src/ucode/ampstein/graphdec.uc:163-172,196-203). x, res, y (1, m, k) fp16, m <= 16; tables
+    and opts as mgemm. Returns C."""
+    _norm_args("mgemm_rms_norm_res", x, res, norm_w, y)
+    for name, t in (("B_ptrs", B_ptrs), ("suh_ptrs", suh_ptrs), ("svh_ptrs", svh_ptrs)):
+        if not isinstance(t, torch.Tensor) or t.dtype != torch.int64 or not t.is_cuda:
+            raise TypeError("mgemm_rms_norm_res: %s must be an int64 CUDA tensor" % name)
+    _check_cuda("mgemm_rms_norm_res", C)
+    if x.dim() != 3 or x.shape[0] != 1 or C.dim() != 3 or C.dtype not in (torch.float16, torch.float32):
+        raise ValueError("mgemm_rms_norm_res: x must be (1, m, k) and C (num, m, n) float16 or float32")
+    num, m, width = C.shape
+    k = x.shape[2]
+    if x.shape[1] != m or not 1 <= m <= 16:
+        raise ValueError("mgemm_rms_norm_res: 1..16 rows, the same in x and C")
+    c_ptrs = n_stride = had_src = None
+    if opts is not None:
+        c_ptrs, n_stride, had_src = opts["c_ptrs"], opts["n_stride_list"], opts["had_src_list"]
+        if opts["size_n_list"].numel() != num or c_ptrs.numel() != num:
+            raise ValueError("mgemm_rms_norm_res: slice tables do not match C")
+    if B_ptrs.numel() < num or svh_ptrs.numel() < num:
+        raise ValueError("mgemm_rms_norm_res: pointer tables shorter than the matrix count")
+    with torch.cuda.device(x.device):
+        _lib.call("amp_exl3_mgemm_rms_norm_res", x.data_ptr(), res.data_ptr(), norm_w.data_ptr(), float(eps), y.data_ptr(),
+                  B_ptrs.data_ptr(), C.data_ptr(), suh_ptrs.data_ptr(), svh_ptrs.data_ptr(), num, m, k, width,
+                  int(K), _cb(mul1, mcg), 1 if C.dtype == torch.float32 else 0,
+                  c_ptrs.data_ptr() if c_ptrs is not None else None,
+                  n_stride.data_ptr() if n_stride is not None else None,
+                  had_src.data_ptr() if had_src is not None else None, _stream(x))
+    return C
+
+
 def exl3_gemm_recon(x, trellis, suh, svh, K, mul1=False, mcg=False):
     """EXL3 matmul for many rows (prefill); returns a new (rows, n) fp16 tensor
     (reference: torch_exl3_gemm_recon)."""

@@ -40,6 +40,17 @@ class LinearEXL3:
             out = out.add(self.bias)
         return out
 
+    def forward_silu_mul(self, gate, up, out=None):
+        """out = this linear of silu(gate) * up in one launch (the down projection behind a gate|up
+        bundle, up to 16 rows); larger batches take the two-step path of the caller."""
+        m = gate.shape[0]
+        if out is None:
+            out = torch.empty((m, self.out_features), dtype=torch.float16, device=gate.device)
+        exl3.exl3_gemm_silu_mul(gate, up, self.trellis, out, self.suh, self.svh, self.mul1, self.mcg)
+        if self.bias is not None:
+            out = out.add(self.bias)
+        return out
+
     def weight_bytes(self):
         return self.trellis.numel() * 2
 
@@ -117,6 +128,15 @@ class Multi:
             a_had = torch.empty((len(self.linears), m, a.in_features), dtype=torch.float16, device=x.device)
         return exl3.mgemm(x, self.B, self.out, self.suh, a_had, self.svh, a.K, a.mcg, a.mul1)
 
+    def run_norm(self, x, res, norm_w, eps, y):
+        """The bundle applied to RMSNorm(x + res) * norm_w, y = fp16(x + res): one launch (up to 16 rows)."""
+        return _run_norm(self, self.out, x, res, norm_w, eps, y, None)
+
+
+def _run_norm(bundle, carrier, x, res, norm_w, eps, y, opts):
+    a = bundle.linears[0]
+    return exl3.mgemm_rms_norm_res(x, res, norm_w, eps, y, bundle.B, carrier, bundle.suh, bundle.svh, a.K, a.mcg, a.mul1, opts)
+
 
 class Sliced:
     """Bundle for unequal widths such as Q/K/V (reference: models.uc sliced(), :367-432): every
@@ -164,6 +184,11 @@ class Sliced:
         if a_had is None and (m >= 5 or x.dtype == torch.bfloat16):
             a_had = torch.empty((len(self.linears), m, a.in_features), dtype=torch.float16, device=x.device)
         exl3.mgemm(x, self.B, self.carrier, self.suh, a_had, self.svh, a.K, a.mcg, a.mul1, self.opts)
+        return self.outs
+
+    def run_norm(self, x, res, norm_w, eps, y):
+        """The bundle applied to RMSNorm(x + res) * norm_w, y = fp16(x + res): one launch (up to 16 rows)."""
+        _run_norm(self, self.carrier, x, res, norm_w, eps, y, self.opts)
         return self.outs
 
 

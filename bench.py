@@ -605,7 +605,7 @@ def measure_moe(steps, warmup, T):
                      "kernel": "exl3_gemv_kernel (grouped modes)", "bytes_per_launch": int(byt) // 2, "traffic": None}}
 
 
-def measure_gemv(steps, warmup, shape, m, tmem=False, mul1=False):
+def measure_gemv(steps, warmup, shape, m, tmem=False, mul1=False, silu_mul=False):
     """One decode GEMV shape on its own (k x n at K bits, m rows): as many distinct copies of the
     matrix as it takes to exceed L2 twice over, one launch per copy, all in one CUDA graph."""
     import torch
@@ -622,7 +622,11 @@ def measure_gemv(steps, warmup, shape, m, tmem=False, mul1=False):
     suh, svh = sgn(k), (sgn(n) / (1.2437 * math.sqrt(k))).to(torch.float16)
     x = torch.randn((m, k), device=dev, generator=g).to(torch.float16)
     y = torch.empty((m, n), dtype=torch.float16, device=dev)
-    graph = DecodeGraph(lambda: [amp.exl3_gemm(x, t, y, suh, svh, mul1=mul1) for t in mats], warmup=max(warmup, 3))
+    if silu_mul:
+        x2 = torch.randn((m, k), device=dev, generator=g).to(torch.float16)
+        graph = DecodeGraph(lambda: [amp.exl3_gemm_silu_mul(x, x2, t, y, suh, svh, mul1=mul1) for t in mats], warmup=max(warmup, 3))
+    else:
+        graph = DecodeGraph(lambda: [amp.exl3_gemm(x, t, y, suh, svh, mul1=mul1) for t in mats], warmup=max(warmup, 3))
     sampler = ClockSampler(0)
     t0 = time.time()
     ms_blk, nblk, _ = timed_blocks(torch, graph.replay, steps, graph.stream, min_s=0.3)
@@ -641,6 +645,7 @@ def measure_gemv(steps, warmup, shape, m, tmem=False, mul1=False):
         "config": {"workload": "one GEMV shape, %d distinct weight copies per graph (%.0f MB, larger than L2)" % (copies, copies * wbytes / 1e6),
                    "kernel_form": "tensor memory (tcgen05)" if tmem else "mma.sync",
                    "codebook": "mul1" if mul1 else "default",
+                   "input": "silu(gate) * up formed in the prologue" if silu_mul else "plain",
                    "timing": "median of %d blocks of %d graph replays" % (nblk, steps)},
         "gpu_launches": copies * steps, "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
@@ -782,6 +787,7 @@ def main():
     ap.add_argument("--tmem-gemv", action="store_true",
                     help="A/B: run the decode GEMVs on the tensor-memory (tcgen05) kernel instead of the mma.sync kernel")
     ap.add_argument("--mul1", action="store_true", help="--workload gemv: the mul1 codebook (one row then takes the int8-activation form)")
+    ap.add_argument("--silu-mul", action="store_true", help="--workload gemv: the down projection with silu(gate) * up folded into its prologue")
     ap.add_argument("--no-int8", action="store_true", help="--workload gemv --mul1: keep the fp16 kernel (A/B)")
     ap.add_argument("--separate", action="store_true",
                     help="--workload prefill: seven separate GEMM calls instead of the q|k|v and gate|up bundles")
@@ -818,7 +824,7 @@ def main():
             if args.no_int8:
                 from ampstein_b200 import _lib
                 _lib.lib().amp_exl3_set_int8_gemv(0, 0)
-            print(json.dumps(measure_gemv(args.steps, args.warmup, shape, args.batch, args.tmem_gemv, args.mul1)), flush=True)
+            print(json.dumps(measure_gemv(args.steps, args.warmup, shape, args.batch, args.tmem_gemv, args.mul1, args.silu_mul)), flush=True)
         else:
             print(json.dumps({"metric": "scheduler cycles per 8 decoded weights and lane (K=4 mix)", "unit": "cycles",
                               "by_warps_per_scheduler": measure_issue()}), flush=True)

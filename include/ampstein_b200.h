@@ -173,6 +173,38 @@ int amp_exl3_gemv_cfg(const void* x, const void* trellis, void* c, const void* s
                       cudaStream_t stream);
 
 /*
+ * Down projection with the gated activation folded into its input side: C (m, n) = the linear of
+ * a = fp16(silu(gate) * up), gate / up (m, k) fp16 (e.g. the two slabs of the gate|up bundle's stacked
+ * output). One launch instead of two; fp32 activation math and one rounding as the stand-alone kernel.
+ * m <= 16.
+ * Replaces: the pair torch.silu_mul + torch.exl3_gemm of the decode step,
+ * src/ucode/ampstein/graphdec.uc:205-217 (kernel amp_silu_mul_kernel, src/torch/amp_kernels.cu:235-251);
+ * the reference has no fused form for dense layers (its fused MoE does the same for experts).
+ */
+int amp_exl3_gemv_silu_mul(const void* gate, const void* up, const void* trellis, void* C, const void* suh, const void* svh,
+                           int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream);
+
+/*
+ * Linear (or bundle) behind the fused residual add + RMSNorm of the decode step, in ONE launch:
+ *   y (m, k)  = fp16(x + res)                                   the updated residual stream
+ *   C         = the linear(s) of  fp16(y * rsqrt(mean(y^2) + eps)) * norm_w   (fp16 multiply)
+ * x, res, y (m, k) fp16, norm_w (k) fp16; y must not alias x or res (every CTA re-reads x while the
+ * first one writes y). The sum of squares is formed per CTA (fp32, a fixed order that differs from
+ * the stand-alone kernel's, so the scale may differ in its last bit). m <= 16. The bundle form
+ * takes amp_exl3_mgemm's tables.
+ * Replaces: torch.rms_norm_res followed by the q|k|v / gate|up bundle or the lm_head,
+ * src/ucode/ampstein/graphdec.uc:163-225 (kernel amp_rms_norm_res_kernel,
+ * src/torch/amp_kernels.cu:279-360); the reference has no fused form.
+ */
+int amp_exl3_gemv_rms_norm_res(const void* x, const void* res, const void* norm_w, float eps, void* y,
+                               const void* trellis, void* C, const void* suh, const void* svh,
+                               int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream);
+int amp_exl3_mgemm_rms_norm_res(const void* x, const void* res, const void* norm_w, float eps, void* y,
+                                const void* trellis_ptrs, void* C, const void* suh_ptrs, const void* svh_ptrs,
+                                int num, int m, int k, int width, int K, int cb, int c_fp32,
+                                const void* c_ptrs, const void* n_stride_list, const void* had_src_list, cudaStream_t stream);
+
+/*
  * Several EXL3 matrices -- or equal-width column slices of matrices -- against ONE shared input
  * x (m, k) in a single launch, m <= 16. Matrices are named by DEVICE pointer tables (int64
  * device arrays), exactly as the reference takes them, so no host synchronisation is needed:

@@ -177,6 +177,27 @@ def linear_int8(x, trellis, suh, svh, fp32_out=False):
     return o32 if fp32_out else o16.view(np.float16)
 
 
+def silu_mul(g, u):
+    """fp16(silu(g) * u) with fp32 math (reference: amp_silu_mul_kernel, src/torch/amp_kernels.cu:235-251)."""
+    gf = np.asarray(g, np.float16).astype(np.float32)
+    uf = np.asarray(u, np.float16).astype(np.float32)
+    s = gf / (np.float32(1.0) + np.exp(-gf, dtype=np.float32))
+    return (s * uf).astype(np.float16)
+
+
+def rms_norm_res(x, res, w, eps):
+    """(y, n): y = fp16(x + res); n = fp16(y * rsqrt(mean(y^2) + eps)) * w in fp16 (reference:
+    amp_rms_norm_res_kernel, src/torch/amp_kernels.cu:279-360). The mean is formed in float64 here
+    (the kernel's fp32 sum order is a property of its launch), which can move the scale by one fp32 ulp."""
+    xf = np.asarray(x, np.float16).astype(np.float32)
+    rf = np.asarray(res, np.float16).astype(np.float32)
+    y = (xf + rf).astype(np.float16)
+    yf = y.astype(np.float32)
+    scale = (1.0 / np.sqrt(np.mean(yf.astype(np.float64) ** 2, axis=-1, keepdims=True) + eps)).astype(np.float32)
+    n = (yf * scale).astype(np.float16) * np.asarray(w, np.float16)
+    return y, n.astype(np.float16)
+
+
 def matmul_f32(a, w):
     aa, ww = _h(a), _h(w)
     m, k = aa.shape

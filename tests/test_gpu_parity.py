@@ -378,6 +378,67 @@ def test_gemm_more_than_16_rows(amp, oracle):
     check_close(y.cpu().numpy(), ref)
 
 
+@pytest.mark.parametrize("m,k,n,K,cb", [(1, 1024, 512, 4, 0), (3, 2048, 256, 5, 1), (8, 768, 384, 3, 2), (12, 512, 256, 6, 0),
+                                        (1, 14336, 1024, 4, 0)])
+def test_down_projection_with_the_activation_in_its_prologue(amp, oracle, m, k, n, K, cb):
+    """exl3_gemm_silu_mul(gate, up, ...) against the two-step sequence it replaces: the oracle's
+    silu_mul then linear, and this library's exl3_gemm on an activation formed by torch (fp32 math,
+    rounded to fp16): same rounding points, so the bound is the linear's own."""
+    trellis, suh, svh, g = make_linear(k, n, K, seed=9500 + m + K, m=m)
+    u = np.random.default_rng(95 + m).standard_normal((m, k)).astype(np.float16)
+    t, su, sv, gd, ud = dev(trellis), dev(suh), dev(svh), dev(g), dev(u)
+    y = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    amp.exl3_gemm_silu_mul(gd, ud, t, y, su, sv, mul1=(cb == 2), mcg=(cb == 1))
+    a = (torch.nn.functional.silu(gd.float()) * ud.float()).to(torch.float16)
+    y2 = torch.empty_like(y)
+    amp.exl3_gemm(a, t, y2, su, sv, mul1=(cb == 2), mcg=(cb == 1))
+    torch.cuda.synchronize()
+    ref = oracle.linear(oracle.silu_mul(g, u), trellis, suh, svh, cb, fp32_out=True)
+    check_close(y.cpu().numpy(), ref)
+    check_close(y.cpu().numpy(), y2.cpu().numpy())
+
+
+@pytest.mark.parametrize("m,k,K,cb", [(1, 1024, 4, 0), (2, 4096, 4, 0), (5, 512, 5, 2), (9, 768, 3, 1)])
+def test_linears_with_the_residual_norm_in_their_prologue(amp, oracle, m, k, K, cb):
+    """exl3_gemm_rms_norm_res and the bundle form against the two-step sequence they replace (the
+    oracle's rms_norm_res, then linear): y bit-exact, the linears within their own bound (the scale may
+    differ in its last fp32 bit: the sum of squares is added in another order)."""
+    from ampstein_b200.models import LinearEXL3, Multi, Sliced
+    n = 512
+    trellis, suh, svh, x = make_linear(k, n, K, seed=9600 + m + K, m=m)
+    rng = np.random.default_rng(96 + m)
+    res = (rng.standard_normal((m, k)) * 0.5).astype(np.float16)
+    w = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float16)
+    eps = 1e-5
+    y_ref, n_ref = oracle.rms_norm_res(x, res, w, eps)
+    t, su, sv, xd, rd, wd = dev(trellis), dev(suh), dev(svh), dev(x), dev(res), dev(w)
+    y = torch.full((m, k), float("nan"), dtype=torch.float16, device="cuda")
+    c = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    amp.exl3_gemm_rms_norm_res(xd, rd, wd, eps, y, t, c, su, sv, mul1=(cb == 2), mcg=(cb == 1))
+    torch.cuda.synchronize()
+    assert np.array_equal(host16(y), y_ref.view(np.uint16))
+    check_close(c.cpu().numpy(), oracle.linear(n_ref, trellis, suh, svh, cb, fp32_out=True))
+    with pytest.raises(ValueError):
+        amp.exl3_gemm_rms_norm_res(xd, rd, wd, eps, xd, t, c, su, sv)
+
+    # bundles: stacked pair and a sliced triple behind the same norm
+    parts = []
+    for i, wd_ in enumerate((512, 256, 256, 384, 384)):
+        tr, s_u, s_v, _ = make_linear(k, wd_, K, seed=9700 + i + m)
+        parts.append(((tr, s_u, s_v), LinearEXL3(dev(tr), dev(s_u), dev(s_v), mul1=(cb == 2), mcg=(cb == 1))))
+    x3, r3 = xd.reshape(1, m, k), rd.reshape(1, m, k)
+    outs = [torch.full((1, m, wd_), float("nan"), dtype=torch.float16, device="cuda") for wd_ in (512, 256, 256)]
+    y.fill_(float("nan"))
+    Sliced([p[1] for p in parts[:3]], outs).run_norm(x3, r3, wd, eps, y.reshape(1, m, k))
+    gu = torch.full((2, m, 384), float("nan"), dtype=torch.float16, device="cuda")
+    y2 = torch.full((1, m, k), float("nan"), dtype=torch.float16, device="cuda")
+    Multi([p[1] for p in parts[3:]], gu).run_norm(x3, r3, wd, eps, y2)
+    torch.cuda.synchronize()
+    assert np.array_equal(host16(y), y_ref.view(np.uint16)) and np.array_equal(host16(y2[0]), y_ref.view(np.uint16))
+    for o, ((tr, s_u, s_v), _) in zip([o[0] for o in outs] + [gu[0], gu[1]], parts):
+        check_close(o.float().cpu().numpy(), oracle.linear(n_ref, tr, s_u, s_v, cb, fp32_out=True))
+
+
 @pytest.mark.parametrize("rows", [200, 1100])
 def test_gemm_recon_next_to_gemm(amp, oracle, rows):
     """The many-rows operator against the in-place operator on the same input, at the two row
