@@ -620,8 +620,9 @@ static __device__ __forceinline__ void gemv_reduce_partials_body(float* part, co
     }
 }
 
-// (out of line for the dense launches, whose main loop is the register-critical one; in line for the
-// grouped modes, where the call's own register needs cost the single-token path more than it saves)
+// (used by the instance that serves five rows and more; out of line so that it does not shape the
+// main loop's code. The other instances keep a plain in-line form: their code shape is what the
+// one-row step and the single-token MoE were tuned on, and any change to it costs them 1-12 %.)
 static __device__ __noinline__ void gemv_reduce_partials(float* part, const float* slots, const float* stage, uint32_t stage_s, int stage_bytes,
                                                          int m, int nrows, int i_first, int i_last, int first_slot, int t)
 {
@@ -1476,12 +1477,13 @@ void exl3_gemv_kernel(const GemvParams P)
             {
                 // only the first contributor can have started before this block (its second slot)
                 const int first_slot = 2 * i_first + (blk * G > split.begin(i_first) ? 1 : 0);
-                if constexpr (MODE == 0)
+                if constexpr (MODE == 0 && GIN == 2)
                     gemv_reduce_partials(part, slots, reinterpret_cast<const float*>(xd), xd_s, m * XPITCH * 4, m, nrows,
                                          i_first, i_last, first_slot, t);
                 else
                 {
-                    // grouped modes: the plain form (runs mostly hold one or two rows)
+                    // every other instance: the plain form (one to four rows, or runs that mostly hold
+                    // one or two); the instance for five rows and more stages through shared memory
                     const size_t pitch = (size_t) 2 * m * 128;
                     for (int idx = t; idx < nrows * 128; idx += GEMV_THREADS)
                     {
