@@ -201,9 +201,12 @@ class P2PComm:
         bufs, ctls = self._bufs[rank]
         cb = 2 if lin.mul1 else (1 if lin.mcg else 0)
         with torch.cuda.device(x.device):
-            _lib.call("amp_exl3_gemv_allreduce", x.data_ptr(), lin.trellis.data_ptr(), out.data_ptr(),
+            # from five rows on, a scratch lets the input be rotated once instead of by every CTA
+            rot = torch.empty_like(x) if m >= 5 else None
+            _lib.call("amp_exl3_gemv_allreduce_rot", x.data_ptr(), lin.trellis.data_ptr(), out.data_ptr(),
                       lin.suh.data_ptr(), lin.svh.data_ptr(), m, lin.in_features, n, lin.K, cb,
-                      bufs, ctls, rank, self.N, self.cap, torch.cuda.current_stream(x.device).cuda_stream)
+                      bufs, ctls, rank, self.N, self.cap, rot.data_ptr() if rot is not None else None,
+                      torch.cuda.current_stream(x.device).cuda_stream)
         return out
 
     # ---- split exchange: push in the producer, gather in the consumer's prologue ----

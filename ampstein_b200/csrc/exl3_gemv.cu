@@ -512,6 +512,27 @@ AMP_API int amp_exl3_gemv_allreduce(const void* x, const void* trellis, void* ou
     return launch_gemv(A, stream);
 }
 
+// The same with a scratch for the rotated input ((m, k) fp16, nullable): from five rows on the input
+// is then rotated once by a small launch of its own instead of by every CTA (as amp_exl3_gemm's A_had).
+AMP_API int amp_exl3_gemv_allreduce_rot(const void* x, const void* trellis, void* out, const void* suh, const void* svh,
+                                        int m, int k, int n, int K, int cb, void* const* bufs, int* const* ctls,
+                                        int rank, int N, long cap, void* x_rot, cudaStream_t stream)
+{
+    AMP_REQUIRE(N >= 2 && N <= COMM_MAXN && rank >= 0 && rank < N, "exl3_gemv_allreduce: bad rank / world size (2..%d ranks)", COMM_MAXN);
+    AMP_REQUIRE(bufs && ctls, "exl3_gemv_allreduce: null buffer table");
+    AMP_REQUIRE(cap > 0 && cap % 8 == 0 && (long) m * n <= cap, "exl3_gemv_allreduce: m * n exceeds the communicator's capacity");
+    GemvLaunch A = direct(x, trellis, out, suh, svh, m, k, n, K, cb, 0, 0, 0);
+    for (int p = 0; p < N; ++p)
+    {
+        AMP_REQUIRE(bufs[p] && ctls[p], "exl3_gemv_allreduce: null buffer of rank %d", p);
+        A.ar.buf[p] = (uint2*) bufs[p];
+    }
+    A.ar.ctl = ctls[rank];
+    A.ar.rank = rank; A.ar.N = N; A.ar.wcap = cap / 2;
+    A.x_rot = x_rot;
+    return launch_gemv(A, stream);
+}
+
 // ---- split exchange: the producer only pushes, the consumer gathers in its x~ prologue ----
 // amp_exl3_gemv_push: a row-parallel linear whose finished column blocks are pushed, as fp16
 // partials, into every rank's all-reduce buffer (this rank's included); nothing waits and no output

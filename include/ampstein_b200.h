@@ -366,6 +366,11 @@ int amp_comm_allreduce_fp16(const void* x, void* out, void* const* bufs, int* co
 int amp_exl3_gemv_allreduce(const void* x, const void* trellis, void* out, const void* suh, const void* svh,
                             int m, int k, int n, int K, int cb, void* const* bufs, int* const* ctls,
                             int rank, int N, long cap, cudaStream_t stream);
+/* The same with an optional scratch for the rotated input ((m, k) fp16 or NULL), used from five rows
+ * on exactly as amp_exl3_gemm uses A_had. */
+int amp_exl3_gemv_allreduce_rot(const void* x, const void* trellis, void* out, const void* suh, const void* svh,
+                                int m, int k, int n, int K, int cb, void* const* bufs, int* const* ctls,
+                                int rank, int N, long cap, void* x_rot, cudaStream_t stream);
 /*
  * The same exchange split between producer and consumer, so that no kernel waits for a peer
  * while its own rank could move on: amp_exl3_gemv_push is the row-parallel linear whose finished

@@ -120,15 +120,16 @@ def test_fused_linear_allreduce_matches_gemv_then_allreduce(oracle):
     plain GEMV followed by the stand-alone all-reduce on every rank, equal to the oracle's
     rank-order sum of the fp16 partials, and mixable with plain all-reduce calls on the same
     communicator (shared sequence numbers). Covers the cluster and the global form of the
-    partial-sum exchange and batches 1 and 3."""
+    partial-sum exchange, batches 1 to 3, and 8 / 13 rows (rotated-input instance)."""
     if ngpu() < 2:
         pytest.skip("needs at least two GPUs")
     from conftest import make_linear
     from ampstein_b200.comm import p2p_comm
     from ampstein_b200.models import LinearEXL3
     for N in sorted({2, min(ngpu(), 8)}):
-        comm = p2p_comm(list(range(N)), 3 * 1024)
-        for call, (k_local, n, m) in enumerate([(1024, 512, 1), (256, 1024, 3), (1024, 512, 1), (2048, 256, 2)]):
+        comm = p2p_comm(list(range(N)), 4 * 1024)
+        for call, (k_local, n, m) in enumerate([(1024, 512, 1), (256, 1024, 3), (1024, 512, 1), (2048, 256, 2),
+                                                (1024, 512, 8), (512, 256, 13)]):     # 5+ rows: input rotated by its own launch
             shards = [make_linear(k_local, n, 4, seed=8800 + 10 * call + r, m=m) for r in range(N)]
             lins, xs = [], []
             for r, (trellis, suh, svh, x) in enumerate(shards):
