@@ -682,6 +682,8 @@ void exl3_gemm_tc2_kernel(const TcParams P)
             // launched as a programmatic dependent of the rotation kernel: everything up to here
             // (tensor-memory allocation, barriers, the decode warps' first weight copies) ran under
             // that kernel; its output is read from here on
+            // (only this thread waits: every other role consumes what it fetches. Any new read of
+            // the rotation kernel's output by another thread must come after a wait of its own.)
             asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int i = 0; i < ksteps && ok; ++i)
             {

@@ -344,6 +344,16 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     P.arin = A.arin;
     P.x2 = (const __half*) A.x2;
     P.norm_w = (const __half*) A.norm_w; P.y = (__half*) A.y; P.eps = A.eps;
+    P.am_key = nullptr; P.am_count = nullptr; P.am_ids = P.am_pos = P.am_log = nullptr; P.am_log_cap = 0; P.am_vocab = 0;
+    if (A.am_ws)
+    {
+        AMP_REQUIRE(fused_norm && m == 1 && !A.c_fp32 && !A.tables && !A.ar.N, "exl3_gemv: the fused argmax needs the norm form, one row and fp16 logits");
+        AMP_REQUIRE(A.am_ids && A.am_pos && A.am_log && ((uintptr_t) A.am_ws & 7) == 0, "exl3_gemv: argmax state pointers missing or misaligned");
+        AMP_REQUIRE(A.am_vocab >= 1 && A.am_vocab <= A.width, "exl3_gemv: vocabulary size out of range");
+        P.am_key = (unsigned long long*) A.am_ws; P.am_count = (unsigned int*) ((char*) A.am_ws + 8);
+        P.am_ids = (long long*) A.am_ids; P.am_pos = (long long*) A.am_pos; P.am_log = (long long*) A.am_log;
+        P.am_log_cap = A.am_log_cap; P.am_vocab = A.am_vocab;
+    }
     if (A.ws_counters) { P.counters = A.ws_counters; P.scratch = A.ws_scratch; }
     else if (int rc = workspace_region(dev, stream, &P.counters, &P.scratch)) return rc;
     {
@@ -458,6 +468,23 @@ AMP_API int amp_exl3_gemv_rms_norm_res(const void* x, const void* res, const voi
     AMP_REQUIRE(x && res && norm_w && y, "exl3_gemv_rms_norm_res: null input");
     GemvLaunch A = direct(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, 0, 0);
     A.x2 = res; A.norm_w = norm_w; A.y = y; A.eps = eps;
+    return launch_gemv(A, stream);
+}
+
+// The last three launches of a greedy decode step in one: final residual add + RMSNorm, lm_head (one
+// row, fp16 logits (1, n)), argmax over the first `vocab` logits and the state advance
+// log[pos] = ids; ids = argmax; pos += 1 (log write skipped when pos is outside [0, log_cap)). Ties go
+// to the lowest index, NaN logits are skipped, no valid logit gives 0. ws: 16 bytes, 8-byte aligned,
+// zero before the first call; every call leaves it zero.
+AMP_API int amp_exl3_lm_head_argmax(const void* x, const void* res, const void* norm_w, float eps, void* y,
+                                    const void* trellis, void* logits, const void* suh, const void* svh,
+                                    int k, int n, int K, int cb, int vocab,
+                                    void* ids, void* pos, void* log, long long log_cap, void* ws, cudaStream_t stream)
+{
+    AMP_REQUIRE(x && res && norm_w && y && ws, "exl3_lm_head_argmax: null input");
+    GemvLaunch A = direct(x, trellis, logits, suh, svh, 1, k, n, K, cb, 0, 0, 0);
+    A.x2 = res; A.norm_w = norm_w; A.y = y; A.eps = eps;
+    A.am_ws = ws; A.am_ids = ids; A.am_pos = pos; A.am_log = log; A.am_log_cap = log_cap; A.am_vocab = vocab;
     return launch_gemv(A, stream);
 }
 

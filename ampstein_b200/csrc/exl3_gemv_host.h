@@ -25,6 +25,10 @@ struct GemvLaunch
     const void* norm_w;  // RMSNorm weight (k) fp16
     void* y;             // (m, k) fp16: receives fp16(x + x2), the updated residual stream (must not alias x)
     float eps;
+    // with norm_w, one row, fp16 output: argmax over the output + decode-state advance (all or none)
+    void* am_ws;         // >= 16 bytes, 8-byte aligned, zero before the first launch (key + block counter)
+    void* am_ids; void* am_pos; void* am_log; long long am_log_cap;
+    int am_vocab;
     void* x_rot;         // optional scratch, (sources, m, k) fp16: with five rows or more the input is rotated
     int num_src;         // once by a launch of its own instead of by every CTA (sources: 1, or the bundle's)
 };

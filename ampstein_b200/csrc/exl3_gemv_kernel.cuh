@@ -234,6 +234,12 @@ struct GemvParams
     const __half* norm_w;       // GIN == 4: RMSNorm weight (k)
     __half* y;                  // GIN == 4: updated residual stream fp16(x + x2), (m, k), written by the first CTA
     float eps;
+    // GIN == 4, one row, fp16 output: greedy next-token pick over the output (the lm_head's logits)
+    // and the decode-state advance, done by the CTAs that finish the column blocks
+    unsigned long long* am_key; // best (ordered value << 32 | ~index) so far; zero between launches
+    unsigned int* am_count;     // finished column blocks; zero between launches
+    long long* am_ids; long long* am_pos; long long* am_log; long long am_log_cap;
+    int am_vocab;               // columns that take part (<= n)
 };
 
 // A ring slot holds one unit of one warp: four tile rows (the 64-row group) of GEMV_NT adjacent
@@ -1598,6 +1604,52 @@ void exl3_gemv_kernel(const GemvParams P)
                         }
                     }
                     reinterpret_cast<half4*>(reinterpret_cast<__half*>(cbase) + (size_t) b * stride + (size_t) nb * 128)[lane] = o;
+                    if constexpr (GIN == 4)
+                    {
+                        if (P.am_key && b == 0)
+                        {
+                            // argmax over the logits just stored (reference: amp_argmax_advance_kernel,
+                            // src/torch/amp_kernels.cu:823-901: largest value, ties to the lowest index,
+                            // NaN skipped): the value goes into the high half of a 64-bit key in an order
+                            // preserving form, the complemented index into the low half, so one atomic
+                            // maximum per column block keeps the winner whatever the arrival order
+                            const int col0 = blk * 128 + lane * 4;
+                            const float v[4] = { __low2float(o.x), __high2float(o.x), __low2float(o.y), __high2float(o.y) };
+                            unsigned long long key = 0ull;
+                            #pragma unroll
+                            for (int j = 3; j >= 0; --j)
+                            {
+                                if (!(v[j] == v[j]) || col0 + j >= P.am_vocab) continue;
+                                const uint32_t u = v[j] == 0.0f ? 0u : __float_as_uint(v[j]);     // -0 and +0 compare equal
+                                const uint32_t ord = u ^ ((u >> 31) ? 0xffffffffu : 0x80000000u);
+                                const unsigned long long kj = ((unsigned long long) ord << 32) | (0xffffffffu - (uint32_t) (col0 + j));
+                                key = kj > key ? kj : key;
+                            }
+                            #pragma unroll
+                            for (int sft = 16; sft > 0; sft >>= 1)
+                            {
+                                const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, sft);
+                                key = other > key ? other : key;
+                            }
+                            if (lane == 0)
+                            {
+                                if (key) atomicMax(P.am_key, key);
+                                __threadfence();
+                                if (atomicAdd(P.am_count, 1u) + 1u == (unsigned) P.blocks)
+                                {
+                                    // last block: every candidate has been merged; advance the decode state
+                                    __threadfence();
+                                    const unsigned long long best = *(volatile unsigned long long*) P.am_key;
+                                    const long long p = P.am_pos[0];
+                                    if (p >= 0 && p < P.am_log_cap) P.am_log[p] = P.am_ids[0];
+                                    P.am_ids[0] = best ? (long long) (0xffffffffu - (uint32_t) (best & 0xffffffffull)) : 0;
+                                    P.am_pos[0] = p + 1;
+                                    *P.am_key = 0ull;
+                                    *P.am_count = 0u;
+                                }
+                            }
+                        }
+                    }
                 }
             }
             if constexpr (MODE == 0)

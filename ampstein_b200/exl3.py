@@ -221,6 +221,33 @@ def exl3_gemm_rms_norm_res(x, res, norm_w, eps, y, B, C, suh, svh, mul1=False, m
     return C
 
 
+def lm_head_argmax(x, res, norm_w, eps, y, B, logits, suh, svh, ids, pos, log, ws, vocab=None, mul1=False, mcg=False):
+    """The end of a greedy decode step in ONE launch: y = fp16(x + res); logits (1, n) fp16 = lm_head of
+    RMSNorm(y) * norm_w; ids = argmax(logits[:vocab]) after log[pos] = ids, pos += 1 (reference:
+    torch.rms_norm_res + torch.exl3_gemm + torch.argmax_advance, src/ucode/ampstein/graphdec.uc:219-240).
+    ids, pos: int64 tensors of one element; log: int64; ws: at least 16 bytes of zero-filled device
+    memory owned by this decoder (any dtype). Returns logits."""
+    _norm_args("lm_head_argmax", x, res, norm_w, y)
+    _check_cuda("lm_head_argmax", B, logits, suh, svh, ids, pos, log, ws)
+    k, n, K = _trellis_dims("lm_head_argmax", B)
+    if logits.dtype != torch.float16 or suh.dtype != torch.float16 or svh.dtype != torch.float16:
+        raise TypeError("lm_head_argmax: logits, suh and svh must be float16")
+    if x.numel() != k or logits.numel() != n or suh.numel() != k or svh.numel() != n:
+        raise ValueError("lm_head_argmax: one row; shapes must match the weight")
+    if ids.dtype != torch.int64 or pos.dtype != torch.int64 or log.dtype != torch.int64 or ids.numel() < 1 or pos.numel() < 1:
+        raise TypeError("lm_head_argmax: ids, pos and log must be int64 tensors")
+    if ws.numel() * ws.element_size() < 16 or ws.data_ptr() % 8:
+        raise ValueError("lm_head_argmax: ws must hold at least 16 bytes, 8-byte aligned")
+    vocab = n if vocab is None else int(vocab)
+    if not 1 <= vocab <= n:
+        raise ValueError("lm_head_argmax: vocab out of range")
+    with torch.cuda.device(x.device):
+        _lib.call("amp_exl3_lm_head_argmax", x.data_ptr(), res.data_ptr(), norm_w.data_ptr(), float(eps), y.data_ptr(),
+                  B.data_ptr(), logits.data_ptr(), suh.data_ptr(), svh.data_ptr(), k, n, K, _cb(mul1, mcg), vocab,
+                  ids.data_ptr(), pos.data_ptr(), log.data_ptr(), log.numel(), ws.data_ptr(), _stream(x))
+    return logits
+
+
 def mgemm_rms_norm_res(x, res, norm_w, eps, y, B_ptrs, C, suh_ptrs, svh_ptrs, K, mcg, mul1, opts=None):
     """The bundle form: y = fp16(x + res), then every matrix / slice of the bundle applied to
     RMSNorm(y) * norm_w in ONE launch (reference: torch.rms_norm_res followed by the q|k|v or gate|up

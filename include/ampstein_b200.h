@@ -199,6 +199,21 @@ int amp_exl3_gemv_silu_mul(const void* gate, const void* up, const void* trellis
 int amp_exl3_gemv_rms_norm_res(const void* x, const void* res, const void* norm_w, float eps, void* y,
                                const void* trellis, void* C, const void* suh, const void* svh,
                                int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream);
+/*
+ * The last three launches of a greedy decode step in one: y = fp16(x + res), logits (1, n) fp16 = the
+ * lm_head of RMSNorm(y) * norm_w, then argmax over the first `vocab` logits and the state advance
+ * log[pos] = ids; ids = argmax; pos += 1 (ids, pos: one int64 each; log: int64 array of log_cap
+ * entries, the write is skipped when pos is outside it). Ties go to the lowest index, NaN logits are
+ * skipped, no valid logit gives 0. ws: 16 bytes, 8-byte aligned, zero before the first call (every
+ * call leaves it zero); one ws per decoder that may run concurrently.
+ * Replaces: torch.rms_norm_res + torch.exl3_gemm + torch.argmax_advance,
+ * src/ucode/ampstein/graphdec.uc:219-240 (kernel amp_argmax_advance_kernel,
+ * src/torch/amp_kernels.cu:823-901, same tie and NaN rules); the reference has no fused form.
+ */
+int amp_exl3_lm_head_argmax(const void* x, const void* res, const void* norm_w, float eps, void* y,
+                            const void* trellis, void* logits, const void* suh, const void* svh,
+                            int k, int n, int K, int cb, int vocab,
+                            void* ids, void* pos, void* log, long long log_cap, void* ws, cudaStream_t stream);
 int amp_exl3_mgemm_rms_norm_res(const void* x, const void* res, const void* norm_w, float eps, void* y,
                                 const void* trellis_ptrs, void* C, const void* suh_ptrs, const void* svh_ptrs,
                                 int num, int m, int k, int width, int K, int cb, int c_fp32,

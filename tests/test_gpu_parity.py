@@ -439,6 +439,45 @@ def test_linears_with_the_residual_norm_in_their_prologue(amp, oracle, m, k, K, 
         check_close(o.float().cpu().numpy(), oracle.linear(n_ref, tr, s_u, s_v, cb, fp32_out=True))
 
 
+def test_lm_head_with_norm_argmax_and_state_advance(amp, oracle):
+    """The end of a greedy decode step in one launch against the oracle's sequence (rms_norm_res,
+    linear, argmax with ties to the lowest index): three steps in a row on one state (the key and the
+    block counter in ws reset themselves), a vocabulary shorter than the padded width, a log too short
+    for the last position."""
+    k, n, K, vocab = 1024, 4096, 6, 4000
+    trellis, suh, svh, _ = make_linear(k, n, K, seed=9800)
+    rng = np.random.default_rng(98)
+    w = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float16)
+    t, su, sv, wd = dev(trellis), dev(suh), dev(svh), dev(w)
+    ids = torch.tensor([7], dtype=torch.int64, device="cuda")
+    pos = torch.tensor([0], dtype=torch.int64, device="cuda")
+    log = torch.full((2,), -1, dtype=torch.int64, device="cuda")
+    ws = torch.zeros(4, dtype=torch.int32, device="cuda")
+    logits = torch.empty((1, n), dtype=torch.float16, device="cuda")
+    y = torch.empty((1, k), dtype=torch.float16, device="cuda")
+    prev, want_log = 7, []
+    for step in range(3):
+        x = rng.standard_normal((1, k)).astype(np.float16)
+        res = (0.5 * rng.standard_normal((1, k))).astype(np.float16)
+        amp.lm_head_argmax(dev(x), dev(res), wd, 1e-5, y, t, logits, su, sv, ids, pos, log, ws, vocab=vocab)
+        torch.cuda.synchronize()
+        y_ref, n_ref = oracle.rms_norm_res(x, res, w, 1e-5)
+        assert np.array_equal(host16(y), y_ref.view(np.uint16))
+        got = logits.cpu().numpy()
+        check_close(got, oracle.linear(n_ref, trellis, suh, svh, 0, fp32_out=True))
+        valid = got[0, :vocab].astype(np.float32)
+        assert int(ids.item()) == int(np.argmax(valid))            # numpy: first occurrence of the maximum
+        assert int(pos.item()) == step + 1
+        want_log.append(prev)
+        prev = int(ids.item())
+        assert ws.cpu().tolist() == [0, 0, 0, 0]
+    assert log.cpu().tolist() == want_log[:2]                      # the third write fell outside the log
+    # ties: equal logits resolve to the lowest index (svh = 0 makes every logit +0)
+    amp.lm_head_argmax(dev(x), dev(res), wd, 1e-5, y, t, logits, su, torch.zeros_like(sv), ids, pos, log, ws, vocab=vocab)
+    torch.cuda.synchronize()
+    assert int(ids.item()) == 0 and int(pos.item()) == 4
+
+
 @pytest.mark.parametrize("rows", [200, 1100])
 def test_gemm_recon_next_to_gemm(amp, oracle, rows):
     """The many-rows operator against the in-place operator on the same input, at the two row
