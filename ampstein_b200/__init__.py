@@ -20,6 +20,9 @@ from .exl3 import (  # noqa: F401
     moe_coop,
     moe_coop_ctr_len,
     ptr_array,
+    rms_norm_res,
+    silu_mul,
+    argmax_advance,
 )
 
-__all__ = ["exl3_gemm", "exl3_gemm_recon", "exl3_gemm_rms_norm_res", "exl3_gemm_silu_mul", "exl3_reconstruct", "exl3_reconstruct_batch", "exl3_reconstruct_had", "had_r_128", "lm_head_argmax", "mgemm", "mgemm_rms_norm_res", "moe_coop", "moe_coop_ctr_len", "ptr_array"]
+__all__ = ["exl3_gemm", "exl3_gemm_recon", "exl3_gemm_rms_norm_res", "exl3_gemm_silu_mul", "exl3_reconstruct", "exl3_reconstruct_batch", "exl3_reconstruct_had", "had_r_128", "lm_head_argmax", "mgemm", "mgemm_rms_norm_res", "moe_coop", "moe_coop_ctr_len", "ptr_array", "rms_norm_res", "silu_mul", "argmax_advance"]

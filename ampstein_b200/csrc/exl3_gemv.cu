@@ -314,7 +314,15 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
         const long need = (per + 1 + 3) / 4 * 4;
         if (need < xgroups) xgroups = (int) need;
     }
-    L = gemv_smem_layout(K, m, xgroups, cluster, A.arin.N != 0);
+    // fused norm, one row that fits: y and the norm weight of the row stay in shared memory (4 k bytes),
+    // as long as that keeps the planned number of CTAs on an SM
+    int rowbuf = 0;
+    if (fused_norm && m == 1 && !tc && ((uintptr_t) A.norm_w & 15) == 0)
+    {
+        const int want = 4 * k;
+        if (smem_per_sm / (gemv_smem_layout(K, m, xgroups, cluster, 0, want).total + 1024) >= ctas_per_sm) rowbuf = want;
+    }
+    L = gemv_smem_layout(K, m, xgroups, cluster, A.arin.N != 0, rowbuf);
     if (tc)
     {
         xgroups = tc_xg;
@@ -343,7 +351,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     P.ar = A.ar;
     P.arin = A.arin;
     P.x2 = (const __half*) A.x2;
-    P.norm_w = (const __half*) A.norm_w; P.y = (__half*) A.y; P.eps = A.eps;
+    P.norm_w = (const __half*) A.norm_w; P.y = (__half*) A.y; P.eps = A.eps; P.rowbuf = rowbuf;
     P.am_key = nullptr; P.am_count = nullptr; P.am_ids = P.am_pos = P.am_log = nullptr; P.am_log_cap = 0; P.am_vocab = 0;
     if (A.am_ws)
     {

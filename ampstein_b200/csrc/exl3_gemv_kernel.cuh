@@ -234,6 +234,7 @@ struct GemvParams
     const __half* norm_w;       // GIN == 4: RMSNorm weight (k)
     __half* y;                  // GIN == 4: updated residual stream fp16(x + x2), (m, k), written by the first CTA
     float eps;
+    int rowbuf;                 // GIN == 4: 4 k bytes of shared memory for y and norm_w of one row (m == 1), or 0
     // GIN == 4, one row, fp16 output: greedy next-token pick over the output (the lm_head's logits)
     // and the decode-state advance, done by the CTAs that finish the column blocks
     unsigned long long* am_key; // best (ordered value << 32 | ~index) so far; zero between launches
@@ -261,7 +262,7 @@ __host__ __device__ constexpr int gemv_xpitch(int xgroups) { return xgroups * 64
 
 // xrows: rows of x~ / partial sums kept (the batch size m)
 // stage: reserve room for the gathered input of one chunk (split exchange), fp16 [xrows][xgroups * 64]
-__host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int xgroups, int cluster = 0, int stage = 0)
+__host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int xgroups, int cluster = 0, int stage = 0, int extra = 0)
 {
     GemvSmem L;
     L.part = 0;                                             // [xrows][128] fp32: the finished block
@@ -272,7 +273,7 @@ __host__ __device__ inline GemvSmem gemv_smem_layout(int K, int xrows, int xgrou
     L.ring = (L.ring + 127) & ~127;
     L.xchg = L.ring + GEMV_WARPS * gemv_stages(K) * gemv_slot_bytes(K);   // [cluster][xrows][128] fp32, filled by the cluster's CTAs
     L.stage = L.xchg + cluster * xrows * 128 * 4;
-    L.total = L.stage + (stage ? xrows * xgroups * 128 : 0);
+    L.total = L.stage + (stage ? xrows * xgroups * 128 : 0) + extra;     // extra: row-resident vectors of the fused norm
     return L;
 }
 
@@ -647,7 +648,7 @@ __global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 3))
 void exl3_gemv_kernel(const GemvParams P)
 {
     extern __shared__ __align__(128) unsigned char smem[];
-    const GemvSmem L = gemv_smem_layout(K, P.m, P.xgroups, P.cluster, GIN == 1);
+    const GemvSmem L = gemv_smem_layout(K, P.m, P.xgroups, P.cluster, GIN == 1, GIN == 4 ? P.rowbuf : 0);
     const int XPITCH = gemv_xpitch(P.xgroups);
     const int XG = P.xgroups;
     float* part = reinterpret_cast<float*>(smem + L.part);
@@ -875,27 +876,84 @@ void exl3_gemv_kernel(const GemvParams P)
             for (int j = 0; j < S - 1; ++j) issue();
             started = true;
         }
-        if (!waited) { if (P.pdl) pdl_wait(); waited = true; }
         const int cnt = k >> 2;
+        if (P.rowbuf)
+        {
+            // One row, short enough to sit in shared memory: the static vectors (norm weight, suh of
+            // the first source) are copied in BEFORE the wait for the producer, the row itself takes a
+            // single batch of loads after it, and the x~ passes then read everything from shared
+            // memory: one L2 round trip on the critical path, like the plain kernel.
+            half4* s_y = reinterpret_cast<half4*>(smem + L.total - P.rowbuf);
+            const uint32_t s_w = smem_u32(s_y) + k * 2;
+            for (int c = t; c < cnt / 2; c += GEMV_THREADS) cp_async16_s(s_w + c * 16, P.norm_w + c * 8);
+            cp_async_commit();
+            if (!waited) { if (P.pdl) pdl_wait(); waited = true; }
+            float acc = 0.0f;
+            for (int c0 = t; c0 < cnt; c0 += 8 * GEMV_THREADS)
+            {
+                half4 xv[8], rv[8];
+                #pragma unroll
+                for (int j = 0; j < 8; ++j)
+                {
+                    const int c = c0 + j * GEMV_THREADS;
+                    if (c < cnt) { xv[j] = reinterpret_cast<const half4*>(P.x)[c]; rv[j] = reinterpret_cast<const half4*>(P.x2)[c]; }
+                }
+                #pragma unroll
+                for (int j = 0; j < 8; ++j)
+                {
+                    const int c = c0 + j * GEMV_THREADS;
+                    if (c >= cnt) continue;
+                    half4 h;
+                    h.x = __floats2half2_rn(__low2float(xv[j].x) + __low2float(rv[j].x), __high2float(xv[j].x) + __high2float(rv[j].x));
+                    h.y = __floats2half2_rn(__low2float(xv[j].y) + __low2float(rv[j].y), __high2float(xv[j].y) + __high2float(rv[j].y));
+                    s_y[c] = h;
+                    if (cta == 0) reinterpret_cast<half4*>(P.y)[c] = h;
+                    const float2 v0 = __half22float2(h.x), v1 = __half22float2(h.y);
+                    acc += v0.x * v0.x + v0.y * v0.y;
+                    acc += v1.x * v1.x + v1.y * v1.y;
+                }
+            }
+            #pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) s_red[0][warp] = acc;
+            cp_async_wait_n<0>();                       // the norm weight (and the first weights: long since there)
+        }
+        else
+        {
+        if (!waited) { if (P.pdl) pdl_wait(); waited = true; }
         for (int b = 0; b < m; ++b)
         {
             const __half* xr = P.x + (size_t) b * k;
             const __half* rr = P.x2 + (size_t) b * k;
             float acc = 0.0f;
-            for (int c = t; c < cnt; c += GEMV_THREADS)
+            for (int c0 = t; c0 < cnt; c0 += 4 * GEMV_THREADS)
             {
-                const half4 xv = reinterpret_cast<const half4*>(xr)[c], rv = reinterpret_cast<const half4*>(rr)[c];
-                half4 h;
-                h.x = __floats2half2_rn(__low2float(xv.x) + __low2float(rv.x), __high2float(xv.x) + __high2float(rv.x));
-                h.y = __floats2half2_rn(__low2float(xv.y) + __low2float(rv.y), __high2float(xv.y) + __high2float(rv.y));
-                if (cta == 0) reinterpret_cast<half4*>(P.y + (size_t) b * k)[c] = h;
-                const float2 v0 = __half22float2(h.x), v1 = __half22float2(h.y);
-                acc += v0.x * v0.x + v0.y * v0.y;
-                acc += v1.x * v1.x + v1.y * v1.y;
+                // four chunks per thread in flight: one after the other they are a chain of L2 round trips
+                half4 xv[4], rv[4];
+                #pragma unroll
+                for (int j = 0; j < 4; ++j)
+                {
+                    const int c = c0 + j * GEMV_THREADS;
+                    if (c < cnt) { xv[j] = reinterpret_cast<const half4*>(xr)[c]; rv[j] = reinterpret_cast<const half4*>(rr)[c]; }
+                }
+                #pragma unroll
+                for (int j = 0; j < 4; ++j)
+                {
+                    const int c = c0 + j * GEMV_THREADS;
+                    if (c >= cnt) continue;
+                    half4 h;
+                    h.x = __floats2half2_rn(__low2float(xv[j].x) + __low2float(rv[j].x), __high2float(xv[j].x) + __high2float(rv[j].x));
+                    h.y = __floats2half2_rn(__low2float(xv[j].y) + __low2float(rv[j].y), __high2float(xv[j].y) + __high2float(rv[j].y));
+                    if (cta == 0) reinterpret_cast<half4*>(P.y + (size_t) b * k)[c] = h;
+                    const float2 v0 = __half22float2(h.x), v1 = __half22float2(h.y);
+                    acc += v0.x * v0.x + v0.y * v0.y;
+                    acc += v1.x * v1.x + v1.y * v1.y;
+                }
             }
             #pragma unroll
             for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (lane == 0) s_red[b][warp] = acc;
+        }
         }
         __syncthreads();
         if (t < m)
@@ -1135,6 +1193,26 @@ void exl3_gemv_kernel(const GemvParams P)
                 // normalised input: n = fp16(fp16(x + r) * scale) * w (fp16), then the usual scale and rotation
                 int b = 0, jb = warp;
                 while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
+                if (P.rowbuf)
+                {
+                    // y and the norm weight come from shared memory; only suh (this source's) is loaded
+                    const half4* s_y = reinterpret_cast<const half4*>(smem + L.total - P.rowbuf);
+                    const half4* s_wv = s_y + (k >> 2);
+                    const float sc = s_scale[0];
+                    for (; jb < nblk; jb += GEMV_WARPS)
+                    {
+                        const int c = cg0 * 16 + jb * 32 + lane;               // 4-half chunk of the row
+                        const half4 vs1 = *reinterpret_cast<const half4*>(suh + (size_t) c * 4);
+                        const half4 h = s_y[c], wv = s_wv[c];
+                        half4 v;
+                        v.x = __hmul2(__floats2half2_rn(__low2float(h.x) * sc, __high2float(h.x) * sc), wv.x);
+                        v.y = __hmul2(__floats2half2_rn(__low2float(h.y) * sc, __high2float(h.y) * sc), wv.y);
+                        v.x = __hmul2(v.x, vs1.x);
+                        v.y = __hmul2(v.y, vs1.y);
+                        had_store(0, jb, __low2float(v.x), __high2float(v.x), __low2float(v.y), __high2float(v.y));
+                    }
+                }
+                else
                 do
                 {
                     constexpr int TB = 3;

@@ -221,6 +221,44 @@ def exl3_gemm_rms_norm_res(x, res, norm_w, eps, y, B, C, suh, svh, mul1=False, m
     return C
 
 
+def rms_norm_res(x, res, norm_w, eps, y=None, n=None):
+    """Stand-alone residual add + RMSNorm (the arithmetic the fused entries apply): returns (y, n),
+    y = fp16(x + res), n = fp16(y * rsqrt(mean(y^2) + eps)) * norm_w (reference: torch.rms_norm_res,
+    src/torch/amp_kernels.cu:279-360)."""
+    y = torch.empty_like(x) if y is None else y
+    n = torch.empty_like(x) if n is None else n
+    _check_cuda("rms_norm_res", x, res, norm_w, y, n)
+    if any(t.dtype != torch.float16 for t in (x, res, norm_w, y, n)) or x.shape != res.shape or norm_w.numel() != x.shape[-1]:
+        raise TypeError("rms_norm_res: float16 tensors of one shape, norm_w one value per column")
+    dim = x.shape[-1]
+    with torch.cuda.device(x.device):
+        _lib.call("amp_b200_rms_norm_res", x.data_ptr(), res.data_ptr(), norm_w.data_ptr(), y.data_ptr(), n.data_ptr(),
+                  x.numel() // dim, dim, float(eps), _stream(x))
+    return y, n
+
+
+def silu_mul(g, u, out=None):
+    """Stand-alone fp16(silu(g) * u) with fp32 math (reference: torch.silu_mul, src/torch/amp_kernels.cu:235-271)."""
+    out = torch.empty_like(g) if out is None else out
+    _check_cuda("silu_mul", g, u, out)
+    if g.dtype != torch.float16 or u.dtype != torch.float16 or out.dtype != torch.float16 or g.shape != u.shape:
+        raise TypeError("silu_mul: float16 tensors of one shape")
+    with torch.cuda.device(g.device):
+        _lib.call("amp_b200_silu_mul", g.data_ptr(), u.data_ptr(), out.data_ptr(), g.numel(), _stream(g))
+    return out
+
+
+def argmax_advance(logits, ids, pos, log, ws):
+    """Stand-alone greedy pick + state advance (reference: torch.argmax_advance,
+    src/torch/amp_kernels.cu:823-960): log[pos] = ids; ids = argmax(logits); pos += 1."""
+    _check_cuda("argmax_advance", logits, ids, pos, log, ws)
+    if logits.dtype != torch.float16 or ids.dtype != torch.int64 or pos.dtype != torch.int64 or log.dtype != torch.int64:
+        raise TypeError("argmax_advance: logits float16; ids, pos, log int64")
+    with torch.cuda.device(logits.device):
+        _lib.call("amp_b200_argmax_advance", logits.data_ptr(), logits.numel(), ids.data_ptr(), pos.data_ptr(), log.data_ptr(),
+                  log.numel(), ws.data_ptr(), _stream(logits))
+
+
 def lm_head_argmax(x, res, norm_w, eps, y, B, logits, suh, svh, ids, pos, log, ws, vocab=None, mul1=False, mcg=False):
     """The end of a greedy decode step in ONE launch: y = fp16(x + res); logits (1, n) fp16 = lm_head of
     RMSNorm(y) * norm_w; ids = argmax(logits[:vocab]) after log[pos] = ids, pos += 1 (reference:

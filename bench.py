@@ -605,7 +605,7 @@ def measure_moe(steps, warmup, T):
                      "kernel": "exl3_gemv_kernel (grouped modes)", "bytes_per_launch": int(byt) // 2, "traffic": None}}
 
 
-def measure_gemv(steps, warmup, shape, m, tmem=False, mul1=False, silu_mul=False):
+def measure_gemv(steps, warmup, shape, m, tmem=False, mul1=False, silu_mul=False, norm=False):
     """One decode GEMV shape on its own (k x n at K bits, m rows): as many distinct copies of the
     matrix as it takes to exceed L2 twice over, one launch per copy, all in one CUDA graph."""
     import torch
@@ -622,7 +622,13 @@ def measure_gemv(steps, warmup, shape, m, tmem=False, mul1=False, silu_mul=False
     suh, svh = sgn(k), (sgn(n) / (1.2437 * math.sqrt(k))).to(torch.float16)
     x = torch.randn((m, k), device=dev, generator=g).to(torch.float16)
     y = torch.empty((m, n), dtype=torch.float16, device=dev)
-    if silu_mul:
+    if norm:
+        x2 = (0.5 * torch.randn((m, k), device=dev, generator=g)).to(torch.float16)
+        nw = (1.0 + 0.05 * torch.randn((k,), device=dev, generator=g)).to(torch.float16)
+        yy = torch.empty((m, k), dtype=torch.float16, device=dev)
+        graph = DecodeGraph(lambda: [amp.exl3_gemm_rms_norm_res(x, x2, nw, 1e-5, yy, t, y, suh, svh, mul1=mul1) for t in mats],
+                            warmup=max(warmup, 3))
+    elif silu_mul:
         x2 = torch.randn((m, k), device=dev, generator=g).to(torch.float16)
         graph = DecodeGraph(lambda: [amp.exl3_gemm_silu_mul(x, x2, t, y, suh, svh, mul1=mul1) for t in mats], warmup=max(warmup, 3))
     else:
@@ -645,12 +651,132 @@ def measure_gemv(steps, warmup, shape, m, tmem=False, mul1=False, silu_mul=False
         "config": {"workload": "one GEMV shape, %d distinct weight copies per graph (%.0f MB, larger than L2)" % (copies, copies * wbytes / 1e6),
                    "kernel_form": "tensor memory (tcgen05)" if tmem else "mma.sync",
                    "codebook": "mul1" if mul1 else "default",
-                   "input": "silu(gate) * up formed in the prologue" if silu_mul else "plain",
+                   "input": "RMSNorm(x + res) * w formed in the prologue" if norm else ("silu(gate) * up formed in the prologue" if silu_mul else "plain"),
                    "timing": "median of %d blocks of %d graph replays" % (nblk, steps)},
         "gpu_launches": copies * steps, "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
                      "peak_source": "measured (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback",
                      "kernel": "exl3_gemv_tc_kernel" if tmem else "exl3_gemv_kernel", "bytes_per_launch": byt, "traffic": None}}
+
+
+def measure_step_with_neighbours(steps, warmup, n_layers=0):
+    """The decode step of the 8B-shaped stack WITH the element-wise kernels that sit between its
+    linears (src/ucode/ampstein/graphdec.uc:151-240; attention itself stays outside): residual add +
+    RMSNorm in front of q|k|v and gate|up, silu(gate) * up in front of down, final norm, lm_head and
+    greedy pick. Three CUDA graphs over the same weights: the linears alone (the headline step), the
+    step with its neighbours as separate launches, and with them folded into the linears."""
+    import torch
+    import ampstein_b200 as amp
+    from ampstein_b200.models import DecodeGraph, Multi, Sliced
+    S = dict(STACKS["decode"])
+    if n_layers:
+        S["layers"] = n_layers
+    dev = torch.device("cuda", 0)
+    layers, head = build_stack(torch, dev, 1234, S)
+    H, I, nl = S["hidden"], S["ffn"], len(layers)
+    f16 = dict(dtype=torch.float16, device=dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3)
+    norm_w = [(1.0 + 0.05 * torch.randn((2, H), device=dev, generator=gen)).to(torch.float16) for _ in range(nl + 1)]
+    q, k_, v = (torch.empty((1, 1, n), **f16) for n in (H, S["kv"], S["kv"]))
+    gu_out = torch.empty((2, 1, I), **f16)
+    hbuf = [torch.empty((1, 1, H), **f16) for _ in range(2)]            # residual stream, ping-pong
+    r = torch.empty((1, 1, H), **f16)
+    a = torch.empty((1, I), **f16)
+    o_out, d_out = torch.empty((1, H), **f16), torch.zeros((1, H), **f16)
+    logits = torch.empty((1, head.out_features), **f16)
+    ids, pos = torch.zeros(1, dtype=torch.int64, device=dev), torch.zeros(1, dtype=torch.int64, device=dev)
+    log = torch.zeros(1 << 20, dtype=torch.int64, device=dev)
+    ws = torch.zeros(4, dtype=torch.int32, device=dev)
+    qkv = [Sliced([L["q"], L["k"], L["v"]], [q, k_, v]) for L in layers]
+    gu = [Multi([L["gate"], L["up"]], gu_out) for L in layers]
+    eps = 1e-5
+    h0 = torch.randn((1, 1, H), device=dev, generator=gen).to(torch.float16)
+
+    def linears_only():
+        x = hbuf[0]
+        for i, L in enumerate(layers):
+            qkv[i].run(x)
+            L["o"].forward(q[0], o_out)
+            gu[i].run(o_out.view(1, 1, H))
+            L["down"].forward(gu_out[0], d_out)
+            x = d_out.view(1, 1, H)
+        head.forward(x[0], logits)
+
+    def unfused():
+        cur = 0
+        for i, L in enumerate(layers):
+            amp.rms_norm_res(hbuf[cur], d_out.view(1, 1, H), norm_w[i][0], eps, hbuf[cur], r)
+            qkv[i].run(r)
+            L["o"].forward(q[0], o_out)
+            amp.rms_norm_res(hbuf[cur], o_out.view(1, 1, H), norm_w[i][1], eps, hbuf[cur], r)
+            gu[i].run(r)
+            amp.silu_mul(gu_out[0], gu_out[1], a)
+            L["down"].forward(a, d_out)
+        amp.rms_norm_res(hbuf[cur], d_out.view(1, 1, H), norm_w[nl][0], eps, hbuf[cur], r)
+        head.forward(r[0], logits)
+        amp.argmax_advance(logits, ids, pos, log, ws)
+
+    def mixed(f_norm, f_act, f_tail):
+        def fn():
+            cur = 0
+            for i, L in enumerate(layers):
+                if f_norm:
+                    qkv[i].run_norm(hbuf[cur], d_out.view(1, 1, H), norm_w[i][0], eps, hbuf[1 - cur])
+                    cur = 1 - cur
+                else:
+                    amp.rms_norm_res(hbuf[cur], d_out.view(1, 1, H), norm_w[i][0], eps, hbuf[cur], r)
+                    qkv[i].run(r)
+                L["o"].forward(q[0], o_out)
+                if f_norm:
+                    gu[i].run_norm(hbuf[cur], o_out.view(1, 1, H), norm_w[i][1], eps, hbuf[1 - cur])
+                    cur = 1 - cur
+                else:
+                    amp.rms_norm_res(hbuf[cur], o_out.view(1, 1, H), norm_w[i][1], eps, hbuf[cur], r)
+                    gu[i].run(r)
+                if f_act:
+                    L["down"].forward_silu_mul(gu_out[0], gu_out[1], d_out)
+                else:
+                    amp.silu_mul(gu_out[0], gu_out[1], a)
+                    L["down"].forward(a, d_out)
+            if f_tail:
+                amp.lm_head_argmax(hbuf[cur][0], d_out, norm_w[nl][0], eps, hbuf[1 - cur][0], head.trellis, logits, head.suh,
+                                   head.svh, ids, pos, log, ws)
+            else:
+                amp.rms_norm_res(hbuf[cur], d_out.view(1, 1, H), norm_w[nl][0], eps, hbuf[cur], r)
+                head.forward(r[0], logits)
+                amp.argmax_advance(logits, ids, pos, log, ws)
+        return fn
+
+    fused = mixed(True, True, True)
+
+    out = {}
+    picks = {}
+    forms = [("linears_only", linears_only, 4 * nl + 1), ("neighbours_separate", unfused, 7 * nl + 3),
+             ("neighbours_fused", fused, 4 * nl + 1)]
+    if os.environ.get("AMP_BENCH_STEP_PARTS"):          # which fusion buys what
+        forms += [("fused_norms_only", mixed(True, False, False), 5 * nl + 3), ("fused_activation_only", mixed(False, True, False), 6 * nl + 3),
+                  ("fused_tail_only", mixed(False, False, True), 7 * nl + 1)]
+    for name, fn, launches in forms:
+        hbuf[0].copy_(h0)
+        d_out.zero_()
+        graph = DecodeGraph(fn, warmup=max(warmup, 3))
+        hbuf[0].copy_(h0)
+        d_out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        picks[name] = int(ids.item())
+        if not torch.isfinite(logits.float()).all():
+            raise SystemExit("bench.py: non-finite logits in %s" % name)
+        ms_blk, nblk, _ = timed_blocks(torch, graph.replay, steps, graph.stream, min_s=0.5)
+        out[name] = {"ms_per_step": round(ms_blk / steps, 4), "tok_s": round(steps * 1e3 / ms_blk, 1), "launches_per_step": launches}
+        del graph
+    return {"metric": "decode step with its element-wise neighbours (8B-shaped stack, batch 1)", "unit": "ms/step",
+            "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3), "data": "synthetic", "dtype": "f16",
+            "config": {"workload": "%d layers x (norm, q|k|v, o, norm, gate|up, silu*mul, down) + final norm, lm_head, greedy pick; "
+                                   "attention not included" % nl,
+                       "same_pick": picks["neighbours_separate"] == picks["neighbours_fused"]},
+            "forms": out}
 
 
 def measure_issue():
@@ -777,10 +903,10 @@ def main():
                     help="tensor-parallel mode: how the all-reduce after o / down runs. fused (default): push and gather in the "
                          "producing GEMV's epilogue; split: the producer only pushes its partial, the consuming GEMV adds the ranks' "
                          "partials up in its prologue (measured slower); separate: a stand-alone all-reduce launch")
-    ap.add_argument("--workload", default="decode", choices=["decode", "tp5", "prefill", "moe", "gemv", "issue"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "tp5", "prefill", "moe", "gemv", "step", "issue"],
                     help="decode (default, the headline step), tp5 (the 64-layer 5-bit tensor-parallel stack), or a secondary "
-                         "one-GPU workload: the prefill GEMM / the fused decode MoE / one GEMV shape (--shape) / the "
-                         "issue-rate microbenchmark")
+                         "one-GPU workload: the prefill GEMM / the fused decode MoE / one GEMV shape (--shape) / the decode "
+                         "step with its element-wise neighbours, separate and fused (step) / the issue-rate microbenchmark")
     ap.add_argument("--shape", default="4096x229376x4", help="--workload gemv: k x n x K (rows, columns, bits per weight)")
     ap.add_argument("--batch", type=int, default=1, help="tokens per decode step (decode / tp5 workloads), 1..16")
     ap.add_argument("--tokens", type=int, default=1, choices=[1, 4, 16], help="tokens per step of --workload moe")
@@ -788,6 +914,7 @@ def main():
                     help="A/B: run the decode GEMVs on the tensor-memory (tcgen05) kernel instead of the mma.sync kernel")
     ap.add_argument("--mul1", action="store_true", help="--workload gemv: the mul1 codebook (one row then takes the int8-activation form)")
     ap.add_argument("--silu-mul", action="store_true", help="--workload gemv: the down projection with silu(gate) * up folded into its prologue")
+    ap.add_argument("--norm", action="store_true", help="--workload gemv: the linear with the residual add + RMSNorm folded into its prologue")
     ap.add_argument("--no-int8", action="store_true", help="--workload gemv --mul1: keep the fp16 kernel (A/B)")
     ap.add_argument("--separate", action="store_true",
                     help="--workload prefill: seven separate GEMM calls instead of the q|k|v and gate|up bundles")
@@ -807,7 +934,7 @@ def main():
         args.warmup = min(args.warmup, 1)
         run_reference(args)
         return
-    if args.workload in ("prefill", "moe", "gemv", "issue"):
+    if args.workload in ("prefill", "moe", "gemv", "step", "issue"):
         import torch
         if not torch.cuda.is_available():
             raise SystemExit("bench.py: no CUDA device (the path has no CPU fallback)")
@@ -815,6 +942,8 @@ def main():
             print(json.dumps(measure_prefill(args.steps, args.warmup, not args.separate)), flush=True)
         elif args.workload == "moe":
             print(json.dumps(measure_moe(args.steps, args.warmup, args.tokens)), flush=True)
+        elif args.workload == "step":
+            print(json.dumps(measure_step_with_neighbours(args.steps, args.warmup, args.layers)), flush=True)
         elif args.workload == "gemv":
             try:
                 shape = tuple(int(v) for v in args.shape.lower().split("x"))
@@ -824,7 +953,7 @@ def main():
             if args.no_int8:
                 from ampstein_b200 import _lib
                 _lib.lib().amp_exl3_set_int8_gemv(0, 0)
-            print(json.dumps(measure_gemv(args.steps, args.warmup, shape, args.batch, args.tmem_gemv, args.mul1, args.silu_mul)), flush=True)
+            print(json.dumps(measure_gemv(args.steps, args.warmup, shape, args.batch, args.tmem_gemv, args.mul1, args.silu_mul, args.norm)), flush=True)
         else:
             print(json.dumps({"metric": "scheduler cycles per 8 decoded weights and lane (K=4 mix)", "unit": "cycles",
                               "by_warps_per_scheduler": measure_issue()}), flush=True)

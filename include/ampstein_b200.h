@@ -200,6 +200,20 @@ int amp_exl3_gemv_rms_norm_res(const void* x, const void* res, const void* norm_
                                const void* trellis, void* C, const void* suh, const void* svh,
                                int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream);
 /*
+ * Stand-alone forms of the three element-wise kernels the fused entry points above absorb (residual
+ * add + RMSNorm, gated activation, greedy pick + state advance), with the arithmetic of the fused
+ * forms. Provided so that fused and unfused sequences can be compared inside one CUDA graph; an
+ * integrator keeps the reference's own kernels (amp_rms_norm_res_fp16, amp_silu_mul_fp16,
+ * amp_argmax_advance_fp16, src/torch/amp_kernels.cu:253-271, 362-390, 903-960) or switches to the
+ * fused entries. y may alias x here (one CTA per row). ws of argmax_advance: 16 bytes, zero before the
+ * first call.
+ */
+int amp_b200_rms_norm_res(const void* x, const void* r, const void* w, void* y, void* n, long rows, int dim, float eps,
+                          cudaStream_t stream);
+int amp_b200_silu_mul(const void* g, const void* u, void* out, long count, cudaStream_t stream);
+int amp_b200_argmax_advance(const void* logits, int n, void* ids, void* pos, void* log, long long log_cap, void* ws,
+                            cudaStream_t stream);
+/*
  * The last three launches of a greedy decode step in one: y = fp16(x + res), logits (1, n) fp16 = the
  * lm_head of RMSNorm(y) * norm_w, then argmax over the first `vocab` logits and the state advance
  * log[pos] = ids; ids = argmax; pos += 1 (ids, pos: one int64 each; log: int64 array of log_cap

@@ -439,6 +439,46 @@ def test_linears_with_the_residual_norm_in_their_prologue(amp, oracle, m, k, K, 
         check_close(o.float().cpu().numpy(), oracle.linear(n_ref, tr, s_u, s_v, cb, fp32_out=True))
 
 
+def test_stand_alone_neighbour_kernels(amp, oracle):
+    """The stand-alone residual norm, gated activation and greedy pick against the oracle / numpy, and
+    the fused sequence against the unfused one built from them: same logits bits, same pick."""
+    k, I, n, K = 1024, 2048, 2048, 4
+    rng = np.random.default_rng(99)
+    x = rng.standard_normal((2, k)).astype(np.float16)
+    res = (0.5 * rng.standard_normal((2, k))).astype(np.float16)
+    w = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float16)
+    y, nn = amp.rms_norm_res(dev(x), dev(res), dev(w), 1e-5)
+    y_ref, n_ref = oracle.rms_norm_res(x, res, w, 1e-5)
+    assert np.array_equal(host16(y), y_ref.view(np.uint16))
+    d = np.abs(nn.float().cpu().numpy() - n_ref.astype(np.float32))
+    assert np.max(d) <= 2e-3 * np.max(np.abs(n_ref.astype(np.float32))) and np.mean(d > 0) < 0.01     # scale may differ in its last bit
+    g = rng.standard_normal((2, I)).astype(np.float16)
+    u = rng.standard_normal((2, I)).astype(np.float16)
+    a = amp.silu_mul(dev(g), dev(u))
+    d = np.abs(a.float().cpu().numpy() - oracle.silu_mul(g, u).astype(np.float32))
+    assert np.max(d) <= 2e-3 and np.mean(d > 0) < 0.01                                                 # __expf against exp
+    # unfused tail (norm, lm_head, pick) against the fused launch: identical logits and pick
+    trellis, suh, svh, _ = make_linear(k, n, K, seed=9900)
+    t, su, sv = dev(trellis), dev(suh), dev(svh)
+    mk = lambda v: torch.tensor([v], dtype=torch.int64, device="cuda")
+    ids1, pos1, ids2, pos2 = mk(3), mk(5), mk(3), mk(5)
+    log1 = torch.zeros(8, dtype=torch.int64, device="cuda"); log2 = torch.zeros(8, dtype=torch.int64, device="cuda")
+    ws1 = torch.zeros(4, dtype=torch.int32, device="cuda"); ws2 = torch.zeros(4, dtype=torch.int32, device="cuda")
+    x1, r1 = dev(x[:1]), dev(res[:1])
+    _, n1 = amp.rms_norm_res(x1, r1, dev(w), 1e-5)
+    lg1 = torch.empty((1, n), dtype=torch.float16, device="cuda")
+    amp.exl3_gemm(n1, t, lg1, su, sv)
+    amp.argmax_advance(lg1, ids1, pos1, log1, ws1)
+    lg2 = torch.empty((1, n), dtype=torch.float16, device="cuda")
+    y2 = torch.empty((1, k), dtype=torch.float16, device="cuda")
+    amp.lm_head_argmax(x1, r1, dev(w), 1e-5, y2, t, lg2, su, sv, ids2, pos2, log2, ws2)
+    torch.cuda.synchronize()
+    assert int(ids1.item()) == int(np.argmax(lg1.float().cpu().numpy()[0]))
+    assert int(ids2.item()) == int(np.argmax(lg2.float().cpu().numpy()[0]))
+    assert torch.equal(log1, log2) and int(pos1.item()) == int(pos2.item()) == 6
+    check_close(lg2.cpu().numpy(), lg1.float().cpu().numpy())
+
+
 def test_lm_head_with_norm_argmax_and_state_advance(amp, oracle):
     """The end of a greedy decode step in one launch against the oracle's sequence (rms_norm_res,
     linear, argmax with ties to the lowest index): three steps in a row on one state (the key and the
