@@ -7,6 +7,8 @@ raises if the shared library is missing or the tensors are not on a CUDA device.
 from . import _lib  # noqa: F401
 from .exl3 import (  # noqa: F401
     exl3_gemm,
+    exl3_gemm_add_res,
+    exl3_gemm_normed,
     exl3_gemm_recon,
     exl3_gemm_rms_norm_res,
     exl3_gemm_silu_mul,
@@ -16,6 +18,7 @@ from .exl3 import (  # noqa: F401
     had_r_128,
     lm_head_argmax,
     mgemm,
+    mgemm_normed,
     mgemm_rms_norm_res,
     moe_coop,
     moe_coop_ctr_len,
@@ -25,4 +28,4 @@ from .exl3 import (  # noqa: F401
     argmax_advance,
 )
 
-__all__ = ["exl3_gemm", "exl3_gemm_recon", "exl3_gemm_rms_norm_res", "exl3_gemm_silu_mul", "exl3_reconstruct", "exl3_reconstruct_batch", "exl3_reconstruct_had", "had_r_128", "lm_head_argmax", "mgemm", "mgemm_rms_norm_res", "moe_coop", "moe_coop_ctr_len", "ptr_array", "rms_norm_res", "silu_mul", "argmax_advance"]
+__all__ = ["exl3_gemm", "exl3_gemm_add_res", "exl3_gemm_normed", "exl3_gemm_recon", "exl3_gemm_rms_norm_res", "exl3_gemm_silu_mul", "exl3_reconstruct", "exl3_reconstruct_batch", "exl3_reconstruct_had", "had_r_128", "lm_head_argmax", "mgemm", "mgemm_normed", "mgemm_rms_norm_res", "moe_coop", "moe_coop_ctr_len", "ptr_array", "rms_norm_res", "silu_mul", "argmax_advance"]

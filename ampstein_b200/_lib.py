@@ -42,6 +42,9 @@ SIGNATURES = {
     "amp_b200_rms_norm_res": [_vp, _vp, _vp, _vp, _vp, ctypes.c_long, _i, ctypes.c_float, _vp],
     "amp_b200_silu_mul": [_vp, _vp, _vp, ctypes.c_long, _vp],
     "amp_b200_argmax_advance": [_vp, _i, _vp, _vp, _vp, ctypes.c_longlong, _vp, _vp],
+    "amp_exl3_gemv_add_res": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "amp_exl3_gemv_normed": [_vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "amp_exl3_mgemm_normed": [_vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "amp_exl3_set_gemm_pair": [_i],
     "amp_exl3_set_int8_gemv": [_i, _i],
     "amp_exl3_set_gemm_relay_release": [_i],

@@ -201,19 +201,27 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     const DevInfo& D = dev_info(dev);
 
     const int MB = m <= 8 ? 1 : 2;
-    const bool tc = !A.mode && m <= TCV_MAX_M && g_gemv_tc && !A.arin.N && !A.ar.push_only && !A.x2;
+    const bool tc = !A.mode && m <= TCV_MAX_M && g_gemv_tc && !A.arin.N && !A.ar.push_only && !A.x2 && !A.h_in && !A.norm_w;
     // five rows or more with a scratch for the rotated input: rotate once, in a launch of its own
-    const bool fused_norm = A.norm_w != nullptr;
+    const bool norm_producer = A.h_in != nullptr;                       // split norm, producer side
+    const bool norm_consumer = A.norm_w != nullptr && A.ssq != nullptr && !A.x2;   // ... consumer side
+    AMP_REQUIRE(!norm_producer || (!A.mode && !A.arin.N && !A.ar.N && !A.tables && !A.c_fp32 && A.y && A.ssq && !A.norm_w && !A.x2 &&
+                                   (((uintptr_t) A.h_in | (uintptr_t) A.y) & 7) == 0),
+                "exl3_gemv: the residual-adding form takes a plain launch with fp16 output, h, y and ssq");
+    AMP_REQUIRE(!norm_consumer || (!A.mode && !A.arin.N && A.x && ((uintptr_t) A.norm_w & 7) == 0),
+                "exl3_gemv: the scaled-norm form takes a plain or bundle launch with x, ssq and norm_w");
+    const bool fused_norm = A.norm_w != nullptr && !norm_consumer;
     const bool fused_act = A.x2 != nullptr && !fused_norm;
     AMP_REQUIRE(!fused_act || (!A.mode && !A.arin.N && !A.tables && ((uintptr_t) A.x2 & 7) == 0),
                 "exl3_gemv: the fused activation takes two plain 8-byte aligned inputs");
     AMP_REQUIRE(!fused_norm || (!A.mode && !A.arin.N && A.x && A.x2 && A.y && A.y != A.x && A.y != A.x2 &&
                                 (((uintptr_t) A.x2 | (uintptr_t) A.norm_w | (uintptr_t) A.y) & 7) == 0),
                 "exl3_gemv: the fused norm takes x, residual, weight and a separate output for the residual stream, 8-byte aligned");
-    const bool prerot = !tc && !A.mode && !A.arin.N && !fused_act && !fused_norm && m >= GEMV_PREROTATE_MIN_M && A.x_rot && A.x;
-    const bool i8 = !tc && !A.mode && !A.arin.N && !fused_act && !fused_norm && A.cb == 2 && m == 1 && g_int8_gemv == 2 && K <= g_int8_max_k;
+    const bool special_in = fused_act || fused_norm || norm_producer || norm_consumer;
+    const bool prerot = !tc && !A.mode && !A.arin.N && !special_in && m >= GEMV_PREROTATE_MIN_M && A.x_rot && A.x;
+    const bool i8 = !tc && !A.mode && !A.arin.N && !special_in && A.cb == 2 && m == 1 && g_int8_gemv == 2 && K <= g_int8_max_k;
     gemv_fn fn = tc ? gemv_tc_kernel_for(K, A.cb, A.ar.N != 0)
-                    : gemv_kernel_for(K, i8 ? 3 : A.cb, MB, A.mode, A.arin.N ? 1 : (fused_norm ? 4 : (fused_act ? 3 : (prerot ? 2 : 0))));
+                    : gemv_kernel_for(K, i8 ? 3 : A.cb, MB, A.mode, A.arin.N ? 1 : (norm_producer ? 5 : (norm_consumer ? 6 : (fused_norm ? 4 : (fused_act ? 3 : (prerot ? 2 : 0))))));
     if (!fn) return fail(AMP_E_UNSUPPORTED, "exl3_gemv: no kernel for K=%d cb=%d", K, A.cb);
 
     // x~ rows resident at a time: at most 16 KB of shared memory (whole segments for small
@@ -352,6 +360,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     P.arin = A.arin;
     P.x2 = (const __half*) A.x2;
     P.norm_w = (const __half*) A.norm_w; P.y = (__half*) A.y; P.eps = A.eps; P.rowbuf = rowbuf;
+    P.h_in = (const __half*) A.h_in; P.ssq = A.ssq;
     P.am_key = nullptr; P.am_count = nullptr; P.am_ids = P.am_pos = P.am_log = nullptr; P.am_log_cap = 0; P.am_vocab = 0;
     if (A.am_ws)
     {
@@ -476,6 +485,49 @@ AMP_API int amp_exl3_gemv_rms_norm_res(const void* x, const void* res, const voi
     AMP_REQUIRE(x && res && norm_w && y, "exl3_gemv_rms_norm_res: null input");
     GemvLaunch A = direct(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, 0, 0);
     A.x2 = res; A.norm_w = norm_w; A.y = y; A.eps = eps;
+    return launch_gemv(A, stream);
+}
+
+// The split form of the residual norm. Producer: y (m, n) = fp16(h + linear(x)) (the updated residual
+// stream; the linear's own output is not stored) and ssq (m, n / 128) = per-block sums of squares of y.
+// Consumer: c = linear(s) of fp16(y * rsqrt(sum(ssq row) / k + eps)) * norm_w. Unlike the one-launch
+// form nothing reads a whole row on a CTA's critical path: the producer's finishing warps hold the
+// values anyway, the consumer adds k / 128 floats. m <= 16. y may not alias h.
+AMP_API int amp_exl3_gemv_add_res(const void* x, const void* trellis, const void* suh, const void* svh,
+                                  const void* h, void* y, void* ssq, int m, int k, int n, int K, int cb, cudaStream_t stream)
+{
+    AMP_REQUIRE(h && y && ssq && h != y, "exl3_gemv_add_res: null pointer, or y aliases h");
+    GemvLaunch A = direct(x, trellis, y, suh, svh, m, k, n, K, cb, 0, 0, 0);
+    A.h_in = h; A.y = y; A.ssq = (float*) ssq;
+    return launch_gemv(A, stream);
+}
+
+AMP_API int amp_exl3_gemv_normed(const void* y, const void* ssq, const void* norm_w, float eps,
+                                 const void* trellis, void* c, const void* suh, const void* svh,
+                                 int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream)
+{
+    AMP_REQUIRE(y && ssq && norm_w, "exl3_gemv_normed: null input");
+    GemvLaunch A = direct(y, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, 0, 0);
+    A.ssq = (float*) ssq; A.norm_w = norm_w; A.eps = eps;
+    return launch_gemv(A, stream);
+}
+
+AMP_API int amp_exl3_mgemm_normed(const void* y, const void* ssq, const void* norm_w, float eps,
+                                  const void* trellis_ptrs, void* C, const void* suh_ptrs, const void* svh_ptrs,
+                                  int num, int m, int k, int width, int K, int cb, int c_fp32,
+                                  const void* c_ptrs, const void* n_stride_list, const void* had_src_list, cudaStream_t stream)
+{
+    if (num == 0 || m == 0) return 0;
+    AMP_REQUIRE(num > 0 && m >= 1 && m <= 16, "exl3_mgemm_normed: 1..16 rows");
+    AMP_REQUIRE(y && ssq && norm_w, "exl3_mgemm_normed: null input");
+    GemvLaunch A = {};
+    A.x = y; A.c = C;
+    A.t_trellis = (const long long*) trellis_ptrs; A.t_suh = (const long long*) suh_ptrs;
+    A.t_svh = (const long long*) svh_ptrs; A.t_c = (const long long*) c_ptrs;
+    A.t_stride = (const int*) n_stride_list; A.t_src = (const int*) had_src_list;
+    A.tables = 1; A.slices = num; A.width = width; A.stride = width;
+    A.m = m; A.k = k; A.K = K; A.cb = cb; A.c_fp32 = c_fp32;
+    A.ssq = (float*) ssq; A.norm_w = norm_w; A.eps = eps;
     return launch_gemv(A, stream);
 }
 

@@ -25,6 +25,9 @@ struct GemvLaunch
     const void* norm_w;  // RMSNorm weight (k) fp16
     void* y;             // (m, k) fp16: receives fp16(x + x2), the updated residual stream (must not alias x)
     float eps;
+    // split norm. Producer (h_in, y, ssq set; norm_w null): y = fp16(h_in + output), ssq (m, n / 128) block
+    // sums of squares. Consumer (ssq and norm_w set, x2 null): input = fp16(x * rsqrt(sum ssq / k + eps)) * norm_w
+    const void* h_in; float* ssq;
     // with norm_w, one row, fp16 output: argmax over the output + decode-state advance (all or none)
     void* am_ws;         // >= 16 bytes, 8-byte aligned, zero before the first launch (key + block counter)
     void* am_ids; void* am_pos; void* am_log; long long am_log_cap;

@@ -42,6 +42,19 @@ gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB, int mode, int gin)
         { exl3_gemv_kernel<AMP_GEMV_K, 1, 1, 0, 4>, exl3_gemv_kernel<AMP_GEMV_K, 1, 2, 0, 4> },
         { exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 0, 4>, exl3_gemv_kernel<AMP_GEMV_K, 2, 2, 0, 4> },
     };
+    // split norm: producer epilogue (5) and consumer prologue (6)
+    static const gemv_fn fnp[3][2] =
+    {
+        { exl3_gemv_kernel<AMP_GEMV_K, 0, 1, 0, 5>, exl3_gemv_kernel<AMP_GEMV_K, 0, 2, 0, 5> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 1, 1, 0, 5>, exl3_gemv_kernel<AMP_GEMV_K, 1, 2, 0, 5> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 0, 5>, exl3_gemv_kernel<AMP_GEMV_K, 2, 2, 0, 5> },
+    };
+    static const gemv_fn fnc[3][2] =
+    {
+        { exl3_gemv_kernel<AMP_GEMV_K, 0, 1, 0, 6>, exl3_gemv_kernel<AMP_GEMV_K, 0, 2, 0, 6> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 1, 1, 0, 6>, exl3_gemv_kernel<AMP_GEMV_K, 1, 2, 0, 6> },
+        { exl3_gemv_kernel<AMP_GEMV_K, 2, 1, 0, 6>, exl3_gemv_kernel<AMP_GEMV_K, 2, 2, 0, 6> },
+    };
     static const gemv_fn fn[3][2] =
     {
         { exl3_gemv_kernel<AMP_GEMV_K, 0, 1>, exl3_gemv_kernel<AMP_GEMV_K, 0, 2> },
@@ -59,6 +72,8 @@ gemv_fn AMP_CAT(gemv_kernel_k, AMP_GEMV_K)(int cb, int MB, int mode, int gin)
     if (cb < 0 || cb > 2 || MB < 1 || MB > 2 || mode < 0 || mode > 2) return nullptr;
     if (mode) return (MB == 1 && !gin) ? moe[cb][mode - 1] : nullptr;
     if (gin == 4) return fnn[cb][MB - 1];
+    if (gin == 5) return fnp[cb][MB - 1];
+    if (gin == 6) return fnc[cb][MB - 1];
     return gin == 3 ? fna[cb][MB - 1] : (gin == 2 ? fnr[cb][MB - 1] : (gin ? fng[cb][MB - 1] : fn[cb][MB - 1]));
 }
 

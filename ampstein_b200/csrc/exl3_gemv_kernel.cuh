@@ -234,6 +234,13 @@ struct GemvParams
     const __half* norm_w;       // GIN == 4: RMSNorm weight (k)
     __half* y;                  // GIN == 4: updated residual stream fp16(x + x2), (m, k), written by the first CTA
     float eps;
+    // GIN == 5 (producer side of the split norm): the fp16 output o of this launch is added to the
+    // residual stream: y = fp16(h + o) is written instead of o, and every finished 128-column block
+    // leaves the sum of squares of its y values in ssq[row][block] (fp32).
+    // GIN == 6 (consumer side): the input is fp16(x * rsqrt(sum(ssq[row][*]) / k + eps)) * norm_w, x = the
+    // residual stream a GIN == 5 launch wrote.
+    const __half* h_in;         // GIN == 5: (m, n) residual stream before the add
+    float* ssq;                 // GIN == 5: (m, n / 128) out; GIN == 6: (m, k / 128) in
     int rowbuf;                 // GIN == 4: 4 k bytes of shared memory for y and norm_w of one row (m == 1), or 0
     // GIN == 4, one row, fp16 output: greedy next-token pick over the output (the lm_head's logits)
     // and the decode-state advance, done by the CTAs that finish the column blocks
@@ -643,6 +650,8 @@ static __device__ __noinline__ void gemv_reduce_partials(float* part, const floa
 // buffers (GemvArIn). 2: the input arrives already rotated (several batch rows, gemv_prerotate_kernel).
 // 3: the input is silu(x) * x2 of two vectors (the gated activation in front of a down projection).
 // 4: the input is RMSNorm(x + x2) * norm_w (residual add and norm in front of q|k|v, gate|up, lm_head).
+// 5 / 6: the same norm split between the producer of the residual contribution (its epilogue adds it to
+// the stream and leaves per-block sums of squares) and the consumer (its prologue only scales).
 template <int K, int CB, int MB, int MODE = 0, int GIN = 0>
 __global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 3))
 void exl3_gemv_kernel(const GemvParams P)
@@ -1250,7 +1259,69 @@ void exl3_gemv_kernel(const GemvParams P)
                     }
                 } while (b < nrows);
             }
-            else if constexpr (MODE == 0 && GIN == 0)
+            else if constexpr (MODE == 0 && GIN == 6)
+            {
+                // Normalised input whose sum of squares the producer already left per 128-column block:
+                // the warp adds the row's block sums up (fixed order), scale = rsqrt(mean + eps), and the
+                // task is n = fp16(x * scale) * w (fp16), then the usual scale and rotation. The block
+                // sums travel in the same batch of loads as the row itself: one round trip after the wait.
+                const int kb = k >> 7;                                  // 128-column blocks of the input row
+                int b = 0, jb = warp;
+                while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
+                do
+                {
+                    constexpr int TB = 4;
+                    half4 vx[TB], vs[TB], vw[TB];
+                    float q[TB];
+                    int tb[TB], tj[TB];
+                    #pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                    {
+                        tb[i] = b; tj[i] = jb;
+                        if (b < nrows)
+                        {
+                            const size_t col = (size_t) cg0 * 64 + (size_t) jb * 128 + lane * 4;
+                            vs[i] = *reinterpret_cast<const half4*>(suh + col);
+                            vw[i] = *reinterpret_cast<const half4*>(P.norm_w + col);
+                            jb += GEMV_WARPS;
+                            while (jb >= nblk && b < nrows) { jb -= nblk; ++b; }
+                        }
+                        else tb[i] = -1;
+                    }
+                    if (!waited) { if (P.pdl) pdl_wait(); waited = true; }
+                    #pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                        if (tb[i] >= 0)
+                        {
+                            vx[i] = *reinterpret_cast<const half4*>(P.x + (size_t) tb[i] * k + (size_t) cg0 * 64 + (size_t) tj[i] * 128 + lane * 4);
+                            float acc = 0.0f;
+                            for (int j = lane; j < kb; j += 32) acc += __ldcg(P.ssq + (size_t) tb[i] * kb + j);
+                            q[i] = acc;
+                        }
+                    if (!started)
+                    {
+                        #pragma unroll
+                        for (int j = 0; j < S - 1; ++j) issue();
+                        started = true;
+                    }
+                    #pragma unroll
+                    for (int i = 0; i < TB; ++i)
+                    {
+                        if (tb[i] < 0) continue;
+                        float tot = q[i];
+                        #pragma unroll
+                        for (int o2 = 16; o2 > 0; o2 >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o2);
+                        const float sc = rsqrtf(tot / (float) k + P.eps);
+                        half4 v;
+                        v.x = __hmul2(__floats2half2_rn(__low2float(vx[i].x) * sc, __high2float(vx[i].x) * sc), vw[i].x);
+                        v.y = __hmul2(__floats2half2_rn(__low2float(vx[i].y) * sc, __high2float(vx[i].y) * sc), vw[i].y);
+                        v.x = __hmul2(v.x, vs[i].x);
+                        v.y = __hmul2(v.y, vs[i].y);
+                        had_store(tb[i], tj[i], __low2float(v.x), __high2float(v.x), __low2float(v.y), __high2float(v.y));
+                    }
+                } while (b < nrows);
+            }
+            else if constexpr (MODE == 0 && (GIN == 0 || GIN == 5))
             {
                 // up to six tasks per pass: all their loads are in flight before the first
                 // transform (at grid start a load takes a microsecond), and the weight stream is
@@ -1680,6 +1751,23 @@ void exl3_gemv_kernel(const GemvParams P)
                             o.x = __floats2half2_rn(acc[0], acc[1]);
                             o.y = __floats2half2_rn(acc[2], acc[3]);
                         }
+                    }
+                    if constexpr (GIN == 5)
+                    {
+                        // producer side of the split norm: y = fp16(h + o) replaces the output, and the
+                        // block's sum of squares of y goes to ssq[row][block] (warp sum, fixed order)
+                        const size_t at = ((size_t) b * stride + (size_t) nb * 128) / 4 + lane;
+                        const half4 hv = reinterpret_cast<const half4*>(P.h_in)[at];
+                        half4 yv;
+                        yv.x = __floats2half2_rn(__low2float(hv.x) + __low2float(o.x), __high2float(hv.x) + __high2float(o.x));
+                        yv.y = __floats2half2_rn(__low2float(hv.y) + __low2float(o.y), __high2float(hv.y) + __high2float(o.y));
+                        reinterpret_cast<half4*>(P.y)[at] = yv;
+                        const float2 a0 = __half22float2(yv.x), a1 = __half22float2(yv.y);
+                        float qs2 = (a0.x * a0.x + a0.y * a0.y) + (a1.x * a1.x + a1.y * a1.y);
+                        #pragma unroll
+                        for (int o2 = 16; o2 > 0; o2 >>= 1) qs2 += __shfl_xor_sync(0xffffffffu, qs2, o2);
+                        if (lane == 0) P.ssq[(size_t) b * P.blocks + blk] = qs2;
+                        continue;
                     }
                     reinterpret_cast<half4*>(reinterpret_cast<__half*>(cbase) + (size_t) b * stride + (size_t) nb * 128)[lane] = o;
                     if constexpr (GIN == 4)

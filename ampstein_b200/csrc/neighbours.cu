@@ -12,25 +12,51 @@
 
 namespace amp {
 
-// y = fp16(x + r); n = fp16(y * rsqrt(mean(y^2) + eps)) * w (fp16 multiply). One CTA per row.
+// y = fp16(x + r); n = fp16(y * rsqrt(mean(y^2) + eps)) * w (fp16 multiply). One CTA per row. The norm
+// weight does not depend on the producer: it is loaded before the wait for it, and the sum y stays in
+// registers between the two passes (rows up to 4096 wide; wider rows re-read y), so one L2 round trip
+// follows the wait.
 __global__ __launch_bounds__(256)
 void rms_norm_res_kernel(const __half* __restrict__ x, const __half* __restrict__ r, const __half* __restrict__ w,
                          __half* __restrict__ y, __half* __restrict__ n, int dim, float eps, int pdl)
 {
     __shared__ float s_red[8];
     __shared__ float s_scale;
-    if (pdl) { pdl_launch_dependents(); pdl_wait(); }
     const int t = threadIdx.x, cnt = dim >> 2;
     const size_t row = (size_t) blockIdx.x * dim;
+    constexpr int KEEP = 4;                                  // chunks per thread held in registers
+    half4 wv[KEEP], h[KEEP];
+    if (pdl) pdl_launch_dependents();
+    #pragma unroll
+    for (int j = 0; j < KEEP; ++j)
+        if (t + j * 256 < cnt) wv[j] = reinterpret_cast<const half4*>(w)[t + j * 256];
+    if (pdl) pdl_wait();
     float acc = 0.0f;
-    for (int c = t; c < cnt; c += 256)
+    {
+        half4 xv[KEEP], rv[KEEP];
+        #pragma unroll
+        for (int j = 0; j < KEEP; ++j)
+            if (t + j * 256 < cnt) { xv[j] = reinterpret_cast<const half4*>(x + row)[t + j * 256]; rv[j] = reinterpret_cast<const half4*>(r + row)[t + j * 256]; }
+        #pragma unroll
+        for (int j = 0; j < KEEP; ++j)
+        {
+            if (t + j * 256 >= cnt) continue;
+            h[j].x = __floats2half2_rn(__low2float(xv[j].x) + __low2float(rv[j].x), __high2float(xv[j].x) + __high2float(rv[j].x));
+            h[j].y = __floats2half2_rn(__low2float(xv[j].y) + __low2float(rv[j].y), __high2float(xv[j].y) + __high2float(rv[j].y));
+            reinterpret_cast<half4*>(y + row)[t + j * 256] = h[j];
+            const float2 a = __half22float2(h[j].x), b = __half22float2(h[j].y);
+            acc += a.x * a.x + a.y * a.y;
+            acc += b.x * b.x + b.y * b.y;
+        }
+    }
+    for (int c = t + KEEP * 256; c < cnt; c += 256)             // rows wider than 4096
     {
         const half4 xv = reinterpret_cast<const half4*>(x + row)[c], rv = reinterpret_cast<const half4*>(r + row)[c];
-        half4 h;
-        h.x = __floats2half2_rn(__low2float(xv.x) + __low2float(rv.x), __high2float(xv.x) + __high2float(rv.x));
-        h.y = __floats2half2_rn(__low2float(xv.y) + __low2float(rv.y), __high2float(xv.y) + __high2float(rv.y));
-        reinterpret_cast<half4*>(y + row)[c] = h;
-        const float2 a = __half22float2(h.x), b = __half22float2(h.y);
+        half4 hh;
+        hh.x = __floats2half2_rn(__low2float(xv.x) + __low2float(rv.x), __high2float(xv.x) + __high2float(rv.x));
+        hh.y = __floats2half2_rn(__low2float(xv.y) + __low2float(rv.y), __high2float(xv.y) + __high2float(rv.y));
+        reinterpret_cast<half4*>(y + row)[c] = hh;
+        const float2 a = __half22float2(hh.x), b = __half22float2(hh.y);
         acc += a.x * a.x + a.y * a.y;
         acc += b.x * b.x + b.y * b.y;
     }
@@ -46,12 +72,21 @@ void rms_norm_res_kernel(const __half* __restrict__ x, const __half* __restrict_
     }
     __syncthreads();
     const float sc = s_scale;
-    for (int c = t; c < cnt; c += 256)
+    #pragma unroll
+    for (int j = 0; j < KEEP; ++j)
     {
-        const half4 h = reinterpret_cast<const half4*>(y + row)[c], wv = reinterpret_cast<const half4*>(w)[c];
+        if (t + j * 256 >= cnt) continue;
         half4 o;
-        o.x = __hmul2(__floats2half2_rn(__low2float(h.x) * sc, __high2float(h.x) * sc), wv.x);
-        o.y = __hmul2(__floats2half2_rn(__low2float(h.y) * sc, __high2float(h.y) * sc), wv.y);
+        o.x = __hmul2(__floats2half2_rn(__low2float(h[j].x) * sc, __high2float(h[j].x) * sc), wv[j].x);
+        o.y = __hmul2(__floats2half2_rn(__low2float(h[j].y) * sc, __high2float(h[j].y) * sc), wv[j].y);
+        reinterpret_cast<half4*>(n + row)[t + j * 256] = o;
+    }
+    for (int c = t + KEEP * 256; c < cnt; c += 256)
+    {
+        const half4 hh = reinterpret_cast<const half4*>(y + row)[c], w1 = reinterpret_cast<const half4*>(w)[c];
+        half4 o;
+        o.x = __hmul2(__floats2half2_rn(__low2float(hh.x) * sc, __high2float(hh.x) * sc), w1.x);
+        o.y = __hmul2(__floats2half2_rn(__low2float(hh.y) * sc, __high2float(hh.y) * sc), w1.y);
         reinterpret_cast<half4*>(n + row)[c] = o;
     }
 }

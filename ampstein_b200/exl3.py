@@ -221,6 +221,63 @@ def exl3_gemm_rms_norm_res(x, res, norm_w, eps, y, B, C, suh, svh, mul1=False, m
     return C
 
 
+def exl3_gemm_add_res(x, B, suh, svh, h, y, ssq, mul1=False, mcg=False):
+    """Producer side of the split residual norm: y (m, n) = fp16(h + linear(x)) and ssq (m, n / 128)
+    fp32 = block sums of squares of y, in the launch of the linear itself (o_proj / down_proj). y must
+    not alias h. Returns (y, ssq)."""
+    _check_cuda("exl3_gemm_add_res", x, B, suh, svh, h, y, ssq)
+    k, n, K = _trellis_dims("exl3_gemm_add_res", B)
+    m = x.numel() // k
+    if any(t.dtype != torch.float16 for t in (x, suh, svh, h, y)) or ssq.dtype != torch.float32:
+        raise TypeError("exl3_gemm_add_res: fp16 tensors, fp32 ssq")
+    if x.shape[-1] != k or not 1 <= m <= 16 or h.numel() != m * n or y.numel() != m * n or ssq.numel() < m * (n // 128) \
+            or y.data_ptr() == h.data_ptr():
+        raise ValueError("exl3_gemm_add_res: incompatible shapes (1..16 rows), or y aliases h")
+    with torch.cuda.device(x.device):
+        _lib.call("amp_exl3_gemv_add_res", x.data_ptr(), B.data_ptr(), suh.data_ptr(), svh.data_ptr(), h.data_ptr(), y.data_ptr(),
+                  ssq.data_ptr(), m, k, n, K, _cb(mul1, mcg), _stream(x))
+    return y, ssq
+
+
+def exl3_gemm_normed(y, ssq, norm_w, eps, B, C, suh, svh, mul1=False, mcg=False):
+    """Consumer side: C = linear(fp16(y * rsqrt(sum(ssq row) / k + eps)) * norm_w). Returns C."""
+    _check_cuda("exl3_gemm_normed", y, ssq, norm_w, B, C, suh, svh)
+    k, n, K = _trellis_dims("exl3_gemm_normed", B)
+    m = y.numel() // k
+    if y.dtype != torch.float16 or norm_w.dtype != torch.float16 or ssq.dtype != torch.float32 or C.dtype not in (torch.float16, torch.float32):
+        raise TypeError("exl3_gemm_normed: y, norm_w fp16; ssq fp32; C fp16 or fp32")
+    if y.shape[-1] != k or not 1 <= m <= 16 or C.numel() != m * n or ssq.numel() < m * (k // 128) or norm_w.numel() != k:
+        raise ValueError("exl3_gemm_normed: incompatible shapes (1..16 rows)")
+    with torch.cuda.device(y.device):
+        _lib.call("amp_exl3_gemv_normed", y.data_ptr(), ssq.data_ptr(), norm_w.data_ptr(), float(eps), B.data_ptr(), C.data_ptr(),
+                  suh.data_ptr(), svh.data_ptr(), m, k, n, K, _cb(mul1, mcg), 1 if C.dtype == torch.float32 else 0, _stream(y))
+    return C
+
+
+def mgemm_normed(y, ssq, norm_w, eps, B_ptrs, C, suh_ptrs, svh_ptrs, K, mcg, mul1, opts=None):
+    """Consumer side, bundle form (tables and opts as mgemm; y (1, m, k) fp16, m <= 16). Returns C."""
+    _check_cuda("mgemm_normed", y, ssq, norm_w, C)
+    if y.dtype != torch.float16 or norm_w.dtype != torch.float16 or ssq.dtype != torch.float32:
+        raise TypeError("mgemm_normed: y, norm_w fp16; ssq fp32")
+    if y.dim() != 3 or y.shape[0] != 1 or C.dim() != 3:
+        raise ValueError("mgemm_normed: y must be (1, m, k) and C (num, m, n)")
+    num, m, width = C.shape
+    k = y.shape[2]
+    if y.shape[1] != m or not 1 <= m <= 16 or ssq.numel() < m * (k // 128) or norm_w.numel() != k:
+        raise ValueError("mgemm_normed: 1..16 rows; ssq (m, k / 128); norm_w (k)")
+    c_ptrs = n_stride = had_src = None
+    if opts is not None:
+        c_ptrs, n_stride, had_src = opts["c_ptrs"], opts["n_stride_list"], opts["had_src_list"]
+    with torch.cuda.device(y.device):
+        _lib.call("amp_exl3_mgemm_normed", y.data_ptr(), ssq.data_ptr(), norm_w.data_ptr(), float(eps),
+                  B_ptrs.data_ptr(), C.data_ptr(), suh_ptrs.data_ptr(), svh_ptrs.data_ptr(), num, m, k, width,
+                  int(K), _cb(mul1, mcg), 1 if C.dtype == torch.float32 else 0,
+                  c_ptrs.data_ptr() if c_ptrs is not None else None,
+                  n_stride.data_ptr() if n_stride is not None else None,
+                  had_src.data_ptr() if had_src is not None else None, _stream(y))
+    return C
+
+
 def rms_norm_res(x, res, norm_w, eps, y=None, n=None):
     """Stand-alone residual add + RMSNorm (the arithmetic the fused entries apply): returns (y, n),
     y = fp16(x + res), n = fp16(y * rsqrt(mean(y^2) + eps)) * norm_w (reference: torch.rms_norm_res,

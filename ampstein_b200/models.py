@@ -51,6 +51,11 @@ class LinearEXL3:
             out = out.add(self.bias)
         return out
 
+    def forward_add_res(self, x, h, y, ssq):
+        """y = fp16(h + this linear of x), ssq = block sums of squares of y: the linear and the residual
+        add of the norm that follows, in one launch (up to 16 rows)."""
+        return exl3.exl3_gemm_add_res(x, self.trellis, self.suh, self.svh, h, y, ssq, self.mul1, self.mcg)
+
     def weight_bytes(self):
         return self.trellis.numel() * 2
 
@@ -132,6 +137,12 @@ class Multi:
         """The bundle applied to RMSNorm(x + res) * norm_w, y = fp16(x + res): one launch (up to 16 rows)."""
         return _run_norm(self, self.out, x, res, norm_w, eps, y, None)
 
+    def run_normed(self, y, ssq, norm_w, eps):
+        """The bundle applied to the norm of a residual stream whose block sums of squares the producing
+        linear left in ssq (LinearEXL3.forward_add_res)."""
+        a = self.linears[0]
+        return exl3.mgemm_normed(y, ssq, norm_w, eps, self.B, self.out, self.suh, self.svh, a.K, a.mcg, a.mul1)
+
 
 def _run_norm(bundle, carrier, x, res, norm_w, eps, y, opts):
     a = bundle.linears[0]
@@ -189,6 +200,13 @@ class Sliced:
     def run_norm(self, x, res, norm_w, eps, y):
         """The bundle applied to RMSNorm(x + res) * norm_w, y = fp16(x + res): one launch (up to 16 rows)."""
         _run_norm(self, self.carrier, x, res, norm_w, eps, y, self.opts)
+        return self.outs
+
+    def run_normed(self, y, ssq, norm_w, eps):
+        """The bundle applied to the norm of a residual stream whose block sums of squares the producing
+        linear left in ssq (LinearEXL3.forward_add_res)."""
+        a = self.linears[0]
+        exl3.mgemm_normed(y, ssq, norm_w, eps, self.B, self.carrier, self.suh, self.svh, a.K, a.mcg, a.mul1, self.opts)
         return self.outs
 
 

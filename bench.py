@@ -749,11 +749,32 @@ def measure_step_with_neighbours(steps, warmup, n_layers=0):
         return fn
 
     fused = mixed(True, True, True)
+    ssq = torch.zeros((1, H // 128), dtype=torch.float32, device=dev)
+
+    def split_norm():
+        # the norm split between producer and consumer: o and down add their output to the residual
+        # stream and leave block sums of squares; q|k|v, gate|up and the lm_head scale in their prologue.
+        # (The very first norm of the step has no producing linear in front of it.)
+        cur = 0
+        amp.rms_norm_res(hbuf[cur], d_out.view(1, 1, H), norm_w[0][0], eps, hbuf[cur], r)
+        for i, L in enumerate(layers):
+            if i == 0:
+                qkv[i].run(r)
+            else:
+                qkv[i].run_normed(hbuf[cur], ssq, norm_w[i][0], eps)
+            L["o"].forward_add_res(q[0], hbuf[cur][0], hbuf[1 - cur][0], ssq)
+            cur = 1 - cur
+            gu[i].run_normed(hbuf[cur], ssq, norm_w[i][1], eps)
+            amp.silu_mul(gu_out[0], gu_out[1], a)
+            L["down"].forward_add_res(a, hbuf[cur][0], hbuf[1 - cur][0], ssq)
+            cur = 1 - cur
+        amp.exl3_gemm_normed(hbuf[cur][0], ssq, norm_w[nl][0], eps, head.trellis, logits, head.suh, head.svh)
+        amp.argmax_advance(logits, ids, pos, log, ws)
 
     out = {}
     picks = {}
     forms = [("linears_only", linears_only, 4 * nl + 1), ("neighbours_separate", unfused, 7 * nl + 3),
-             ("neighbours_fused", fused, 4 * nl + 1)]
+             ("neighbours_fused", fused, 4 * nl + 1), ("norm_split_producer_consumer", split_norm, 5 * nl + 3)]
     if os.environ.get("AMP_BENCH_STEP_PARTS"):          # which fusion buys what
         forms += [("fused_norms_only", mixed(True, False, False), 5 * nl + 3), ("fused_activation_only", mixed(False, True, False), 6 * nl + 3),
                   ("fused_tail_only", mixed(False, False, True), 7 * nl + 1)]
@@ -775,7 +796,7 @@ def measure_step_with_neighbours(steps, warmup, n_layers=0):
             "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3), "data": "synthetic", "dtype": "f16",
             "config": {"workload": "%d layers x (norm, q|k|v, o, norm, gate|up, silu*mul, down) + final norm, lm_head, greedy pick; "
                                    "attention not included" % nl,
-                       "same_pick": picks["neighbours_separate"] == picks["neighbours_fused"]},
+                       "same_pick": len(set(picks[n] for n in picks if n != "linears_only")) == 1},
             "forms": out}
 
 

@@ -214,6 +214,28 @@ int amp_b200_silu_mul(const void* g, const void* u, void* out, long count, cudaS
 int amp_b200_argmax_advance(const void* logits, int n, void* ids, void* pos, void* log, long long log_cap, void* ws,
                             cudaStream_t stream);
 /*
+ * The residual norm split between the launches on either side of it (the form that pays: nothing
+ * reads a whole row on a CTA's critical path).
+ *   amp_exl3_gemv_add_res   y (m, n) = fp16(h + linear(x)), the updated residual stream (the linear's own
+ *                           output is not stored), and ssq (m, n / 128) fp32 = the sum of squares of y per
+ *                           128-column block, written by the warps that finish the blocks. y must not
+ *                           alias h. Replaces exl3_gemm (o_proj / down_proj) + the add of rms_norm_res.
+ *   amp_exl3_gemv_normed /  the linear / bundle of fp16(y * rsqrt(sum(ssq row) / k + eps)) * norm_w: the
+ *   amp_exl3_mgemm_normed   prologue adds the k / 128 block sums up and scales. Replaces the norm of
+ *                           rms_norm_res + the q|k|v / gate|up bundle or the lm_head.
+ * m <= 16; fp16 y. Same rounding points as amp_rms_norm_res_kernel (src/torch/amp_kernels.cu:279-360);
+ * the sum of squares is added in another (fixed) order. The reference has no such entry points.
+ */
+int amp_exl3_gemv_add_res(const void* x, const void* trellis, const void* suh, const void* svh,
+                          const void* h, void* y, void* ssq, int m, int k, int n, int K, int cb, cudaStream_t stream);
+int amp_exl3_gemv_normed(const void* y, const void* ssq, const void* norm_w, float eps,
+                         const void* trellis, void* C, const void* suh, const void* svh,
+                         int m, int k, int n, int K, int cb, int c_fp32, cudaStream_t stream);
+int amp_exl3_mgemm_normed(const void* y, const void* ssq, const void* norm_w, float eps,
+                          const void* trellis_ptrs, void* C, const void* suh_ptrs, const void* svh_ptrs,
+                          int num, int m, int k, int width, int K, int cb, int c_fp32,
+                          const void* c_ptrs, const void* n_stride_list, const void* had_src_list, cudaStream_t stream);
+/*
  * The last three launches of a greedy decode step in one: y = fp16(x + res), logits (1, n) fp16 = the
  * lm_head of RMSNorm(y) * norm_w, then argmax over the first `vocab` logits and the state advance
  * log[pos] = ids; ids = argmax; pos += 1 (ids, pos: one int64 each; log: int64 array of log_cap

@@ -439,6 +439,50 @@ def test_linears_with_the_residual_norm_in_their_prologue(amp, oracle, m, k, K, 
         check_close(o.float().cpu().numpy(), oracle.linear(n_ref, tr, s_u, s_v, cb, fp32_out=True))
 
 
+@pytest.mark.parametrize("m,K,cb", [(1, 4, 0), (3, 5, 2), (8, 3, 1)])
+def test_residual_norm_split_between_producer_and_consumer(amp, oracle, m, K, cb):
+    """exl3_gemm_add_res (the producing linear adds its output to the residual stream and leaves block
+    sums of squares) followed by exl3_gemm_normed / the bundle form (the consumer scales): against the
+    oracle's sequence linear -> rms_norm_res -> linear. y bit-exact given the producer's own fp16
+    output; the block sums within fp32 rounding of numpy's; the consumers within their bound."""
+    from ampstein_b200.models import LinearEXL3, Multi
+    k0, H, n = 768, 1024, 512
+    tr0, su0, sv0, x = make_linear(k0, H, K, seed=9950 + m, m=m)
+    sv0 = (sv0.astype(np.float32) / (1.2437 * np.sqrt(k0))).astype(np.float16)
+    tr1, su1, sv1, _ = make_linear(H, n, K, seed=9960 + m)
+    rng = np.random.default_rng(995 + m)
+    h = rng.standard_normal((m, H)).astype(np.float16)
+    w = (1.0 + 0.1 * rng.standard_normal(H)).astype(np.float16)
+    eps = 1e-5
+    mul1, mcg = cb == 2, cb == 1
+    xd, hd = dev(x), dev(h)
+    # the producer's own fp16 output, from the plain entry (same kernel arithmetic)
+    o = torch.empty((m, H), dtype=torch.float16, device="cuda")
+    amp.exl3_gemm(xd, dev(tr0), o, dev(su0), dev(sv0), mul1=mul1, mcg=mcg)
+    y = torch.full((m, H), float("nan"), dtype=torch.float16, device="cuda")
+    ssq = torch.full((m, H // 128), float("nan"), dtype=torch.float32, device="cuda")
+    amp.exl3_gemm_add_res(xd, dev(tr0), dev(su0), dev(sv0), hd, y, ssq, mul1=mul1, mcg=mcg)
+    torch.cuda.synchronize()
+    y_ref, n_ref = oracle.rms_norm_res(h, o.cpu().numpy(), w, eps)
+    assert np.array_equal(host16(y), y_ref.view(np.uint16))
+    want = (y_ref.astype(np.float64) ** 2).reshape(m, H // 128, 128).sum(axis=2)
+    assert np.allclose(ssq.cpu().numpy(), want, rtol=1e-5)
+    c = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    amp.exl3_gemm_normed(y, ssq, dev(w), eps, dev(tr1), c, dev(su1), dev(sv1), mul1=mul1, mcg=mcg)
+    torch.cuda.synchronize()
+    check_close(c.cpu().numpy(), oracle.linear(n_ref, tr1, su1, sv1, cb, fp32_out=True))
+    # bundle form
+    parts = []
+    for i in range(2):
+        tr, s_u, s_v, _ = make_linear(H, 384, K, seed=9970 + i + m)
+        parts.append(((tr, s_u, s_v), LinearEXL3(dev(tr), dev(s_u), dev(s_v), mul1=mul1, mcg=mcg)))
+    gu = torch.full((2, m, 384), float("nan"), dtype=torch.float16, device="cuda")
+    Multi([p[1] for p in parts], gu).run_normed(y.reshape(1, m, H), ssq, dev(w), eps)
+    torch.cuda.synchronize()
+    for i, ((tr, s_u, s_v), _) in enumerate(parts):
+        check_close(gu[i].float().cpu().numpy(), oracle.linear(n_ref, tr, s_u, s_v, cb, fp32_out=True))
+
+
 def test_stand_alone_neighbour_kernels(amp, oracle):
     """The stand-alone residual norm, gated activation and greedy pick against the oracle / numpy, and
     the fused sequence against the unfused one built from them: same logits bits, same pick."""
