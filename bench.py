@@ -822,6 +822,8 @@ def secondary():
     out = {}
     p = measure_prefill(10, 3)
     out["prefill"] = {k: p[k] for k in ("metric", "value", "unit", "ms_per_step", "roofline", "clocks")}
+    st = measure_step_with_neighbours(10, 3)
+    out["decode_step_with_neighbours"] = {"metric": st["metric"], "unit": st["unit"], "config": st["config"], "forms": st["forms"]}
     for T in (1, 4, 16):
         r = measure_moe(20, 3, T)
         out["moe_T%d" % T] = {"metric": r["metric"], "value": r["value"], "unit": r["unit"],
