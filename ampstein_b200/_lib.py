@@ -60,6 +60,9 @@ SIGNATURES = {
     "amp_comm_free": [_vp],
     "amp_exl3_moe_coop": [_vp, _vp],
     "amp_exl3_moe_coop_ctr_len": [_l, _l, _l, _l],
+    "amp_exl3_moe_sorted": [_vp, _vp],
+    "amp_exl3_moe_sorted_workspace": [_l, _l, _l, _l, _l],
+    "amp_exl3_moe_sorted_status": [_vp, ctypes.POINTER(ctypes.c_int), _vp],
     "amp_exl3_gemm_bf16": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "amp_exl3_gemm_status": [ctypes.POINTER(ctypes.c_int)],
     "amp_exl3_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
@@ -87,6 +90,7 @@ def lib():
             fn.argtypes = args
             fn.restype = ctypes.c_int
         L.amp_exl3_moe_coop_ctr_len.restype = ctypes.c_long
+        L.amp_exl3_moe_sorted_workspace.restype = ctypes.c_long
         L.amp_comm_buffer_bytes.restype = ctypes.c_long
         L.amp_comm_ctl_bytes.restype = ctypes.c_long
         L.amp_b200_last_error.restype = ctypes.c_char_p

@@ -82,6 +82,17 @@ struct TcParams
     const long long* t_c;       // may be null: outputs stacked in c as (slices, M, n)
     const int* t_stride;        // may be null: row width = n
     const int* t_src;           // may be null: rotated input of slice i is source i
+    // expert groups (grouped instances of the single-CTA kernel): blockIdx.y walks a tile table
+    // that a kernel in front of this one built from the routing, blockIdx.x = projection * (n / 128)
+    // + column block. A tile is up to sub * 128 consecutive rows of ONE expert in the padded,
+    // expert-sorted row space of xt / c (M = its capacity); t_trellis / t_svh hold g_kinds *
+    // g_experts entries, projection-major; projection p reads xt + p * M * k halves and writes
+    // c + p * M * n elements.
+    const int* g_ntiles;        // device: tiles in use (CTAs beyond it return at once)
+    const int* g_tile_e;        // device: expert of a tile
+    const int* g_tile_row0;     // device: first padded row of a tile (a multiple of 8)
+    const int* g_tile_rows;     // device: valid rows of a tile (1 .. sub * 128)
+    int g_experts;
 };
 
 // What one CTA (pair) works on: its weight, scales, output, rotated input and column block
@@ -194,10 +205,12 @@ __device__ __forceinline__ uint32_t weights2(uint32_t sa, uint32_t sb)
     }
 }
 
-template <int K, int CB>
+template <int K, int CB, bool GROUPED = false>
 __global__ __launch_bounds__(TC_THREADS, 1)
 void exl3_gemm_tc_kernel(const TcParams P)
 {
+    if constexpr (GROUPED)
+        if ((int) blockIdx.y >= *P.g_ntiles || P.g_tile_rows[blockIdx.y] <= 0) return;     // the whole CTA, before any barrier or allocation
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment is required by the swizzled layout
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
@@ -206,10 +219,28 @@ void exl3_gemm_tc_kernel(const TcParams P)
     __shared__ volatile int s_bad;
 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const TcSlice W = tc_slice<TC_BN>(P, blockIdx.x);
-    const int nb = W.nb, mb = blockIdx.y;
-    const int m0 = mb * (P.sub * TC_BM);
-    const int rows = min(P.sub * TC_BM, P.M - m0);     // valid token rows of this CTA
+    TcSlice W;
+    int m0, rows;                                       // first row and valid token rows of this CTA
+    if constexpr (GROUPED)
+    {
+        const int tile = blockIdx.y, bpk = P.n / TC_BN, kind = (int) blockIdx.x / bpk;
+        const size_t idx = (size_t) kind * P.g_experts + P.g_tile_e[tile];
+        W.trellis = reinterpret_cast<const unsigned char*>(P.t_trellis[idx]);
+        W.svh = reinterpret_cast<const __half*>(P.t_svh[idx]);
+        W.c = reinterpret_cast<unsigned char*>(P.c) + (size_t) kind * P.M * P.n * (P.c_fp32 ? 4 : 2);
+        W.xt = P.xt + (size_t) kind * P.M * P.k * 2;
+        W.n_row = P.n;
+        W.nb = (int) blockIdx.x - kind * bpk;
+        m0 = P.g_tile_row0[tile];
+        rows = min(P.g_tile_rows[tile], P.sub * TC_BM);
+    }
+    else
+    {
+        W = tc_slice<TC_BN>(P, blockIdx.x);
+        m0 = (int) blockIdx.y * (P.sub * TC_BM);
+        rows = min(P.sub * TC_BM, P.M - m0);
+    }
+    const int nb = W.nb;
     const int nsub = (rows + TC_BM - 1) / TC_BM;        // sub-tiles that hold any of them
     const int ksteps = P.k / TC_BK;
     const size_t tiles_n = (size_t) W.n_row >> 4;
@@ -417,7 +448,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
             for (int r = ew; r < TC_BM; r += TC_DECODE_WARPS)
             {
                 const int grow = m0 + sub * TC_BM + r;
-                if (grow >= P.M) break;
+                if (sub * TC_BM + r >= rows) break;
                 const float4 v = *reinterpret_cast<const float4*>(tile + r * TP + lane * 4);
                 float h0 = v.x, h1 = v.y, h2 = v.z, h3 = v.w;
                 warp_had128(h0, h1, h2, h3, lane);
@@ -864,7 +895,7 @@ void exl3_gemm_tc2_kernel(const TcParams P)
             for (int r = ew; r < TC_BM; r += TC_DECODE_WARPS)
             {
                 const int grow = m0 + sub * TC_BM + r;
-                if (grow >= P.M) break;
+                if (sub * TC_BM + r >= rows) break;
                 const float4 v = *reinterpret_cast<const float4*>(tile + r * TP + lane * 4);
                 float h0 = v.x, h1 = v.y, h2 = v.z, h3 = v.w;
                 warp_had128(h0, h1, h2, h3, lane);
@@ -900,6 +931,11 @@ typedef void (*tc_fn)(const TcParams);
                          exl3_gemm_tc_kernel<5, cb>, exl3_gemm_tc_kernel<6, cb>, exl3_gemm_tc_kernel<7, cb>, exl3_gemm_tc_kernel<8, cb> }
 static const tc_fn k_tc[3][8] = { AMP_TC_ROW(0), AMP_TC_ROW(1), AMP_TC_ROW(2) };
 #undef AMP_TC_ROW
+#define AMP_TCG_ROW(cb) { exl3_gemm_tc_kernel<1, cb, true>, exl3_gemm_tc_kernel<2, cb, true>, exl3_gemm_tc_kernel<3, cb, true>, \
+                          exl3_gemm_tc_kernel<4, cb, true>, exl3_gemm_tc_kernel<5, cb, true>, exl3_gemm_tc_kernel<6, cb, true>, \
+                          exl3_gemm_tc_kernel<7, cb, true>, exl3_gemm_tc_kernel<8, cb, true> }
+static const tc_fn k_tcg[3][8] = { AMP_TCG_ROW(0), AMP_TCG_ROW(1), AMP_TCG_ROW(2) };
+#undef AMP_TCG_ROW
 #define AMP_TC2_ROW(cb) { exl3_gemm_tc2_kernel<1, cb>, exl3_gemm_tc2_kernel<2, cb>, exl3_gemm_tc2_kernel<3, cb>, exl3_gemm_tc2_kernel<4, cb>, \
                           exl3_gemm_tc2_kernel<5, cb>, exl3_gemm_tc2_kernel<6, cb>, exl3_gemm_tc2_kernel<7, cb>, exl3_gemm_tc2_kernel<8, cb> }
 static const tc_fn k_tc2[3][8] = { AMP_TC2_ROW(0), AMP_TC2_ROW(1), AMP_TC2_ROW(2) };
@@ -991,6 +1027,43 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
     dim3 grid((unsigned) (slices * (n / 128)), (unsigned) mblocks);
     fn<<<grid, TC_THREADS, smem_bytes, stream>>>(P);
     return cuda_rc(cudaGetLastError(), "exl3_gemm_tc launch");
+}
+
+// Expert-grouped form for token-sorted MoE prefill: xt / c are (kinds, Mcap, k / n) in the padded,
+// expert-sorted row space, the tile table lives in device memory (see TcParams). One CTA per
+// (tile, projection, 128-column block); the grid is sized for G.max_tiles and the surplus returns.
+int launch_gemm_tc_grouped(const void* xt, void* c, long Mcap, int k, int n, int K, int cb, int c_fp32,
+                           const long long* t_trellis, const long long* t_svh, const TcGroups& G, cudaStream_t stream)
+{
+    AMP_REQUIRE(xt && c && t_trellis && t_svh && G.ntiles && G.tile_e && G.tile_row0 && G.tile_rows, "exl3_moe_sorted: null pointer");
+    AMP_REQUIRE(K >= 1 && K <= 8 && cb >= 0 && cb <= 2, "exl3_moe_sorted: unsupported bitrate / codebook");
+    AMP_REQUIRE(Mcap >= 1 && Mcap <= 0x7fffffffL && k % 128 == 0 && n % 128 == 0 && k > 0 && n > 0, "exl3_moe_sorted: k and n must be multiples of 128");
+    AMP_REQUIRE(((uintptr_t) xt & 15) == 0 && ((uintptr_t) c & 15) == 0, "exl3_moe_sorted: misaligned pointer");
+    AMP_REQUIRE(G.kinds >= 1 && G.kinds <= 2 && G.sub >= 1 && G.sub <= TC_SUB && G.experts >= 1, "exl3_moe_sorted: bad grouping");
+    AMP_REQUIRE(G.max_tiles >= 1 && G.max_tiles <= 65535, "exl3_moe_sorted: too many row tiles");
+    int dev = 0;
+    if (cudaError_t e = cudaGetDevice(&dev)) return cuda_rc(e, "cudaGetDevice");
+    tc_fn fn = k_tcg[cb][K - 1];
+    const int smem_bytes = tc_smem_bytes(K);
+    if (cudaError_t e = ensure_smem(fn, smem_bytes, dev)) return cuda_rc(e, "exl3_moe_sorted smem attribute");
+    TcParams P = {};
+    P.xt = (const unsigned char*) xt; P.c = c;
+    P.M = (int) Mcap; P.k = k; P.n = n; P.c_fp32 = c_fp32; P.sub = G.sub;
+    P.t_trellis = t_trellis; P.t_svh = t_svh;
+    P.g_ntiles = G.ntiles; P.g_tile_e = G.tile_e; P.g_tile_row0 = G.tile_row0; P.g_tile_rows = G.tile_rows;
+    P.g_experts = G.experts;
+    {
+        static int* status_ptr[64] = {};
+        static std::mutex status_mu;
+        std::lock_guard<std::mutex> lock(status_mu);
+        int*& sp = status_ptr[dev & 63];
+        if (!sp)
+            if (cudaError_t e = cudaGetSymbolAddress((void**) &sp, g_tc_status)) return cuda_rc(e, "status symbol");
+        P.status = sp;
+    }
+    dim3 grid((unsigned) (G.kinds * (n / 128)), (unsigned) G.max_tiles);
+    fn<<<grid, TC_THREADS, smem_bytes, stream>>>(P);
+    return cuda_rc(cudaGetLastError(), "exl3_moe_sorted gemm launch");
 }
 
 }  // namespace amp

@@ -56,6 +56,18 @@ int launch_gemm_tc(const void* xh, const void* trellis, void* c, const void* svh
 int launch_had_tiled(const void* in, void* out, const void* pre, long M, int k, int bf16, cudaStream_t stream,
                      const long long* pre_table = nullptr, int sources = 1);
 
+// Tile table of the expert-grouped prefill GEMM (device arrays written by moe_sorted_prep_kernel)
+struct TcGroups
+{
+    const int* ntiles; const int* tile_e; const int* tile_row0; const int* tile_rows;
+    int experts;         // entries per projection in the pointer tables
+    int max_tiles;       // grid height: an upper bound of *ntiles
+    int sub;             // 128-row sub-tiles per tile (1..4)
+    int kinds;           // projections in one launch (gate and up: 2)
+};
+int launch_gemm_tc_grouped(const void* xt, void* c, long Mcap, int k, int n, int K, int cb, int c_fp32,
+                           const long long* t_trellis, const long long* t_svh, const TcGroups& G, cudaStream_t stream);
+
 extern int g_pdl;
 
 }  // namespace amp

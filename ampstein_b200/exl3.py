@@ -582,3 +582,118 @@ def moe_coop(x, sel, rw, cfg, sh_out=None):
     with torch.cuda.device(x.device):
         _lib.call("amp_exl3_moe_coop", ctypes.byref(a), _stream(x))
     return None
+
+
+class _MoeSortedArgs(__import__("ctypes").Structure):
+    """ctypes image of amp_moe_sorted_args (include/ampstein_b200.h)."""
+    import ctypes as _c
+    _fields_ = [
+        ("y", _c.c_void_p), ("out", _c.c_void_p), ("count", _c.c_void_p), ("tok_sorted", _c.c_void_p),
+        ("w_sorted", _c.c_void_p),
+        ("T", _c.c_int), ("H", _c.c_int), ("I", _c.c_int), ("E", _c.c_int), ("A", _c.c_long),
+        ("g_trellis", _c.c_void_p), ("g_suh", _c.c_void_p), ("g_svh", _c.c_void_p),
+        ("u_trellis", _c.c_void_p), ("u_suh", _c.c_void_p), ("u_svh", _c.c_void_p),
+        ("d_trellis", _c.c_void_p), ("d_suh", _c.c_void_p), ("d_svh", _c.c_void_p),
+        ("Kg", _c.c_int), ("Ku", _c.c_int), ("Kd", _c.c_int), ("cb", _c.c_int), ("act", _c.c_int),
+        ("act_limit", _c.c_float), ("gated", _c.c_int), ("count_lo", _c.c_int), ("count_hi", _c.c_int),
+        ("workspace", _c.c_void_p), ("workspace_bytes", _c.c_long),
+    ]
+
+
+def moe_sort_routing(sel, rw, n_experts, e0=0):
+    """Routing of a prefill chunk sorted by expert, as the reference prepares it for torch.moe_fused
+    (moe_sorted_begin, src/ucode/ampstein/glm5.uc:1096-1170): sel / rw (T, picks) -> count
+    (n_experts + 1) int64, tok_sorted (T * picks) int64, w_sorted (T * picks) fp16. Picks outside
+    [e0, e0 + n_experts) fall into the sentinel bin n_experts, which no kernel touches. The sort is
+    stable: inside an expert the rows keep their token order."""
+    T, K = sel.shape
+    fe = sel.reshape(-1).to(torch.int64) - int(e0)
+    fe = torch.where((fe < 0) | (fe >= n_experts), torch.full_like(fe, n_experts), fe)
+    order = torch.sort(fe, stable=True).indices
+    tok = (torch.arange(T * K, device=sel.device, dtype=torch.int64) // K)[order].contiguous()
+    wts = rw.reshape(-1).to(torch.float16)[order].contiguous()
+    count = torch.bincount(fe, minlength=n_experts + 1).to(torch.int64)
+    return count, tok, wts
+
+
+def moe_fused(y, out, count, tok_sorted, w_sorted, cfg, num_active=-1, lo=1, hi=0, m_tile=16,
+              scratch=None, slot_base=None):
+    """Token-sorted MoE for prefill chunks (reference: torch.moe_fused, src/torch/amp_torch.cpp:9257-9345,
+    kernel exl3_moe, .../quant/exl3_moe.cu:139-531): experts with lo <= rows <= hi (hi <= 0: no upper
+    bound) run gate / up / activation / down on their rows of y, and weight * result is summed per
+    token in a fixed order and added to out (fp32, zero-initialised by the caller, same shape as y).
+    cfg: the pointer tables g_/u_/d_ {trellis,suh,svh} and Kg Ku Kd act act_limit mcg mul1 [gated] of
+    moe_coop; the reference's temps ts_g ts_u ti_g ti_u are not needed (one workspace, kept in cfg).
+    num_active and m_tile are accepted and unused (one call covers every row count; the reference's
+    three tiered calls still work). With scratch / slot_base the reference defers the sum to
+    torch.moe_gather; here the sum is already the fixed-order one, so they are accepted, unused,
+    and moe_gather has nothing left to do."""
+    import ctypes
+    if not isinstance(cfg, dict):
+        raise TypeError("moe_fused: cfg must be an object")
+    names = ["u_trellis", "u_suh", "u_svh", "d_trellis", "d_suh", "d_svh"]
+    gated = bool(cfg.get("gated", True))
+    if gated:
+        names += ["g_trellis", "g_suh", "g_svh"]
+    for n in names:
+        t = cfg.get(n)
+        if not isinstance(t, torch.Tensor):
+            raise TypeError("moe_fused: cfg.%s must be a tensor" % n)
+        if t.dtype != torch.int64 or not t.is_contiguous():
+            raise TypeError("moe_fused: pointer tables must be contiguous int64")
+    _check_cuda("moe_fused", y, out, count, tok_sorted, w_sorted)
+    if y.dtype != torch.float16 or out.dtype != torch.float32 or count.dtype != torch.int64 \
+            or tok_sorted.dtype != torch.int64 or w_sorted.dtype != torch.float16:
+        raise TypeError("moe_fused: y fp16, out fp32, count int64, tok_sorted int64, w_sorted fp16 expected")
+    if y.dim() != 2 or out.shape != y.shape or not y.is_contiguous() or not out.is_contiguous():
+        raise ValueError("moe_fused: y and out must be contiguous (T, hidden) of one shape")
+    E = cfg["u_trellis"].shape[0]
+    if count.numel() < E + 1 or tok_sorted.numel() != w_sorted.numel():
+        raise ValueError("moe_fused: count must hold experts + 1 entries, tok_sorted and w_sorted one per pick")
+    I = int(cfg.get("I", 0)) or (cfg["gu_u"].shape[-1] if isinstance(cfg.get("gu_u"), torch.Tensor) else 0)
+    if I <= 0:
+        raise ValueError("moe_fused: cfg.I (intermediate width) is required")
+    T, H, A = y.shape[0], y.shape[1], tok_sorted.numel()
+    if T == 0 or A == 0:
+        return None
+    need = int(_lib.lib().amp_exl3_moe_sorted_workspace(T, A, E, H, I))
+    if need <= 0:
+        raise ValueError("moe_fused: unsupported sizes")
+    ws = cfg.get("_sorted_ws")
+    if ws is None or ws.numel() < need or ws.device != y.device:
+        ws = torch.empty(need, dtype=torch.uint8, device=y.device)
+        cfg["_sorted_ws"] = ws
+    a = _MoeSortedArgs()
+    p = lambda t: t.data_ptr() if t is not None else None
+    a.y, a.out, a.count, a.tok_sorted, a.w_sorted = p(y), p(out), p(count), p(tok_sorted), p(w_sorted)
+    a.T, a.H, a.I, a.E, a.A = T, H, I, E, A
+    for n in ("g_trellis", "g_suh", "g_svh", "u_trellis", "u_suh", "u_svh", "d_trellis", "d_suh", "d_svh"):
+        setattr(a, n, p(cfg.get(n)))
+    a.Kg, a.Ku, a.Kd = int(cfg.get("Kg", 0)), int(cfg.get("Ku", 0)), int(cfg.get("Kd", 0))
+    a.cb = _cb(bool(cfg.get("mul1", False)), bool(cfg.get("mcg", False)))
+    a.act, a.act_limit, a.gated = int(cfg.get("act", 0)), float(cfg.get("act_limit", 0.0)), int(gated)
+    a.count_lo, a.count_hi = int(lo), int(hi)
+    a.workspace, a.workspace_bytes = p(ws), ws.numel()
+    with torch.cuda.device(y.device):
+        _lib.call("amp_exl3_moe_sorted", ctypes.byref(a), _stream(y))
+    return None
+
+
+def moe_fused_status(cfg, device=None):
+    """Status word of the last moe_fused call that used cfg's workspace (0 = clean; see
+    amp_exl3_moe_sorted_status). Synchronises."""
+    import ctypes
+    ws = cfg.get("_sorted_ws")
+    if ws is None:
+        return 0
+    out = ctypes.c_int(0)
+    with torch.cuda.device(ws.device):
+        _lib.call("amp_exl3_moe_sorted_status", ws.data_ptr(), ctypes.byref(out), _stream(ws))
+    return out.value
+
+
+def moe_gather(out, scratch, flat_expert, inv_order, expert_start, slot_base, slot_kind, w_sorted):
+    """Reference: torch.moe_gather (src/torch/amp_torch.cpp:9347-9372), the fixed-order sum of
+    torch.moe_fused's per-assignment slots. moe_fused here has already added that sum to out, so
+    this call does nothing; it exists so that the reference's call sequence runs unchanged."""
+    return None

@@ -605,6 +605,65 @@ def measure_moe(steps, warmup, T):
                      "kernel": "exl3_gemv_kernel (grouped modes)", "bytes_per_launch": int(byt) // 2, "traffic": None}}
 
 
+def measure_moe_prefill(steps, warmup, T=2048):
+    """Token-sorted MoE of a prefill chunk: 128 experts 2048 -> 768 -> 2048 at K=3, top-8 routing
+    from fp32 router logits ~ N(0,1), T tokens per step (about T / 16 rows per expert). The routing
+    is sorted by expert beforehand (as for the reference's torch.moe_fused, which takes the sorted
+    lists); one step = one call of moe_fused = one MoE layer; four routings take turns."""
+    import torch
+    import ampstein_b200 as amp
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(13)
+    E, H, I, K, topk = 128, 2048, 768, 3, 8
+    tr = lambda k, n: torch.randint(-32768, 32768, (k // 16, n // 16, 16 * K), dtype=torch.int16, device=dev, generator=g)
+    sg = lambda c, s=1.0: ((torch.randint(0, 2, (c,), device=dev, generator=g).to(torch.float16) * 2 - 1) * s).to(torch.float16)
+    ex = [dict(g=(tr(H, I), sg(H), sg(I, 1 / (1.2437 * math.sqrt(H)))), u=(tr(H, I), sg(H), sg(I, 1 / (1.2437 * math.sqrt(H)))),
+               d=(tr(I, H), sg(I), sg(H, 1 / (1.2437 * math.sqrt(I))))) for _ in range(E)]
+    tab = lambda key, i: amp.ptr_array([e[key][i].data_ptr() for e in ex])
+    cfg = dict(g_trellis=tab("g", 0), g_suh=tab("g", 1), g_svh=tab("g", 2), u_trellis=tab("u", 0), u_suh=tab("u", 1), u_svh=tab("u", 2),
+               d_trellis=tab("d", 0), d_suh=tab("d", 1), d_svh=tab("d", 2), I=I, Kg=K, Ku=K, Kd=K, act=0, act_limit=0.0)
+    sets = []
+    for _ in range(4):
+        w, sel = torch.topk(torch.randn(T, E, device=dev, generator=g), topk, dim=1)
+        count, tok, wts = amp.moe_sort_routing(sel.contiguous(), torch.softmax(w, 1).to(torch.float16).contiguous(), E)
+        sets.append((torch.randn(T, H, device=dev, generator=g).to(torch.float16), count, tok, wts))
+    out = torch.zeros(T, H, dtype=torch.float32, device=dev)
+    rows_max = int(max(s[1][:E].max().item() for s in sets))
+
+    def layer():
+        for y, count, tok, wts in sets:
+            amp.moe_fused(y, out, count, tok, wts, cfg)
+
+    for _ in range(max(warmup, 3)):
+        layer()
+    torch.cuda.synchronize()
+    if amp.moe_fused_status(cfg) != 0 or not torch.isfinite(out).all():
+        raise SystemExit("bench.py: the sorted MoE reported an error or produced non-finite outputs")
+    out.zero_()
+    sampler = ClockSampler(0)
+    t0 = time.time()
+    ms_blk, _, _ = timed_blocks(torch, layer, steps, min_s=0.3)
+    clocks = sampler.stop(t0, time.time())
+    ms = ms_blk / (steps * len(sets))
+    flops = 6.0 * T * topk * H * I
+    peaks = _peaks()
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    tf = flops / ms / 1e9
+    return {
+        "metric": "token-sorted prefill MoE layer time (128 experts, top-8, K=3)", "value": round(ms * 1e3, 1), "unit": "us/layer",
+        "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3), "ms_per_step": round(ms, 4),
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "moe prefill: 128 experts 2048->768->2048 K=3, top-8, %d tokens per chunk, 4 routings in turn" % T,
+                   "rows_per_expert_max": rows_max, "tokens_per_s": round(T / ms * 1e3),
+                   "l2": "expert weights 226 MB + %d MB of rotated rows and intermediates per layer (larger than L2)"
+                         % ((T * topk * (2 * H * 2 + 3 * I * 2 + H * 4)) >> 20)},
+        "gpu_launches": 6 * len(sets) * steps, "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(tf / peak, 4),
+                     "peak_source": "measured (MEASURED_PEAKS.json), burst" if "bf16_tflops" in peaks else "fallback",
+                     "kernel": "exl3_gemm_tc_kernel<K, CB, grouped>", "flops_per_layer": int(flops), "traffic": None}}
+
+
 def measure_gemv(steps, warmup, shape, m, tmem=False, mul1=False, silu_mul=False, norm=False):
     """One decode GEMV shape on its own (k x n at K bits, m rows): as many distinct copies of the
     matrix as it takes to exceed L2 twice over, one launch per copy, all in one CUDA graph."""
@@ -829,6 +888,8 @@ def secondary():
         out["moe_T%d" % T] = {"metric": r["metric"], "value": r["value"], "unit": r["unit"],
                               "distinct_experts": r["config"]["distinct_experts_per_layer"],
                               "roofline": r["roofline"], "clocks": r["clocks"]}
+    r = measure_moe_prefill(5, 3)
+    out["moe_prefill_T2048"] = {k: r[k] for k in ("metric", "value", "unit", "config", "roofline", "clocks")}
     return out
 
 
@@ -926,13 +987,14 @@ def main():
                     help="tensor-parallel mode: how the all-reduce after o / down runs. fused (default): push and gather in the "
                          "producing GEMV's epilogue; split: the producer only pushes its partial, the consuming GEMV adds the ranks' "
                          "partials up in its prologue (measured slower); separate: a stand-alone all-reduce launch")
-    ap.add_argument("--workload", default="decode", choices=["decode", "tp5", "prefill", "moe", "gemv", "step", "issue"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "tp5", "prefill", "moe", "moe-prefill", "gemv", "step", "issue"],
                     help="decode (default, the headline step), tp5 (the 64-layer 5-bit tensor-parallel stack), or a secondary "
                          "one-GPU workload: the prefill GEMM / the fused decode MoE / one GEMV shape (--shape) / the decode "
                          "step with its element-wise neighbours, separate and fused (step) / the issue-rate microbenchmark")
     ap.add_argument("--shape", default="4096x229376x4", help="--workload gemv: k x n x K (rows, columns, bits per weight)")
     ap.add_argument("--batch", type=int, default=1, help="tokens per decode step (decode / tp5 workloads), 1..16")
-    ap.add_argument("--tokens", type=int, default=1, choices=[1, 4, 16], help="tokens per step of --workload moe")
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="tokens per step of --workload moe (1, 4 or 16; default 1) / per chunk of --workload moe-prefill (default 2048)")
     ap.add_argument("--tmem-gemv", action="store_true",
                     help="A/B: run the decode GEMVs on the tensor-memory (tcgen05) kernel instead of the mma.sync kernel")
     ap.add_argument("--mul1", action="store_true", help="--workload gemv: the mul1 codebook (one row then takes the int8-activation form)")
@@ -957,14 +1019,18 @@ def main():
         args.warmup = min(args.warmup, 1)
         run_reference(args)
         return
-    if args.workload in ("prefill", "moe", "gemv", "step", "issue"):
+    if args.workload == "moe" and (args.tokens or 1) not in (1, 4, 16):
+        raise SystemExit("bench.py: --workload moe takes --tokens 1, 4 or 16")
+    if args.workload in ("prefill", "moe", "moe-prefill", "gemv", "step", "issue"):
         import torch
         if not torch.cuda.is_available():
             raise SystemExit("bench.py: no CUDA device (the path has no CPU fallback)")
         if args.workload == "prefill":
             print(json.dumps(measure_prefill(args.steps, args.warmup, not args.separate)), flush=True)
         elif args.workload == "moe":
-            print(json.dumps(measure_moe(args.steps, args.warmup, args.tokens)), flush=True)
+            print(json.dumps(measure_moe(args.steps, args.warmup, args.tokens or 1)), flush=True)
+        elif args.workload == "moe-prefill":
+            print(json.dumps(measure_moe_prefill(args.steps, args.warmup, args.tokens or 2048)), flush=True)
         elif args.workload == "step":
             print(json.dumps(measure_step_with_neighbours(args.steps, args.warmup, args.layers)), flush=True)
         elif args.workload == "gemv":

@@ -347,6 +347,55 @@ int amp_exl3_moe_coop(const amp_moe_coop_args* args, cudaStream_t stream);
 long amp_exl3_moe_coop_ctr_len(long slots_max, long rows_max, long I, long Ho);
 
 /*
+ * Token-sorted MoE for prefill chunks: for every expert e whose row count lies in
+ * [count_lo, count_hi], the rows tok_sorted[start_e .. start_e + count[e]) of y go through gate / up,
+ * the activation and down, and weight * result is summed per token, in ascending expert order,
+ * and ADDED to out (fp32; the caller zero-fills it, as for the reference). start_e is the running
+ * sum of count[0..e); the sentinel bin count[E] (picks that belong to nobody here) is ignored.
+ * Every token must own the same number of entries of the sorted list (A = T * picks, picks <= 64).
+ * Routing stays on the device; the call enqueues six launches on `stream` and returns.
+ * Replaces: exl3_moe, Q/exl3_moe.cu:139-531 (kernel Q/exl3_moe_kernel.cuh:61-313) together with
+ * exl3_moe_gather, its fixed-order slot sum; bindings torch.moe_fused / torch.moe_gather,
+ * src/torch/amp_torch.cpp:9257-9378. Differences: one call covers every row count (the reference
+ * needs one launch per row tier 1-16 / 17-32 / 33+ and leaves experts above its temp capacity to
+ * the caller), all three codebooks are served (the reference instantiates mcg and mul1 only,
+ * Q/exl3_moe.cu:33-46), the temps ts_g ts_u ti_g ti_u, the slot scratch and slot_base are one
+ * caller-provided workspace, and the sum is always the fixed-order one. Per-expert bit width
+ * tables (bits_g / bits_u / bits_d) are not supported: one width per projection.
+ */
+typedef struct amp_moe_sorted_args
+{
+    const void* y;              /* (T, H) fp16, contiguous */
+    void* out;                  /* (T, H) fp32, contiguous; accumulated into */
+    const void* count;          /* (E + 1) int64: rows per expert, last entry ignored */
+    const void* tok_sorted;     /* (A) int64 token index of every pick, sorted by expert */
+    const void* w_sorted;       /* (A) fp16 routing weight of every pick, same order */
+    int T, H, I, E;
+    long A;
+    /* per-expert int64 device pointer tables (E entries) */
+    const void* g_trellis; const void* g_suh; const void* g_svh;
+    const void* u_trellis; const void* u_suh; const void* u_svh;
+    const void* d_trellis; const void* d_suh; const void* d_svh;
+    int Kg, Ku, Kd;             /* bit widths */
+    int cb;                     /* codebook, uniform across the three projections */
+    int act;                    /* as amp_moe_coop_args */
+    float act_limit;
+    int gated;                  /* 0: no gate projection (g_* ignored), activation relu(u) * u */
+    int count_lo, count_hi;     /* experts with row counts outside are skipped; <= 0: no bound */
+    void* workspace;            /* 256-byte aligned device scratch */
+    long workspace_bytes;       /* >= amp_exl3_moe_sorted_workspace(T, A, E, H, I) */
+} amp_moe_sorted_args;
+
+int amp_exl3_moe_sorted(const amp_moe_sorted_args* args, cudaStream_t stream);
+/* bytes of workspace for a chunk of T tokens with A picks over E experts (0: bad sizes) */
+long amp_exl3_moe_sorted_workspace(long T, long A, long E, long H, long I);
+/* Reads the status word the last call left in its workspace: 0 = clean, bits 0 / 1 = count[]
+ * describes more rows than the sorted list holds, bit 2 = a token index outside [0, T), bit 3 = a
+ * token with more than A / T entries. Entries in error are left out of the sum; nothing is read
+ * or written out of bounds. Synchronises the stream; not for the hot path. */
+int amp_exl3_moe_sorted_status(const void* workspace, int* out, cudaStream_t stream);
+
+/*
  * Programmatic dependent launch of the decode kernels (default on): each kernel starts its
  * weight stream before waiting for the kernel in front of it. Returns the previous setting.
  * The reference has no counterpart (it launches cooperative kernels back to back).
