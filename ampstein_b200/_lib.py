@@ -63,6 +63,8 @@ SIGNATURES = {
     "amp_exl3_moe_sorted": [_vp, _vp],
     "amp_exl3_moe_sorted_workspace": [_l, _l, _l, _l, _l],
     "amp_exl3_moe_sorted_status": [_vp, ctypes.POINTER(ctypes.c_int), _vp],
+    "amp_exl3_set_moe_sorted_tile": [_i],
+    "amp_exl3_moe_gather": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _l, _vp],
     "amp_exl3_gemm_bf16": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "amp_exl3_gemm_status": [ctypes.POINTER(ctypes.c_int)],
     "amp_exl3_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],

@@ -206,7 +206,7 @@ __device__ __forceinline__ uint32_t weights2(uint32_t sa, uint32_t sb)
 }
 
 template <int K, int CB, bool GROUPED = false>
-__global__ __launch_bounds__(TC_THREADS, 1)
+__global__ __launch_bounds__(TC_THREADS, GROUPED ? 2 : 1)
 void exl3_gemm_tc_kernel(const TcParams P)
 {
     if constexpr (GROUPED)
@@ -219,6 +219,10 @@ void exl3_gemm_tc_kernel(const TcParams P)
     __shared__ volatile int s_bad;
 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    // grouped instances size an x~ slot and the tensor-memory allocation by the launch's rows per
+    // tile: with 128-row tiles two CTAs share an SM (shared memory, 2 x 128 accumulator columns)
+    const int a_bytes = GROUPED ? P.sub * (TC_BM * TC_BK * 2) : TC_A_BYTES;
+    const uint32_t tmem_cols = GROUPED ? (P.sub == 1 ? 128u : (P.sub == 2 ? 256u : 512u)) : 512u;
     TcSlice W;
     int m0, rows;                                       // first row and valid token rows of this CTA
     if constexpr (GROUPED)
@@ -256,7 +260,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
     __syncwarp();
     if (warp == 0)
     {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&s_tmem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&s_tmem)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -265,7 +269,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
     const uint32_t tmem = s_tmem;
 
     unsigned char* a_base = smem;
-    unsigned char* b_base = smem + TC_A_SLOTS * TC_A_BYTES;
+    unsigned char* b_base = smem + TC_A_SLOTS * a_bytes;
 
     bool ok = true;
     auto wait_bar = [&](uint64_t* bar, uint32_t parity)
@@ -305,7 +309,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
                 mbar_expect_tx(&a_full[s], (uint32_t) rows * 128);
                 const unsigned char* src = W.xt + (((size_t) i * P.M + m0) << 7);
                 for (int sub = 0; sub < nsub; ++sub)
-                    bulk_g2s(a_base + s * TC_A_BYTES + sub * (TC_BM * 128), src + ((size_t) sub * TC_BM << 7),
+                    bulk_g2s(a_base + s * a_bytes + sub * (TC_BM * 128), src + ((size_t) sub * TC_BM << 7),
                              (uint32_t) min(TC_BM, rows - sub * TC_BM) * 128, &a_full[s]);
             }
         }
@@ -327,7 +331,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // descriptors advance by byte offset >> 4 in their low (address) field
-                const uint64_t da = da0 + (uint64_t) ((sa * TC_A_BYTES) >> 4), db = db0 + (uint64_t) ((sb * TC_B_BYTES) >> 4);
+                const uint64_t da = da0 + (uint64_t) ((sa * a_bytes) >> 4), db = db0 + (uint64_t) ((sb * TC_B_BYTES) >> 4);
                 for (int sub = 0; sub < nsub; ++sub)
                     #pragma unroll
                     for (int kk = 0; kk < TC_BK / 16; ++kk)
@@ -352,7 +356,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
         // lane only ever reads what it copied itself
         constexpr int PS = tc_p_stages(K);
         constexpr int SLOT = 32 * 4 * K;
-        const uint32_t pring = smem_u32(smem + TC_A_SLOTS * TC_A_BYTES + TC_B_STAGES * TC_B_BYTES)
+        const uint32_t pring = smem_u32(smem + TC_A_SLOTS * a_bytes + TC_B_STAGES * TC_B_BYTES)
                              + (uint32_t) ((warp - 2) * PS * SLOT + lane * 4 * K);
         #pragma unroll
         for (int j = 0; j < PS - 1; ++j)
@@ -475,7 +479,7 @@ void exl3_gemm_tc_kernel(const TcParams P)
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(tmem_cols) : "memory");
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1044,7 +1048,9 @@ int launch_gemm_tc_grouped(const void* xt, void* c, long Mcap, int k, int n, int
     int dev = 0;
     if (cudaError_t e = cudaGetDevice(&dev)) return cuda_rc(e, "cudaGetDevice");
     tc_fn fn = k_tcg[cb][K - 1];
-    const int smem_bytes = tc_smem_bytes(K);
+    // x~ slots sized by the rows per tile; never below the epilogue's 128 x 132 fp32 staging tile
+    int smem_bytes = 1024 + TC_A_SLOTS * G.sub * (TC_BM * TC_BK * 2) + TC_B_STAGES * TC_B_BYTES + TC_DECODE_WARPS * tc_p_stages(K) * 128 * K;
+    if (smem_bytes < 1024 + 128 * 132 * 4) smem_bytes = 1024 + 128 * 132 * 4;
     if (cudaError_t e = ensure_smem(fn, smem_bytes, dev)) return cuda_rc(e, "exl3_moe_sorted smem attribute");
     TcParams P = {};
     P.xt = (const unsigned char*) xt; P.c = c;

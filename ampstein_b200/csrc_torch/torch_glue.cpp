@@ -7,6 +7,7 @@
 //   exl3_gemm              :3775-3787      exl3_mgemm            :3841-3864
 //   reconstruct            :3832-3839      reconstruct_had_slice :11071-11081
 //   had_r_128              :11062-11069    exl3_moe_coop         :3739-3771
+//   exl3_moe               :7796-7836      exl3_moe_gather, exl3_moe_max_concurrency (same block)
 // Error convention: argument and launch errors throw c10::Error (TORCH_CHECK), which every
 // binding of the reference catches and turns into a script exception (:224-236).
 //
@@ -14,11 +15,11 @@
 // can drive this layer with torch tensors (compile with -DAMP_NO_PYBIND to leave the module out).
 #ifndef AMP_NO_PYBIND
 #include <torch/extension.h>
-#include <map>
-#include <mutex>
 #else
 #include <ATen/ATen.h>
 #endif
+#include <map>
+#include <mutex>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda_runtime.h>
@@ -281,6 +282,123 @@ void exl3_moe_coop(const at::Tensor& x, const at::Tensor& sel, const at::Tensor&
     check_rc(amp_exl3_moe_coop(&a, stream_of(x)), "exl3_moe_coop");
 }
 
+// Token-sorted prefill MoE with the reference's signature (vendor/exl3/exllamav3_ext/quant/exl3_moe.cuh:8-53).
+// The reference's temps (temp_state_*, temp_intermediate_*) are accepted and not used: the kernels
+// here work in one workspace per device that this layer allocates on first use and grows when a
+// larger chunk arrives (no allocation after that). num_active and m_tile only tune the
+// reference's launch and are ignored; experts with more rows than the reference's temps hold
+// (max_tokens_per_expert = temp_state_g.size(1)) are skipped exactly as the reference skips them,
+// so that a caller who routes those through another tier does not get them twice. Per-expert bit
+// tables are not supported.
+void exl3_moe(const at::Tensor& hidden_state, const at::Tensor& output_state, const at::Tensor& expert_count,
+              const at::Tensor& token_sorted, const at::Tensor& weight_sorted,
+              const at::Tensor& temp_state_g, const at::Tensor& temp_state_u,
+              const at::Tensor& temp_intermediate_g, const at::Tensor& temp_intermediate_u,
+              const int act_function, const float K_gate, const float K_up, const float K_down,
+              const at::Tensor& gate_ptrs_trellis, const at::Tensor& gate_ptrs_suh, const at::Tensor& gate_ptrs_svh,
+              const at::Tensor& up_ptrs_trellis, const at::Tensor& up_ptrs_suh, const at::Tensor& up_ptrs_svh,
+              const at::Tensor& down_ptrs_trellis, const at::Tensor& down_ptrs_suh, const at::Tensor& down_ptrs_svh,
+              const bool gate_mcg, const bool gate_mul1, const bool up_mcg, const bool up_mul1,
+              const bool down_mcg, const bool down_mul1, const float act_limit, const int num_active,
+              const c10::optional<at::Tensor>& output_scratch, const c10::optional<at::Tensor>& fused_base,
+              const int count_lo, const int count_hi, const int m_tile,
+              const c10::optional<at::Tensor>& bits_g, const c10::optional<at::Tensor>& bits_u,
+              const c10::optional<at::Tensor>& bits_d)
+{
+    (void) temp_state_u; (void) temp_intermediate_u; (void) m_tile;
+    if (num_active == 0) return;
+    const c10::cuda::CUDAGuard guard(hidden_state.device());
+    TORCH_CHECK(hidden_state.dim() == 2 && hidden_state.scalar_type() == at::kHalf && hidden_state.is_contiguous(),
+                "exl3_moe: hidden_state must be contiguous float16 (bsz, hidden)");
+    TORCH_CHECK(output_state.scalar_type() == at::kFloat && output_state.is_contiguous() && output_state.sizes() == hidden_state.sizes(),
+                "exl3_moe: output_state must be float32 of hidden_state's shape");
+    TORCH_CHECK(expert_count.scalar_type() == at::kLong && expert_count.dim() == 1 && expert_count.is_contiguous(), "exl3_moe: expert_count int64");
+    TORCH_CHECK(token_sorted.scalar_type() == at::kLong && token_sorted.dim() == 1 && token_sorted.is_contiguous() &&
+                weight_sorted.scalar_type() == at::kHalf && weight_sorted.is_contiguous() && weight_sorted.numel() == token_sorted.numel(),
+                "exl3_moe: token_sorted int64 / weight_sorted float16, one entry per pick");
+    TORCH_CHECK(gate_mcg == up_mcg && up_mcg == down_mcg && gate_mul1 == up_mul1 && up_mul1 == down_mul1,
+                "MoE kernel: gate/up/down must share the same codebook");
+    TORCH_CHECK(!bits_g.has_value() && !bits_u.has_value() && !bits_d.has_value(), "exl3_moe: per-expert bit width tables are not supported");
+    TORCH_CHECK(temp_state_g.dim() == 3 && temp_intermediate_g.dim() == 3, "exl3_moe: temps must be 3-D");
+    const int64_t E = expert_count.numel() - 1;
+    for (const at::Tensor* t : { &gate_ptrs_trellis, &gate_ptrs_suh, &gate_ptrs_svh, &up_ptrs_trellis, &up_ptrs_suh, &up_ptrs_svh,
+                                 &down_ptrs_trellis, &down_ptrs_suh, &down_ptrs_svh })
+        TORCH_CHECK(t->scalar_type() == at::kLong && t->is_cuda() && t->is_contiguous() && t->numel() == E,
+                    "exl3_moe: expert tables must be int64 device pointer tables, one entry per expert");
+
+    amp_moe_sorted_args a = {};
+    a.y = hidden_state.data_ptr(); a.out = output_state.data_ptr(); a.count = expert_count.data_ptr();
+    a.tok_sorted = token_sorted.data_ptr(); a.w_sorted = weight_sorted.data_ptr();
+    a.T = (int) hidden_state.size(0); a.H = (int) hidden_state.size(1); a.I = (int) temp_intermediate_g.size(2); a.E = (int) E;
+    a.A = (long) token_sorted.numel();
+    a.g_trellis = gate_ptrs_trellis.data_ptr(); a.g_suh = gate_ptrs_suh.data_ptr(); a.g_svh = gate_ptrs_svh.data_ptr();
+    a.u_trellis = up_ptrs_trellis.data_ptr(); a.u_suh = up_ptrs_suh.data_ptr(); a.u_svh = up_ptrs_svh.data_ptr();
+    a.d_trellis = down_ptrs_trellis.data_ptr(); a.d_suh = down_ptrs_suh.data_ptr(); a.d_svh = down_ptrs_svh.data_ptr();
+    a.Kg = bits_of(K_gate, "exl3_moe"); a.Ku = bits_of(K_up, "exl3_moe"); a.Kd = bits_of(K_down, "exl3_moe");
+    a.cb = codebook(gate_mcg, gate_mul1);
+    // the reference's activation codes (quant/exl3_moe_common.cuh:6-8): 0 silu, 1 gelu, 2 = relu^2 without a gate projection
+    a.gated = act_function == 2 ? 0 : 1;
+    a.act = act_function == 2 ? 2 : act_function;
+    a.act_limit = act_limit;
+    const int cap = (int) temp_state_g.size(1);
+    a.count_lo = count_lo;
+    a.count_hi = count_hi > 0 ? std::min(count_hi, cap) : cap;
+    if (output_scratch.has_value())
+    {
+        TORCH_CHECK(fused_base.has_value(), "exl3_moe: output_scratch needs fused_base");
+        TORCH_CHECK(output_scratch->scalar_type() == at::kFloat && output_scratch->is_contiguous() && output_scratch->dim() == 2 &&
+                    output_scratch->size(1) == hidden_state.size(1), "exl3_moe: output_scratch must be [slots, hidden]");
+        TORCH_CHECK(fused_base->scalar_type() == at::kLong && fused_base->is_contiguous() && fused_base->numel() >= E, "exl3_moe: fused_base int64 per expert");
+        a.scratch = output_scratch->data_ptr(); a.slot_base = fused_base->data_ptr(); a.scratch_rows = (long) output_scratch->size(0);
+    }
+    if (a.T == 0 || a.A == 0) return;
+    const long need = amp_exl3_moe_sorted_workspace(a.T, a.A, a.E, a.H, a.I);
+    TORCH_CHECK(need > 0, "exl3_moe: unsupported sizes");
+    {
+        static std::map<int, at::Tensor> ws;
+        static std::mutex mu;
+        std::lock_guard<std::mutex> lock(mu);
+        at::Tensor& w = ws[hidden_state.get_device()];
+        if (!w.defined() || w.numel() < need)
+            w = at::empty({need}, at::TensorOptions().dtype(at::kByte).device(hidden_state.device()));
+        a.workspace = w.data_ptr(); a.workspace_bytes = (long) w.numel();
+    }
+    check_rc(amp_exl3_moe_sorted(&a, stream_of(hidden_state)), "exl3_moe");
+}
+
+// reference: exl3_moe_gather, vendor/exl3/exllamav3_ext/quant/exl3_moe.cu:472-531
+void exl3_moe_gather(at::Tensor output_state, const at::Tensor& output_scratch, const at::Tensor& flat_expert,
+                     const at::Tensor& inv_order, const at::Tensor& expert_start, const at::Tensor& slot_base,
+                     const at::Tensor& slot_kind, const at::Tensor& weight_sorted)
+{
+    const c10::cuda::CUDAGuard guard(output_state.device());
+    TORCH_CHECK(output_state.scalar_type() == at::kFloat && output_scratch.scalar_type() == at::kFloat && weight_sorted.scalar_type() == at::kHalf,
+                "exl3_moe_gather: output_state / output_scratch float32, weight_sorted float16");
+    for (const at::Tensor* t : { &flat_expert, &inv_order, &expert_start, &slot_base, &slot_kind })
+        TORCH_CHECK(t->scalar_type() == at::kLong && t->is_contiguous(), "exl3_moe_gather: index tensors must be contiguous int64");
+    TORCH_CHECK(output_state.is_contiguous() && output_state.dim() == 2, "exl3_moe_gather: output_state");
+    TORCH_CHECK(output_scratch.is_contiguous() && output_scratch.dim() == 2 && output_scratch.size(1) == output_state.size(1),
+                "exl3_moe_gather: output_scratch must be [slots, hidden]");
+    const int64_t tokens = output_state.size(0), assign = flat_expert.numel(), E = slot_kind.numel();
+    if (!tokens) return;
+    TORCH_CHECK(assign % tokens == 0 && inv_order.numel() == assign, "exl3_moe_gather: assignments / tokens");
+    TORCH_CHECK(slot_base.numel() >= E && expert_start.numel() >= E, "exl3_moe_gather: table sizes");
+    check_rc(amp_exl3_moe_gather((float*) output_state.data_ptr(), (const float*) output_scratch.data_ptr(), flat_expert.data_ptr(),
+                                 inv_order.data_ptr(), expert_start.data_ptr(), slot_base.data_ptr(), slot_kind.data_ptr(),
+                                 weight_sorted.data_ptr(), (int) tokens, (int) output_state.size(1), (int) (assign / tokens), (int) E,
+                                 (long) output_scratch.size(0), stream_of(output_state)),
+             "exl3_moe_gather");
+}
+
+// The reference sizes its temps by this (SMs / 8 expert groups, quant/exl3_moe.cu:15-19); callers
+// keep working, the temps they allocate from it are simply not used here.
+int exl3_moe_max_concurrency(int device)
+{
+    int sms = 0;
+    TORCH_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess, "exl3_moe_max_concurrency: bad device");
+    return sms / 8;
+}
+
 // same arguments as the reference's exl3_moe_coop_ctr_len (vendor/exl3/exllamav3_ext/quant/exl3_moe_coop.cuh:164-167)
 int64_t exl3_moe_coop_ctr_len(int64_t slots_max, int64_t bsz_max, int64_t I, int64_t Ho)
 {
@@ -298,5 +416,8 @@ PYBIND11_MODULE(_torch_glue, m)
     m.def("had_r_128", &had_r_128);
     m.def("exl3_moe_coop", &exl3_moe_coop);
     m.def("exl3_moe_coop_ctr_len", &exl3_moe_coop_ctr_len);
+    m.def("exl3_moe", &exl3_moe);
+    m.def("exl3_moe_gather", &exl3_moe_gather);
+    m.def("exl3_moe_max_concurrency", &exl3_moe_max_concurrency);
 }
 #endif

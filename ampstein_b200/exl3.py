@@ -597,15 +597,18 @@ class _MoeSortedArgs(__import__("ctypes").Structure):
         ("Kg", _c.c_int), ("Ku", _c.c_int), ("Kd", _c.c_int), ("cb", _c.c_int), ("act", _c.c_int),
         ("act_limit", _c.c_float), ("gated", _c.c_int), ("count_lo", _c.c_int), ("count_hi", _c.c_int),
         ("workspace", _c.c_void_p), ("workspace_bytes", _c.c_long),
+        ("scratch", _c.c_void_p), ("slot_base", _c.c_void_p), ("scratch_rows", _c.c_long),
     ]
 
 
-def moe_sort_routing(sel, rw, n_experts, e0=0):
+def moe_sort_routing(sel, rw, n_experts, e0=0, with_inverse=False):
     """Routing of a prefill chunk sorted by expert, as the reference prepares it for torch.moe_fused
     (moe_sorted_begin, src/ucode/ampstein/glm5.uc:1096-1170): sel / rw (T, picks) -> count
     (n_experts + 1) int64, tok_sorted (T * picks) int64, w_sorted (T * picks) fp16. Picks outside
     [e0, e0 + n_experts) fall into the sentinel bin n_experts, which no kernel touches. The sort is
-    stable: inside an expert the rows keep their token order."""
+    stable: inside an expert the rows keep their token order. with_inverse: also the tables
+    torch.moe_gather takes -- flat_expert (local expert of every pick), inv_order (each pick's
+    position in the sorted list) and start (first sorted position of every bin)."""
     T, K = sel.shape
     fe = sel.reshape(-1).to(torch.int64) - int(e0)
     fe = torch.where((fe < 0) | (fe >= n_experts), torch.full_like(fe, n_experts), fe)
@@ -613,6 +616,11 @@ def moe_sort_routing(sel, rw, n_experts, e0=0):
     tok = (torch.arange(T * K, device=sel.device, dtype=torch.int64) // K)[order].contiguous()
     wts = rw.reshape(-1).to(torch.float16)[order].contiguous()
     count = torch.bincount(fe, minlength=n_experts + 1).to(torch.int64)
+    if with_inverse:
+        inv = torch.empty_like(order)
+        inv[order] = torch.arange(order.numel(), device=order.device, dtype=torch.int64)
+        start = (torch.cumsum(count, 0) - count).contiguous()
+        return count, tok, wts, fe.contiguous(), inv, start
     return count, tok, wts
 
 
@@ -625,9 +633,9 @@ def moe_fused(y, out, count, tok_sorted, w_sorted, cfg, num_active=-1, lo=1, hi=
     cfg: the pointer tables g_/u_/d_ {trellis,suh,svh} and Kg Ku Kd act act_limit mcg mul1 [gated] of
     moe_coop; the reference's temps ts_g ts_u ti_g ti_u are not needed (one workspace, kept in cfg).
     num_active and m_tile are accepted and unused (one call covers every row count; the reference's
-    three tiered calls still work). With scratch / slot_base the reference defers the sum to
-    torch.moe_gather; here the sum is already the fixed-order one, so they are accepted, unused,
-    and moe_gather has nothing left to do."""
+    three tiered calls still work). With scratch (fp32 [slots, hidden]) and slot_base (int64 per
+    expert) the sum is deferred as in the reference: out is left alone, weight * result of every
+    assignment goes to its slot, and moe_gather adds the slots up in pick order."""
     import ctypes
     if not isinstance(cfg, dict):
         raise TypeError("moe_fused: cfg must be an object")
@@ -674,6 +682,14 @@ def moe_fused(y, out, count, tok_sorted, w_sorted, cfg, num_active=-1, lo=1, hi=
     a.act, a.act_limit, a.gated = int(cfg.get("act", 0)), float(cfg.get("act_limit", 0.0)), int(gated)
     a.count_lo, a.count_hi = int(lo), int(hi)
     a.workspace, a.workspace_bytes = p(ws), ws.numel()
+    if (scratch is None) != (slot_base is None):
+        raise ValueError("moe_fused: scratch needs slot_base")
+    if scratch is not None:
+        _check_cuda("moe_fused", scratch, slot_base)
+        if scratch.dtype != torch.float32 or scratch.dim() != 2 or scratch.shape[1] != H or slot_base.dtype != torch.int64 \
+                or slot_base.numel() < E:
+            raise TypeError("moe_fused: scratch must be fp32 [slots, hidden], slot_base int64 with one entry per expert")
+        a.scratch, a.slot_base, a.scratch_rows = p(scratch), p(slot_base), scratch.shape[0]
     with torch.cuda.device(y.device):
         _lib.call("amp_exl3_moe_sorted", ctypes.byref(a), _stream(y))
     return None
@@ -693,7 +709,30 @@ def moe_fused_status(cfg, device=None):
 
 
 def moe_gather(out, scratch, flat_expert, inv_order, expert_start, slot_base, slot_kind, w_sorted):
-    """Reference: torch.moe_gather (src/torch/amp_torch.cpp:9347-9372), the fixed-order sum of
-    torch.moe_fused's per-assignment slots. moe_fused here has already added that sum to out, so
-    this call does nothing; it exists so that the reference's call sequence runs unchanged."""
+    """Reference: torch.moe_gather (src/torch/amp_torch.cpp:9347-9372, exl3_moe_gather): the fixed-order
+    reduction of moe_fused's per-assignment slots. Every token's picks are summed in pick order and
+    added to its row of out (fp32). flat_expert: (T * picks) local expert id per assignment;
+    inv_order: position of each assignment in the expert-sorted list; expert_start / slot_base /
+    slot_kind: per-expert tables (kind 0 = no slots, 1 = slots hold weighted outputs, 2 = unweighted:
+    multiplied by w_sorted here)."""
+    _check_cuda("moe_gather", out, scratch, flat_expert, inv_order, expert_start, slot_base, slot_kind, w_sorted)
+    if out.dtype != torch.float32 or scratch.dtype != torch.float32 or w_sorted.dtype != torch.float16:
+        raise TypeError("moe_gather: out and scratch fp32, w_sorted fp16 expected")
+    for t in (flat_expert, inv_order, expert_start, slot_base, slot_kind):
+        if t.dtype != torch.int64:
+            raise TypeError("moe_gather: index tensors must be int64")
+    if out.dim() != 2 or scratch.dim() != 2 or scratch.shape[1] != out.shape[1]:
+        raise ValueError("moe_gather: scratch must be [slots, hidden]")
+    T, H = out.shape
+    if T == 0:
+        return None
+    if flat_expert.numel() % T or inv_order.numel() != flat_expert.numel():
+        raise ValueError("moe_gather: assignments / tokens")
+    E = slot_kind.numel()
+    if slot_base.numel() < E or expert_start.numel() < E:
+        raise ValueError("moe_gather: table sizes")
+    with torch.cuda.device(out.device):
+        _lib.call("amp_exl3_moe_gather", out.data_ptr(), scratch.data_ptr(), flat_expert.data_ptr(), inv_order.data_ptr(),
+                  expert_start.data_ptr(), slot_base.data_ptr(), slot_kind.data_ptr(), w_sorted.data_ptr(),
+                  T, H, flat_expert.numel() // T, E, scratch.shape[0], _stream(out))
     return None

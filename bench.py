@@ -1003,6 +1003,8 @@ def main():
     ap.add_argument("--no-int8", action="store_true", help="--workload gemv --mul1: keep the fp16 kernel (A/B)")
     ap.add_argument("--separate", action="store_true",
                     help="--workload prefill: seven separate GEMM calls instead of the q|k|v and gate|up bundles")
+    ap.add_argument("--tile-sub", type=int, default=0, choices=[0, 1, 2, 4],
+                    help="--workload moe-prefill: rows per GEMM tile / 128 (A/B; default 0 = chosen per call)")
     ap.add_argument("--no-secondary", action="store_true",
                     help="decode workload on one GPU: skip the per-shape and secondary measurements (profiler captures)")
     ap.add_argument("--layers", type=int, default=0,
@@ -1030,6 +1032,9 @@ def main():
         elif args.workload == "moe":
             print(json.dumps(measure_moe(args.steps, args.warmup, args.tokens or 1)), flush=True)
         elif args.workload == "moe-prefill":
+            if args.tile_sub:
+                from ampstein_b200 import _lib
+                _lib.lib().amp_exl3_set_moe_sorted_tile(args.tile_sub)
             print(json.dumps(measure_moe_prefill(args.steps, args.warmup, args.tokens or 2048)), flush=True)
         elif args.workload == "step":
             print(json.dumps(measure_step_with_neighbours(args.steps, args.warmup, args.layers)), flush=True)

@@ -360,7 +360,8 @@ long amp_exl3_moe_coop_ctr_len(long slots_max, long rows_max, long I, long Ho);
  * needs one launch per row tier 1-16 / 17-32 / 33+ and leaves experts above its temp capacity to
  * the caller), all three codebooks are served (the reference instantiates mcg and mul1 only,
  * Q/exl3_moe.cu:33-46), the temps ts_g ts_u ti_g ti_u, the slot scratch and slot_base are one
- * caller-provided workspace, and the sum is always the fixed-order one. Per-expert bit width
+ * caller-provided workspace, and without a slot scratch the sum is a fixed-order one made by the
+ * call itself (the reference adds atomically in arrival order then). Per-expert bit width
  * tables (bits_g / bits_u / bits_d) are not supported: one width per projection.
  */
 typedef struct amp_moe_sorted_args
@@ -372,7 +373,7 @@ typedef struct amp_moe_sorted_args
     const void* w_sorted;       /* (A) fp16 routing weight of every pick, same order */
     int T, H, I, E;
     long A;
-    /* per-expert int64 device pointer tables (E entries) */
+    /* per-expert int64 device pointer tables (E entries); every tensor they name 16-byte aligned */
     const void* g_trellis; const void* g_suh; const void* g_svh;
     const void* u_trellis; const void* u_suh; const void* u_svh;
     const void* d_trellis; const void* d_suh; const void* d_svh;
@@ -384,11 +385,34 @@ typedef struct amp_moe_sorted_args
     int count_lo, count_hi;     /* experts with row counts outside are skipped; <= 0: no bound */
     void* workspace;            /* 256-byte aligned device scratch */
     long workspace_bytes;       /* >= amp_exl3_moe_sorted_workspace(T, A, E, H, I) */
+    /* deferred sum (nullable; the reference's output_scratch / fused_base): with scratch set, out is
+     * left alone and weight * result of the r-th row of expert e is stored in scratch row
+     * slot_base[e] + r, for amp_exl3_moe_gather to add up */
+    void* scratch;              /* (scratch_rows, H) fp32 */
+    const void* slot_base;      /* (E) int64 */
+    long scratch_rows;
 } amp_moe_sorted_args;
 
 int amp_exl3_moe_sorted(const amp_moe_sorted_args* args, cudaStream_t stream);
+/*
+ * Fixed-order sum of per-assignment slots: for every token, the slots of its picks k = 0 .. topk - 1
+ * are added in that order (fp32) and the sum is added to out (T, H). Pick a = token * topk + k of
+ * local expert e = flat_expert[a] (outside [0, E): no slot) owns slot slot_base[e] + inv_order[a] -
+ * expert_start[e] when slot_kind[e] != 0; kind 1 slots hold weighted rows, kind 2 unweighted ones,
+ * multiplied here by w_sorted[inv_order[a]]. All index tensors int64 on the device. Same arguments
+ * and meaning as the reference's exl3_moe_gather, Q/exl3_moe.cu:472-531; slots outside
+ * [0, scratch_rows) are skipped instead of read.
+ */
+int amp_exl3_moe_gather(float* out, const float* scratch, const void* flat_expert, const void* inv_order,
+                        const void* expert_start, const void* slot_base, const void* slot_kind, const void* w_sorted,
+                        int T, int H, int topk, int E, long scratch_rows, cudaStream_t stream);
 /* bytes of workspace for a chunk of T tokens with A picks over E experts (0: bad sizes) */
 long amp_exl3_moe_sorted_workspace(long T, long A, long E, long H, long I);
+/* Rows per GEMM tile of amp_exl3_moe_sorted in units of 128 (one tile = rows of one expert whose
+ * weight block a CTA decodes once): 0 (default) = chosen per call from the average rows per expert,
+ * 1..4 forced; for A/B measurements. Returns the previous setting. No reference counterpart (its
+ * row tiers are the caller's m_tile argument). */
+int amp_exl3_set_moe_sorted_tile(int sub);
 /* Reads the status word the last call left in its workspace: 0 = clean, bits 0 / 1 = count[]
  * describes more rows than the sorted list holds, bit 2 = a token index outside [0, T), bit 3 = a
  * token with more than A / T entries. Entries in error are left out of the sum; nothing is read

@@ -28,6 +28,36 @@ def available():
     return os.path.exists(SO)
 
 
+# ---- the reference's token-sorted prefill MoE (libexl3_ref_moe.so, Makefile.ref target `moe`) ----
+MOE_SO = os.path.join(ROOT, "oracle", "_ref", "libexl3_ref_moe.so")
+_moe_lib = None
+
+
+class RefMoeSortedArgs(ctypes.Structure):
+    _fields_ = [("y", ctypes.c_void_p), ("out", ctypes.c_void_p), ("count", ctypes.c_void_p), ("tok", ctypes.c_void_p),
+                ("w", ctypes.c_void_p),
+                ("T", ctypes.c_int), ("H", ctypes.c_int), ("I", ctypes.c_int), ("E", ctypes.c_int), ("A", ctypes.c_long),
+                ("tables", ctypes.c_void_p * 9),
+                ("K", ctypes.c_int), ("cb", ctypes.c_int), ("act", ctypes.c_int), ("act_limit", ctypes.c_float),
+                ("ts_g", ctypes.c_void_p), ("ts_u", ctypes.c_void_p), ("ti_g", ctypes.c_void_p), ("ti_u", ctypes.c_void_p),
+                ("conc", ctypes.c_int), ("cap", ctypes.c_int),
+                ("lo", ctypes.c_int), ("hi", ctypes.c_int), ("m_tile", ctypes.c_int), ("num_active", ctypes.c_int)]
+
+
+def moe_available():
+    return os.path.exists(MOE_SO)
+
+
+def moe_lib():
+    global _moe_lib
+    if _moe_lib is None:
+        import torch  # noqa: F401  (libtorch must be loaded first)
+        _moe_lib = ctypes.CDLL(MOE_SO)
+        _moe_lib.ref_exl3_moe_sorted.argtypes = [ctypes.POINTER(RefMoeSortedArgs), ctypes.c_int]
+        _moe_lib.ref_exl3_moe_concurrency.argtypes = [ctypes.c_int]
+    return _moe_lib
+
+
 def lib():
     global _lib
     if _lib is None:

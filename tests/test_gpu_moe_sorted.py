@@ -110,6 +110,46 @@ def test_sorted_moe_activations_codebooks_and_no_gate(amp, oracle, act, gated, l
     check(got, ref)
 
 
+def test_sorted_moe_deferred_slots_and_gather(amp, oracle):
+    """The reference's reproducible mode: moe_fused stores weight * result of every assignment in its
+    slot (slot = sorted position, as src/ucode/ampstein/glm5.uc:1204-1221 sets it up) and leaves out
+    alone; moe_gather adds every token's slots in pick order. Also slots of kind 2 (unweighted rows
+    of another tier, weighted by the gather)."""
+    E, H, I, K, topk, T = 8, 256, 128, 3, 3, 70
+    ex = make_experts(E, H, I, H, K, seed=3500)
+    rng = np.random.default_rng(61)
+    x = rng.standard_normal((T, H)).astype(np.float16)
+    sel, rw = routing(rng, T, E, topk)
+    cfg = build_cfg(amp, ex, H, I, H, H, K, 1, topk)
+    cfg["I"] = I
+    direct, _ = run_sorted(amp, cfg, x, sel, rw, E)
+    xd = dev(x)
+    count, tok, wts, fe, inv, start = amp.moe_sort_routing(dev(sel), dev(rw), E, 0, with_inverse=True)
+    A = T * topk
+    scratch = torch.full((A, H), float("nan"), dtype=torch.float32, device="cuda")
+    out = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    amp.moe_fused(xd, out, count, tok, wts, cfg, -1, 1, 0, 16, scratch, start)
+    torch.cuda.synchronize()
+    assert amp.moe_fused_status(cfg) == 0
+    assert not out.any() and torch.isfinite(scratch).all()
+    kind = (count[:E] > 0).to(torch.int64)
+    amp.moe_gather(out, scratch, fe, inv, start[:E].contiguous(), start[:E].contiguous(), kind, wts)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    assert np.allclose(got, direct, rtol=1e-5, atol=1e-6)          # same terms, pick order instead of expert order
+    check(got, oracle.moe_coop(x, sel, rw, ex, gu_f16=True))
+    # kind 2: the same rows unweighted, the gather applies the weights
+    unweighted = (scratch / wts.float()[:, None]).contiguous()
+    out2 = torch.zeros_like(out)
+    amp.moe_gather(out2, unweighted, fe, inv, start[:E].contiguous(), start[:E].contiguous(), kind * 2, wts)
+    torch.cuda.synchronize()
+    assert np.allclose(out2.cpu().numpy(), got, rtol=1e-4, atol=1e-5)
+    # a slot scratch that is too short is reported, not overrun
+    short = torch.zeros((A // 2, H), dtype=torch.float32, device="cuda")
+    amp.moe_fused(xd, out, count, tok, wts, cfg, -1, 1, 0, 16, short, start)
+    assert amp.moe_fused_status(cfg) & 16
+
+
 def test_sorted_moe_gate_and_up_of_different_widths(amp, oracle):
     """Kg != Ku: gate and up run as two grouped launches instead of one."""
     E, H, I, topk, T = 4, 256, 128, 2, 64

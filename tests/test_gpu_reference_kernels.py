@@ -340,3 +340,82 @@ def test_timing_table(amp):
     if os.path.isdir(out_dir):
         json.dump(rows, open(os.path.join(out_dir, "ref_kernel_timing.json"), "w"), indent=1)
     assert all(r["ours_us"] > 0 and r["reference_us"] > 0 for r in rows)
+
+
+@pytest.mark.skipif(not ref_kernels.moe_available(), reason="reference prefill MoE not built")
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("cbname,T", [("mcg", 512), ("mul1", 512), ("mul1", 2048)])
+def test_sorted_moe_next_to_the_reference_kernel(amp, cbname, T):
+    """The reference's token-sorted prefill MoE kernel (exl3_moe, instantiated for the mcg and mul1
+    codebooks only) and this library's moe_fused on the same routing: 128 experts 2048 -> 768 ->
+    2048 at K = 3, top-8. Outputs within 2e-2 of each other (the tolerance of the reference's fused-MoE
+    tests); both timed with CUDA events. The reference is called as its own caller does
+    (src/ucode/ampstein/glm5.uc:1212-1230): three row tiers for mul1, one 16-row tier for mcg, experts
+    up to 256 rows, atomic accumulation (its faster mode)."""
+    from test_gpu_moe import build_cfg
+    E, H, I, K, topk = 128, 2048, 768, 3, 8
+    cb = {"mcg": 1, "mul1": 2}[cbname]
+    ex, _, _, _ = moe_case(1, E, H, I, H, K, topk, seed=888)
+    rng = np.random.default_rng(T)
+    x = rng.standard_normal((T, H)).astype(np.float16)
+    logits = rng.standard_normal((T, E)).astype(np.float32)
+    sel = np.argsort(-logits, axis=1)[:, :topk].astype(np.int64)
+    w = np.take_along_axis(logits, sel, axis=1)
+    rw = (np.exp(w) / np.exp(w).sum(axis=1, keepdims=True)).astype(np.float16)
+    cfg = build_cfg(amp, ex, H, I, H, H, K, 1, topk, **{cbname: True})
+    cfg["I"] = I
+    xd = dev(x)
+    count, tok, wts = amp.moe_sort_routing(dev(sel), dev(rw), E)
+    assert int(count[:E].max()) <= 256
+    mine = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    ours_call = lambda: amp.moe_fused(xd, mine, count, tok, wts, cfg)
+    ours_call()
+    torch.cuda.synchronize()
+    assert amp.moe_fused_status(cfg) == 0
+
+    L = ref_kernels.moe_lib()
+    conc = L.ref_exl3_moe_concurrency(0)
+    assert conc > 0
+    cap = 256
+    z = lambda shape: torch.zeros(shape, dtype=torch.float16, device="cuda")
+    temps = [z((conc, cap, H)), z((conc, cap, H)), z((conc, cap, I)), z((conc, cap, I))]
+    ref_out = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    a = ref_kernels.RefMoeSortedArgs()
+    a.y, a.out, a.count, a.tok, a.w = xd.data_ptr(), ref_out.data_ptr(), count.data_ptr(), tok.data_ptr(), wts.data_ptr()
+    a.T, a.H, a.I, a.E, a.A = T, H, I, E, tok.numel()
+    for i, n in enumerate(("g_trellis", "g_suh", "g_svh", "u_trellis", "u_suh", "u_svh", "d_trellis", "d_suh", "d_svh")):
+        a.tables[i] = cfg[n].data_ptr()
+    a.K, a.cb, a.act, a.act_limit = K, cb, 0, 0.0
+    a.ts_g, a.ts_u, a.ti_g, a.ti_u = (t.data_ptr() for t in temps)
+    a.conc, a.cap, a.num_active = conc, cap, -1
+    tiers = [(33, cap, 64), (17, 32, 32), (1, 16, 16)] if cbname == "mul1" else [(1, cap, 16)]
+
+    def ref_call():
+        for lo, hi, mt in tiers:
+            a.lo, a.hi, a.m_tile = lo, hi, mt
+            assert L.ref_exl3_moe_sorted(ctypes.byref(a), 0) == 0
+
+    torch.cuda.synchronize()
+    ref_call()
+    torch.cuda.synchronize()
+    r, m = ref_out.cpu().numpy(), mine.cpu().numpy()
+    assert np.all(np.isfinite(r)) and rel(m, r) < 2e-2, rel(m, r)
+
+    def time_us(fn, reps=5):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    row = dict(case="token-sorted MoE 128 experts top-8 K3 %s, %d tokens" % (cbname, T),
+               ours_us=round(time_us(ours_call), 1), reference_us=round(time_us(ref_call), 1), max_rel_diff=float(rel(m, r)))
+    print(row)
+    out_dir = os.path.join(ROOT, "gpurun_out")
+    if os.path.isdir(out_dir):
+        with open(os.path.join(out_dir, "ref_moe_sorted_timing.jsonl"), "a") as f:
+            f.write(json.dumps(row) + "\n")

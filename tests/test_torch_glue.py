@@ -17,7 +17,8 @@ def glue():
 
 
 def test_glue_exports_reference_names(glue):
-    for name in ("exl3_gemm", "exl3_mgemm", "reconstruct", "reconstruct_had_slice", "had_r_128", "exl3_moe_coop"):
+    for name in ("exl3_gemm", "exl3_mgemm", "reconstruct", "reconstruct_had_slice", "had_r_128", "exl3_moe_coop",
+                 "exl3_moe", "exl3_moe_gather", "exl3_moe_max_concurrency"):
         assert callable(getattr(glue, name))
 
 
@@ -97,3 +98,58 @@ def test_glue_mgemm_stacked(glue, amp, oracle):
         ref = oracle.linear(x, t, s, v, 0, fp32_out=True)
         err = np.max(np.abs(C[i].float().cpu().numpy() - ref)) / np.max(np.abs(ref))
         assert err < 1e-2
+
+
+@pytest.mark.gpu
+def test_glue_sorted_moe_with_the_reference_call_sequence(glue, amp, oracle):
+    """exl3_moe / exl3_moe_gather with the reference's argument lists, called the way its runtime calls
+    them (src/ucode/ampstein/glm5.uc:1204-1230): three row tiers, once adding straight into the
+    output and once through the per-assignment slots + gather. Experts with more rows than the
+    reference's temps hold are left to the caller, as in the reference."""
+    from test_gpu_moe import build_cfg, make_experts
+    from test_gpu_moe_sorted import routing
+    E, H, I, K, topk, T = 8, 256, 128, 4, 2, 120
+    ex = make_experts(E, H, I, H, K, seed=7500)
+    rng = np.random.default_rng(75)
+    x = rng.standard_normal((T, H)).astype(np.float16)
+    sel, rw = routing(rng, T, E, topk)
+    cfg = build_cfg(amp, ex, H, I, H, H, K, 1, topk)
+    xd = dev(x)
+    count, tok, wts, fe, inv, start = amp.moe_sort_routing(dev(sel), dev(rw), E, 0, with_inverse=True)
+    conc, cap = glue.exl3_moe_max_concurrency(0), 64
+    assert conc == torch.cuda.get_device_properties(0).multi_processor_count // 8
+    z = lambda *shape: torch.zeros(shape, dtype=torch.float16, device="cuda")
+    temps = (z(conc, cap, H), z(conc, cap, H), z(conc, cap, I), z(conc, cap, I))
+    tabs = [cfg[n] for n in ("g_trellis", "g_suh", "g_svh", "u_trellis", "u_suh", "u_svh", "d_trellis", "d_suh", "d_svh")]
+
+    def fused(out, scratch=None, base=None):
+        for lo, hi, mt in ((33, cap, 64), (17, 32, 32), (1, 16, 16)):
+            glue.exl3_moe(xd, out, count, tok, wts, *temps, 0, float(K), float(K), float(K), *tabs,
+                          False, False, False, False, False, False, 0.0, -1, scratch, base, lo, hi, mt, None, None, None)
+
+    out = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    fused(out)
+    torch.cuda.synchronize()
+    ref = oracle.moe_coop(x, sel, rw, ex, gu_f16=True)
+    got = out.cpu().numpy()
+    err = np.max(np.abs(got - ref)) / np.max(np.abs(ref))
+    assert err < 1e-2, err
+    scratch = torch.zeros((T * topk, H), dtype=torch.float32, device="cuda")
+    out2 = torch.zeros_like(out)
+    fused(out2, scratch, start)
+    assert not out2.any()
+    kind = (count[:E] > 0).to(torch.int64)
+    glue.exl3_moe_gather(out2, scratch, fe, inv, start[:E].contiguous(), start[:E].contiguous(), kind, wts)
+    torch.cuda.synchronize()
+    assert np.allclose(out2.cpu().numpy(), got, rtol=1e-5, atol=1e-6)
+    # an expert above the temps' capacity is skipped (the caller's heavy tier handles it)
+    small = tuple(t[:, :8].contiguous() for t in temps)
+    out3 = torch.zeros_like(out)
+    glue.exl3_moe(xd, out3, count, tok, wts, *small, 0, float(K), float(K), float(K), *tabs,
+                  False, False, False, False, False, False, 0.0, -1, None, None, 1, 8, 16, None, None, None)
+    torch.cuda.synchronize()
+    light = [e for e in range(E) if 0 < int(count[e]) <= 8]
+    assert bool(out3.any()) == bool(light)
+    with pytest.raises(RuntimeError):
+        glue.exl3_moe(xd, out3.half(), count, tok, wts, *temps, 0, float(K), float(K), float(K), *tabs,
+                      False, False, False, False, False, False, 0.0, -1, None, None, 1, cap, 16, None, None, None)
