@@ -204,16 +204,17 @@ struct MsRot
     const __half* gu; int I; const long long* d_suh; int act, gated; float act_limit;
 };
 
-// 128-point Hadamard with four lanes per 128-value chunk: lane quarter q holds elements 32q ..
-// 32q + 31. Same butterflies in the same order as warp_had128 (index bits 0..4 inside the lane,
-// then bits 5 and 6 across the four lanes; lower = a + b, upper = a - b), hence the same bits out,
-// with 2 shuffles per value instead of 5: the rotation kernels below were bound by the shuffle pipe.
-__device__ __forceinline__ void quad_had128(float (&h)[32], int q)
+// 128-point Hadamard with eight lanes per 128-value chunk: lane piece pc (0..7) holds the two 16-byte
+// pieces (eight values each) at elements 8 pc .. and 64 + 8 pc .. . Same butterflies in the same
+// order as warp_had128 (index bits 0..6 in turn; lower = a + b, upper = a - b), hence the same bits
+// out: bits 0-2 and 6 inside the lane, bits 3-5 across the eight lanes. 3 shuffles per value
+// instead of 5, and both the loads and the stores of a chunk are whole 128-byte lines per eight lanes.
+__device__ __forceinline__ void oct_had128(float (&h)[16], int pc)
 {
     #pragma unroll
-    for (int b = 1; b < 32; b <<= 1)
+    for (int b = 1; b < 8; b <<= 1)
         #pragma unroll
-        for (int i = 0; i < 32; ++i)
+        for (int i = 0; i < 16; ++i)
             if (!(i & b))
             {
                 const float lo = h[i], hi = h[i | b];
@@ -221,55 +222,62 @@ __device__ __forceinline__ void quad_had128(float (&h)[32], int q)
                 h[i | b] = lo - hi;
             }
     #pragma unroll
-    for (int m = 1; m <= 2; m <<= 1)
+    for (int m = 1; m <= 4; m <<= 1)
     {
-        const bool up = (q & m) != 0;
+        const bool up = (pc & m) != 0;
         #pragma unroll
-        for (int i = 0; i < 32; ++i)
+        for (int i = 0; i < 16; ++i)
         {
             const float p = __shfl_xor_sync(0xffffffffu, h[i], m);
             h[i] = up ? p - h[i] : h[i] + p;
         }
     }
+    #pragma unroll
+    for (int i = 0; i < 8; ++i)
+    {
+        const float lo = h[i], hi = h[i + 8];
+        h[i] = lo + hi;
+        h[i + 8] = lo - hi;
+    }
 }
 
-// a lane's 32 rotated values -> their place in the k-step-major, swizzled layout (see
-// had_tiled_kernel): k step 2 * chunk + q / 2, four 16-byte pieces (4 * (q & 1) + i) ^ (row & 7)
-__device__ __forceinline__ void ms_store_quarter(unsigned char* xt, int mcap, int p, int cb, int q, const float (&h)[32])
+// a lane's 16 rotated values -> their place in the k-step-major, swizzled layout (see
+// had_tiled_kernel): k steps 2 * chunk and 2 * chunk + 1, 16-byte piece pc ^ (row & 7) of each
+__device__ __forceinline__ void ms_store_pieces(unsigned char* xt, int mcap, int p, int cb, int pc, const float (&h)[16])
 {
-    unsigned char* row = xt + (((size_t) (2 * cb + (q >> 1)) * (size_t) mcap + (size_t) p) << 7);
     #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int j = 0; j < 2; ++j)
     {
-        const __half2 a = __floats2half2_rn(h[8 * i + 0] * kRScale, h[8 * i + 1] * kRScale);
-        const __half2 b = __floats2half2_rn(h[8 * i + 2] * kRScale, h[8 * i + 3] * kRScale);
-        const __half2 c = __floats2half2_rn(h[8 * i + 4] * kRScale, h[8 * i + 5] * kRScale);
-        const __half2 d = __floats2half2_rn(h[8 * i + 6] * kRScale, h[8 * i + 7] * kRScale);
+        const __half2 a = __floats2half2_rn(h[8 * j + 0] * kRScale, h[8 * j + 1] * kRScale);
+        const __half2 b = __floats2half2_rn(h[8 * j + 2] * kRScale, h[8 * j + 3] * kRScale);
+        const __half2 c = __floats2half2_rn(h[8 * j + 4] * kRScale, h[8 * j + 5] * kRScale);
+        const __half2 d = __floats2half2_rn(h[8 * j + 6] * kRScale, h[8 * j + 7] * kRScale);
         uint4 o;
         o.x = *reinterpret_cast<const uint32_t*>(&a); o.y = *reinterpret_cast<const uint32_t*>(&b);
         o.z = *reinterpret_cast<const uint32_t*>(&c); o.w = *reinterpret_cast<const uint32_t*>(&d);
-        *reinterpret_cast<uint4*>(row + ((((4 * (q & 1) + i) ^ (p & 7))) << 4)) = o;
+        unsigned char* row = xt + (((size_t) (2 * cb + j) * (size_t) mcap + (size_t) p) << 7);
+        *reinterpret_cast<uint4*>(row + ((pc ^ (p & 7)) << 4)) = o;
     }
 }
 
-// 32 halves (64 bytes) -> 16 half2
-__device__ __forceinline__ void ms_load32(const __half* src, __half2 (&v)[16])
+// the lane's two pieces of a chunk (src = first value of the chunk): elements 8 pc .. and 64 + 8 pc ..
+__device__ __forceinline__ void ms_load_pieces(const __half* src, int pc, __half2 (&v)[8])
 {
     #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int j = 0; j < 2; ++j)
     {
-        const uint4 r = reinterpret_cast<const uint4*>(src)[i];
-        v[4 * i + 0] = *reinterpret_cast<const __half2*>(&r.x); v[4 * i + 1] = *reinterpret_cast<const __half2*>(&r.y);
-        v[4 * i + 2] = *reinterpret_cast<const __half2*>(&r.z); v[4 * i + 3] = *reinterpret_cast<const __half2*>(&r.w);
+        const uint4 r = *reinterpret_cast<const uint4*>(src + 64 * j + 8 * pc);
+        v[4 * j + 0] = *reinterpret_cast<const __half2*>(&r.x); v[4 * j + 1] = *reinterpret_cast<const __half2*>(&r.y);
+        v[4 * j + 2] = *reinterpret_cast<const __half2*>(&r.z); v[4 * j + 3] = *reinterpret_cast<const __half2*>(&r.w);
     }
 }
 
-// task = (tile, group of 8 rows): one row per warp; a warp takes eight 128-value chunks of its row
-// per pass, four lanes each.
+// task = (tile, group of 8 rows): one row per warp; a warp takes four 128-value chunks of its row
+// per pass, eight lanes each.
 __global__ __launch_bounds__(256)
 void moe_sorted_rotate_in_kernel(const MsRot P)
 {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q = lane & 3, cl = lane >> 2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, pc = lane & 7, cl = lane >> 3;
     const int ntasks = P.hdr[0] * P.groups, chunks = P.H >> 7;
     for (int task = blockIdx.x; task < ntasks; task += gridDim.x)
     {
@@ -295,34 +303,34 @@ void moe_sorted_rotate_in_kernel(const MsRot P)
         }
         const __half* src = P.y + (size_t) tok * P.H;
         unsigned char* xu = P.xt + (gs ? (size_t) P.mcap * P.H * 2 : 0);
-        for (int c0 = 0; c0 < chunks; c0 += 8)
+        for (int c0 = 0; c0 < chunks; c0 += 4)
         {
             const int cb = c0 + cl;
             const bool live = cb < chunks;                 // (idle lanes still take part in the shuffles)
-            const int off = (live ? cb : 0) * 128 + 32 * q;
-            __half2 v[16], sc[16];
-            float h[32];
-            ms_load32(src + off, v);
-            ms_load32(us + off, sc);
+            const int off = (live ? cb : 0) * 128;
+            __half2 v[8], su[8], sg[8];
+            float h[16];
+            ms_load_pieces(src + off, pc, v);
+            ms_load_pieces(us + off, pc, su);
+            if (gs) ms_load_pieces(gs + off, pc, sg);
             #pragma unroll
-            for (int i = 0; i < 16; ++i)
+            for (int i = 0; i < 8; ++i)
             {
-                const __half2 a = __hmul2(v[i], sc[i]);
+                const __half2 a = __hmul2(v[i], su[i]);
                 h[2 * i] = __low2float(a); h[2 * i + 1] = __high2float(a);
             }
-            quad_had128(h, q);
-            if (live) ms_store_quarter(xu, P.mcap, p, cb, q, h);
+            oct_had128(h, pc);
+            if (live) ms_store_pieces(xu, P.mcap, p, cb, pc, h);
             if (gs)
             {
-                ms_load32(gs + off, sc);
                 #pragma unroll
-                for (int i = 0; i < 16; ++i)
+                for (int i = 0; i < 8; ++i)
                 {
-                    const __half2 a = __hmul2(v[i], sc[i]);
+                    const __half2 a = __hmul2(v[i], sg[i]);
                     h[2 * i] = __low2float(a); h[2 * i + 1] = __high2float(a);
                 }
-                quad_had128(h, q);
-                if (live) ms_store_quarter(P.xt, P.mcap, p, cb, q, h);
+                oct_had128(h, pc);
+                if (live) ms_store_pieces(P.xt, P.mcap, p, cb, pc, h);
             }
         }
     }
@@ -331,7 +339,7 @@ void moe_sorted_rotate_in_kernel(const MsRot P)
 __global__ __launch_bounds__(256)
 void moe_sorted_rotate_act_kernel(const MsRot P)
 {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q = lane & 3, cl = lane >> 2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, pc = lane & 7, cl = lane >> 3;
     const int ntasks = P.hdr[0] * P.groups, chunks = P.I >> 7;
     const __half* gbase = P.gu;                                                     // gate outputs (projection 0)
     const __half* ubase = P.gu + (P.gated ? (size_t) P.mcap * P.I : 0);              // up outputs
@@ -345,24 +353,24 @@ void moe_sorted_rotate_act_kernel(const MsRot P)
         const __half* ds = reinterpret_cast<const __half*>(P.d_suh[e]);
         const __half* ur = ubase + (size_t) p * P.I;
         const __half* gr = gbase + (size_t) p * P.I;
-        for (int c0 = 0; c0 < chunks; c0 += 8)
+        for (int c0 = 0; c0 < chunks; c0 += 4)
         {
             const int cb = c0 + cl;
             const bool live = cb < chunks;
-            const int off = (live ? cb : 0) * 128 + 32 * q;
-            __half2 u[16], g[16], sc[16];
-            float h[32];
-            ms_load32(ur + off, u);
-            ms_load32((P.gated ? gr : ur) + off, g);
-            ms_load32(ds + off, sc);
+            const int off = (live ? cb : 0) * 128;
+            __half2 u[8], g[8], sc[8];
+            float h[16];
+            ms_load_pieces(ur + off, pc, u);
+            ms_load_pieces((P.gated ? gr : ur) + off, pc, g);
+            ms_load_pieces(ds + off, pc, sc);
             #pragma unroll
-            for (int i = 0; i < 16; ++i)
+            for (int i = 0; i < 8; ++i)
             {
                 h[2 * i] = moe_act_gate(P.act, P.gated, __low2float(g[i]), __low2float(u[i]), P.act_limit) * __low2float(sc[i]);
                 h[2 * i + 1] = moe_act_gate(P.act, P.gated, __high2float(g[i]), __high2float(u[i]), P.act_limit) * __high2float(sc[i]);
             }
-            quad_had128(h, q);
-            if (live) ms_store_quarter(P.xt, P.mcap, p, cb, q, h);
+            oct_had128(h, pc);
+            if (live) ms_store_pieces(P.xt, P.mcap, p, cb, pc, h);
         }
     }
 }
