@@ -154,3 +154,38 @@ def test_moe_128_experts_top8(amp, oracle, T):
     torch.cuda.synchronize()
     ref = oracle.moe_coop(x, sel, rw, ex)
     check_close(cfg["out"][:T].cpu().numpy(), ref)
+
+
+def test_sorted_moe_128_experts_2048_tokens(amp, oracle):
+    """The token-sorted prefill MoE at the MoE configuration's size (128 experts 2048 -> 768 -> 2048,
+    3 bits, top-8) on a 2048-token chunk. The oracle checks the first 48 tokens' rows (their picks
+    land anywhere in the 16384-row sorted list); the whole chunk is checked through properties that
+    hold bit for bit: doubling every routing weight doubles every output (fp16 doubling and fp32
+    doubling are exact), and reversing the token order reverses the outputs (a row's result does
+    not depend on where in an expert's tile it sits, and a token's sum runs in expert order)."""
+    from test_gpu_moe import build_cfg, make_experts
+    E, H, I, K, topk, T = 128, 2048, 768, 3, 8, 2048
+    ex = make_experts(E, H, I, H, K, seed=12000)
+    rng = np.random.default_rng(2048)
+    x = rng.standard_normal((T, H)).astype(np.float16)
+    logits = rng.standard_normal((T, E)).astype(np.float32)
+    sel = np.argsort(-logits, axis=1)[:, :topk].astype(np.int64)
+    w = np.take_along_axis(logits, sel, axis=1)
+    w = np.exp(w - w.max(axis=1, keepdims=True))
+    rw = (w / w.sum(axis=1, keepdims=True)).astype(np.float16)
+    cfg = build_cfg(amp, ex, H, I, H, H, K, 1, topk)
+    cfg["I"] = I
+
+    def run(xa, sa, wa):
+        count, tok, wts = amp.moe_sort_routing(dev(sa), dev(wa), E)
+        out = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+        amp.moe_fused(dev(xa), out, count, tok, wts, cfg)
+        torch.cuda.synchronize()
+        assert amp.moe_fused_status(cfg) == 0
+        return out.cpu().numpy()
+
+    got = run(x, sel, rw)
+    n = 48
+    check_close(got[:n], oracle.moe_coop(x[:n], sel[:n], rw[:n], ex, gu_f16=True))
+    assert np.array_equal(run(x, sel, (rw.astype(np.float32) * 2).astype(np.float16)), got * np.float32(2))
+    assert np.array_equal(run(x[::-1].copy(), sel[::-1].copy(), rw[::-1].copy()), got[::-1])
