@@ -93,6 +93,9 @@ struct TcParams
     const int* g_tile_row0;     // device: first padded row of a tile (a multiple of 8)
     const int* g_tile_rows;     // device: valid rows of a tile (1 .. sub * 128)
     int g_experts;
+    // experts of different bit widths: per projection a device table of the experts' widths (null:
+    // all of this launch's width); a CTA whose expert has another width than this instance returns
+    const unsigned char* g_bits[2];
 };
 
 // What one CTA (pair) works on: its weight, scales, output, rotated input and column block
@@ -210,7 +213,12 @@ __global__ __launch_bounds__(TC_THREADS, GROUPED ? 2 : 1)
 void exl3_gemm_tc_kernel(const TcParams P)
 {
     if constexpr (GROUPED)
-        if ((int) blockIdx.y >= *P.g_ntiles || P.g_tile_rows[blockIdx.y] <= 0) return;     // the whole CTA, before any barrier or allocation
+    {
+        // the whole CTA leaves, before any barrier or allocation
+        if ((int) blockIdx.y >= *P.g_ntiles || P.g_tile_rows[blockIdx.y] <= 0) return;
+        const unsigned char* bits = P.g_bits[(int) blockIdx.x / (P.n / TC_BN)];
+        if (bits && bits[P.g_tile_e[blockIdx.y]] != K) return;
+    }
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment is required by the swizzled layout
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
@@ -1058,6 +1066,7 @@ int launch_gemm_tc_grouped(const void* xt, void* c, long Mcap, int k, int n, int
     P.t_trellis = t_trellis; P.t_svh = t_svh;
     P.g_ntiles = G.ntiles; P.g_tile_e = G.tile_e; P.g_tile_row0 = G.tile_row0; P.g_tile_rows = G.tile_rows;
     P.g_experts = G.experts;
+    P.g_bits[0] = G.bits[0]; P.g_bits[1] = G.bits[1];
     {
         static int* status_ptr[64] = {};
         static std::mutex status_mu;

@@ -64,6 +64,7 @@ struct TcGroups
     int max_tiles;       // grid height: an upper bound of *ntiles
     int sub;             // 128-row sub-tiles per tile (1..4)
     int kinds;           // projections in one launch (gate and up: 2)
+    const unsigned char* bits[2];   // per projection: device table of per-expert bit widths, or null (uniform)
 };
 int launch_gemm_tc_grouped(const void* xt, void* c, long Mcap, int k, int n, int K, int cb, int c_fp32,
                            const long long* t_trellis, const long long* t_svh, const TcGroups& G, cudaStream_t stream);

@@ -527,7 +527,14 @@ AMP_API int amp_exl3_moe_sorted(const amp_moe_sorted_args* a, cudaStream_t strea
     AMP_REQUIRE(a->A <= 0x3fffffffL && a->T <= 0x3fffffffL && a->E <= (1 << 20), "exl3_moe_sorted: sizes out of range");
     AMP_REQUIRE(a->u_trellis && a->u_suh && a->u_svh && a->d_trellis && a->d_suh && a->d_svh, "exl3_moe_sorted: pointer tables missing");
     AMP_REQUIRE(!a->gated || (a->g_trellis && a->g_suh && a->g_svh), "exl3_moe_sorted: gate tables missing");
-    AMP_REQUIRE(a->Ku >= 1 && a->Ku <= 8 && a->Kd >= 1 && a->Kd <= 8 && (!a->gated || (a->Kg >= 1 && a->Kg <= 8)), "exl3_moe_sorted: K out of range");
+    if (a->g_bits || a->u_bits || a->d_bits)
+    {
+        AMP_REQUIRE(a->u_bits && a->d_bits && (!a->gated || a->g_bits), "exl3_moe_sorted: give all bit width tables or none");
+        AMP_REQUIRE(a->kmask_gu > 0 && a->kmask_gu < 256 && a->kmask_d > 0 && a->kmask_d < 256,
+                    "exl3_moe_sorted: kmask_gu / kmask_d must name the bit widths (1..8) that occur in the tables");
+    }
+    else
+        AMP_REQUIRE(a->Ku >= 1 && a->Ku <= 8 && a->Kd >= 1 && a->Kd <= 8 && (!a->gated || (a->Kg >= 1 && a->Kg <= 8)), "exl3_moe_sorted: K out of range");
     AMP_REQUIRE(a->cb >= 0 && a->cb <= 2, "exl3_moe_sorted: codebook index out of range");
     AMP_REQUIRE(a->act >= 0 && a->act <= 3, "exl3_moe_sorted: unknown activation");
     // (16 bytes also for every scale vector the tables point to: the rotation kernels load them in 16-byte pieces)
@@ -580,7 +587,19 @@ AMP_API int amp_exl3_moe_sorted(const amp_moe_sorted_args* a, cudaStream_t strea
     G.experts = E; G.max_tiles = L.max_tiles; G.sub = L.sub;
     const long long* tab = Pp.tab;
     __half* gu = (__half*) (ws + L.gu);
-    if (gated && a->Kg == a->Ku)
+    const bool mixed = a->g_bits || a->u_bits || a->d_bits;
+    if (mixed)
+    {
+        // one launch per width that occurs; each CTA works only if its expert has the launch's width
+        const unsigned char* ub = (const unsigned char*) a->u_bits;
+        G.kinds = gated ? 2 : 1;
+        G.bits[0] = gated ? (const unsigned char*) a->g_bits : ub; G.bits[1] = ub;
+        for (int K = 1; K <= 8; ++K)
+            if (a->kmask_gu & (1 << (K - 1)))
+                if (int rc = launch_gemm_tc_grouped(ws + L.xt_gu, gu, L.mcap, a->H, a->I, K, a->cb, 0,
+                                                    gated ? tab : tab + E, gated ? tab + 2 * E : tab + 3 * E, G, stream)) return rc;
+    }
+    else if (gated && a->Kg == a->Ku)
     {
         G.kinds = 2;
         if (int rc = launch_gemm_tc_grouped(ws + L.xt_gu, gu, L.mcap, a->H, a->I, a->Ku, a->cb, 0, tab, tab + 2 * E, G, stream)) return rc;
@@ -602,7 +621,10 @@ AMP_API int amp_exl3_moe_sorted(const amp_moe_sorted_args* a, cudaStream_t strea
     if (cudaError_t e = cudaGetLastError()) return cuda_rc(e, "exl3_moe_sorted activation launch");
 
     G.kinds = 1;
-    if (int rc = launch_gemm_tc_grouped(ws + L.xt_d, ws + L.dout, L.mcap, a->I, a->H, a->Kd, a->cb, 1, tab + 4 * E, tab + 5 * E, G, stream)) return rc;
+    G.bits[0] = G.bits[1] = mixed ? (const unsigned char*) a->d_bits : nullptr;
+    for (int K = 1; K <= 8; ++K)
+        if (mixed ? (a->kmask_d & (1 << (K - 1))) != 0 : K == a->Kd)
+            if (int rc = launch_gemm_tc_grouped(ws + L.xt_d, ws + L.dout, L.mcap, a->I, a->H, K, a->cb, 1, tab + 4 * E, tab + 5 * E, G, stream)) return rc;
 
     if (a->scratch)
     {

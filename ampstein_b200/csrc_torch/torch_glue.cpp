@@ -60,6 +60,31 @@ const void* opt_ptr(const c10::optional<at::Tensor>& t) { return t.has_value() &
 
 cudaStream_t stream_of(const at::Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
 
+// Mixed bit widths: the C ABI wants to know which widths occur in a per-expert uint8 table (bit K-1
+// of the mask per width K). The tables are static, so each is read back once (keyed by address and
+// length) and remembered.
+int bit_mask_of(const at::Tensor& t, int n, const char* who)
+{
+    TORCH_CHECK(t.scalar_type() == at::kByte && t.is_cuda() && t.is_contiguous() && t.numel() >= n,
+                who, ": bit width tables must be contiguous uint8 device tensors with one entry per expert");
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, int> masks;
+    std::lock_guard<std::mutex> lock(mu);
+    const auto key = std::make_pair((const void*) t.data_ptr(), n);
+    auto it = masks.find(key);
+    if (it != masks.end()) return it->second;
+    const at::Tensor h = t.narrow(0, 0, n).cpu();
+    int m = 0;
+    for (int i = 0; i < n; ++i)
+    {
+        const int K = h.data_ptr<uint8_t>()[i];
+        TORCH_CHECK(K >= 1 && K <= 8, who, ": bit widths must be 1..8");
+        m |= 1 << (K - 1);
+    }
+    masks[key] = m;
+    return m;
+}
+
 void same_device(const at::Tensor& a, const at::Tensor& b, const char* who)
 {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.get_device() == b.get_device(), who, ": tensors must live on one CUDA device");
@@ -250,34 +275,10 @@ void exl3_moe_coop(const at::Tensor& x, const at::Tensor& sel, const at::Tensor&
     a.sh_out = opt_ptr(sh_out); a.sh_gate_w = opt_ptr(sh_gate_w);
     if (bits_g.has_value() || bits_u.has_value() || bits_d.has_value())
     {
-        // mixed bit widths: the C ABI wants to know which widths occur; the tables are static, so
-        // they are read back once per table (keyed by address) and remembered
         TORCH_CHECK(bits_g.has_value() && bits_u.has_value() && bits_d.has_value(), "exl3_moe_coop: give all three bit width tables or none");
-        for (const at::Tensor* t : { &bits_g.value(), &bits_u.value(), &bits_d.value() })
-            TORCH_CHECK(t->scalar_type() == at::kByte && t->is_cuda() && t->is_contiguous() && t->numel() >= a.n_local,
-                        "exl3_moe_coop: bit width tables must be contiguous uint8 device tensors with one entry per expert");
-        static std::mutex mu;
-        static std::map<std::pair<const void*, int>, int> masks;
-        auto mask_of = [&](const at::Tensor& t)
-        {
-            std::lock_guard<std::mutex> lock(mu);
-            const auto key = std::make_pair((const void*) t.data_ptr(), a.n_local);
-            auto it = masks.find(key);
-            if (it != masks.end()) return it->second;
-            const at::Tensor h = t.narrow(0, 0, a.n_local).cpu();
-            int m = 0;
-            for (int i = 0; i < a.n_local; ++i)
-            {
-                const int K = h.data_ptr<uint8_t>()[i];
-                TORCH_CHECK(K >= 1 && K <= 8, "exl3_moe_coop: bit widths must be 1..8");
-                m |= 1 << (K - 1);
-            }
-            masks[key] = m;
-            return m;
-        };
         a.g_bits = bits_g->data_ptr(); a.u_bits = bits_u->data_ptr(); a.d_bits = bits_d->data_ptr();
-        a.kmask_gu = mask_of(*bits_u); a.kmask_d = mask_of(*bits_d);
-        if (gated) TORCH_CHECK(mask_of(*bits_g) == a.kmask_gu, "exl3_moe_coop: gate and up of an expert must share a bit width");
+        a.kmask_gu = bit_mask_of(*bits_u, a.n_local, "exl3_moe_coop"); a.kmask_d = bit_mask_of(*bits_d, a.n_local, "exl3_moe_coop");
+        if (gated) TORCH_CHECK(bit_mask_of(*bits_g, a.n_local, "exl3_moe_coop") == a.kmask_gu, "exl3_moe_coop: gate and up of an expert must share a bit width");
     }
     check_rc(amp_exl3_moe_coop(&a, stream_of(x)), "exl3_moe_coop");
 }
@@ -289,7 +290,7 @@ void exl3_moe_coop(const at::Tensor& x, const at::Tensor& sel, const at::Tensor&
 // reference's launch and are ignored; experts with more rows than the reference's temps hold
 // (max_tokens_per_expert = temp_state_g.size(1)) are skipped exactly as the reference skips them,
 // so that a caller who routes those through another tier does not get them twice. Per-expert bit
-// tables are not supported.
+// tables are served for every codebook.
 void exl3_moe(const at::Tensor& hidden_state, const at::Tensor& output_state, const at::Tensor& expert_count,
               const at::Tensor& token_sorted, const at::Tensor& weight_sorted,
               const at::Tensor& temp_state_g, const at::Tensor& temp_state_u,
@@ -318,7 +319,6 @@ void exl3_moe(const at::Tensor& hidden_state, const at::Tensor& output_state, co
                 "exl3_moe: token_sorted int64 / weight_sorted float16, one entry per pick");
     TORCH_CHECK(gate_mcg == up_mcg && up_mcg == down_mcg && gate_mul1 == up_mul1 && up_mul1 == down_mul1,
                 "MoE kernel: gate/up/down must share the same codebook");
-    TORCH_CHECK(!bits_g.has_value() && !bits_u.has_value() && !bits_d.has_value(), "exl3_moe: per-expert bit width tables are not supported");
     TORCH_CHECK(temp_state_g.dim() == 3 && temp_intermediate_g.dim() == 3, "exl3_moe: temps must be 3-D");
     const int64_t E = expert_count.numel() - 1;
     for (const at::Tensor* t : { &gate_ptrs_trellis, &gate_ptrs_suh, &gate_ptrs_svh, &up_ptrs_trellis, &up_ptrs_suh, &up_ptrs_svh,
@@ -334,7 +334,6 @@ void exl3_moe(const at::Tensor& hidden_state, const at::Tensor& output_state, co
     a.g_trellis = gate_ptrs_trellis.data_ptr(); a.g_suh = gate_ptrs_suh.data_ptr(); a.g_svh = gate_ptrs_svh.data_ptr();
     a.u_trellis = up_ptrs_trellis.data_ptr(); a.u_suh = up_ptrs_suh.data_ptr(); a.u_svh = up_ptrs_svh.data_ptr();
     a.d_trellis = down_ptrs_trellis.data_ptr(); a.d_suh = down_ptrs_suh.data_ptr(); a.d_svh = down_ptrs_svh.data_ptr();
-    a.Kg = bits_of(K_gate, "exl3_moe"); a.Ku = bits_of(K_up, "exl3_moe"); a.Kd = bits_of(K_down, "exl3_moe");
     a.cb = codebook(gate_mcg, gate_mul1);
     // the reference's activation codes (quant/exl3_moe_common.cuh:6-8): 0 silu, 1 gelu, 2 = relu^2 without a gate projection
     a.gated = act_function == 2 ? 0 : 1;
@@ -343,6 +342,17 @@ void exl3_moe(const at::Tensor& hidden_state, const at::Tensor& output_state, co
     const int cap = (int) temp_state_g.size(1);
     a.count_lo = count_lo;
     a.count_hi = count_hi > 0 ? std::min(count_hi, cap) : cap;
+    if (bits_g.has_value() || bits_u.has_value() || bits_d.has_value())
+    {
+        TORCH_CHECK(bits_g.has_value() && bits_u.has_value() && bits_d.has_value(), "exl3_moe: give all three bit width tables or none");
+        a.g_bits = a.gated ? bits_g->data_ptr() : nullptr; a.u_bits = bits_u->data_ptr(); a.d_bits = bits_d->data_ptr();
+        a.kmask_gu = bit_mask_of(*bits_u, a.E, "exl3_moe"); a.kmask_d = bit_mask_of(*bits_d, a.E, "exl3_moe");
+        if (a.gated) TORCH_CHECK(bit_mask_of(*bits_g, a.E, "exl3_moe") == a.kmask_gu, "exl3_moe: gate and up of an expert must share a bit width");
+    }
+    else
+    {
+        a.Kg = bits_of(K_gate, "exl3_moe"); a.Ku = bits_of(K_up, "exl3_moe"); a.Kd = bits_of(K_down, "exl3_moe");
+    }
     if (output_scratch.has_value())
     {
         TORCH_CHECK(fused_base.has_value(), "exl3_moe: output_scratch needs fused_base");

@@ -483,6 +483,28 @@ class _MoeArgs(__import__("ctypes").Structure):
     ]
 
 
+def _moe_bit_masks(who, cfg, n_local, gated):
+    """Mixed bit widths: checks the uint8 tables g_bits / u_bits / d_bits of a cfg object and returns
+    (kmask_gu, kmask_d), bit K-1 set for every width K that occurs. The tables are static: they are
+    read back once and the masks kept in cfg["_kmask"]."""
+    for n in (("g_bits", "u_bits", "d_bits") if gated else ("u_bits", "d_bits")):
+        t = cfg.get(n)
+        if not isinstance(t, torch.Tensor) or t.dtype != torch.uint8 or not t.is_cuda or not t.is_contiguous() \
+                or t.numel() < n_local:
+            raise TypeError("%s: give all three bit width tables (contiguous uint8 CUDA, one entry per expert) or none" % who)
+    if "_kmask" not in cfg:
+        if gated and not torch.equal(cfg["g_bits"][:n_local], cfg["u_bits"][:n_local]):
+            raise ValueError("%s: gate and up of an expert must share a bit width" % who)
+        masks = []
+        for n in ("u_bits", "d_bits"):
+            ks = torch.unique(cfg[n][:n_local]).tolist()
+            if not ks or min(ks) < 1 or max(ks) > 8:
+                raise ValueError("%s: bit widths must be 1..8" % who)
+            masks.append(sum(1 << (int(k) - 1) for k in ks))
+        cfg["_kmask"] = tuple(masks)
+    return cfg["_kmask"]
+
+
 def moe_coop_ctr_len(slots_max, rows_max=None, I=0, Ho=None):
     """int32 entries of the `ctr` scratch (reference: exl3_moe_coop_ctr_len,
     .../quant/exl3_moe_coop.cuh:164-167). Without rows_max / Ho an upper bound is returned (one
@@ -560,23 +582,10 @@ def moe_coop(x, sel, rw, cfg, sh_out=None):
     a.sh_out = p(sh_out)
     a.sh_gate_w = p(cfg.get("sh_gate_w"))
     if any(cfg.get(n) is not None for n in ("g_bits", "u_bits", "d_bits")):
-        # mixed bit widths: uint8 tables, one entry per expert. The widths that occur are read once
-        # (the tables are static) and kept in the cfg object.
-        for n in ("g_bits", "u_bits", "d_bits"):
-            t = cfg.get(n)
-            if not isinstance(t, torch.Tensor) or t.dtype != torch.uint8 or not t.is_cuda or not t.is_contiguous() \
-                    or t.numel() < a.n_local:
-                raise TypeError("exl3_moe_coop: give all three bit width tables (contiguous uint8 CUDA, one entry per expert) or none")
-        if "_kmask" not in cfg:
-            if gated and not torch.equal(cfg["g_bits"][:a.n_local], cfg["u_bits"][:a.n_local]):
-                raise ValueError("exl3_moe_coop: gate and up of an expert must share a bit width")
-            masks = []
-            for n in ("u_bits", "d_bits"):
-                ks = torch.unique(cfg[n][:a.n_local]).tolist()
-                if not ks or min(ks) < 1 or max(ks) > 8:
-                    raise ValueError("exl3_moe_coop: bit widths must be 1..8")
-                masks.append(sum(1 << (int(k) - 1) for k in ks))
-            cfg["_kmask"] = tuple(masks)
+        # mixed bit widths: uint8 tables, one entry per expert
+        if any(cfg.get(n) is None for n in ("g_bits", "u_bits", "d_bits")):
+            raise TypeError("exl3_moe_coop: give all three bit width tables (contiguous uint8 CUDA, one entry per expert) or none")
+        _moe_bit_masks("exl3_moe_coop", cfg, a.n_local, gated)
         a.g_bits, a.u_bits, a.d_bits = p(cfg["g_bits"]), p(cfg["u_bits"]), p(cfg["d_bits"])
         a.kmask_gu, a.kmask_d = cfg["_kmask"]
     with torch.cuda.device(x.device):
@@ -598,6 +607,8 @@ class _MoeSortedArgs(__import__("ctypes").Structure):
         ("act_limit", _c.c_float), ("gated", _c.c_int), ("count_lo", _c.c_int), ("count_hi", _c.c_int),
         ("workspace", _c.c_void_p), ("workspace_bytes", _c.c_long),
         ("scratch", _c.c_void_p), ("slot_base", _c.c_void_p), ("scratch_rows", _c.c_long),
+        ("g_bits", _c.c_void_p), ("u_bits", _c.c_void_p), ("d_bits", _c.c_void_p),
+        ("kmask_gu", _c.c_int), ("kmask_d", _c.c_int),
     ]
 
 
@@ -630,8 +641,9 @@ def moe_fused(y, out, count, tok_sorted, w_sorted, cfg, num_active=-1, lo=1, hi=
     kernel exl3_moe, .../quant/exl3_moe.cu:139-531): experts with lo <= rows <= hi (hi <= 0: no upper
     bound) run gate / up / activation / down on their rows of y, and weight * result is summed per
     token in a fixed order and added to out (fp32, zero-initialised by the caller, same shape as y).
-    cfg: the pointer tables g_/u_/d_ {trellis,suh,svh} and Kg Ku Kd act act_limit mcg mul1 [gated] of
-    moe_coop; the reference's temps ts_g ts_u ti_g ti_u are not needed (one workspace, kept in cfg).
+    cfg: the pointer tables g_/u_/d_ {trellis,suh,svh} and Kg Ku Kd act act_limit mcg mul1 [gated]
+    [g_bits u_bits d_bits] of moe_coop; the reference's temps ts_g ts_u ti_g ti_u are not needed (one
+    workspace, kept in cfg).
     num_active and m_tile are accepted and unused (one call covers every row count; the reference's
     three tiered calls still work). With scratch (fp32 [slots, hidden]) and slot_base (int64 per
     expert) the sum is deferred as in the reference: out is left alone, weight * result of every
@@ -682,6 +694,9 @@ def moe_fused(y, out, count, tok_sorted, w_sorted, cfg, num_active=-1, lo=1, hi=
     a.act, a.act_limit, a.gated = int(cfg.get("act", 0)), float(cfg.get("act_limit", 0.0)), int(gated)
     a.count_lo, a.count_hi = int(lo), int(hi)
     a.workspace, a.workspace_bytes = p(ws), ws.numel()
+    if any(cfg.get(n) is not None for n in ("g_bits", "u_bits", "d_bits")):
+        a.kmask_gu, a.kmask_d = _moe_bit_masks("moe_fused", cfg, E, gated)
+        a.g_bits, a.u_bits, a.d_bits = p(cfg.get("g_bits") if gated else None), p(cfg["u_bits"]), p(cfg["d_bits"])
     if (scratch is None) != (slot_base is None):
         raise ValueError("moe_fused: scratch needs slot_base")
     if scratch is not None:

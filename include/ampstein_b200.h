@@ -362,7 +362,7 @@ long amp_exl3_moe_coop_ctr_len(long slots_max, long rows_max, long I, long Ho);
  * Q/exl3_moe.cu:33-46), the temps ts_g ts_u ti_g ti_u, the slot scratch and slot_base are one
  * caller-provided workspace, and without a slot scratch the sum is a fixed-order one made by the
  * call itself (the reference adds atomically in arrival order then). Per-expert bit width
- * tables (bits_g / bits_u / bits_d) are not supported: one width per projection.
+ * tables are served for every codebook (the reference: mul1 only).
  */
 typedef struct amp_moe_sorted_args
 {
@@ -391,6 +391,12 @@ typedef struct amp_moe_sorted_args
     void* scratch;              /* (scratch_rows, H) fp32 */
     const void* slot_base;      /* (E) int64 */
     long scratch_rows;
+    /* experts of different bit widths (nullable, all or none; g_bits only when gated): uint8 device
+     * tables indexed by expert, gate and up of an expert sharing one width; kmask_gu / kmask_d as in
+     * amp_moe_coop_args (host values); Kg / Ku / Kd are ignored then. One GEMM launch per width that
+     * occurs. Reference: bits_g / bits_u / bits_d of exl3_moe, Q/exl3_moe.cuh:50-52 (there mul1 only). */
+    const void* g_bits; const void* u_bits; const void* d_bits;
+    int kmask_gu, kmask_d;
 } amp_moe_sorted_args;
 
 int amp_exl3_moe_sorted(const amp_moe_sorted_args* args, cudaStream_t stream);

@@ -169,6 +169,33 @@ def test_sorted_moe_gate_and_up_of_different_widths(amp, oracle):
     check(got, oracle.moe_coop(x, sel, rw, ex, gu_f16=True))
 
 
+def test_sorted_moe_experts_of_different_bit_widths(amp, oracle):
+    """Mixed packs (the reference's bits_g / bits_u / bits_d tables of exl3_moe, exl3_moe.cuh:50-52):
+    every expert's gate|up and down have their own bit width; one grouped GEMM launch per width that
+    occurs, each serving the tiles of its width. Default codebook (the reference: mul1 only)."""
+    E, H, I, topk, T = 8, 256, 256, 3, 200
+    kgu = [3, 4, 4, 3, 5, 4, 3, 5]
+    kd = [4, 4, 2, 2, 4, 6, 6, 2]
+    ex = []
+    for e in range(E):
+        def one(k, n, K, s):
+            t, su, sv, _ = make_linear(k, n, K, seed=3700 + s)
+            sv = (sv.astype(np.float32) / (1.2437 * np.sqrt(k))).astype(np.float16)
+            return (t, su, sv)
+        ex.append({"gate": one(H, I, kgu[e], 3 * e), "up": one(H, I, kgu[e], 3 * e + 1), "down": one(I, H, kd[e], 3 * e + 2)})
+    rng = np.random.default_rng(71)
+    x = rng.standard_normal((T, H)).astype(np.float16)
+    sel, rw = routing(rng, T, E, topk)
+    bits = lambda v: torch.tensor(v, dtype=torch.uint8, device="cuda")
+    cfg = build_cfg(amp, ex, H, I, H, H, 0, 1, topk, g_bits=bits(kgu), u_bits=bits(kgu), d_bits=bits(kd))
+    cfg["I"] = I
+    ref = oracle.moe_coop(x, sel, rw, ex, gu_f16=True)
+    for _ in range(2):                                   # the second call reuses the cached masks
+        got, _ = run_sorted(amp, cfg, x, sel, rw, E)
+        check(got, ref)
+    assert cfg["_kmask"] == (0b11100, 0b101010)
+
+
 def test_sorted_moe_agrees_with_the_decode_moe(amp):
     """16 tokens through both fused forms of this library (grouped GEMV and grouped tensor-core
     GEMM): same element arithmetic, different summation order inside the dot products."""
