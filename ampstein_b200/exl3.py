@@ -635,6 +635,29 @@ def moe_sort_routing(sel, rw, n_experts, e0=0, with_inverse=False):
     return count, tok, wts
 
 
+def moe_prep(idx, w, n_experts, e0=0):
+    """Token-sorted MoE dispatch in one kernel (reference: torch.moe_prep, src/torch/amp_torch.cpp:8168-8215):
+    idx (T, K) int64 global expert ids, w (T, K) fp32 -> [fe (A) int64, order (A) int64, tok (A) int64,
+    wts (A) fp16, count (E + 1) int64, start (E + 1) int64, inv (A) int64, kind (E) int64] for the
+    experts [e0, e0 + E): a stable sort of the assignments by local expert, foreign picks last."""
+    _check_cuda("moe_prep", idx, w)
+    E = int(n_experts)
+    if idx.dim() != 2 or idx.dtype != torch.int64 or w.dtype != torch.float32 or w.shape != idx.shape \
+            or w.device != idx.device or E < 1 or E > 4096:
+        raise ValueError("moe_prep: idx (T, K) int64 and w (T, K) fp32, contiguous on one CUDA device, 1 <= E <= 4096")
+    A, K = idx.numel(), idx.shape[1]
+    lo = dict(dtype=torch.int64, device=idx.device)
+    fe, order, tok, inv = (torch.empty(A, **lo) for _ in range(4))
+    wts = torch.empty(A, dtype=torch.float16, device=idx.device)
+    count, start, kind = torch.empty(E + 1, **lo), torch.empty(E + 1, **lo), torch.empty(E, **lo)
+    if A == 0:
+        return [fe, order, tok, wts, count.zero_(), start.zero_(), inv, kind.zero_()]
+    with torch.cuda.device(idx.device):
+        _lib.call("amp_moe_prep", idx.data_ptr(), w.data_ptr(), A, K, E, int(e0), fe.data_ptr(), order.data_ptr(),
+                  tok.data_ptr(), wts.data_ptr(), count.data_ptr(), start.data_ptr(), inv.data_ptr(), kind.data_ptr(), _stream(idx))
+    return [fe, order, tok, wts, count, start, inv, kind]
+
+
 def moe_fused(y, out, count, tok_sorted, w_sorted, cfg, num_active=-1, lo=1, hi=0, m_tile=16,
               scratch=None, slot_base=None):
     """Token-sorted MoE for prefill chunks (reference: torch.moe_fused, src/torch/amp_torch.cpp:9257-9345,

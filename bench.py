@@ -626,8 +626,8 @@ def measure_moe_prefill(steps, warmup, T=2048):
     sets = []
     for _ in range(4):
         w, sel = torch.topk(torch.randn(T, E, device=dev, generator=g), topk, dim=1)
-        count, tok, wts = amp.moe_sort_routing(sel.contiguous(), torch.softmax(w, 1).to(torch.float16).contiguous(), E)
-        sets.append((torch.randn(T, H, device=dev, generator=g).to(torch.float16), count, tok, wts))
+        pr = amp.moe_prep(sel.contiguous(), torch.softmax(w, 1).contiguous(), E, 0)      # [fe, order, tok, wts, count, ...]
+        sets.append((torch.randn(T, H, device=dev, generator=g).to(torch.float16), pr[4], pr[2], pr[3]))
     out = torch.zeros(T, H, dtype=torch.float32, device=dev)
     rows_max = int(max(s[1][:E].max().item() for s in sets))
 

@@ -401,6 +401,19 @@ typedef struct amp_moe_sorted_args
 
 int amp_exl3_moe_sorted(const amp_moe_sorted_args* args, cudaStream_t stream);
 /*
+ * Token-sorted MoE dispatch in one launch: idx (A = T * K) int64 global expert ids and w (A) fp32
+ * router weights become, for the experts [e0, e0 + E) of this rank (foreign picks in the sentinel
+ * bucket E): fe (A) bucket per assignment, order (A) the assignment at every sorted position (a
+ * stable sort by bucket), tok (A) its token, wts (A) fp16 its weight, count / start (E + 1) sizes
+ * and first positions of the buckets, inv (A) the sorted position of every assignment, kind (E) =
+ * count > 0. All index tensors int64 on the device; 1 <= E <= 4096. Returns a cudaError_t.
+ * Same name, signature and meaning as the reference's amp_moe_prep, src/torch/amp_kernels.cu:7024-7043
+ * (binding torch.moe_prep, src/torch/amp_torch.cpp:8164-8215).
+ */
+int amp_moe_prep(const long long* idx, const float* w, int A, int K, int E, long long e0, long long* fe,
+                 long long* order, long long* tok, void* wts, long long* count, long long* start,
+                 long long* inv, long long* kind, cudaStream_t stream);
+/*
  * Fixed-order sum of per-assignment slots: for every token, the slots of its picks k = 0 .. topk - 1
  * are added in that order (fp32) and the sum is added to out (T, H). Pick a = token * topk + k of
  * local expert e = flat_expert[a] (outside [0, E): no slot) owns slot slot_base[e] + inv_order[a] -
