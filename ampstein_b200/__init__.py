@@ -23,6 +23,8 @@ from .exl3 import (  # noqa: F401
     moe_coop,
     moe_fused,
     moe_fused_status,
+    exl3_shard_cols,
+    exl3_shard_rows,
     moe_gather,
     moe_prep,
     moe_sort_routing,
@@ -33,4 +35,4 @@ from .exl3 import (  # noqa: F401
     argmax_advance,
 )
 
-__all__ = ["exl3_gemm", "exl3_gemm_add_res", "exl3_gemm_normed", "exl3_gemm_recon", "exl3_gemm_rms_norm_res", "exl3_gemm_silu_mul", "exl3_reconstruct", "exl3_reconstruct_batch", "exl3_reconstruct_had", "had_r_128", "lm_head_argmax", "mgemm", "mgemm_normed", "mgemm_rms_norm_res", "moe_coop", "moe_coop_ctr_len", "moe_fused", "moe_fused_status", "moe_gather", "moe_prep", "moe_sort_routing", "ptr_array", "rms_norm_res", "silu_mul", "argmax_advance"]
+__all__ = ["exl3_gemm", "exl3_gemm_add_res", "exl3_gemm_normed", "exl3_gemm_recon", "exl3_gemm_rms_norm_res", "exl3_gemm_silu_mul", "exl3_reconstruct", "exl3_reconstruct_batch", "exl3_reconstruct_had", "had_r_128", "lm_head_argmax", "mgemm", "mgemm_normed", "mgemm_rms_norm_res", "moe_coop", "moe_coop_ctr_len", "moe_fused", "moe_fused_status", "exl3_shard_cols", "exl3_shard_rows", "moe_gather", "moe_prep", "moe_sort_routing", "ptr_array", "rms_norm_res", "silu_mul", "argmax_advance"]

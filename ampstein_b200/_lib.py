@@ -64,6 +64,8 @@ SIGNATURES = {
     "amp_exl3_moe_sorted_workspace": [_l, _l, _l, _l, _l],
     "amp_exl3_moe_sorted_status": [_vp, ctypes.POINTER(ctypes.c_int), _vp],
     "amp_exl3_set_moe_sorted_tile": [_i],
+    "amp_exl3_shard_cols": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp],
+    "amp_exl3_shard_rows": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "amp_moe_prep": [_vp, _vp, _i, _i, _i, ctypes.c_longlong, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "amp_exl3_moe_gather": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _l, _vp],
     "amp_exl3_gemm_bf16": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],

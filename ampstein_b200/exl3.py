@@ -635,6 +635,49 @@ def moe_sort_routing(sel, rw, n_experts, e0=0, with_inverse=False):
     return count, tok, wts
 
 
+def exl3_shard_cols(trellis, svh, ranges):
+    """Column shard of an EXL3 linear cut on the device in one launch (reference: sub_columns / cols,
+    src/ucode/ampstein/models.uc:440-545): the output columns of `ranges` ([start, length] pairs,
+    multiples of 128) concatenated. Returns (trellis (k/16, total/16, 16K), svh (total))."""
+    import ctypes
+    _check_cuda("exl3_shard_cols", trellis, svh)
+    k, n, K = _trellis_dims("exl3_shard_cols", trellis)
+    if svh.dtype != torch.float16 or svh.numel() != n:
+        raise ValueError("exl3_shard_cols: svh must be fp16 with one value per output column")
+    ranges = [(int(a), int(b)) for a, b in ranges]
+    for a, ln in ranges:
+        if a % 128 or ln % 128 or a < 0 or ln <= 0 or a + ln > n:
+            raise ValueError("models.sub_columns: range [%d, %d] not 128-aligned/in bounds" % (a, ln))
+    if not 1 <= len(ranges) <= 16:
+        raise ValueError("exl3_shard_cols: 1..16 ranges")
+    total = sum(ln for _, ln in ranges)
+    out = torch.empty((k // 16, total // 16, 16 * K), dtype=trellis.dtype, device=trellis.device)
+    out_svh = torch.empty(total, dtype=torch.float16, device=trellis.device)
+    flat = (ctypes.c_int * (2 * len(ranges)))(*[v for r in ranges for v in r])
+    with torch.cuda.device(trellis.device):
+        _lib.call("amp_exl3_shard_cols", trellis.data_ptr(), svh.data_ptr(), out.data_ptr(), out_svh.data_ptr(), k, n, K,
+                  ctypes.cast(flat, ctypes.c_void_p), len(ranges), _stream(trellis))
+    return out, out_svh
+
+
+def exl3_shard_rows(trellis, suh, k0, klen):
+    """Row shard (reference: rows, src/ucode/ampstein/models.uc:547-562): input rows [k0, k0 + klen),
+    multiples of 128, of the trellis and of suh, as copies of their own."""
+    _check_cuda("exl3_shard_rows", trellis, suh)
+    k, n, K = _trellis_dims("exl3_shard_rows", trellis)
+    if suh.dtype != torch.float16 or suh.numel() != k:
+        raise ValueError("exl3_shard_rows: suh must be fp16 with one value per input row")
+    k0, klen = int(k0), int(klen)
+    if k0 % 128 or klen % 128 or k0 < 0 or klen <= 0 or k0 + klen > k:
+        raise ValueError("models.rows: range [%d, %d] not 128-aligned/in bounds" % (k0, klen))
+    out = torch.empty((klen // 16, n // 16, 16 * K), dtype=trellis.dtype, device=trellis.device)
+    out_suh = torch.empty(klen, dtype=torch.float16, device=trellis.device)
+    with torch.cuda.device(trellis.device):
+        _lib.call("amp_exl3_shard_rows", trellis.data_ptr(), suh.data_ptr(), out.data_ptr(), out_suh.data_ptr(), k, n, K,
+                  k0, klen, _stream(trellis))
+    return out, out_suh
+
+
 def moe_prep(idx, w, n_experts, e0=0):
     """Token-sorted MoE dispatch in one kernel (reference: torch.moe_prep, src/torch/amp_torch.cpp:8168-8215):
     idx (T, K) int64 global expert ids, w (T, K) fp32 -> [fe (A) int64, order (A) int64, tok (A) int64,

@@ -88,10 +88,14 @@ def cols(lin, ranges):
     """Column-parallel shard: output columns ([start, length] pairs, 256-aligned) concatenated;
     suh whole, svh sliced (reference: models.uc cols(), :537-545)."""
     for n0, w in ranges:
-        if n0 % 16 or w % 16:
-            raise ValueError("models.cols: ranges must be multiples of 16 columns")
-    tr = torch.cat([lin.trellis[:, n0 // 16:(n0 + w) // 16] for n0, w in ranges], dim=1).contiguous()
-    svh = torch.cat([lin.svh[n0:n0 + w] for n0, w in ranges]).contiguous()
+        if n0 % 128 or w % 128 or n0 < 0 or w <= 0 or n0 + w > lin.out_features:
+            raise ValueError("models.sub_columns: range [%d, %d] not 128-aligned/in bounds" % (n0, w))
+    if lin.trellis.is_cuda:
+        tr, svh = exl3.exl3_shard_cols(lin.trellis, lin.svh, ranges)        # one launch on the device
+    else:
+        # weights still in host memory (before the upload): plain slices of the host tensors
+        tr = torch.cat([lin.trellis[:, n0 // 16:(n0 + w) // 16] for n0, w in ranges], dim=1).contiguous()
+        svh = torch.cat([lin.svh[n0:n0 + w] for n0, w in ranges]).contiguous()
     return LinearEXL3(tr, lin.suh, svh, mul1=lin.mul1, mcg=lin.mcg)
 
 
@@ -99,10 +103,13 @@ def rows(lin, k0, klen):
     """Row-parallel shard: input rows [k0, k0 + klen), 128-aligned, with the matching suh slice
     and the whole svh; the shards' outputs SUM to the full product (reference: models.uc rows(),
     :547-562)."""
-    if k0 % 128 or klen % 128 or k0 + klen > lin.in_features:
+    if k0 % 128 or klen % 128 or k0 < 0 or klen <= 0 or k0 + klen > lin.in_features:
         raise ValueError("models.rows: range [%d, %d] not 128-aligned/in bounds" % (k0, klen))
-    tr = lin.trellis[k0 // 16:(k0 + klen) // 16].clone()
-    return LinearEXL3(tr, lin.suh[k0:k0 + klen].clone(), lin.svh, mul1=lin.mul1, mcg=lin.mcg)
+    if lin.trellis.is_cuda:
+        tr, suh = exl3.exl3_shard_rows(lin.trellis, lin.suh, k0, klen)
+    else:
+        tr, suh = lin.trellis[k0 // 16:(k0 + klen) // 16].clone(), lin.suh[k0:k0 + klen].clone()
+    return LinearEXL3(tr, suh, lin.svh, mul1=lin.mul1, mcg=lin.mcg)
 
 
 def _bundle_check(linears):

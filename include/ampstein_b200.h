@@ -401,6 +401,20 @@ typedef struct amp_moe_sorted_args
 
 int amp_exl3_moe_sorted(const amp_moe_sorted_args* args, cudaStream_t stream);
 /*
+ * Tensor-parallel shards cut on the device (load path). amp_exl3_shard_cols: the output columns of
+ * `ranges` (nranges <= 16 host pairs [start, length], multiples of 128, in order) of a trellis
+ * (k/16, n/16, 16K) concatenated into out_trellis (k/16, total/16, 16K), and the same slices of svh (n)
+ * into out_svh (total) (both null: trellis only), one launch; the destinations may live on another
+ * GPU when peer access is enabled. amp_exl3_shard_rows: input rows [k0, k0 + klen) (multiples of
+ * 128) of the trellis and of suh, two contiguous copies. Byte moves, bit-exact. Replace the
+ * narrow / torch.cat / contiguous / .cuda(dev) chains of sub_columns, cols and rows,
+ * src/ucode/ampstein/models.uc:440-562 (same alignment rules and error cases).
+ */
+int amp_exl3_shard_cols(const void* trellis, const void* svh, void* out_trellis, void* out_svh, int k, int n, int K,
+                        const int* ranges, int nranges, cudaStream_t stream);
+int amp_exl3_shard_rows(const void* trellis, const void* suh, void* out_trellis, void* out_suh, int k, int n, int K,
+                        int k0, int klen, cudaStream_t stream);
+/*
  * Token-sorted MoE dispatch in one launch: idx (A = T * K) int64 global expert ids and w (A) fp32
  * router weights become, for the experts [e0, e0 + E) of this rank (foreign picks in the sentinel
  * bucket E): fe (A) bucket per assignment, order (A) the assignment at every sorted position (a

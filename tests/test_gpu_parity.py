@@ -778,3 +778,40 @@ def test_reference_kernels_agree_when_built(amp, oracle):
         amp.exl3_reconstruct_had(mineh, t, dev(suh), dev(svh), K, mul1=(cb == 2), mcg=(cb == 1))
         torch.cuda.synchronize()
         assert np.array_equal(host16(refh), host16(mineh))
+
+
+@pytest.mark.parametrize("K", [3, 4, 5])
+def test_shards_cut_on_the_device_are_the_host_slices(K):
+    """amp_exl3_shard_cols / amp_exl3_shard_rows (load path): byte moves, bit for bit the narrow + cat
+    of the reference's sub_columns / rows (src/ucode/ampstein/models.uc:440-562), several ranges in
+    one launch, and the sharded linears still give the full product's columns / partial sums."""
+    import ampstein_b200 as amp
+    from ampstein_b200.models import LinearEXL3, cols, rows
+    k, n = 512, 1024
+    trellis, suh, svh, x = make_linear(k, n, K, seed=9100 + K, m=2)
+    t, s, v = dev(trellis), dev(suh), dev(svh)
+    ranges = [(256, 128), (0, 256), (768, 256)]
+    tr, sv = amp.exl3_shard_cols(t, v, ranges)
+    torch.cuda.synchronize()
+    want_t = np.concatenate([trellis[:, a // 16:(a + ln) // 16] for a, ln in ranges], axis=1)
+    want_v = np.concatenate([svh[a:a + ln] for a, ln in ranges])
+    assert np.array_equal(tr.cpu().numpy().view(np.uint16), want_t.view(np.uint16))
+    assert np.array_equal(sv.cpu().numpy().view(np.uint16), want_v.view(np.uint16))
+    tr2, su2 = amp.exl3_shard_rows(t, s, 128, 256)
+    torch.cuda.synchronize()
+    assert np.array_equal(tr2.cpu().numpy().view(np.uint16), trellis[8:24].view(np.uint16))
+    assert np.array_equal(su2.cpu().numpy().view(np.uint16), suh[128:384].view(np.uint16))
+    # through the model layer: column shards give the columns, row shards sum to the whole
+    lin = LinearEXL3(t, s, v)
+    xd = dev(x)
+    full = lin.forward(xd).float().cpu().numpy()
+    part = cols(lin, ranges).forward(xd).float().cpu().numpy()
+    want = np.concatenate([full[:, a:a + ln] for a, ln in ranges], axis=1)
+    assert np.max(np.abs(part - want)) / np.max(np.abs(full)) < 2e-3       # (the k split of the launch may differ)
+    halves = sum(rows(lin, k0, 256).forward(xd[:, k0:k0 + 256].contiguous()).float().cpu().numpy() for k0 in (0, 256))
+    assert np.max(np.abs(halves - full)) / np.max(np.abs(full)) < 1e-2
+    for bad in ([(64, 128)], [(0, 100)], [(1024, 128)], []):
+        with pytest.raises(ValueError):
+            amp.exl3_shard_cols(t, v, bad)
+    with pytest.raises(ValueError):
+        amp.exl3_shard_rows(t, s, 64, 128)
