@@ -2,8 +2,8 @@
 kernels, exl3_mgemm, exl3_moe_coop), compiled unmodified for sm_100a into oracle/_ref, run next
 to this library on identical inputs: a second oracle (outputs within 1e-2 of the fp32-accumulated
 CPU oracle and of each other; the fused MoE within the 0.02 of the reference's own
-tests/moe_mixed.uc) and the bar for the timing table (`-s` prints it; it is also written to
-gpurun_out/ref_kernel_timing.json). Skipped when the reference library was not built."""
+tests/moe_mixed.uc) and the bar for the timing table (`-s` prints it; with AMP_RESULTS_DIR set it is
+also written there as ref_kernel_timing.json). Skipped when the reference library was not built."""
 import ctypes
 import json
 import os
@@ -336,8 +336,8 @@ def test_timing_table(amp):
 
     for r in rows:
         print(r)
-    out_dir = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out_dir):
+    out_dir = os.environ.get("AMP_RESULTS_DIR")
+    if out_dir and os.path.isdir(out_dir):
         json.dump(rows, open(os.path.join(out_dir, "ref_kernel_timing.json"), "w"), indent=1)
     assert all(r["ours_us"] > 0 and r["reference_us"] > 0 for r in rows)
 
@@ -415,7 +415,7 @@ def test_sorted_moe_next_to_the_reference_kernel(amp, cbname, T):
     row = dict(case="token-sorted MoE 128 experts top-8 K3 %s, %d tokens" % (cbname, T),
                ours_us=round(time_us(ours_call), 1), reference_us=round(time_us(ref_call), 1), max_rel_diff=float(rel(m, r)))
     print(row)
-    out_dir = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out_dir):
+    out_dir = os.environ.get("AMP_RESULTS_DIR")
+    if out_dir and os.path.isdir(out_dir):
         with open(os.path.join(out_dir, "ref_moe_sorted_timing.jsonl"), "a") as f:
             f.write(json.dumps(row) + "\n")
