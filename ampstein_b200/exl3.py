@@ -376,9 +376,21 @@ def mgemm_rms_norm_res(x, res, norm_w, eps, y, B_ptrs, C, suh_ptrs, svh_ptrs, K,
     return C
 
 
-def exl3_gemm_recon(x, trellis, suh, svh, K, mul1=False, mcg=False):
-    """EXL3 matmul for many rows (prefill); returns a new (rows, n) fp16 tensor
-    (reference: torch_exl3_gemm_recon)."""
+# Widest weight that takes the reconstruct-then-matmul form in exl3_gemm_recon. Measured on B200 at
+# 256..4096 rows (k = 4096 / 5120, 5 bits): up to 2048 columns the decode-once form is 1.25-2.2x
+# faster than the tensor-core trellis GEMM (whose k loop is as long for a narrow weight as for a
+# wide one, with most SMs idle), at 4096 columns the two are level, above it the trellis GEMM wins.
+RECON_MM_MAX_N = 2048
+
+
+def exl3_gemm_recon(x, trellis, suh, svh, K, mul1=False, mcg=False, out=None, scratch=None):
+    """EXL3 matmul for many rows (prefill); returns a (rows, n) fp16 tensor (reference:
+    torch_exl3_gemm_recon, src/torch/amp_torch.cpp:11128-11230). Narrow weights (n <= RECON_MM_MAX_N)
+    take the reference's own form of this operator -- the weight decoded ONCE into fp16 with both
+    Hadamards and scales folded in (this library's reconstruct_had kernel), then one plain library
+    GEMM; wider ones the tensor-core trellis GEMM, which never writes the decoded weight to memory.
+    out / scratch: optional preallocated result and (k, n) fp16 buffer for the decoded weight (the
+    reference allocates both per call from the caching allocator; so does this function without them)."""
     _check_cuda("exl3_gemm_recon", x, trellis, suh, svh)
     k, n, Kt = _trellis_dims("exl3_gemm_recon", trellis)
     if x.dim() != 2 or x.shape[1] != k or suh.numel() != k or svh.numel() != n or n > 32768:
@@ -386,7 +398,11 @@ def exl3_gemm_recon(x, trellis, suh, svh, K, mul1=False, mcg=False):
                          % (tuple(x.shape), k, n))
     if float(K) != float(Kt):
         raise ValueError("exl3_gemm_recon: K does not match the trellis")
-    y = torch.empty((x.shape[0], n), dtype=torch.float16, device=x.device)
+    y = out if out is not None else torch.empty((x.shape[0], n), dtype=torch.float16, device=x.device)
+    if n <= RECON_MM_MAX_N and x.dtype == torch.float16 and x.shape[0] > 16:
+        w = scratch if scratch is not None else torch.empty((k, n), dtype=torch.float16, device=x.device)
+        exl3_reconstruct_had(w, trellis, suh, svh, K, mul1, mcg)
+        return torch.mm(x, w, out=y)
     return exl3_gemm(x, trellis, y, suh, svh, mul1, mcg)
 
 

@@ -562,6 +562,21 @@ def test_lm_head_with_norm_argmax_and_state_advance(amp, oracle):
     assert int(ids.item()) == 0 and int(pos.item()) == 4
 
 
+def test_gemm_recon_takes_the_trellis_gemm_for_wide_weights(amp, oracle):
+    """Above RECON_MM_MAX_N columns the many-rows operator is the tensor-core trellis GEMM (same bits
+    as exl3_gemm); at or below it the weight is reconstructed once and multiplied by a library GEMM."""
+    from ampstein_b200 import exl3
+    k, n, K, rows = 256, exl3.RECON_MM_MAX_N + 256, 4, 150
+    trellis, suh, svh, x = make_linear(k, n, K, seed=6250, m=rows)
+    t, su, sv, xx = dev(trellis), dev(suh), dev(svh), dev(x)
+    y = torch.empty((rows, n), dtype=torch.float16, device="cuda")
+    amp.exl3_gemm(xx, t, y, su, sv)
+    z = amp.exl3_gemm_recon(xx, t, su, sv, K)
+    torch.cuda.synchronize()
+    assert torch.equal(y, z)
+    check_close(z.float().cpu().numpy(), oracle.linear(x, trellis, suh, svh, 0, fp32_out=True))
+
+
 @pytest.mark.parametrize("rows", [200, 1100])
 def test_gemm_recon_next_to_gemm(amp, oracle, rows):
     """The many-rows operator against the in-place operator on the same input, at the two row

@@ -246,12 +246,14 @@ def test_timing_table(amp):
                 x = torch.randn((M, k), device="cuda", generator=g).to(torch.float16)
                 y = torch.empty((M, n), dtype=torch.float16, device="cuda")
                 w = torch.empty((k, n), dtype=torch.float16, device="cuda")
+                w2 = torch.empty((k, n), dtype=torch.float16, device="cuda")
                 a_had = torch.empty_like(x)
                 from ampstein_b200 import _lib
 
                 def ours_call(L):
-                    _lib.call("amp_exl3_gemm", x.data_ptr(), L.trellis.data_ptr(), y.data_ptr(), L.suh.data_ptr(), a_had.data_ptr(),
-                              L.svh.data_ptr(), M, k, n, K, 0, 0, torch.cuda.current_stream().cuda_stream)
+                    # the operator of this row count (reference: torch.exl3_gemm_recon): the tensor-core trellis
+                    # GEMM, or reconstruct_had + a library GEMM for narrow weights
+                    amp.exl3_gemm_recon(x, L.trellis, L.suh, L.svh, K, out=y, scratch=w2)
 
                 def ref_call(L):
                     # (the reference kernels run on the legacy default stream, so they are timed eagerly)
