@@ -159,8 +159,8 @@ constexpr int GEMV_PREROTATE_MIN_M = 5;
 
 // Int8-activation form of the one-row GEMV for mul1 (codebook 2) tensors, as the reference's
 // EXL3_INT8_GEMV switch (vendor/exl3/exllamav3_ext/quant/exl3_gemv_int8.cu:20-52): 0 = off, 2 = plain
-// int8 (the reference's default). Its mode 1 (int8 + residual pass) is not implemented: the fp16
-// kernel, which is more precise than either, runs instead. The environment variables are read once.
+// int8 (the reference's default), 1 = int8 with the error-feedback pass. The environment variables
+// are read once.
 static int int8_env(const char* name, int fallback)
 {
     const char* e = getenv(name);
@@ -219,9 +219,11 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
                 "exl3_gemv: the fused norm takes x, residual, weight and a separate output for the residual stream, 8-byte aligned");
     const bool special_in = fused_act || fused_norm || norm_producer || norm_consumer;
     const bool prerot = !tc && !A.mode && !A.arin.N && !special_in && m >= GEMV_PREROTATE_MIN_M && A.x_rot && A.x;
-    const bool i8 = !tc && !A.mode && !A.arin.N && !special_in && A.cb == 2 && m == 1 && g_int8_gemv == 2 && K <= g_int8_max_k;
+    // mul1, one row: int8 activations (kernel instance 3), or int8 with error-feedback codes (instance 4)
+    const int i8 = (!tc && !A.mode && !A.arin.N && !special_in && A.cb == 2 && m == 1 && K <= g_int8_max_k)
+                       ? (g_int8_gemv == 2 ? 3 : (g_int8_gemv == 1 ? 4 : 0)) : 0;
     gemv_fn fn = tc ? gemv_tc_kernel_for(K, A.cb, A.ar.N != 0)
-                    : gemv_kernel_for(K, i8 ? 3 : A.cb, MB, A.mode, A.arin.N ? 1 : (norm_producer ? 5 : (norm_consumer ? 6 : (fused_norm ? 4 : (fused_act ? 3 : (prerot ? 2 : 0))))));
+                    : gemv_kernel_for(K, i8 ? i8 : A.cb, MB, A.mode, A.arin.N ? 1 : (norm_producer ? 5 : (norm_consumer ? 6 : (fused_norm ? 4 : (fused_act ? 3 : (prerot ? 2 : 0))))));
     if (!fn) return fail(AMP_E_UNSUPPORTED, "exl3_gemv: no kernel for K=%d cb=%d", K, A.cb);
 
     // x~ rows resident at a time: at most 16 KB of shared memory (whole segments for small
@@ -255,7 +257,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
     }
     // tensor-memory kernel: x~ in chunks of four 64-row groups (two 128-row transforms), two buffers
     const int tc_xg = G < 4 ? G : 4;
-    GemvSmem L = gemv_smem_layout(K, m, xcap);
+    GemvSmem L = gemv_smem_layout(K, m, xcap, 0, 0, i8 == 4 ? gemv_xpitch(xcap) * 4 : 0);     // (instance 4: a second x~ area for the error codes)
     if (tc) L.total = tcv_smem_layout(K, m, tc_xg).total;
     AMP_REQUIRE(L.total <= D.smem_optin, "exl3_gemv: shared memory layout does not fit (%d bytes)", L.total);
     // CTAs per SM: the decode is bound by the rate of the integer pipes, not by latency, so
@@ -330,6 +332,7 @@ int launch_gemv(const GemvLaunch& A, cudaStream_t stream)
         const int want = 4 * k;
         if (smem_per_sm / (gemv_smem_layout(K, m, xgroups, cluster, 0, want).total + 1024) >= ctas_per_sm) rowbuf = want;
     }
+    if (i8 == 4) rowbuf = gemv_xpitch(xgroups) * 4;
     L = gemv_smem_layout(K, m, xgroups, cluster, A.arin.N != 0, rowbuf);
     if (tc)
     {
@@ -450,13 +453,15 @@ AMP_API int amp_exl3_gemv(const void* x, const void* trellis, void* c, const voi
     return launch_gemv(direct(x, trellis, c, suh, svh, m, k, n, K, cb, c_fp32, 0, 0), stream);
 }
 
-// 0 = the mul1 one-row GEMV runs the fp16 kernel, 2 = int8 activations (the reference's
-// EXL3_INT8_GEMV modes; 1 is accepted and means 0 here). max_k > 0 also sets the highest bit width
-// that takes the int8 form (EXL3_INT8_GEMV_MAX_K). Returns the previous mode.
+// 0 = the mul1 one-row GEMV runs the fp16 kernel, 2 = int8 activations, 1 = int8 activations with an
+// error-feedback pass (the rounding error of the codes quantised again and accumulated by a second
+// dp4a: ~15 bits of effective activation precision) -- the reference's EXL3_INT8_GEMV modes.
+// max_k > 0 also sets the highest bit width that takes the int8 forms (EXL3_INT8_GEMV_MAX_K).
+// Returns the previous mode.
 AMP_API int amp_exl3_set_int8_gemv(int mode, int max_k)
 {
     const int old = g_int8_gemv;
-    g_int8_gemv = mode == 2 ? 2 : 0;
+    g_int8_gemv = (mode == 1 || mode == 2) ? mode : 0;
     if (max_k > 0) g_int8_max_k = max_k > 8 ? 8 : max_k;
     return old;
 }

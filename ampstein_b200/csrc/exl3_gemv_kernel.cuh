@@ -441,6 +441,26 @@ __device__ __forceinline__ void decode_dp4a_r(const uint32_t (&w)[K], uint32_t p
     a1[1] = dp4a_us(s[7] * 0x83DCD12Du, xs[2 * R + 9], a1[1]);
 }
 
+// The same with a second set of activation codes (the int8 rounding error of the first set, quantised
+// again): the decoded products are shared, each costs one more dp4a.
+template <int K, int R>
+__device__ __forceinline__ void decode_dp4a2_r(const uint32_t (&w)[K], uint32_t prev, const uint32_t (&xs)[16], const uint32_t (&xr)[16],
+                                               int (&a0)[2], int (&a1)[2], int (&b0)[2], int (&b1)[2])
+{
+    uint32_t s[8];
+    states8<K, R, false>(w, prev, s);
+    #pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] *= 0x83DCD12Du;
+    a0[0] = dp4a_us(s[0], xs[2 * R], a0[0]);         b0[0] = dp4a_us(s[0], xr[2 * R], b0[0]);
+    a0[1] = dp4a_us(s[2], xs[2 * R + 8], a0[1]);     b0[1] = dp4a_us(s[2], xr[2 * R + 8], b0[1]);
+    a1[0] = dp4a_us(s[4], xs[2 * R], a1[0]);         b1[0] = dp4a_us(s[4], xr[2 * R], b1[0]);
+    a1[1] = dp4a_us(s[6], xs[2 * R + 8], a1[1]);     b1[1] = dp4a_us(s[6], xr[2 * R + 8], b1[1]);
+    a0[0] = dp4a_us(s[1], xs[2 * R + 1], a0[0]);     b0[0] = dp4a_us(s[1], xr[2 * R + 1], b0[0]);
+    a0[1] = dp4a_us(s[3], xs[2 * R + 9], a0[1]);     b0[1] = dp4a_us(s[3], xr[2 * R + 9], b0[1]);
+    a1[0] = dp4a_us(s[5], xs[2 * R + 1], a1[0]);     b1[0] = dp4a_us(s[5], xr[2 * R + 1], b1[0]);
+    a1[1] = dp4a_us(s[7], xs[2 * R + 9], a1[1]);     b1[1] = dp4a_us(s[7], xr[2 * R + 9], b1[1]);
+}
+
 // thread-block cluster helpers: rank of this CTA, address of a shared-memory location in another
 // CTA of the cluster, a store there, and the cluster-wide barrier (release / acquire)
 __device__ __forceinline__ uint32_t cluster_rank()
@@ -657,13 +677,15 @@ __global__ __launch_bounds__(GEMV_THREADS, (MB == 1 ? AMP_GEMV_MINBLOCKS : 3))
 void exl3_gemv_kernel(const GemvParams P)
 {
     extern __shared__ __align__(128) unsigned char smem[];
-    const GemvSmem L = gemv_smem_layout(K, P.m, P.xgroups, P.cluster, GIN == 1, GIN == 4 ? P.rowbuf : 0);
+    const GemvSmem L = gemv_smem_layout(K, P.m, P.xgroups, P.cluster, GIN == 1, (GIN == 4 || CB == 4) ? P.rowbuf : 0);
     const int XPITCH = gemv_xpitch(P.xgroups);
     const int XG = P.xgroups;
     float* part = reinterpret_cast<float*>(smem + L.part);
     uint32_t* xd = reinterpret_cast<uint32_t*>(smem + L.xd);
     float* gsum = reinterpret_cast<float*>(smem + L.gsum);
     float* qs = reinterpret_cast<float*>(smem + L.qs);
+    uint32_t* xd2 = reinterpret_cast<uint32_t*>(smem + L.total - (CB == 4 ? P.rowbuf : 0));   // CB 4: second set of int8 codes
+    (void) xd2;
     __shared__ int s_last;
 
     constexpr int S = gemv_stages(K);
@@ -1055,7 +1077,7 @@ void exl3_gemv_kernel(const GemvParams P)
             // store one task's four rotated values per lane; b, jb name the task
             auto frag_store = [&](int b, int jb, const __half2 o01, const __half2 o23)
             {
-                if constexpr (CB == 3)
+                if constexpr (CB == 3 || CB == 4)
                 {
                     // int8 activations: one scale per 128-row block (this warp's task), codes
                     // replicated into the four bytes of the word the fp16 pair would occupy
@@ -1072,14 +1094,31 @@ void exl3_gemv_kernel(const GemvParams P)
                     const int r = jb * 128 + lane * 4;
                     const int word = (r >> 6) * 64 + ((r & 15) >> 2) * 16 + ((r & 63) >> 4) * 4;
                     *reinterpret_cast<uint4*>(xd + b * XPITCH + word) = d;
+                    const float q = __fdiv_rn(mx, 127.0f);
                     // per 64-row group (lanes 0-15 / 16-31): the dequantised sum of the codes and the scale
                     int si = (i0 + i1) + (i2 + i3);
                     #pragma unroll
                     for (int i = 1; i < 16; i <<= 1) si += __shfl_xor_sync(0xffffffffu, si, i);
+                    float gs = q * (float) si;
+                    if constexpr (CB == 4)
+                    {
+                        // error feedback: the rounding error of the first code (within +- q / 2) quantised with
+                        // the fixed scale q / 254 (reference: gemv_int8_stage_splats, exl3_gemv_int8_kernel.cuh:251-280)
+                        const float inv2 = mx > 0.0f ? 254.0f * inv : 0.0f;
+                        auto code2 = [&](float v, int c) { return max(-127, min(127, __float2int_rn(fmaf(-q, (float) c, v) * inv2))); };
+                        const int j0 = code2(v0, i0), j1 = code2(v1, i1), j2 = code2(v2, i2), j3 = code2(v3, i3);
+                        uint4 e;
+                        e.x = (uint32_t) (j0 & 0xff) * 0x01010101u; e.y = (uint32_t) (j1 & 0xff) * 0x01010101u;
+                        e.z = (uint32_t) (j2 & 0xff) * 0x01010101u; e.w = (uint32_t) (j3 & 0xff) * 0x01010101u;
+                        *reinterpret_cast<uint4*>(xd2 + b * XPITCH + word) = e;
+                        int sj = (j0 + j1) + (j2 + j3);
+                        #pragma unroll
+                        for (int i = 1; i < 16; i <<= 1) sj += __shfl_xor_sync(0xffffffffu, sj, i);
+                        gs = fmaf(q * (1.0f / 254.0f), (float) sj, gs);
+                    }
                     if ((lane & 15) == 0)
                     {
-                        const float q = __fdiv_rn(mx, 127.0f);
-                        gsum[b * XG + 2 * jb + (lane >> 4)] = q * (float) si;
+                        gsum[b * XG + 2 * jb + (lane >> 4)] = gs;
                         qs[b * XG + 2 * jb + (lane >> 4)] = q;
                     }
                     return;
@@ -1464,7 +1503,7 @@ void exl3_gemv_kernel(const GemvParams P)
             __syncthreads();
 
             const int c0 = max(cg0, g0);                // first group of the chunk that belongs to the range
-            if constexpr (CB == 2 || CB == 3)
+            if constexpr (CB == 2 || CB == 3 || CB == 4)
             {
                 #pragma unroll
                 for (int mb = 0; mb < MB; ++mb)
@@ -1503,7 +1542,29 @@ void exl3_gemv_kernel(const GemvParams P)
                     load_chunk_s<K>(w_off + cslot + nt * TILE_BYTES, w[nt]);
                     prev[nt] = lds32(p_off + cslot + nt * TILE_BYTES);
                 }
-                if constexpr (CB == 3)
+                if constexpr (CB == 4)
+                {
+                    // int8 activations with the error-feedback codes: two exact integer sums per unit
+                    uint32_t xr[16];
+                    #pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        lds128(xaddr + (uint32_t) ((xd2 - xd) * 4) + xrow[0] * 4 + i * 64, xr[4 * i], xr[4 * i + 1], xr[4 * i + 2], xr[4 * i + 3]);
+                    const float q = qs[(c0 - cg0) + (cg1 - c0 - n)], q2 = q * (1.0f / 254.0f);
+                    #pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                    {
+                        int a0[2] = { 0, 0 }, a1[2] = { 0, 0 }, b0[2] = { 0, 0 }, b1[2] = { 0, 0 };
+                        decode_dp4a2_r<K, 0>(w[nt], prev[nt], xb[0], xr, a0, a1, b0, b1);
+                        decode_dp4a2_r<K, 1>(w[nt], prev[nt], xb[0], xr, a0, a1, b0, b1);
+                        decode_dp4a2_r<K, 2>(w[nt], prev[nt], xb[0], xr, a0, a1, b0, b1);
+                        decode_dp4a2_r<K, 3>(w[nt], prev[nt], xb[0], xr, a0, a1, b0, b1);
+                        acc0[nt][0][0] = fmaf(q, (float) (a0[0] + a0[1]), acc0[nt][0][0]);
+                        acc0[nt][0][2] = fmaf(q, (float) (a1[0] + a1[1]), acc0[nt][0][2]);
+                        acc1[nt][0][0] = fmaf(q2, (float) (b0[0] + b0[1]), acc1[nt][0][0]);
+                        acc1[nt][0][2] = fmaf(q2, (float) (b1[0] + b1[1]), acc1[nt][0][2]);
+                    }
+                }
+                else if constexpr (CB == 3)
                 {
                     // int8 activations (one batch row): exact integer sums over the unit, scaled by
                     // the unit's block scale into the fp32 sums of the segment
@@ -1566,7 +1627,7 @@ void exl3_gemv_kernel(const GemvParams P)
                 d0 = d0 * kinv + xsum[mb][0] * kbias; d1 = d1 * kinv + xsum[mb][1] * kbias;
                 d2 = d2 * kinv + xsum[mb][0] * kbias; d3 = d3 * kinv + xsum[mb][1] * kbias;
             }
-            if constexpr (CB == 3)
+            if constexpr (CB == 3 || CB == 4)
             {
                 // the four lanes of a column hold the sums of their tile rows: add them up (fixed
                 // order), then sum x*w = k_inv * sum x*bytesum + (1024 k_inv + k_bias) * sum x

@@ -1001,6 +1001,8 @@ def main():
     ap.add_argument("--silu-mul", action="store_true", help="--workload gemv: the down projection with silu(gate) * up folded into its prologue")
     ap.add_argument("--norm", action="store_true", help="--workload gemv: the linear with the residual add + RMSNorm folded into its prologue")
     ap.add_argument("--no-int8", action="store_true", help="--workload gemv --mul1: keep the fp16 kernel (A/B)")
+    ap.add_argument("--int8-residual", action="store_true",
+                    help="--workload gemv --mul1: the int8 form with the error-feedback pass (the reference's EXL3_INT8_GEMV=1)")
     ap.add_argument("--separate", action="store_true",
                     help="--workload prefill: seven separate GEMM calls instead of the q|k|v and gate|up bundles")
     ap.add_argument("--tile-sub", type=int, default=0, choices=[0, 1, 2, 4],
@@ -1044,9 +1046,9 @@ def main():
                 assert len(shape) == 3 and shape[0] % 128 == 0 and shape[1] % 128 == 0 and 1 <= shape[2] <= 8
             except (ValueError, AssertionError):
                 raise SystemExit("bench.py: --shape must be KxNxBITS with k, n multiples of 128 and 1..8 bits")
-            if args.no_int8:
+            if args.no_int8 or args.int8_residual:
                 from ampstein_b200 import _lib
-                _lib.lib().amp_exl3_set_int8_gemv(0, 0)
+                _lib.lib().amp_exl3_set_int8_gemv(1 if args.int8_residual else 0, 0)
             print(json.dumps(measure_gemv(args.steps, args.warmup, shape, args.batch, args.tmem_gemv, args.mul1, args.silu_mul, args.norm)), flush=True)
         else:
             print(json.dumps({"metric": "scheduler cycles per 8 decoded weights and lane (K=4 mix)", "unit": "cycles",

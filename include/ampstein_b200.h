@@ -115,10 +115,11 @@ int amp_exl3_set_gemm_pair(int mode);
  * Int8-activation form of the one-row GEMV for mul1 (codebook 2) tensors up to max_k bits: the
  * rotated input is quantised to int8 with one scale per 128 rows of k and the dot product runs as
  * dp4a on the byte sum of the codebook's product, exact in int32 (about 6e-3 relative rms against
- * the fp16 form). mode: 0 off, 2 on (default, as the reference's EXL3_INT8_GEMV, whose value this
- * library also reads from the environment at load, with EXL3_INT8_GEMV_MAX_K, default 6); the
- * reference's mode 1 (residual pass) is not implemented and selects the fp16 kernel. max_k <= 0
- * leaves the bit-width limit as it is. Returns the previous mode.
+ * the fp16 form). mode: 0 off, 2 on (default), 1 on with the error-feedback pass (the rounding error of
+ * the codes quantised again at 1/254 of the scale and accumulated by a second dp4a: about 2e-4
+ * relative rms, at the speed of the fp16 kernel) -- the reference's EXL3_INT8_GEMV modes, whose
+ * value this library also reads from the environment at load, with EXL3_INT8_GEMV_MAX_K, default 6.
+ * max_k <= 0 leaves the bit-width limit as it is. Returns the previous mode.
  * Replaces: the dispatch of exl3_gemm to exl3_gemv_int8, Q/exl3_gemm.cu:188-196,
  * Q/exl3_gemv_int8.cu:20-52, kernel Q/exl3_gemv_int8_kernel.cuh (m == 1 only; half-integer
  * bitrates are not supported).

@@ -162,9 +162,10 @@ def linear(x, trellis, suh, svh, cb=0, fp32_out=False, what=None):
     return o32 if fp32_out else o16.view(np.float16)
 
 
-def linear_int8(x, trellis, suh, svh, fp32_out=False):
+def linear_int8(x, trellis, suh, svh, fp32_out=False, residual=False):
     """The mul1 (cb 2) linear with int8-quantised rotated activations, one scale per 128 rows of k
-    (the arithmetic of the int8-activation GEMV). Returns fp16 (m,n), or fp32 when fp32_out."""
+    (the arithmetic of the int8-activation GEMV); residual: with the error-feedback codes (the
+    rounding error quantised again at scale q / 254). Returns fp16 (m,n), or fp32 when fp32_out."""
     xx = _h(x)
     m, k = xx.shape
     t = _h(trellis)
@@ -172,7 +173,8 @@ def linear_int8(x, trellis, suh, svh, fp32_out=False):
     assert kk == k
     o16 = np.empty((m, n), np.uint16)
     o32 = np.empty((m, n), np.float32)
-    rc = lib().exl3o_linear_int8(_p16(xx), _p16(t), _p16(_h(suh)), _p16(_h(svh)), m, k, n, K, _p16(o16), _p32(o32))
+    fn = lib().exl3o_linear_int8_residual if residual else lib().exl3o_linear_int8
+    rc = fn(_p16(xx), _p16(t), _p16(_h(suh)), _p16(_h(svh)), m, k, n, K, _p16(o16), _p32(o32))
     assert rc == 0, rc
     return o32 if fp32_out else o16.view(np.float16)
 

@@ -213,6 +213,45 @@ def test_sorted_moe_agrees_with_the_decode_moe(amp):
     check(got, dec, tol=5e-3)
 
 
+def test_sorted_moe_replays_from_a_cuda_graph_with_new_routing(amp, oracle):
+    """Nothing in the call depends on the routing's values on the host: captured once in a CUDA graph,
+    the six launches serve a different routing (other counts, other tiles) written into the same
+    device tensors before a replay."""
+    E, H, I, K, topk, T = 8, 256, 128, 3, 2, 96
+    ex = make_experts(E, H, I, H, K, seed=3900)
+    cfg = build_cfg(amp, ex, H, I, H, H, K, 1, topk)
+    cfg["I"] = I
+    rng = np.random.default_rng(81)
+    cases = []
+    for i in range(2):
+        x = rng.standard_normal((T, H)).astype(np.float16)
+        sel, rw = routing(rng, T, E, topk)
+        if i == 1:
+            sel[:60, 0] = 5                              # a heavy expert and two empty ones
+            sel[:, 1] = np.where(np.isin(sel[:, 1], (0, 5, 7)), 3, sel[:, 1])
+            sel[:, 0] = np.where(np.isin(sel[:, 0], (0, 7)), 2, sel[:, 0])
+            sel[:, 1] = np.where(sel[:, 1] == sel[:, 0], (sel[:, 0] + 1) % 7 + (sel[:, 0] + 1) // 7, sel[:, 1])
+        cases.append((x, sel, rw))
+    xd = dev(cases[0][0])
+    count, tok, wts = amp.moe_sort_routing(dev(cases[0][1]), dev(cases[0][2]), E)
+    out = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    st, gr = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+    with torch.cuda.stream(st):
+        amp.moe_fused(xd, out, count, tok, wts, cfg)    # warm-up: workspace and kernel attributes exist before capture
+    torch.cuda.synchronize()
+    with torch.cuda.stream(st), torch.cuda.graph(gr, stream=st):
+        amp.moe_fused(xd, out, count, tok, wts, cfg)
+    for x, sel, rw in cases[::-1]:
+        c2, t2, w2 = amp.moe_sort_routing(dev(sel), dev(rw), E)
+        xd.copy_(dev(x)); count.copy_(c2); tok.copy_(t2); wts.copy_(w2)
+        out.zero_()
+        torch.cuda.synchronize()
+        gr.replay()
+        torch.cuda.synchronize()
+        assert amp.moe_fused_status(cfg) == 0
+        check(out.cpu().numpy(), oracle.moe_coop(x, sel, rw, ex, gu_f16=True))
+
+
 def test_sorted_moe_reports_bad_routing_without_touching_memory(amp):
     """A token index outside [0, T) and counts that describe more rows than the list holds set the
     status word; the entries in error are left out."""

@@ -347,6 +347,14 @@ def test_int8_activation_gemv_mul1(amp, oracle, k, n, K):
     assert 1e-4 < rms < 1e-2, rms                                  # really the int8 form, and within its figure
     fp = run(x1, 0)
     check_close(fp, ref)                                           # switch off: the fp16 kernel
+    # mode 1, the error-feedback form: agrees with its own CPU restatement and is far closer to
+    # the fp32-accumulated linear than the plain int8 form (about 15 bits of activation precision)
+    ref8r = oracle.linear_int8(x1, trellis, suh, svh, fp32_out=True, residual=True)
+    got_r = run(x1, 1)
+    assert np.all(np.isfinite(got_r))
+    assert np.max(np.abs(got_r - ref8r)) / np.max(np.abs(ref8r)) < 1e-4
+    rms_r = np.sqrt(np.mean((got_r.astype(np.float64) - ref) ** 2) / np.mean(ref.astype(np.float64) ** 2))
+    assert rms_r < 1e-3 and rms_r < rms / 4, (rms_r, rms)
     assert np.array_equal(run(x1, 2, max_k=K - 1), fp) if K > 1 else True    # above the bit-width limit
     both = run(x, 2)                                               # two rows: fp16 kernel
     check_close(both, oracle.linear(x, trellis, suh, svh, 2, fp32_out=True))
