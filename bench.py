@@ -664,6 +664,52 @@ def measure_moe_prefill(steps, warmup, T=2048):
                      "kernel": "exl3_gemm_tc_kernel<K, CB, grouped>", "flops_per_layer": int(flops), "traffic": None}}
 
 
+def measure_gemm(steps, warmup, shape, rows):
+    """One prefill shape (rows x k through a k x n weight at K bits) through both many-row forms:
+    the tensor-core trellis GEMM (exl3_gemm) and reconstruct_had + a library GEMM (what
+    exl3_gemm_recon takes for narrow weights). Distinct weight copies exceed L2; eager launches."""
+    import torch
+    import ampstein_b200 as amp
+    k, n, K = shape
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(6)
+    wbytes = k * n * K // 8
+    copies = max(2, min(32, -(-2 * 126 * 2 ** 20 // (wbytes + 2 * k * n))))
+    mats = [torch.randint(-32768, 32768, (k // 16, n // 16, 16 * K), dtype=torch.int16, device=dev, generator=g) for _ in range(copies)]
+    sgn = lambda c: (torch.randint(0, 2, (c,), device=dev, generator=g).to(torch.float16) * 2 - 1)
+    suh, svh = sgn(k), (sgn(n) / (1.2437 * math.sqrt(k))).to(torch.float16)
+    x = torch.randn((rows, k), device=dev, generator=g).to(torch.float16)
+    y = torch.empty((rows, n), dtype=torch.float16, device=dev)
+    w = torch.empty((k, n), dtype=torch.float16, device=dev)
+
+    def trellis():
+        for t in mats:
+            amp.exl3_gemm(x, t, y, suh, svh)
+
+    def recon():
+        for t in mats:
+            amp.exl3_reconstruct_had(w, t, suh, svh, K)
+            torch.mm(x, w, out=y)
+
+    out = {}
+    sampler = ClockSampler(0)
+    t0 = time.time()
+    for name, fn in (("trellis_gemm", trellis), ("reconstruct_plus_library_gemm", recon)):
+        for _ in range(max(warmup, 3)):
+            fn()
+        ms_blk, _, _ = timed_blocks(torch, fn, steps, min_s=0.2)
+        us = ms_blk * 1e3 / (steps * copies)
+        out[name] = {"us": round(us, 1), "tflops": round(2.0 * rows * k * n / us / 1e6, 1)}
+    clocks = sampler.stop(t0, time.time())
+    pick = "reconstruct_plus_library_gemm" if n <= amp.exl3.RECON_MM_MAX_N else "trellis_gemm"
+    return {"metric": "prefill GEMM time (%d rows x %dx%d, K=%d)" % (rows, k, n, K), "value": out[pick]["us"], "unit": "us/launch",
+            "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3), "higher_is_better": False, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "one prefill shape, %d distinct weight copies in turn (larger than L2), eager launches" % copies,
+                       "exl3_gemm_recon_takes": pick},
+            "forms": out, "gpu_launches": copies * steps, "clocks": clocks}
+
+
 def measure_gemv(steps, warmup, shape, m, tmem=False, mul1=False, silu_mul=False, norm=False):
     """One decode GEMV shape on its own (k x n at K bits, m rows): as many distinct copies of the
     matrix as it takes to exceed L2 twice over, one launch per copy, all in one CUDA graph."""
@@ -987,14 +1033,14 @@ def main():
                     help="tensor-parallel mode: how the all-reduce after o / down runs. fused (default): push and gather in the "
                          "producing GEMV's epilogue; split: the producer only pushes its partial, the consuming GEMV adds the ranks' "
                          "partials up in its prologue (measured slower); separate: a stand-alone all-reduce launch")
-    ap.add_argument("--workload", default="decode", choices=["decode", "tp5", "prefill", "moe", "moe-prefill", "gemv", "step", "issue"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "tp5", "prefill", "moe", "moe-prefill", "gemv", "gemm", "step", "issue"],
                     help="decode (default, the headline step), tp5 (the 64-layer 5-bit tensor-parallel stack), or a secondary "
                          "one-GPU workload: the prefill GEMM / the fused decode MoE / one GEMV shape (--shape) / the decode "
                          "step with its element-wise neighbours, separate and fused (step) / the issue-rate microbenchmark")
     ap.add_argument("--shape", default="4096x229376x4", help="--workload gemv: k x n x K (rows, columns, bits per weight)")
     ap.add_argument("--batch", type=int, default=1, help="tokens per decode step (decode / tp5 workloads), 1..16")
     ap.add_argument("--tokens", type=int, default=0,
-                    help="tokens per step of --workload moe (1, 4 or 16; default 1) / per chunk of --workload moe-prefill (default 2048)")
+                    help="tokens per step of --workload moe (1, 4 or 16; default 1) / per chunk of --workload moe-prefill / rows of --workload gemm (default 2048)")
     ap.add_argument("--tmem-gemv", action="store_true",
                     help="A/B: run the decode GEMVs on the tensor-memory (tcgen05) kernel instead of the mma.sync kernel")
     ap.add_argument("--mul1", action="store_true", help="--workload gemv: the mul1 codebook (one row then takes the int8-activation form)")
@@ -1025,7 +1071,7 @@ def main():
         return
     if args.workload == "moe" and (args.tokens or 1) not in (1, 4, 16):
         raise SystemExit("bench.py: --workload moe takes --tokens 1, 4 or 16")
-    if args.workload in ("prefill", "moe", "moe-prefill", "gemv", "step", "issue"):
+    if args.workload in ("prefill", "moe", "moe-prefill", "gemv", "gemm", "step", "issue"):
         import torch
         if not torch.cuda.is_available():
             raise SystemExit("bench.py: no CUDA device (the path has no CPU fallback)")
@@ -1040,6 +1086,13 @@ def main():
             print(json.dumps(measure_moe_prefill(args.steps, args.warmup, args.tokens or 2048)), flush=True)
         elif args.workload == "step":
             print(json.dumps(measure_step_with_neighbours(args.steps, args.warmup, args.layers)), flush=True)
+        elif args.workload == "gemm":
+            try:
+                shape = tuple(int(v) for v in args.shape.lower().split("x"))
+                assert len(shape) == 3 and shape[0] % 128 == 0 and shape[1] % 128 == 0 and 1 <= shape[2] <= 8
+            except (ValueError, AssertionError):
+                raise SystemExit("bench.py: --shape must be KxNxBITS with k, n multiples of 128 and 1..8 bits")
+            print(json.dumps(measure_gemm(args.steps, args.warmup, shape, args.tokens or 2048)), flush=True)
         elif args.workload == "gemv":
             try:
                 shape = tuple(int(v) for v in args.shape.lower().split("x"))
