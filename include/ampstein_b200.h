@@ -354,7 +354,9 @@ long amp_exl3_moe_coop_ctr_len(long slots_max, long rows_max, long I, long Ho);
  * and ADDED to out (fp32; the caller zero-fills it, as for the reference). start_e is the running
  * sum of count[0..e); the sentinel bin count[E] (picks that belong to nobody here) is ignored.
  * Every token must own the same number of entries of the sorted list (A = T * picks, picks <= 64).
- * Routing stays on the device; the call enqueues six launches on `stream` and returns.
+ * Routing stays on the device; the call enqueues six launches on `stream` and returns (no
+ * allocation, no host read-back: capturable in a CUDA graph and replayable with other routing in the
+ * same tensors). Calls that share a workspace must be ordered on one stream.
  * Replaces: exl3_moe, Q/exl3_moe.cu:139-531 (kernel Q/exl3_moe_kernel.cuh:61-313) together with
  * exl3_moe_gather, its fixed-order slot sum; bindings torch.moe_fused / torch.moe_gather,
  * src/torch/amp_torch.cpp:9257-9378. Differences: one call covers every row count (the reference
