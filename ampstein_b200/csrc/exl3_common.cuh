@@ -74,6 +74,21 @@ __device__ __forceinline__ uint32_t window_rt(const uint32_t* ring, int t)
     return __funnelshift_r(ring[j1], ring[j0], sh) & 0xffffu;
 }
 
+// Half-integer bitrates KA + 0.5 (reference: dq8_half, vendor/exl3/exllamav3_ext/quant/exl3_dq.cuh:254-284):
+// positions alternate KA and KA + 1 bits, the odd ones carrying the extra bit; with B2 = 2 KA + 1 the
+// window of position t ends (exclusive) at bit (t / 2) * B2 + KA for even t, (t / 2 + 1) * B2 for
+// odd t, in a ring of 4 * B2 words per tile.
+template <int KA>
+__device__ __forceinline__ uint32_t window_rt_half(const uint32_t* ring, int t)
+{
+    constexpr int B2 = 2 * KA + 1, W = 4 * B2;
+    const int last = ((t & 1) ? ((t >> 1) + 1) * B2 : (t >> 1) * B2 + KA) - 1;
+    const int j1 = last >> 5;
+    const int j0 = (j1 + W - 1) % W;
+    const int sh = 31 - (last & 31);
+    return __funnelshift_r(ring[j1], ring[j0], sh) & 0xffffu;
+}
+
 // (x & 0xffff) on the FMA-heavy pipe (dp2a with a one-hot byte vector), leaving the integer ALU
 // to the shifts
 __device__ __forceinline__ uint32_t mask16_fma(uint32_t x)

@@ -774,6 +774,17 @@ static int gemm_any(const void* A, int a_bf16, const void* trellis, void* C, con
 {
     AMP_REQUIRE(m >= 0, "exl3_gemm: negative m");
     if (m == 0) return 0;
+    if (K > 256)
+    {
+        // half-integer bitrate KA + 0.5 (K = AMP_EXL3_HALF_RATE(KA)), mul1 codebook: the input is rotated into
+        // A_had by the Hadamard kernel, then the half-rate decode kernel runs (up to 16 rows; the
+        // many-rows operator reconstructs the weight once instead, see exl3_gemm_recon)
+        AMP_REQUIRE(K <= 256 + 3 && cb == 2, "exl3_gemm: half-integer bitrates are 1.5 / 2.5 / 3.5 with the mul1 codebook");
+        AMP_REQUIRE(m <= 16 && !a_bf16, "exl3_gemm: half-integer bitrates take up to 16 fp16 rows here");
+        AMP_REQUIRE(A && suh && A_had && k > 0 && k % 128 == 0, "exl3_gemm: half-integer bitrates need the A_had scratch (same shape as A)");
+        if (int rc = amp_had_r_128(A, A_had, suh, nullptr, m, k, 0, 1.0f, stream)) return rc;
+        return launch_gemv_half(A_had, trellis, svh, C, m, k, n, K - 256, c_fp32, stream);
+    }
     if (m <= 16 && !a_bf16)
     {
         GemvLaunch L = direct(A, trellis, C, suh, svh, m, k, n, K, cb, c_fp32, 0, 0);

@@ -17,7 +17,8 @@ namespace amp {
 // HBM-bound: K/8 bytes in, 2 bytes out per weight.
 // ------------------------------------------------------------------------------------------
 
-template <int K, int CB>
+// HALF: K is the integer part KA of a half-integer rate KA + 0.5 (a tile is 4 * (2 KA + 1) words)
+template <int K, int CB, bool HALF = false>
 __global__ __launch_bounds__(256)
 void reconstruct_kernel(__half* __restrict__ out, const uint16_t* __restrict__ trellis,
                         int tiles_n, int tile_n_offset, int n_out, const long long* __restrict__ t_trellis, size_t mat_elems)
@@ -29,15 +30,15 @@ void reconstruct_kernel(__half* __restrict__ out, const uint16_t* __restrict__ t
         trellis = reinterpret_cast<const uint16_t*>(t_trellis[blockIdx.z]);
         out += (size_t) blockIdx.z * mat_elems;
     }
-    constexpr int TW = 8 * K;                 // uint32 words per tile
+    constexpr int TW = HALF ? 4 * (2 * K + 1) : 8 * K;     // uint32 words per tile
     __shared__ __align__(16) uint32_t s_packed[8 * TW];
     __shared__ __align__(16) __half s_tile[16][128 + 8];
 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int kt = blockIdx.y, nb = blockIdx.x;
 
-    const uint16_t* src = trellis + ((size_t) kt * tiles_n + tile_n_offset + nb * 8) * (16 * K);
-    if (t < 2 * TW)                            // 8 tiles * 32K bytes = 2*TW int4
+    const uint16_t* src = trellis + ((size_t) kt * tiles_n + tile_n_offset + nb * 8) * (2 * TW);
+    if (t < 2 * TW)                            // 8 tiles * 4 TW bytes = 2*TW int4
         reinterpret_cast<int4*>(s_packed)[t] = reinterpret_cast<const int4*>(src)[t];
     __syncthreads();
 
@@ -45,7 +46,9 @@ void reconstruct_kernel(__half* __restrict__ out, const uint16_t* __restrict__ t
     #pragma unroll
     for (int j = 0; j < 8; ++j)
     {
-        uint32_t s = window_rt<K>(ring, lane * 8 + j);
+        uint32_t s;
+        if constexpr (HALF) s = window_rt_half<K>(ring, lane * 8 + j);
+        else s = window_rt<K>(ring, lane * 8 + j);
         int row = 2 * (lane & 3) + (j & 1) + 8 * ((j >> 1) & 1);
         int col = (lane >> 2) + 8 * (j >> 2);
         s_tile[row][warp * 16 + col] = decode_state<CB>(s);
@@ -73,7 +76,7 @@ __device__ __forceinline__ __half2 had_tail_h2(__half2 v, int lane)
     return v;
 }
 
-template <int K, int CB>
+template <int K, int CB, bool HALF = false>
 __global__ __launch_bounds__(256)
 void reconstruct_had_kernel(__half* __restrict__ out, const uint16_t* __restrict__ trellis,
                             const __half* __restrict__ suh, const __half* __restrict__ svh,
@@ -87,7 +90,7 @@ void reconstruct_had_kernel(__half* __restrict__ out, const uint16_t* __restrict
         svh = reinterpret_cast<const __half*>(t_svh[blockIdx.z]);
         out += (size_t) blockIdx.z * mat_elems;
     }
-    constexpr int TW = 8 * K;
+    constexpr int TW = HALF ? 4 * (2 * K + 1) : 8 * K;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half* st = reinterpret_cast<__half*>(smem_raw);                       // [128][128] swizzled
     uint32_t* s_packed = reinterpret_cast<uint32_t*>(smem_raw + 128 * 128 * 2);   // [8][8][TW]
@@ -103,7 +106,7 @@ void reconstruct_had_kernel(__half* __restrict__ out, const uint16_t* __restrict
     for (int u = t; u < 8 * 2 * TW; u += 256)
     {
         int j = u / (2 * TW), r = u % (2 * TW);
-        const uint16_t* src = trellis + ((size_t) (kb * 8 + j) * tiles_n + tile_n_offset + nb * 8) * (16 * K);
+        const uint16_t* src = trellis + ((size_t) (kb * 8 + j) * tiles_n + tile_n_offset + nb * 8) * (2 * TW);
         reinterpret_cast<int4*>(s_packed + j * 8 * TW)[r] = reinterpret_cast<const int4*>(src)[r];
     }
     __syncthreads();
@@ -114,7 +117,9 @@ void reconstruct_had_kernel(__half* __restrict__ out, const uint16_t* __restrict
         #pragma unroll
         for (int i = 0; i < 8; ++i)
         {
-            uint32_t s = window_rt<K>(ring, lane * 8 + i);
+            uint32_t s;
+            if constexpr (HALF) s = window_rt_half<K>(ring, lane * 8 + i);
+            else s = window_rt<K>(ring, lane * 8 + i);
             int row = j * 16 + 2 * (lane & 3) + (i & 1) + 8 * ((i >> 1) & 1);
             int col = warp * 16 + (lane >> 2) + 8 * (i >> 2);
             st[at(row, col)] = decode_state<CB>(s);
@@ -184,11 +189,19 @@ typedef void (*recon_had_fn)(__half*, const uint16_t*, const __half*, const __ha
 static const recon_fn k_recon[3][8] = { AMP_ROW(reconstruct_kernel, 0), AMP_ROW(reconstruct_kernel, 1), AMP_ROW(reconstruct_kernel, 2) };
 static const recon_had_fn k_recon_had[3][8] = { AMP_ROW(reconstruct_had_kernel, 0), AMP_ROW(reconstruct_had_kernel, 1), AMP_ROW(reconstruct_had_kernel, 2) };
 #undef AMP_ROW
+// half-integer rates 1.5 / 2.5 / 3.5: mul1 codebook only, as in the reference (Q/reconstruct.cu:116-127)
+static const recon_fn k_recon_half[3] = { reconstruct_kernel<1, 2, true>, reconstruct_kernel<2, 2, true>, reconstruct_kernel<3, 2, true> };
+static const recon_had_fn k_recon_had_half[3] = { reconstruct_had_kernel<1, 2, true>, reconstruct_had_kernel<2, 2, true>,
+                                                  reconstruct_had_kernel<3, 2, true> };
+
+// K as the C ABI passes it: 1..8, or AMP_EXL3_HALF_RATE(KA) = 256 + KA for KA + 0.5 bits per weight
+static inline bool k_is_half(int K) { return K > 256 && K <= 256 + 3; }
 
 static int check_common(const void* out, const void* trellis, int k, int n, int K, int cb, int n_offset, int n_out)
 {
     AMP_REQUIRE(out && trellis, "reconstruct: null pointer");
-    AMP_REQUIRE(K >= 1 && K <= 8, "reconstruct: unsupported EXL3 bitrate %d (integer 1..8)", K);
+    AMP_REQUIRE((K >= 1 && K <= 8) || k_is_half(K), "reconstruct: unsupported EXL3 bitrate %d (integer 1..8, or 1.5 / 2.5 / 3.5)", K);
+    AMP_REQUIRE(!k_is_half(K) || cb == 2, "reconstruct: half-integer bitrates require the mul1 codebook");
     AMP_REQUIRE(cb >= 0 && cb <= 2, "reconstruct: codebook index %d out of range", cb);
     AMP_REQUIRE(k >= 0 && n >= 0 && k % 16 == 0 && n % 16 == 0, "reconstruct: k and n must be multiples of 16");
     AMP_REQUIRE(n_out % 128 == 0, "unpacked N dimension must be divisible by 128");
@@ -209,8 +222,8 @@ AMP_API int amp_exl3_reconstruct(void* unpacked, const void* trellis, int k, int
     if (int rc = check_common(unpacked, trellis, k, n, K, cb, n_offset, n_out)) return rc;
     AMP_REQUIRE(k / 16 <= 65535, "reconstruct: k too large");
     dim3 grid(n_out / 128, k / 16);
-    k_recon[cb][K - 1]<<<grid, 256, 0, stream>>>((__half*) unpacked, (const uint16_t*) trellis,
-                                                 n / 16, n_offset / 16, n_out, nullptr, 0);
+    const recon_fn fn = k_is_half(K) ? k_recon_half[K - 257] : k_recon[cb][K - 1];
+    fn<<<grid, 256, 0, stream>>>((__half*) unpacked, (const uint16_t*) trellis, n / 16, n_offset / 16, n_out, nullptr, 0);
     return cuda_rc(cudaGetLastError(), "amp_exl3_reconstruct");
 }
 
@@ -223,6 +236,7 @@ AMP_API int amp_exl3_reconstruct_batch(void* unpacked, const void* packed_ptrs, 
     if (batch == 0 || k == 0 || n == 0) return 0;
     AMP_REQUIRE(packed_ptrs, "reconstruct_batch: null pointer table");
     if (int rc = check_common(unpacked, unpacked, k, n, K, cb, 0, n)) return rc;
+    AMP_REQUIRE(!k_is_half(K), "reconstruct_batch: integer bitrates only");
     AMP_REQUIRE(k / 16 <= 65535, "reconstruct: k too large");
     dim3 grid(n / 128, k / 16, batch);
     k_recon[cb][K - 1]<<<grid, 256, 0, stream>>>((__half*) unpacked, nullptr, n / 16, 0, n,
@@ -240,8 +254,9 @@ AMP_API int amp_exl3_reconstruct_had(void* unpacked, const void* trellis, const 
     AMP_REQUIRE(k % 128 == 0, "reconstruct_had: K dimension must be divisible by 128");
     AMP_REQUIRE(((uintptr_t) svh & 7) == 0, "reconstruct_had: svh must be 8-byte aligned");
     AMP_REQUIRE(k / 128 <= 65535, "reconstruct_had: k too large");
-    const int smem = 128 * 128 * 2 + 64 * 8 * K * 4;
-    recon_had_fn fn = k_recon_had[cb][K - 1];
+    const bool half = k_is_half(K);
+    const int smem = 128 * 128 * 2 + 64 * (half ? 4 * (2 * (K - 256) + 1) : 8 * K) * 4;
+    recon_had_fn fn = half ? k_recon_had_half[K - 257] : k_recon_had[cb][K - 1];
     int dev = 0;
     if (cudaError_t e = cudaGetDevice(&dev)) return cuda_rc(e, "cudaGetDevice");
     if (cudaError_t e = ensure_smem(fn, smem, dev)) return cuda_rc(e, "reconstruct_had smem");
@@ -260,6 +275,7 @@ AMP_API int amp_exl3_reconstruct_had_batch(void* unpacked, const void* packed_pt
     if (batch == 0 || k == 0 || n == 0) return 0;
     AMP_REQUIRE(packed_ptrs && suh_ptrs && svh_ptrs, "reconstruct_had_batch: null pointer table");
     if (int rc = check_common(unpacked, unpacked, k, n, K, cb, 0, n)) return rc;
+    AMP_REQUIRE(!k_is_half(K), "reconstruct_had_batch: integer bitrates only");
     AMP_REQUIRE(k % 128 == 0, "reconstruct_had_batch: K dimension must be divisible by 128");
     AMP_REQUIRE(k / 128 <= 65535, "reconstruct_had: k too large");
     const int smem = 128 * 128 * 2 + 64 * 8 * K * 4;

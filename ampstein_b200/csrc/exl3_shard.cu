@@ -55,7 +55,7 @@ AMP_API int amp_exl3_shard_cols(const void* trellis, const void* svh, void* out_
 {
     AMP_REQUIRE(trellis && out_trellis && ranges, "exl3_shard_cols: null pointer");
     AMP_REQUIRE((svh == nullptr) == (out_svh == nullptr), "exl3_shard_cols: give svh and its destination, or neither");
-    AMP_REQUIRE(k > 0 && n > 0 && k % 16 == 0 && n % 16 == 0 && K >= 1 && K <= 8, "exl3_shard_cols: shape");
+    AMP_REQUIRE(k > 0 && n > 0 && k % 16 == 0 && n % 16 == 0 && ((K >= 1 && K <= 8) || (K > 256 && K <= 259)), "exl3_shard_cols: shape");
     AMP_REQUIRE(nranges >= 1 && nranges <= SHARD_MAX_RANGES, "exl3_shard_cols: 1..16 ranges");
     AMP_REQUIRE(((uintptr_t) trellis & 15) == 0 && ((uintptr_t) out_trellis & 15) == 0 && ((uintptr_t) svh & 15) == 0 &&
                 ((uintptr_t) out_svh & 15) == 0, "exl3_shard_cols: misaligned pointer");
@@ -71,7 +71,8 @@ AMP_API int amp_exl3_shard_cols(const void* trellis, const void* svh, void* out_
     }
     P.trellis = (const unsigned char*) trellis; P.out = (unsigned char*) out_trellis;
     P.svh = (const unsigned char*) svh; P.out_svh = (unsigned char*) out_svh;
-    P.tile_bytes = 32 * K; P.nranges = nranges; P.tile_rows = k / 16;
+    P.tile_bytes = K > 256 ? 16 * (2 * (K - 256) + 1) : 32 * K;        // half-integer rates: 4 * (2 KA + 1) words per tile
+    P.nranges = nranges; P.tile_rows = k / 16;
     P.tile_row_bytes_in = (long) (n / 16) * P.tile_bytes; P.tile_row_bytes_out = (long) (total / 16) * P.tile_bytes;
     const int bx = P.tile_rows < 2048 ? P.tile_rows : 2048;
     shard_cols_kernel<<<dim3((unsigned) bx, (unsigned) nranges), 256, 0, stream>>>(P);
@@ -82,10 +83,10 @@ AMP_API int amp_exl3_shard_rows(const void* trellis, const void* suh, void* out_
                                 int k0, int klen, cudaStream_t stream)
 {
     AMP_REQUIRE(trellis && suh && out_trellis && out_suh, "exl3_shard_rows: null pointer");
-    AMP_REQUIRE(k > 0 && n > 0 && k % 16 == 0 && n % 16 == 0 && K >= 1 && K <= 8, "exl3_shard_rows: shape");
+    AMP_REQUIRE(k > 0 && n > 0 && k % 16 == 0 && n % 16 == 0 && ((K >= 1 && K <= 8) || (K > 256 && K <= 259)), "exl3_shard_rows: shape");
     AMP_REQUIRE(k0 >= 0 && klen > 0 && k0 % 128 == 0 && klen % 128 == 0 && (long) k0 + klen <= k,
                 "exl3_shard_rows: range [%d, %d] not 128-aligned/in bounds", k0, klen);
-    const size_t row_bytes = (size_t) (n / 16) * 32 * K;
+    const size_t row_bytes = (size_t) (n / 16) * (K > 256 ? 16 * (2 * (K - 256) + 1) : 32 * K);
     if (cudaError_t e = cudaMemcpyAsync(out_trellis, (const unsigned char*) trellis + (size_t) (k0 / 16) * row_bytes,
                                         (size_t) (klen / 16) * row_bytes, cudaMemcpyDefault, stream))
         return cuda_rc(e, "exl3_shard_rows trellis copy");

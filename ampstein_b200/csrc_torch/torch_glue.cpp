@@ -56,6 +56,26 @@ int bits_of(float K, const char* who)
     return (int) K;
 }
 
+// the same for the entries that also take the half-integer rates 1.5 / 2.5 / 3.5 (third dimension
+// 16 KA + 8, mul1 only): the C ABI's code AMP_EXL3_HALF_RATE(KA) comes back for those
+int bits_or_half(const at::Tensor& trellis, bool mul1, const char* who)
+{
+    TORCH_CHECK(trellis.dim() == 3, who, ": trellis must be int16 (k/16, n/16, 16K)");
+    const int64_t w = trellis.size(2);
+    if (w % 16 != 8) return bits_of(trellis, who);
+    TORCH_CHECK(trellis.scalar_type() == at::kShort && trellis.is_contiguous(), who, ": trellis must be contiguous int16");
+    TORCH_CHECK(w / 16 >= 1 && w / 16 <= 3, who, ": unsupported EXL3 bitrate");
+    TORCH_CHECK(mul1, who, ": half-integer bitrates require the mul1 codebook");
+    return AMP_EXL3_HALF_RATE((int) (w / 16));
+}
+
+int bits_or_half(float K, const char* who)
+{
+    const int b = (int) K;
+    if (K - (float) b == 0.5f && b >= 1 && b <= 3) return AMP_EXL3_HALF_RATE(b);
+    return bits_of(K, who);
+}
+
 const void* opt_ptr(const c10::optional<at::Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
 
 cudaStream_t stream_of(const at::Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
@@ -101,7 +121,7 @@ int exl3_gemm(const at::Tensor& A, const at::Tensor& B, at::Tensor& C, const c10
     (void) force_shape_idx; (void) force_num_sms;
     const c10::cuda::CUDAGuard guard(A.device());
     same_device(A, B, "exl3_gemm"); same_device(A, C, "exl3_gemm");
-    const int K = bits_of(B, "exl3_gemm");
+    const int K = bits_or_half(B, mul1, "exl3_gemm");
     TORCH_CHECK(A.dim() == 2 && C.dim() == 2 && A.is_contiguous() && C.is_contiguous(), "exl3_gemm: A and C must be contiguous 2-D");
     TORCH_CHECK(A.scalar_type() == at::kHalf || A.scalar_type() == at::kBFloat16, "exl3_gemm: A must be float16 (or bfloat16)");
     TORCH_CHECK(C.scalar_type() == at::kHalf || C.scalar_type() == at::kFloat, "exl3_gemm: C must be float16 or float32");
@@ -115,6 +135,17 @@ int exl3_gemm(const at::Tensor& A, const at::Tensor& B, at::Tensor& C, const c10
                     "exl3_gemm: A_had must be contiguous float16 of A's size");
     if (m == 0 || n == 0) return 0;
     const bool bf16 = A.scalar_type() == at::kBFloat16;
+    if (K > 256 && (m > 16 || bf16 || !(A_had.has_value() && A_had->defined())))
+    {
+        // half-integer bitrate beyond the decode kernel's reach (more than 16 rows, or no scratch
+        // for the rotated input): the weight is decoded once into the original basis and
+        // multiplied by a library GEMM, as the reference's torch_exl3_gemm_recon does
+        at::Tensor w = at::empty({k, n}, A.options().dtype(at::kHalf));
+        check_rc(amp_exl3_reconstruct_had(w.data_ptr(), B.data_ptr(), suh->data_ptr(), svh->data_ptr(), (int) k, (int) n, K, 2, 0, (int) n,
+                                          stream_of(A)), "exl3_gemm");
+        C.copy_(at::mm(A.to(at::kHalf), w));
+        return 100;
+    }
     auto fn = bf16 ? amp_exl3_gemm_bf16 : amp_exl3_gemm;
     check_rc(fn(A.data_ptr(), B.data_ptr(), C.data_ptr(), suh->data_ptr(), const_cast<void*>(opt_ptr(A_had)), svh->data_ptr(),
                 (int) m, (int) k, (int) n, K, codebook(mcg, mul1), C.scalar_type() == at::kFloat ? 1 : 0, stream_of(A)),
@@ -181,8 +212,8 @@ void reconstruct(at::Tensor unpacked, at::Tensor packed, float K_, bool mcg, boo
 {
     const c10::cuda::CUDAGuard guard(unpacked.device());
     same_device(unpacked, packed, "reconstruct");
-    const int K = bits_of(packed, "reconstruct");
-    TORCH_CHECK(bits_of(K_, "reconstruct") == K, "reconstruct: K does not match the trellis");
+    const int K = bits_or_half(packed, mul1, "reconstruct");
+    TORCH_CHECK(bits_or_half(K_, "reconstruct") == K, "reconstruct: K does not match the trellis");
     TORCH_CHECK(unpacked.scalar_type() == at::kHalf && unpacked.dim() == 2 && unpacked.is_contiguous(), "reconstruct: unpacked must be contiguous float16 (k, n)");
     const int64_t k = packed.size(0) * 16, n = packed.size(1) * 16;
     TORCH_CHECK(unpacked.size(0) == k && unpacked.size(1) == n, "reconstruct: shape mismatch");
@@ -196,8 +227,8 @@ void reconstruct_had_slice(at::Tensor unpacked, at::Tensor packed, at::Tensor su
 {
     const c10::cuda::CUDAGuard guard(unpacked.device());
     same_device(unpacked, packed, "reconstruct_had_slice");
-    const int K = bits_of(packed, "reconstruct_had_slice");
-    TORCH_CHECK(bits_of(K_, "reconstruct_had_slice") == K, "reconstruct_had_slice: K does not match the trellis");
+    const int K = bits_or_half(packed, mul1, "reconstruct_had_slice");
+    TORCH_CHECK(bits_or_half(K_, "reconstruct_had_slice") == K, "reconstruct_had_slice: K does not match the trellis");
     TORCH_CHECK(unpacked.scalar_type() == at::kHalf && unpacked.dim() == 2 && unpacked.is_contiguous(), "reconstruct_had_slice: unpacked must be contiguous float16");
     TORCH_CHECK(suh.scalar_type() == at::kHalf && svh.scalar_type() == at::kHalf, "reconstruct_had_slice: suh, svh must be float16");
     const int64_t k = packed.size(0) * 16, n = packed.size(1) * 16, n_out = unpacked.size(1);

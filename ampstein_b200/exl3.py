@@ -30,30 +30,43 @@ def _cb(mul1, mcg):
     return 2 if mul1 else (1 if mcg else 0)
 
 
-def _trellis_dims(name, trellis):
+def _trellis_dims(name, trellis, half_ok=False):
+    """(k, n, K) of a trellis tensor (k/16, n/16, 16 K). With half_ok the half-integer rates 1.5 / 2.5 /
+    3.5 (third dimension 16 KA + 8) are accepted and K comes back as a float."""
     if trellis.dim() != 3:
         raise ValueError("%s: trellis must be 3-D" % name)
     if trellis.dtype not in (torch.int16, torch.uint16):
         raise TypeError("%s: trellis must be int16" % name)
     w = trellis.shape[2]
+    if half_ok and w % 16 == 8 and 1 <= w // 16 <= 3:
+        return trellis.shape[0] * 16, trellis.shape[1] * 16, w / 16.0
     if w % 16 != 0 or not (1 <= w // 16 <= 8):
-        raise ValueError("%s: unsupported EXL3 bitrate %s (integer 1..8)" % (name, w / 16))
+        raise ValueError("%s: unsupported EXL3 bitrate %s (integer 1..8%s)" % (name, w / 16, ", or 1.5 / 2.5 / 3.5" if half_ok else ""))
     return trellis.shape[0] * 16, trellis.shape[1] * 16, w // 16
+
+
+def _kcode(name, K, mul1):
+    """K as the C ABI takes it: the integer, or AMP_EXL3_HALF_RATE(KA) = 256 + KA for KA + 0.5."""
+    if float(K) == int(K):
+        return int(K)
+    if not mul1:
+        raise ValueError("%s: half-integer bitrates require the mul1 codebook" % name)
+    return 256 + int(K)
 
 
 def exl3_reconstruct(unpacked, packed, K, mul1=False, mcg=False):
     """Dequantize an EXL3 trellis tensor into `unpacked` (fp16 (k, n), in place); returns it.
     K is the bitrate (packed.shape[-1] / 16)."""
     _check_cuda("exl3_reconstruct", unpacked, packed)
-    k, n, Kt = _trellis_dims("exl3_reconstruct", packed)
+    k, n, Kt = _trellis_dims("exl3_reconstruct", packed, half_ok=True)
     if float(K) != float(Kt):
-        raise ValueError("exl3_reconstruct: K=%s does not match the trellis (%d)" % (K, Kt))
+        raise ValueError("exl3_reconstruct: K=%s does not match the trellis (%s)" % (K, Kt))
     if unpacked.dtype != torch.float16 or unpacked.dim() != 2:
         raise TypeError("exl3_reconstruct: unpacked must be 2-D float16")
     if unpacked.shape[0] != k or unpacked.shape[1] != n:
         raise ValueError("exl3_reconstruct: unpacked must be (%d, %d)" % (k, n))
     with torch.cuda.device(packed.device):
-        _lib.call("amp_exl3_reconstruct", unpacked.data_ptr(), packed.data_ptr(), k, n, Kt,
+        _lib.call("amp_exl3_reconstruct", unpacked.data_ptr(), packed.data_ptr(), k, n, _kcode("exl3_reconstruct", Kt, mul1),
                   _cb(mul1, mcg), 0, n, _stream(packed))
     return unpacked
 
@@ -63,7 +76,7 @@ def exl3_reconstruct_had(unpacked, packed, suh, svh, K, mul1=False, mcg=False, n
     [n_offset, n_offset + unpacked.shape[1]); svh is the slice's own vector (reference:
     reconstruct_had_slice, vendor/exl3/exllamav3_ext/quant/reconstruct.cu:431-503)."""
     _check_cuda("exl3_reconstruct_had", unpacked, packed, suh, svh)
-    k, n, Kt = _trellis_dims("exl3_reconstruct_had", packed)
+    k, n, Kt = _trellis_dims("exl3_reconstruct_had", packed, half_ok=True)
     if float(K) != float(Kt):
         raise ValueError("exl3_reconstruct_had: K does not match the trellis")
     if unpacked.dtype != torch.float16 or suh.dtype != torch.float16 or svh.dtype != torch.float16:
@@ -74,7 +87,7 @@ def exl3_reconstruct_had(unpacked, packed, suh, svh, K, mul1=False, mcg=False, n
         raise ValueError("reconstruct_had: suh / svh size")
     with torch.cuda.device(packed.device):
         _lib.call("amp_exl3_reconstruct_had", unpacked.data_ptr(), packed.data_ptr(), suh.data_ptr(),
-                  svh.data_ptr(), k, n, Kt, _cb(mul1, mcg), int(n_offset), unpacked.shape[1],
+                  svh.data_ptr(), k, n, _kcode("exl3_reconstruct_had", Kt, mul1), _cb(mul1, mcg), int(n_offset), unpacked.shape[1],
                   _stream(packed))
     return unpacked
 
@@ -142,7 +155,7 @@ def exl3_gemm(A, B, C, suh, svh, mul1=False, mcg=False):
     if suh is None or svh is None:
         raise TypeError("expected (A, B, C, suh, svh, mul1?, mcg?)")
     _check_cuda("exl3_gemm", A, B, C, suh, svh)
-    k, n, K = _trellis_dims("exl3_gemm", B)
+    k, n, K = _trellis_dims("exl3_gemm", B, half_ok=True)
     if A.dtype not in (torch.float16, torch.bfloat16) or suh.dtype != torch.float16 or svh.dtype != torch.float16:
         raise TypeError("exl3_gemm: A must be float16 (or bfloat16), suh and svh float16")
     if C.dtype not in (torch.float16, torch.float32):
@@ -156,10 +169,22 @@ def exl3_gemm(A, B, C, suh, svh, mul1=False, mcg=False):
     if m == 0:
         return C
     bf16 = A.dtype == torch.bfloat16
+    half_rate = float(K) != int(K)
+    if half_rate and (m > 16 or bf16):
+        # half-integer bitrates, many rows: the weight is decoded once into the original basis
+        # (reconstruct_had) and multiplied by a library GEMM, the reference's form of this case
+        # (torch_exl3_gemm_recon, src/torch/amp_torch.cpp:11128-11230)
+        w = torch.empty((k, n), dtype=torch.float16, device=A.device)
+        exl3_reconstruct_had(w, B, suh, svh, K, mul1, mcg)
+        y = torch.mm(A.reshape(m, k).to(torch.float16), w)
+        C.copy_(y.reshape(C.shape))
+        return C
+    K = _kcode("exl3_gemm", K, mul1)
     # the binding allocates the input-rotation scratch per call, as the reference's does
     # (src/torch/amp_torch.cpp:11282); the decode kernel (<= 16 rows) does not need it
-    # (from five rows on it lets the input be rotated once instead of by every CTA)
-    A_had = torch.empty(A.shape, dtype=torch.float16, device=A.device) if (m >= 5 or bf16) else None
+    # (from five rows on it lets the input be rotated once instead of by every CTA; the half-rate
+    # kernel always takes its input rotated)
+    A_had = torch.empty(A.shape, dtype=torch.float16, device=A.device) if (m >= 5 or bf16 or half_rate) else None
     with torch.cuda.device(A.device):
         _lib.call("amp_exl3_gemm_bf16" if bf16 else "amp_exl3_gemm", A.data_ptr(), B.data_ptr(), C.data_ptr(),
                   suh.data_ptr(), A_had.data_ptr() if A_had is not None else None, svh.data_ptr(), m, k, n, K,
@@ -392,14 +417,14 @@ def exl3_gemm_recon(x, trellis, suh, svh, K, mul1=False, mcg=False, out=None, sc
     out / scratch: optional preallocated result and (k, n) fp16 buffer for the decoded weight (the
     reference allocates both per call from the caching allocator; so does this function without them)."""
     _check_cuda("exl3_gemm_recon", x, trellis, suh, svh)
-    k, n, Kt = _trellis_dims("exl3_gemm_recon", trellis)
+    k, n, Kt = _trellis_dims("exl3_gemm_recon", trellis, half_ok=True)
     if x.dim() != 2 or x.shape[1] != k or suh.numel() != k or svh.numel() != n or n > 32768:
         raise ValueError("exl3_gemm_recon: incompatible shapes (x %s, weight %d x %d)"
                          % (tuple(x.shape), k, n))
     if float(K) != float(Kt):
         raise ValueError("exl3_gemm_recon: K does not match the trellis")
     y = out if out is not None else torch.empty((x.shape[0], n), dtype=torch.float16, device=x.device)
-    if n <= RECON_MM_MAX_N and x.dtype == torch.float16 and x.shape[0] > 16:
+    if (n <= RECON_MM_MAX_N or float(Kt) != int(Kt)) and x.dtype == torch.float16 and x.shape[0] > 16:
         w = scratch if scratch is not None else torch.empty((k, n), dtype=torch.float16, device=x.device)
         exl3_reconstruct_had(w, trellis, suh, svh, K, mul1, mcg)
         return torch.mm(x, w, out=y)
@@ -657,7 +682,8 @@ def exl3_shard_cols(trellis, svh, ranges):
     multiples of 128) concatenated. Returns (trellis (k/16, total/16, 16K), svh (total))."""
     import ctypes
     _check_cuda("exl3_shard_cols", trellis, svh)
-    k, n, K = _trellis_dims("exl3_shard_cols", trellis)
+    k, n, K = _trellis_dims("exl3_shard_cols", trellis, half_ok=True)
+    K = _kcode("exl3_shard_cols", K, True)
     if svh.dtype != torch.float16 or svh.numel() != n:
         raise ValueError("exl3_shard_cols: svh must be fp16 with one value per output column")
     ranges = [(int(a), int(b)) for a, b in ranges]
@@ -667,7 +693,7 @@ def exl3_shard_cols(trellis, svh, ranges):
     if not 1 <= len(ranges) <= 16:
         raise ValueError("exl3_shard_cols: 1..16 ranges")
     total = sum(ln for _, ln in ranges)
-    out = torch.empty((k // 16, total // 16, 16 * K), dtype=trellis.dtype, device=trellis.device)
+    out = torch.empty((k // 16, total // 16, trellis.shape[2]), dtype=trellis.dtype, device=trellis.device)
     out_svh = torch.empty(total, dtype=torch.float16, device=trellis.device)
     flat = (ctypes.c_int * (2 * len(ranges)))(*[v for r in ranges for v in r])
     with torch.cuda.device(trellis.device):
@@ -680,13 +706,14 @@ def exl3_shard_rows(trellis, suh, k0, klen):
     """Row shard (reference: rows, src/ucode/ampstein/models.uc:547-562): input rows [k0, k0 + klen),
     multiples of 128, of the trellis and of suh, as copies of their own."""
     _check_cuda("exl3_shard_rows", trellis, suh)
-    k, n, K = _trellis_dims("exl3_shard_rows", trellis)
+    k, n, K = _trellis_dims("exl3_shard_rows", trellis, half_ok=True)
+    K = _kcode("exl3_shard_rows", K, True)
     if suh.dtype != torch.float16 or suh.numel() != k:
         raise ValueError("exl3_shard_rows: suh must be fp16 with one value per input row")
     k0, klen = int(k0), int(klen)
     if k0 % 128 or klen % 128 or k0 < 0 or klen <= 0 or k0 + klen > k:
         raise ValueError("models.rows: range [%d, %d] not 128-aligned/in bounds" % (k0, klen))
-    out = torch.empty((klen // 16, n // 16, 16 * K), dtype=trellis.dtype, device=trellis.device)
+    out = torch.empty((klen // 16, n // 16, trellis.shape[2]), dtype=trellis.dtype, device=trellis.device)
     out_suh = torch.empty(klen, dtype=torch.float16, device=trellis.device)
     with torch.cuda.device(trellis.device):
         _lib.call("amp_exl3_shard_rows", trellis.data_ptr(), suh.data_ptr(), out.data_ptr(), out_suh.data_ptr(), k, n, K,

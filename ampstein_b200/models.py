@@ -19,10 +19,13 @@ class LinearEXL3:
     def __init__(self, trellis, suh, svh, bias=None, mul1=False, mcg=False):
         if mul1 and mcg:
             raise ValueError("LinearEXL3: both mul1 and mcg set")
-        if trellis.dim() != 3 or trellis.shape[2] % 16:
-            raise ValueError("LinearEXL3: half-integer bitrates are not supported")
+        if trellis.dim() != 3 or trellis.shape[2] % 8:
+            raise ValueError("LinearEXL3: trellis must be (k/16, n/16, 16 K)")
+        if trellis.shape[2] % 16 and not (mul1 and 1 <= trellis.shape[2] // 16 <= 3):
+            # (reference: models.uc:9-15, 68-71: K = shape[2] / 16 as a float; bits_k.cuh:14-20)
+            raise ValueError("LinearEXL3: half-integer bitrates are 1.5 / 2.5 / 3.5 with the mul1 codebook")
         self.trellis, self.suh, self.svh, self.bias = trellis, suh, svh, bias
-        self.K = trellis.shape[2] // 16
+        self.K = trellis.shape[2] // 16 if trellis.shape[2] % 16 == 0 else trellis.shape[2] / 16.0     # 1.5 / 2.5 / 3.5: 16 K + 8 words
         self.mul1, self.mcg = mul1, mcg
         self.in_features = trellis.shape[0] * 16
         self.out_features = trellis.shape[1] * 16

@@ -37,6 +37,16 @@ int amp_b200_version(void);
 const char* amp_b200_last_error(void);
 
 /*
+ * Bitrate argument K of the entry points below: 1..8 bits per weight, or, where an entry says so,
+ * AMP_EXL3_HALF_RATE(KA) for the half-integer rates KA + 0.5 = 1.5 / 2.5 / 3.5 (mul1 codebook only;
+ * the trellis tensor's third dimension is then 16 KA + 8). The reference passes these rates as a
+ * float K (Q/bits_k.cuh:14-29). Entries that accept them: amp_exl3_reconstruct,
+ * amp_exl3_reconstruct_had, amp_exl3_gemm (up to 16 rows, A_had required), amp_exl3_shard_cols /
+ * amp_exl3_shard_rows. The fused / bundle / grouped entries and the int8 form take integer rates only.
+ */
+#define AMP_EXL3_HALF_RATE(KA) (256 + (KA))
+
+/*
  * Dequantize a trellis into fp16 W_hat (rotated basis). Bit-exact with the reference.
  * Replaces: reconstruct / reconstruct_slice, Q/reconstruct.cu:141-197, 512-523
  *           (binding torch.exl3_reconstruct, src/torch/amp_torch.cpp:11015-11060).

@@ -61,9 +61,15 @@ def _h(a):
 
 
 def trellis_dims(trellis):
+    """(k, n, K) of a trellis tensor (k/16, n/16, 16 K); K is 1.5 / 2.5 / 3.5 for the half-integer
+    rates, whose third dimension is 16 KA + 8."""
     tk, tn, w = trellis.shape
-    assert w % 16 == 0
-    return tk * 16, tn * 16, w // 16
+    assert w % 8 == 0
+    return tk * 16, tn * 16, (w // 16 if w % 16 == 0 else w / 16.0)
+
+
+def _is_half(K):
+    return float(K) != int(K)
 
 
 def decode_table(cb):
@@ -100,7 +106,10 @@ def reconstruct(trellis, cb=0):
     t = _h(trellis)
     k, n, K = trellis_dims(t)
     out = np.empty((k, n), np.uint16)
-    rc = lib().exl3o_reconstruct(_p16(t), k, n, K, cb, _p16(out))
+    if _is_half(K):
+        rc = lib().exl3o_reconstruct_half(_p16(t), k, n, int(K), cb, _p16(out))
+    else:
+        rc = lib().exl3o_reconstruct(_p16(t), k, n, K, cb, _p16(out))
     assert rc == 0, rc
     return out.view(np.float16)
 
@@ -109,7 +118,11 @@ def reconstruct_had(trellis, suh, svh, cb=0):
     t = _h(trellis)
     k, n, K = trellis_dims(t)
     out = np.empty((k, n), np.uint16)
-    rc = lib().exl3o_reconstruct_had(_p16(t), _p16(_h(suh)), _p16(_h(svh)), k, n, K, cb, _p16(out))
+    if _is_half(K):
+        what = np.ascontiguousarray(_h(reconstruct(t, cb)))
+        rc = lib().exl3o_reconstruct_had_w(_p16(what), _p16(_h(suh)), _p16(_h(svh)), k, n, _p16(out))
+    else:
+        rc = lib().exl3o_reconstruct_had(_p16(t), _p16(_h(suh)), _p16(_h(svh)), k, n, K, cb, _p16(out))
     assert rc == 0, rc
     return out.view(np.float16)
 
@@ -152,6 +165,8 @@ def linear(x, trellis, suh, svh, cb=0, fp32_out=False, what=None):
     assert kk == k
     o16 = np.empty((m, n), np.uint16)
     o32 = np.empty((m, n), np.float32)
+    if what is None and _is_half(K):
+        what = reconstruct(t, cb)
     if what is None:
         rc = lib().exl3o_linear(_p16(xx), _p16(t), _p16(_h(suh)), _p16(_h(svh)), m, k, n, K, cb,
                                 _p16(o16), _p32(o32))

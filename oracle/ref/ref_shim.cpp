@@ -47,6 +47,27 @@ extern "C" int ref_reconstruct_had(void* unpacked, void* trellis, void* suh, voi
     )
 }
 
+// half-integer bitrates KA + 0.5 (mul1 codebook only): the trellis' third dimension is 16 KA + 8
+extern "C" int ref_reconstruct_half(void* unpacked, void* trellis, int k, int n, int KA, int dev)
+{
+    GUARDED(
+        auto u = view(unpacked, {k, n}, at::kHalf, dev);
+        auto p = view(trellis, {k / 16, n / 16, 16 * KA + 8}, at::kShort, dev);
+        reconstruct(u, p, (float) KA + 0.5f, false, true);
+    )
+}
+
+extern "C" int ref_reconstruct_had_half(void* unpacked, void* trellis, void* suh, void* svh, int k, int n, int KA, int dev)
+{
+    GUARDED(
+        auto u = view(unpacked, {k, n}, at::kHalf, dev);
+        auto p = view(trellis, {k / 16, n / 16, 16 * KA + 8}, at::kShort, dev);
+        auto su = view(suh, {k}, at::kHalf, dev);
+        auto sv = view(svh, {n}, at::kHalf, dev);
+        reconstruct_had_slice(u, p, su, sv, (float) KA + 0.5f, false, true, 0);
+    )
+}
+
 // dtype: 0 = fp16 in/out, 1 = fp32 in/out; pre/post may be null
 extern "C" int ref_had_r_128(void* in, void* out, void* pre, void* post, int rows, int cols,
                              int dtype, float scale, int dev)

@@ -17,7 +17,7 @@ def make_linear(k, n, K, seed, m=1):
     """Seeded synthetic EXL3 linear: uniform random trellis words (every bit pattern is a valid
     stream), +-1 sign vectors, N(0,1) activations."""
     rng = np.random.default_rng(seed)
-    trellis = rng.integers(0, 65536, size=(k // 16, n // 16, 16 * K), dtype=np.uint16)
+    trellis = rng.integers(0, 65536, size=(k // 16, n // 16, int(round(16 * K))), dtype=np.uint16)      # K may be 1.5 / 2.5 / 3.5
     suh = rng.choice(np.array([-1.0, 1.0], np.float16), size=k)
     svh = rng.choice(np.array([-1.0, 1.0], np.float16), size=n)
     x = rng.standard_normal((m, k)).astype(np.float16)

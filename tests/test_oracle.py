@@ -281,3 +281,45 @@ def test_int8_activation_linear_against_the_fp_linear(oracle):
         assert 1e-4 < rms < 1e-2, rms
     z = oracle.linear_int8(np.zeros((1, 512), np.float16), trellis, suh, svh, fp32_out=True)
     assert np.all(z == 0)
+
+
+@pytest.mark.parametrize("KA", [1, 2, 3])
+def test_half_integer_bitrates_pack_and_decode(oracle, KA):
+    """Half-integer bitrates KA + 0.5: positions alternate KA and KA + 1 bits (odd positions carry the
+    extra bit, Q/exl3_dq.cuh:254-284). The packer's bits come back as the low bits of the decoded
+    states, and a bit-array restatement in numpy gives the same 256 states and the same weights."""
+    import ctypes
+    L = oracle.lib()
+    rng = np.random.default_rng(40 + KA)
+    bits2 = 2 * KA + 1
+    p16 = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_uint16))
+    codes = rng.integers(0, 65536, 256).astype(np.uint16)
+    tile = np.zeros(8 * bits2, np.uint16)
+    L.exl3o_pack_tile_half(p16(codes), KA, p16(tile))
+    st = np.zeros(256, np.uint16)
+    L.exl3o_tile_states_half(p16(tile), KA, p16(st))
+    for t in range(256):
+        nb = KA + (t & 1)
+        assert (int(st[t]) ^ int(codes[t])) & ((1 << nb) - 1) == 0
+    # numpy: the tile as a bit array (uint32 words, MSB first), windows by slicing
+    tile = rng.integers(0, 65536, 8 * bits2).astype(np.uint16)
+    words = tile[0::2].astype(np.uint32) | (tile[1::2].astype(np.uint32) << 16)
+    bits = ((words[:, None] >> (31 - np.arange(32, dtype=np.uint32))) & 1).reshape(-1)
+    ring = np.concatenate([bits, bits])
+    n = bits.size
+    assert n == 128 * bits2
+    want = np.zeros(256, np.uint16)
+    for t in range(256):
+        end = (t // 2 + 1) * bits2 if t & 1 else (t // 2) * bits2 + KA
+        start = (end - 16) % n
+        w = ring[start:start + 16]
+        want[t] = int("".join(str(int(b)) for b in w), 2)
+    L.exl3o_tile_states_half(p16(tile), KA, p16(st))
+    assert np.array_equal(st, want)
+    # through reconstruct: a (16, 16) weight of one tile
+    table = oracle.decode_table(2)
+    w = oracle.reconstruct(tile.reshape(1, 1, -1), 2)
+    for t in range(256):
+        l, j = t // 8, t % 8
+        row, col = 2 * (l % 4) + (j & 1) + 8 * ((j >> 1) & 1), (l // 4) + 8 * (j >> 2)
+        assert w[row, col].view(np.uint16) == table[want[t]].view(np.uint16)

@@ -153,3 +153,31 @@ def test_glue_sorted_moe_with_the_reference_call_sequence(glue, amp, oracle):
     with pytest.raises(RuntimeError):
         glue.exl3_moe(xd, out3.half(), count, tok, wts, *temps, 0, float(K), float(K), float(K), *tabs,
                       False, False, False, False, False, False, 0.0, -1, None, None, 1, cap, 16, None, None, None)
+
+
+@pytest.mark.gpu
+def test_glue_half_integer_bitrates(glue, oracle):
+    """The reference's float K at the C++ boundary (bits_from_K, vendor/exl3/exllamav3_ext/quant/bits_k.cuh:14-29):
+    2.5 bits per weight through reconstruct, reconstruct_had_slice and exl3_gemm (decode kernel with the
+    A_had scratch, reconstruct + library GEMM above 16 rows or without it)."""
+    K, k, n = 2.5, 256, 256
+    trellis, suh, svh, x = make_linear(k, n, K, seed=7700, m=20)
+    t, su, sv = dev(trellis), dev(suh), dev(svh)
+    w = torch.empty((k, n), dtype=torch.float16, device="cuda")
+    glue.reconstruct(w, t, 2.5, False, True)
+    assert np.array_equal(w.cpu().numpy().view(np.uint16), oracle.reconstruct(trellis, 2).view(np.uint16))
+    glue.reconstruct_had_slice(w, t, su, sv, 2.5, False, True, 0)
+    assert np.array_equal(w.cpu().numpy().view(np.uint16), oracle.reconstruct_had(trellis, suh, svh, 2).view(np.uint16))
+    ref = oracle.linear(x, trellis, suh, svh, 2, fp32_out=True)
+    for rows, scratch in ((1, True), (4, False), (20, True)):
+        xx = dev(x[:rows])
+        y = torch.empty((rows, n), dtype=torch.float16, device="cuda")
+        fam = glue.exl3_gemm(xx, t, y, su, torch.empty_like(xx) if scratch else None, sv, 0, False, True, 0)
+        torch.cuda.synchronize()
+        assert fam == (90 if rows <= 16 and scratch else 100)
+        err = np.max(np.abs(y.float().cpu().numpy() - ref[:rows])) / np.max(np.abs(ref[:rows]))
+        assert err < 1e-2, (rows, err)
+    with pytest.raises(RuntimeError):
+        glue.reconstruct(w, t, 2.5, False, False)                   # mul1 only
+    with pytest.raises(RuntimeError):
+        glue.reconstruct(w, t, 2.0, False, True)                    # K must match the trellis
