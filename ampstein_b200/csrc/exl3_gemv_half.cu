@@ -8,7 +8,8 @@
 // over; here a warp stages one tile (4 * (2 KA + 1) words) at a time in shared memory and every lane
 // cuts its eight windows with run-time shifts. fp32 accumulation over k in tile order, the four
 // lanes that share a column are added by shuffles, then the same Hadamard / svh epilogue as the
-// other kernels. Correct and deterministic; not tuned (one CTA per 128 columns, no k split).
+// other kernels. Correct and deterministic; lightly tuned (words requested four tiles ahead; one CTA
+// per 128 columns, no k split).
 #include "exl3_common.cuh"
 #include "host_common.h"
 
@@ -34,32 +35,48 @@ void exl3_gemv_half_kernel(const __half* __restrict__ xt, const uint16_t* __rest
     #pragma unroll
     for (int b = 0; b < 16; ++b) acc[b][0] = acc[b][1] = 0.0f;
 
-    for (int k0 = 0; k0 < k; k0 += GH_XROWS)
+    // a lane's word of a tile is requested four tiles ahead (the tiles of a column come from HBM
+    // 4 TW bytes at a time, one latency each if asked for only when needed)
+    const int ktiles = k >> 4;
+    const uint32_t* base = reinterpret_cast<const uint32_t*>(trellis) + ((size_t) nb * 8 + warp) * TW;
+    const size_t kstride = (size_t) tiles_n * TW;
+    auto fetch = [&](int kt) { return (lane < TW && kt < ktiles) ? __ldg(base + (size_t) kt * kstride + lane) : 0u; };
+    uint32_t pf[4];
+    #pragma unroll
+    for (int j = 0; j < 4; ++j) pf[j] = fetch(j);
+
+    for (int kt0 = 0; kt0 < ktiles; kt0 += 4)
     {
-        const int rows = min(GH_XROWS, k - k0);
-        __syncthreads();
-        for (int i = t; i < m * (rows >> 3); i += 256)
+        if ((kt0 & (GH_XROWS / 16 - 1)) == 0)
         {
-            const int b = i / (rows >> 3), j = i - b * (rows >> 3);
-            reinterpret_cast<uint4*>(xs + b * GH_XROWS)[j] = reinterpret_cast<const uint4*>(xt + (size_t) b * k + k0)[j];
+            // next chunk of the rotated input rows
+            const int k0 = kt0 << 4, rows = min(GH_XROWS, k - k0);
+            __syncthreads();
+            for (int i = t; i < m * (rows >> 3); i += 256)
+            {
+                const int b = i / (rows >> 3), j = i - b * (rows >> 3);
+                reinterpret_cast<uint4*>(xs + b * GH_XROWS)[j] = reinterpret_cast<const uint4*>(xt + (size_t) b * k + k0)[j];
+            }
+            __syncthreads();
         }
-        __syncthreads();
-        for (int kt = 0; kt < (rows >> 4); ++kt)
+        #pragma unroll
+        for (int j = 0; j < 4; ++j)
         {
-            const uint32_t* src = reinterpret_cast<const uint32_t*>(trellis) +
-                                  ((size_t) ((k0 >> 4) + kt) * tiles_n + (size_t) nb * 8 + warp) * TW;
+            const int kt = kt0 + j;                        // (k is a multiple of 128: the tile count is a multiple of 8)
             __syncwarp();
-            if (lane < TW) s_tile[warp][lane] = __ldg(src + lane);
+            if (lane < TW) s_tile[warp][lane] = pf[j];
+            pf[j] = fetch(kt + 4);
             __syncwarp();
             float w[8];
             #pragma unroll
-            for (int j = 0; j < 8; ++j) w[j] = __half2float(decode_state<2>(window_rt_half<KA>(s_tile[warp], lane * 8 + j)));
-            // position j of the lane: row r0 + (j & 1) + 8 * ((j >> 1) & 1), column ca + 8 * (j >> 2)
+            for (int i = 0; i < 8; ++i) w[i] = __half2float(decode_state<2>(window_rt_half<KA>(s_tile[warp], lane * 8 + i)));
+            // position i of the lane: row r0 + (i & 1) + 8 * ((i >> 1) & 1), column ca + 8 * (i >> 2)
+            const int xoff = (kt & (GH_XROWS / 16 - 1)) * 16 + r0;
             #pragma unroll
             for (int b = 0; b < 16; ++b)
                 if (b < m)
                 {
-                    const __half* xr = xs + b * GH_XROWS + kt * 16 + r0;
+                    const __half* xr = xs + b * GH_XROWS + xoff;
                     const float x0 = __half2float(xr[0]), x1 = __half2float(xr[1]), x8 = __half2float(xr[8]), x9 = __half2float(xr[9]);
                     acc[b][0] = fmaf(w[0], x0, fmaf(w[1], x1, fmaf(w[2], x8, fmaf(w[3], x9, acc[b][0]))));
                     acc[b][1] = fmaf(w[4], x0, fmaf(w[5], x1, fmaf(w[6], x8, fmaf(w[7], x9, acc[b][1]))));

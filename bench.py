@@ -720,9 +720,9 @@ def measure_gemv(steps, warmup, shape, m, tmem=False, mul1=False, silu_mul=False
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev)
     g.manual_seed(5)
-    wbytes = k * n * K // 8
+    wbytes = int(k * n * K) // 8
     copies = max(1, min(64, -(-2 * 126 * 2 ** 20 // wbytes)))
-    mats = [torch.randint(-32768, 32768, (k // 16, n // 16, 16 * K), dtype=torch.int16, device=dev, generator=g) for _ in range(copies)]
+    mats = [torch.randint(-32768, 32768, (k // 16, n // 16, int(16 * K)), dtype=torch.int16, device=dev, generator=g) for _ in range(copies)]
     sgn = lambda c: (torch.randint(0, 2, (c,), device=dev, generator=g).to(torch.float16) * 2 - 1)
     suh, svh = sgn(k), (sgn(n) / (1.2437 * math.sqrt(k))).to(torch.float16)
     x = torch.randn((m, k), device=dev, generator=g).to(torch.float16)
@@ -750,7 +750,7 @@ def measure_gemv(steps, warmup, shape, m, tmem=False, mul1=False, silu_mul=False
     peak = float(peaks.get("hbm_gbs", 6650.0))
     gbs = byt / us / 1e3
     return {
-        "metric": "decode GEMV time (%dx%d, K=%d, m=%d)" % (k, n, K, m), "value": round(us, 2), "unit": "us/launch",
+        "metric": "decode GEMV time (%dx%d, K=%s, m=%d)" % (k, n, K, m), "value": round(us, 2), "unit": "us/launch",
         "n_gpus": 1, "steps": steps, "warmup": max(warmup, 3), "ms_per_step": round(us * copies / 1e3, 4),
         "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "one GEMV shape, %d distinct weight copies per graph (%.0f MB, larger than L2)" % (copies, copies * wbytes / 1e6),
@@ -1095,10 +1095,13 @@ def main():
             print(json.dumps(measure_gemm(args.steps, args.warmup, shape, args.tokens or 2048)), flush=True)
         elif args.workload == "gemv":
             try:
-                shape = tuple(int(v) for v in args.shape.lower().split("x"))
-                assert len(shape) == 3 and shape[0] % 128 == 0 and shape[1] % 128 == 0 and 1 <= shape[2] <= 8
-            except (ValueError, AssertionError):
-                raise SystemExit("bench.py: --shape must be KxNxBITS with k, n multiples of 128 and 1..8 bits")
+                parts = args.shape.lower().split("x")
+                bits = float(parts[2])
+                shape = (int(parts[0]), int(parts[1]), int(bits) if bits == int(bits) else bits)
+                assert len(parts) == 3 and shape[0] % 128 == 0 and shape[1] % 128 == 0 and (bits in (1.5, 2.5, 3.5) or (bits == int(bits) and 1 <= bits <= 8))
+                assert bits == int(bits) or args.mul1
+            except (ValueError, AssertionError, IndexError):
+                raise SystemExit("bench.py: --shape must be KxNxBITS with k, n multiples of 128 and 1..8 bits (1.5 / 2.5 / 3.5 with --mul1)")
             if args.no_int8 or args.int8_residual:
                 from ampstein_b200 import _lib
                 _lib.lib().amp_exl3_set_int8_gemv(1 if args.int8_residual else 0, 0)
