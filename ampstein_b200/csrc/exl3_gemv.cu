@@ -783,7 +783,12 @@ static int gemm_any(const void* A, int a_bf16, const void* trellis, void* C, con
         AMP_REQUIRE(m <= 16 && !a_bf16, "exl3_gemm: half-integer bitrates take up to 16 fp16 rows here");
         AMP_REQUIRE(A && suh && A_had && k > 0 && k % 128 == 0, "exl3_gemm: half-integer bitrates need the A_had scratch (same shape as A)");
         if (int rc = amp_had_r_128(A, A_had, suh, nullptr, m, k, 0, 1.0f, stream)) return rc;
-        return launch_gemv_half(A_had, trellis, svh, C, m, k, n, K - 256, c_fp32, stream);
+        int dev = 0;
+        if (cudaError_t e = cudaGetDevice(&dev)) return cuda_rc(e, "cudaGetDevice");
+        int* counters = nullptr; float* scratch = nullptr;
+        if (int rc = workspace_region(dev, stream, &counters, &scratch)) return rc;
+        return launch_gemv_half(A_had, trellis, svh, C, m, k, n, K - 256, c_fp32, counters, scratch, GEMV_SCRATCH_BYTES,
+                                GEMV_MAX_BLOCKS, dev_info(dev).sms, stream);
     }
     if (m <= 16 && !a_bf16)
     {

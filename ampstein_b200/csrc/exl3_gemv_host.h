@@ -71,7 +71,7 @@ int launch_gemm_tc_grouped(const void* xt, void* c, long Mcap, int k, int n, int
 
 // decode kernel of the half-integer bitrates (exl3_gemv_half.cu); xt = the rotated input, (m, k) fp16
 int launch_gemv_half(const void* xt, const void* trellis, const void* svh, void* c, int m, int k, int n, int KA, int c_fp32,
-                     cudaStream_t stream);
+                     int* counters, float* scratch, size_t scratch_bytes, int max_blocks, int sms, cudaStream_t stream);
 
 extern int g_pdl;
 
