@@ -316,8 +316,8 @@ void exl3_moe_coop(const at::Tensor& x, const at::Tensor& sel, const at::Tensor&
 
 // Token-sorted prefill MoE with the reference's signature (vendor/exl3/exllamav3_ext/quant/exl3_moe.cuh:8-53).
 // The reference's temps (temp_state_*, temp_intermediate_*) are accepted and not used: the kernels
-// here work in one workspace per device that this layer allocates on first use and grows when a
-// larger chunk arrives (no allocation after that). num_active and m_tile only tune the
+// here work in one workspace per device and stream that this layer allocates on first use and grows
+// when a larger chunk arrives (no allocation after that). num_active and m_tile only tune the
 // reference's launch and are ignored; experts with more rows than the reference's temps hold
 // (max_tokens_per_expert = temp_state_g.size(1)) are skipped exactly as the reference skips them,
 // so that a caller who routes those through another tier does not get them twice. Per-expert bit
@@ -396,10 +396,11 @@ void exl3_moe(const at::Tensor& hidden_state, const at::Tensor& output_state, co
     const long need = amp_exl3_moe_sorted_workspace(a.T, a.A, a.E, a.H, a.I);
     TORCH_CHECK(need > 0, "exl3_moe: unsupported sizes");
     {
-        static std::map<int, at::Tensor> ws;
+        // one workspace per (device, stream): calls on different streams may overlap on the GPU
+        static std::map<std::pair<int, const void*>, at::Tensor> ws;
         static std::mutex mu;
         std::lock_guard<std::mutex> lock(mu);
-        at::Tensor& w = ws[hidden_state.get_device()];
+        at::Tensor& w = ws[std::make_pair((int) hidden_state.get_device(), (const void*) stream_of(hidden_state))];
         if (!w.defined() || w.numel() < need)
             w = at::empty({need}, at::TensorOptions().dtype(at::kByte).device(hidden_state.device()));
         a.workspace = w.data_ptr(); a.workspace_bytes = (long) w.numel();

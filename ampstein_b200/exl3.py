@@ -756,7 +756,8 @@ def moe_fused(y, out, count, tok_sorted, w_sorted, cfg, num_active=-1, lo=1, hi=
     num_active and m_tile are accepted and unused (one call covers every row count; the reference's
     three tiered calls still work). With scratch (fp32 [slots, hidden]) and slot_base (int64 per
     expert) the sum is deferred as in the reference: out is left alone, weight * result of every
-    assignment goes to its slot, and moe_gather adds the slots up in pick order."""
+    assignment goes to its slot, and moe_gather adds the slots up in pick order. The workspace lives in
+    cfg: calls that share a cfg object must be ordered on one stream (use one cfg per stream otherwise)."""
     import ctypes
     if not isinstance(cfg, dict):
         raise TypeError("moe_fused: cfg must be an object")
