@@ -51,3 +51,24 @@ def test_algorithmic_bytes_of_the_steps():
     # sharded: the ranks' weight bytes add up to the whole
     tot = sum(bench.algorithmic_bytes(S, 1, r, 8) for r in range(8))
     assert abs(tot - bench.algorithmic_bytes(S, 1)) < 0.01 * tot
+
+
+def _run_bench(*args):
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    return subprocess.run([sys.executable, os.path.join(root, "bench.py")] + list(args), capture_output=True, text=True, env=env, timeout=300)
+
+
+def test_secondary_workloads_refuse_to_run_without_a_gpu_and_check_their_arguments():
+    """No CPU path: every GPU workload stops with a message instead of computing on the host; bad
+    shapes and token counts are rejected before any device work."""
+    for wl in ("moe-prefill", "gemm", "gemv", "moe", "prefill"):
+        r = _run_bench("--workload", wl)
+        assert r.returncode != 0 and "no CUDA device" in (r.stderr + r.stdout), (wl, r.stderr[-300:])
+    r = _run_bench("--workload", "moe", "--tokens", "3")
+    assert r.returncode != 0 and "--tokens 1, 4 or 16" in r.stderr
+    r = _run_bench("--workload", "bogus")
+    assert r.returncode != 0
