@@ -63,6 +63,18 @@ class LinearEXL3:
         return self.trellis.numel() * 2
 
 
+def linear(ws, key, dev=0):
+    """EXL3 linear `key` of a weight set on device `dev` (reference: models.uc LinearEXL3(ws, key, dev),
+    :49-110): <key>.trellis / .suh / .svh (+ optional .bias), the codebook from the marker tensors
+    <key>.mul1 / <key>.mcg (mutually exclusive), the bitrate from the trellis shape."""
+    mul1, mcg = ws.has(key + ".mul1"), ws.has(key + ".mcg")
+    if mul1 and mcg:
+        raise ValueError("LinearEXL3: %s: both .mul1 and .mcg marker tensors present" % key)
+    bias = ws.gpu16(key + ".bias", dev) if ws.has(key + ".bias") else None
+    return LinearEXL3(ws.gpu(key + ".trellis", dev), ws.gpu(key + ".suh", dev), ws.gpu(key + ".svh", dev), bias=bias,
+                      mul1=mul1, mcg=mcg)
+
+
 def split_n(total, unit, weights):
     """Cut `total` (a multiple of `unit`) into per-rank [start, length] ranges proportional to
     `weights` by largest remainder (reference: src/ucode/ampstein/qwen35_tp.uc:40-72)."""
