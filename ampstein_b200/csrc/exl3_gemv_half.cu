@@ -26,7 +26,7 @@ void exl3_gemv_half_kernel(const __half* __restrict__ xt, const uint16_t* __rest
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half* xs = reinterpret_cast<__half*>(smem_raw);       // [m][GH_XROWS] rotated input rows of the chunk
     float* outs = reinterpret_cast<float*>(smem_raw);       // [m][128] after the k loop (reuses xs)
-    __shared__ uint32_t s_tile[8][TW];
+    __shared__ uint32_t s_tile[8][4][TW];                   // per warp: the four tiles of one pass
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int nb = blockIdx.x, tiles_n = n >> 4;
     const int S = gridDim.y, z = blockIdx.y;                // k split: this CTA takes tile rows [z, z + 1) * (k / 16) / S
@@ -61,17 +61,22 @@ void exl3_gemv_half_kernel(const __half* __restrict__ xt, const uint16_t* __rest
             }
             __syncthreads();
         }
+        // four tiles per pass: staged together, so that their decode chains overlap
+        __syncwarp();
         #pragma unroll
         for (int j = 0; j < 4; ++j)
         {
-            const int kt = kt0 + j;                        // (k is a multiple of 128: the tile count is a multiple of 8)
-            __syncwarp();
-            if (lane < TW) s_tile[warp][lane] = pf[j];
-            pf[j] = fetch(kt + 4);
-            __syncwarp();
+            if (lane < TW) s_tile[warp][j][lane] = pf[j];
+            pf[j] = fetch(kt0 + j + 4);                    // (k is a multiple of 128: the tile count is a multiple of 8)
+        }
+        __syncwarp();
+        #pragma unroll
+        for (int j = 0; j < 4; ++j)
+        {
+            const int kt = kt0 + j;
             float w[8];
             #pragma unroll
-            for (int i = 0; i < 8; ++i) w[i] = __half2float(decode_state<2>(window_rt_half<KA>(s_tile[warp], lane * 8 + i)));
+            for (int i = 0; i < 8; ++i) w[i] = __half2float(decode_state<2>(window_rt_half<KA>(s_tile[warp][j], lane * 8 + i)));
             // position i of the lane: row r0 + (i & 1) + 8 * ((i >> 1) & 1), column ca + 8 * (i >> 2)
             const int xoff = (kt & (GH_XROWS / 16 - 1)) * 16 + r0;
             #pragma unroll
